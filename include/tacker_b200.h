@@ -1,0 +1,200 @@
+/*
+ * tacker_b200.h -- C ABI of libtacker_b200.so: hand-written sm_100a kernels for the
+ * fused tensor-core / CUDA-core hot path of Tacker/Aker.
+ *
+ * The reference has no plugin ABI: its operator boundary is the table
+ *     std::unordered_map<std::string, void*> fmap           (src/main.cu:108-159)
+ * whose values are __global__ symbols that GPTBKernel::executeImpl / MixKernel::executeImpl
+ * launch with cudaLaunchKernel(func, grid, block, void** params, smem, stream)
+ * (src/GPTBKernel.h:99-119, src/MixKernel.h:86-104).  This library replaces every value of
+ * that table that lies on the hot path by a *launcher* with the same calling shape:
+ *
+ *     int launcher(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+ *                  unsigned smem_bytes, void* stream);
+ *
+ * `params[i]` points at the i-th kernel argument exactly as for cudaLaunchKernel (values are
+ * read during the call; they need not outlive it).  The argument lists are the reference
+ * kernels' lists (cited per launcher below) with three documented changes:
+ *   - tzgemm takes `float alpha` after K_GLOBAL (the reference hard-codes 1.1f,
+ *     src/header/tzgemm_header.h:64, and has the parameter commented out);
+ *   - cp takes the packed atom array as a device pointer after `energygrid` (the reference
+ *     reads a 64-entry __constant__ symbol filled by copyatomstoconstbuf,
+ *     src/ori_kernel/cp_kernel.cu:159-179);
+ *   - mriq takes the packed k-space samples as a device pointer after `Qi` (the reference
+ *     reads a 1024-entry __constant__ symbol, src/ori_kernel/mriq_kernel.cu:9).
+ * grid/block: grid[0] persistent CTAs are launched; block[0] is honoured for the CUDA-core
+ * kernels (rounded down to the role's thread granularity) and for the CUDA-core part of a
+ * fused kernel (block[0] - 192 threads); the tensor role always uses 192 threads.  The
+ * virtual-block range [ptb_start_block_pos, ptb_end_block_pos) is honoured exactly, in the
+ * reference's units; ptb_iter_block_step is accepted and ignored (the stride is grid[0]).
+ *
+ * All pointers in `params` are device pointers owned by the caller.  Nothing here allocates
+ * device memory on the launch path, nothing exits the process; every entry point returns a
+ * tk_status.  Launches are asynchronous on `stream`.  The library is thread-compatible: calls
+ * for one device must not race with tk_set_option.
+ * There is no CPU fallback: without a CUDA device the launchers return TK_ERR_CUDA.
+ */
+#ifndef TACKER_B200_H
+#define TACKER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tk_status {
+    TK_OK = 0,
+    TK_ERR_ARGS = -1,        /* wrong parameter count, null pointer, negative size */
+    TK_ERR_ALIGN = -2,       /* pointer or leading dimension not aligned as required */
+    TK_ERR_SHAPE = -3,       /* shape outside the kernel's contract (see each launcher) */
+    TK_ERR_UNKNOWN_KEY = -4, /* tk_lookup / tk_query: no such kernel */
+    TK_ERR_CUDA = -5,        /* a CUDA runtime or driver call failed; see tk_last_error() */
+    TK_ERR_LAUNCH_CONFIG = -6, /* grid/block not usable for this kernel */
+    TK_ERR_DEVICE_WAIT = -7, /* a bounded device-side wait expired; see tk_device_status() */
+    TK_ERR_CAPACITY = -8     /* request exceeds a fixed capacity of the entry point */
+} tk_status;
+
+typedef int (*tk_launch_fn)(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                            unsigned smem_bytes, void* stream);
+
+/* ---- library ------------------------------------------------------------------------ */
+int tk_version(void);
+const char* tk_status_string(int status);
+/* text of the most recent CUDA failure seen by this thread ("" if none) */
+const char* tk_last_error(void);
+/* number of SMs of the current device: replaces the compile-time SM_NUM
+ * (src/header/pets_common.h:4-6) */
+int tk_sm_count(int* sm_count);
+/* tuning / numerics switches (name -> integer):
+ *   "tzgemm_bn"      0 = choose per shape, 128 or 256 = force the super-tile width
+ *   "cp_exact"       1 = IEEE 1/sqrt as the reference computes it (default 0: hardware rsqrt)
+ *   "cp_ppt"         points per thread and work item: 8 (reference granularity), 4 or 2
+ *   "mriq_accurate"  1 = cosf/sinf as the reference calls them (default 0: reduced argument +
+ *                    hardware sin/cos)
+ */
+int tk_set_option(const char* name, int value);
+int tk_get_option(const char* name, int* value);
+/* Reads and clears the device status word that bounded device-side waits write when they
+ * give up (0 = no expiry).  Synchronises the device. */
+int tk_device_status(unsigned* code);
+
+/* ---- the fmap replacement --------------------------------------------------------------
+ * Keys (same strings as the reference table): "gptb_tzgemm", "gptb_stencil", "gptb_cp",
+ * "gptb_mriq", "tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq"; plus "ori_stencil", "ori_cp",
+ * "ori_mriq" for the non-persistent launch shape of the solo kernels. */
+tk_launch_fn tk_lookup(const char* key);
+int tk_num_keys(void);
+const char* tk_key(int index);
+
+typedef struct tk_kernel_info {
+    int threads_tensor;   /* threads of the tensor role (0 for CUDA-core kernels) */
+    int threads_cd_min;   /* thread granularity of the CUDA-core role */
+    int threads_cd_default;
+    int regs_per_thread;  /* from cudaFuncGetAttributes */
+    int static_smem;      /* bytes */
+    int dynamic_smem;     /* bytes requested at launch */
+    int tmem_columns;     /* tensor-memory columns held by one CTA */
+    int max_ctas_per_sm;  /* occupancy at the default block size */
+    int nparams;          /* length of the params array the launcher expects */
+} tk_kernel_info;
+/* Resource figures the scheduler and the fused-kernel generator need; replaces the
+ * register/shared_memory/blocksize fields of src/config/kinfo-*.json and the table in
+ * fusion/code/data.py:25-35. */
+int tk_query(const char* key, tk_kernel_info* info);
+
+/* ---- persistent solo kernels -------------------------------------------------------------
+ * gptb_tzgemm  replaces general_ptb_tzgemm (src/gptb_kernel/tzgemm_kernel.cu:430-449).
+ *   params (17): half* A, half* B, float* C, int M_GLOBAL, int N_GLOBAL, int K_GLOBAL,
+ *                float alpha,
+ *                int grid_dimension_{x,y,z}, int block_dimension_{x,y,z},
+ *                int ptb_start_block_pos, int ptb_iter_block_step, int ptb_end_block_pos,
+ *                int thread_base
+ *   C[M][N] = alpha * A[M][K] * B[N][K]^T, fp16 in, fp32 accumulate and out; one virtual block =
+ *   one 64x64 tile of C, tiles numbered row-major (tzgemm_kernel.cu:247-249).
+ *   Contract: M % 128 == 0, N % 64 == 0, K % 64 == 0, all >= 64 (the reference rounds every
+ *   dimension down to a multiple of 128 before the call, src/tzgemm_kernel.h:30-34);
+ *   A, B, C 16-byte aligned. */
+int tk_launch_gptb_tzgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                          unsigned smem_bytes, void* stream);
+
+/* gptb_stencil  replaces general_ptb_stencil (src/gptb_kernel/stencil_kernel.cu:3-105).
+ *   params (17): float c0, float c1, float* A0, float* Anext, int nx, int ny, int nz,
+ *                6 geometry ints, start, step, end, thread_base
+ *   geometry: grid_dimension_x/y = ceil(nx/64), ceil(ny/4); block_dimension_x/y = 32, 4
+ *   (src/ori_kernel/stencil_kernel.cu:173-178).  One virtual block = 64 x 4 columns, all z. */
+int tk_launch_gptb_stencil(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                           unsigned smem_bytes, void* stream);
+
+/* gptb_cp  replaces g_general_ptb_cp (src/gptb_kernel/cp_kernel.cu:8-96).
+ *   params (14): int numatoms, float gridspacing, float* energygrid, float4* atoms_packed,
+ *                6 geometry ints, start, step, end, thread_base
+ *   atoms_packed[i] = {x, y, (zplane - z)^2, q} (tk_cp_pack_atoms); any numatoms >= 0.
+ *   geometry: grid_dimension_x/y = nx/128, ny/8; block_dimension_x/y = 16, 8; the lattice pitch is
+ *   grid_dimension_x * 128 floats.  Adds to energygrid (+=) like the reference. */
+int tk_launch_gptb_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                      unsigned smem_bytes, void* stream);
+
+/* gptb_mriq  replaces g_general_ptb_mriq (src/gptb_kernel/mriq_kernel.cu:3-70).
+ *   params (18): int numK, int kGlobalIndex (ignored), float* x, float* y, float* z, float* Qr,
+ *                float* Qi, float4* kvals, 6 geometry ints, start, step, end, thread_base
+ *   kvals[k] = {Kx, Ky, Kz, phiR^2 + phiI^2} (tk_mriq_pack_kvalues); all numK samples are summed in
+ *   one launch.  geometry: grid_dimension_x = numX / 256, block_dimension_x = 256. */
+int tk_launch_gptb_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                        unsigned smem_bytes, void* stream);
+
+/* ---- fused kernels: tensor role + CUDA-core role in one persistent CTA ---------------------
+ * Replace stencil_tzgemm_mix / cp_tzgemm_mix / mriq_tzgemm_mix
+ * (src/mix_kernel/tzgemm_stencil.cu:281-299, tzgemm_cp.cu:994-1017, tzgemm_mriq.cu:638-657).
+ * params = CUDA-core kernel's list without thread_base, then tzgemm's list without thread_base,
+ * the order MixKernel::initParams builds (src/MixKernel.h:55-73):
+ *   tzgemm_stencil (32) = stencil 7 + 6 + 3, tzgemm 7 + 6 + 3
+ *   tzgemm_cp      (29) = cp 4 + 6 + 3,      tzgemm 7 + 6 + 3
+ *   tzgemm_mriq    (33) = mriq 8 + 6 + 3,    tzgemm 7 + 6 + 3
+ * block[0] = 192 + CUDA-core threads.  Either range may be empty. */
+int tk_launch_mix_tzgemm_stencil(void** params, int nparams, const unsigned grid[3],
+                                 const unsigned block[3], unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzgemm_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                            unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzgemm_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                              unsigned smem_bytes, void* stream);
+
+/* ---- non-persistent launch shape of the solo kernels ------------------------------------------
+ * ori_stencil (7 params, src/ori_kernel/stencil_kernel.cu:9), ori_cp (4 params with atoms_packed,
+ * src/ori_kernel/cp_kernel.cu:26), ori_mriq (8 params with kvals, src/ori_kernel/mriq_kernel.cu:56):
+ * grid/block are the reference launch geometry, every virtual block is computed. */
+int tk_launch_ori_stencil(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                          unsigned smem_bytes, void* stream);
+int tk_launch_ori_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                     unsigned smem_bytes, void* stream);
+int tk_launch_ori_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                       unsigned smem_bytes, void* stream);
+
+/* ---- input preparation the reference does on the host -------------------------------------------
+ * tk_cp_pack_atoms  replaces copyatomstoconstbuf (src/ori_kernel/cp_kernel.cu:159-179):
+ *   atoms_xyzq[count][4] (device) -> packed[count] = {x, y, (zplane - z)^2, q} (device). */
+int tk_cp_pack_atoms(const float* atoms_xyzq, int count, float zplane, float* packed, void* stream);
+/* tk_mriq_pack_kvalues  replaces ori_ComputePhiMag plus the host loop that fills the kValues
+ * structs (src/ori_kernel/mriq_kernel.cu:47-54, src/header/mriq_header.h:12-17). */
+int tk_mriq_pack_kvalues(const float* kx, const float* ky, const float* kz, const float* phiR,
+                         const float* phiI, int numK, float* kvals, void* stream);
+
+/* ---- LC-layer helpers -----------------------------------------------------------------------------
+ * tk_im2col_f32  replaces im2col_gpu_kernel (src/include/dnn.h:45-92): Caffe layout,
+ *   data_col[(c*kh*kw + i*kw + j)][h_col][w_col], zero padding. */
+int tk_im2col_f32(const float* data_im, int channels, int height, int width, int kernel_h, int kernel_w,
+                  int pad_h, int pad_w, int stride_h, int stride_w, int dilation_h, int dilation_w,
+                  float* data_col, void* stream);
+/* tk_convert_fp32_to_fp16  replaces convertFp32ToFp16 (src/include/dnn.h:94-99); out is __half. */
+int tk_convert_fp32_to_fp16(void* out_half, const float* in, long long n, void* stream);
+/* tk_tzgemm_dims  replaces getTZGEMMGridDim (src/tzgemm_kernel.h:30-48): {M_GLOBAL, N_GLOBAL,
+ *   K_GLOBAL, number of 64x64 tiles}. */
+int tk_tzgemm_dims(int m, int n, int k, int out[4]);
+/* tk_conv_mnk  replaces get_mnk_from_cudnn_args (src/TaskManager.cu:92-123). */
+int tk_conv_mnk(const int cudnn_args[14], int mnk[3]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TACKER_B200_H */

@@ -1,0 +1,542 @@
+/*
+ * tacker_oracle.c -- CPU restatement of the reference's fused-kernel hot path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA kernels are
+ * compared against; it is never linked into, imported by or executed from the
+ * product library.  Only the test-suite, the smoke check and the benchmark's
+ * CPU-baseline leg may load it.
+ *
+ * The reference project (sjtu-epcc/Tacker) ships no host implementation and no
+ * golden vectors for any of these operators; every function below restates the
+ * arithmetic of one reference CUDA kernel (cited per function, paths relative
+ * to the reference project root) in scalar C.  Parity of this restatement is
+ * pinned against fixtures produced by the reference's own kernels compiled for
+ * sm_100 (see ref_shim.cu beside this file and tests/golden/).
+ *
+ * Two arithmetic modes exist for the floating-point operators:
+ *   *_f32  follows the reference kernel's operation order in binary32, with the
+ *          fused multiply-adds nvcc's default -fmad=true produces written out
+ *          explicitly (fmaf), so a device kernel with the same order can match
+ *          bit for bit;
+ *   *_f64  accumulates in binary64 and is the yard-stick for the stated
+ *          relative tolerances.
+ *
+ * Build: gcc -O3 -fopenmp -ffp-contract=off -shared -fPIC (see Makefile).
+ * -ffp-contract=off matters: the host compiler must not invent FMAs.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define TKO_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------------- */
+/* threads                                                                    */
+/* ------------------------------------------------------------------------- */
+TKO_API int tko_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
+TKO_API int tko_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ------------------------------------------------------------------------- */
+/* binary16 <-> binary32 (round to nearest even), bit-level, no _Float16      */
+/* ------------------------------------------------------------------------- */
+static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+static inline uint16_t f32_to_f16_bits(float f) {
+    uint32_t x = f32_bits(f);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t absx = x & 0x7fffffffu;
+    if (absx >= 0x7f800000u) {                       /* inf / nan */
+        return (uint16_t)(sign | 0x7c00u | ((absx > 0x7f800000u) ? 0x200u : 0u));
+    }
+    if (absx >= 0x477ff000u) {                       /* rounds to >= 65520 -> inf */
+        return (uint16_t)(sign | 0x7c00u);
+    }
+    if (absx < 0x38800000u) {                        /* subnormal half or zero */
+        if (absx < 0x33000000u) return (uint16_t)sign;   /* < 2^-25 -> 0 */
+        uint32_t e = absx >> 23;                     /* biased exponent, 102..112 */
+        uint32_t m = (absx & 0x7fffffu) | 0x800000u; /* 24-bit significand */
+        uint32_t shift = 126u - e;                   /* 14..24: bits dropped */
+        uint32_t half = m >> shift;
+        uint32_t rem = m & ((1u << shift) - 1u);
+        uint32_t mid = 1u << (shift - 1u);
+        if (rem > mid || (rem == mid && (half & 1u))) half++;
+        return (uint16_t)(sign | half);
+    }
+    uint32_t e = (absx >> 23) - 112u;                /* rebias 127 -> 15 */
+    uint32_t m = absx & 0x7fffffu;
+    uint32_t half = (e << 10) | (m >> 13);
+    uint32_t rem = m & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (half & 1u))) half++;
+    return (uint16_t)(sign | half);
+}
+
+static inline float f16_bits_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t e = (h >> 10) & 0x1fu;
+    uint32_t m = h & 0x3ffu;
+    if (e == 0) {
+        if (m == 0) return bits_f32(sign);
+        /* subnormal: value = m * 2^-24 */
+        float v = (float)m * 5.9604644775390625e-08f;
+        return sign ? -v : v;
+    }
+    if (e == 31) return bits_f32(sign | 0x7f800000u | (m << 13));
+    return bits_f32(sign | ((e + 112u) << 23) | (m << 13));
+}
+
+TKO_API void tko_f32_to_f16(const float *in, uint16_t *out, int64_t n) {
+    for (int64_t i = 0; i < n; i++) out[i] = f32_to_f16_bits(in[i]);
+}
+
+TKO_API void tko_f16_to_f32(const uint16_t *in, float *out, int64_t n) {
+    for (int64_t i = 0; i < n; i++) out[i] = f16_bits_to_f32(in[i]);
+}
+
+/* ------------------------------------------------------------------------- */
+/* seeded inputs: counter-based SplitMix64, one draw per element              */
+/*   element i of stream (seed) = mix(seed * GOLDEN + i + 1)                  */
+/*   u in [0,1) from the top 24 bits, value = lo + u * (hi - lo) in binary32  */
+/* ------------------------------------------------------------------------- */
+static inline uint64_t splitmix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+static inline float unit_draw(uint64_t seed, uint64_t i) {
+    uint64_t r = splitmix64(seed * 0xD1342543DE82EF95ull + i);
+    return (float)(r >> 40) * (1.0f / 16777216.0f);
+}
+
+TKO_API void tko_fill_uniform_f32(float *out, int64_t n, uint64_t seed, float lo, float hi) {
+    float span = hi - lo;
+    for (int64_t i = 0; i < n; i++) out[i] = lo + unit_draw(seed, (uint64_t)i) * span;
+}
+
+/* uniform draw rounded to binary16; also returns the rounded value as binary32 */
+TKO_API void tko_fill_uniform_f16(uint16_t *out_bits, float *out_f32, int64_t n, uint64_t seed,
+                                  float lo, float hi) {
+    float span = hi - lo;
+    for (int64_t i = 0; i < n; i++) {
+        uint16_t h = f32_to_f16_bits(lo + unit_draw(seed, (uint64_t)i) * span);
+        if (out_bits) out_bits[i] = h;
+        if (out_f32) out_f32[i] = f16_bits_to_f32(h);
+    }
+}
+
+/* standard normal via Box-Muller on two counter draws (for the DNN inputs) */
+TKO_API void tko_fill_normal_f32(float *out, int64_t n, uint64_t seed, float mean, float stddev) {
+    for (int64_t i = 0; i < n; i++) {
+        float u1 = unit_draw(seed, (uint64_t)(2 * i));
+        float u2 = unit_draw(seed, (uint64_t)(2 * i + 1));
+        double r = sqrt(-2.0 * log((double)u1 + 2.98023223876953125e-08));
+        out[i] = mean + stddev * (float)(r * cos(6.283185307179586 * (double)u2));
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* tzgemm: C = alpha * A * B^T on 64x64 output tiles [start,end)              */
+/* reference: src/gptb_kernel/tzgemm_kernel.cu:247-253 (tile p -> row tile    */
+/*   p / (N/64), column tile p % (N/64)), :284-287 (A is M x K row-major, B   */
+/*   is N x K with K contiguous), :375 (scale by alpha), :391 (row-major C);  */
+/*   dimension rounding src/tzgemm_kernel.h:30-48.                            */
+/* The reference has no host GEMM; accumulation here is the plain k-ascending */
+/* binary32 triple loop the headline configuration names as its check.        */
+/* ------------------------------------------------------------------------- */
+TKO_API void tko_tzgemm_dims(int m, int n, int k, int out[4]) {
+    int M = (m < 128) ? 128 : (m / 128) * 128;
+    int N = (n < 128) ? 128 : (n / 128) * 128;
+    int K = (k < 128) ? 128 : (k / 128) * 128;
+    out[0] = M; out[1] = N; out[2] = K;
+    out[3] = ((M / 16) * (N / 16)) / 16;             /* number of 64x64 tiles */
+}
+
+/* A, B given as binary32 values already rounded to binary16 */
+TKO_API void tko_tzgemm_f32(const float *A, const float *B, float *C, int M, int N, int K,
+                            float alpha, int start, int end) {
+    int nt = N / 64;
+    (void)M;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int p = start; p < end; p++) {
+        int r0 = (p / nt) * 64, c0 = (p % nt) * 64;
+        for (int i = r0; i < r0 + 64; i++) {
+            const float *a = A + (size_t)i * K;
+            for (int j = c0; j < c0 + 64; j++) {
+                const float *b = B + (size_t)j * K;
+                float acc = 0.0f;
+                for (int k = 0; k < K; k++) acc += a[k] * b[k];
+                C[(size_t)i * N + j] = alpha * acc;
+            }
+        }
+    }
+}
+
+TKO_API void tko_tzgemm_f64(const float *A, const float *B, double *C, int M, int N, int K,
+                            double alpha, int start, int end) {
+    int nt = N / 64;
+    (void)M;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int p = start; p < end; p++) {
+        int r0 = (p / nt) * 64, c0 = (p % nt) * 64;
+        for (int i = r0; i < r0 + 64; i++) {
+            const float *a = A + (size_t)i * K;
+            for (int j = c0; j < c0 + 64; j++) {
+                const float *b = B + (size_t)j * K;
+                double acc = 0.0;
+                for (int k = 0; k < K; k++) acc += (double)a[k] * (double)b[k];
+                C[(size_t)i * N + j] = alpha * acc;
+            }
+        }
+    }
+}
+
+/* sum_k |a_ik| |b_jk| for a list of sampled (i,j): the scale a relative GEMM
+ * error is measured against (a dot product that cancels to ~0 has no
+ * meaningful element-wise relative error). */
+TKO_API void tko_tzgemm_sampled(const float *A, const float *B, int N, int K, double alpha,
+                                const int32_t *rows, const int32_t *cols, int64_t ns,
+                                double *value, double *magnitude) {
+    (void)N;
+#pragma omp parallel for schedule(static)
+    for (int64_t s = 0; s < ns; s++) {
+        const float *a = A + (size_t)rows[s] * K;
+        const float *b = B + (size_t)cols[s] * K;
+        double acc = 0.0, mag = 0.0;
+        for (int k = 0; k < K; k++) {
+            double t = (double)a[k] * (double)b[k];
+            acc += t;
+            mag += fabs(t);
+        }
+        value[s] = alpha * acc;
+        magnitude[s] = fabs(alpha) * mag;
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* 7-point stencil, one sweep over virtual blocks [start,end)                 */
+/* reference: src/ori_kernel/stencil_kernel.cu:26-27 (interior predicate),    */
+/*   :68-69 and :82-83 (operand order top,bottom,up(j+1),down(j-1),right(i+1),*/
+/*   left(i-1); result sum*c1 - centre*c0), src/gptb_kernel/stencil_kernel.cu */
+/*   :18-19 (block p -> (p % gx, (p / gx) % gy)), :22-24 (64 x 4 columns per  */
+/*   block: 32 threads x 2-way x coarsening by 4 rows),                       */
+/*   src/header/stencil_header.h:5 (index i + nx*(j + ny*k)).                 */
+/* Cells outside the interior are never written.                              */
+/* contract = 0: sum*c1 and centre*c0 are rounded separately (the form the    */
+/*   device kernel of this repository uses, bit-exact against it);            */
+/* contract = 1: fma(sum, c1, -(centre*c0)); contract = 2: fma(-centre, c0,   */
+/*   sum*c1) -- the two contractions nvcc -fmad=true may pick for the         */
+/*   reference kernel.                                                        */
+/* ------------------------------------------------------------------------- */
+#define TKO_STENCIL_BX 64
+#define TKO_STENCIL_BY 4
+
+static inline float stencil_point(const float *A0, int nx, int ny, int i, int j, int k,
+                                  float c0, float c1, int contract) {
+    size_t sxy = (size_t)nx * ny;
+    size_t c = (size_t)i + (size_t)nx * ((size_t)j + (size_t)ny * k);
+    float sum = A0[c + sxy] + A0[c - sxy];
+    sum = sum + A0[c + nx];
+    sum = sum + A0[c - nx];
+    sum = sum + A0[c + 1];
+    sum = sum + A0[c - 1];
+    float ctr = A0[c];
+    if (contract == 1) return fmaf(sum, c1, -(ctr * c0));
+    if (contract == 2) return fmaf(-ctr, c0, sum * c1);
+    return sum * c1 - ctr * c0;
+}
+
+TKO_API void tko_stencil_sweep_f32(float c0, float c1, const float *A0, float *Anext, int nx, int ny,
+                                   int nz, int gx, int gy, int start, int end, int contract) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int p = start; p < end; p++) {
+        int bx = p % gx, by = (p / gx) % gy;
+        for (int k = 1; k < nz - 1; k++)
+            for (int j = by * TKO_STENCIL_BY; j < by * TKO_STENCIL_BY + TKO_STENCIL_BY; j++) {
+                if (j <= 0 || j >= ny - 1) continue;
+                for (int i = bx * TKO_STENCIL_BX; i < bx * TKO_STENCIL_BX + TKO_STENCIL_BX; i++) {
+                    if (i <= 0 || i >= nx - 1) continue;
+                    Anext[(size_t)i + (size_t)nx * ((size_t)j + (size_t)ny * k)] =
+                        stencil_point(A0, nx, ny, i, j, k, c0, c1, contract);
+                }
+            }
+    }
+}
+
+TKO_API void tko_stencil_sweep_f64(double c0, double c1, const float *A0, double *Anext, int nx, int ny,
+                                   int nz, int gx, int gy, int start, int end) {
+    size_t sxy = (size_t)nx * ny;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int p = start; p < end; p++) {
+        int bx = p % gx, by = (p / gx) % gy;
+        for (int k = 1; k < nz - 1; k++)
+            for (int j = by * TKO_STENCIL_BY; j < by * TKO_STENCIL_BY + TKO_STENCIL_BY; j++) {
+                if (j <= 0 || j >= ny - 1) continue;
+                for (int i = bx * TKO_STENCIL_BX; i < bx * TKO_STENCIL_BX + TKO_STENCIL_BX; i++) {
+                    if (i <= 0 || i >= nx - 1) continue;
+                    size_t c = (size_t)i + (size_t)nx * ((size_t)j + (size_t)ny * k);
+                    double s = (double)A0[c + sxy] + A0[c - sxy] + A0[c + nx] + A0[c - nx] + A0[c + 1] +
+                               A0[c - 1];
+                    Anext[c] = s * c1 - (double)A0[c] * c0;
+                }
+            }
+    }
+}
+
+/* `iters` Jacobi sweeps with the two arrays swapped between sweeps; both arrays
+ * carry the caller's boundary values, which no sweep touches.  The result of
+ * the last sweep is in (iters odd ? b : a).  The reference's own "iteration"
+ * argument repeats the same sweep (fusion/kernel/stencil_kernel.cu:1-3); the
+ * headline configuration asks for true ping-pong sweeps. */
+TKO_API void tko_stencil_jacobi_f32(float c0, float c1, float *a, float *b, int nx, int ny, int nz,
+                                    int iters, int contract) {
+    int gx = (nx + TKO_STENCIL_BX - 1) / TKO_STENCIL_BX, gy = (ny + TKO_STENCIL_BY - 1) / TKO_STENCIL_BY;
+    for (int it = 0; it < iters; it++) {
+        const float *src = (it & 1) ? b : a;
+        float *dst = (it & 1) ? a : b;
+        tko_stencil_sweep_f32(c0, c1, src, dst, nx, ny, nz, gx, gy, 0, gx * gy, contract);
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Coulomb potential on a 2-D lattice slice                                   */
+/* reference: src/ori_kernel/cp_kernel.cu:159-179 (host packs {x, y, dz^2, q} */
+/*   with dz = zplane - z), :33-36 (coor = spacing * index), :50-69 (per atom */
+/*   dy, dyz2 = dy*dy + dz2, dx_1 = coorx - x, dx_{u+1} = dx_u + spacing*16,  */
+/*   e_u += q * (1/sqrt(dx_u^2 + dyz2))), :71-78 (lattice += e_u);            */
+/*   src/gptb_kernel/cp_kernel.cu:39-47 (block p -> 128 x 8 lattice patch,    */
+/*   thread (tx,ty) owns x = bx*128 + tx + 16u, u = 0..7).                    */
+/* The reference feeds atoms 64 at a time (MAXATOMS, src/header/cp_header.h:5)*/
+/* with one launch and one `+=` per chunk; `chunk` restates that two-level    */
+/* summation (chunk <= 0 means a single chunk).                               */
+/* ------------------------------------------------------------------------- */
+#define TKO_CP_BX 16
+#define TKO_CP_BY 8
+#define TKO_CP_UNROLL 8
+
+TKO_API void tko_cp_pack_atoms(const float *atoms_xyzq, int count, float zplane, float *packed) {
+    for (int i = 0; i < count; i++) {
+        packed[4 * i] = atoms_xyzq[4 * i];
+        packed[4 * i + 1] = atoms_xyzq[4 * i + 1];
+        float dz = zplane - atoms_xyzq[4 * i + 2];
+        packed[4 * i + 2] = dz * dz;
+        packed[4 * i + 3] = atoms_xyzq[4 * i + 3];
+    }
+}
+
+/* packed = {x, y, dz^2, q}; lattice is ny rows of pitch (gx*128) floats */
+TKO_API void tko_cp_f32(const float *packed, int count, float spacing, float *lattice, int gx, int gy,
+                        int start, int end, int chunk) {
+    if (chunk <= 0) chunk = count > 0 ? count : 1;
+    int pitch = gx * TKO_CP_BX * TKO_CP_UNROLL;
+    float spacing_u = spacing * (float)TKO_CP_BX;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int p = start; p < end; p++) {
+        int bx = p % gx, by = (p / gx) % gy;
+        for (int ty = 0; ty < TKO_CP_BY; ty++)
+            for (int tx = 0; tx < TKO_CP_BX; tx++) {
+                unsigned xi = (unsigned)(bx * TKO_CP_BX * TKO_CP_UNROLL + tx);
+                unsigned yi = (unsigned)(by * TKO_CP_BY + ty);
+                float coory = spacing * (float)yi, coorx = spacing * (float)xi;
+                float *out = lattice + (size_t)pitch * yi + xi;
+                for (int a0 = 0; a0 < count; a0 += chunk) {
+                    int a1 = a0 + chunk < count ? a0 + chunk : count;
+                    float e[TKO_CP_UNROLL] = {0};
+                    for (int a = a0; a < a1; a++) {
+                        const float *at = packed + 4 * (size_t)a;
+                        float dy = coory - at[1];
+                        float dyz2 = fmaf(dy, dy, at[2]);
+                        float dx = coorx - at[0];
+                        for (int u = 0; u < TKO_CP_UNROLL; u++) {
+                            float r2 = fmaf(dx, dx, dyz2);
+                            e[u] = fmaf(at[3], 1.0f / sqrtf(r2), e[u]);
+                            dx = dx + spacing_u;
+                        }
+                    }
+                    for (int u = 0; u < TKO_CP_UNROLL; u++) out[u * TKO_CP_BX] += e[u];
+                }
+            }
+    }
+}
+
+/* binary64 potential and the magnitude sum  sum_a |q_a| / r_a  (error scale) */
+TKO_API void tko_cp_f64(const float *packed, int count, float spacing, double *lattice, double *magnitude,
+                        int gx, int gy, int start, int end) {
+    int pitch = gx * TKO_CP_BX * TKO_CP_UNROLL;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int p = start; p < end; p++) {
+        int bx = p % gx, by = (p / gx) % gy;
+        for (int ty = 0; ty < TKO_CP_BY; ty++)
+            for (int x = 0; x < TKO_CP_BX * TKO_CP_UNROLL; x++) {
+                unsigned xi = (unsigned)(bx * TKO_CP_BX * TKO_CP_UNROLL + x);
+                unsigned yi = (unsigned)(by * TKO_CP_BY + ty);
+                /* lattice coordinates are the reference's binary32 products */
+                double coory = (double)(spacing * (float)yi), coorx = (double)(spacing * (float)xi);
+                double e = 0.0, m = 0.0;
+                for (int a = 0; a < count; a++) {
+                    const float *at = packed + 4 * (size_t)a;
+                    double dy = coory - at[1], dx = coorx - at[0];
+                    double t = 1.0 / sqrt(dx * dx + dy * dy + (double)at[2]);
+                    e += (double)at[3] * t;
+                    m += fabs((double)at[3]) * t;
+                }
+                size_t o = (size_t)pitch * yi + xi;
+                lattice[o] += e;
+                if (magnitude) magnitude[o] += m;
+            }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* MRI-Q: non-uniform Fourier sum                                             */
+/* reference: src/ori_kernel/mriq_kernel.cu:47-54 (phiMag = re*re + im*im),   */
+/*   :88-100 (expArg = 2pi_f32 * (Kx*x + Ky*y + Kz*z); Qr += phiMag*cos,      */
+/*   Qi += phiMag*sin; k ascending, two per trip), src/header/mriq_header.h:3 */
+/*   (binary32 2*pi constant), :12-17 (packed {Kx,Ky,Kz,PhiMag});             */
+/*   src/gptb_kernel/mriq_kernel.cu:18,32 (block p = 256 consecutive voxels). */
+/* nvcc -fmad=true turns the dot product into mul, fma, fma and each          */
+/* accumulation into one fma; that is written out here.  cos/sin of the       */
+/* binary32 argument are taken in binary64 and rounded once (the reference    */
+/* calls the accurate cosf/sinf, <= 2 ulp).                                   */
+/* ------------------------------------------------------------------------- */
+#define TKO_MRIQ_2PI_F32 6.2831853071795864769252867665590058f
+#define TKO_MRIQ_BLOCK 256
+
+TKO_API void tko_mriq_phimag(const float *phiR, const float *phiI, float *phiMag, int numK) {
+    for (int k = 0; k < numK; k++) phiMag[k] = fmaf(phiR[k], phiR[k], phiI[k] * phiI[k]);
+}
+
+/* binary32 has two candidate contractions for re*re + im*im; mode 1 picks the other one */
+TKO_API void tko_mriq_phimag_mode(const float *phiR, const float *phiI, float *phiMag, int numK, int mode) {
+    for (int k = 0; k < numK; k++) {
+        if (mode == 0) phiMag[k] = phiR[k] * phiR[k] + phiI[k] * phiI[k];
+        else if (mode == 1) phiMag[k] = fmaf(phiI[k], phiI[k], phiR[k] * phiR[k]);
+        else phiMag[k] = fmaf(phiR[k], phiR[k], phiI[k] * phiI[k]);
+    }
+}
+
+TKO_API void tko_mriq_pack(const float *kx, const float *ky, const float *kz, const float *phiMag,
+                           float *kvals, int numK) {
+    for (int k = 0; k < numK; k++) {
+        kvals[4 * k] = kx[k]; kvals[4 * k + 1] = ky[k]; kvals[4 * k + 2] = kz[k]; kvals[4 * k + 3] = phiMag[k];
+    }
+}
+
+static inline float mriq_arg(const float *kv, float x, float y, float z) {
+    float t = kv[0] * x;
+    t = fmaf(kv[1], y, t);
+    t = fmaf(kv[2], z, t);
+    return TKO_MRIQ_2PI_F32 * t;
+}
+
+TKO_API void tko_mriq_f32(const float *kvals, int numK, const float *x, const float *y, const float *z,
+                          float *Qr, float *Qi, int start, int end) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int p = start; p < end; p++)
+        for (int t = 0; t < TKO_MRIQ_BLOCK; t++) {
+            int xi = p * TKO_MRIQ_BLOCK + t;
+            float sx = x[xi], sy = y[xi], sz = z[xi], qr = Qr[xi], qi = Qi[xi];
+            for (int k = 0; k < numK; k++) {
+                const float *kv = kvals + 4 * (size_t)k;
+                double a = (double)mriq_arg(kv, sx, sy, sz);
+                qr = fmaf(kv[3], (float)cos(a), qr);
+                qi = fmaf(kv[3], (float)sin(a), qi);
+            }
+            Qr[xi] = qr; Qi[xi] = qi;
+        }
+}
+
+/* binary64 accumulation of the same binary32 arguments, plus sum_k phiMag_k
+ * (the scale of each voxel's sum: |Q| <= sum_k phiMag_k) */
+TKO_API void tko_mriq_f64(const float *kvals, int numK, const float *x, const float *y, const float *z,
+                          double *Qr, double *Qi, int start, int end) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int p = start; p < end; p++)
+        for (int t = 0; t < TKO_MRIQ_BLOCK; t++) {
+            int xi = p * TKO_MRIQ_BLOCK + t;
+            float sx = x[xi], sy = y[xi], sz = z[xi];
+            double qr = Qr[xi], qi = Qi[xi];
+            for (int k = 0; k < numK; k++) {
+                const float *kv = kvals + 4 * (size_t)k;
+                double a = (double)mriq_arg(kv, sx, sy, sz);
+                qr += (double)kv[3] * cos(a);
+                qi += (double)kv[3] * sin(a);
+            }
+            Qr[xi] = qr; Qi[xi] = qi;
+        }
+}
+
+/* ------------------------------------------------------------------------- */
+/* im2col (Caffe layout) and the conv -> GEMM shape rule                      */
+/* reference: src/include/dnn.h:45-92 (one work item per (c_im, h_col, w_col),*/
+/*   column row index (c_im*kh*kw + i*kw + j), zero padding),                 */
+/*   src/TaskManager.cu:92-123 (M = n*h_col*w_col, N = k_out, K = kh*kw*c).   */
+/* ------------------------------------------------------------------------- */
+TKO_API void tko_conv_mnk(const int a[14], int mnk[3]) {
+    int hcol = (a[2] + 2 * a[8] - (a[12] * (a[6] - 1) + 1)) / a[10] + 1;
+    int wcol = (a[3] + 2 * a[9] - (a[13] * (a[7] - 1) + 1)) / a[11] + 1;
+    mnk[0] = a[0] * hcol * wcol;
+    mnk[1] = a[4];
+    mnk[2] = a[6] * a[7] * a[1];
+}
+
+TKO_API void tko_im2col_f32(const float *im, int channels, int height, int width, int kh, int kw, int pad_h,
+                            int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, float *col) {
+    int hcol = (height + 2 * pad_h - (dil_h * (kh - 1) + 1)) / stride_h + 1;
+    int wcol = (width + 2 * pad_w - (dil_w * (kw - 1) + 1)) / stride_w + 1;
+#pragma omp parallel for schedule(static)
+    for (int c = 0; c < channels; c++)
+        for (int i = 0; i < kh; i++)
+            for (int j = 0; j < kw; j++) {
+                float *dst = col + ((size_t)(c * kh * kw + i * kw + j) * hcol) * wcol;
+                for (int h = 0; h < hcol; h++)
+                    for (int w = 0; w < wcol; w++) {
+                        int hi = h * stride_h - pad_h + i * dil_h, wi = w * stride_w - pad_w + j * dil_w;
+                        dst[(size_t)h * wcol + w] = (hi >= 0 && wi >= 0 && hi < height && wi < width)
+                                                        ? im[((size_t)c * height + hi) * width + wi]
+                                                        : 0.0f;
+                    }
+            }
+}
+
+/* ------------------------------------------------------------------------- */
+/* comparison helpers                                                         */
+/* ------------------------------------------------------------------------- */
+TKO_API int64_t tko_count_bit_mismatch_f32(const float *a, const float *b, int64_t n) {
+    int64_t bad = 0;
+    for (int64_t i = 0; i < n; i++) bad += (f32_bits(a[i]) != f32_bits(b[i]));
+    return bad;
+}
+
+/* max over i of |got_i - want_i| / max(scale_i, floor) */
+TKO_API double tko_max_scaled_err(const float *got, const double *want, const double *scale, double floor_,
+                                  int64_t n) {
+    double worst = 0.0;
+    for (int64_t i = 0; i < n; i++) {
+        double s = scale ? scale[i] : fabs(want[i]);
+        if (s < floor_) s = floor_;
+        double e = fabs((double)got[i] - want[i]) / s;
+        if (!(e <= worst)) worst = e;                /* also catches NaN */
+    }
+    return worst;
+}

@@ -1,0 +1,298 @@
+// CUDA-core roles: 7-point stencil, Coulomb direct summation, MRI-Q Fourier sum.
+//
+// Each role is a device function over a group of `nthreads` threads (a whole CTA for the solo
+// persistent kernels, the upper warps of a CTA in a fused kernel).  `tid` is the thread's
+// index inside the role (the reference's `threadIdx.x - thread_base`), `cta`/`ncta` give the
+// persistent-block stride: role instance `cta` handles virtual blocks start+cta, start+cta+ncta,
+// ... below `end`, i.e. the reference's GPTB loop
+// (src/gptb_kernel/stencil_kernel.cu:6-16: block_pos = blockIdx.x + start; += step; >= end -> return).
+// None of the roles needs shared memory or a CTA-wide barrier: neighbours are exchanged with warp
+// shuffles and the small read-only tables (atoms, k-space samples) are fetched with warp-uniform
+// 128-bit loads that the L1 serves as broadcasts.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tk {
+
+// =====================================================================================
+// 7-point stencil (reference: src/ori_kernel/stencil_kernel.cu:9-94,
+//                  src/gptb_kernel/stencil_kernel.cu:3-105)
+//   Anext[i,j,k] = (A0[k+1] + A0[k-1] + A0[j+1] + A0[j-1] + A0[i+1] + A0[i-1]) * c1 - A0[i,j,k] * c0
+//   for 0 < i < nx-1, 0 < j < ny-1, 0 < k < nz-1; other cells are not written.
+// Virtual block p = the 64 x 4 (x, y) column bundle (p % gx, (p / gx) % gy), all z.
+// Here 64 threads (16 x-lanes of one float4 each, 4 rows) cover one z-slab of the bundle and
+// march through it with the three planes of their column in registers; nthreads/64 slabs split
+// the z range.  y neighbours inside a warp (which holds two rows) and x neighbours inside a row
+// come from shuffles, the rest of the halo from global memory.
+// =====================================================================================
+struct StencilArgs {
+    float c0, c1;
+    const float* A0;
+    float* Anext;
+    int nx, ny, nz;
+    int gx, gy;      // virtual grid (64-wide, 4-high bundles)
+    int start, end;  // virtual block range
+};
+
+constexpr int kStencilGroup = 64;  // threads per z-slab
+
+__device__ __forceinline__ float stencil_point(float top, float bot, float up, float down, float right,
+                                               float left, float ctr, float c0, float c1) {
+    float s = __fadd_rn(top, bot);
+    s = __fadd_rn(s, up);
+    s = __fadd_rn(s, down);
+    s = __fadd_rn(s, right);
+    s = __fadd_rn(s, left);
+    // the single contraction nvcc's default -fmad=true applies to `s*c1 - ctr*c0`
+    return __fmaf_rn(s, c1, -__fmul_rn(ctr, c0));
+}
+
+__device__ __forceinline__ float4 stencil_ld4(const float* __restrict__ row, int x, int nx, bool valid,
+                                              bool vec) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (valid) {
+        if (vec) {
+            v = __ldg(reinterpret_cast<const float4*>(row + x));
+        } else {
+            if (x + 0 < nx) v.x = __ldg(row + x + 0);
+            if (x + 1 < nx) v.y = __ldg(row + x + 1);
+            if (x + 2 < nx) v.z = __ldg(row + x + 2);
+            if (x + 3 < nx) v.w = __ldg(row + x + 3);
+        }
+    }
+    return v;
+}
+
+__device__ __forceinline__ void stencil_role(const StencilArgs s, const int tid, const int nthreads,
+                                             const int cta, const int ncta) {
+    const int nslab = nthreads / kStencilGroup;
+    const int slab = tid / kStencilGroup;
+    if (slab >= nslab) return;  // whole warps only: nthreads is a multiple of 32, groups are 2 warps
+    const int t = tid % kStencilGroup;
+    const int lx = t & 15, ly = t >> 4;
+    const bool even_row = (ly & 1) == 0;  // lanes 0-15 of the warp
+    const int nx = s.nx, ny = s.ny, nz = s.nz;
+    if (nz < 3) return;
+    const bool vec = (nx % 4 == 0) && ((reinterpret_cast<uintptr_t>(s.A0) & 15u) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(s.Anext) & 15u) == 0);
+    const size_t plane = static_cast<size_t>(nx) * ny;
+
+    // z range of this slab: interior planes 1 .. nz-2 split evenly
+    const int planes = nz - 2;
+    const int per = (planes + nslab - 1) / nslab;
+    const int k0 = 1 + slab * per;
+    const int k1 = min(k0 + per, nz - 1);
+
+    for (int p = s.start + cta; p < s.end; p += ncta) {
+        const int bx = p % s.gx, by = (p / s.gx) % s.gy;
+        const int x = bx * 64 + 4 * lx;
+        const int j = by * 4 + ly;
+        const bool col_ok = (j < ny) && (x < nx);
+        const int jh = even_row ? j - 1 : j + 1;  // the y neighbour outside this warp's two rows
+        const bool halo_ok = (jh >= 0) && (jh < ny) && (x < nx);
+        const bool row_interior = (j > 0) && (j < ny - 1);
+        const float* __restrict__ col = s.A0 + static_cast<size_t>(nx) * j;
+        const float* __restrict__ colh = s.A0 + static_cast<size_t>(nx) * jh;
+        float* __restrict__ out = s.Anext + static_cast<size_t>(nx) * j;
+        const bool need_left = (lx == 0) && (x > 0) && (j < ny);
+        const bool need_right = (lx == 15) && (x + 4 < nx) && (j < ny);
+
+        if (k0 < k1) {
+            float4 bot = stencil_ld4(col + plane * (k0 - 1), x, nx, col_ok, vec);
+            float4 ctr = stencil_ld4(col + plane * k0, x, nx, col_ok, vec);
+#pragma unroll 2
+            for (int k = k0; k < k1; ++k) {
+                const float4 top = stencil_ld4(col + plane * (k + 1), x, nx, col_ok, vec);
+                const float4 gh = stencil_ld4(colh + plane * k, x, nx, halo_ok, vec);
+                float left = __shfl_up_sync(0xffffffffu, ctr.w, 1, 16);
+                float right = __shfl_down_sync(0xffffffffu, ctr.x, 1, 16);
+                if (need_left) left = __ldg(col + plane * k + x - 1);
+                if (need_right) right = __ldg(col + plane * k + x + 4);
+                float4 other;
+                other.x = __shfl_xor_sync(0xffffffffu, ctr.x, 16);
+                other.y = __shfl_xor_sync(0xffffffffu, ctr.y, 16);
+                other.z = __shfl_xor_sync(0xffffffffu, ctr.z, 16);
+                other.w = __shfl_xor_sync(0xffffffffu, ctr.w, 16);
+                const float4 up = even_row ? other : gh;
+                const float4 down = even_row ? gh : other;
+                if (row_interior && col_ok) {
+                    float4 o;
+                    o.x = stencil_point(top.x, bot.x, up.x, down.x, ctr.y, left, ctr.x, s.c0, s.c1);
+                    o.y = stencil_point(top.y, bot.y, up.y, down.y, ctr.z, ctr.x, ctr.y, s.c0, s.c1);
+                    o.z = stencil_point(top.z, bot.z, up.z, down.z, ctr.w, ctr.y, ctr.z, s.c0, s.c1);
+                    o.w = stencil_point(top.w, bot.w, up.w, down.w, right, ctr.z, ctr.w, s.c0, s.c1);
+                    float* dst = out + plane * k + x;
+                    if (vec && x > 0 && x + 4 < nx) {
+                        *reinterpret_cast<float4*>(dst) = o;
+                    } else {
+                        if (x + 0 > 0 && x + 0 < nx - 1) dst[0] = o.x;
+                        if (x + 1 < nx - 1) dst[1] = o.y;
+                        if (x + 2 < nx - 1) dst[2] = o.z;
+                        if (x + 3 < nx - 1) dst[3] = o.w;
+                    }
+                }
+                bot = ctr;
+                ctr = top;
+            }
+        }
+    }
+}
+
+// =====================================================================================
+// Coulomb potential on a lattice slice (reference: src/ori_kernel/cp_kernel.cu:26-79,
+//   src/gptb_kernel/cp_kernel.cu:8-96).  Virtual block p = lattice patch of 128 x 8 points at
+//   (p % gx, (p / gx) % gy); reference thread (tx, ty) of 16 x 8 owns the eight points
+//   x = 128 bx + tx + 16 u, y = 8 by + ty and adds sum_a q_a / sqrt(dx^2 + dy^2 + dz_a^2) to them,
+//   with dx_1 = x*h - ax and dx_{u+1} = dx_u + 16 h.
+// The reference keeps the atoms in a 64-entry __constant__ array and launches once per 64 atoms;
+// here the packed atoms {x, y, dz^2, q} sit in global memory, any count, and the per-point sum is
+// still folded into the lattice every 64 atoms (same two-level summation order).
+// Work item = one warp = two rows of a patch (PPT = 8 points per thread), or a half / quarter of
+// the u range of those rows (PPT = 4 / 2) for finer load balance; the dx chain always starts at
+// u = 0 so every variant rounds exactly like the reference.
+// EXACT: IEEE 1/sqrt as in the reference (bit-exact against the binary32 restatement);
+// otherwise the hardware reciprocal square root (2 ulp).
+// =====================================================================================
+struct CpArgs {
+    int numatoms;
+    float spacing;
+    float* lattice;
+    const float4* atoms;  // packed {x, y, dz^2, q}
+    int gx, gy;
+    int start, end;
+};
+
+constexpr int kCpChunk = 64;  // atoms per `+=` into the lattice (reference MAXATOMS, src/header/cp_header.h:5)
+
+template <int PPT, bool EXACT>
+__device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int nthreads, const int cta,
+                                        const int ncta) {
+    constexpr int kParts = 8 / PPT;
+    constexpr int kItemsPerBlock = 4 * kParts;
+    const int nwarp = nthreads >> 5, warp = tid >> 5, lane = tid & 31;
+    const int tx = lane & 15, tyl = lane >> 4;
+    const long long nitems = static_cast<long long>(a.end - a.start) * kItemsPerBlock;
+    const int pitch = a.gx * 128;
+    const float spacing_u = a.spacing * 16.0f;
+
+    // items are dealt CTA-first so that a short job spreads over all SMs
+    for (long long item = static_cast<long long>(warp) * ncta + cta; item < nitems;
+         item += static_cast<long long>(nwarp) * ncta) {
+        const int p = a.start + static_cast<int>(item / kItemsPerBlock);
+        const int sub = static_cast<int>(item % kItemsPerBlock);
+        const int wq = sub / kParts, part = sub % kParts;
+        const int bx = p % a.gx, by = (p / a.gx) % a.gy;
+        const unsigned xi = static_cast<unsigned>(bx * 128 + tx);
+        const unsigned yi = static_cast<unsigned>(by * 8 + 2 * wq + tyl);
+        const float coory = a.spacing * static_cast<float>(yi);
+        const float coorx = a.spacing * static_cast<float>(xi);
+        float* out = a.lattice + static_cast<size_t>(pitch) * yi + xi + 16 * PPT * part;
+
+        for (int a0 = 0; a0 < a.numatoms; a0 += kCpChunk) {
+            const int a1 = min(a0 + kCpChunk, a.numatoms);
+            float e[PPT];
+#pragma unroll
+            for (int u = 0; u < PPT; ++u) e[u] = 0.0f;
+#pragma unroll 2
+            for (int i = a0; i < a1; ++i) {
+                const float4 at = __ldg(a.atoms + i);
+                const float dy = __fsub_rn(coory, at.y);
+                const float dyz2 = __fmaf_rn(dy, dy, at.z);
+                float dx = __fsub_rn(coorx, at.x);
+#pragma unroll
+                for (int u = 0; u < PPT * part; ++u) dx = __fadd_rn(dx, spacing_u);
+#pragma unroll
+                for (int u = 0; u < PPT; ++u) {
+                    const float r2 = __fmaf_rn(dx, dx, dyz2);
+                    float inv;
+                    if (EXACT) inv = __fdiv_rn(1.0f, __fsqrt_rn(r2));
+                    else inv = rsqrtf(r2);
+                    e[u] = __fmaf_rn(at.w, inv, e[u]);
+                    dx = __fadd_rn(dx, spacing_u);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < PPT; ++u) out[16 * u] += e[u];
+        }
+    }
+}
+
+// =====================================================================================
+// MRI-Q (reference: src/ori_kernel/mriq_kernel.cu:56-105, src/gptb_kernel/mriq_kernel.cu:3-70)
+//   Qr[x] += sum_k phiMag_k cos(2 pi k.x),  Qi[x] += sum_k phiMag_k sin(2 pi k.x), k ascending,
+//   argument formed in binary32 as 2pi_f32 * fma(Kz, z, fma(Kx, x, Ky * y)).
+// Virtual block p = 256 consecutive voxels ((p % gx) * 256 ...).  The reference streams the
+// samples through a 1024-entry __constant__ array; here they are read from global memory, any
+// count, in one launch.  Work item = one warp = 64 voxels (two per thread).
+// ACCURATE: cosf/sinf as the reference calls them; otherwise the argument is reduced to
+// [-pi, pi] with a two-constant Cody-Waite step and fed to the hardware sin/cos units.
+// =====================================================================================
+struct MriqArgs {
+    int numK;
+    const float4* kvals;  // {Kx, Ky, Kz, PhiMag}
+    const float* x;
+    const float* y;
+    const float* z;
+    float* Qr;
+    float* Qi;
+    int gx;
+    int start, end;
+};
+
+constexpr float kMriq2Pi = 6.2831853071795864769252867665590058f;  // src/header/mriq_header.h:3
+
+__device__ __forceinline__ float mriq_arg(const float4 kv, float x, float y, float z) {
+    const float t = __fmaf_rn(kv.z, z, __fmaf_rn(kv.x, x, __fmul_rn(kv.y, y)));
+    return __fmul_rn(kMriq2Pi, t);
+}
+
+template <bool ACCURATE>
+__device__ __forceinline__ void mriq_sincos(float a, float& s, float& c) {
+    if (ACCURATE) {
+        s = sinf(a);
+        c = cosf(a);
+    } else {
+        // n = nearest integer to a / 2pi via the 1.5 * 2^23 trick (|a / 2pi| << 2^22)
+        const float n = __fsub_rn(__fmaf_rn(a, 0.15915494309189535f, 12582912.0f), 12582912.0f);
+        float r = __fmaf_rn(n, -6.2831854820251465f, a);    // float(2 pi)
+        r = __fmaf_rn(n, 1.7484555314695172e-07f, r);       // float(2 pi) - 2 pi
+        s = __sinf(r);
+        c = __cosf(r);
+    }
+}
+
+template <bool ACCURATE>
+__device__ __forceinline__ void mriq_role(const MriqArgs m, const int tid, const int nthreads,
+                                          const int cta, const int ncta) {
+    constexpr int kItemsPerBlock = 4;
+    const int nwarp = nthreads >> 5, warp = tid >> 5, lane = tid & 31;
+    const long long nitems = static_cast<long long>(m.end - m.start) * kItemsPerBlock;
+    for (long long item = static_cast<long long>(warp) * ncta + cta; item < nitems;
+         item += static_cast<long long>(nwarp) * ncta) {
+        const int p = m.start + static_cast<int>(item / kItemsPerBlock);
+        const int sub = static_cast<int>(item % kItemsPerBlock);
+        const size_t i0 = static_cast<size_t>(p % m.gx) * 256 + sub * 64 + lane;
+        const size_t i1 = i0 + 32;
+        const float x0 = m.x[i0], y0 = m.y[i0], z0 = m.z[i0];
+        const float x1 = m.x[i1], y1 = m.y[i1], z1 = m.z[i1];
+        float qr0 = m.Qr[i0], qi0 = m.Qi[i0], qr1 = m.Qr[i1], qi1 = m.Qi[i1];
+#pragma unroll 4
+        for (int k = 0; k < m.numK; ++k) {
+            const float4 kv = __ldg(m.kvals + k);
+            float s0, c0, s1, c1;
+            mriq_sincos<ACCURATE>(mriq_arg(kv, x0, y0, z0), s0, c0);
+            mriq_sincos<ACCURATE>(mriq_arg(kv, x1, y1, z1), s1, c1);
+            qr0 = __fmaf_rn(kv.w, c0, qr0);
+            qi0 = __fmaf_rn(kv.w, s0, qi0);
+            qr1 = __fmaf_rn(kv.w, c1, qr1);
+            qi1 = __fmaf_rn(kv.w, s1, qi1);
+        }
+        m.Qr[i0] = qr0;
+        m.Qi[i0] = qi0;
+        m.Qr[i1] = qr1;
+        m.Qi[i1] = qi1;
+    }
+}
+
+}  // namespace tk

@@ -1,0 +1,262 @@
+// tzgemm as a persistent, warp-specialised tcgen05 role.
+//
+// Computes C[M][N] (fp32, row-major) = alpha * A[M][K] (fp16, row-major) * B[N][K]^T (fp16, K
+// contiguous) on the 64x64 output tiles whose row-major tile index lies in [start, end) --
+// the operand layout, scaling and virtual-block unit of the reference kernel
+// (src/gptb_kernel/tzgemm_kernel.cu:247-253, 284-287, 375, 391).  The reference computes each
+// 64x64 tile with 4 wmma warps; here one CTA per SM owns 128 x BN super-tiles:
+//
+//   warp 0      TMA producer : A 128x64 and B BNx64 fp16 tiles, 128-byte swizzle, STAGES deep
+//   warp 1      MMA issuer   : one thread issues tcgen05.mma 128xBNx16, accumulators in TMEM,
+//                              two accumulator buffers so tile i+1 starts while tile i drains
+//   warps 2..5  epilogue     : tcgen05.ld -> scale by alpha -> 128-bit global stores, masked per
+//                              64x64 sub-tile so that exactly the tiles in [start, end) are written
+//
+// The six warps synchronise among themselves on named barrier 1 only, so other warps of the
+// same CTA (the CUDA-core role of a fused kernel) are never involved.
+#pragma once
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace tk {
+
+constexpr int kGemmWarps = 6;
+constexpr int kGemmThreads = kGemmWarps * 32;
+constexpr int kGemmBM = 128;
+constexpr int kGemmBK = 64;
+constexpr uint32_t kGemmBarrierId = 1;
+
+struct GemmArgs {
+    float* C;
+    int M, N, K;
+    float alpha;
+    int start, end;    // 64x64 tiles, row-major over (M/64) x (N/64)
+    unsigned* status;  // device status word (bounded-wait expiries)
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+    static constexpr int kABytes = kGemmBM * kGemmBK * 2;
+    static constexpr int kBBytes = BN * kGemmBK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarOffset = STAGES * kStageBytes;
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kTmemSlotOffset = kBarOffset + kNumBars * 8;
+    static constexpr int kAbortOffset = kTmemSlotOffset + 4;
+    // rounded so that whatever follows (a CUDA-core role's scratch) starts 128-byte aligned
+    static constexpr int kBytes = ((kAbortOffset + 4 + 127) / 128) * 128;
+};
+
+// Enumeration of the super-tiles that intersect [start, end); identical in every role.
+template <int BN>
+struct SuperTileWalk {
+    int nt;     // 64-wide tiles per C row
+    int sc;     // super-tile columns
+    int r0;     // first super-tile row touched
+    int ncand;  // candidates = touched super-tile rows x sc
+    int start, end, mt;
+
+    __device__ __forceinline__ void init(const GemmArgs& g) {
+        nt = g.N / 64;
+        mt = g.M / 64;
+        sc = (g.N + BN - 1) / BN;
+        start = g.start < 0 ? 0 : g.start;
+        end = g.end > nt * mt ? nt * mt : g.end;
+        if (start >= end) {
+            ncand = 0;
+            r0 = 0;
+            return;
+        }
+        r0 = (start / nt) / 2;
+        const int r1 = ((end - 1) / nt) / 2;
+        ncand = (r1 - r0 + 1) * sc;
+    }
+
+    // bit (h * (BN/64) + cb) set <=> sub-tile (64-row half h, 64-column block cb) is in range
+    __device__ __forceinline__ uint32_t mask(int cand, int& R, int& Cc) const {
+        R = r0 + cand / sc;
+        Cc = cand % sc;
+        uint32_t m = 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = 2 * R + h;
+            if (row >= mt) continue;
+#pragma unroll
+            for (int cb = 0; cb < BN / 64; ++cb) {
+                const int col = Cc * (BN / 64) + cb;
+                const int id = row * nt + col;
+                if (col < nt && id >= start && id < end) m |= 1u << (h * (BN / 64) + cb);
+            }
+        }
+        return m;
+    }
+};
+
+// `warp` is the warp index inside the role (0..5); all 192 threads of the role must call this.
+template <int BN, int STAGES>
+__device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a,
+                                          const CUtensorMap* __restrict__ tmap_b, const GemmArgs g,
+                                          uint8_t* smem, const int warp, const int lane) {
+    using L = GemmSmem<BN, STAGES>;
+    constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers (256 or 512: powers of two)
+    constexpr uint32_t kIdesc = umma_idesc_f16_f32(kGemmBM, BN);
+
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + L::kBarOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemSlotOffset);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAbortOffset);
+
+    SuperTileWalk<BN> walk;
+    walk.init(g);
+    const int kblocks = g.K / kGemmBK;
+
+    // ---- set-up: barriers (warp 0) and TMEM (warp 1) ----
+    if (warp == 0 && lane == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(tmap_a);
+        tma_prefetch_desc(tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    named_bar_sync(kGemmBarrierId, kGemmThreads);
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int cand = blockIdx.x; cand < walk.ncand && ok; cand += gridDim.x) {
+                int R, Cc;
+                if (walk.mask(cand, R, Cc) == 0u) continue;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_EMPTY);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+                    const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+                    tma_load_2d(a_dst, tmap_a, full_bar(stage), kb * kGemmBK, R * kGemmBM);
+                    tma_load_2d(a_dst + L::kABytes, tmap_b, full_bar(stage), kb * kGemmBK, Cc * BN);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            // tail: the last commits arrive on the empty barriers asynchronously; do not let the
+            // CTA retire (and its shared memory be handed to another CTA) before they have landed
+            for (int s = 0; s < STAGES && ok; ++s) {
+                ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_EMPTY);
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int cand = blockIdx.x; cand < walk.ncand && ok; cand += gridDim.x) {
+                int R, Cc;
+                if (walk.mask(cand, R, Cc) == 0u) continue;
+                const uint32_t as = it & 1u, aphase = (it >> 1) & 1u;
+                ok = mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + as * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait(full_bar(stage), phase, abort_flag, g.status, DEV_TIMEOUT_FULL);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_src = smem_base + stage * L::kStageBytes;
+                    const uint64_t a_desc = umma_smem_desc_sw128(a_src);
+                    const uint64_t b_desc = umma_smem_desc_sw128(a_src + L::kABytes);
+#pragma unroll
+                    for (int k = 0; k < kGemmBK / 16; ++k) {
+                        // 16 fp16 = 32 bytes further along K inside the swizzled row: +2 in units of 16 B
+                        umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));  // frees the stage once these UMMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(as));  // accumulator complete
+                ++it;
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int q = warp & 3;  // the TMEM lane quarter this warp is allowed to read
+        const int h = q >> 1;    // which 64-row half of the super-tile those lanes are
+        uint32_t it = 0;
+        bool ok = true;
+        for (int cand = blockIdx.x; cand < walk.ncand && ok; cand += gridDim.x) {
+            int R, Cc;
+            const uint32_t m = walk.mask(cand, R, Cc);
+            if (m == 0u) continue;
+            const uint32_t as = it & 1u, aphase = (it >> 1) & 1u;
+            ok = mbar_wait(tfull_bar(as), aphase, abort_flag, g.status, DEV_TIMEOUT_TMEM_FULL);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = R * kGemmBM + q * 32 + lane;
+            float* crow = g.C + static_cast<size_t>(row) * g.N + static_cast<size_t>(Cc) * BN;
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                if (((m >> (h * (BN / 64) + (c >> 1))) & 1u) == 0u) continue;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32(t_lane + c * 32, r);
+                tmem_ld_wait();
+                float4* dst = reinterpret_cast<float4*>(crow + c * 32);
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float4 o;
+                    o.x = g.alpha * __uint_as_float(r[4 * v + 0]);
+                    o.y = g.alpha * __uint_as_float(r[4 * v + 1]);
+                    o.z = g.alpha * __uint_as_float(r[4 * v + 2]);
+                    o.w = g.alpha * __uint_as_float(r[4 * v + 3]);
+                    dst[v] = o;
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(as));
+            ++it;
+        }
+    }
+
+    // ---- teardown: every role gets here, also after a bounded wait gave up ----
+    __syncwarp();
+    if (*abort_flag) __nanosleep(1000000u);  // let bulk copies still in flight land before smem is released
+    tc_fence_before_sync();
+    named_bar_sync(kGemmBarrierId, kGemmThreads);
+    tc_fence_after_sync();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace tk

@@ -1,0 +1,921 @@
+// libtacker_b200.so: kernels and C-ABI launchers (see include/tacker_b200.h for the contract).
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "../../include/tacker_b200.h"
+#include "cd_roles.cuh"
+#include "gemm_role.cuh"
+
+#define TK_API extern "C" __attribute__((visibility("default")))
+
+namespace tk {
+
+// -------------------------------------------------------------------------------------------------
+// device status word (bounded waits report here)
+// -------------------------------------------------------------------------------------------------
+__device__ unsigned g_dev_status;
+
+// -------------------------------------------------------------------------------------------------
+// kernels
+// -------------------------------------------------------------------------------------------------
+constexpr int kMaxMixThreads = 704;  // 192 tensor-role threads + up to 512 CUDA-core threads
+
+__device__ __forceinline__ uint8_t* align_smem_1024(uint8_t* p) {
+    const uint32_t a = smem_u32(p);
+    return p + ((1024u - (a & 1023u)) & 1023u);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+tzgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), threadIdx.x >> 5, threadIdx.x & 31);
+}
+
+__global__ void __launch_bounds__(512) stencil_kernel(const StencilArgs s) {
+    stencil_role(s, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+}
+
+template <int PPT, bool EXACT>
+__global__ void __launch_bounds__(512) cp_kernel(const CpArgs a) {
+    cp_role<PPT, EXACT>(a, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+}
+
+template <bool ACCURATE>
+__global__ void __launch_bounds__(512) mriq_kernel(const MriqArgs m) {
+    mriq_role<ACCURATE>(m, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+}
+
+// Fused kernels: warps 0..5 run the tensor role, the remaining warps the CUDA-core role.  The
+// two roles share the SM and nothing else (the reference dispatches on threadIdx.x ranges the
+// same way, src/mix_kernel/tzgemm_stencil.cu:284-298).
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kMaxMixThreads, 1)
+mix_stencil_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmArgs g, const StencilArgs s) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
+    } else {
+        stencil_role(s, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+    }
+}
+
+template <int BN, int STAGES, int PPT>
+__global__ void __launch_bounds__(kMaxMixThreads, 1)
+mix_cp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              const GemmArgs g, const CpArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
+    } else {
+        cp_role<PPT, false>(a, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+    }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kMaxMixThreads, 1)
+mix_mriq_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmArgs g, const MriqArgs m) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
+    } else {
+        mriq_role<false>(m, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+    }
+}
+
+// ---- input preparation ----
+__global__ void cp_pack_kernel(const float4* __restrict__ atoms, int count, float zplane,
+                               float4* __restrict__ packed) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) {
+        float4 a = atoms[i];
+        const float dz = __fsub_rn(zplane, a.z);
+        a.z = __fmul_rn(dz, dz);
+        packed[i] = a;
+    }
+}
+
+__global__ void mriq_pack_kernel(const float* __restrict__ kx, const float* __restrict__ ky,
+                                 const float* __restrict__ kz, const float* __restrict__ phiR,
+                                 const float* __restrict__ phiI, int numK, float4* __restrict__ kvals) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < numK) {
+        const float re = phiR[k], im = phiI[k];
+        // real*real + imag*imag with the contraction nvcc applies to the reference's expression
+        kvals[k] = make_float4(kx[k], ky[k], kz[k], __fmaf_rn(re, re, __fmul_rn(im, im)));
+    }
+}
+
+// ---- LC-layer helpers ----
+// One thread per (channel, output row, output column) as in the reference; consecutive threads
+// take consecutive output columns so every one of the kh*kw stores of a warp is coalesced.
+__global__ void im2col_kernel(long long n, const float* __restrict__ im, int height, int width, int kh,
+                              int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                              int hcol, int wcol, float* __restrict__ col) {
+    for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < n;
+         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int w = static_cast<int>(idx % wcol);
+        const long long hidx = idx / wcol;
+        const int h = static_cast<int>(hidx % hcol);
+        const int c = static_cast<int>(hidx / hcol);
+        const int h0 = h * stride_h - pad_h, w0 = w * stride_w - pad_w;
+        float* dst = col + (static_cast<size_t>(c) * kh * kw * hcol + h) * wcol + w;
+        const float* src = im + static_cast<size_t>(c) * height * width;
+        for (int i = 0; i < kh; ++i)
+            for (int j = 0; j < kw; ++j) {
+                const int hi = h0 + i * dil_h, wi = w0 + j * dil_w;
+                *dst = (hi >= 0 && wi >= 0 && hi < height && wi < width)
+                           ? __ldg(src + static_cast<size_t>(hi) * width + wi)
+                           : 0.0f;
+                dst += static_cast<size_t>(hcol) * wcol;
+            }
+    }
+}
+
+__global__ void cvt_f32_f16_kernel(__half* __restrict__ out, const float* __restrict__ in, long long n) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long n4 = n / 4;
+    const bool vec = ((reinterpret_cast<uintptr_t>(in) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(out) & 7u) == 0);
+    if (vec) {
+        for (long long i = i0; i < n4; i += stride) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(in) + i);
+            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&lo);
+            o.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(out)[i] = o;
+        }
+        for (long long i = n4 * 4 + i0; i < n; i += stride) out[i] = __float2half_rn(in[i]);
+    } else {
+        for (long long i = i0; i < n; i += stride) out[i] = __float2half_rn(in[i]);
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// host side
+// -------------------------------------------------------------------------------------------------
+thread_local std::string t_last_error;
+
+static int cuda_fail(cudaError_t e, const char* what) {
+    t_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return TK_ERR_CUDA;
+}
+#define TK_CUDA(call)                                         \
+    do {                                                      \
+        cudaError_t _e = (call);                              \
+        if (_e != cudaSuccess) return cuda_fail(_e, #call);   \
+    } while (0)
+
+struct Options {
+    int tzgemm_bn = 0;
+    int cp_exact = 0;
+    int cp_ppt = 8;
+    int mriq_accurate = 0;
+};
+static Options g_opt;
+
+struct DeviceInfo {
+    int sm_count = 0;
+    unsigned* status_ptr = nullptr;
+};
+static std::mutex g_mutex;
+static std::map<int, DeviceInfo> g_devices;
+
+static int device_info(DeviceInfo** out) {
+    int dev = 0;
+    TK_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_devices.find(dev);
+    if (it == g_devices.end()) {
+        DeviceInfo d;
+        TK_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        TK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_dev_status));
+        it = g_devices.emplace(dev, d).first;
+    }
+    *out = &it->second;
+    return TK_OK;
+}
+
+// ---- TMA descriptors (driver entry point fetched through the runtime; libcuda is not linked) ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int get_encoder() {
+    if (g_encode) return TK_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    TK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || fn == nullptr) {
+        t_last_error = "cuTensorMapEncodeTiled is not available in this driver";
+        return TK_ERR_CUDA;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return TK_OK;
+}
+
+// fp16 matrix [rows][k], k contiguous; box = 64 (k) x box_rows, 128-byte swizzle
+static int make_tmap(CUtensorMap* m, const void* base, int rows, int k, int box_rows) {
+    int rc = get_encoder();
+    if (rc != TK_OK) return rc;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kGemmBK), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        t_last_error = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(r));
+        return TK_ERR_CUDA;
+    }
+    return TK_OK;
+}
+
+// ---- parameter access ----
+template <typename T>
+static inline T arg(void** params, int i) {
+    T v;
+    std::memcpy(&v, params[i], sizeof(T));
+    return v;
+}
+
+static int check_params(void** params, int nparams, int expected) {
+    if (params == nullptr || nparams != expected) return TK_ERR_ARGS;
+    for (int i = 0; i < nparams; ++i)
+        if (params[i] == nullptr) return TK_ERR_ARGS;
+    return TK_OK;
+}
+
+struct GemmCall {
+    const __half* A;
+    const __half* B;
+    GemmArgs g;
+};
+
+// params[base .. base+6] = A, B, C, M, N, K, alpha; start/end at the given indices
+static int parse_gemm(void** params, int base, int i_start, int i_end, GemmCall* c) {
+    c->A = arg<const __half*>(params, base + 0);
+    c->B = arg<const __half*>(params, base + 1);
+    c->g.C = arg<float*>(params, base + 2);
+    c->g.M = arg<int>(params, base + 3);
+    c->g.N = arg<int>(params, base + 4);
+    c->g.K = arg<int>(params, base + 5);
+    c->g.alpha = arg<float>(params, base + 6);
+    c->g.start = arg<int>(params, i_start);
+    c->g.end = arg<int>(params, i_end);
+    c->g.status = nullptr;
+    const bool empty = c->g.start >= c->g.end;
+    if (c->g.M < 128 || c->g.N < 64 || c->g.K < 64) return TK_ERR_SHAPE;
+    if (c->g.M % 128 || c->g.N % 64 || c->g.K % 64) return TK_ERR_SHAPE;
+    if (!empty && (c->A == nullptr || c->B == nullptr || c->g.C == nullptr)) return TK_ERR_ARGS;
+    if ((reinterpret_cast<uintptr_t>(c->A) & 15u) || (reinterpret_cast<uintptr_t>(c->B) & 15u) ||
+        (reinterpret_cast<uintptr_t>(c->g.C) & 15u))
+        return TK_ERR_ALIGN;
+    if (c->g.start < 0) return TK_ERR_ARGS;
+    return TK_OK;
+}
+
+static int choose_bn(const GemmArgs& g, int ctas) {
+    if (g_opt.tzgemm_bn == 128 || g_opt.tzgemm_bn == 256) return g_opt.tzgemm_bn;
+    if (g.N % 256 != 0) return 128;
+    // time model: waves x per-tile cost; a 128-wide tile re-reads A from shared memory twice as
+    // often per flop, so it is charged a little more than half of a 256-wide one
+    const long long t256 = static_cast<long long>(g.M / 128) * (g.N / 256);
+    const long long t128 = static_cast<long long>(g.M / 128) * (g.N / 128);
+    const double c256 = static_cast<double>((t256 + ctas - 1) / ctas) * 2.0;
+    const double c128 = static_cast<double>((t128 + ctas - 1) / ctas) * 1.15;
+    return c256 <= c128 ? 256 : 128;
+}
+
+constexpr int kStages256 = 4;
+constexpr int kStages128 = 6;
+template <int BN>
+struct StagesFor {
+    static constexpr int value = BN == 256 ? kStages256 : kStages128;
+};
+
+template <int BN>
+static constexpr int gemm_smem_bytes() {
+    return GemmSmem<BN, StagesFor<BN>::value>::kBytes + 1024;  // + slack for the 1024-byte alignment
+}
+
+template <typename KernelT>
+static int enable_smem(KernelT kernel, int bytes) {
+    // idempotent and cheap; done on every call so that it holds for every device that is used
+    TK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    return TK_OK;
+}
+
+static int validate_grid(const unsigned grid[3], const unsigned block[3]) {
+    if (grid == nullptr || block == nullptr) return TK_ERR_ARGS;
+    if (grid[0] == 0 || grid[1] > 1 || grid[2] > 1) return TK_ERR_LAUNCH_CONFIG;
+    if (block[0] == 0 || block[1] > 1 || block[2] > 1) return TK_ERR_LAUNCH_CONFIG;
+    return TK_OK;
+}
+
+// ---- CUDA-core argument parsing (reference argument order) ----
+static int parse_stencil(void** p, int i_start, int i_end, StencilArgs* s) {
+    s->c0 = arg<float>(p, 0);
+    s->c1 = arg<float>(p, 1);
+    s->A0 = arg<const float*>(p, 2);
+    s->Anext = arg<float*>(p, 3);
+    s->nx = arg<int>(p, 4);
+    s->ny = arg<int>(p, 5);
+    s->nz = arg<int>(p, 6);
+    s->gx = arg<int>(p, 7);
+    s->gy = arg<int>(p, 8);
+    const int bdx = arg<int>(p, 10), bdy = arg<int>(p, 11);
+    s->start = arg<int>(p, i_start);
+    s->end = arg<int>(p, i_end);
+    if (s->nx <= 0 || s->ny <= 0 || s->nz <= 0 || s->gx <= 0 || s->gy <= 0 || s->start < 0) return TK_ERR_ARGS;
+    if (bdx != 32 || bdy != 4) return TK_ERR_SHAPE;  // the 64 x 4 bundle is the virtual-block unit
+    if (s->start < s->end && (s->A0 == nullptr || s->Anext == nullptr)) return TK_ERR_ARGS;
+    if ((reinterpret_cast<uintptr_t>(s->A0) & 3u) || (reinterpret_cast<uintptr_t>(s->Anext) & 3u)) return TK_ERR_ALIGN;
+    return TK_OK;
+}
+
+static int parse_cp(void** p, int i_start, int i_end, CpArgs* a) {
+    a->numatoms = arg<int>(p, 0);
+    a->spacing = arg<float>(p, 1);
+    a->lattice = arg<float*>(p, 2);
+    a->atoms = arg<const float4*>(p, 3);
+    a->gx = arg<int>(p, 4);
+    a->gy = arg<int>(p, 5);
+    const int bdx = arg<int>(p, 7), bdy = arg<int>(p, 8);
+    a->start = arg<int>(p, i_start);
+    a->end = arg<int>(p, i_end);
+    if (a->numatoms < 0 || a->gx <= 0 || a->gy <= 0 || a->start < 0) return TK_ERR_ARGS;
+    if (bdx != 16 || bdy != 8) return TK_ERR_SHAPE;
+    if (a->start < a->end && (a->lattice == nullptr || (a->numatoms > 0 && a->atoms == nullptr))) return TK_ERR_ARGS;
+    if ((reinterpret_cast<uintptr_t>(a->atoms) & 15u) || (reinterpret_cast<uintptr_t>(a->lattice) & 3u))
+        return TK_ERR_ALIGN;
+    return TK_OK;
+}
+
+static int parse_mriq(void** p, int i_start, int i_end, MriqArgs* m) {
+    m->numK = arg<int>(p, 0);
+    m->x = arg<const float*>(p, 2);
+    m->y = arg<const float*>(p, 3);
+    m->z = arg<const float*>(p, 4);
+    m->Qr = arg<float*>(p, 5);
+    m->Qi = arg<float*>(p, 6);
+    m->kvals = arg<const float4*>(p, 7);
+    m->gx = arg<int>(p, 8);
+    const int bdx = arg<int>(p, 11);
+    m->start = arg<int>(p, i_start);
+    m->end = arg<int>(p, i_end);
+    if (m->numK < 0 || m->gx <= 0 || m->start < 0) return TK_ERR_ARGS;
+    if (bdx != 256) return TK_ERR_SHAPE;
+    if (m->start < m->end &&
+        (!m->x || !m->y || !m->z || !m->Qr || !m->Qi || (m->numK > 0 && m->kvals == nullptr)))
+        return TK_ERR_ARGS;
+    if (reinterpret_cast<uintptr_t>(m->kvals) & 15u) return TK_ERR_ALIGN;
+    return TK_OK;
+}
+
+static int launch_error(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    return TK_OK;
+}
+
+// ---- solo launches ----
+template <int BN>
+static int launch_tzgemm(const GemmCall& c, unsigned ctas, cudaStream_t st) {
+    constexpr int STAGES = StagesFor<BN>::value;
+    CUtensorMap ta, tb;
+    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
+    if (rc != TK_OK) return rc;
+    rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN);
+    if (rc != TK_OK) return rc;
+    auto kernel = tzgemm_kernel<BN, STAGES>;
+    rc = enable_smem(kernel, gemm_smem_bytes<BN>());
+    if (rc != TK_OK) return rc;
+    kernel<<<ctas, kGemmThreads, gemm_smem_bytes<BN>(), st>>>(ta, tb, c.g);
+    return launch_error("tzgemm_kernel launch");
+}
+
+static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st) {
+    DeviceInfo* d = nullptr;
+    int rc = device_info(&d);
+    if (rc != TK_OK) return rc;
+    c.g.status = d->status_ptr;
+    if (c.g.start >= c.g.end) return TK_OK;
+    // one CTA per SM holds the whole tensor memory; more CTAs than SMs would only queue
+    const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
+    return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_tzgemm<256>(c, ctas, st)
+                                                        : launch_tzgemm<128>(c, ctas, st);
+}
+
+static unsigned cd_threads(unsigned requested, unsigned granule, unsigned cap) {
+    unsigned t = requested > cap ? cap : requested;
+    t = (t / granule) * granule;
+    return t;
+}
+
+static int run_stencil(const StencilArgs& s, unsigned grid0, unsigned block0, cudaStream_t st) {
+    if (s.start >= s.end) return TK_OK;
+    const unsigned threads = cd_threads(block0, kStencilGroup, 512);
+    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    stencil_kernel<<<grid0, threads, 0, st>>>(s);
+    return launch_error("stencil_kernel launch");
+}
+
+static int run_cp(const CpArgs& a, unsigned grid0, unsigned block0, cudaStream_t st) {
+    if (a.start >= a.end) return TK_OK;
+    const unsigned threads = cd_threads(block0, 32, 512);
+    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    const int ppt = g_opt.cp_ppt;
+    if (g_opt.cp_exact) {
+        if (ppt == 2) cp_kernel<2, true><<<grid0, threads, 0, st>>>(a);
+        else if (ppt == 4) cp_kernel<4, true><<<grid0, threads, 0, st>>>(a);
+        else cp_kernel<8, true><<<grid0, threads, 0, st>>>(a);
+    } else {
+        if (ppt == 2) cp_kernel<2, false><<<grid0, threads, 0, st>>>(a);
+        else if (ppt == 4) cp_kernel<4, false><<<grid0, threads, 0, st>>>(a);
+        else cp_kernel<8, false><<<grid0, threads, 0, st>>>(a);
+    }
+    return launch_error("cp_kernel launch");
+}
+
+static int run_mriq(const MriqArgs& m, unsigned grid0, unsigned block0, cudaStream_t st) {
+    if (m.start >= m.end) return TK_OK;
+    const unsigned threads = cd_threads(block0, 32, 512);
+    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    if (g_opt.mriq_accurate) mriq_kernel<true><<<grid0, threads, 0, st>>>(m);
+    else mriq_kernel<false><<<grid0, threads, 0, st>>>(m);
+    return launch_error("mriq_kernel launch");
+}
+
+// ---- fused launches ----
+enum CdKind { CD_STENCIL, CD_CP, CD_MRIQ };
+
+struct CdCall {
+    CdKind kind;
+    StencilArgs s;
+    CpArgs a;
+    MriqArgs m;
+    bool empty() const {
+        switch (kind) {
+            case CD_STENCIL: return s.start >= s.end;
+            case CD_CP: return a.start >= a.end;
+            default: return m.start >= m.end;
+        }
+    }
+};
+
+template <int BN>
+static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsigned threads, cudaStream_t st) {
+    constexpr int STAGES = StagesFor<BN>::value;
+    CUtensorMap ta, tb;
+    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
+    if (rc != TK_OK) return rc;
+    rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN);
+    if (rc != TK_OK) return rc;
+    const int smem = gemm_smem_bytes<BN>();
+    switch (cd.kind) {
+        case CD_STENCIL: {
+            auto k = mix_stencil_kernel<BN, STAGES>;
+            if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+            k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.s);
+            break;
+        }
+        case CD_CP: {
+            if (g_opt.cp_ppt == 2) {
+                auto k = mix_cp_kernel<BN, STAGES, 2>;
+                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
+            } else if (g_opt.cp_ppt == 4) {
+                auto k = mix_cp_kernel<BN, STAGES, 4>;
+                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
+            } else {
+                auto k = mix_cp_kernel<BN, STAGES, 8>;
+                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
+            }
+            break;
+        }
+        default: {
+            auto k = mix_mriq_kernel<BN, STAGES>;
+            if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+            k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.m);
+            break;
+        }
+    }
+    return launch_error("mix kernel launch");
+}
+
+static int run_mix(GemmCall& c, const CdCall& cd, unsigned grid0, unsigned block0, cudaStream_t st) {
+    DeviceInfo* d = nullptr;
+    int rc = device_info(&d);
+    if (rc != TK_OK) return rc;
+    c.g.status = d->status_ptr;
+    const bool gemm_empty = c.g.start >= c.g.end;
+    if (gemm_empty && cd.empty()) return TK_OK;
+    if (block0 <= static_cast<unsigned>(kGemmThreads)) return TK_ERR_LAUNCH_CONFIG;
+    const unsigned granule = cd.kind == CD_STENCIL ? kStencilGroup : 32;
+    const unsigned cdt = cd_threads(block0 - kGemmThreads, granule, kMaxMixThreads - kGemmThreads);
+    if (cdt == 0) return TK_ERR_LAUNCH_CONFIG;
+    if (gemm_empty) {  // nothing for the tensor role: run the CUDA-core kernel alone
+        switch (cd.kind) {
+            case CD_STENCIL: return run_stencil(cd.s, grid0, cdt, st);
+            case CD_CP: return run_cp(cd.a, grid0, cdt, st);
+            default: return run_mriq(cd.m, grid0, cdt, st);
+        }
+    }
+    if (cd.empty()) return run_tzgemm(c, grid0, st);
+    const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
+    const unsigned threads = kGemmThreads + cdt;
+    return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_mix<256>(c, cd, ctas, threads, st)
+                                                        : launch_mix<128>(c, cd, ctas, threads, st);
+}
+
+}  // namespace tk
+
+using namespace tk;
+
+// =================================================================================================
+// C ABI
+// =================================================================================================
+TK_API int tk_version(void) { return 100; }
+
+TK_API const char* tk_status_string(int status) {
+    switch (status) {
+        case TK_OK: return "ok";
+        case TK_ERR_ARGS: return "bad arguments";
+        case TK_ERR_ALIGN: return "misaligned pointer";
+        case TK_ERR_SHAPE: return "shape outside the kernel's contract";
+        case TK_ERR_UNKNOWN_KEY: return "unknown kernel key";
+        case TK_ERR_CUDA: return "CUDA call failed";
+        case TK_ERR_LAUNCH_CONFIG: return "unusable grid/block";
+        case TK_ERR_DEVICE_WAIT: return "a bounded device-side wait expired";
+        case TK_ERR_CAPACITY: return "request exceeds a fixed capacity";
+        default: return "unknown status";
+    }
+}
+
+TK_API const char* tk_last_error(void) { return t_last_error.c_str(); }
+
+TK_API int tk_sm_count(int* sm_count) {
+    if (!sm_count) return TK_ERR_ARGS;
+    DeviceInfo* d = nullptr;
+    int rc = device_info(&d);
+    if (rc != TK_OK) return rc;
+    *sm_count = d->sm_count;
+    return TK_OK;
+}
+
+static int* option_slot(const char* name) {
+    if (!name) return nullptr;
+    if (!std::strcmp(name, "tzgemm_bn")) return &g_opt.tzgemm_bn;
+    if (!std::strcmp(name, "cp_exact")) return &g_opt.cp_exact;
+    if (!std::strcmp(name, "cp_ppt")) return &g_opt.cp_ppt;
+    if (!std::strcmp(name, "mriq_accurate")) return &g_opt.mriq_accurate;
+    return nullptr;
+}
+
+TK_API int tk_set_option(const char* name, int value) {
+    int* slot = option_slot(name);
+    if (!slot) return TK_ERR_UNKNOWN_KEY;
+    if (slot == &g_opt.tzgemm_bn && value != 0 && value != 128 && value != 256) return TK_ERR_ARGS;
+    if (slot == &g_opt.cp_ppt && value != 8 && value != 4 && value != 2) return TK_ERR_ARGS;
+    *slot = value;
+    return TK_OK;
+}
+
+TK_API int tk_get_option(const char* name, int* value) {
+    int* slot = option_slot(name);
+    if (!slot || !value) return slot ? TK_ERR_ARGS : TK_ERR_UNKNOWN_KEY;
+    *value = *slot;
+    return TK_OK;
+}
+
+TK_API int tk_device_status(unsigned* code) {
+    if (!code) return TK_ERR_ARGS;
+    DeviceInfo* d = nullptr;
+    int rc = device_info(&d);
+    if (rc != TK_OK) return rc;
+    TK_CUDA(cudaDeviceSynchronize());
+    TK_CUDA(cudaMemcpy(code, d->status_ptr, sizeof(unsigned), cudaMemcpyDeviceToHost));
+    if (*code != 0u) TK_CUDA(cudaMemset(d->status_ptr, 0, sizeof(unsigned)));
+    return TK_OK;
+}
+
+// ---- solo launchers ----
+TK_API int tk_launch_gptb_tzgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                 unsigned, void* stream) {
+    int rc = check_params(params, nparams, 17);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    GemmCall c;
+    if ((rc = parse_gemm(params, 0, 13, 15, &c)) != TK_OK) return rc;
+    return run_tzgemm(c, grid[0], static_cast<cudaStream_t>(stream));
+}
+
+TK_API int tk_launch_gptb_stencil(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                  unsigned, void* stream) {
+    int rc = check_params(params, nparams, 17);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    StencilArgs s;
+    if ((rc = parse_stencil(params, 13, 15, &s)) != TK_OK) return rc;
+    return run_stencil(s, grid[0], block[0], static_cast<cudaStream_t>(stream));
+}
+
+TK_API int tk_launch_gptb_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                             unsigned, void* stream) {
+    int rc = check_params(params, nparams, 14);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    CpArgs a;
+    if ((rc = parse_cp(params, 10, 12, &a)) != TK_OK) return rc;
+    return run_cp(a, grid[0], block[0], static_cast<cudaStream_t>(stream));
+}
+
+TK_API int tk_launch_gptb_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                               unsigned, void* stream) {
+    int rc = check_params(params, nparams, 18);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    MriqArgs m;
+    if ((rc = parse_mriq(params, 14, 16, &m)) != TK_OK) return rc;
+    return run_mriq(m, grid[0], block[0], static_cast<cudaStream_t>(stream));
+}
+
+// ---- fused launchers: params = CUDA-core list (n_cd + 6 + 3), then tzgemm (7 + 6 + 3) ----
+static int launch_mix_common(CdKind kind, int n_cd, void** params, int nparams, const unsigned grid[3],
+                             const unsigned block[3], void* stream) {
+    const int cd_len = n_cd + 6 + 3;
+    int rc = check_params(params, nparams, cd_len + 16);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    CdCall cd;
+    cd.kind = kind;
+    const int i_start = n_cd + 6, i_end = n_cd + 8;
+    switch (kind) {
+        case CD_STENCIL: rc = parse_stencil(params, i_start, i_end, &cd.s); break;
+        case CD_CP: rc = parse_cp(params, i_start, i_end, &cd.a); break;
+        default: rc = parse_mriq(params, i_start, i_end, &cd.m); break;
+    }
+    if (rc != TK_OK) return rc;
+    GemmCall c;
+    if ((rc = parse_gemm(params, cd_len, cd_len + 13, cd_len + 15, &c)) != TK_OK) return rc;
+    return run_mix(c, cd, grid[0], block[0], static_cast<cudaStream_t>(stream));
+}
+
+TK_API int tk_launch_mix_tzgemm_stencil(void** params, int nparams, const unsigned grid[3],
+                                        const unsigned block[3], unsigned, void* stream) {
+    return launch_mix_common(CD_STENCIL, 7, params, nparams, grid, block, stream);
+}
+
+TK_API int tk_launch_mix_tzgemm_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                   unsigned, void* stream) {
+    return launch_mix_common(CD_CP, 4, params, nparams, grid, block, stream);
+}
+
+TK_API int tk_launch_mix_tzgemm_mriq(void** params, int nparams, const unsigned grid[3],
+                                     const unsigned block[3], unsigned, void* stream) {
+    return launch_mix_common(CD_MRIQ, 8, params, nparams, grid, block, stream);
+}
+
+// ---- non-persistent shape: every virtual block of the reference grid ----
+TK_API int tk_launch_ori_stencil(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                 unsigned, void* stream) {
+    int rc = check_params(params, nparams, 7);
+    if (rc != TK_OK) return rc;
+    if (!grid || !block || grid[0] == 0 || grid[1] == 0) return TK_ERR_LAUNCH_CONFIG;
+    if (block[0] != 32 || block[1] != 4) return TK_ERR_SHAPE;
+    int gx = static_cast<int>(grid[0]), gy = static_cast<int>(grid[1]), one = 1, bx = 32, by = 4;
+    int start = 0, end = gx * gy, step = 0, tb = 0;
+    void* p[17] = {params[0], params[1], params[2], params[3], params[4], params[5], params[6], &gx, &gy,
+                   &one, &bx, &by, &one, &start, &step, &end, &tb};
+    StencilArgs s;
+    if ((rc = parse_stencil(p, 13, 15, &s)) != TK_OK) return rc;
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    return run_stencil(s, static_cast<unsigned>(d->sm_count) * 4u, 256, static_cast<cudaStream_t>(stream));
+}
+
+TK_API int tk_launch_ori_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                            unsigned, void* stream) {
+    int rc = check_params(params, nparams, 4);
+    if (rc != TK_OK) return rc;
+    if (!grid || !block || grid[0] == 0 || grid[1] == 0) return TK_ERR_LAUNCH_CONFIG;
+    if (block[0] != 16 || block[1] != 8) return TK_ERR_SHAPE;
+    int gx = static_cast<int>(grid[0]), gy = static_cast<int>(grid[1]), one = 1, bx = 16, by = 8;
+    int start = 0, end = gx * gy, step = 0, tb = 0;
+    void* p[14] = {params[0], params[1], params[2], params[3], &gx, &gy, &one, &bx, &by, &one,
+                   &start, &step, &end, &tb};
+    CpArgs a;
+    if ((rc = parse_cp(p, 10, 12, &a)) != TK_OK) return rc;
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    return run_cp(a, static_cast<unsigned>(d->sm_count), 256, static_cast<cudaStream_t>(stream));
+}
+
+TK_API int tk_launch_ori_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                              unsigned, void* stream) {
+    int rc = check_params(params, nparams, 8);
+    if (rc != TK_OK) return rc;
+    if (!grid || !block || grid[0] == 0) return TK_ERR_LAUNCH_CONFIG;
+    if (block[0] != 256) return TK_ERR_SHAPE;
+    int gx = static_cast<int>(grid[0]), one = 1, bx = 256;
+    int start = 0, end = gx, step = 0, tb = 0;
+    void* p[18] = {params[0], params[1], params[2], params[3], params[4], params[5], params[6], params[7],
+                   &gx, &one, &one, &bx, &one, &one, &start, &step, &end, &tb};
+    MriqArgs m;
+    if ((rc = parse_mriq(p, 14, 16, &m)) != TK_OK) return rc;
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    return run_mriq(m, static_cast<unsigned>(d->sm_count), 256, static_cast<cudaStream_t>(stream));
+}
+
+// ---- preparation ----
+TK_API int tk_cp_pack_atoms(const float* atoms_xyzq, int count, float zplane, float* packed, void* stream) {
+    if (count < 0) return TK_ERR_ARGS;
+    if (count == 0) return TK_OK;
+    if (!atoms_xyzq || !packed) return TK_ERR_ARGS;
+    if ((reinterpret_cast<uintptr_t>(atoms_xyzq) & 15u) || (reinterpret_cast<uintptr_t>(packed) & 15u))
+        return TK_ERR_ALIGN;
+    cp_pack_kernel<<<(count + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(atoms_xyzq), count, zplane, reinterpret_cast<float4*>(packed));
+    return launch_error("cp_pack_kernel launch");
+}
+
+TK_API int tk_mriq_pack_kvalues(const float* kx, const float* ky, const float* kz, const float* phiR,
+                                const float* phiI, int numK, float* kvals, void* stream) {
+    if (numK < 0) return TK_ERR_ARGS;
+    if (numK == 0) return TK_OK;
+    if (!kx || !ky || !kz || !phiR || !phiI || !kvals) return TK_ERR_ARGS;
+    if (reinterpret_cast<uintptr_t>(kvals) & 15u) return TK_ERR_ALIGN;
+    mriq_pack_kernel<<<(numK + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        kx, ky, kz, phiR, phiI, numK, reinterpret_cast<float4*>(kvals));
+    return launch_error("mriq_pack_kernel launch");
+}
+
+TK_API int tk_im2col_f32(const float* data_im, int channels, int height, int width, int kernel_h, int kernel_w,
+                         int pad_h, int pad_w, int stride_h, int stride_w, int dilation_h, int dilation_w,
+                         float* data_col, void* stream) {
+    if (!data_im || !data_col) return TK_ERR_ARGS;
+    if (channels <= 0 || height <= 0 || width <= 0 || kernel_h <= 0 || kernel_w <= 0 || stride_h <= 0 ||
+        stride_w <= 0 || dilation_h <= 0 || dilation_w <= 0 || pad_h < 0 || pad_w < 0)
+        return TK_ERR_ARGS;
+    const int hcol = (height + 2 * pad_h - (dilation_h * (kernel_h - 1) + 1)) / stride_h + 1;
+    const int wcol = (width + 2 * pad_w - (dilation_w * (kernel_w - 1) + 1)) / stride_w + 1;
+    if (hcol <= 0 || wcol <= 0) return TK_ERR_SHAPE;
+    DeviceInfo* d = nullptr;
+    int rc = device_info(&d);
+    if (rc != TK_OK) return rc;
+    const long long n = static_cast<long long>(channels) * hcol * wcol;
+    long long blocks = (n + 255) / 256;
+    const long long cap = static_cast<long long>(d->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    im2col_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        n, data_im, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, dilation_h, dilation_w,
+        hcol, wcol, data_col);
+    return launch_error("im2col_kernel launch");
+}
+
+TK_API int tk_convert_fp32_to_fp16(void* out_half, const float* in, long long n, void* stream) {
+    if (n < 0) return TK_ERR_ARGS;
+    if (n == 0) return TK_OK;
+    if (!out_half || !in) return TK_ERR_ARGS;
+    DeviceInfo* d = nullptr;
+    int rc = device_info(&d);
+    if (rc != TK_OK) return rc;
+    long long blocks = (n / 4 + 255) / 256 + 1;
+    const long long cap = static_cast<long long>(d->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    cvt_f32_f16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__half*>(out_half), in, n);
+    return launch_error("cvt_f32_f16_kernel launch");
+}
+
+TK_API int tk_tzgemm_dims(int m, int n, int k, int out[4]) {
+    if (!out) return TK_ERR_ARGS;
+    const int M = (m < 128) ? 128 : (m / 128) * 128;
+    const int N = (n < 128) ? 128 : (n / 128) * 128;
+    const int K = (k < 128) ? 128 : (k / 128) * 128;
+    out[0] = M;
+    out[1] = N;
+    out[2] = K;
+    out[3] = (M / 64) * (N / 64);
+    return TK_OK;
+}
+
+TK_API int tk_conv_mnk(const int a[14], int mnk[3]) {
+    if (!a || !mnk) return TK_ERR_ARGS;
+    if (a[10] <= 0 || a[11] <= 0) return TK_ERR_ARGS;
+    const int hcol = (a[2] + 2 * a[8] - (a[12] * (a[6] - 1) + 1)) / a[10] + 1;
+    const int wcol = (a[3] + 2 * a[9] - (a[13] * (a[7] - 1) + 1)) / a[11] + 1;
+    mnk[0] = a[0] * hcol * wcol;
+    mnk[1] = a[4];
+    mnk[2] = a[6] * a[7] * a[1];
+    return TK_OK;
+}
+
+// ---- registry ----
+struct KeyEntry {
+    const char* key;
+    tk_launch_fn fn;
+    int nparams;
+};
+static const KeyEntry kKeys[] = {
+    {"gptb_tzgemm", tk_launch_gptb_tzgemm, 17},       {"gptb_stencil", tk_launch_gptb_stencil, 17},
+    {"gptb_cp", tk_launch_gptb_cp, 14},               {"gptb_mriq", tk_launch_gptb_mriq, 18},
+    {"tzgemm_stencil", tk_launch_mix_tzgemm_stencil, 32}, {"tzgemm_cp", tk_launch_mix_tzgemm_cp, 29},
+    {"tzgemm_mriq", tk_launch_mix_tzgemm_mriq, 33},   {"ori_stencil", tk_launch_ori_stencil, 7},
+    {"ori_cp", tk_launch_ori_cp, 4},                  {"ori_mriq", tk_launch_ori_mriq, 8},
+};
+static constexpr int kNumKeys = sizeof(kKeys) / sizeof(kKeys[0]);
+
+TK_API tk_launch_fn tk_lookup(const char* key) {
+    if (!key) return nullptr;
+    for (int i = 0; i < kNumKeys; ++i)
+        if (!std::strcmp(kKeys[i].key, key)) return kKeys[i].fn;
+    return nullptr;
+}
+
+TK_API int tk_num_keys(void) { return kNumKeys; }
+
+TK_API const char* tk_key(int index) { return (index >= 0 && index < kNumKeys) ? kKeys[index].key : nullptr; }
+
+template <typename KernelT>
+static int fill_info(KernelT kernel, int threads, int dyn_smem, tk_kernel_info* info) {
+    cudaFuncAttributes fa;
+    TK_CUDA(cudaFuncGetAttributes(&fa, kernel));
+    info->regs_per_thread = fa.numRegs;
+    info->static_smem = static_cast<int>(fa.sharedSizeBytes);
+    info->dynamic_smem = dyn_smem;
+    if (dyn_smem > 48 * 1024) {
+        int rc = enable_smem(kernel, dyn_smem);
+        if (rc != TK_OK) return rc;
+    }
+    int nb = 0;
+    TK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, threads, dyn_smem));
+    info->max_ctas_per_sm = nb;
+    return TK_OK;
+}
+
+TK_API int tk_query(const char* key, tk_kernel_info* info) {
+    if (!key || !info) return TK_ERR_ARGS;
+    std::memset(info, 0, sizeof(*info));
+    int idx = -1;
+    for (int i = 0; i < kNumKeys; ++i)
+        if (!std::strcmp(kKeys[i].key, key)) idx = i;
+    if (idx < 0) return TK_ERR_UNKNOWN_KEY;
+    info->nparams = kKeys[idx].nparams;
+    const std::string k(key);
+    const int gsm = gemm_smem_bytes<256>();
+    if (k == "gptb_tzgemm") {
+        info->threads_tensor = kGemmThreads;
+        info->tmem_columns = 512;
+        return fill_info(tzgemm_kernel<256, kStages256>, kGemmThreads, gsm, info);
+    }
+    if (k == "gptb_stencil" || k == "ori_stencil") {
+        info->threads_cd_min = kStencilGroup;
+        info->threads_cd_default = 256;
+        return fill_info(stencil_kernel, 256, 0, info);
+    }
+    if (k == "gptb_cp" || k == "ori_cp") {
+        info->threads_cd_min = 32;
+        info->threads_cd_default = 256;
+        return fill_info(cp_kernel<8, false>, 256, 0, info);
+    }
+    if (k == "gptb_mriq" || k == "ori_mriq") {
+        info->threads_cd_min = 32;
+        info->threads_cd_default = 256;
+        return fill_info(mriq_kernel<false>, 256, 0, info);
+    }
+    info->threads_tensor = kGemmThreads;
+    info->tmem_columns = 512;
+    info->threads_cd_default = 256;
+    if (k == "tzgemm_stencil") {
+        info->threads_cd_min = kStencilGroup;
+        return fill_info(mix_stencil_kernel<256, kStages256>, kGemmThreads + 256, gsm, info);
+    }
+    if (k == "tzgemm_cp") {
+        info->threads_cd_min = 32;
+        return fill_info(mix_cp_kernel<256, kStages256, 8>, kGemmThreads + 256, gsm, info);
+    }
+    info->threads_cd_min = 32;
+    return fill_info(mix_mriq_kernel<256, kStages256>, kGemmThreads + 256, gsm, info);
+}

@@ -1,0 +1,277 @@
+"""Python mirror of the reference's operator surface over the C ABI.
+
+Same roles and argument marshalling as the reference classes, so that a test or a benchmark
+drives the kernels the way the reference runtime does:
+
+  Kernel       src/Kernel.h:12-47         launchGridDim/launchBlockDim/kernelParams/smem
+  GPTBKernel   src/GPTBKernel.h:12-124    solo kernel's params + 6 geometry ints, then at launch
+                                          start, step, end, thread_base
+  MixKernel    src/MixKernel.h:9-115      kernel1 params + {start, step, end} ++ kernel2 params +
+                                          {start, step, end}; kernel1 = CUDA-core, kernel2 = tzgemm
+                                          (src/TaskManager.cu:253-264)
+  fmap         src/main.cu:108-159        key -> launcher (here: tk_lookup)
+
+Device buffers are plain integers (device addresses, e.g. ``tensor.data_ptr()``); nothing in
+this module allocates or touches device memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Sequence
+
+from . import LAUNCH_FN, KernelInfo, TackerError, check, lib
+
+SM_NUM_FALLBACK = 148
+
+
+def sm_count() -> int:
+    n = C.c_int(0)
+    check(lib().tk_sm_count(C.byref(n)), "tk_sm_count")
+    return n.value
+
+
+def set_option(name: str, value: int) -> None:
+    check(lib().tk_set_option(name.encode(), int(value)), f"tk_set_option({name})")
+
+
+def get_option(name: str) -> int:
+    v = C.c_int(0)
+    check(lib().tk_get_option(name.encode(), C.byref(v)), f"tk_get_option({name})")
+    return v.value
+
+
+def device_status() -> int:
+    code = C.c_uint(0)
+    check(lib().tk_device_status(C.byref(code)), "tk_device_status")
+    return code.value
+
+
+def query(key: str) -> KernelInfo:
+    info = KernelInfo()
+    check(lib().tk_query(key.encode(), C.byref(info)), f"tk_query({key})")
+    return info
+
+
+def lookup(key: str):
+    """fmap[key]: returns a callable launcher or raises like the reference's `load kernel {key} failed`."""
+    addr = lib().tk_lookup(key.encode())
+    if not addr:
+        raise KeyError(f"load kernel {{{key}}} failed!")
+    return LAUNCH_FN(addr)
+
+
+def _dim3(v) -> "C.Array":
+    if isinstance(v, int):
+        v = (v, 1, 1)
+    v = tuple(v) + (1,) * (3 - len(v))
+    return (C.c_uint * 3)(*v)
+
+
+def raw_launch(key: str, params: Sequence, grid, block, smem: int = 0, stream: int = 0) -> int:
+    """cudaLaunchKernel-shaped call: `params` are ctypes scalars, passed by address."""
+    fn = lookup(key)
+    arr = (C.c_void_p * len(params))(*[C.cast(C.pointer(p), C.c_void_p) for p in params])
+    return fn(arr, len(params), _dim3(grid), _dim3(block), smem, C.c_void_p(stream))
+
+
+class Kernel:
+    """src/Kernel.h:12-47."""
+
+    kernelName = ""
+    funcKey = ""
+
+    def __init__(self):
+        self.kernelParams: List = []
+        self.launchGridDim = (1, 1, 1)
+        self.launchBlockDim = (1, 1, 1)
+        self.smem = 0
+        self.mixable = 0
+
+    def execute(self, stream: int = 0) -> None:
+        check(raw_launch(self.funcKey, self.kernelParams, self.launchGridDim, self.launchBlockDim, self.smem,
+                         stream), self.funcKey)
+
+    def getArgs(self) -> List[int]:
+        return []
+
+
+def tzgemm_dims(m: int, n: int, k: int):
+    """getTZGEMMGridDim, src/tzgemm_kernel.h:30-48."""
+    out = (C.c_int * 4)()
+    check(lib().tk_tzgemm_dims(m, n, k, out), "tk_tzgemm_dims")
+    return tuple(out)
+
+
+class OriTZGEMMKernel(Kernel):
+    """src/tzgemm_kernel.h:56-147; buffers are the caller's (the reference uses global scratch)."""
+
+    kernelName = "tzgemm"
+    funcKey = "gptb_tzgemm"
+
+    def __init__(self, A: int, B: int, Cm: int, m: int, n: int, k: int, alpha: float = 1.1):
+        super().__init__()
+        self.M_GLOBAL, self.N_GLOBAL, self.K_GLOBAL, self.ori_blks = tzgemm_dims(m, n, k)
+        self.kernelParams = [C.c_void_p(A), C.c_void_p(B), C.c_void_p(Cm), C.c_int(self.M_GLOBAL),
+                             C.c_int(self.N_GLOBAL), C.c_int(self.K_GLOBAL), C.c_float(alpha)]
+        self.launchGridDim = (self.ori_blks, 1, 1)
+        self.launchBlockDim = (192, 1, 1)
+
+
+class OriSTENCILKernel(Kernel):
+    """src/ori_kernel/stencil_kernel.cu:114-204 (launch geometry :173-178)."""
+
+    kernelName = "stencil"
+    funcKey = "ori_stencil"
+
+    def __init__(self, c0: float, c1: float, A0: int, Anext: int, nx: int, ny: int, nz: int):
+        super().__init__()
+        self.kernelParams = [C.c_float(c0), C.c_float(c1), C.c_void_p(A0), C.c_void_p(Anext), C.c_int(nx),
+                             C.c_int(ny), C.c_int(nz)]
+        self.launchGridDim = ((nx + 63) // 64, (ny + 3) // 4, 1)
+        self.launchBlockDim = (32, 4, 1)
+
+
+class OriCPKernel(Kernel):
+    """src/ori_kernel/cp_kernel.cu:271-340; `atoms` = packed {x, y, dz^2, q} device array."""
+
+    kernelName = "cp"
+    funcKey = "ori_cp"
+
+    def __init__(self, numatoms: int, gridspacing: float, energygrid: int, atoms: int, nx: int, ny: int):
+        super().__init__()
+        self.kernelParams = [C.c_int(numatoms), C.c_float(gridspacing), C.c_void_p(energygrid), C.c_void_p(atoms)]
+        self.launchGridDim = (nx // 128, ny // 8, 1)
+        self.launchBlockDim = (16, 8, 1)
+
+
+class OriMRIQKernel(Kernel):
+    """src/ori_kernel/mriq_kernel.cu:107-330; `kvals` = packed {Kx, Ky, Kz, PhiMag} device array."""
+
+    kernelName = "mriq"
+    funcKey = "ori_mriq"
+
+    def __init__(self, numK: int, x: int, y: int, z: int, Qr: int, Qi: int, kvals: int, numX: int):
+        super().__init__()
+        self.kernelParams = [C.c_int(numK), C.c_int(0), C.c_void_p(x), C.c_void_p(y), C.c_void_p(z),
+                             C.c_void_p(Qr), C.c_void_p(Qi), C.c_void_p(kvals)]
+        self.launchGridDim = (numX // 256, 1, 1)
+        self.launchBlockDim = (256, 1, 1)
+
+
+class GPTBKernel(Kernel):
+    """src/GPTBKernel.h:12-124."""
+
+    def __init__(self, kernelName: str, funcKey: str, kernel: Kernel, gridDim, blockDim, ptb_start_block_pos: int,
+                 ptb_end_block_pos: int):
+        super().__init__()
+        lookup(funcKey)  # loadKernel(): fail at construction like the reference
+        self.kernelName = kernelName
+        self.funcKey = funcKey
+        self.kernel_ = kernel
+        self.launchGridDim = tuple(_dim3(gridDim))
+        self.launchBlockDim = tuple(_dim3(blockDim))
+        g, b = _dim3(kernel.launchGridDim), _dim3(kernel.launchBlockDim)
+        self.gptbParams = dict(grid=(g[0], g[1], g[2]), block=(b[0], b[1], b[2]))
+        self.ptb_start_block_pos = ptb_start_block_pos
+        self.ptb_end_block_pos = ptb_end_block_pos
+        self.smem = kernel.smem
+        self.kernelParams = list(kernel.kernelParams) + [C.c_int(v) for v in (g[0], g[1], g[2], b[0], b[1], b[2])]
+
+    @property
+    def ptb_iter_block_step(self) -> int:
+        g = self.launchGridDim
+        return g[0] * g[1] * g[2]
+
+    def execute(self, stream: int = 0) -> None:
+        tail = [C.c_int(self.ptb_start_block_pos), C.c_int(self.ptb_iter_block_step),
+                C.c_int(self.ptb_end_block_pos), C.c_int(0)]
+        check(raw_launch(self.funcKey, self.kernelParams + tail, self.launchGridDim, self.launchBlockDim,
+                         self.smem, stream), self.funcKey)
+
+
+class MixKernel(Kernel):
+    """src/MixKernel.h:9-115."""
+
+    def __init__(self, funcKey: str, kernel1: GPTBKernel, kernel2: GPTBKernel, gridDim, blockDim,
+                 ptb_start_block_pos1: int, ptb_end_block_pos1: int, ptb_start_block_pos2: int,
+                 ptb_end_block_pos2: int):
+        super().__init__()
+        lookup(funcKey)
+        self.kernelName = funcKey
+        self.funcKey = funcKey
+        self.launchGridDim = tuple(_dim3(gridDim))
+        self.launchBlockDim = tuple(_dim3(blockDim))
+        step = self.launchGridDim[0] * self.launchGridDim[1] * self.launchGridDim[2]
+        self.kernelParams = (list(kernel1.kernelParams) +
+                             [C.c_int(ptb_start_block_pos1), C.c_int(step), C.c_int(ptb_end_block_pos1)] +
+                             list(kernel2.kernelParams) +
+                             [C.c_int(ptb_start_block_pos2), C.c_int(step), C.c_int(ptb_end_block_pos2)])
+
+
+# ---- input preparation -------------------------------------------------------------------------
+def cp_pack_atoms(atoms_xyzq: int, count: int, zplane: float, packed: int, stream: int = 0) -> None:
+    check(lib().tk_cp_pack_atoms(C.c_void_p(atoms_xyzq), count, C.c_float(zplane), C.c_void_p(packed),
+                                 C.c_void_p(stream)), "tk_cp_pack_atoms")
+
+
+def mriq_pack_kvalues(kx: int, ky: int, kz: int, phiR: int, phiI: int, numK: int, kvals: int,
+                      stream: int = 0) -> None:
+    check(lib().tk_mriq_pack_kvalues(C.c_void_p(kx), C.c_void_p(ky), C.c_void_p(kz), C.c_void_p(phiR),
+                                     C.c_void_p(phiI), numK, C.c_void_p(kvals), C.c_void_p(stream)),
+          "tk_mriq_pack_kvalues")
+
+
+def im2col_f32(data_im: int, channels: int, height: int, width: int, kh: int, kw: int, pad_h: int, pad_w: int,
+               stride_h: int, stride_w: int, dil_h: int, dil_w: int, data_col: int, stream: int = 0) -> None:
+    check(lib().tk_im2col_f32(C.c_void_p(data_im), channels, height, width, kh, kw, pad_h, pad_w, stride_h,
+                              stride_w, dil_h, dil_w, C.c_void_p(data_col), C.c_void_p(stream)), "tk_im2col_f32")
+
+
+def convert_fp32_to_fp16(out_half: int, inp: int, n: int, stream: int = 0) -> None:
+    check(lib().tk_convert_fp32_to_fp16(C.c_void_p(out_half), C.c_void_p(inp), C.c_longlong(n),
+                                        C.c_void_p(stream)), "tk_convert_fp32_to_fp16")
+
+
+def conv_mnk(args14):
+    a = (C.c_int * 14)(*[int(v) for v in args14])
+    out = (C.c_int * 3)()
+    check(lib().tk_conv_mnk(a, out), "tk_conv_mnk")
+    return tuple(out)
+
+
+# ---- convenience constructors used by tests and the benchmark -------------------------------------
+def gptb_tzgemm(A, B, Cm, m, n, k, alpha=1.1, start=0, end=None, grid=None) -> GPTBKernel:
+    ori = OriTZGEMMKernel(A, B, Cm, m, n, k, alpha)
+    return GPTBKernel("tzgemm", "gptb_tzgemm", ori, (grid or sm_count(), 1, 1), (192, 1, 1), start,
+                      ori.ori_blks if end is None else end)
+
+
+def gptb_stencil(c0, c1, A0, Anext, nx, ny, nz, start=0, end=None, grid=None, block=256) -> GPTBKernel:
+    ori = OriSTENCILKernel(c0, c1, A0, Anext, nx, ny, nz)
+    total = ori.launchGridDim[0] * ori.launchGridDim[1]
+    return GPTBKernel("stencil", "gptb_stencil", ori, (grid or sm_count() * 4, 1, 1), (block, 1, 1), start,
+                      total if end is None else end)
+
+
+def gptb_cp(numatoms, spacing, energygrid, atoms, nx, ny, start=0, end=None, grid=None, block=256) -> GPTBKernel:
+    ori = OriCPKernel(numatoms, spacing, energygrid, atoms, nx, ny)
+    total = ori.launchGridDim[0] * ori.launchGridDim[1]
+    return GPTBKernel("cp", "gptb_cp", ori, (grid or sm_count(), 1, 1), (block, 1, 1), start,
+                      total if end is None else end)
+
+
+def gptb_mriq(numK, x, y, z, Qr, Qi, kvals, numX, start=0, end=None, grid=None, block=256) -> GPTBKernel:
+    ori = OriMRIQKernel(numK, x, y, z, Qr, Qi, kvals, numX)
+    return GPTBKernel("mriq", "gptb_mriq", ori, (grid or sm_count(), 1, 1), (block, 1, 1), start,
+                      ori.launchGridDim[0] if end is None else end)
+
+
+def mix(cd: GPTBKernel, tz: GPTBKernel, cd_threads=256, grid=None, cd_range=None, tz_range=None) -> MixKernel:
+    """tzgemm_<cd> fused kernel as TaskManager builds it (src/TaskManager.cu:253-264)."""
+    cs, ce = cd_range if cd_range is not None else (cd.ptb_start_block_pos, cd.ptb_end_block_pos)
+    ts, te = tz_range if tz_range is not None else (tz.ptb_start_block_pos, tz.ptb_end_block_pos)
+    return MixKernel("tzgemm_" + cd.kernelName, cd, tz, (grid or sm_count(), 1, 1), (192 + cd_threads, 1, 1),
+                     cs, ce, ts, te)
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]
