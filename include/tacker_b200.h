@@ -27,6 +27,10 @@
  * fused kernel (block[0] - 192 threads); the tensor role always uses 192 threads.  The
  * virtual-block range [ptb_start_block_pos, ptb_end_block_pos) is honoured exactly, in the
  * reference's units; ptb_iter_block_step is accepted and ignored (the stride is grid[0]).
+ * A range that runs past the last virtual block is clamped to it: the reference kernels wrap
+ * such indices around (block_pos % grid_dimension_x) and would then update the same outputs from
+ * two CTAs at once; its scheduler never asks for that (src/TaskManager.cu:598 takes the min with
+ * the block count).
  *
  * All pointers in `params` are device pointers owned by the caller.  Nothing here allocates
  * device memory on the launch path, nothing exits the process; every entry point returns a

@@ -322,7 +322,8 @@ TKO_API void tko_stencil_jacobi_f32(float c0, float c1, float *a, float *b, int 
 /* Coulomb potential on a 2-D lattice slice                                   */
 /* reference: src/ori_kernel/cp_kernel.cu:159-179 (host packs {x, y, dz^2, q} */
 /*   with dz = zplane - z), :33-36 (coor = spacing * index), :50-69 (per atom */
-/*   dy, dyz2 = dy*dy + dz2, dx_1 = coorx - x, dx_{u+1} = dx_u + spacing*16,  */
+/*   dy = coory - y, dyz2 = dy*dy + dz2, dx_1 = coorx - x, each contracted by */
+/*   nvcc into fma(spacing, index, -coordinate); dx_{u+1} = dx_u + spacing*16,*/
 /*   e_u += q * (1/sqrt(dx_u^2 + dyz2))), :71-78 (lattice += e_u);            */
 /*   src/gptb_kernel/cp_kernel.cu:39-47 (block p -> 128 x 8 lattice patch,    */
 /*   thread (tx,ty) owns x = bx*128 + tx + 16u, u = 0..7).                    */
@@ -357,16 +358,16 @@ TKO_API void tko_cp_f32(const float *packed, int count, float spacing, float *la
             for (int tx = 0; tx < TKO_CP_BX; tx++) {
                 unsigned xi = (unsigned)(bx * TKO_CP_BX * TKO_CP_UNROLL + tx);
                 unsigned yi = (unsigned)(by * TKO_CP_BY + ty);
-                float coory = spacing * (float)yi, coorx = spacing * (float)xi;
                 float *out = lattice + (size_t)pitch * yi + xi;
                 for (int a0 = 0; a0 < count; a0 += chunk) {
                     int a1 = a0 + chunk < count ? a0 + chunk : count;
                     float e[TKO_CP_UNROLL] = {0};
                     for (int a = a0; a < a1; a++) {
                         const float *at = packed + 4 * (size_t)a;
-                        float dy = coory - at[1];
+                        /* coor - atom with coor = spacing * index: one fma each under -fmad=true */
+                        float dy = fmaf(spacing, (float)yi, -at[1]);
                         float dyz2 = fmaf(dy, dy, at[2]);
-                        float dx = coorx - at[0];
+                        float dx = fmaf(spacing, (float)xi, -at[0]);
                         for (int u = 0; u < TKO_CP_UNROLL; u++) {
                             float r2 = fmaf(dx, dx, dyz2);
                             e[u] = fmaf(at[3], 1.0f / sqrtf(r2), e[u]);
@@ -390,8 +391,7 @@ TKO_API void tko_cp_f64(const float *packed, int count, float spacing, double *l
             for (int x = 0; x < TKO_CP_BX * TKO_CP_UNROLL; x++) {
                 unsigned xi = (unsigned)(bx * TKO_CP_BX * TKO_CP_UNROLL + x);
                 unsigned yi = (unsigned)(by * TKO_CP_BY + ty);
-                /* lattice coordinates are the reference's binary32 products */
-                double coory = (double)(spacing * (float)yi), coorx = (double)(spacing * (float)xi);
+                double coory = (double)spacing * (double)yi, coorx = (double)spacing * (double)xi;
                 double e = 0.0, m = 0.0;
                 for (int a = 0; a < count; a++) {
                     const float *at = packed + 4 * (size_t)a;
@@ -443,18 +443,19 @@ TKO_API void tko_mriq_pack(const float *kx, const float *ky, const float *kz, co
 }
 
 static inline float mriq_arg(const float *kv, float x, float y, float z) {
-    float t = kv[0] * x;
-    t = fmaf(kv[1], y, t);
+    /* (Kx*x + Ky*y) + Kz*z: the first product of each sum is the one that gets fused */
+    float t = fmaf(kv[0], x, kv[1] * y);
     t = fmaf(kv[2], z, t);
     return TKO_MRIQ_2PI_F32 * t;
 }
 
 TKO_API void tko_mriq_f32(const float *kvals, int numK, const float *x, const float *y, const float *z,
-                          float *Qr, float *Qi, int start, int end) {
-#pragma omp parallel for schedule(dynamic, 1)
+                          float *Qr, float *Qi, int gx, int start, int end) {
+    /* sequential over blocks: a range longer than gx wraps and accumulates again, as in the reference */
     for (int p = start; p < end; p++)
+#pragma omp parallel for schedule(static)
         for (int t = 0; t < TKO_MRIQ_BLOCK; t++) {
-            int xi = p * TKO_MRIQ_BLOCK + t;
+            int xi = (p % gx) * TKO_MRIQ_BLOCK + t;
             float sx = x[xi], sy = y[xi], sz = z[xi], qr = Qr[xi], qi = Qi[xi];
             for (int k = 0; k < numK; k++) {
                 const float *kv = kvals + 4 * (size_t)k;
@@ -469,11 +470,11 @@ TKO_API void tko_mriq_f32(const float *kvals, int numK, const float *x, const fl
 /* binary64 accumulation of the same binary32 arguments, plus sum_k phiMag_k
  * (the scale of each voxel's sum: |Q| <= sum_k phiMag_k) */
 TKO_API void tko_mriq_f64(const float *kvals, int numK, const float *x, const float *y, const float *z,
-                          double *Qr, double *Qi, int start, int end) {
-#pragma omp parallel for schedule(dynamic, 1)
+                          double *Qr, double *Qi, int gx, int start, int end) {
     for (int p = start; p < end; p++)
+#pragma omp parallel for schedule(static)
         for (int t = 0; t < TKO_MRIQ_BLOCK; t++) {
-            int xi = p * TKO_MRIQ_BLOCK + t;
+            int xi = (p % gx) * TKO_MRIQ_BLOCK + t;
             float sx = x[xi], sy = y[xi], sz = z[xi];
             double qr = Qr[xi], qi = Qi[xi];
             for (int k = 0; k < numK; k++) {

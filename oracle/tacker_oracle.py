@@ -229,7 +229,7 @@ def mriq_f32(kvals, x, y, z, Qr, Qi, start=0, end=None):
     if end is None:
         end = x.size // 256
     lib().tko_mriq_f32(_p(kvals, _f32p), kvals.shape[0], _p(x, _f32p), _p(y, _f32p), _p(z, _f32p),
-                       _p(Qr, _f32p), _p(Qi, _f32p), start, end)
+                       _p(Qr, _f32p), _p(Qi, _f32p), x.size // 256, start, end)
     return Qr, Qi
 
 
@@ -240,7 +240,7 @@ def mriq_f64(kvals, x, y, z, start=0, end=None):
     Qr = np.zeros(x.size, dtype=np.float64)
     Qi = np.zeros(x.size, dtype=np.float64)
     lib().tko_mriq_f64(_p(kvals, _f32p), kvals.shape[0], _p(x, _f32p), _p(y, _f32p), _p(z, _f32p),
-                       _p(Qr, _f64p), _p(Qi, _f64p), start, end)
+                       _p(Qr, _f64p), _p(Qi, _f64p), x.size // 256, start, end)
     return Qr, Qi
 
 

@@ -1,0 +1,93 @@
+"""ctypes front end of oracle/_ref/libtacker_ref.so: the reference's own CUDA kernels built for sm_100.
+
+TEST INFRASTRUCTURE ONLY (see ref_shim.cu).  Needs a GPU; device buffers are raw addresses.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_ref", "libtacker_ref.so")
+_lib = None
+
+
+def available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(LIB_PATH)
+    return _lib
+
+
+def _vp(x):
+    return C.c_void_p(int(x))
+
+
+def _f32p(a: np.ndarray):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def alpha() -> float:
+    return lib().ref_alpha_times_1000() / 1000.0
+
+
+def tzgemm(A, B, Cm, M, N, K, start, end, grid, stream=0) -> int:
+    return lib().ref_tzgemm(_vp(A), _vp(B), _vp(Cm), M, N, K, start, end, grid, _vp(stream))
+
+
+def stencil(c0, c1, A0, Anext, nx, ny, nz, start, end, grid, stream=0) -> int:
+    return lib().ref_stencil(C.c_float(c0), C.c_float(c1), _vp(A0), _vp(Anext), nx, ny, nz, start, end, grid,
+                             _vp(stream))
+
+
+def cp(packed_host: np.ndarray, spacing, lattice, gx, gy, start, end, grid, stream=0) -> int:
+    packed_host = np.ascontiguousarray(packed_host, dtype=np.float32)
+    return lib().ref_cp(_f32p(packed_host), packed_host.shape[0], C.c_float(spacing), _vp(lattice), gx, gy, start,
+                        end, grid, _vp(stream))
+
+
+def mriq(kvals_host: np.ndarray, x, y, z, Qr, Qi, gx, start, end, grid, stream=0) -> int:
+    kvals_host = np.ascontiguousarray(kvals_host, dtype=np.float32)
+    return lib().ref_mriq(_f32p(kvals_host), kvals_host.shape[0], _vp(x), _vp(y), _vp(z), _vp(Qr), _vp(Qi), gx, start,
+                          end, grid, _vp(stream))
+
+
+def mix_stencil(c0, c1, A0, Anext, nx, ny, nz, cd_start, cd_end, A, B, Cm, M, N, K, tz_start, tz_end, grid,
+                stream=0) -> int:
+    return lib().ref_mix_stencil(C.c_float(c0), C.c_float(c1), _vp(A0), _vp(Anext), nx, ny, nz, cd_start, cd_end,
+                                 _vp(A), _vp(B), _vp(Cm), M, N, K, tz_start, tz_end, grid, _vp(stream))
+
+
+def cp_load_atoms(packed_host: np.ndarray) -> int:
+    packed_host = np.ascontiguousarray(packed_host, dtype=np.float32)
+    return lib().ref_cp_load_atoms(_f32p(packed_host), packed_host.shape[0])
+
+
+def cp_launch(numatoms, spacing, lattice, gx, gy, start, end, grid, stream=0) -> int:
+    return lib().ref_cp_launch(numatoms, C.c_float(spacing), _vp(lattice), gx, gy, start, end, grid, _vp(stream))
+
+
+def mix_cp(numatoms, spacing, lattice, gx, gy, cd_start, cd_end, A, B, Cm, M, N, K, tz_start, tz_end, grid,
+           stream=0) -> int:
+    return lib().ref_mix_cp(numatoms, C.c_float(spacing), _vp(lattice), gx, gy, cd_start, cd_end, _vp(A), _vp(B),
+                            _vp(Cm), M, N, K, tz_start, tz_end, grid, _vp(stream))
+
+
+def mriq_load_kvals(kvals_host: np.ndarray) -> int:
+    kvals_host = np.ascontiguousarray(kvals_host, dtype=np.float32)
+    return lib().ref_mriq_load_kvals(_f32p(kvals_host), kvals_host.shape[0])
+
+
+def mriq_launch(numK, x, y, z, Qr, Qi, gx, start, end, grid, stream=0) -> int:
+    return lib().ref_mriq_launch(numK, _vp(x), _vp(y), _vp(z), _vp(Qr), _vp(Qi), gx, start, end, grid, _vp(stream))
+
+
+def mix_mriq(numK, x, y, z, Qr, Qi, gx, cd_start, cd_end, A, B, Cm, M, N, K, tz_start, tz_end, grid, stream=0) -> int:
+    return lib().ref_mix_mriq(numK, _vp(x), _vp(y), _vp(z), _vp(Qr), _vp(Qi), gx, cd_start, cd_end, _vp(A), _vp(B),
+                              _vp(Cm), M, N, K, tz_start, tz_end, grid, _vp(stream))

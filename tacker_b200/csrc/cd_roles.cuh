@@ -185,8 +185,7 @@ __device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int
         const int bx = p % a.gx, by = (p / a.gx) % a.gy;
         const unsigned xi = static_cast<unsigned>(bx * 128 + tx);
         const unsigned yi = static_cast<unsigned>(by * 8 + 2 * wq + tyl);
-        const float coory = a.spacing * static_cast<float>(yi);
-        const float coorx = a.spacing * static_cast<float>(xi);
+        const float yf = static_cast<float>(yi), xf = static_cast<float>(xi);
         float* out = a.lattice + static_cast<size_t>(pitch) * yi + xi + 16 * PPT * part;
 
         for (int a0 = 0; a0 < a.numatoms; a0 += kCpChunk) {
@@ -197,9 +196,10 @@ __device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int
 #pragma unroll 2
             for (int i = a0; i < a1; ++i) {
                 const float4 at = __ldg(a.atoms + i);
-                const float dy = __fsub_rn(coory, at.y);
+                // spacing * index - coordinate as the single fma nvcc makes of the reference's expression
+                const float dy = __fmaf_rn(a.spacing, yf, -at.y);
                 const float dyz2 = __fmaf_rn(dy, dy, at.z);
-                float dx = __fsub_rn(coorx, at.x);
+                float dx = __fmaf_rn(a.spacing, xf, -at.x);
 #pragma unroll
                 for (int u = 0; u < PPT * part; ++u) dx = __fadd_rn(dx, spacing_u);
 #pragma unroll

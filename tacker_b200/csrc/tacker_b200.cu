@@ -346,6 +346,7 @@ static int parse_stencil(void** p, int i_start, int i_end, StencilArgs* s) {
     s->end = arg<int>(p, i_end);
     if (s->nx <= 0 || s->ny <= 0 || s->nz <= 0 || s->gx <= 0 || s->gy <= 0 || s->start < 0) return TK_ERR_ARGS;
     if (bdx != 32 || bdy != 4) return TK_ERR_SHAPE;  // the 64 x 4 bundle is the virtual-block unit
+    if (s->end > s->gx * s->gy) s->end = s->gx * s->gy;  // see the note on ranges in the header
     if (s->start < s->end && (s->A0 == nullptr || s->Anext == nullptr)) return TK_ERR_ARGS;
     if ((reinterpret_cast<uintptr_t>(s->A0) & 3u) || (reinterpret_cast<uintptr_t>(s->Anext) & 3u)) return TK_ERR_ALIGN;
     return TK_OK;
@@ -363,6 +364,7 @@ static int parse_cp(void** p, int i_start, int i_end, CpArgs* a) {
     a->end = arg<int>(p, i_end);
     if (a->numatoms < 0 || a->gx <= 0 || a->gy <= 0 || a->start < 0) return TK_ERR_ARGS;
     if (bdx != 16 || bdy != 8) return TK_ERR_SHAPE;
+    if (a->end > a->gx * a->gy) a->end = a->gx * a->gy;
     if (a->start < a->end && (a->lattice == nullptr || (a->numatoms > 0 && a->atoms == nullptr))) return TK_ERR_ARGS;
     if ((reinterpret_cast<uintptr_t>(a->atoms) & 15u) || (reinterpret_cast<uintptr_t>(a->lattice) & 3u))
         return TK_ERR_ALIGN;
@@ -383,6 +385,7 @@ static int parse_mriq(void** p, int i_start, int i_end, MriqArgs* m) {
     m->end = arg<int>(p, i_end);
     if (m->numK < 0 || m->gx <= 0 || m->start < 0) return TK_ERR_ARGS;
     if (bdx != 256) return TK_ERR_SHAPE;
+    if (m->end > m->gx) m->end = m->gx;
     if (m->start < m->end &&
         (!m->x || !m->y || !m->z || !m->Qr || !m->Qi || (m->numK > 0 && m->kvals == nullptr)))
         return TK_ERR_ARGS;

@@ -108,9 +108,13 @@ class OriTZGEMMKernel(Kernel):
     kernelName = "tzgemm"
     funcKey = "gptb_tzgemm"
 
-    def __init__(self, A: int, B: int, Cm: int, m: int, n: int, k: int, alpha: float = 1.1):
+    def __init__(self, A: int, B: int, Cm: int, m: int, n: int, k: int, alpha: float = 1.1,
+                 round_dims: bool = True):
         super().__init__()
-        self.M_GLOBAL, self.N_GLOBAL, self.K_GLOBAL, self.ori_blks = tzgemm_dims(m, n, k)
+        if round_dims:   # the reference always rounds (initParams, src/tzgemm_kernel.h:79-86)
+            self.M_GLOBAL, self.N_GLOBAL, self.K_GLOBAL, self.ori_blks = tzgemm_dims(m, n, k)
+        else:            # the kernel itself also takes N and K in multiples of 64
+            self.M_GLOBAL, self.N_GLOBAL, self.K_GLOBAL, self.ori_blks = m, n, k, (m // 64) * (n // 64)
         self.kernelParams = [C.c_void_p(A), C.c_void_p(B), C.c_void_p(Cm), C.c_int(self.M_GLOBAL),
                              C.c_int(self.N_GLOBAL), C.c_int(self.K_GLOBAL), C.c_float(alpha)]
         self.launchGridDim = (self.ori_blks, 1, 1)
@@ -240,8 +244,8 @@ def conv_mnk(args14):
 
 
 # ---- convenience constructors used by tests and the benchmark -------------------------------------
-def gptb_tzgemm(A, B, Cm, m, n, k, alpha=1.1, start=0, end=None, grid=None) -> GPTBKernel:
-    ori = OriTZGEMMKernel(A, B, Cm, m, n, k, alpha)
+def gptb_tzgemm(A, B, Cm, m, n, k, alpha=1.1, start=0, end=None, grid=None, round_dims=True) -> GPTBKernel:
+    ori = OriTZGEMMKernel(A, B, Cm, m, n, k, alpha, round_dims)
     return GPTBKernel("tzgemm", "gptb_tzgemm", ori, (grid or sm_count(), 1, 1), (192, 1, 1), start,
                       ori.ori_blks if end is None else end)
 
