@@ -198,6 +198,33 @@ int tk_tzgemm_dims(int m, int n, int k, int out[4]);
 /* tk_conv_mnk  replaces get_mnk_from_cudnn_args (src/TaskManager.cu:92-123). */
 int tk_conv_mnk(const int cudnn_args[14], int mnk[3]);
 
+/* ---- whole operators (device buffers; the caller supplies the scratch) ---------------------------
+ * tk_mriq_compute = tk_mriq_pack_kvalues + every virtual block of gptb_mriq: the sequence
+ *   OriMRIQKernel::initParams + executeImpl run (src/ori_kernel/mriq_kernel.cu:125-330).
+ *   kvals_scratch: numK * 16 bytes of device memory, 16-byte aligned.  numX % 256 == 0. */
+int tk_mriq_compute(const float* kx, const float* ky, const float* kz, const float* phiR, const float* phiI,
+                    int numK, const float* x, const float* y, const float* z, float* Qr, float* Qi, int numX,
+                    float* kvals_scratch, void* stream);
+/* tk_coulomb_compute = tk_cp_pack_atoms + every virtual block of gptb_cp (OriCPKernel::initParams +
+ *   executeImpl, src/ori_kernel/cp_kernel.cu:271-340, all atoms in one call).
+ *   packed_scratch: numatoms * 16 bytes of device memory, 16-byte aligned.  nx % 128 == 0, ny % 8 == 0. */
+int tk_coulomb_compute(const float* atoms_xyzq, int numatoms, float zplane, float gridspacing, float* energygrid,
+                       int nx, int ny, float* packed_scratch, void* stream);
+
+/* ---- host-buffer pair (what an end-to-end caller times) ---------------------------------------------
+ * C = alpha * A * B^T together with `sweeps` ping-pong stencil sweeps of A0, as `sweeps` fused launches
+ * (sweep i co-runs with the i-th slice of the GEMM's tiles).  All five buffers are HOST memory (pinned
+ * for full copy speed); inputs are copied to the device workspace and results copied back on `stream`;
+ * the call returns once everything is enqueued.  Mirrors what the reference's harness does around a
+ * fused launch: cudaMemcpy of the inputs in initParams (src/ori_kernel/stencil_kernel.cu:143-160), the
+ * launch (src/TaskManager.cu:285), and the copy-back its test mains do (fusion/code/cp_code.py:99-121).
+ * workspace: device memory of at least tk_pair_tzgemm_stencil_workspace() bytes, 256-byte aligned. */
+int tk_pair_tzgemm_stencil_workspace(int M, int N, int K, int nx, int ny, int nz, size_t* bytes);
+int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, float* C_host, int M, int N, int K,
+                                float alpha, float c0, float c1, const float* A0_host, float* Aout_host, int nx,
+                                int ny, int nz, int sweeps, int cd_threads, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -922,3 +922,128 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
     info->threads_cd_min = 32;
     return fill_info(mix_mriq_kernel<256, kStages256>, kGemmThreads + 256, gsm, info);
 }
+
+// =================================================================================================
+// whole-operator entry points (device buffers; scratch supplied by the caller)
+// =================================================================================================
+TK_API int tk_mriq_compute(const float* kx, const float* ky, const float* kz, const float* phiR, const float* phiI,
+                           int numK, const float* x, const float* y, const float* z, float* Qr, float* Qi, int numX,
+                           float* kvals_scratch, void* stream) {
+    if (numK < 0 || numX < 0 || numX % 256) return numX % 256 ? TK_ERR_SHAPE : TK_ERR_ARGS;
+    if (numX == 0) return TK_OK;
+    if (numK > 0 && kvals_scratch == nullptr) return TK_ERR_ARGS;
+    int rc = tk_mriq_pack_kvalues(kx, ky, kz, phiR, phiI, numK, kvals_scratch, stream);
+    if (rc != TK_OK) return rc;
+    MriqArgs m;
+    m.numK = numK;
+    m.kvals = reinterpret_cast<const float4*>(kvals_scratch);
+    m.x = x;
+    m.y = y;
+    m.z = z;
+    m.Qr = Qr;
+    m.Qi = Qi;
+    m.gx = numX / 256;
+    m.start = 0;
+    m.end = m.gx;
+    if (!x || !y || !z || !Qr || !Qi) return TK_ERR_ARGS;
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    return run_mriq(m, static_cast<unsigned>(d->sm_count), 256, static_cast<cudaStream_t>(stream));
+}
+
+TK_API int tk_coulomb_compute(const float* atoms_xyzq, int numatoms, float zplane, float gridspacing, float* energygrid,
+                              int nx, int ny, float* packed_scratch, void* stream) {
+    if (numatoms < 0 || nx <= 0 || ny <= 0) return TK_ERR_ARGS;
+    if (nx % 128 || ny % 8) return TK_ERR_SHAPE;
+    if (!energygrid || (numatoms > 0 && (!atoms_xyzq || !packed_scratch))) return TK_ERR_ARGS;
+    int rc = tk_cp_pack_atoms(atoms_xyzq, numatoms, zplane, packed_scratch, stream);
+    if (rc != TK_OK) return rc;
+    CpArgs a;
+    a.numatoms = numatoms;
+    a.spacing = gridspacing;
+    a.lattice = energygrid;
+    a.atoms = reinterpret_cast<const float4*>(packed_scratch);
+    a.gx = nx / 128;
+    a.gy = ny / 8;
+    a.start = 0;
+    a.end = a.gx * a.gy;
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    return run_cp(a, static_cast<unsigned>(d->sm_count), 256, static_cast<cudaStream_t>(stream));
+}
+
+// =================================================================================================
+// host-buffer pair: tzgemm + `sweeps` Jacobi sweeps, one fused launch per sweep
+// =================================================================================================
+static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+TK_API int tk_pair_tzgemm_stencil_workspace(int M, int N, int K, int nx, int ny, int nz, size_t* bytes) {
+    if (!bytes || M <= 0 || N <= 0 || K <= 0 || nx <= 0 || ny <= 0 || nz <= 0) return TK_ERR_ARGS;
+    const size_t grid = align256(sizeof(float) * static_cast<size_t>(nx) * ny * nz);
+    *bytes = align256(2 * static_cast<size_t>(M) * K) + align256(2 * static_cast<size_t>(N) * K) +
+             align256(4 * static_cast<size_t>(M) * N) + 2 * grid;
+    return TK_OK;
+}
+
+TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, float* C_host, int M, int N, int K,
+                                       float alpha, float c0, float c1, const float* A0_host, float* Aout_host,
+                                       int nx, int ny, int nz, int sweeps, int cd_threads, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+    size_t need = 0;
+    int rc = tk_pair_tzgemm_stencil_workspace(M, N, K, nx, ny, nz, &need);
+    if (rc != TK_OK) return rc;
+    if (!A_host || !B_host || !C_host || !A0_host || !Aout_host || !workspace || sweeps < 1) return TK_ERR_ARGS;
+    if (workspace_bytes < need) return TK_ERR_CAPACITY;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return TK_ERR_ALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* w = static_cast<uint8_t*>(workspace);
+    const size_t a_bytes = 2 * static_cast<size_t>(M) * K, b_bytes = 2 * static_cast<size_t>(N) * K;
+    const size_t c_bytes = 4 * static_cast<size_t>(M) * N;
+    const size_t g_bytes = sizeof(float) * static_cast<size_t>(nx) * ny * nz;
+    __half* dA = reinterpret_cast<__half*>(w);
+    __half* dB = reinterpret_cast<__half*>(w + align256(a_bytes));
+    float* dC = reinterpret_cast<float*>(w + align256(a_bytes) + align256(b_bytes));
+    float* g0 = reinterpret_cast<float*>(w + align256(a_bytes) + align256(b_bytes) + align256(c_bytes));
+    float* g1 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(g0) + align256(g_bytes));
+    TK_CUDA(cudaMemcpyAsync(dA, A_host, a_bytes, cudaMemcpyHostToDevice, st));
+    TK_CUDA(cudaMemcpyAsync(dB, B_host, b_bytes, cudaMemcpyHostToDevice, st));
+    TK_CUDA(cudaMemcpyAsync(g0, A0_host, g_bytes, cudaMemcpyHostToDevice, st));
+    TK_CUDA(cudaMemcpyAsync(g1, g0, g_bytes, cudaMemcpyDeviceToDevice, st));  // boundary cells of the second buffer
+
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    GemmCall c;
+    c.A = dA;
+    c.B = dB;
+    c.g.C = dC;
+    c.g.M = M;
+    c.g.N = N;
+    c.g.K = K;
+    c.g.alpha = alpha;
+    c.g.status = nullptr;
+    if (M < 128 || N < 64 || K < 64 || M % 128 || N % 64 || K % 64) return TK_ERR_SHAPE;
+    const int tiles = (M / 64) * (N / 64);
+    CdCall cd;
+    cd.kind = CD_STENCIL;
+    cd.s.c0 = c0;
+    cd.s.c1 = c1;
+    cd.s.nx = nx;
+    cd.s.ny = ny;
+    cd.s.nz = nz;
+    cd.s.gx = (nx + 63) / 64;
+    cd.s.gy = (ny + 3) / 4;
+    cd.s.start = 0;
+    cd.s.end = cd.s.gx * cd.s.gy;
+    const unsigned block = kGemmThreads + static_cast<unsigned>(cd_threads > 0 ? cd_threads : 256);
+    for (int it = 0; it < sweeps; ++it) {
+        cd.s.A0 = (it & 1) ? g1 : g0;
+        cd.s.Anext = (it & 1) ? g0 : g1;
+        // the GEMM's tiles are dealt evenly over the sweeps
+        c.g.start = static_cast<int>(static_cast<long long>(tiles) * it / sweeps);
+        c.g.end = static_cast<int>(static_cast<long long>(tiles) * (it + 1) / sweeps);
+        if ((rc = run_mix(c, cd, static_cast<unsigned>(d->sm_count), block, st)) != TK_OK) return rc;
+    }
+    TK_CUDA(cudaMemcpyAsync(C_host, dC, c_bytes, cudaMemcpyDeviceToHost, st));
+    TK_CUDA(cudaMemcpyAsync(Aout_host, (sweeps & 1) ? g1 : g0, g_bytes, cudaMemcpyDeviceToHost, st));
+    return TK_OK;
+}

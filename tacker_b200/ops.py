@@ -278,4 +278,34 @@ def mix(cd: GPTBKernel, tz: GPTBKernel, cd_threads=256, grid=None, cd_range=None
                      cs, ce, ts, te)
 
 
+# ---- whole operators and the host-buffer pair ---------------------------------------------------------
+def mriq_compute(kx, ky, kz, phiR, phiI, numK, x, y, z, Qr, Qi, numX, kvals_scratch, stream: int = 0) -> None:
+    check(lib().tk_mriq_compute(*[C.c_void_p(p) for p in (kx, ky, kz, phiR, phiI)], numK,
+                                *[C.c_void_p(p) for p in (x, y, z, Qr, Qi)], numX, C.c_void_p(kvals_scratch),
+                                C.c_void_p(stream)), "tk_mriq_compute")
+
+
+def coulomb_compute(atoms_xyzq, numatoms, zplane, spacing, energygrid, nx, ny, packed_scratch,
+                    stream: int = 0) -> None:
+    check(lib().tk_coulomb_compute(C.c_void_p(atoms_xyzq), numatoms, C.c_float(zplane), C.c_float(spacing),
+                                   C.c_void_p(energygrid), nx, ny, C.c_void_p(packed_scratch), C.c_void_p(stream)),
+          "tk_coulomb_compute")
+
+
+def pair_tzgemm_stencil_workspace(M, N, K, nx, ny, nz) -> int:
+    n = C.c_size_t(0)
+    check(lib().tk_pair_tzgemm_stencil_workspace(M, N, K, nx, ny, nz, C.byref(n)), "tk_pair_tzgemm_stencil_workspace")
+    return n.value
+
+
+def pair_tzgemm_stencil_host(A_host, B_host, C_host, M, N, K, alpha, c0, c1, A0_host, Aout_host, nx, ny, nz, sweeps,
+                             cd_threads, workspace, workspace_bytes, stream: int = 0) -> None:
+    """All five buffers are host addresses (pinned); `workspace` is a device address."""
+    check(lib().tk_pair_tzgemm_stencil_host(C.c_void_p(A_host), C.c_void_p(B_host), C.c_void_p(C_host), M, N, K,
+                                            C.c_float(alpha), C.c_float(c0), C.c_float(c1), C.c_void_p(A0_host),
+                                            C.c_void_p(Aout_host), nx, ny, nz, sweeps, cd_threads,
+                                            C.c_void_p(workspace), C.c_size_t(workspace_bytes), C.c_void_p(stream)),
+          "tk_pair_tzgemm_stencil_host")
+
+
 __all__ = [n for n in dir() if not n.startswith("_")]
