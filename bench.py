@@ -32,7 +32,8 @@ sys.path.insert(0, ROOT)
 M, N, K = 4096, 4096, 1024
 NX, NY, NZ, SWEEPS = 512, 512, 64, 10
 C0, C1 = 1.0 / 6.0, -1.0 / 6.0
-CD_THREADS = 256
+CD_THREADS = 384        # CUDA-core threads of the fused CTA (12 warps next to the 6 tensor-role warps)
+SOLO_CD_THREADS = 256   # solo stencil: 2 CTAs of 8 warps per SM
 TILES = (M // 64) * (N // 64)
 CD_BLOCKS = (NX // 64) * (NY // 4)
 WORKLOAD = (f"config 2: fused tzgemm {M}x{N}x{K} fp16->fp32 + {SWEEPS} Jacobi sweeps of the 7-point stencil on "
@@ -218,7 +219,7 @@ def run_ours(args):
     def cd_kernel(it, start=0, end=None, grid=None):
         src, dst = grids[it & 1], grids[(it + 1) & 1]
         return ops.gptb_stencil(C0, C1, src.data_ptr(), dst.data_ptr(), NX, NY, NZ, start=start, end=end,
-                                grid=grid or sms * 4, block=CD_THREADS)
+                                grid=grid or sms * 2, block=SOLO_CD_THREADS)
 
     bounds = [TILES * i // SWEEPS for i in range(SWEEPS + 1)]
     fused = [ops.mix(cd_kernel(i), tz_kernel(0, TILES), cd_threads=CD_THREADS, grid=sms,

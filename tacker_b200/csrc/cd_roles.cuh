@@ -21,9 +21,9 @@ namespace tk {
 //   Anext[i,j,k] = (A0[k+1] + A0[k-1] + A0[j+1] + A0[j-1] + A0[i+1] + A0[i-1]) * c1 - A0[i,j,k] * c0
 //   for 0 < i < nx-1, 0 < j < ny-1, 0 < k < nz-1; other cells are not written.
 // Virtual block p = the 64 x 4 (x, y) column bundle (p % gx, (p / gx) % gy), all z.
-// Here 64 threads (16 x-lanes of one float4 each, 4 rows) cover one z-slab of the bundle and
-// march through it with the three planes of their column in registers; nthreads/64 slabs split
-// the z range.  y neighbours inside a warp (which holds two rows) and x neighbours inside a row
+// Here 64 threads (16 x-lanes of one float4 each, 4 rows) take one work item = one z-slab of one
+// bundle and march through it with the three planes of their column in registers; the host
+// picks how many slabs a bundle is cut into so that the items fill the launched groups evenly.  y neighbours inside a warp (which holds two rows) and x neighbours inside a row
 // come from shuffles, the rest of the halo from global memory.
 // =====================================================================================
 struct StencilArgs {
@@ -33,9 +33,32 @@ struct StencilArgs {
     int nx, ny, nz;
     int gx, gy;      // virtual grid (64-wide, 4-high bundles)
     int start, end;  // virtual block range
+    int slabs, per;  // z split chosen by the host: `slabs` work items per block, `per` planes each
 };
 
-constexpr int kStencilGroup = 64;  // threads per z-slab
+constexpr int kStencilGroup = 64;  // threads per work item: 16 float4 lanes x 4 rows own a z-slab of a bundle
+
+// Host-side choice of the z split for `groups` 64-thread groups working on `blocks` bundles:
+// minimise rounds x (planes per item + the two halo planes every item re-reads).
+__host__ __device__ inline void stencil_pick_split(int nz, long long blocks, long long groups, int* slabs,
+                                                   int* per) {
+    const int planes = nz - 2 > 0 ? nz - 2 : 1;
+    long long best_cost = -1;
+    *slabs = 1;
+    *per = planes;
+    for (int s = 1; s <= 32 && s <= planes; ++s) {
+        const int pp = (planes + s - 1) / s;
+        const int eff = (planes + pp - 1) / pp;
+        const long long items = blocks * eff;
+        const long long rounds = (items + groups - 1) / (groups > 0 ? groups : 1);
+        const long long cost = rounds * (pp + 2);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            *slabs = eff;
+            *per = pp;
+        }
+    }
+}
 
 __device__ __forceinline__ float stencil_point(float top, float bot, float up, float down, float right,
                                                float left, float ctr, float c0, float c1) {
@@ -48,27 +71,33 @@ __device__ __forceinline__ float stencil_point(float top, float bot, float up, f
     return __fmaf_rn(s, c1, -__fmul_rn(ctr, c0));
 }
 
-__device__ __forceinline__ float4 stencil_ld4(const float* __restrict__ row, int x, int nx, bool valid,
-                                              bool vec) {
+// p points at element x of the row; nx bounds the scalar path
+__device__ __forceinline__ float4 stencil_ld4(const float* __restrict__ p, int x, int nx, bool valid, bool vec) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (valid) {
         if (vec) {
-            v = __ldg(reinterpret_cast<const float4*>(row + x));
+            v = __ldg(reinterpret_cast<const float4*>(p));
         } else {
-            if (x + 0 < nx) v.x = __ldg(row + x + 0);
-            if (x + 1 < nx) v.y = __ldg(row + x + 1);
-            if (x + 2 < nx) v.z = __ldg(row + x + 2);
-            if (x + 3 < nx) v.w = __ldg(row + x + 3);
+            if (x + 0 < nx) v.x = __ldg(p + 0);
+            if (x + 1 < nx) v.y = __ldg(p + 1);
+            if (x + 2 < nx) v.z = __ldg(p + 2);
+            if (x + 3 < nx) v.w = __ldg(p + 3);
         }
     }
     return v;
 }
 
+__device__ __forceinline__ void stencil_prefetch_l2(const float* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// PF = distance, in planes, of an L2 prefetch of the thread's column ahead of its loads (0 = none).
+template <int PF>
 __device__ __forceinline__ void stencil_role(const StencilArgs s, const int tid, const int nthreads,
                                              const int cta, const int ncta) {
-    const int nslab = nthreads / kStencilGroup;
-    const int slab = tid / kStencilGroup;
-    if (slab >= nslab) return;  // whole warps only: nthreads is a multiple of 32, groups are 2 warps
+    const int ngroups = nthreads / kStencilGroup;
+    const int group = tid / kStencilGroup;
+    if (group >= ngroups) return;  // whole warps only: a group is two warps
     const int t = tid % kStencilGroup;
     const int lx = t & 15, ly = t >> 4;
     const bool even_row = (ly & 1) == 0;  // lanes 0-15 of the warp
@@ -77,64 +106,82 @@ __device__ __forceinline__ void stencil_role(const StencilArgs s, const int tid,
     const bool vec = (nx % 4 == 0) && ((reinterpret_cast<uintptr_t>(s.A0) & 15u) == 0) &&
                      ((reinterpret_cast<uintptr_t>(s.Anext) & 15u) == 0);
     const size_t plane = static_cast<size_t>(nx) * ny;
+    const int nitems = (s.end - s.start) * s.slabs;
 
-    // z range of this slab: interior planes 1 .. nz-2 split evenly
-    const int planes = nz - 2;
-    const int per = (planes + nslab - 1) / nslab;
-    const int k0 = 1 + slab * per;
-    const int k1 = min(k0 + per, nz - 1);
-
-    for (int p = s.start + cta; p < s.end; p += ncta) {
+    // items are dealt CTA-first: at any moment the running CTAs cover a contiguous range of bundles
+    for (int item = group * ncta + cta; item < nitems; item += ncta * ngroups) {
+        const int p = s.start + item / s.slabs;
+        const int slab = item % s.slabs;
+        const int k0 = 1 + slab * s.per;
+        const int k1 = min(k0 + s.per, nz - 1);
+        if (k0 >= k1) continue;
         const int bx = p % s.gx, by = (p / s.gx) % s.gy;
         const int x = bx * 64 + 4 * lx;
         const int j = by * 4 + ly;
         const bool col_ok = (j < ny) && (x < nx);
         const int jh = even_row ? j - 1 : j + 1;  // the y neighbour outside this warp's two rows
         const bool halo_ok = (jh >= 0) && (jh < ny) && (x < nx);
-        const bool row_interior = (j > 0) && (j < ny - 1);
-        const float* __restrict__ col = s.A0 + static_cast<size_t>(nx) * j;
-        const float* __restrict__ colh = s.A0 + static_cast<size_t>(nx) * jh;
-        float* __restrict__ out = s.Anext + static_cast<size_t>(nx) * j;
+        const bool writes = (j > 0) && (j < ny - 1) && col_ok;
+        const bool vec_store = vec && x > 0 && x + 4 < nx;
         const bool need_left = (lx == 0) && (x > 0) && (j < ny);
         const bool need_right = (lx == 15) && (x + 4 < nx) && (j < ny);
+        // element x of this thread's row / halo row / output row at plane k0
+        const float* __restrict__ pc = s.A0 + plane * k0 + static_cast<size_t>(nx) * j + x;
+        const float* __restrict__ ph = s.A0 + plane * k0 + static_cast<size_t>(nx) * jh + x;
+        float* __restrict__ po = s.Anext + plane * k0 + static_cast<size_t>(nx) * j + x;
 
-        if (k0 < k1) {
-            float4 bot = stencil_ld4(col + plane * (k0 - 1), x, nx, col_ok, vec);
-            float4 ctr = stencil_ld4(col + plane * k0, x, nx, col_ok, vec);
-#pragma unroll 2
-            for (int k = k0; k < k1; ++k) {
-                const float4 top = stencil_ld4(col + plane * (k + 1), x, nx, col_ok, vec);
-                const float4 gh = stencil_ld4(colh + plane * k, x, nx, halo_ok, vec);
-                float left = __shfl_up_sync(0xffffffffu, ctr.w, 1, 16);
-                float right = __shfl_down_sync(0xffffffffu, ctr.x, 1, 16);
-                if (need_left) left = __ldg(col + plane * k + x - 1);
-                if (need_right) right = __ldg(col + plane * k + x + 4);
-                float4 other;
-                other.x = __shfl_xor_sync(0xffffffffu, ctr.x, 16);
-                other.y = __shfl_xor_sync(0xffffffffu, ctr.y, 16);
-                other.z = __shfl_xor_sync(0xffffffffu, ctr.z, 16);
-                other.w = __shfl_xor_sync(0xffffffffu, ctr.w, 16);
-                const float4 up = even_row ? other : gh;
-                const float4 down = even_row ? gh : other;
-                if (row_interior && col_ok) {
-                    float4 o;
-                    o.x = stencil_point(top.x, bot.x, up.x, down.x, ctr.y, left, ctr.x, s.c0, s.c1);
-                    o.y = stencil_point(top.y, bot.y, up.y, down.y, ctr.z, ctr.x, ctr.y, s.c0, s.c1);
-                    o.z = stencil_point(top.z, bot.z, up.z, down.z, ctr.w, ctr.y, ctr.z, s.c0, s.c1);
-                    o.w = stencil_point(top.w, bot.w, up.w, down.w, right, ctr.z, ctr.w, s.c0, s.c1);
-                    float* dst = out + plane * k + x;
-                    if (vec && x > 0 && x + 4 < nx) {
-                        *reinterpret_cast<float4*>(dst) = o;
-                    } else {
-                        if (x + 0 > 0 && x + 0 < nx - 1) dst[0] = o.x;
-                        if (x + 1 < nx - 1) dst[1] = o.y;
-                        if (x + 2 < nx - 1) dst[2] = o.z;
-                        if (x + 3 < nx - 1) dst[3] = o.w;
-                    }
-                }
-                bot = ctr;
-                ctr = top;
+        float4 bot = stencil_ld4(pc - plane, x, nx, col_ok, vec);
+        float4 ctr = stencil_ld4(pc, x, nx, col_ok, vec);
+        // software pipeline: the loads of step k+1 are in flight while step k is computed
+        float4 top = stencil_ld4(pc + plane, x, nx, col_ok, vec);
+        float4 gh = stencil_ld4(ph, x, nx, halo_ok, vec);
+        float lf = need_left ? __ldg(pc - 1) : 0.0f;
+        float rt = need_right ? __ldg(pc + 4) : 0.0f;
+        for (int k = k0; k < k1; ++k) {
+            float4 ntop = top, ngh = gh;
+            float nlf = lf, nrt = rt;
+            if (k + 1 < k1) {
+                ntop = stencil_ld4(pc + 2 * plane, x, nx, col_ok, vec);
+                ngh = stencil_ld4(ph + plane, x, nx, halo_ok, vec);
+                if (need_left) nlf = __ldg(pc + plane - 1);
+                if (need_right) nrt = __ldg(pc + plane + 4);
             }
+            if (PF > 0 && col_ok && (lx & 7) == 0 && k + 2 + PF < nz) stencil_prefetch_l2(pc + plane * (2 + PF));
+            float left = __shfl_up_sync(0xffffffffu, ctr.w, 1, 16);
+            float right = __shfl_down_sync(0xffffffffu, ctr.x, 1, 16);
+            if (need_left) left = lf;
+            if (need_right) right = rt;
+            float4 other;
+            other.x = __shfl_xor_sync(0xffffffffu, ctr.x, 16);
+            other.y = __shfl_xor_sync(0xffffffffu, ctr.y, 16);
+            other.z = __shfl_xor_sync(0xffffffffu, ctr.z, 16);
+            other.w = __shfl_xor_sync(0xffffffffu, ctr.w, 16);
+            const float4 up = even_row ? other : gh;
+            const float4 down = even_row ? gh : other;
+            if (writes) {
+                float4 o;
+                o.x = stencil_point(top.x, bot.x, up.x, down.x, ctr.y, left, ctr.x, s.c0, s.c1);
+                o.y = stencil_point(top.y, bot.y, up.y, down.y, ctr.z, ctr.x, ctr.y, s.c0, s.c1);
+                o.z = stencil_point(top.z, bot.z, up.z, down.z, ctr.w, ctr.y, ctr.z, s.c0, s.c1);
+                o.w = stencil_point(top.w, bot.w, up.w, down.w, right, ctr.z, ctr.w, s.c0, s.c1);
+                if (vec_store) {
+                    *reinterpret_cast<float4*>(po) = o;
+                } else {
+                    if (x + 0 > 0 && x + 0 < nx - 1) po[0] = o.x;
+                    if (x + 1 < nx - 1) po[1] = o.y;
+                    if (x + 2 < nx - 1) po[2] = o.z;
+                    if (x + 3 < nx - 1) po[3] = o.w;
+                }
+            }
+            bot = ctr;
+            ctr = top;
+            top = ntop;
+            gh = ngh;
+            lf = nlf;
+            rt = nrt;
+            pc += plane;
+            ph += plane;
+            po += plane;
         }
     }
 }

@@ -13,6 +13,7 @@
 #include "../../include/tacker_b200.h"
 #include "cd_roles.cuh"
 #include "gemm_role.cuh"
+#include "stencil_tma.cuh"
 
 #define TK_API extern "C" __attribute__((visibility("default")))
 
@@ -26,7 +27,7 @@ __device__ unsigned g_dev_status;
 // -------------------------------------------------------------------------------------------------
 // kernels
 // -------------------------------------------------------------------------------------------------
-constexpr int kMaxMixThreads = 704;  // 192 tensor-role threads + up to 512 CUDA-core threads
+constexpr int kMaxMixThreads = 896;  // 192 tensor-role threads + up to 704 CUDA-core threads (<= 73 registers each)
 
 __device__ __forceinline__ uint8_t* align_smem_1024(uint8_t* p) {
     const uint32_t a = smem_u32(p);
@@ -41,8 +42,23 @@ tzgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), threadIdx.x >> 5, threadIdx.x & 31);
 }
 
+template <int PF>
 __global__ void __launch_bounds__(512) stencil_kernel(const StencilArgs s) {
-    stencil_role(s, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+    stencil_role<PF>(s, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+}
+
+__device__ __forceinline__ uint8_t* align_smem_128(uint8_t* p) {
+    const uint32_t a = smem_u32(p);
+    return p + ((128u - (a & 127u)) & 127u);
+}
+
+// TMA-fed form: every warp streams its planes through a private ring of `ring` slots
+__global__ void __launch_bounds__(512)
+stencil_tma_kernel(const __grid_constant__ CUtensorMap tmap_grid, const StencilArgs s, const int ring,
+                   unsigned* status) {
+    extern __shared__ uint8_t smem_raw[];
+    stencil_role_tma(&tmap_grid, s, align_smem_128(smem_raw), ring, threadIdx.x >> 5, blockDim.x >> 5,
+                     threadIdx.x & 31, blockIdx.x, gridDim.x, status);
 }
 
 template <int PPT, bool EXACT>
@@ -58,16 +74,23 @@ __global__ void __launch_bounds__(512) mriq_kernel(const MriqArgs m) {
 // Fused kernels: warps 0..5 run the tensor role, the remaining warps the CUDA-core role.  The
 // two roles share the SM and nothing else (the reference dispatches on threadIdx.x ranges the
 // same way, src/mix_kernel/tzgemm_stencil.cu:284-298).
+// ring > 0: the stencil warps use the TMA-fed role with their rings placed behind the tensor role's
+// shared memory; ring == 0: the register role (shapes TMA cannot describe).
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kMaxMixThreads, 1)
 mix_stencil_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const GemmArgs g, const StencilArgs s) {
+                   const GemmArgs g, const __grid_constant__ CUtensorMap tmap_grid, const StencilArgs s,
+                   const int ring) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5;
+    uint8_t* smem = align_smem_1024(smem_raw);
     if (warp < kGemmWarps) {
-        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
+        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31);
+    } else if (ring > 0) {
+        stencil_role_tma(&tmap_grid, s, smem + GemmSmem<BN, STAGES>::kBytes, ring, warp - kGemmWarps,
+                         (blockDim.x >> 5) - kGemmWarps, threadIdx.x & 31, blockIdx.x, gridDim.x, g.status);
     } else {
-        stencil_role(s, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+        stencil_role<0>(s, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
     }
 }
 
@@ -186,6 +209,10 @@ struct Options {
     int cp_exact = 0;
     int cp_ppt = 8;
     int mriq_accurate = 0;
+    int stencil_prefetch = 0;   // register role: L2 prefetch distance in planes (0 or 8)
+    int stencil_tma = 1;        // 1 = TMA-fed role whenever the shape allows, 0 = always the register role
+    int stencil_ring = 4;       // ring depth per warp, solo kernel (2 planes in flight per warp measured best)
+    int mix_stencil_ring = 12;  // upper bound of the ring depth in the fused kernel (shared memory decides)
 };
 static Options g_opt;
 
@@ -247,6 +274,31 @@ static int make_tmap(CUtensorMap* m, const void* base, int rows, int k, int box_
     }
     return TK_OK;
 }
+
+// fp32 grid [nz][ny][nx]; box = 72 x 6 x 1 (a 64 x 4 bundle plus its halo), no swizzle, zero fill
+static int make_tmap_grid(CUtensorMap* m, const float* base, int nx, int ny, int nz) {
+    int rc = get_encoder();
+    if (rc != TK_OK) return rc;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(nx), static_cast<cuuint64_t>(ny), static_cast<cuuint64_t>(nz)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(nx) * 4, static_cast<cuuint64_t>(nx) * ny * 4};
+    cuuint32_t box[3] = {kStTileCols, kStTileRows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        t_last_error = "cuTensorMapEncodeTiled (grid) failed with CUresult " + std::to_string(static_cast<int>(r));
+        return TK_ERR_CUDA;
+    }
+    return TK_OK;
+}
+
+static bool stencil_tma_ok(const StencilArgs& s) {
+    return g_opt.stencil_tma != 0 && s.nx % 4 == 0 && s.nz >= 3 &&
+           (reinterpret_cast<uintptr_t>(s.A0) & 15u) == 0 && (reinterpret_cast<uintptr_t>(s.Anext) & 15u) == 0;
+}
+
+constexpr int kMaxDynSmem = 232448;  // 227 KiB per CTA on sm_100
 
 // ---- parameter access ----
 template <typename T>
@@ -433,11 +485,31 @@ static unsigned cd_threads(unsigned requested, unsigned granule, unsigned cap) {
     return t;
 }
 
-static int run_stencil(const StencilArgs& s, unsigned grid0, unsigned block0, cudaStream_t st) {
+static int run_stencil(StencilArgs s, unsigned grid0, unsigned block0, cudaStream_t st) {
     if (s.start >= s.end) return TK_OK;
-    const unsigned threads = cd_threads(block0, kStencilGroup, 512);
+    const unsigned threads = cd_threads(block0, 32, 512);
     if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
-    stencil_kernel<<<grid0, threads, 0, st>>>(s);
+    if (stencil_tma_ok(s)) {
+        DeviceInfo* d = nullptr;
+        int rc = device_info(&d);
+        if (rc != TK_OK) return rc;
+        const int nwarps = static_cast<int>(threads / 32);
+        int ring = g_opt.stencil_ring;
+        while (ring > kStMinRing && nwarps * stencil_tma_warp_bytes(ring) + 128 > kMaxDynSmem) --ring;
+        const int smem = nwarps * stencil_tma_warp_bytes(ring) + 128;
+        CUtensorMap tg;
+        if ((rc = make_tmap_grid(&tg, s.A0, s.nx, s.ny, s.nz)) != TK_OK) return rc;
+        if ((rc = enable_smem(stencil_tma_kernel, smem)) != TK_OK) return rc;
+        stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(grid0) * nwarps, &s.slabs, &s.per);
+        stencil_tma_kernel<<<grid0, threads, smem, st>>>(tg, s, ring, d->status_ptr);
+        return launch_error("stencil_tma_kernel launch");
+    }
+    const unsigned rthreads = cd_threads(threads, kStencilGroup, 512);
+    if (rthreads == 0) return TK_ERR_LAUNCH_CONFIG;
+    stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(grid0) * (rthreads / kStencilGroup), &s.slabs,
+                       &s.per);
+    if (g_opt.stencil_prefetch) stencil_kernel<8><<<grid0, rthreads, 0, st>>>(s);
+    else stencil_kernel<0><<<grid0, rthreads, 0, st>>>(s);
     return launch_error("stencil_kernel launch");
 }
 
@@ -484,6 +556,43 @@ struct CdCall {
     }
 };
 
+// The stencil's rings share the CTA's shared memory with the tensor role's stages: fewer, larger
+// stages for the GEMM here than in the solo kernel, so that the rings get about 80 KB.
+template <int BN>
+struct StagesMixStencil {
+    static constexpr int value = BN == 256 ? 3 : 4;
+};
+
+template <int BN>
+static int launch_mix_stencil(const GemmCall& c, const CUtensorMap& ta, const CUtensorMap& tb, StencilArgs s,
+                              unsigned ctas, unsigned threads, cudaStream_t st) {
+    constexpr int STAGES = StagesMixStencil<BN>::value;
+    constexpr int kGemmBytes = GemmSmem<BN, STAGES>::kBytes + 1024;
+    auto k = mix_stencil_kernel<BN, STAGES>;
+    const int nwarps = static_cast<int>((threads - kGemmThreads) / 32);
+    int ring = 0, smem = kGemmBytes, rc;
+    CUtensorMap tg;
+    std::memset(&tg, 0, sizeof(tg));
+    if (stencil_tma_ok(s)) {
+        ring = g_opt.mix_stencil_ring;
+        while (ring >= kStMinRing && kGemmBytes + nwarps * stencil_tma_warp_bytes(ring) > kMaxDynSmem) --ring;
+        if (ring < kStMinRing) ring = 0;
+    }
+    if (ring > 0) {
+        if ((rc = make_tmap_grid(&tg, s.A0, s.nx, s.ny, s.nz)) != TK_OK) return rc;
+        smem += nwarps * stencil_tma_warp_bytes(ring);
+        stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(ctas) * nwarps, &s.slabs, &s.per);
+    } else {
+        const unsigned groups = (threads - kGemmThreads) / kStencilGroup;
+        if (groups == 0) return TK_ERR_LAUNCH_CONFIG;
+        threads = kGemmThreads + groups * kStencilGroup;
+        stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(ctas) * groups, &s.slabs, &s.per);
+    }
+    if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+    k<<<ctas, threads, smem, st>>>(ta, tb, c.g, tg, s, ring);
+    return launch_error("mix_stencil_kernel launch");
+}
+
 template <int BN>
 static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsigned threads, cudaStream_t st) {
     constexpr int STAGES = StagesFor<BN>::value;
@@ -494,12 +603,8 @@ static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsign
     if (rc != TK_OK) return rc;
     const int smem = gemm_smem_bytes<BN>();
     switch (cd.kind) {
-        case CD_STENCIL: {
-            auto k = mix_stencil_kernel<BN, STAGES>;
-            if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
-            k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.s);
-            break;
-        }
+        case CD_STENCIL:
+            return launch_mix_stencil<BN>(c, ta, tb, cd.s, ctas, threads, st);
         case CD_CP: {
             if (g_opt.cp_ppt == 2) {
                 auto k = mix_cp_kernel<BN, STAGES, 2>;
@@ -534,7 +639,7 @@ static int run_mix(GemmCall& c, const CdCall& cd, unsigned grid0, unsigned block
     const bool gemm_empty = c.g.start >= c.g.end;
     if (gemm_empty && cd.empty()) return TK_OK;
     if (block0 <= static_cast<unsigned>(kGemmThreads)) return TK_ERR_LAUNCH_CONFIG;
-    const unsigned granule = cd.kind == CD_STENCIL ? kStencilGroup : 32;
+    const unsigned granule = 32;
     const unsigned cdt = cd_threads(block0 - kGemmThreads, granule, kMaxMixThreads - kGemmThreads);
     if (cdt == 0) return TK_ERR_LAUNCH_CONFIG;
     if (gemm_empty) {  // nothing for the tensor role: run the CUDA-core kernel alone
@@ -592,6 +697,10 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "cp_exact")) return &g_opt.cp_exact;
     if (!std::strcmp(name, "cp_ppt")) return &g_opt.cp_ppt;
     if (!std::strcmp(name, "mriq_accurate")) return &g_opt.mriq_accurate;
+    if (!std::strcmp(name, "stencil_prefetch")) return &g_opt.stencil_prefetch;
+    if (!std::strcmp(name, "stencil_tma")) return &g_opt.stencil_tma;
+    if (!std::strcmp(name, "stencil_ring")) return &g_opt.stencil_ring;
+    if (!std::strcmp(name, "mix_stencil_ring")) return &g_opt.mix_stencil_ring;
     return nullptr;
 }
 
@@ -600,6 +709,9 @@ TK_API int tk_set_option(const char* name, int value) {
     if (!slot) return TK_ERR_UNKNOWN_KEY;
     if (slot == &g_opt.tzgemm_bn && value != 0 && value != 128 && value != 256) return TK_ERR_ARGS;
     if (slot == &g_opt.cp_ppt && value != 8 && value != 4 && value != 2) return TK_ERR_ARGS;
+    if (slot == &g_opt.stencil_prefetch && value != 0 && value != 8) return TK_ERR_ARGS;
+    if ((slot == &g_opt.stencil_ring || slot == &g_opt.mix_stencil_ring) && (value < kStMinRing || value > kStMaxRing))
+        return TK_ERR_ARGS;
     *slot = value;
     return TK_OK;
 }
@@ -714,7 +826,7 @@ TK_API int tk_launch_ori_stencil(void** params, int nparams, const unsigned grid
     if ((rc = parse_stencil(p, 13, 15, &s)) != TK_OK) return rc;
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
-    return run_stencil(s, static_cast<unsigned>(d->sm_count) * 4u, 256, static_cast<cudaStream_t>(stream));
+    return run_stencil(s, static_cast<unsigned>(d->sm_count) * 2u, 256, static_cast<cudaStream_t>(stream));
 }
 
 TK_API int tk_launch_ori_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
@@ -894,9 +1006,9 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
         return fill_info(tzgemm_kernel<256, kStages256>, kGemmThreads, gsm, info);
     }
     if (k == "gptb_stencil" || k == "ori_stencil") {
-        info->threads_cd_min = kStencilGroup;
+        info->threads_cd_min = 32;
         info->threads_cd_default = 256;
-        return fill_info(stencil_kernel, 256, 0, info);
+        return fill_info(stencil_kernel<0>, 256, 0, info);
     }
     if (k == "gptb_cp" || k == "ori_cp") {
         info->threads_cd_min = 32;
@@ -912,8 +1024,8 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
     info->tmem_columns = 512;
     info->threads_cd_default = 256;
     if (k == "tzgemm_stencil") {
-        info->threads_cd_min = kStencilGroup;
-        return fill_info(mix_stencil_kernel<256, kStages256>, kGemmThreads + 256, gsm, info);
+        info->threads_cd_min = 32;
+        return fill_info(mix_stencil_kernel<256, 3>, kGemmThreads + 256, gsm, info);
     }
     if (k == "tzgemm_cp") {
         info->threads_cd_min = 32;

@@ -253,7 +253,7 @@ def gptb_tzgemm(A, B, Cm, m, n, k, alpha=1.1, start=0, end=None, grid=None, roun
 def gptb_stencil(c0, c1, A0, Anext, nx, ny, nz, start=0, end=None, grid=None, block=256) -> GPTBKernel:
     ori = OriSTENCILKernel(c0, c1, A0, Anext, nx, ny, nz)
     total = ori.launchGridDim[0] * ori.launchGridDim[1]
-    return GPTBKernel("stencil", "gptb_stencil", ori, (grid or sm_count() * 4, 1, 1), (block, 1, 1), start,
+    return GPTBKernel("stencil", "gptb_stencil", ori, (grid or sm_count() * 2, 1, 1), (block, 1, 1), start,
                       total if end is None else end)
 
 
