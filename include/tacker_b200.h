@@ -225,6 +225,28 @@ int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, float* C
                                 int ny, int nz, int sweeps, int cd_threads, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/* ---- MRI-Q for callers that cannot allocate device memory ----------------------------------------------
+ * (No counterpart in the reference: it always cudaMallocs its buffers up front.)
+ * Same computation and same results as tk_mriq_compute, but the packed k-space table is a fixed array
+ * inside the library instead of caller-supplied scratch, so the call needs no buffer beyond its inputs
+ * and outputs.  Meant for code that runs where cudaMalloc is off limits: inside a real-time or
+ * latency-critical loop that must not take the allocator's locks or implicit synchronisation, in a
+ * process whose device memory has been handed out completely to a pool owned by someone else, or in
+ * a plug-in that is only given the buffers of its host application.
+ *   - Limit: numK <= TK_MRIQ_STATIC_MAX_K samples; more returns TK_ERR_CAPACITY (tk_last_error() says
+ *     so) and nothing is launched.  The table costs 64 KiB of device memory on every GPU that loads the
+ *     library, for the life of the process.
+ *   - The first call on each device looks the table's device address up (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call before starting any stream capture.
+ *   - It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - All calls on one device share the table.  Calls that overlap on the GPU (different streams, or
+ *     different host threads without ordering) race on it; calls queued on one stream are safe.  The
+ *     table keeps the last call's samples, which the next call overwrites before reading. */
+#define TK_MRIQ_STATIC_MAX_K 4096
+int tk_mriq_compute_static(const float* kx, const float* ky, const float* kz, const float* phiR,
+                           const float* phiI, int numK, const float* x, const float* y, const float* z,
+                           float* Qr, float* Qi, int numX, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

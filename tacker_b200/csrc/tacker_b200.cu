@@ -1159,3 +1159,41 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     TK_CUDA(cudaMemcpyAsync(Aout_host, (sweeps & 1) ? g1 : g0, g_bytes, cudaMemcpyDeviceToHost, st));
     return TK_OK;
 }
+
+// =================================================================================================
+// MRI-Q without any allocation: the packed k-space table lives in a fixed device array
+// =================================================================================================
+// Every GPU that loads this library holds these 64 KiB until the process exits.
+static __device__ __align__(256) float4 g_mriq_static_kvals[TK_MRIQ_STATIC_MAX_K];
+
+// device -> address of g_mriq_static_kvals on that device.  In host code the array's name is only a
+// handle for the runtime, not a device address: the kernels must be given what
+// cudaGetSymbolAddress returns for the device that is current.
+static std::map<int, float*> g_mriq_static_addr;
+
+TK_API int tk_mriq_compute_static(const float* kx, const float* ky, const float* kz, const float* phiR,
+                                  const float* phiI, int numK, const float* x, const float* y, const float* z,
+                                  float* Qr, float* Qi, int numX, void* stream) {
+    if (numK < 0 || numX < 0) return TK_ERR_ARGS;
+    if (numK > TK_MRIQ_STATIC_MAX_K) {
+        t_last_error = "tk_mriq_compute_static: numK = " + std::to_string(numK) + " exceeds the fixed table of " +
+                       std::to_string(TK_MRIQ_STATIC_MAX_K) + " samples; use tk_mriq_compute with caller scratch";
+        return TK_ERR_CAPACITY;
+    }
+    int dev = 0;
+    TK_CUDA(cudaGetDevice(&dev));
+    float* table = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        auto it = g_mriq_static_addr.find(dev);
+        if (it == g_mriq_static_addr.end()) {
+            void* p = nullptr;
+            TK_CUDA(cudaGetSymbolAddress(&p, g_mriq_static_kvals));  // once per device, that device current
+            it = g_mriq_static_addr.emplace(dev, static_cast<float*>(p)).first;
+        }
+        table = it->second;
+    }
+    // entries [0, numK) are rewritten by the pack step before the sum reads them; nothing is carried
+    // over from an earlier call and nothing needs clearing
+    return tk_mriq_compute(kx, ky, kz, phiR, phiI, numK, x, y, z, Qr, Qi, numX, table, stream);
+}

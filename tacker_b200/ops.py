@@ -285,6 +285,13 @@ def mriq_compute(kx, ky, kz, phiR, phiI, numK, x, y, z, Qr, Qi, numX, kvals_scra
                                 C.c_void_p(stream)), "tk_mriq_compute")
 
 
+def mriq_compute_static(kx, ky, kz, phiR, phiI, numK, x, y, z, Qr, Qi, numX, stream: int = 0) -> None:
+    """MRI-Q with the library's fixed k-space table instead of caller scratch (no allocation anywhere)."""
+    check(lib().tk_mriq_compute_static(*[C.c_void_p(p) for p in (kx, ky, kz, phiR, phiI)], numK,
+                                       *[C.c_void_p(p) for p in (x, y, z, Qr, Qi)], numX, C.c_void_p(stream)),
+          "tk_mriq_compute_static")
+
+
 def coulomb_compute(atoms_xyzq, numatoms, zplane, spacing, energygrid, nx, ny, packed_scratch,
                     stream: int = 0) -> None:
     check(lib().tk_coulomb_compute(C.c_void_p(atoms_xyzq), numatoms, C.c_float(zplane), C.c_float(spacing),
