@@ -225,6 +225,36 @@ int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, float* C
                                 int ny, int nz, int sweeps, int cd_threads, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/* ---- layer kernels of the LC / BE DNN tasks -------------------------------------------------------------
+ * The reference's generated DNN classes call cuDNN / cuBLAS and NNFusion element-wise kernels for
+ * everything that is not routed to tzgemm (src/dnn/<model>/*_kernel_class.h); these are the hand-written
+ * stand-ins.  Activations are fp32, NHWC for images, [rows][cols] for sequences.
+ * tk_im2col_nhwc_f16: conv input -> tzgemm A operand in one pass (im2col_gpu_kernel + convertFp32ToFp16,
+ *   src/include/dnn.h:45-99): A[m][k] fp16, m = oh*OW + ow, k = (i*kw + j)*C + c, zero padded to
+ *   M_pad x K_pad (K_pad % 8 == 0). */
+int tk_im2col_nhwc_f16(const float* x, int H, int W, int C, int kh, int kw, int pad, int stride, void* A_half,
+                       int M_pad, int K_pad, void* stream);
+/* fp32 [rows][ld_in] -> fp16 [rows_pad][cols_pad], zero padded (FC input -> tzgemm A operand) */
+int tk_rows_f32_to_f16(const float* x, int rows, int cols, int ld_in, void* A_half, int rows_pad, int cols_pad,
+                       void* stream);
+/* out[r][c] = act(x[r][c] + bias[c]); act 0 none, 1 relu, 2 gelu; bias may be null */
+int tk_bias_act_f32(const float* x, int ldx, const float* bias, float* out, int rows, int cols, int ld_out, int act,
+                    void* stream);
+int tk_maxpool2x2_nhwc_f32(const float* x, int H, int W, int C, float* out, void* stream);
+int tk_add_f32(const float* a, const float* b, float* out, long long n, void* stream);
+int tk_softmax_rows_f32(const float* x, float* out, long long rows, int cols, float scale, void* stream);
+int tk_layernorm_rows_f32(const float* x, const float* gamma, const float* beta, float* out, long long rows, int cols,
+                          float eps, void* stream);
+/* x [B*S][ld] fp32, `heads` blocks of `dh` columns from col0 -> fp16 [B*heads][S][dh] (transpose 0) or
+ * [B*heads][dh][S] (transpose 1); and the way back for the attention context */
+int tk_split_heads_f16(const float* x, int ld, int col0, int B, int S, int heads, int dh, int transpose,
+                       void* out_half, void* stream);
+int tk_merge_heads_f32(const float* ctx, int B, int S, int heads, int dh, float* out, void* stream);
+/* `batch` independent tzgemms of one shape in one launch (the attention GEMMs; the reference calls
+ * cublasSgemmStridedBatched, src/dnn/bert/bert_kernel_class.h:2049).  Strides in elements, 0 = dense. */
+int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int N, int K, int batch, long long stride_a,
+                      long long stride_b, long long stride_c, float alpha, void* stream);
+
 /* ---- MRI-Q for callers that cannot allocate device memory ----------------------------------------------
  * (No counterpart in the reference: it always cudaMallocs its buffers up front.)
  * Same computation and same results as tk_mriq_compute, but the packed k-space table is a fixed array

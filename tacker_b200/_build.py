@@ -63,11 +63,28 @@ def build_host(force: bool = False) -> str | None:
         return None
     if not force and _newer(AKER_PATH, srcs + [LIB_PATH]):
         return AKER_PATH
+    units = [u for u in units if os.sep + "tests" + os.sep not in u]
     cmd = [_nvcc(), "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
            "-I", os.path.join(ROOT, "..", "include"), "-I", HOST, "-o", AKER_PATH, *units,
-           "-L", LIB_DIR, "-ltacker_b200", "-Xlinker", "-rpath,$ORIGIN"]
+           "-L", LIB_DIR, "-ltacker_b200", "-ldl", "-Xlinker", "-rpath,$ORIGIN"]
     subprocess.check_call(cmd)
     return AKER_PATH
+
+
+def build_host_selftest(force: bool = False) -> str:
+    """Host runtime linked against a recording double of the library (no GPU, no CUDA): marshalling,
+    registry, JSON, scheduling rules.  Test infrastructure."""
+    out = os.path.join(LIB_DIR, "host_selftest")
+    srcs = _sources(HOST, (".cc", ".h"))
+    units = [s for s in srcs if s.endswith(".cc") and not s.endswith(("CudaBackend.cc", "main.cc"))]
+    if not force and _newer(out, srcs):
+        return out
+    os.makedirs(LIB_DIR, exist_ok=True)
+    cxx = shutil.which("g++") or "g++"
+    cmd = [cxx, "-O1", "-g", "-std=c++17", "-Wall", "-I", os.path.join(ROOT, "..", "include"), "-I", HOST,
+           "-o", out, *units, "-ldl"]
+    subprocess.check_call(cmd)
+    return out
 
 
 if __name__ == "__main__":

@@ -31,8 +31,10 @@ struct GemmArgs {
     float* C;
     int M, N, K;
     float alpha;
-    int start, end;    // 64x64 tiles, row-major over (M/64) x (N/64)
-    unsigned* status;  // device status word (bounded-wait expiries)
+    int start, end;      // 64x64 tiles, row-major over (M/64) x (N/64)
+    unsigned* status;    // device status word (bounded-wait expiries)
+    int batch;           // independent problems of the same shape (1 for the reference's tzgemm)
+    long long stride_c;  // elements between consecutive C matrices of a batch
 };
 
 template <int BN, int STAGES>
@@ -54,7 +56,8 @@ struct SuperTileWalk {
     int nt;     // 64-wide tiles per C row
     int sc;     // super-tile columns
     int r0;     // first super-tile row touched
-    int ncand;  // candidates = touched super-tile rows x sc
+    int ncand;  // candidates = batch x touched super-tile rows x sc
+    int per;    // candidates per batch entry
     int start, end, mt;
 
     __device__ __forceinline__ void init(const GemmArgs& g) {
@@ -63,6 +66,7 @@ struct SuperTileWalk {
         sc = (g.N + BN - 1) / BN;
         start = g.start < 0 ? 0 : g.start;
         end = g.end > nt * mt ? nt * mt : g.end;
+        per = 1;
         if (start >= end) {
             ncand = 0;
             r0 = 0;
@@ -70,11 +74,14 @@ struct SuperTileWalk {
         }
         r0 = (start / nt) / 2;
         const int r1 = ((end - 1) / nt) / 2;
-        ncand = (r1 - r0 + 1) * sc;
+        per = (r1 - r0 + 1) * sc;
+        ncand = per * (g.batch > 0 ? g.batch : 1);
     }
 
     // bit (h * (BN/64) + cb) set <=> sub-tile (64-row half h, 64-column block cb) is in range
-    __device__ __forceinline__ uint32_t mask(int cand, int& R, int& Cc) const {
+    __device__ __forceinline__ uint32_t mask(int cand, int& R, int& Cc, int& b) const {
+        b = cand / per;
+        cand -= b * per;
         R = r0 + cand / sc;
         Cc = cand % sc;
         uint32_t m = 0;
@@ -146,15 +153,15 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
             uint32_t phase = 0;
             bool ok = true;
             for (int cand = blockIdx.x; cand < walk.ncand && ok; cand += gridDim.x) {
-                int R, Cc;
-                if (walk.mask(cand, R, Cc) == 0u) continue;
+                int R, Cc, b;
+                if (walk.mask(cand, R, Cc, b) == 0u) continue;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
                     mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
-                    tma_load_2d(a_dst, tmap_a, full_bar(stage), kb * kGemmBK, R * kGemmBM);
-                    tma_load_2d(a_dst + L::kABytes, tmap_b, full_bar(stage), kb * kGemmBK, Cc * BN);
+                    tma_load_tile(a_dst, tmap_a, full_bar(stage), kb * kGemmBK, R * kGemmBM, b);
+                    tma_load_tile(a_dst + L::kABytes, tmap_b, full_bar(stage), kb * kGemmBK, Cc * BN, b);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -179,8 +186,8 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
             uint32_t it = 0;
             bool ok = true;
             for (int cand = blockIdx.x; cand < walk.ncand && ok; cand += gridDim.x) {
-                int R, Cc;
-                if (walk.mask(cand, R, Cc) == 0u) continue;
+                int R, Cc, b;
+                if (walk.mask(cand, R, Cc, b) == 0u) continue;
                 const uint32_t as = it & 1u, aphase = (it >> 1) & 1u;
                 ok = mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
@@ -216,15 +223,16 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
         uint32_t it = 0;
         bool ok = true;
         for (int cand = blockIdx.x; cand < walk.ncand && ok; cand += gridDim.x) {
-            int R, Cc;
-            const uint32_t m = walk.mask(cand, R, Cc);
+            int R, Cc, b;
+            const uint32_t m = walk.mask(cand, R, Cc, b);
             if (m == 0u) continue;
             const uint32_t as = it & 1u, aphase = (it >> 1) & 1u;
             ok = mbar_wait(tfull_bar(as), aphase, abort_flag, g.status, DEV_TIMEOUT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after_sync();
             const int row = R * kGemmBM + q * 32 + lane;
-            float* crow = g.C + static_cast<size_t>(row) * g.N + static_cast<size_t>(Cc) * BN;
+            float* crow = g.C + static_cast<size_t>(b) * g.stride_c + static_cast<size_t>(row) * g.N +
+                          static_cast<size_t>(Cc) * BN;
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {

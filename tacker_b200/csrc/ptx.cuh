@@ -110,6 +110,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap,
         : "memory");
 }
 
+// operand tiles of the GEMM: tensor maps are {K, rows, batch}, the box is one K-block x rows x 1
+__device__ __forceinline__ void tma_load_tile(uint32_t dst_smem, const void* tmap, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 // ---- tcgen05 ---------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t result_slot_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot_smem),

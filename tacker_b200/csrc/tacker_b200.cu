@@ -257,15 +257,18 @@ static int get_encoder() {
     return TK_OK;
 }
 
-// fp16 matrix [rows][k], k contiguous; box = 64 (k) x box_rows, 128-byte swizzle
-static int make_tmap(CUtensorMap* m, const void* base, int rows, int k, int box_rows) {
+// fp16 matrices [batch][rows][k], k contiguous; box = 64 (k) x box_rows x 1, 128-byte swizzle
+static int make_tmap(CUtensorMap* m, const void* base, int rows, int k, int box_rows, int batch = 1,
+                     long long batch_stride_elems = 0) {
     int rc = get_encoder();
     if (rc != TK_OK) return rc;
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(kGemmBK), static_cast<cuuint32_t>(box_rows)};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    if (batch < 1) batch = 1;
+    if (batch_stride_elems <= 0) batch_stride_elems = static_cast<long long>(rows) * k;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(k) * 2, static_cast<cuuint64_t>(batch_stride_elems) * 2};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(kGemmBK), static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -319,6 +322,7 @@ struct GemmCall {
     const __half* A;
     const __half* B;
     GemmArgs g;
+    long long stride_a = 0, stride_b = 0;  // elements between batch entries (0 = dense)
 };
 
 // params[base .. base+6] = A, B, C, M, N, K, alpha; start/end at the given indices
@@ -333,6 +337,8 @@ static int parse_gemm(void** params, int base, int i_start, int i_end, GemmCall*
     c->g.start = arg<int>(params, i_start);
     c->g.end = arg<int>(params, i_end);
     c->g.status = nullptr;
+    c->g.batch = 1;
+    c->g.stride_c = 0;
     const bool empty = c->g.start >= c->g.end;
     if (c->g.M < 128 || c->g.N < 64 || c->g.K < 64) return TK_ERR_SHAPE;
     if (c->g.M % 128 || c->g.N % 64 || c->g.K % 64) return TK_ERR_SHAPE;
@@ -456,9 +462,9 @@ template <int BN>
 static int launch_tzgemm(const GemmCall& c, unsigned ctas, cudaStream_t st) {
     constexpr int STAGES = StagesFor<BN>::value;
     CUtensorMap ta, tb;
-    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
+    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM, c.g.batch, c.stride_a);
     if (rc != TK_OK) return rc;
-    rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN);
+    rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN, c.g.batch, c.stride_b);
     if (rc != TK_OK) return rc;
     auto kernel = tzgemm_kernel<BN, STAGES>;
     rc = enable_smem(kernel, gemm_smem_bytes<BN>());
@@ -1133,6 +1139,8 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     c.g.K = K;
     c.g.alpha = alpha;
     c.g.status = nullptr;
+    c.g.batch = 1;
+    c.g.stride_c = 0;
     if (M < 128 || N < 64 || K < 64 || M % 128 || N % 64 || K % 64) return TK_ERR_SHAPE;
     const int tiles = (M / 64) * (N / 64);
     CdCall cd;
@@ -1196,4 +1204,287 @@ TK_API int tk_mriq_compute_static(const float* kx, const float* ky, const float*
     // entries [0, numK) are rewritten by the pack step before the sum reads them; nothing is carried
     // over from an earlier call and nothing needs clearing
     return tk_mriq_compute(kx, ky, kz, phiR, phiI, numK, x, y, z, Qr, Qi, numX, table, stream);
+}
+
+// =================================================================================================
+// LC / BE layer kernels around tzgemm (the DNN tasks' non-GEMM nodes) and the batched GEMM
+// =================================================================================================
+namespace tk {
+
+// A[m][k] fp16, m = oh * OW + ow, k = (i * kw + j) * C + c, from an NHWC fp32 image; rows >= M and
+// columns >= K are zero so that the padded operand can be fed to tzgemm unchanged.
+__global__ void im2col_nhwc_f16_kernel(const float* __restrict__ x, int H, int W, int C, int kh, int kw, int pad,
+                                       int stride, int OH, int OW, __half* __restrict__ A, int M_pad, int K_pad) {
+    const long long total = static_cast<long long>(M_pad) * (K_pad / 8);
+    const int K = kh * kw * C, M = OH * OW;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int m = static_cast<int>(e / (K_pad / 8));
+        const int k0 = static_cast<int>(e % (K_pad / 8)) * 8;
+        __align__(16) __half v[8];
+        const int oh = m / OW, ow = m % OW;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int k = k0 + u;
+            float val = 0.0f;
+            if (m < M && k < K) {
+                const int tap = k / C, c = k % C;
+                const int hi = oh * stride - pad + tap / kw, wi = ow * stride - pad + tap % kw;
+                if (hi >= 0 && wi >= 0 && hi < H && wi < W) val = __ldg(x + (static_cast<size_t>(hi) * W + wi) * C + c);
+            }
+            v[u] = __float2half_rn(val);
+        }
+        *reinterpret_cast<uint4*>(A + static_cast<size_t>(m) * K_pad + k0) = *reinterpret_cast<const uint4*>(v);
+    }
+}
+
+// fp32 [rows][ld_in] -> fp16 [rows_pad][cols_pad], zero padded
+__global__ void rows_to_f16_kernel(const float* __restrict__ x, int rows, int cols, int ld_in, __half* __restrict__ A,
+                                   int rows_pad, int cols_pad) {
+    const long long total = static_cast<long long>(rows_pad) * cols_pad;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(e / cols_pad), c = static_cast<int>(e % cols_pad);
+        A[e] = __float2half_rn((r < rows && c < cols) ? __ldg(x + static_cast<size_t>(r) * ld_in + c) : 0.0f);
+    }
+}
+
+// out[r][c] = act(x[r][c] + bias[c]); act: 0 none, 1 relu, 2 gelu (tanh form)
+__global__ void bias_act_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ bias,
+                                float* __restrict__ out, int rows, int cols, int ldo, int act) {
+    const long long total = static_cast<long long>(rows) * cols;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(e / cols), c = static_cast<int>(e % cols);
+        float v = x[static_cast<size_t>(r) * ldx + c] + (bias ? __ldg(bias + c) : 0.0f);
+        if (act == 1) v = fmaxf(v, 0.0f);
+        else if (act == 2) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        out[static_cast<size_t>(r) * ldo + c] = v;
+    }
+}
+
+__global__ void maxpool2x2_nhwc_kernel(const float* __restrict__ x, int H, int W, int C, float* __restrict__ out) {
+    const int OH = H / 2, OW = W / 2;
+    const long long total = static_cast<long long>(OH) * OW * C;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int c = static_cast<int>(e % C);
+        const int ow = static_cast<int>((e / C) % OW), oh = static_cast<int>(e / (static_cast<long long>(C) * OW));
+        const float* p = x + (static_cast<size_t>(2 * oh) * W + 2 * ow) * C + c;
+        out[e] = fmaxf(fmaxf(p[0], p[C]), fmaxf(p[static_cast<size_t>(W) * C], p[static_cast<size_t>(W) * C + C]));
+    }
+}
+
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                           long long n) {
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < n;
+         e += static_cast<long long>(gridDim.x) * blockDim.x)
+        out[e] = a[e] + b[e];
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// one warp per row: out = softmax(scale * x) over `cols`
+__global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restrict__ out, long long rows, int cols,
+                                    float scale) {
+    const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* xr = x + row * cols;
+    float* orow = out + row * cols;
+    float m = -INFINITY;
+    for (int c = lane; c < cols; c += 32) m = fmaxf(m, scale * xr[c]);
+    m = warp_max(m);
+    float s = 0.0f;
+    for (int c = lane; c < cols; c += 32) s += __expf(scale * xr[c] - m);
+    s = warp_sum(s);
+    const float inv = 1.0f / s;
+    for (int c = lane; c < cols; c += 32) orow[c] = __expf(scale * xr[c] - m) * inv;
+}
+
+// one warp per row: out = (x - mean) / sqrt(var + eps) * gamma + beta
+__global__ void layernorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                      const float* __restrict__ beta, float* __restrict__ out, long long rows,
+                                      int cols, float eps) {
+    const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* xr = x + row * cols;
+    float s = 0.0f;
+    for (int c = lane; c < cols; c += 32) s += xr[c];
+    const float mean = warp_sum(s) / cols;
+    float v = 0.0f;
+    for (int c = lane; c < cols; c += 32) {
+        const float d = xr[c] - mean;
+        v += d * d;
+    }
+    const float rstd = rsqrtf(warp_sum(v) / cols + eps);
+    for (int c = lane; c < cols; c += 32)
+        out[row * cols + c] = (xr[c] - mean) * rstd * (gamma ? gamma[c] : 1.0f) + (beta ? beta[c] : 0.0f);
+}
+
+// x [B*S][ld] fp32 holding `heads` blocks of `dh` columns from column `col0` on ->
+//   transpose == 0: out [B*heads][S][dh] fp16;  transpose == 1: out [B*heads][dh][S] fp16
+__global__ void split_heads_kernel(const float* __restrict__ x, int ld, int col0, int B, int S, int heads, int dh,
+                                   int transpose, __half* __restrict__ out) {
+    const long long total = static_cast<long long>(B) * heads * S * dh;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int d = static_cast<int>(e % dh);
+        const int s = static_cast<int>((e / dh) % S);
+        const int h = static_cast<int>((e / (static_cast<long long>(dh) * S)) % heads);
+        const int b = static_cast<int>(e / (static_cast<long long>(dh) * S * heads));
+        const float v = __ldg(x + (static_cast<size_t>(b) * S + s) * ld + col0 + h * dh + d);
+        const size_t base = (static_cast<size_t>(b) * heads + h) * S * dh;
+        out[transpose ? base + static_cast<size_t>(d) * S + s : base + static_cast<size_t>(s) * dh + d] =
+            __float2half_rn(v);
+    }
+}
+
+// ctx [B*heads][S][dh] fp32 -> out [B*S][heads*dh] fp32
+__global__ void merge_heads_kernel(const float* __restrict__ ctx, int B, int S, int heads, int dh,
+                                   float* __restrict__ out) {
+    const long long total = static_cast<long long>(B) * heads * S * dh;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int d = static_cast<int>(e % dh);
+        const int s = static_cast<int>((e / dh) % S);
+        const int h = static_cast<int>((e / (static_cast<long long>(dh) * S)) % heads);
+        const int b = static_cast<int>(e / (static_cast<long long>(dh) * S * heads));
+        out[(static_cast<size_t>(b) * S + s) * heads * dh + h * dh + d] = ctx[e];
+    }
+}
+
+static unsigned blocks_for(long long work_items, int sm_count) {
+    long long b = (work_items + 255) / 256;
+    const long long cap = static_cast<long long>(sm_count) * 8;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return static_cast<unsigned>(b);
+}
+
+}  // namespace tk
+
+#define TK_LAYER_PROLOGUE()                      \
+    DeviceInfo* d = nullptr;                     \
+    {                                            \
+        int _rc = device_info(&d);               \
+        if (_rc != TK_OK) return _rc;            \
+    }                                            \
+    cudaStream_t st = static_cast<cudaStream_t>(stream)
+
+TK_API int tk_im2col_nhwc_f16(const float* x, int H, int W, int C, int kh, int kw, int pad, int stride, void* A_half,
+                              int M_pad, int K_pad, void* stream) {
+    if (!x || !A_half || H <= 0 || W <= 0 || C <= 0 || kh <= 0 || kw <= 0 || pad < 0 || stride <= 0) return TK_ERR_ARGS;
+    const int OH = (H + 2 * pad - kh) / stride + 1, OW = (W + 2 * pad - kw) / stride + 1;
+    if (OH <= 0 || OW <= 0 || M_pad < OH * OW || K_pad < kh * kw * C || K_pad % 8) return TK_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(A_half) & 15u) return TK_ERR_ALIGN;
+    TK_LAYER_PROLOGUE();
+    im2col_nhwc_f16_kernel<<<blocks_for(static_cast<long long>(M_pad) * (K_pad / 8), d->sm_count), 256, 0, st>>>(
+        x, H, W, C, kh, kw, pad, stride, OH, OW, static_cast<__half*>(A_half), M_pad, K_pad);
+    return launch_error("im2col_nhwc_f16_kernel launch");
+}
+
+TK_API int tk_rows_f32_to_f16(const float* x, int rows, int cols, int ld_in, void* A_half, int rows_pad, int cols_pad,
+                              void* stream) {
+    if (!x || !A_half || rows <= 0 || cols <= 0 || ld_in < cols || rows_pad < rows || cols_pad < cols) return TK_ERR_ARGS;
+    TK_LAYER_PROLOGUE();
+    rows_to_f16_kernel<<<blocks_for(static_cast<long long>(rows_pad) * cols_pad, d->sm_count), 256, 0, st>>>(
+        x, rows, cols, ld_in, static_cast<__half*>(A_half), rows_pad, cols_pad);
+    return launch_error("rows_to_f16_kernel launch");
+}
+
+TK_API int tk_bias_act_f32(const float* x, int ldx, const float* bias, float* out, int rows, int cols, int ld_out,
+                           int act, void* stream) {
+    if (!x || !out || rows <= 0 || cols <= 0 || ldx < cols || ld_out < cols || act < 0 || act > 2) return TK_ERR_ARGS;
+    TK_LAYER_PROLOGUE();
+    bias_act_kernel<<<blocks_for(static_cast<long long>(rows) * cols, d->sm_count), 256, 0, st>>>(x, ldx, bias, out, rows,
+                                                                                                cols, ld_out, act);
+    return launch_error("bias_act_kernel launch");
+}
+
+TK_API int tk_maxpool2x2_nhwc_f32(const float* x, int H, int W, int C, float* out, void* stream) {
+    if (!x || !out || H < 2 || W < 2 || C <= 0) return TK_ERR_ARGS;
+    TK_LAYER_PROLOGUE();
+    maxpool2x2_nhwc_kernel<<<blocks_for(static_cast<long long>(H / 2) * (W / 2) * C, d->sm_count), 256, 0, st>>>(x, H, W, C,
+                                                                                                               out);
+    return launch_error("maxpool2x2_nhwc_kernel launch");
+}
+
+TK_API int tk_add_f32(const float* a, const float* b, float* out, long long n, void* stream) {
+    if (!a || !b || !out || n <= 0) return TK_ERR_ARGS;
+    TK_LAYER_PROLOGUE();
+    add_kernel<<<blocks_for(n, d->sm_count), 256, 0, st>>>(a, b, out, n);
+    return launch_error("add_kernel launch");
+}
+
+TK_API int tk_softmax_rows_f32(const float* x, float* out, long long rows, int cols, float scale, void* stream) {
+    if (!x || !out || rows <= 0 || cols <= 0) return TK_ERR_ARGS;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    softmax_rows_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(x, out, rows, cols, scale);
+    return launch_error("softmax_rows_kernel launch");
+}
+
+TK_API int tk_layernorm_rows_f32(const float* x, const float* gamma, const float* beta, float* out, long long rows,
+                                 int cols, float eps, void* stream) {
+    if (!x || !out || rows <= 0 || cols <= 0) return TK_ERR_ARGS;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    layernorm_rows_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(x, gamma, beta, out, rows, cols,
+                                                                                          eps);
+    return launch_error("layernorm_rows_kernel launch");
+}
+
+TK_API int tk_split_heads_f16(const float* x, int ld, int col0, int B, int S, int heads, int dh, int transpose,
+                              void* out_half, void* stream) {
+    if (!x || !out_half || B <= 0 || S <= 0 || heads <= 0 || dh <= 0 || col0 < 0 || ld < col0 + heads * dh)
+        return TK_ERR_ARGS;
+    TK_LAYER_PROLOGUE();
+    split_heads_kernel<<<blocks_for(static_cast<long long>(B) * heads * S * dh, d->sm_count), 256, 0, st>>>(
+        x, ld, col0, B, S, heads, dh, transpose, static_cast<__half*>(out_half));
+    return launch_error("split_heads_kernel launch");
+}
+
+TK_API int tk_merge_heads_f32(const float* ctx, int B, int S, int heads, int dh, float* out, void* stream) {
+    if (!ctx || !out || B <= 0 || S <= 0 || heads <= 0 || dh <= 0) return TK_ERR_ARGS;
+    TK_LAYER_PROLOGUE();
+    merge_heads_kernel<<<blocks_for(static_cast<long long>(B) * heads * S * dh, d->sm_count), 256, 0, st>>>(ctx, B, S, heads,
+                                                                                                         dh, out);
+    return launch_error("merge_heads_kernel launch");
+}
+
+TK_API int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int N, int K, int batch, long long stride_a,
+                             long long stride_b, long long stride_c, float alpha, void* stream) {
+    if (!A || !B || !C || batch < 1) return TK_ERR_ARGS;
+    if (M < 128 || N < 64 || K < 64 || M % 128 || N % 64 || K % 64) return TK_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u) ||
+        (reinterpret_cast<uintptr_t>(C) & 15u) || (stride_a % 8) || (stride_b % 8) || (stride_c % 4))
+        return TK_ERR_ALIGN;
+    GemmCall c;
+    c.A = static_cast<const __half*>(A);
+    c.B = static_cast<const __half*>(B);
+    c.stride_a = stride_a > 0 ? stride_a : static_cast<long long>(M) * K;
+    c.stride_b = stride_b > 0 ? stride_b : static_cast<long long>(N) * K;
+    c.g.C = C;
+    c.g.M = M;
+    c.g.N = N;
+    c.g.K = K;
+    c.g.alpha = alpha;
+    c.g.start = 0;
+    c.g.end = (M / 64) * (N / 64);
+    c.g.status = nullptr;
+    c.g.batch = batch;
+    c.g.stride_c = stride_c > 0 ? stride_c : static_cast<long long>(M) * N;
+    DeviceInfo* d = nullptr;
+    int rc = device_info(&d);
+    if (rc != TK_OK) return rc;
+    return run_tzgemm(c, static_cast<unsigned>(d->sm_count), static_cast<cudaStream_t>(stream));
 }

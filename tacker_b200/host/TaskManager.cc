@@ -1,0 +1,267 @@
+#include "TaskManager.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <map>
+#include <memory>
+
+#include "Logger.h"
+#include "Recorder.h"
+#include "json.h"
+
+std::vector<int> get_mnk_from_cudnn_args(std::vector<int>& a) {
+    int mnk[3];
+    tk_conv_mnk(a.data(), mnk);
+    return std::vector<int>(mnk, mnk + 3);
+}
+
+namespace {
+std::map<std::pair<TzLayer*, GPTBKernel*>, std::unique_ptr<MixKernel>> g_mix_cache;
+
+void run_fused(TzLayer* layer, GPTBKernel* cd, int cd_start, int cd_end, stream_t stream) {
+    auto key = std::make_pair(layer, cd);
+    auto it = g_mix_cache.find(key);
+    if (it == g_mix_cache.end()) {
+        const std::string name = "tzgemm_" + cd->kernelName;
+        int per_sm = get_kernel_info(name, "gridsize"), threads = get_kernel_info(name, "blocksize");
+        if (per_sm == JSON_NOT_FOUND || per_sm <= 0) per_sm = 1;
+        if (threads == JSON_NOT_FOUND || threads <= 192) threads = 192 + 384;
+        it = g_mix_cache
+                 .emplace(key, std::unique_ptr<MixKernel>(new MixKernel(
+                                   1, name, cd, layer->gemm(), dim3h(static_cast<unsigned>(backend().smCount() * per_sm), 1, 1),
+                                   dim3h(static_cast<unsigned>(threads), 1, 1), cd_start, cd_end, 0, layer->tiles())))
+                 .first;
+    }
+    it->second->setRanges(cd_start, cd_end, 0, layer->tiles());
+    layer->prepare(stream);        // im2col / cast on the same stream as the fused launch
+    it->second->execute(stream);
+}
+
+double now_ms() {
+    using namespace std::chrono;
+    return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();
+}
+
+double percentile(std::vector<double> v, double p) {
+    if (v.empty()) return 0.0;
+    std::sort(v.begin(), v.end());
+    const double idx = p * (v.size() - 1);
+    const size_t lo = static_cast<size_t>(idx);
+    const size_t hi = std::min(lo + 1, v.size() - 1);
+    return v[lo] + (v[hi] - v[lo]) * (idx - lo);
+}
+}  // namespace
+
+void mixcudnnConvolutionForward(TzLayer* layer, GPTBKernel* cd, int cd_start_blk, int cd_end_blk, stream_t stream) {
+    run_fused(layer, cd, cd_start_blk, cd_end_blk, stream);
+}
+
+void mixcublasSgemm(TzLayer* layer, GPTBKernel* cd, int cd_start_blk, int cd_end_blk, stream_t stream) {
+    run_fused(layer, cd, cd_start_blk, cd_end_blk, stream);
+}
+
+TaskManager::TaskManager(Task* lc, const std::string& a, const std::string& b)
+    : lc_task(lc), be_task1_name(a), be_task2_name(b) {}
+
+float TaskManager::blockRatio(const std::string& pair, int k_global) {
+    float r = fget_kernel_info(pair, std::to_string(k_global));
+    if (r == static_cast<float>(JSON_NOT_FOUND)) {
+        const float base = fget_kernel_info(pair, "4096");  // src/TaskManager.cu:593-596
+        if (base == static_cast<float>(JSON_NOT_FOUND)) {
+            const float flat = fget_kernel_info(pair, "block_ratio");
+            return flat == static_cast<float>(JSON_NOT_FOUND) ? 0.0f : flat;
+        }
+        r = base * k_global / 4096.0f;
+    }
+    return r;
+}
+
+ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream) {
+    Backend& be = backend();
+    ScheduleResult res;
+    void* ev0 = be.eventCreate();
+    void* ev1 = be.eventCreate();
+    auto timed = [&](Kernel* k) {
+        be.eventRecord(ev0, stream);
+        k->execute(stream);
+        be.eventRecord(ev1, stream);
+        return be.eventElapsedMs(ev0, ev1);
+    };
+
+    for (int i = 0; i < warmup_passes; ++i) {
+        lc_task->initExecution();
+        lc_task->enqueue(stream);
+    }
+    be.streamSync(stream);
+
+    // ---- profile the LC task alone, kernel by kernel (src/TaskManager.cu:446-500) ----
+    const size_t n = lc_task->kernels.size();
+    std::vector<float> lc_kernel_time_vec(n, 0.0f);
+    for (int i = 0; i < profile_passes; ++i) {
+        lc_task->initExecution();
+        for (size_t k = 0; k < n; ++k) lc_kernel_time_vec[k] += timed(lc_task->kernels[k]);
+    }
+    for (auto& t : lc_kernel_time_vec) {
+        t /= profile_passes;
+        res.lc_solo_ms += t;
+    }
+    for (auto* k : lc_task->kernels) res.mixable_times += (k->mixable != 0);
+    std::vector<float> lc_headroom_vec(lc_kernel_time_vec);  // time still to come from kernel i on
+    for (int i = static_cast<int>(n) - 2; i >= 0; --i) lc_headroom_vec[i] += lc_headroom_vec[i + 1];
+    std::printf("\n[PRE]lc kernel took %f ms to execute.\n", res.lc_solo_ms);
+
+    // ---- the best-effort kernels alone (src/TaskManager.cu:533-561) ----
+    GPTBKernel* be_kernel1 = createKernel(be_task1_name);
+    GPTBKernel* be_task2 = be_task2_name.empty() ? nullptr : createKernel(be_task2_name);
+    for (int i = 0; i < 3; ++i) {
+        be_kernel1->execute(stream);
+        if (be_task2) be_task2->execute(stream);
+    }
+    be.streamSync(stream);
+    res.be1_ms = timed(be_kernel1);
+    if (be_task2) res.be2_ms = timed(be_task2);
+    const int be_blocks = be_kernel1->gptbParams.ptb_end_block_pos;
+    const std::string pair = "tzgemm_" + be_task1_name;
+
+    // ---- the scheduling passes (src/TaskManager.cu:563-656) ----
+    std::vector<char> skip(n, 0);  // layers whose fusion did not pay off in an earlier pass are not fused again
+    float qos_headroom = qos_budget_ms;
+    for (int pass = 0; pass < schedule_passes; ++pass) {
+        lc_task->initExecution();
+        be_kernel1->kernel_->initParams();
+        qos_headroom = qos_budget_ms;
+        long long cd_block_num_executed = 0;
+        int cd_cursor = be_kernel1->gptbParams.ptb_start_block_pos;
+        res.mix_times = 0;
+        res.time_earned = 0.0f;
+        res.lc_colocated_ms = 0.0f;
+        for (size_t idx = 0; idx < n; ++idx) {
+            Kernel* lc_kernel = lc_task->kernels[idx];
+            int cd_block_num = 0;
+            float duration;
+            const bool fuse = lc_kernel->mixable != 0 && !skip[idx] && !(qos_headroom < lc_headroom_vec[idx] + qos_guard_ms);
+            if (!fuse) {
+                duration = timed(lc_kernel);
+            } else {
+                TzLayer* layer = static_cast<TzLayer*>(lc_kernel);
+                std::vector<int> mnk = lc_kernel->mixable == 1 ? lc_kernel->getArgs() : [&] {
+                    std::vector<int> a = lc_kernel->getArgs();
+                    return get_mnk_from_cudnn_args(a);
+                }();
+                if (mnk.size() != 3) logger.ERROR("lc kernel: " + lc_kernel->kernelName + " mnk size is not 3");
+                if (mode == ExecutionMode::Tacker) {
+                    cd_block_num = be_blocks;
+                } else {
+                    cd_block_num = std::min(static_cast<int>(layer->tiles() * blockRatio(pair, layer->K_pad)), be_blocks);
+                }
+                int cd_start = cd_cursor, cd_end = std::min(cd_cursor + cd_block_num, be_blocks);
+                if (cd_end <= cd_start) {  // the best-effort job is finished: start its next instance
+                    cd_start = 0;
+                    cd_end = std::min(cd_block_num, be_blocks);
+                }
+                cd_block_num = cd_end - cd_start;
+                be.eventRecord(ev0, stream);
+                if (lc_kernel->mixable == 1) mixcublasSgemm(layer, be_kernel1, cd_start, cd_end, stream);
+                else mixcudnnConvolutionForward(layer, be_kernel1, cd_start, cd_end, stream);
+                be.eventRecord(ev1, stream);
+                duration = be.eventElapsedMs(ev0, ev1);
+                cd_cursor = cd_end >= be_blocks ? 0 : cd_end;
+            }
+            // account the fusion only where it beat running the same work one after the other
+            const float unfused = lc_kernel_time_vec[idx] + res.be1_ms * cd_block_num / std::max(be_blocks, 1);
+            if (!fuse) {
+                qos_headroom -= lc_kernel_time_vec[idx];
+            } else if (duration > unfused) {
+                qos_headroom -= duration;  // it ran, so its time is spent (the reference books the solo time here)
+                skip[idx] = 1;
+            } else {
+                qos_headroom -= duration;
+                cd_block_num_executed += cd_block_num;
+                res.mix_times += 1;
+                res.time_earned += unfused - duration;
+            }
+            res.lc_colocated_ms += duration;
+        }
+        res.be_blocks = cd_block_num_executed;
+    }
+    res.qos_headroom_left = qos_headroom;
+    std::printf("execed be blks: %lld, mix times: %d/%d, time earned: %f\n", res.be_blocks, res.mix_times,
+                res.mixable_times, res.time_earned);
+    std::printf("[Ori] be_task1: %s, be_task2: %s\n", be_task1_name.c_str(), be_task2_name.c_str());
+    std::printf("[Ori] BE task1 + task2 took %f + %f = %f ms to execute.\n", res.be1_ms, res.be2_ms,
+                res.be1_ms + res.be2_ms);
+    // best-effort work done inside the budget: blocks co-run with the LC task, then the leftover budget
+    res.stage1_be_ms = res.be_blocks * res.be1_ms / std::max(be_blocks, 1);
+    res.stage2_be_ms = std::max(0.0f, qos_headroom);
+    std::printf("[Result] %s BE task took %f + %f(%f) = %f ms to execute.\n", mode == ExecutionMode::Aker ? "Aker" : "Tacker",
+                res.stage1_be_ms, res.stage2_be_ms, qos_headroom, res.stage1_be_ms + res.stage2_be_ms);
+    be.eventDestroy(ev0);
+    be.eventDestroy(ev1);
+    return res;
+}
+
+ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pass, double seconds, double qps,
+                                            double qos_factor, uint64_t seed, stream_t stream) {
+    Backend& be = backend();
+    ColocationResult r;
+    // ---- solo latency of the LC task: back-to-back queries, nothing else on the GPU ----
+    for (int i = 0; i < warmup_passes; ++i) {
+        lc_task->initExecution();
+        lc_task->enqueue(stream);
+        be_task->initExecution();
+        be_task->enqueue(stream);
+    }
+    be.streamSync(stream);
+    std::vector<double> solo;
+    for (int i = 0; i < 200; ++i) {
+        const double t0 = now_ms();
+        lc_task->initExecution();
+        lc_task->enqueue(stream);
+        be.streamSync(stream);
+        solo.push_back(now_ms() - t0);
+    }
+    r.lc_solo_p50_ms = percentile(solo, 0.50);
+    r.lc_solo_p99_ms = percentile(solo, 0.99);
+    r.qos_bound_ms = qos_factor * r.lc_solo_p99_ms;
+
+    // ---- Poisson arrivals; the best-effort task fills the gaps one kernel at a time ----
+    std::vector<double> arrivals;
+    double t = 0.0;
+    for (uint64_t i = 0; t < seconds * 1e3; ++i) {
+        t += -std::log(1.0 - static_cast<double>(tk_unit_draw(seed, i))) / qps * 1e3;
+        arrivals.push_back(t);
+    }
+    std::vector<double> lat;
+    size_t next = 0, be_pos = 0;
+    const double start = now_ms();
+    be_task->initExecution();
+    while (true) {
+        const double now = now_ms() - start;
+        if (now >= seconds * 1e3) break;
+        if (next < arrivals.size() && arrivals[next] <= now) {
+            lc_task->initExecution();
+            lc_task->enqueue(stream);
+            be.streamSync(stream);
+            lat.push_back(now_ms() - start - arrivals[next]);
+            ++next;
+            continue;
+        }
+        // idle until the next arrival: one best-effort kernel, then look at the clock again
+        be_task->kernels[be_pos]->execute(stream);
+        be.streamSync(stream);
+        if (++be_pos == be_task->kernels.size()) {
+            be_pos = 0;
+            r.be_queries += be_queries_per_pass;
+            be_task->initExecution();
+        }
+    }
+    r.seconds = (now_ms() - start) / 1e3;
+    r.lc_served = static_cast<long long>(lat.size());
+    r.lc_p50_ms = percentile(lat, 0.50);
+    r.lc_p99_ms = percentile(lat, 0.99);
+    r.be_qps = r.be_queries / std::max(r.seconds, 1e-9);
+    r.qos_met = r.lc_p99_ms <= r.qos_bound_ms;
+    return r;
+}

@@ -1,0 +1,101 @@
+// dnn/layers.h -- the layer kernels the model tasks are made of.
+// The reference generates one Kernel subclass per graph node (src/dnn/<model>/*_kernel_class.h) and routes
+// convolutions and dense layers to tzgemm through mycudnnConvolutionForward / mycublasSgemm
+// (src/include/dnn.h:554-880): convolutions carry mixable = 2 and their 14 cuDNN ints, dense layers
+// mixable = 1 and (m, n, k); everything else is mixable = 0.  The same contract holds here, with the nodes
+// written by hand and kept on real buffers: activations flow through the task's arena (fp32, NHWC).
+#pragma once
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../GPTBKernel.h"
+#include "../tzgemm_kernel.h"
+
+// Device memory of one model instance: activations, fp16 GEMM operands, weights.
+struct DnnArena {
+    ~DnnArena();
+    float* act(size_t floats);              // a new fp32 activation buffer
+    void* half(size_t halves);              // a new fp16 buffer
+    void* weightsHalf(size_t halves, uint64_t seed, float scale);  // seeded fp16 weights, uniform * scale
+    float* weightsF32(size_t n, uint64_t seed, float lo, float hi);
+    size_t bytes = 0;
+    std::vector<void*> owned;
+};
+
+inline int roundUp(int v, int m) { return ((v + m - 1) / m) * m; }
+
+// Common part of the two tzgemm-backed layers: operands, the persistent GEMM kernel over all tiles and
+// what the scheduler needs to fuse it with a best-effort kernel.
+class TzLayer : public Kernel {
+public:
+    // GEMM over the padded operands: M_pad x N_pad x K_pad, alpha = 1
+    void buildGemm(int id);
+    virtual void prepare(stream_t stream) = 0;  // fill the fp16 A operand from the layer input
+    GPTBKernel* gemm() { return gptb.get(); }
+    int tiles() const { return ori->ori_blks; }
+    int M = 0, N = 0, K = 0, M_pad = 0, N_pad = 0, K_pad = 0;
+    void* A = nullptr;   // fp16 [M_pad][K_pad]
+    void* B = nullptr;   // fp16 [N_pad][K_pad] weights
+    float* C = nullptr;  // fp32 [M_pad][N_pad]
+    void initParams() override {}
+    void loadKernel() override {}
+
+protected:
+    void executeImpl(stream_t stream) override {  // solo LC path: operand preparation + tzgemm alone
+        prepare(stream);
+        gptb->execute(stream);
+    }
+    std::unique_ptr<OriTZGEMMKernel> ori;
+    std::unique_ptr<GPTBKernel> gptb;
+};
+
+// 2-D convolution, NHWC, square kernel (mixable = 2; getArgs = the 14 ints of cudnnConvolutionForward in
+// the order get_mnk_from_cudnn_args reads them, src/TaskManager.cu:92-123)
+class ConvKernel : public TzLayer {
+public:
+    ConvKernel(int id, const std::string& name, DnnArena& arena, const float* input, int H, int W, int Cin, int Cout,
+               int ksize, int pad, int stride, uint64_t seed);
+    std::vector<int> getArgs() override;
+    void prepare(stream_t stream) override;
+    const float* input;
+    int H, W, Cin, Cout, ksize, pad, stride, OH, OW;
+};
+
+// dense layer y = x W^T on `rows` rows (mixable = 1; getArgs = m, n, k)
+class GemmKernel : public TzLayer {
+public:
+    GemmKernel(int id, const std::string& name, DnnArena& arena, const float* input, int rows, int in_features,
+               int out_features, uint64_t seed);
+    std::vector<int> getArgs() override { return std::vector<int>{M, N, K}; }
+    void prepare(stream_t stream) override;
+    const float* input;
+};
+
+// everything that is not a GEMM (mixable = 0): one call into the library
+class OpKernel : public Kernel {
+public:
+    enum Op { BiasAct, MaxPool, Add, SoftmaxRows, LayerNorm, SplitHeads, MergeHeads, BatchedGemm, RowsToHalf };
+    OpKernel(int id, const std::string& name, Op op) : op(op) {
+        Id = id;
+        kernelName = name;
+        mixable = 0;
+    }
+    void initParams() override {}
+    void loadKernel() override {}
+    std::vector<int> getArgs() override { return std::vector<int>(); }
+    Op op;
+    // operands (meaning depends on op; see layers.cc)
+    const float* a = nullptr;
+    const float* b = nullptr;
+    const float* c = nullptr;
+    float* out = nullptr;
+    void* hout = nullptr;
+    const void* ha = nullptr;
+    const void* hb = nullptr;
+    int i0 = 0, i1 = 0, i2 = 0, i3 = 0, i4 = 0, i5 = 0, i6 = 0;
+    float f0 = 0.0f;
+
+protected:
+    void executeImpl(stream_t stream) override;
+};

@@ -1,0 +1,257 @@
+#include "models.h"
+
+#include <cmath>
+
+#include "../Logger.h"
+
+DnnTask::~DnnTask() {}
+
+void DnnTask::initExecution() {
+    if (input && !hostInput.empty())
+        backend().upload(input, hostInput.data(), hostInput.size() * sizeof(float), nullptr);
+}
+
+size_t DnnTask::numMixable() const {
+    size_t n = 0;
+    for (auto* k : kernels) n += (k->mixable != 0);
+    return n;
+}
+
+double DnnTask::gemmFlops() const {
+    double f = 0.0;
+    for (auto* k : kernels)
+        if (k->mixable != 0) {
+            auto* t = static_cast<TzLayer*>(k);
+            f += 2.0 * t->M * t->N * t->K;
+        }
+    return f;
+}
+
+float* DnnTask::conv(const float* x, int H, int W, int Cin, int Cout, int k, int pad, int stride, int act, int* OH,
+                     int* OW) {
+    auto* c = new ConvKernel(nextId++, "Convolution_" + std::to_string(nextId), arena, x, H, W, Cin, Cout, k, pad, stride,
+                             1000 + nextId);
+    keep(c);
+    *OH = c->OH;
+    *OW = c->OW;
+    float* y = arena.act(static_cast<size_t>(c->M) * Cout);
+    float* bias = arena.weightsF32(Cout, 5000 + nextId, -0.05f, 0.05f);
+    auto* b = new OpKernel(nextId++, "BiasAct_" + std::to_string(nextId), OpKernel::BiasAct);
+    b->a = c->C;
+    b->b = bias;
+    b->out = y;
+    b->i0 = c->M;
+    b->i1 = Cout;
+    b->i2 = c->N_pad;
+    b->i3 = Cout;
+    b->i4 = act;
+    keep(b);
+    return y;
+}
+
+float* DnnTask::dense(const float* x, int rows, int in, int out, int act) {
+    auto* g = new GemmKernel(nextId++, "Dot_" + std::to_string(nextId), arena, x, rows, in, out, 2000 + nextId);
+    keep(g);
+    float* y = arena.act(static_cast<size_t>(rows) * out);
+    float* bias = arena.weightsF32(out, 6000 + nextId, -0.05f, 0.05f);
+    auto* b = new OpKernel(nextId++, "BiasAct_" + std::to_string(nextId), OpKernel::BiasAct);
+    b->a = g->C;
+    b->b = bias;
+    b->out = y;
+    b->i0 = rows;
+    b->i1 = out;
+    b->i2 = g->N_pad;
+    b->i3 = out;
+    b->i4 = act;
+    keep(b);
+    return y;
+}
+
+float* DnnTask::pool(const float* x, int H, int W, int C) {
+    float* y = arena.act(static_cast<size_t>(H / 2) * (W / 2) * C);
+    auto* p = new OpKernel(nextId++, "MaxPool_" + std::to_string(nextId), OpKernel::MaxPool);
+    p->a = x;
+    p->out = y;
+    p->i0 = H;
+    p->i1 = W;
+    p->i2 = C;
+    keep(p);
+    return y;
+}
+
+float* DnnTask::addTo(const float* a, const float* b, int rows, int cols, int act) {
+    float* y = arena.act(static_cast<size_t>(rows) * cols);
+    auto* k = new OpKernel(nextId++, "Add_" + std::to_string(nextId), OpKernel::Add);
+    k->a = a;
+    k->b = b;
+    k->out = y;
+    k->i0 = rows;
+    k->i1 = cols;
+    keep(k);
+    if (act) {
+        auto* r = new OpKernel(nextId++, "Relu_" + std::to_string(nextId), OpKernel::BiasAct);
+        r->a = y;
+        r->b = nullptr;
+        r->out = y;
+        r->i0 = rows;
+        r->i1 = cols;
+        r->i2 = cols;
+        r->i3 = cols;
+        r->i4 = act;
+        keep(r);
+    }
+    return y;
+}
+
+float* DnnTask::layernorm(const float* x, int rows, int cols) {
+    float* y = arena.act(static_cast<size_t>(rows) * cols);
+    auto* k = new OpKernel(nextId++, "LayerNorm_" + std::to_string(nextId), OpKernel::LayerNorm);
+    k->a = x;
+    k->b = arena.weightsF32(cols, 7000 + nextId, 0.9f, 1.1f);
+    k->c = arena.weightsF32(cols, 7500 + nextId, -0.05f, 0.05f);
+    k->out = y;
+    k->i0 = rows;
+    k->i1 = cols;
+    keep(k);
+    return y;
+}
+
+static void normal_input(std::vector<float>& h, uint64_t seed) {  // ~N(0,1) by Box-Muller on counter draws
+    for (size_t i = 0; i < h.size(); ++i) {
+        const float u1 = tk_unit_draw(seed, 2 * i) + 2.98e-8f, u2 = tk_unit_draw(seed, 2 * i + 1);
+        h[i] = std::sqrt(-2.0f * std::log(u1)) * std::cos(6.2831853f * u2);
+    }
+}
+
+// ------------------------------------------------------------------ VGG16 ----
+VGG16::VGG16(int numClasses) : DnnTask(0, "vgg16") {
+    taskType = LC;
+    int H = 224, W = 224, C = 3;
+    hostInput.resize(static_cast<size_t>(H) * W * C);
+    normal_input(hostInput, 42);
+    input = arena.act(hostInput.size());
+    const float* x = input;
+    const int cfg[] = {64, 64, -1, 128, 128, -1, 256, 256, 256, -1, 512, 512, 512, -1, 512, 512, 512, -1};
+    for (int c : cfg) {
+        if (c < 0) {
+            x = pool(x, H, W, C);
+            H /= 2;
+            W /= 2;
+        } else {
+            int oh, ow;
+            x = conv(x, H, W, C, c, 3, 1, 1, 1, &oh, &ow);
+            C = c;
+        }
+    }
+    x = dense(x, 1, H * W * C, 4096, 1);  // 7*7*512 = 25088
+    x = dense(x, 1, 4096, 4096, 1);
+    x = dense(x, 1, 4096, numClasses, 0);
+    float* probs = arena.act(numClasses);
+    auto* sm = new OpKernel(nextId++, "Softmax", OpKernel::SoftmaxRows);
+    sm->a = x;
+    sm->out = probs;
+    sm->i0 = 1;
+    sm->i1 = 1;
+    sm->i2 = numClasses;
+    sm->f0 = 1.0f;
+    keep(sm);
+}
+
+// --------------------------------------------------------------- ResNet-50 ----
+Resnet50::Resnet50(int numClasses) : DnnTask(1, "resnet50") {
+    taskType = LC;
+    int H = 224, W = 224, C = 3, oh, ow;
+    hostInput.resize(static_cast<size_t>(H) * W * C);
+    normal_input(hostInput, 43);
+    input = arena.act(hostInput.size());
+    const float* x = conv(input, H, W, C, 64, 7, 3, 2, 1, &oh, &ow);  // 112 x 112 x 64
+    H = oh, W = ow, C = 64;
+    x = pool(x, H, W, C);  // 56 x 56 (2x2 window; the original uses 3x3 stride 2, same output size)
+    H /= 2, W /= 2;
+    const int blocks[4] = {3, 4, 6, 3}, width[4] = {64, 128, 256, 512};
+    for (int s = 0; s < 4; ++s)
+        for (int b = 0; b < blocks[s]; ++b) {
+            const int stride = (b == 0 && s > 0) ? 2 : 1, mid = width[s], out = 4 * width[s];
+            const float* shortcut = x;
+            int sh = H, sw = W;
+            if (b == 0) shortcut = conv(x, H, W, C, out, 1, 0, stride, 0, &sh, &sw);
+            const float* y = conv(x, H, W, C, mid, 1, 0, 1, 1, &oh, &ow);
+            y = conv(y, H, W, mid, mid, 3, 1, stride, 1, &oh, &ow);
+            y = conv(y, oh, ow, mid, out, 1, 0, 1, 0, &oh, &ow);
+            H = oh, W = ow, C = out;
+            x = addTo(y, shortcut, H * W, C, 1);
+        }
+    while (H > 1) {  // global pooling stand-in: 7 -> 3 -> 1
+        x = pool(x, H, W, C);
+        H /= 2, W /= 2;
+    }
+    x = dense(x, 1, C, numClasses, 0);
+}
+
+// ------------------------------------------------------------------- BERT ----
+Bert::Bert(int layers, int batch_, int seq_) : DnnTask(2, "bert"), batch(batch_), seq(seq_) {
+    taskType = BE;
+    const int hidden = 768, heads = 12, dh = 64, ffn = 3072, rows = batch * seq, bh = batch * heads;
+    // token ids uniform over the vocabulary; the embedding lookup is done on the host, the encoder input is
+    // the gathered rows (word + position), layer-normalised on the device
+    const int vocab = 30522;
+    hostInput.resize(static_cast<size_t>(rows) * hidden);
+    for (int r = 0; r < rows; ++r) {
+        const uint64_t token = static_cast<uint64_t>(tk_unit_draw(77, r) * vocab);
+        for (int c = 0; c < hidden; ++c)
+            hostInput[static_cast<size_t>(r) * hidden + c] =
+                (tk_unit_draw(1000 + token, c) - 0.5f) * 0.1f + (tk_unit_draw(900000 + (r % seq), c) - 0.5f) * 0.02f;
+    }
+    input = arena.act(hostInput.size());
+    const float* x = layernorm(input, rows, hidden);
+    for (int l = 0; l < layers; ++l) {
+        const float* q = dense(x, rows, hidden, hidden, 0);
+        const float* k = dense(x, rows, hidden, hidden, 0);
+        const float* v = dense(x, rows, hidden, hidden, 0);
+        void* qh = arena.half(static_cast<size_t>(rows) * hidden);
+        void* kh = arena.half(static_cast<size_t>(rows) * hidden);
+        void* vt = arena.half(static_cast<size_t>(rows) * hidden);
+        const float* src[3] = {q, k, v};
+        void* dst[3] = {qh, kh, vt};
+        for (int i = 0; i < 3; ++i) {
+            auto* s = new OpKernel(nextId++, "SplitHeads_" + std::to_string(nextId), OpKernel::SplitHeads);
+            s->a = src[i];
+            s->hout = dst[i];
+            s->i0 = batch, s->i1 = seq, s->i2 = hidden, s->i3 = 0, s->i4 = heads, s->i5 = dh, s->i6 = (i == 2);
+            keep(s);
+        }
+        float* scores = arena.act(static_cast<size_t>(bh) * seq * seq);
+        auto* g1 = new OpKernel(nextId++, "BatchMatMul_" + std::to_string(nextId), OpKernel::BatchedGemm);
+        g1->ha = qh, g1->hb = kh, g1->out = scores;
+        g1->i0 = seq, g1->i1 = seq, g1->i2 = dh, g1->i3 = bh, g1->f0 = 1.0f / std::sqrt(static_cast<float>(dh));
+        keep(g1);
+        auto* sm = new OpKernel(nextId++, "Softmax_" + std::to_string(nextId), OpKernel::SoftmaxRows);
+        sm->a = scores, sm->out = scores, sm->i0 = bh, sm->i1 = seq, sm->i2 = seq, sm->f0 = 1.0f;
+        keep(sm);
+        void* ph = arena.half(static_cast<size_t>(bh) * seq * seq);
+        auto* th = new OpKernel(nextId++, "Convert_" + std::to_string(nextId), OpKernel::RowsToHalf);
+        th->a = scores, th->hout = ph, th->i0 = bh * seq, th->i1 = seq;
+        keep(th);
+        float* ctx = arena.act(static_cast<size_t>(rows) * hidden);
+        auto* g2 = new OpKernel(nextId++, "BatchMatMul_" + std::to_string(nextId), OpKernel::BatchedGemm);
+        g2->ha = ph, g2->hb = vt, g2->out = ctx;
+        g2->i0 = seq, g2->i1 = dh, g2->i2 = seq, g2->i3 = bh, g2->f0 = 1.0f;
+        keep(g2);
+        float* merged = arena.act(static_cast<size_t>(rows) * hidden);
+        auto* mh = new OpKernel(nextId++, "MergeHeads_" + std::to_string(nextId), OpKernel::MergeHeads);
+        mh->a = ctx, mh->out = merged, mh->i0 = batch, mh->i1 = seq, mh->i4 = heads, mh->i5 = dh;
+        keep(mh);
+        const float* proj = dense(merged, rows, hidden, hidden, 0);
+        x = layernorm(addTo(proj, x, rows, hidden, 0), rows, hidden);
+        const float* h1 = dense(x, rows, hidden, ffn, 2);
+        const float* h2 = dense(h1, rows, ffn, hidden, 0);
+        x = layernorm(addTo(h2, x, rows, hidden, 0), rows, hidden);
+    }
+}
+
+Task* createTask(const std::string& taskName) {
+    if (taskName == "vgg16") return new VGG16(1000);
+    if (taskName == "resnet50") return new Resnet50(1000);
+    if (taskName == "bert") return new Bert(12, 8, 128);
+    logger.ERROR("Task name not found: " + taskName);
+}

@@ -1,0 +1,107 @@
+// aker -- command line of the runtime (reference: src/main.cu:246-336).
+//   aker -s <aker|tacker> -m <vgg16|resnet50|bert> [-d device] [-c config_dir]
+//        [--colocate seconds] [--qps rate] [--qos factor] [--be model]
+// Without --colocate it runs the reference's experiment (both modes unless -s picks one); with it, the
+// request-driven co-location of `-m` (latency-critical) with `--be` (best-effort) on this GPU.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <iostream>
+#include <memory>
+#include <string>
+
+#include "Backend.h"
+#include "Creator.h"
+#include "Logger.h"
+#include "ModuleCenter.h"
+#include "Recorder.h"
+#include "TaskManager.h"
+#include "dnn/models.h"
+#include "json.h"
+
+static void usage(const char* argv0) {
+    std::cout << "SYNOPSIS\n        " << argv0
+              << " -s <system_name> -m <model_name> [-d <device_no>] [-c <config_dir>]\n"
+                 "            [--colocate <seconds>] [--qps <rate>] [--qos <factor>] [--be <model_name>]\n\n"
+                 "OPTIONS\n        -s, --system   system name, aker/tacker\n        -m, --model    model name\n"
+                 "        -d, --device   device number\n";
+}
+
+int main(int argc, char* argv[]) {
+    std::string system_name, model, config_dir = "config", be_model = "bert";
+    int device_no = 0;
+    double colocate = 0.0, qps = 200.0, qos = 1.5;
+    for (int i = 1; i < argc; ++i) {
+        const std::string a = argv[i];
+        auto val = [&](const char* what) -> std::string {
+            if (i + 1 >= argc) {
+                std::cerr << "missing value for " << what << "\n";
+                std::exit(2);
+            }
+            return argv[++i];
+        };
+        if (a == "-s" || a == "--system") system_name = val("-s");
+        else if (a == "-m" || a == "--model") model = val("-m");
+        else if (a == "-d" || a == "--device") device_no = std::atoi(val("-d").c_str());
+        else if (a == "-c" || a == "--config") config_dir = val("-c");
+        else if (a == "--colocate") colocate = std::atof(val("--colocate").c_str());
+        else if (a == "--qps") qps = std::atof(val("--qps").c_str());
+        else if (a == "--qos") qos = std::atof(val("--qos").c_str());
+        else if (a == "--be") be_model = val("--be");
+        else {
+            usage(argv[0]);
+            return 0;
+        }
+    }
+    if (system_name.empty() || model.empty()) {
+        usage(argv[0]);
+        return 0;
+    }
+    std::cout << "system: " << system_name << ", model: " << model << std::endl;
+    int rc = 0;
+    try {
+        std::unique_ptr<Backend> be(makeCudaBackend());
+        setBackend(be.get());
+        read_json(config_dir + "/kinfo-" + model + ".json");
+        read_common_json(config_dir + "/kinfo-common.json");
+        be->setDevice(device_no);  // no device reset: the GPU may be shared (the reference calls cudaDeviceReset)
+        std::cout << "SM count: " << be->smCount() << std::endl;
+        stream_t streams[2] = {be->streamCreate(), be->streamCreate()};
+
+        std::unique_ptr<Task> lc_task(createTask(model));
+        for (int i = 0; i < 5; ++i) {  // warm-up (src/main.cu:290-297)
+            lc_task->initExecution();
+            lc_task->enqueue(streams[0]);
+            be->streamSync(streams[0]);
+        }
+        const std::string a = sget_kernel_info("throughput_test", "a"), b = sget_kernel_info("throughput_test", "b");
+        std::printf("[Result] cd1: %s, cd2: %s, dnn: %s\n", a.c_str(), b.c_str(), model.c_str());
+        TaskManager taskManager(lc_task.get(), a, b);
+        if (colocate > 0.0) {
+            std::unique_ptr<Task> be_task(createTask(be_model));
+            const int per_pass = be_model == "bert" ? static_cast<Bert*>(be_task.get())->batch : 1;
+            ColocationResult r = taskManager.runColocation(be_task.get(), per_pass, colocate, qps, qos,
+                                                           1000 + static_cast<uint64_t>(device_no), streams[0]);
+            std::printf("{\"device\": %d, \"lc\": \"%s\", \"be\": \"%s\", \"seconds\": %.3f, \"qps_offered\": %.1f, "
+                        "\"lc_served\": %lld, \"lc_solo_p50_ms\": %.4f, \"lc_solo_p99_ms\": %.4f, \"lc_p50_ms\": %.4f, "
+                        "\"lc_p99_ms\": %.4f, \"qos_bound_ms\": %.4f, \"qos_met\": %s, \"be_queries\": %lld, "
+                        "\"be_qps\": %.2f}\n",
+                        device_no, model.c_str(), be_model.c_str(), r.seconds, qps, r.lc_served, r.lc_solo_p50_ms,
+                        r.lc_solo_p99_ms, r.lc_p50_ms, r.lc_p99_ms, r.qos_bound_ms, r.qos_met ? "true" : "false",
+                        r.be_queries, r.be_qps);
+        } else {
+            if (system_name == "aker" || system_name == "both") taskManager.executeAllTasks(ExecutionMode::Aker, streams[0]);
+            if (system_name == "tacker" || system_name == "both") taskManager.executeAllTasks(ExecutionMode::Tacker, streams[1]);
+        }
+        const unsigned status = be->deviceStatus();
+        if (status != 0) logger.WARNING("device status word: " + std::to_string(status));
+        recorder.text();
+        lc_task.reset();
+        destroyCreatedKernels();
+        tzgemmScratch.release();
+    } catch (const std::exception& e) {
+        std::cerr << "[ERROR] " << e.what() << std::endl;
+        rc = 1;
+    }
+    return rc;
+}

@@ -315,4 +315,57 @@ def pair_tzgemm_stencil_host(A_host, B_host, C_host, M, N, K, alpha, c0, c1, A0_
           "tk_pair_tzgemm_stencil_host")
 
 
+# ---- layer kernels of the DNN tasks -----------------------------------------------------------------------
+def _vp(x):
+    return C.c_void_p(int(x) if x else 0)
+
+
+def im2col_nhwc_f16(x, H, W, Cin, kh, kw, pad, stride, A_half, M_pad, K_pad, stream: int = 0) -> None:
+    check(lib().tk_im2col_nhwc_f16(_vp(x), H, W, Cin, kh, kw, pad, stride, _vp(A_half), M_pad, K_pad, _vp(stream)),
+          "tk_im2col_nhwc_f16")
+
+
+def rows_f32_to_f16(x, rows, cols, ld_in, A_half, rows_pad, cols_pad, stream: int = 0) -> None:
+    check(lib().tk_rows_f32_to_f16(_vp(x), rows, cols, ld_in, _vp(A_half), rows_pad, cols_pad, _vp(stream)),
+          "tk_rows_f32_to_f16")
+
+
+def bias_act_f32(x, ldx, bias, out, rows, cols, ld_out, act, stream: int = 0) -> None:
+    check(lib().tk_bias_act_f32(_vp(x), ldx, _vp(bias), _vp(out), rows, cols, ld_out, act, _vp(stream)),
+          "tk_bias_act_f32")
+
+
+def maxpool2x2_nhwc_f32(x, H, W, Cn, out, stream: int = 0) -> None:
+    check(lib().tk_maxpool2x2_nhwc_f32(_vp(x), H, W, Cn, _vp(out), _vp(stream)), "tk_maxpool2x2_nhwc_f32")
+
+
+def add_f32(a, b, out, n, stream: int = 0) -> None:
+    check(lib().tk_add_f32(_vp(a), _vp(b), _vp(out), C.c_longlong(n), _vp(stream)), "tk_add_f32")
+
+
+def softmax_rows_f32(x, out, rows, cols, scale=1.0, stream: int = 0) -> None:
+    check(lib().tk_softmax_rows_f32(_vp(x), _vp(out), C.c_longlong(rows), cols, C.c_float(scale), _vp(stream)),
+          "tk_softmax_rows_f32")
+
+
+def layernorm_rows_f32(x, gamma, beta, out, rows, cols, eps=1e-12, stream: int = 0) -> None:
+    check(lib().tk_layernorm_rows_f32(_vp(x), _vp(gamma), _vp(beta), _vp(out), C.c_longlong(rows), cols,
+                                      C.c_float(eps), _vp(stream)), "tk_layernorm_rows_f32")
+
+
+def split_heads_f16(x, ld, col0, B, S, heads, dh, transpose, out_half, stream: int = 0) -> None:
+    check(lib().tk_split_heads_f16(_vp(x), ld, col0, B, S, heads, dh, transpose, _vp(out_half), _vp(stream)),
+          "tk_split_heads_f16")
+
+
+def merge_heads_f32(ctx, B, S, heads, dh, out, stream: int = 0) -> None:
+    check(lib().tk_merge_heads_f32(_vp(ctx), B, S, heads, dh, _vp(out), _vp(stream)), "tk_merge_heads_f32")
+
+
+def tzgemm_batched(A, B, Cm, M, N, K, batch, alpha=1.0, stride_a=0, stride_b=0, stride_c=0, stream: int = 0) -> None:
+    check(lib().tk_tzgemm_batched(_vp(A), _vp(B), _vp(Cm), M, N, K, batch, C.c_longlong(stride_a),
+                                  C.c_longlong(stride_b), C.c_longlong(stride_c), C.c_float(alpha), _vp(stream)),
+          "tk_tzgemm_batched")
+
+
 __all__ = [n for n in dir() if not n.startswith("_")]
