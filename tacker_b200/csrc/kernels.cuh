@@ -1,0 +1,184 @@
+// Device status word and every __global__ kernel of the library (solo, fused, preparation).
+// Included by tacker_b200.cu and by the sources the fused-kernel generator emits.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "cd_roles.cuh"
+#include "gemm_role.cuh"
+#include "stencil_tma.cuh"
+
+namespace tk {
+
+// -------------------------------------------------------------------------------------------------
+// device status word (bounded waits report here)
+// -------------------------------------------------------------------------------------------------
+__device__ unsigned g_dev_status;
+
+// -------------------------------------------------------------------------------------------------
+// kernels
+// -------------------------------------------------------------------------------------------------
+constexpr int kMaxMixThreads = 896;  // 192 tensor-role threads + up to 704 CUDA-core threads (<= 73 registers each)
+
+__device__ __forceinline__ uint8_t* align_smem_1024(uint8_t* p) {
+    const uint32_t a = smem_u32(p);
+    return p + ((1024u - (a & 1023u)) & 1023u);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+tzgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), threadIdx.x >> 5, threadIdx.x & 31);
+}
+
+template <int PF>
+__global__ void __launch_bounds__(512) stencil_kernel(const StencilArgs s) {
+    stencil_role<PF>(s, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+}
+
+__device__ __forceinline__ uint8_t* align_smem_128(uint8_t* p) {
+    const uint32_t a = smem_u32(p);
+    return p + ((128u - (a & 127u)) & 127u);
+}
+
+// TMA-fed form: every warp streams its planes through a private ring of `ring` slots
+__global__ void __launch_bounds__(512)
+stencil_tma_kernel(const __grid_constant__ CUtensorMap tmap_grid, const StencilArgs s, const int ring,
+                   unsigned* status) {
+    extern __shared__ uint8_t smem_raw[];
+    stencil_role_tma(&tmap_grid, s, align_smem_128(smem_raw), ring, threadIdx.x >> 5, blockDim.x >> 5,
+                     threadIdx.x & 31, blockIdx.x, gridDim.x, status);
+}
+
+template <int PPT, bool EXACT>
+__global__ void __launch_bounds__(512) cp_kernel(const CpArgs a) {
+    cp_role<PPT, EXACT>(a, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+}
+
+template <bool ACCURATE>
+__global__ void __launch_bounds__(512) mriq_kernel(const MriqArgs m) {
+    mriq_role<ACCURATE>(m, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+}
+
+// Fused kernels: warps 0..5 run the tensor role, the remaining warps the CUDA-core role.  The
+// two roles share the SM and nothing else (the reference dispatches on threadIdx.x ranges the
+// same way, src/mix_kernel/tzgemm_stencil.cu:284-298).
+// ring > 0: the stencil warps use the TMA-fed role with their rings placed behind the tensor role's
+// shared memory; ring == 0: the register role (shapes TMA cannot describe).
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kMaxMixThreads, 1)
+mix_stencil_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmArgs g, const __grid_constant__ CUtensorMap tmap_grid, const StencilArgs s,
+                   const int ring) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    uint8_t* smem = align_smem_1024(smem_raw);
+    if (warp < kGemmWarps) {
+        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31);
+    } else if (ring > 0) {
+        stencil_role_tma(&tmap_grid, s, smem + GemmSmem<BN, STAGES>::kBytes, ring, warp - kGemmWarps,
+                         (blockDim.x >> 5) - kGemmWarps, threadIdx.x & 31, blockIdx.x, gridDim.x, g.status);
+    } else {
+        stencil_role<0>(s, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+    }
+}
+
+template <int BN, int STAGES, int PPT>
+__global__ void __launch_bounds__(kMaxMixThreads, 1)
+mix_cp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              const GemmArgs g, const CpArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
+    } else {
+        cp_role<PPT, false>(a, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+    }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kMaxMixThreads, 1)
+mix_mriq_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmArgs g, const MriqArgs m) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
+    } else {
+        mriq_role<false>(m, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+    }
+}
+
+// ---- input preparation ----
+__global__ void cp_pack_kernel(const float4* __restrict__ atoms, int count, float zplane,
+                               float4* __restrict__ packed) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) {
+        float4 a = atoms[i];
+        const float dz = __fsub_rn(zplane, a.z);
+        a.z = __fmul_rn(dz, dz);
+        packed[i] = a;
+    }
+}
+
+__global__ void mriq_pack_kernel(const float* __restrict__ kx, const float* __restrict__ ky,
+                                 const float* __restrict__ kz, const float* __restrict__ phiR,
+                                 const float* __restrict__ phiI, int numK, float4* __restrict__ kvals) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < numK) {
+        const float re = phiR[k], im = phiI[k];
+        // real*real + imag*imag with the contraction nvcc applies to the reference's expression
+        kvals[k] = make_float4(kx[k], ky[k], kz[k], __fmaf_rn(re, re, __fmul_rn(im, im)));
+    }
+}
+
+// ---- LC-layer helpers ----
+// One thread per (channel, output row, output column) as in the reference; consecutive threads
+// take consecutive output columns so every one of the kh*kw stores of a warp is coalesced.
+__global__ void im2col_kernel(long long n, const float* __restrict__ im, int height, int width, int kh,
+                              int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                              int hcol, int wcol, float* __restrict__ col) {
+    for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < n;
+         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int w = static_cast<int>(idx % wcol);
+        const long long hidx = idx / wcol;
+        const int h = static_cast<int>(hidx % hcol);
+        const int c = static_cast<int>(hidx / hcol);
+        const int h0 = h * stride_h - pad_h, w0 = w * stride_w - pad_w;
+        float* dst = col + (static_cast<size_t>(c) * kh * kw * hcol + h) * wcol + w;
+        const float* src = im + static_cast<size_t>(c) * height * width;
+        for (int i = 0; i < kh; ++i)
+            for (int j = 0; j < kw; ++j) {
+                const int hi = h0 + i * dil_h, wi = w0 + j * dil_w;
+                *dst = (hi >= 0 && wi >= 0 && hi < height && wi < width)
+                           ? __ldg(src + static_cast<size_t>(hi) * width + wi)
+                           : 0.0f;
+                dst += static_cast<size_t>(hcol) * wcol;
+            }
+    }
+}
+
+__global__ void cvt_f32_f16_kernel(__half* __restrict__ out, const float* __restrict__ in, long long n) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long n4 = n / 4;
+    const bool vec = ((reinterpret_cast<uintptr_t>(in) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(out) & 7u) == 0);
+    if (vec) {
+        for (long long i = i0; i < n4; i += stride) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(in) + i);
+            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&lo);
+            o.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(out)[i] = o;
+        }
+        for (long long i = n4 * 4 + i0; i < n; i += stride) out[i] = __float2half_rn(in[i]);
+    } else {
+        for (long long i = i0; i < n; i += stride) out[i] = __float2half_rn(in[i]);
+    }
+}
+
+}  // namespace tk

@@ -1,668 +1,8 @@
-// libtacker_b200.so: kernels and C-ABI launchers (see include/tacker_b200.h for the contract).
-#include <cuda.h>
-#include <cuda_fp16.h>
-#include <cuda_runtime.h>
-
-#include <cstdio>
-#include <cstring>
-#include <map>
-#include <mutex>
-#include <string>
-#include <tuple>
-
-#include "../../include/tacker_b200.h"
-#include "cd_roles.cuh"
-#include "gemm_role.cuh"
-#include "stencil_tma.cuh"
+// libtacker_b200.so: the C-ABI entry points (see include/tacker_b200.h for the contract).
+#include "host_launch.cuh"
 
 #define TK_API extern "C" __attribute__((visibility("default")))
 
-namespace tk {
-
-// -------------------------------------------------------------------------------------------------
-// device status word (bounded waits report here)
-// -------------------------------------------------------------------------------------------------
-__device__ unsigned g_dev_status;
-
-// -------------------------------------------------------------------------------------------------
-// kernels
-// -------------------------------------------------------------------------------------------------
-constexpr int kMaxMixThreads = 896;  // 192 tensor-role threads + up to 704 CUDA-core threads (<= 73 registers each)
-
-__device__ __forceinline__ uint8_t* align_smem_1024(uint8_t* p) {
-    const uint32_t a = smem_u32(p);
-    return p + ((1024u - (a & 1023u)) & 1023u);
-}
-
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-tzgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-              const GemmArgs g) {
-    extern __shared__ uint8_t smem_raw[];
-    gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), threadIdx.x >> 5, threadIdx.x & 31);
-}
-
-template <int PF>
-__global__ void __launch_bounds__(512) stencil_kernel(const StencilArgs s) {
-    stencil_role<PF>(s, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
-}
-
-__device__ __forceinline__ uint8_t* align_smem_128(uint8_t* p) {
-    const uint32_t a = smem_u32(p);
-    return p + ((128u - (a & 127u)) & 127u);
-}
-
-// TMA-fed form: every warp streams its planes through a private ring of `ring` slots
-__global__ void __launch_bounds__(512)
-stencil_tma_kernel(const __grid_constant__ CUtensorMap tmap_grid, const StencilArgs s, const int ring,
-                   unsigned* status) {
-    extern __shared__ uint8_t smem_raw[];
-    stencil_role_tma(&tmap_grid, s, align_smem_128(smem_raw), ring, threadIdx.x >> 5, blockDim.x >> 5,
-                     threadIdx.x & 31, blockIdx.x, gridDim.x, status);
-}
-
-template <int PPT, bool EXACT>
-__global__ void __launch_bounds__(512) cp_kernel(const CpArgs a) {
-    cp_role<PPT, EXACT>(a, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
-}
-
-template <bool ACCURATE>
-__global__ void __launch_bounds__(512) mriq_kernel(const MriqArgs m) {
-    mriq_role<ACCURATE>(m, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
-}
-
-// Fused kernels: warps 0..5 run the tensor role, the remaining warps the CUDA-core role.  The
-// two roles share the SM and nothing else (the reference dispatches on threadIdx.x ranges the
-// same way, src/mix_kernel/tzgemm_stencil.cu:284-298).
-// ring > 0: the stencil warps use the TMA-fed role with their rings placed behind the tensor role's
-// shared memory; ring == 0: the register role (shapes TMA cannot describe).
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(kMaxMixThreads, 1)
-mix_stencil_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const GemmArgs g, const __grid_constant__ CUtensorMap tmap_grid, const StencilArgs s,
-                   const int ring) {
-    extern __shared__ uint8_t smem_raw[];
-    const int warp = threadIdx.x >> 5;
-    uint8_t* smem = align_smem_1024(smem_raw);
-    if (warp < kGemmWarps) {
-        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31);
-    } else if (ring > 0) {
-        stencil_role_tma(&tmap_grid, s, smem + GemmSmem<BN, STAGES>::kBytes, ring, warp - kGemmWarps,
-                         (blockDim.x >> 5) - kGemmWarps, threadIdx.x & 31, blockIdx.x, gridDim.x, g.status);
-    } else {
-        stencil_role<0>(s, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
-    }
-}
-
-template <int BN, int STAGES, int PPT>
-__global__ void __launch_bounds__(kMaxMixThreads, 1)
-mix_cp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-              const GemmArgs g, const CpArgs a) {
-    extern __shared__ uint8_t smem_raw[];
-    const int warp = threadIdx.x >> 5;
-    if (warp < kGemmWarps) {
-        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
-    } else {
-        cp_role<PPT, false>(a, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
-    }
-}
-
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(kMaxMixThreads, 1)
-mix_mriq_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const GemmArgs g, const MriqArgs m) {
-    extern __shared__ uint8_t smem_raw[];
-    const int warp = threadIdx.x >> 5;
-    if (warp < kGemmWarps) {
-        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
-    } else {
-        mriq_role<false>(m, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
-    }
-}
-
-// ---- input preparation ----
-__global__ void cp_pack_kernel(const float4* __restrict__ atoms, int count, float zplane,
-                               float4* __restrict__ packed) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < count) {
-        float4 a = atoms[i];
-        const float dz = __fsub_rn(zplane, a.z);
-        a.z = __fmul_rn(dz, dz);
-        packed[i] = a;
-    }
-}
-
-__global__ void mriq_pack_kernel(const float* __restrict__ kx, const float* __restrict__ ky,
-                                 const float* __restrict__ kz, const float* __restrict__ phiR,
-                                 const float* __restrict__ phiI, int numK, float4* __restrict__ kvals) {
-    const int k = blockIdx.x * blockDim.x + threadIdx.x;
-    if (k < numK) {
-        const float re = phiR[k], im = phiI[k];
-        // real*real + imag*imag with the contraction nvcc applies to the reference's expression
-        kvals[k] = make_float4(kx[k], ky[k], kz[k], __fmaf_rn(re, re, __fmul_rn(im, im)));
-    }
-}
-
-// ---- LC-layer helpers ----
-// One thread per (channel, output row, output column) as in the reference; consecutive threads
-// take consecutive output columns so every one of the kh*kw stores of a warp is coalesced.
-__global__ void im2col_kernel(long long n, const float* __restrict__ im, int height, int width, int kh,
-                              int kw, int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
-                              int hcol, int wcol, float* __restrict__ col) {
-    for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < n;
-         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int w = static_cast<int>(idx % wcol);
-        const long long hidx = idx / wcol;
-        const int h = static_cast<int>(hidx % hcol);
-        const int c = static_cast<int>(hidx / hcol);
-        const int h0 = h * stride_h - pad_h, w0 = w * stride_w - pad_w;
-        float* dst = col + (static_cast<size_t>(c) * kh * kw * hcol + h) * wcol + w;
-        const float* src = im + static_cast<size_t>(c) * height * width;
-        for (int i = 0; i < kh; ++i)
-            for (int j = 0; j < kw; ++j) {
-                const int hi = h0 + i * dil_h, wi = w0 + j * dil_w;
-                *dst = (hi >= 0 && wi >= 0 && hi < height && wi < width)
-                           ? __ldg(src + static_cast<size_t>(hi) * width + wi)
-                           : 0.0f;
-                dst += static_cast<size_t>(hcol) * wcol;
-            }
-    }
-}
-
-__global__ void cvt_f32_f16_kernel(__half* __restrict__ out, const float* __restrict__ in, long long n) {
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    const long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    const long long n4 = n / 4;
-    const bool vec = ((reinterpret_cast<uintptr_t>(in) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(out) & 7u) == 0);
-    if (vec) {
-        for (long long i = i0; i < n4; i += stride) {
-            const float4 v = __ldg(reinterpret_cast<const float4*>(in) + i);
-            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-            uint2 o;
-            o.x = *reinterpret_cast<uint32_t*>(&lo);
-            o.y = *reinterpret_cast<uint32_t*>(&hi);
-            reinterpret_cast<uint2*>(out)[i] = o;
-        }
-        for (long long i = n4 * 4 + i0; i < n; i += stride) out[i] = __float2half_rn(in[i]);
-    } else {
-        for (long long i = i0; i < n; i += stride) out[i] = __float2half_rn(in[i]);
-    }
-}
-
-// -------------------------------------------------------------------------------------------------
-// host side
-// -------------------------------------------------------------------------------------------------
-thread_local std::string t_last_error;
-
-static int cuda_fail(cudaError_t e, const char* what) {
-    t_last_error = std::string(what) + ": " + cudaGetErrorString(e);
-    return TK_ERR_CUDA;
-}
-#define TK_CUDA(call)                                         \
-    do {                                                      \
-        cudaError_t _e = (call);                              \
-        if (_e != cudaSuccess) return cuda_fail(_e, #call);   \
-    } while (0)
-
-struct Options {
-    int tzgemm_bn = 0;
-    int cp_exact = 0;
-    int cp_ppt = 8;
-    int mriq_accurate = 0;
-    int stencil_prefetch = 0;   // register role: L2 prefetch distance in planes (0 or 8)
-    int stencil_tma = 1;        // 1 = TMA-fed role whenever the shape allows, 0 = always the register role
-    int stencil_ring = 4;       // ring depth per warp, solo kernel (2 planes in flight per warp measured best)
-    int mix_stencil_ring = 12;  // upper bound of the ring depth in the fused kernel (shared memory decides)
-};
-static Options g_opt;
-
-struct DeviceInfo {
-    int sm_count = 0;
-    unsigned* status_ptr = nullptr;
-};
-static std::mutex g_mutex;
-static std::map<int, DeviceInfo> g_devices;
-
-static int device_info(DeviceInfo** out) {
-    int dev = 0;
-    TK_CUDA(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lock(g_mutex);
-    auto it = g_devices.find(dev);
-    if (it == g_devices.end()) {
-        DeviceInfo d;
-        TK_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
-        TK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_dev_status));
-        it = g_devices.emplace(dev, d).first;
-    }
-    *out = &it->second;
-    return TK_OK;
-}
-
-// ---- TMA descriptors (driver entry point fetched through the runtime; libcuda is not linked) ----
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn g_encode = nullptr;
-
-static int get_encoder() {
-    if (g_encode) return TK_OK;
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    TK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-    if (q != cudaDriverEntryPointSuccess || fn == nullptr) {
-        t_last_error = "cuTensorMapEncodeTiled is not available in this driver";
-        return TK_ERR_CUDA;
-    }
-    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-    return TK_OK;
-}
-
-// fp16 matrices [batch][rows][k], k contiguous; box = 64 (k) x box_rows x 1, 128-byte swizzle
-static int make_tmap(CUtensorMap* m, const void* base, int rows, int k, int box_rows, int batch = 1,
-                     long long batch_stride_elems = 0) {
-    int rc = get_encoder();
-    if (rc != TK_OK) return rc;
-    if (batch < 1) batch = 1;
-    if (batch_stride_elems <= 0) batch_stride_elems = static_cast<long long>(rows) * k;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(k) * 2, static_cast<cuuint64_t>(batch_stride_elems) * 2};
-    cuuint32_t box[3] = {static_cast<cuuint32_t>(kGemmBK), static_cast<cuuint32_t>(box_rows), 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        t_last_error = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(static_cast<int>(r));
-        return TK_ERR_CUDA;
-    }
-    return TK_OK;
-}
-
-// fp32 grid [nz][ny][nx]; box = 72 x 6 x 1 (a 64 x 4 bundle plus its halo), no swizzle, zero fill
-static int make_tmap_grid(CUtensorMap* m, const float* base, int nx, int ny, int nz) {
-    int rc = get_encoder();
-    if (rc != TK_OK) return rc;
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(nx), static_cast<cuuint64_t>(ny), static_cast<cuuint64_t>(nz)};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(nx) * 4, static_cast<cuuint64_t>(nx) * ny * 4};
-    cuuint32_t box[3] = {kStTileCols, kStTileRows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        t_last_error = "cuTensorMapEncodeTiled (grid) failed with CUresult " + std::to_string(static_cast<int>(r));
-        return TK_ERR_CUDA;
-    }
-    return TK_OK;
-}
-
-static bool stencil_tma_ok(const StencilArgs& s) {
-    return g_opt.stencil_tma != 0 && s.nx % 4 == 0 && s.nz >= 3 &&
-           (reinterpret_cast<uintptr_t>(s.A0) & 15u) == 0 && (reinterpret_cast<uintptr_t>(s.Anext) & 15u) == 0;
-}
-
-constexpr int kMaxDynSmem = 232448;  // 227 KiB per CTA on sm_100
-
-// ---- parameter access ----
-template <typename T>
-static inline T arg(void** params, int i) {
-    T v;
-    std::memcpy(&v, params[i], sizeof(T));
-    return v;
-}
-
-static int check_params(void** params, int nparams, int expected) {
-    if (params == nullptr || nparams != expected) return TK_ERR_ARGS;
-    for (int i = 0; i < nparams; ++i)
-        if (params[i] == nullptr) return TK_ERR_ARGS;
-    return TK_OK;
-}
-
-struct GemmCall {
-    const __half* A;
-    const __half* B;
-    GemmArgs g;
-    long long stride_a = 0, stride_b = 0;  // elements between batch entries (0 = dense)
-};
-
-// params[base .. base+6] = A, B, C, M, N, K, alpha; start/end at the given indices
-static int parse_gemm(void** params, int base, int i_start, int i_end, GemmCall* c) {
-    c->A = arg<const __half*>(params, base + 0);
-    c->B = arg<const __half*>(params, base + 1);
-    c->g.C = arg<float*>(params, base + 2);
-    c->g.M = arg<int>(params, base + 3);
-    c->g.N = arg<int>(params, base + 4);
-    c->g.K = arg<int>(params, base + 5);
-    c->g.alpha = arg<float>(params, base + 6);
-    c->g.start = arg<int>(params, i_start);
-    c->g.end = arg<int>(params, i_end);
-    c->g.status = nullptr;
-    c->g.batch = 1;
-    c->g.stride_c = 0;
-    const bool empty = c->g.start >= c->g.end;
-    if (c->g.M < 128 || c->g.N < 64 || c->g.K < 64) return TK_ERR_SHAPE;
-    if (c->g.M % 128 || c->g.N % 64 || c->g.K % 64) return TK_ERR_SHAPE;
-    if (!empty && (c->A == nullptr || c->B == nullptr || c->g.C == nullptr)) return TK_ERR_ARGS;
-    if ((reinterpret_cast<uintptr_t>(c->A) & 15u) || (reinterpret_cast<uintptr_t>(c->B) & 15u) ||
-        (reinterpret_cast<uintptr_t>(c->g.C) & 15u))
-        return TK_ERR_ALIGN;
-    if (c->g.start < 0) return TK_ERR_ARGS;
-    return TK_OK;
-}
-
-static int choose_bn(const GemmArgs& g, int ctas) {
-    if (g_opt.tzgemm_bn == 128 || g_opt.tzgemm_bn == 256) return g_opt.tzgemm_bn;
-    if (g.N % 256 != 0) return 128;
-    // time model: waves x per-tile cost; a 128-wide tile re-reads A from shared memory twice as
-    // often per flop, so it is charged a little more than half of a 256-wide one
-    const long long t256 = static_cast<long long>(g.M / 128) * (g.N / 256);
-    const long long t128 = static_cast<long long>(g.M / 128) * (g.N / 128);
-    const double c256 = static_cast<double>((t256 + ctas - 1) / ctas) * 2.0;
-    const double c128 = static_cast<double>((t128 + ctas - 1) / ctas) * 1.15;
-    return c256 <= c128 ? 256 : 128;
-}
-
-constexpr int kStages256 = 4;
-constexpr int kStages128 = 6;
-template <int BN>
-struct StagesFor {
-    static constexpr int value = BN == 256 ? kStages256 : kStages128;
-};
-
-template <int BN>
-static constexpr int gemm_smem_bytes() {
-    return GemmSmem<BN, StagesFor<BN>::value>::kBytes + 1024;  // + slack for the 1024-byte alignment
-}
-
-template <typename KernelT>
-static int enable_smem(KernelT kernel, int bytes) {
-    // idempotent and cheap; done on every call so that it holds for every device that is used
-    TK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    return TK_OK;
-}
-
-static int validate_grid(const unsigned grid[3], const unsigned block[3]) {
-    if (grid == nullptr || block == nullptr) return TK_ERR_ARGS;
-    if (grid[0] == 0 || grid[1] > 1 || grid[2] > 1) return TK_ERR_LAUNCH_CONFIG;
-    if (block[0] == 0 || block[1] > 1 || block[2] > 1) return TK_ERR_LAUNCH_CONFIG;
-    return TK_OK;
-}
-
-// ---- CUDA-core argument parsing (reference argument order) ----
-static int parse_stencil(void** p, int i_start, int i_end, StencilArgs* s) {
-    s->c0 = arg<float>(p, 0);
-    s->c1 = arg<float>(p, 1);
-    s->A0 = arg<const float*>(p, 2);
-    s->Anext = arg<float*>(p, 3);
-    s->nx = arg<int>(p, 4);
-    s->ny = arg<int>(p, 5);
-    s->nz = arg<int>(p, 6);
-    s->gx = arg<int>(p, 7);
-    s->gy = arg<int>(p, 8);
-    const int bdx = arg<int>(p, 10), bdy = arg<int>(p, 11);
-    s->start = arg<int>(p, i_start);
-    s->end = arg<int>(p, i_end);
-    if (s->nx <= 0 || s->ny <= 0 || s->nz <= 0 || s->gx <= 0 || s->gy <= 0 || s->start < 0) return TK_ERR_ARGS;
-    if (bdx != 32 || bdy != 4) return TK_ERR_SHAPE;  // the 64 x 4 bundle is the virtual-block unit
-    if (s->end > s->gx * s->gy) s->end = s->gx * s->gy;  // see the note on ranges in the header
-    if (s->start < s->end && (s->A0 == nullptr || s->Anext == nullptr)) return TK_ERR_ARGS;
-    if ((reinterpret_cast<uintptr_t>(s->A0) & 3u) || (reinterpret_cast<uintptr_t>(s->Anext) & 3u)) return TK_ERR_ALIGN;
-    return TK_OK;
-}
-
-static int parse_cp(void** p, int i_start, int i_end, CpArgs* a) {
-    a->numatoms = arg<int>(p, 0);
-    a->spacing = arg<float>(p, 1);
-    a->lattice = arg<float*>(p, 2);
-    a->atoms = arg<const float4*>(p, 3);
-    a->gx = arg<int>(p, 4);
-    a->gy = arg<int>(p, 5);
-    const int bdx = arg<int>(p, 7), bdy = arg<int>(p, 8);
-    a->start = arg<int>(p, i_start);
-    a->end = arg<int>(p, i_end);
-    if (a->numatoms < 0 || a->gx <= 0 || a->gy <= 0 || a->start < 0) return TK_ERR_ARGS;
-    if (bdx != 16 || bdy != 8) return TK_ERR_SHAPE;
-    if (a->end > a->gx * a->gy) a->end = a->gx * a->gy;
-    if (a->start < a->end && (a->lattice == nullptr || (a->numatoms > 0 && a->atoms == nullptr))) return TK_ERR_ARGS;
-    if ((reinterpret_cast<uintptr_t>(a->atoms) & 15u) || (reinterpret_cast<uintptr_t>(a->lattice) & 3u))
-        return TK_ERR_ALIGN;
-    return TK_OK;
-}
-
-static int parse_mriq(void** p, int i_start, int i_end, MriqArgs* m) {
-    m->numK = arg<int>(p, 0);
-    m->x = arg<const float*>(p, 2);
-    m->y = arg<const float*>(p, 3);
-    m->z = arg<const float*>(p, 4);
-    m->Qr = arg<float*>(p, 5);
-    m->Qi = arg<float*>(p, 6);
-    m->kvals = arg<const float4*>(p, 7);
-    m->gx = arg<int>(p, 8);
-    const int bdx = arg<int>(p, 11);
-    m->start = arg<int>(p, i_start);
-    m->end = arg<int>(p, i_end);
-    if (m->numK < 0 || m->gx <= 0 || m->start < 0) return TK_ERR_ARGS;
-    if (bdx != 256) return TK_ERR_SHAPE;
-    if (m->end > m->gx) m->end = m->gx;
-    if (m->start < m->end &&
-        (!m->x || !m->y || !m->z || !m->Qr || !m->Qi || (m->numK > 0 && m->kvals == nullptr)))
-        return TK_ERR_ARGS;
-    if (reinterpret_cast<uintptr_t>(m->kvals) & 15u) return TK_ERR_ALIGN;
-    return TK_OK;
-}
-
-static int launch_error(const char* what) {
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, what);
-    return TK_OK;
-}
-
-// ---- solo launches ----
-template <int BN>
-static int launch_tzgemm(const GemmCall& c, unsigned ctas, cudaStream_t st) {
-    constexpr int STAGES = StagesFor<BN>::value;
-    CUtensorMap ta, tb;
-    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM, c.g.batch, c.stride_a);
-    if (rc != TK_OK) return rc;
-    rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN, c.g.batch, c.stride_b);
-    if (rc != TK_OK) return rc;
-    auto kernel = tzgemm_kernel<BN, STAGES>;
-    rc = enable_smem(kernel, gemm_smem_bytes<BN>());
-    if (rc != TK_OK) return rc;
-    kernel<<<ctas, kGemmThreads, gemm_smem_bytes<BN>(), st>>>(ta, tb, c.g);
-    return launch_error("tzgemm_kernel launch");
-}
-
-static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st) {
-    DeviceInfo* d = nullptr;
-    int rc = device_info(&d);
-    if (rc != TK_OK) return rc;
-    c.g.status = d->status_ptr;
-    if (c.g.start >= c.g.end) return TK_OK;
-    // one CTA per SM holds the whole tensor memory; more CTAs than SMs would only queue
-    const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
-    return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_tzgemm<256>(c, ctas, st)
-                                                        : launch_tzgemm<128>(c, ctas, st);
-}
-
-static unsigned cd_threads(unsigned requested, unsigned granule, unsigned cap) {
-    unsigned t = requested > cap ? cap : requested;
-    t = (t / granule) * granule;
-    return t;
-}
-
-static int run_stencil(StencilArgs s, unsigned grid0, unsigned block0, cudaStream_t st) {
-    if (s.start >= s.end) return TK_OK;
-    const unsigned threads = cd_threads(block0, 32, 512);
-    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
-    if (stencil_tma_ok(s)) {
-        DeviceInfo* d = nullptr;
-        int rc = device_info(&d);
-        if (rc != TK_OK) return rc;
-        const int nwarps = static_cast<int>(threads / 32);
-        int ring = g_opt.stencil_ring;
-        while (ring > kStMinRing && nwarps * stencil_tma_warp_bytes(ring) + 128 > kMaxDynSmem) --ring;
-        const int smem = nwarps * stencil_tma_warp_bytes(ring) + 128;
-        CUtensorMap tg;
-        if ((rc = make_tmap_grid(&tg, s.A0, s.nx, s.ny, s.nz)) != TK_OK) return rc;
-        if ((rc = enable_smem(stencil_tma_kernel, smem)) != TK_OK) return rc;
-        stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(grid0) * nwarps, &s.slabs, &s.per);
-        stencil_tma_kernel<<<grid0, threads, smem, st>>>(tg, s, ring, d->status_ptr);
-        return launch_error("stencil_tma_kernel launch");
-    }
-    const unsigned rthreads = cd_threads(threads, kStencilGroup, 512);
-    if (rthreads == 0) return TK_ERR_LAUNCH_CONFIG;
-    stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(grid0) * (rthreads / kStencilGroup), &s.slabs,
-                       &s.per);
-    if (g_opt.stencil_prefetch) stencil_kernel<8><<<grid0, rthreads, 0, st>>>(s);
-    else stencil_kernel<0><<<grid0, rthreads, 0, st>>>(s);
-    return launch_error("stencil_kernel launch");
-}
-
-static int run_cp(const CpArgs& a, unsigned grid0, unsigned block0, cudaStream_t st) {
-    if (a.start >= a.end) return TK_OK;
-    const unsigned threads = cd_threads(block0, 32, 512);
-    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
-    const int ppt = g_opt.cp_ppt;
-    if (g_opt.cp_exact) {
-        if (ppt == 2) cp_kernel<2, true><<<grid0, threads, 0, st>>>(a);
-        else if (ppt == 4) cp_kernel<4, true><<<grid0, threads, 0, st>>>(a);
-        else cp_kernel<8, true><<<grid0, threads, 0, st>>>(a);
-    } else {
-        if (ppt == 2) cp_kernel<2, false><<<grid0, threads, 0, st>>>(a);
-        else if (ppt == 4) cp_kernel<4, false><<<grid0, threads, 0, st>>>(a);
-        else cp_kernel<8, false><<<grid0, threads, 0, st>>>(a);
-    }
-    return launch_error("cp_kernel launch");
-}
-
-static int run_mriq(const MriqArgs& m, unsigned grid0, unsigned block0, cudaStream_t st) {
-    if (m.start >= m.end) return TK_OK;
-    const unsigned threads = cd_threads(block0, 32, 512);
-    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
-    if (g_opt.mriq_accurate) mriq_kernel<true><<<grid0, threads, 0, st>>>(m);
-    else mriq_kernel<false><<<grid0, threads, 0, st>>>(m);
-    return launch_error("mriq_kernel launch");
-}
-
-// ---- fused launches ----
-enum CdKind { CD_STENCIL, CD_CP, CD_MRIQ };
-
-struct CdCall {
-    CdKind kind;
-    StencilArgs s;
-    CpArgs a;
-    MriqArgs m;
-    bool empty() const {
-        switch (kind) {
-            case CD_STENCIL: return s.start >= s.end;
-            case CD_CP: return a.start >= a.end;
-            default: return m.start >= m.end;
-        }
-    }
-};
-
-// The stencil's rings share the CTA's shared memory with the tensor role's stages: fewer, larger
-// stages for the GEMM here than in the solo kernel, so that the rings get about 80 KB.
-template <int BN>
-struct StagesMixStencil {
-    static constexpr int value = BN == 256 ? 3 : 4;
-};
-
-template <int BN>
-static int launch_mix_stencil(const GemmCall& c, const CUtensorMap& ta, const CUtensorMap& tb, StencilArgs s,
-                              unsigned ctas, unsigned threads, cudaStream_t st) {
-    constexpr int STAGES = StagesMixStencil<BN>::value;
-    constexpr int kGemmBytes = GemmSmem<BN, STAGES>::kBytes + 1024;
-    auto k = mix_stencil_kernel<BN, STAGES>;
-    const int nwarps = static_cast<int>((threads - kGemmThreads) / 32);
-    int ring = 0, smem = kGemmBytes, rc;
-    CUtensorMap tg;
-    std::memset(&tg, 0, sizeof(tg));
-    if (stencil_tma_ok(s)) {
-        ring = g_opt.mix_stencil_ring;
-        while (ring >= kStMinRing && kGemmBytes + nwarps * stencil_tma_warp_bytes(ring) > kMaxDynSmem) --ring;
-        if (ring < kStMinRing) ring = 0;
-    }
-    if (ring > 0) {
-        if ((rc = make_tmap_grid(&tg, s.A0, s.nx, s.ny, s.nz)) != TK_OK) return rc;
-        smem += nwarps * stencil_tma_warp_bytes(ring);
-        stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(ctas) * nwarps, &s.slabs, &s.per);
-    } else {
-        const unsigned groups = (threads - kGemmThreads) / kStencilGroup;
-        if (groups == 0) return TK_ERR_LAUNCH_CONFIG;
-        threads = kGemmThreads + groups * kStencilGroup;
-        stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(ctas) * groups, &s.slabs, &s.per);
-    }
-    if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
-    k<<<ctas, threads, smem, st>>>(ta, tb, c.g, tg, s, ring);
-    return launch_error("mix_stencil_kernel launch");
-}
-
-template <int BN>
-static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsigned threads, cudaStream_t st) {
-    constexpr int STAGES = StagesFor<BN>::value;
-    CUtensorMap ta, tb;
-    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
-    if (rc != TK_OK) return rc;
-    rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN);
-    if (rc != TK_OK) return rc;
-    const int smem = gemm_smem_bytes<BN>();
-    switch (cd.kind) {
-        case CD_STENCIL:
-            return launch_mix_stencil<BN>(c, ta, tb, cd.s, ctas, threads, st);
-        case CD_CP: {
-            if (g_opt.cp_ppt == 2) {
-                auto k = mix_cp_kernel<BN, STAGES, 2>;
-                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
-                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
-            } else if (g_opt.cp_ppt == 4) {
-                auto k = mix_cp_kernel<BN, STAGES, 4>;
-                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
-                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
-            } else {
-                auto k = mix_cp_kernel<BN, STAGES, 8>;
-                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
-                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
-            }
-            break;
-        }
-        default: {
-            auto k = mix_mriq_kernel<BN, STAGES>;
-            if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
-            k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.m);
-            break;
-        }
-    }
-    return launch_error("mix kernel launch");
-}
-
-static int run_mix(GemmCall& c, const CdCall& cd, unsigned grid0, unsigned block0, cudaStream_t st) {
-    DeviceInfo* d = nullptr;
-    int rc = device_info(&d);
-    if (rc != TK_OK) return rc;
-    c.g.status = d->status_ptr;
-    const bool gemm_empty = c.g.start >= c.g.end;
-    if (gemm_empty && cd.empty()) return TK_OK;
-    if (block0 <= static_cast<unsigned>(kGemmThreads)) return TK_ERR_LAUNCH_CONFIG;
-    const unsigned granule = 32;
-    const unsigned cdt = cd_threads(block0 - kGemmThreads, granule, kMaxMixThreads - kGemmThreads);
-    if (cdt == 0) return TK_ERR_LAUNCH_CONFIG;
-    if (gemm_empty) {  // nothing for the tensor role: run the CUDA-core kernel alone
-        switch (cd.kind) {
-            case CD_STENCIL: return run_stencil(cd.s, grid0, cdt, st);
-            case CD_CP: return run_cp(cd.a, grid0, cdt, st);
-            default: return run_mriq(cd.m, grid0, cdt, st);
-        }
-    }
-    if (cd.empty()) return run_tzgemm(c, grid0, st);
-    const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
-    const unsigned threads = kGemmThreads + cdt;
-    return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_mix<256>(c, cd, ctas, threads, st)
-                                                        : launch_mix<128>(c, cd, ctas, threads, st);
-}
-
-}  // namespace tk
 
 using namespace tk;
 

@@ -1,0 +1,72 @@
+"""Self-check of a generated module (reference: fusion/code/gen_test.py:58-131 and the *_code.py templates,
+which emit a main() that runs ORI, GPTB and the fused kernel on the same seeded inputs and compares).
+
+Here one harness serves every pair: it loads the module, launches the generated kernel and the library's solo
+kernels on identical seeded inputs and demands bit-identical outputs of the CUDA-core kernel and of the GEMM.
+Needs a GPU; PyTorch only provides the device buffers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+
+def check_module(so_path: str, name: str, cd: str) -> dict:
+    import numpy as np
+    import torch
+
+    from .. import LAUNCH_FN, ops
+
+    mod = C.CDLL(so_path)
+    fn = LAUNCH_FN(C.cast(getattr(mod, f"tk_launch_{name}"), C.c_void_p).value)
+    info = (C.c_int * 4)()
+    getattr(mod, f"tk_generated_info_{name}")(info)
+    threads = info[0]
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    M, N, K = 512, 512, 256
+    A = (torch.rand(M, K, device="cuda", generator=gen) * 2 - 1).half()
+    B = (torch.rand(N, K, device="cuda", generator=gen) * 2 - 1).half()
+    sms = ops.sm_count()
+
+    def cd_kernel(bufs):
+        if cd == "stencil":
+            return ops.gptb_stencil(0.5, 0.25, bufs[0].data_ptr(), bufs[1].data_ptr(), 192, 12, 10)
+        if cd == "cp":
+            return ops.gptb_cp(150, 0.125, bufs[1].data_ptr(), bufs[0].data_ptr(), 256, 32)
+        return ops.gptb_mriq(64, bufs[0].data_ptr(), bufs[1].data_ptr(), bufs[2].data_ptr(), bufs[3].data_ptr(),
+                             bufs[4].data_ptr(), bufs[5].data_ptr(), 1024)
+
+    def fresh():
+        g = torch.Generator(device="cuda").manual_seed(11)
+        if cd == "stencil":
+            a0 = torch.rand(10, 12, 192, device="cuda", generator=g)
+            return [a0, a0.clone()], 1
+        if cd == "cp":
+            atoms = torch.rand(150, 4, device="cuda", generator=g) * 8
+            atoms[:, 2] = (atoms[:, 2] - 4) ** 2 + 0.5
+            return [atoms.contiguous(), torch.zeros(32, 256, device="cuda")], 1
+        xyz = [torch.rand(1024, device="cuda", generator=g) * 64 - 32 for _ in range(3)]
+        kv = torch.rand(64, 4, device="cuda", generator=g) - 0.5
+        return xyz + [torch.zeros(1024, device="cuda"), torch.zeros(1024, device="cuda"), kv.contiguous()], 3
+
+    st = torch.cuda.current_stream().cuda_stream
+    results = {}
+    for mode in ("solo", "generated"):
+        bufs, out_idx = fresh()
+        Cm = torch.zeros(M, N, device="cuda")
+        tz = ops.gptb_tzgemm(A.data_ptr(), B.data_ptr(), Cm.data_ptr(), M, N, K, alpha=1.1, grid=sms)
+        cdk = cd_kernel(bufs)
+        if mode == "solo":
+            tz.execute(st)
+            cdk.execute(st)
+        else:
+            mk = ops.mix(cdk, tz, cd_threads=threads - 192, grid=sms)
+            arr = (C.c_void_p * len(mk.kernelParams))(*[C.cast(C.pointer(p), C.c_void_p) for p in mk.kernelParams])
+            rc = fn(arr, len(mk.kernelParams), (C.c_uint * 3)(sms, 1, 1), (C.c_uint * 3)(threads, 1, 1), 0,
+                    C.c_void_p(st))
+            assert rc == 0, f"generated launcher returned {rc}"
+        torch.cuda.synchronize()
+        results[mode] = (Cm.cpu().numpy(), bufs[out_idx].cpu().numpy())
+    same_gemm = bool(np.array_equal(results["solo"][0], results["generated"][0]))
+    same_cd = bool(np.array_equal(results["solo"][1], results["generated"][1]))
+    return {"name": name, "threads": threads, "gemm_bit_identical": same_gemm, "cd_bit_identical": same_cd,
+            "ok": same_gemm and same_cd and bool(np.abs(results["generated"][0]).max() > 0)}

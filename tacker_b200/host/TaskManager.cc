@@ -206,7 +206,7 @@ ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pa
                                             double qos_factor, uint64_t seed, stream_t stream) {
     Backend& be = backend();
     ColocationResult r;
-    // ---- solo latency of the LC task: back-to-back queries, nothing else on the GPU ----
+    // ---- warm both tasks ----
     for (int i = 0; i < warmup_passes; ++i) {
         lc_task->initExecution();
         lc_task->enqueue(stream);
@@ -214,50 +214,49 @@ ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pa
         be_task->enqueue(stream);
     }
     be.streamSync(stream);
-    std::vector<double> solo;
-    for (int i = 0; i < 200; ++i) {
-        const double t0 = now_ms();
-        lc_task->initExecution();
-        lc_task->enqueue(stream);
-        be.streamSync(stream);
-        solo.push_back(now_ms() - t0);
-    }
-    r.lc_solo_p50_ms = percentile(solo, 0.50);
-    r.lc_solo_p99_ms = percentile(solo, 0.99);
-    r.qos_bound_ms = qos_factor * r.lc_solo_p99_ms;
-
-    // ---- Poisson arrivals; the best-effort task fills the gaps one kernel at a time ----
+    // ---- Poisson arrivals (the same sequence for both phases) ----
     std::vector<double> arrivals;
     double t = 0.0;
     for (uint64_t i = 0; t < seconds * 1e3; ++i) {
         t += -std::log(1.0 - static_cast<double>(tk_unit_draw(seed, i))) / qps * 1e3;
         arrivals.push_back(t);
     }
-    std::vector<double> lat;
-    size_t next = 0, be_pos = 0;
-    const double start = now_ms();
-    be_task->initExecution();
-    while (true) {
-        const double now = now_ms() - start;
-        if (now >= seconds * 1e3) break;
-        if (next < arrivals.size() && arrivals[next] <= now) {
-            lc_task->initExecution();
-            lc_task->enqueue(stream);
+    // One phase: serve every arrival in order; when idle, run the best-effort task one kernel at a time
+    // (or just wait, in the solo phase).  A query's latency runs from its arrival to the end of its last kernel,
+    // so queueing behind an earlier query or behind a best-effort kernel in flight is part of it.
+    size_t be_pos = 0;
+    auto phase = [&](Task* be_or_null, std::vector<double>& lat, long long* be_queries) {
+        size_t next = 0;
+        const double start = now_ms();
+        if (be_or_null) be_or_null->initExecution();
+        while (true) {
+            const double now = now_ms() - start;
+            if (now >= seconds * 1e3) break;
+            if (next < arrivals.size() && arrivals[next] <= now) {
+                lc_task->initExecution();
+                lc_task->enqueue(stream);
+                be.streamSync(stream);
+                lat.push_back(now_ms() - start - arrivals[next]);
+                ++next;
+                continue;
+            }
+            if (!be_or_null) continue;
+            be_or_null->kernels[be_pos]->execute(stream);
             be.streamSync(stream);
-            lat.push_back(now_ms() - start - arrivals[next]);
-            ++next;
-            continue;
+            if (++be_pos == be_or_null->kernels.size()) {
+                be_pos = 0;
+                *be_queries += be_queries_per_pass;
+                be_or_null->initExecution();
+            }
         }
-        // idle until the next arrival: one best-effort kernel, then look at the clock again
-        be_task->kernels[be_pos]->execute(stream);
-        be.streamSync(stream);
-        if (++be_pos == be_task->kernels.size()) {
-            be_pos = 0;
-            r.be_queries += be_queries_per_pass;
-            be_task->initExecution();
-        }
-    }
-    r.seconds = (now_ms() - start) / 1e3;
+        return (now_ms() - start) / 1e3;
+    };
+    std::vector<double> solo, lat;
+    phase(nullptr, solo, nullptr);   // the LC task alone under the same arrivals: the QoS yard-stick
+    r.lc_solo_p50_ms = percentile(solo, 0.50);
+    r.lc_solo_p99_ms = percentile(solo, 0.99);
+    r.qos_bound_ms = qos_factor * r.lc_solo_p99_ms;
+    r.seconds = phase(be_task, lat, &r.be_queries);
     r.lc_served = static_cast<long long>(lat.size());
     r.lc_p50_ms = percentile(lat, 0.50);
     r.lc_p99_ms = percentile(lat, 0.99);
