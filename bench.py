@@ -32,7 +32,7 @@ sys.path.insert(0, ROOT)
 M, N, K = 4096, 4096, 1024
 NX, NY, NZ, SWEEPS = 512, 512, 64, 10
 C0, C1 = 1.0 / 6.0, -1.0 / 6.0
-CD_THREADS = 384        # CUDA-core threads of the fused CTA (12 warps next to the 6 tensor-role warps)
+CD_THREADS = 512        # CUDA-core threads of the fused CTA (16 warps next to the 6 tensor-role warps)
 SOLO_CD_THREADS = 256   # solo stencil: 2 CTAs of 8 warps per SM
 TILES = (M // 64) * (N // 64)
 CD_BLOCKS = (NX // 64) * (NY // 4)
@@ -47,7 +47,7 @@ GEMM_BYTES = 2 * (M * K + N * K) + 4 * M * N
 LAUNCH_BYTES = SWEEP_BYTES + GEMM_BYTES / SWEEPS
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused launch, from the ncu capture
 # summarised in profiles/mix_stencil_config2_ncu.md (None until a capture exists)
-NCU_TRAFFIC_BYTES = None
+NCU_TRAFFIC_BYTES = {}
 
 
 def measured_peaks():
@@ -172,69 +172,19 @@ def run_reference(args):
 def run_ours(args):
     import torch
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the kernels are sm_100a only and there is no CPU fallback")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_
-
-        dist = dist_
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
     from tacker_b200 import ops
+    from tacker_b200.replicas import Replicas
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-
-    def max_over_ranks(v: float) -> float:
-        if dist is None:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
+    rep = Replicas(backend="nccl", device=torch.device("cuda", local))
+    rank, world = rep.rank, rep.world
     sms = ops.sm_count()
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    A = (torch.rand(M, K, device="cuda", generator=gen) * 2 - 1).half()
-    B = (torch.rand(N, K, device="cuda", generator=gen) * 2 - 1).half()
-    Cm = torch.zeros(M, N, device="cuda")
-    g0 = torch.rand(NZ, NY, NX, device="cuda", generator=gen)
-    for sl in ((0,), (-1,), (slice(None), 0), (slice(None), -1), (slice(None), slice(None), 0),
-               (slice(None), slice(None), -1)):
-        g0[sl] = 0.0
-    g1 = g0.clone()
-    grids = (g0, g1)
     stream = torch.cuda.Stream()
     st = stream.cuda_stream
-
-    def tz_kernel(start, end):
-        return ops.gptb_tzgemm(A.data_ptr(), B.data_ptr(), Cm.data_ptr(), M, N, K, alpha=1.0, start=start, end=end,
-                               grid=sms)
-
-    def cd_kernel(it, start=0, end=None, grid=None):
-        src, dst = grids[it & 1], grids[(it + 1) & 1]
-        return ops.gptb_stencil(C0, C1, src.data_ptr(), dst.data_ptr(), NX, NY, NZ, start=start, end=end,
-                                grid=grid or sms * 2, block=SOLO_CD_THREADS)
-
-    bounds = [TILES * i // SWEEPS for i in range(SWEEPS + 1)]
-    fused = [ops.mix(cd_kernel(i), tz_kernel(0, TILES), cd_threads=CD_THREADS, grid=sms,
-                     tz_range=(bounds[i], bounds[i + 1])) for i in range(SWEEPS)]
-    solo_tz = tz_kernel(0, TILES)
-    solo_cd = [cd_kernel(i) for i in range(SWEEPS)]
-
-    def fused_step():
-        for k in fused:
-            k.execute(st)
-
-    def sequential_step():
-        solo_tz.execute(st)
-        for k in solo_cd:
-            k.execute(st)
 
     def make_graph(fn):
         if args.no_graph:
@@ -253,23 +203,73 @@ def run_ours(args):
                 fn()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
-            barrier()
+            rep.barrier()
             e0.record(stream)
             for _ in range(steps):
                 fn()
             e1.record(stream)
             torch.cuda.synchronize()
-            barrier()
-        return max_over_ranks(e0.elapsed_time(e1)) / steps  # ms per step, max over ranks
+            rep.barrier()
+        return rep.max(e0.elapsed_time(e1)) / steps  # ms per step, max over ranks
+
+    def t_of(kernels, reps=None):
+        """us per pass over `kernels`; `reps` passes back to back in one graph so launch overhead cannot starve the GPU"""
+        reps = reps or (2 if args.quick else 20)
+
+        def fn():
+            for _ in range(reps):
+                for k in kernels:
+                    k.execute(st)
+        return timed(make_graph(fn), 3, 2) / reps * 1e3
+
+    # ---------------- config 2: GEMM 4096 x 4096 x 1024 + 10 Jacobi sweeps ----------------
+    A = (torch.rand(M, K, device="cuda", generator=gen) * 2 - 1).half()
+    B = (torch.rand(N, K, device="cuda", generator=gen) * 2 - 1).half()
+    Cm = torch.zeros(M, N, device="cuda")
+    g0 = torch.rand(NZ, NY, NX, device="cuda", generator=gen)
+    for sl in ((0,), (-1,), (slice(None), 0), (slice(None), -1), (slice(None), slice(None), 0),
+               (slice(None), slice(None), -1)):
+        g0[sl] = 0.0
+    g1 = g0.clone()
+    grids = (g0, g1)
+
+    def tz_kernel(start=0, end=TILES):
+        return ops.gptb_tzgemm(A.data_ptr(), B.data_ptr(), Cm.data_ptr(), M, N, K, alpha=1.0, start=start, end=end,
+                               grid=sms)
+
+    def cd_kernel(it):
+        src, dst = grids[it & 1], grids[(it + 1) & 1]
+        return ops.gptb_stencil(C0, C1, src.data_ptr(), dst.data_ptr(), NX, NY, NZ, grid=sms * 2, block=SOLO_CD_THREADS)
+
+    def schedule(fuse_sweeps):
+        """The pair as `fuse_sweeps` fused launches (sweep i + an equal share of the GEMM's tiles) followed by
+        the remaining sweeps alone.  10 = every sweep fused (1 tensor tile : 2.5 CUDA-core blocks)."""
+        bounds = [TILES * i // fuse_sweeps for i in range(fuse_sweeps + 1)]
+        ks = [ops.mix(cd_kernel(i), tz_kernel(), cd_threads=CD_THREADS, grid=sms, tz_range=(bounds[i], bounds[i + 1]))
+              for i in range(fuse_sweeps)]
+        return ks + [cd_kernel(i) for i in range(fuse_sweeps, SWEEPS)]
+
+    sequential = [tz_kernel()] + [cd_kernel(i) for i in range(SWEEPS)]
+
+    def runner(kernels):
+        def fn():
+            for k in kernels:
+                k.execute(st)
+        return make_graph(fn)
 
     sampler = ClockSampler(physical_gpu_index(local))
     sampler.start()
-
-    fused_fn = make_graph(fused_step)
-    seq_fn = make_graph(sequential_step)
     warm = max(args.warmup, 3)
-
     sampler.active.set()
+
+    # pick the fused schedule (each candidate timed briefly; every rank picks the same one)
+    cands = {}
+    for f in (SWEEPS, 2, 1):
+        cands[f] = timed(runner(schedule(f)), 10 if not args.quick else 2, 3)
+    best = min(cands, key=cands.get) if args.fuse_sweeps == 0 else args.fuse_sweeps
+    fused_kernels = schedule(best)
+    fused_fn = runner(fused_kernels)
+    seq_fn = runner(sequential)
     ms_fused = timed(fused_fn, args.steps, warm)
     ms_seq = timed(seq_fn, args.steps, warm)
     # continuation of the same fused loop, only to give the 20 ms clock sampler enough samples
@@ -282,32 +282,33 @@ def run_ours(args):
     sampler.active.clear()
     status = ops.device_status()
 
-    # ---- solo kernels and the tile-ratio sweep (explain the headline; rank 0 prints) ----
-    def t_of(kernels, reps=None):
-        reps = reps or (2 if args.quick else 20)
-        # `reps` back-to-back repetitions in one graph, so that launch overhead cannot starve the GPU
-        def fn():
-            for _ in range(reps):
-                for k in kernels:
-                    k.execute(st)
-        return timed(make_graph(fn), 3, 2) / reps
-
-    ms_gemm = t_of([solo_tz])
-    ms_sweep = t_of(solo_cd) / SWEEPS
+    # ---- the kernels one by one (explain the headline) ----
+    us_gemm = t_of([tz_kernel()])
+    us_sweep = t_of([cd_kernel(i) for i in range(SWEEPS)]) / SWEEPS
+    us_fused_launch = {}
+    for f in (SWEEPS, 2, 1):
+        lo, hi = 0, TILES // f
+        us_fused_launch[f] = t_of([ops.mix(cd_kernel(i), tz_kernel(), cd_threads=CD_THREADS, grid=sms, tz_range=(lo, hi))
+                                   for i in range(2)]) / 2
     sweep = []
     if not args.quick:
         for r in (1, 2, 3, 4, 5, 6, 7, 8):
             nt = CD_BLOCKS // r  # GEMM tiles co-run with one sweep's 1024 CUDA-core blocks: 1 : r
-            f = t_of([ops.mix(cd_kernel(0), tz_kernel(0, TILES), cd_threads=CD_THREADS, grid=sms, tz_range=(0, nt))])
-            s = t_of([tz_kernel(0, nt)]) + ms_sweep
+            f = t_of([ops.mix(cd_kernel(i), tz_kernel(), cd_threads=CD_THREADS, grid=sms, tz_range=(0, nt))
+                      for i in range(2)]) / 2
+            s_ = t_of([tz_kernel(0, nt)]) + us_sweep
             sweep.append({"tensor_to_cd_tiles": f"1:{r}", "gemm_tiles": nt, "cd_blocks": CD_BLOCKS,
-                          "fused_us": round(f * 1e3, 2), "sequential_us": round(s * 1e3, 2), "ratio": round(f / s, 4)})
-        # balanced point: as many GEMM tiles as take about one sweep's time
-        nt = min(TILES, max(64, int(TILES * ms_sweep / ms_gemm)))
-        f = t_of([ops.mix(cd_kernel(0), tz_kernel(0, TILES), cd_threads=CD_THREADS, grid=sms, tz_range=(0, nt))])
-        s = t_of([tz_kernel(0, nt)]) + ms_sweep
-        sweep.append({"tensor_to_cd_tiles": f"balanced {nt}:{CD_BLOCKS}", "gemm_tiles": nt, "cd_blocks": CD_BLOCKS,
-                      "fused_us": round(f * 1e3, 2), "sequential_us": round(s * 1e3, 2), "ratio": round(f / s, 4)})
+                          "fused_us": round(f, 2), "sequential_us": round(s_, 2), "ratio": round(f / s_, 4)})
+        for nt in (2048, 4096):
+            s_ = t_of([tz_kernel(0, nt)]) + us_sweep
+            f = us_fused_launch[TILES // nt]
+            sweep.append({"tensor_to_cd_tiles": f"{nt // CD_BLOCKS}:1", "gemm_tiles": nt, "cd_blocks": CD_BLOCKS,
+                          "fused_us": round(f, 2), "sequential_us": round(s_, 2), "ratio": round(f / s_, 4)})
+
+    # ---- the other two pairs (configs 3 and 4): fused vs sequential on identical work ----
+    pairs = None
+    if not args.quick:
+        pairs = other_pairs(torch, ops, sms, gen, t_of, st)
 
     # ---- end to end through the host-buffer C-ABI call ----
     hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
@@ -334,7 +335,9 @@ def run_ours(args):
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
         import tacker_ref as ref
 
-        if ref.available() and rank == 0 and not args.quick:
+        if ref.available() and rank == 0 and world == 1 and not args.quick:
+            bounds = [TILES * i // SWEEPS for i in range(SWEEPS + 1)]
+
             def ref_fused():
                 for i in range(SWEEPS):
                     src, dst = grids[i & 1], grids[(i + 1) & 1]
@@ -347,13 +350,29 @@ def run_ours(args):
                     src, dst = grids[i & 1], grids[(i + 1) & 1]
                     ref.stencil(C0, C1, src.data_ptr(), dst.data_ptr(), NX, NY, NZ, 0, CD_BLOCKS, sms * 3, st)
 
-            if dist is None:
-                rf, rs = timed(ref_fused, 10, 3), timed(ref_seq, 10, 3)
-                ref_gpu = {"what": "reference wmma/GPTB kernels recompiled for sm_100, same pair, same GPU",
-                           "fused_ms_per_pair": round(rf, 4), "sequential_ms_per_pair": round(rs, 4),
-                           "fused_vs_sequential": round(rf / rs, 4)}
+            rf, rs = timed(ref_fused, 10, 3), timed(ref_seq, 10, 3)
+            ref_gpu = {"what": "reference wmma/GPTB kernels recompiled for sm_100, same pair, same GPU",
+                       "fused_ms_per_pair": round(rf, 4), "sequential_ms_per_pair": round(rs, 4),
+                       "fused_vs_sequential": round(rf / rs, 4)}
     except Exception as e:  # test infrastructure absent: not an error of the product
         ref_gpu = {"unavailable": repr(e)[:120]}
+
+    # ---- request-driven co-location on this GPU (LC VGG16 b1 at 200 q/s Poisson, BE BERT-base b8 s128) ----
+    coloc = None
+    if not args.quick and args.colocate_s > 0:
+        try:
+            from tacker_b200 import colocate
+
+            c = colocate.run(1, args.colocate_s, 200.0, 1.5, devices=[physical_gpu_index(local)])
+            coloc = {k: c[k] for k in ("be_qps_total", "lc_p99_ms_max", "lc_solo_p99_ms_max", "qos_met_all", "seconds",
+                                       "lc", "be", "qps_offered_per_gpu")}
+        except Exception as e:
+            coloc = {"unavailable": repr(e)[:200]}
+        gathered = rep.gather(coloc)
+        if all(isinstance(g, dict) and "be_qps_total" in g for g in gathered):
+            coloc = dict(coloc, be_qps_total=sum(g["be_qps_total"] for g in gathered),
+                         lc_p99_ms_max=max(g["lc_p99_ms_max"] for g in gathered),
+                         qos_met_all=all(g["qos_met_all"] for g in gathered), gpus=world)
 
     cpu = None
     if rank == 0 and world == 1 and not args.quick:
@@ -365,41 +384,109 @@ def run_ours(args):
                "sample": "1/4 of the GEMM's tiles + 5 of the 10 sweeps, scaled to one pair; best of 2"}
 
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        rep.close()
         return
     hbm, tflops, which = measured_peaks()
-    launch_s = ms_fused / SWEEPS / 1e3
-    achieved = LAUNCH_BYTES / launch_s / 1e9
+    # the kernel with the largest share of the step's device time
+    n_solo = SWEEPS - best
+    share_solo = n_solo * us_sweep / (ms_fused * 1e3)
+    if share_solo >= 0.5:
+        roof = {"kernel": "stencil_tma_kernel (one sweep, solo)", "launches_per_step": n_solo,
+                "share_of_step": round(share_solo, 3), "bound": "hbm", "achieved": SWEEP_BYTES / (us_sweep * 1e-6) / 1e9,
+                "algorithmic_bytes_per_launch": SWEEP_BYTES, "traffic": NCU_TRAFFIC_BYTES.get("stencil_tma_kernel")}
+    else:
+        bytes_launch = SWEEP_BYTES + GEMM_BYTES / best
+        roof = {"kernel": "mix_stencil_kernel (one sweep + 1/%d of the GEMM tiles)" % best, "launches_per_step": best,
+                "share_of_step": round(1.0 - share_solo, 3), "bound": "hbm",
+                "achieved": bytes_launch / (us_fused_launch[best] * 1e-6) / 1e9,
+                "algorithmic_bytes_per_launch": bytes_launch, "traffic": NCU_TRAFFIC_BYTES.get("mix_stencil_kernel")}
+    roof.update({"peak": hbm, "unit": "GB/s", "frac": roof["achieved"] / hbm,
+                 "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({which})",
+                 "tensor_frac_solo_gemm": round(2.0 * M * N * K / (us_gemm * 1e-6) / 1e12 / tflops, 4)})
     line = {
         "metric": METRIC, "value": world * 1e3 / ms_fused, "unit": "pairs/s", "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": ms_fused, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16 inputs, f32 accumulate (tensor role) / f32 (CUDA-core role)", "data": "synthetic",
         "config": {"workload": WORKLOAD, "cd_threads": CD_THREADS, "grid": sms, "replicas": world,
+                   "schedule": f"{best} fused launches (sweep + {TILES // best} GEMM tiles each) + {SWEEPS - best} solo sweeps",
                    "l2": "inputs 80 MiB (GEMM) + 128 MiB (grids) exceed the 126 MB L2; no flush between steps",
-                   "launch": "CUDA graph of the 10 fused launches" if not args.no_graph else "10 stream launches"},
+                   "launch": "CUDA graph of the step's launches" if not args.no_graph else "stream launches"},
         "fused_vs_sequential": ms_fused / ms_seq, "sequential_ms_per_step": ms_seq,
-        "solo_us": {"tzgemm_4096x4096x1024": round(ms_gemm * 1e3, 2), "stencil_sweep": round(ms_sweep * 1e3, 2),
-                    "tzgemm_tflops": round(2.0 * M * N * K / (ms_gemm * 1e-3) / 1e12, 1),
-                    "stencil_gbs": round(SWEEP_BYTES / (ms_sweep * 1e-3) / 1e9, 1)},
-        "ratio_sweep": sweep,
-        "clocks": clocks,
+        "schedules_ms_per_pair": {f"{f}_fused_launches": round(v, 4) for f, v in cands.items()},
+        "solo_us": {"tzgemm_4096x4096x1024": round(us_gemm, 2), "stencil_sweep": round(us_sweep, 2),
+                    "tzgemm_tflops": round(2.0 * M * N * K / (us_gemm * 1e-6) / 1e12, 1),
+                    "stencil_gbs": round(SWEEP_BYTES / (us_sweep * 1e-6) / 1e9, 1),
+                    "fused_launch_us": {f"sweep+{TILES // f}_tiles": round(v, 2) for f, v in us_fused_launch.items()}},
+        "ratio_sweep": sweep, "pairs": pairs, "clocks": clocks,
         "e2e": {"value": world * 1e3 / ms_e2e, "unit": "pairs/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e, "steps": e2e_steps,
                 "call": "tk_pair_tzgemm_stencil_host (pinned host buffers in and out)"},
-        "gpu_launches": args.steps * SWEEPS,
-        "roofline": {"kernel": "mix_stencil_kernel (fused tzgemm tiles + one stencil sweep)", "bound": "hbm",
-                     "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                     "traffic": NCU_TRAFFIC_BYTES, "algorithmic_bytes_per_launch": LAUNCH_BYTES,
-                     "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({which})",
-                     "tensor_frac_solo_gemm": round(2.0 * M * N * K / (ms_gemm * 1e-3) / 1e12 / tflops, 4)},
-        "cpu_baseline": cpu,
-        "ref_gpu": ref_gpu,
-        "device_status": status,
+        "gpu_launches": args.steps * len(fused_kernels),
+        "roofline": roof, "cpu_baseline": cpu, "ref_gpu": ref_gpu, "colocation": coloc, "device_status": status,
     }
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    rep.close()
+
+
+def other_pairs(torch, ops, sms, gen, t_of, st):
+    """Configs 3 and 4: GEMM + Coulomb (compute-bound CUDA-core pair), GEMM + MRI-Q (SFU-bound pair)."""
+    out = {}
+
+    def gemm(m, n, k):
+        a = (torch.rand(m, k, device="cuda", generator=gen) * 2 - 1).half()
+        b = (torch.rand(n, k, device="cuda", generator=gen) * 2 - 1).half()
+        c = torch.zeros(m, n, device="cuda")
+        return lambda s=0, e=None: ops.gptb_tzgemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, alpha=1.0, start=s,
+                                                   end=e, grid=sms), (a, b, c)
+
+    # config 3: GEMM 2048^3 + 8192 atoms on a 512 x 512 lattice
+    tz, keep3 = gemm(2048, 2048, 2048)
+    atoms = torch.rand(8192, 4, device="cuda", generator=gen) * 64
+    atoms[:, 3] = torch.rand(8192, device="cuda", generator=gen) * 2 - 1
+    packed = torch.empty_like(atoms)
+    lat = torch.zeros(512, 512, device="cuda")
+    ops.cp_pack_atoms(atoms.data_ptr(), 8192, 32.0, packed.data_ptr(), st)
+    cp = lambda s=0, e=None, grid=None, block=256: ops.gptb_cp(8192, 0.125, lat.data_ptr(), packed.data_ptr(), 512, 512,
+                                                               start=s, end=e, grid=grid or sms * 2, block=block)
+    ops.set_option("cp_ppt", 4)
+    try:
+        t_g, t_c = t_of([tz()], 10), t_of([cp()], 3)
+        t_f = t_of([ops.mix(cp(), tz(), cd_threads=448, grid=sms)], 3)
+        nb = max(8, int(round(256 * t_g / t_c)))           # blocks of Coulomb work worth one GEMM
+        t_cb = t_of([cp(0, nb)], 5)
+        t_fb = t_of([ops.mix(cp(0, nb), tz(), cd_threads=448, grid=sms)], 5)
+    finally:
+        ops.set_option("cp_ppt", 8)
+    pairs3 = 8192.0 * 512 * 512
+    out["config3_gemm2048_coulomb"] = {
+        "gemm_us": round(t_g, 1), "coulomb_us": round(t_c, 1), "fused_us": round(t_f, 1),
+        "fused_vs_sequential": round(t_f / (t_g + t_c), 4), "coulomb_gpairs_per_s": round(pairs3 / t_c / 1e3, 1),
+        "balanced": {"coulomb_blocks": nb, "coulomb_us": round(t_cb, 1), "fused_us": round(t_fb, 1),
+                     "fused_vs_sequential": round(t_fb / (t_g + t_cb), 4)}}
+
+    # config 4: GEMM 4096 x 4096 x 2048 + MRI-Q 2048 samples x 262144 voxels
+    tz4, keep4 = gemm(4096, 4096, 2048)
+    numK, numX = 2048, 262144
+    kv = torch.rand(numK, 4, device="cuda", generator=gen) - 0.5
+    kv[:, 3] = torch.rand(numK, device="cuda", generator=gen)
+    xyz = [torch.rand(numX, device="cuda", generator=gen) * 64 - 32 for _ in range(3)]
+    qr, qi = torch.zeros(numX, device="cuda"), torch.zeros(numX, device="cuda")
+    mq = lambda s=0, e=None, grid=None, block=512: ops.gptb_mriq(numK, xyz[0].data_ptr(), xyz[1].data_ptr(),
+                                                                 xyz[2].data_ptr(), qr.data_ptr(), qi.data_ptr(),
+                                                                 kv.data_ptr(), numX, start=s, end=e, grid=grid or sms * 2,
+                                                                 block=block)
+    t_g, t_m = t_of([tz4()], 10), t_of([mq()], 3)
+    t_f = t_of([ops.mix(mq(), tz4(), cd_threads=704, grid=sms)], 3)
+    nb = max(148, int(round(1024 * t_g / t_m)))
+    t_mb = t_of([mq(0, nb)], 5)
+    t_fb = t_of([ops.mix(mq(0, nb), tz4(), cd_threads=704, grid=sms)], 5)
+    out["config4_gemm4096x2048_mriq"] = {
+        "gemm_us": round(t_g, 1), "mriq_us": round(t_m, 1), "fused_us": round(t_f, 1),
+        "fused_vs_sequential": round(t_f / (t_g + t_m), 4), "mriq_gpairs_per_s": round(numK * numX / t_m / 1e3, 1),
+        "balanced": {"mriq_blocks": nb, "mriq_us": round(t_mb, 1), "fused_us": round(t_fb, 1),
+                     "fused_vs_sequential": round(t_fb / (t_g + t_mb), 4)}}
+    del keep3, keep4
+    return out
 
 
 def main():
@@ -411,6 +498,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the 10 kernels of a step one by one")
     ap.add_argument("--quick", action="store_true", help="skip the ratio sweep, the CPU sample and the reference kernels")
     ap.add_argument("--sustain-ms", type=float, default=400.0)
+    ap.add_argument("--colocate-s", type=float, default=5.0, help="seconds of the LC/BE co-location run (0 = skip)")
+    ap.add_argument("--fuse-sweeps", type=int, default=0, choices=(0, 1, 2, 10),
+                    help="how many sweeps are fused with the GEMM (0 = time 10, 2 and 1 briefly and take the best)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps == 200:

@@ -212,8 +212,8 @@ int tk_coulomb_compute(const float* atoms_xyzq, int numatoms, float zplane, floa
                        int nx, int ny, float* packed_scratch, void* stream);
 
 /* ---- host-buffer pair (what an end-to-end caller times) ---------------------------------------------
- * C = alpha * A * B^T together with `sweeps` ping-pong stencil sweeps of A0, as `sweeps` fused launches
- * (sweep i co-runs with the i-th slice of the GEMM's tiles).  All five buffers are HOST memory (pinned
+ * C = alpha * A * B^T together with `sweeps` ping-pong stencil sweeps of A0: the first two sweeps are fused
+ * launches that each co-run with half of the GEMM's tiles, the remaining sweeps run alone.  All five buffers are HOST memory (pinned
  * for full copy speed); inputs are copied to the device workspace and results copied back on `stream`;
  * the call returns once everything is enqueued.  Mirrors what the reference's harness does around a
  * fused launch: cudaMemcpy of the inputs in initParams (src/ori_kernel/stencil_kernel.cu:143-160), the

@@ -1,0 +1,59 @@
+"""Per-GPU co-location across a node: one `aker --colocate` process per GPU, independent request streams,
+no communication between them (co-location is per GPU); the result lines are summed here.
+
+    python -m tacker_b200.colocate --gpus 8 --seconds 60 --qps 200 --qos 1.5 --lc vgg16 --be bert
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+
+from . import _build
+
+HOST = os.path.join(os.path.dirname(os.path.abspath(__file__)), "host")
+
+
+def run(gpus: int, seconds: float, qps: float, qos: float, lc: str = "vgg16", be: str = "bert", devices=None) -> dict:
+    exe = os.path.join(_build.LIB_DIR, "aker")
+    if not os.path.exists(exe):
+        raise RuntimeError(f"{exe} is missing: build it with `python -m tacker_b200._build`")
+    devices = list(range(gpus)) if devices is None else list(devices)
+    procs = []
+    for d in devices:
+        cmd = [exe, "-s", "aker", "-m", lc, "-d", str(d), "-c", os.path.join(HOST, "config"), "--colocate",
+               str(seconds), "--qps", str(qps), "--qos", str(qos), "--be", be]
+        procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd="/tmp"))
+    per_gpu = []
+    for d, p in zip(devices, procs):
+        out, err = p.communicate(timeout=seconds * 3 + 300)
+        if p.returncode != 0:
+            raise RuntimeError(f"aker on device {d} failed: {err[-500:]}")
+        per_gpu.append(json.loads([l for l in out.splitlines() if l.startswith("{")][-1]))
+    return {
+        "gpus": len(devices), "lc": lc, "be": be, "qps_offered_per_gpu": qps, "seconds": seconds,
+        "be_qps_total": sum(r["be_qps"] for r in per_gpu),
+        "lc_p99_ms_max": max(r["lc_p99_ms"] for r in per_gpu),
+        "lc_solo_p99_ms_max": max(r["lc_solo_p99_ms"] for r in per_gpu),
+        "qos_met_all": all(r["qos_met"] for r in per_gpu),
+        "per_gpu": per_gpu,
+    }
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--seconds", type=float, default=60.0)
+    ap.add_argument("--qps", type=float, default=200.0)
+    ap.add_argument("--qos", type=float, default=1.5)
+    ap.add_argument("--lc", default="vgg16")
+    ap.add_argument("--be", default="bert")
+    a = ap.parse_args(argv)
+    print(json.dumps(run(a.gpus, a.seconds, a.qps, a.qos, a.lc, a.be)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -34,6 +34,7 @@ struct StencilArgs {
     int gx, gy;      // virtual grid (64-wide, 4-high bundles)
     int start, end;  // virtual block range
     int slabs, per;  // z split chosen by the host: `slabs` work items per block, `per` planes each
+    int l2_hints;    // 1: planes are loaded with the evict-first L2 priority (they are streamed once)
 };
 
 constexpr int kStencilGroup = 64;  // threads per work item: 16 float4 lanes x 4 rows own a z-slab of a bundle

@@ -35,6 +35,7 @@ struct GemmArgs {
     unsigned* status;    // device status word (bounded-wait expiries)
     int batch;           // independent problems of the same shape (1 for the reference's tzgemm)
     long long stride_c;  // elements between consecutive C matrices of a batch
+    int l2_hints;        // 1: operand tiles are loaded with the evict-last L2 priority
 };
 
 template <int BN, int STAGES>
@@ -152,6 +153,7 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const uint64_t keep = l2_policy_evict_last();
             for (int cand = blockIdx.x; cand < walk.ncand && ok; cand += gridDim.x) {
                 int R, Cc, b;
                 if (walk.mask(cand, R, Cc, b) == 0u) continue;
@@ -160,8 +162,13 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
                     if (!ok) break;
                     mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
-                    tma_load_tile(a_dst, tmap_a, full_bar(stage), kb * kGemmBK, R * kGemmBM, b);
-                    tma_load_tile(a_dst + L::kABytes, tmap_b, full_bar(stage), kb * kGemmBK, Cc * BN, b);
+                    if (g.l2_hints) {
+                        tma_load_tile_hint(a_dst, tmap_a, full_bar(stage), kb * kGemmBK, R * kGemmBM, b, keep);
+                        tma_load_tile_hint(a_dst + L::kABytes, tmap_b, full_bar(stage), kb * kGemmBK, Cc * BN, b, keep);
+                    } else {
+                        tma_load_tile(a_dst, tmap_a, full_bar(stage), kb * kGemmBK, R * kGemmBM, b);
+                        tma_load_tile(a_dst + L::kABytes, tmap_b, full_bar(stage), kb * kGemmBK, Cc * BN, b);
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;

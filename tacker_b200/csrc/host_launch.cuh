@@ -39,6 +39,9 @@ struct Options {
     int stencil_tma = 1;        // 1 = TMA-fed role whenever the shape allows, 0 = always the register role
     int stencil_ring = 4;       // ring depth per warp, solo kernel (2 planes in flight per warp measured best)
     int mix_stencil_ring = 12;  // upper bound of the ring depth in the fused kernel (shared memory decides)
+    int l2_hints = 0;           // fused kernels: GEMM tiles evict-last, stencil planes evict-first in L2
+    int mix_stencil_cfg = 0;    // tensor-role shape of the fused stencil kernel: 0 auto, 1 = 256x3 stages,
+                                // 2 = 128x4, 3 = 128x3, 4 = 128x2
 };
 static Options g_opt;
 
@@ -165,6 +168,7 @@ static int parse_gemm(void** params, int base, int i_start, int i_end, GemmCall*
     c->g.status = nullptr;
     c->g.batch = 1;
     c->g.stride_c = 0;
+    c->g.l2_hints = 0;
     const bool empty = c->g.start >= c->g.end;
     if (c->g.M < 128 || c->g.N < 64 || c->g.K < 64) return TK_ERR_SHAPE;
     if (c->g.M % 128 || c->g.N % 64 || c->g.K % 64) return TK_ERR_SHAPE;
@@ -228,6 +232,9 @@ static int parse_stencil(void** p, int i_start, int i_end, StencilArgs* s) {
     const int bdx = arg<int>(p, 10), bdy = arg<int>(p, 11);
     s->start = arg<int>(p, i_start);
     s->end = arg<int>(p, i_end);
+    s->l2_hints = 0;
+    s->slabs = 1;
+    s->per = 1;
     if (s->nx <= 0 || s->ny <= 0 || s->nz <= 0 || s->gx <= 0 || s->gy <= 0 || s->start < 0) return TK_ERR_ARGS;
     if (bdx != 32 || bdy != 4) return TK_ERR_SHAPE;  // the 64 x 4 bundle is the virtual-block unit
     if (s->end > s->gx * s->gy) s->end = s->gx * s->gy;  // see the note on ranges in the header
@@ -388,23 +395,20 @@ struct CdCall {
     }
 };
 
-// The stencil's rings share the CTA's shared memory with the tensor role's stages: fewer, larger
-// stages for the GEMM here than in the solo kernel, so that the rings get about 80 KB.
-template <int BN>
-struct StagesMixStencil {
-    static constexpr int value = BN == 256 ? 3 : 4;
-};
-
-template <int BN>
-static int launch_mix_stencil(const GemmCall& c, const CUtensorMap& ta, const CUtensorMap& tb, StencilArgs s,
-                              unsigned ctas, unsigned threads, cudaStream_t st) {
-    constexpr int STAGES = StagesMixStencil<BN>::value;
+// The stencil's rings share the CTA's shared memory with the tensor role's stages, so the fused stencil
+// kernel exists in several (super-tile width, stage count) shapes: a launch whose GEMM share is small gives
+// most of the shared memory to the rings, a GEMM-heavy launch keeps a deep operand pipeline.
+template <int BN, int STAGES>
+static int launch_mix_stencil(const GemmCall& c, StencilArgs s, unsigned ctas, unsigned threads, cudaStream_t st) {
     constexpr int kGemmBytes = GemmSmem<BN, STAGES>::kBytes + 1024;
     auto k = mix_stencil_kernel<BN, STAGES>;
-    const int nwarps = static_cast<int>((threads - kGemmThreads) / 32);
-    int ring = 0, smem = kGemmBytes, rc;
-    CUtensorMap tg;
+    CUtensorMap ta, tb, tg;
     std::memset(&tg, 0, sizeof(tg));
+    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
+    if (rc != TK_OK) return rc;
+    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN)) != TK_OK) return rc;
+    const int nwarps = static_cast<int>((threads - kGemmThreads) / 32);
+    int ring = 0, smem = kGemmBytes;
     if (stencil_tma_ok(s)) {
         ring = g_opt.mix_stencil_ring;
         while (ring >= kStMinRing && kGemmBytes + nwarps * stencil_tma_warp_bytes(ring) > kMaxDynSmem) --ring;
@@ -425,6 +429,19 @@ static int launch_mix_stencil(const GemmCall& c, const CUtensorMap& ta, const CU
     return launch_error("mix_stencil_kernel launch");
 }
 
+static int run_mix_stencil(const GemmCall& c, const StencilArgs& s, unsigned ctas, unsigned threads, cudaStream_t st) {
+    int cfg = g_opt.mix_stencil_cfg;
+    // Measured on B200 (config 2, 8 to 22 CUDA-core warps, 64 to 4096 GEMM tiles): the 128-wide super-tile with
+    // 4 stages is the best or within 2% of the best everywhere -- it leaves ~100 KB to the stencil's rings.
+    if (cfg == 0) cfg = 2;
+    switch (cfg) {
+        case 1: return launch_mix_stencil<256, 3>(c, s, ctas, threads, st);
+        case 2: return launch_mix_stencil<128, 4>(c, s, ctas, threads, st);
+        case 3: return launch_mix_stencil<128, 3>(c, s, ctas, threads, st);
+        default: return launch_mix_stencil<128, 2>(c, s, ctas, threads, st);
+    }
+}
+
 template <int BN>
 static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsigned threads, cudaStream_t st) {
     constexpr int STAGES = StagesFor<BN>::value;
@@ -436,7 +453,7 @@ static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsign
     const int smem = gemm_smem_bytes<BN>();
     switch (cd.kind) {
         case CD_STENCIL:
-            return launch_mix_stencil<BN>(c, ta, tb, cd.s, ctas, threads, st);
+            return TK_ERR_ARGS;  // handled by run_mix_stencil
         case CD_CP: {
             if (g_opt.cp_ppt == 2) {
                 auto k = mix_cp_kernel<BN, STAGES, 2>;
@@ -463,11 +480,14 @@ static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsign
     return launch_error("mix kernel launch");
 }
 
-static int run_mix(GemmCall& c, const CdCall& cd, unsigned grid0, unsigned block0, cudaStream_t st) {
+static int run_mix(GemmCall& c, const CdCall& cd_in, unsigned grid0, unsigned block0, cudaStream_t st) {
     DeviceInfo* d = nullptr;
     int rc = device_info(&d);
     if (rc != TK_OK) return rc;
     c.g.status = d->status_ptr;
+    CdCall cd = cd_in;
+    c.g.l2_hints = g_opt.l2_hints;
+    cd.s.l2_hints = g_opt.l2_hints;
     const bool gemm_empty = c.g.start >= c.g.end;
     if (gemm_empty && cd.empty()) return TK_OK;
     if (block0 <= static_cast<unsigned>(kGemmThreads)) return TK_ERR_LAUNCH_CONFIG;
@@ -484,6 +504,7 @@ static int run_mix(GemmCall& c, const CdCall& cd, unsigned grid0, unsigned block
     if (cd.empty()) return run_tzgemm(c, grid0, st);
     const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
     const unsigned threads = kGemmThreads + cdt;
+    if (cd.kind == CD_STENCIL) return run_mix_stencil(c, cd.s, ctas, threads, st);
     return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_mix<256>(c, cd, ctas, threads, st)
                                                         : launch_mix<128>(c, cd, ctas, threads, st);
 }

@@ -118,6 +118,27 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst_smem, const void* tma
         : "memory");
 }
 
+// L2 eviction-priority policies for bulk loads: operands that are re-read by other CTAs (GEMM tiles) are
+// kept, data that is streamed once (stencil planes) is marked to go first.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma_load_tile_hint(uint32_t dst_smem, const void* tmap, uint32_t bar, int x, int y,
+                                                   int z, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+        : "memory");
+}
+
 // ---- tcgen05 ---------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t result_slot_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot_smem),

@@ -118,11 +118,16 @@ __device__ __forceinline__ void stencil_role_tma(const CUtensorMap* __restrict__
     int cslot = 0;                    // slot of the consumer's next plane
     uint32_t cphase = 0;              // parity of the full barrier the consumer waits on next
 
+    const uint64_t stream_once = l2_policy_evict_first();
     auto fill = [&]() {  // lane 0: issue as far ahead as the ring allows
         while (prod.n != 0 && issued < freed + static_cast<uint32_t>(ring)) {
             const uint32_t bar = bars + 8u * pslot;
             mbar_arrive_expect_tx(bar, kStPlaneBytes);
-            tma_load_3d(slots + pslot * kStSlotBytes, tmap, bar, prod.x0 - 4, prod.j0 - 1, prod.kbase + prod.q);
+            if (s.l2_hints)
+                tma_load_tile_hint(slots + pslot * kStSlotBytes, tmap, bar, prod.x0 - 4, prod.j0 - 1, prod.kbase + prod.q,
+                                   stream_once);
+            else
+                tma_load_3d(slots + pslot * kStSlotBytes, tmap, bar, prod.x0 - 4, prod.j0 - 1, prod.kbase + prod.q);
             if (++pslot == ring) pslot = 0;
             ++issued;
             prod.advance(s, nitems);

@@ -47,6 +47,8 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "stencil_tma")) return &g_opt.stencil_tma;
     if (!std::strcmp(name, "stencil_ring")) return &g_opt.stencil_ring;
     if (!std::strcmp(name, "mix_stencil_ring")) return &g_opt.mix_stencil_ring;
+    if (!std::strcmp(name, "l2_hints")) return &g_opt.l2_hints;
+    if (!std::strcmp(name, "mix_stencil_cfg")) return &g_opt.mix_stencil_cfg;
     return nullptr;
 }
 
@@ -481,6 +483,7 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     c.g.status = nullptr;
     c.g.batch = 1;
     c.g.stride_c = 0;
+    c.g.l2_hints = 0;
     if (M < 128 || N < 64 || K < 64 || M % 128 || N % 64 || K % 64) return TK_ERR_SHAPE;
     const int tiles = (M / 64) * (N / 64);
     CdCall cd;
@@ -495,13 +498,21 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     cd.s.start = 0;
     cd.s.end = cd.s.gx * cd.s.gy;
     const unsigned block = kGemmThreads + static_cast<unsigned>(cd_threads > 0 ? cd_threads : 256);
+    // The GEMM co-runs with the first sweeps (half of its tiles with each of the first two); the other sweeps
+    // run alone.  A sweep is memory bound on its own, so spreading the GEMM thinner only lengthens every launch.
+    const int fused = sweeps < 2 ? sweeps : 2;
+    cd.s.l2_hints = 0;
     for (int it = 0; it < sweeps; ++it) {
         cd.s.A0 = (it & 1) ? g1 : g0;
         cd.s.Anext = (it & 1) ? g0 : g1;
-        // the GEMM's tiles are dealt evenly over the sweeps
-        c.g.start = static_cast<int>(static_cast<long long>(tiles) * it / sweeps);
-        c.g.end = static_cast<int>(static_cast<long long>(tiles) * (it + 1) / sweeps);
-        if ((rc = run_mix(c, cd, static_cast<unsigned>(d->sm_count), block, st)) != TK_OK) return rc;
+        if (it < fused) {
+            c.g.start = static_cast<int>(static_cast<long long>(tiles) * it / fused);
+            c.g.end = static_cast<int>(static_cast<long long>(tiles) * (it + 1) / fused);
+            rc = run_mix(c, cd, static_cast<unsigned>(d->sm_count), block, st);
+        } else {
+            rc = run_stencil(cd.s, static_cast<unsigned>(d->sm_count) * 2u, 256, st);
+        }
+        if (rc != TK_OK) return rc;
     }
     TK_CUDA(cudaMemcpyAsync(C_host, dC, c_bytes, cudaMemcpyDeviceToHost, st));
     TK_CUDA(cudaMemcpyAsync(Aout_host, (sweeps & 1) ? g1 : g0, g_bytes, cudaMemcpyDeviceToHost, st));
@@ -822,6 +833,7 @@ TK_API int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int 
     c.g.end = (M / 64) * (N / 64);
     c.g.status = nullptr;
     c.g.batch = batch;
+    c.g.l2_hints = 0;
     c.g.stride_c = stride_c > 0 ? stride_c : static_cast<long long>(M) * N;
     DeviceInfo* d = nullptr;
     int rc = device_info(&d);
