@@ -448,7 +448,6 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
     ops.cp_pack_atoms(atoms.data_ptr(), 8192, 32.0, packed.data_ptr(), st)
     cp = lambda s=0, e=None, grid=None, block=256: ops.gptb_cp(8192, 0.125, lat.data_ptr(), packed.data_ptr(), 512, 512,
                                                                start=s, end=e, grid=grid or sms * 2, block=block)
-    ops.set_option("cp_ppt", 4)
     try:
         t_g, t_c = t_of([tz()], 10), t_of([cp()], 3)
         t_f = t_of([ops.mix(cp(), tz(), cd_threads=448, grid=sms)], 3)
@@ -456,7 +455,7 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
         t_cb = t_of([cp(0, nb)], 5)
         t_fb = t_of([ops.mix(cp(0, nb), tz(), cd_threads=448, grid=sms)], 5)
     finally:
-        ops.set_option("cp_ppt", 8)
+        pass
     pairs3 = 8192.0 * 512 * 512
     out["config3_gemm2048_coulomb"] = {
         "gemm_us": round(t_g, 1), "coulomb_us": round(t_c, 1), "fused_us": round(t_f, 1),
@@ -471,9 +470,9 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
     kv[:, 3] = torch.rand(numK, device="cuda", generator=gen)
     xyz = [torch.rand(numX, device="cuda", generator=gen) * 64 - 32 for _ in range(3)]
     qr, qi = torch.zeros(numX, device="cuda"), torch.zeros(numX, device="cuda")
-    mq = lambda s=0, e=None, grid=None, block=512: ops.gptb_mriq(numK, xyz[0].data_ptr(), xyz[1].data_ptr(),
+    mq = lambda s=0, e=None, grid=None, block=256: ops.gptb_mriq(numK, xyz[0].data_ptr(), xyz[1].data_ptr(),
                                                                  xyz[2].data_ptr(), qr.data_ptr(), qi.data_ptr(),
-                                                                 kv.data_ptr(), numX, start=s, end=e, grid=grid or sms * 2,
+                                                                 kv.data_ptr(), numX, start=s, end=e, grid=grid or sms * 4,
                                                                  block=block)
     t_g, t_m = t_of([tz4()], 10), t_of([mq()], 3)
     t_f = t_of([ops.mix(mq(), tz4(), cd_threads=704, grid=sms)], 3)

@@ -74,7 +74,8 @@ int tk_sm_count(int* sm_count);
 /* tuning / numerics switches (name -> integer):
  *   "tzgemm_bn"      0 = choose per shape, 128 or 256 = force the super-tile width
  *   "cp_exact"       1 = IEEE 1/sqrt as the reference computes it (default 0: hardware rsqrt)
- *   "cp_ppt"         points per thread and work item: 8 (reference granularity), 4 or 2
+ *   "cp_ppt"         solo Coulomb kernel: points per thread and work item, 8 (reference granularity), 4
+ *                    (default) or 2; "mix_cp_ppt" the same for the fused kernel (default 8)
  *   "mriq_accurate"  1 = cosf/sinf as the reference calls them (default 0: reduced argument +
  *                    hardware sin/cos)
  */

@@ -213,6 +213,14 @@ struct CpArgs {
 
 constexpr int kCpChunk = 64;  // atoms per `+=` into the lattice (reference MAXATOMS, src/header/cp_header.h:5)
 
+// one MUFU.RSQ: the squared distance is a sum of squares of finite coordinates, never a denormal that would
+// need the slower, range-checked sequence `rsqrtf` expands to
+__device__ __forceinline__ float cp_rsqrt(float x) {
+    float y;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int PPT, bool EXACT>
 __device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int nthreads, const int cta,
                                         const int ncta) {
@@ -236,12 +244,17 @@ __device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int
         const float yf = static_cast<float>(yi), xf = static_cast<float>(xi);
         float* out = a.lattice + static_cast<size_t>(pitch) * yi + xi + 16 * PPT * part;
 
+        // running potential of this thread's points: starts from what the lattice holds and gets one
+        // rounded addition per 64-atom chunk, exactly the sequence of `+=` the reference's launches make
+        float acc[PPT];
+#pragma unroll
+        for (int u = 0; u < PPT; ++u) acc[u] = out[16 * u];
         for (int a0 = 0; a0 < a.numatoms; a0 += kCpChunk) {
             const int a1 = min(a0 + kCpChunk, a.numatoms);
             float e[PPT];
 #pragma unroll
             for (int u = 0; u < PPT; ++u) e[u] = 0.0f;
-#pragma unroll 2
+#pragma unroll 4
             for (int i = a0; i < a1; ++i) {
                 const float4 at = __ldg(a.atoms + i);
                 // spacing * index - coordinate as the single fma nvcc makes of the reference's expression
@@ -255,14 +268,16 @@ __device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int
                     const float r2 = __fmaf_rn(dx, dx, dyz2);
                     float inv;
                     if (EXACT) inv = __fdiv_rn(1.0f, __fsqrt_rn(r2));
-                    else inv = rsqrtf(r2);
+                    else inv = cp_rsqrt(r2);
                     e[u] = __fmaf_rn(at.w, inv, e[u]);
                     dx = __fadd_rn(dx, spacing_u);
                 }
             }
 #pragma unroll
-            for (int u = 0; u < PPT; ++u) out[16 * u] += e[u];
+            for (int u = 0; u < PPT; ++u) acc[u] = __fadd_rn(acc[u], e[u]);
         }
+#pragma unroll
+        for (int u = 0; u < PPT; ++u) out[16 * u] = acc[u];
     }
 }
 

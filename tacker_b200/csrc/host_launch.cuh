@@ -33,7 +33,8 @@ static int cuda_fail(cudaError_t e, const char* what) {
 struct Options {
     int tzgemm_bn = 0;
     int cp_exact = 0;
-    int cp_ppt = 8;
+    int cp_ppt = 4;      // solo kernel: points per thread and work item (8 = the reference's granularity)
+    int mix_cp_ppt = 8;  // fused kernel
     int mriq_accurate = 0;
     int stencil_prefetch = 0;   // register role: L2 prefetch distance in planes (0 or 8)
     int stencil_tma = 1;        // 1 = TMA-fed role whenever the shape allows, 0 = always the register role
@@ -455,11 +456,11 @@ static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsign
         case CD_STENCIL:
             return TK_ERR_ARGS;  // handled by run_mix_stencil
         case CD_CP: {
-            if (g_opt.cp_ppt == 2) {
+            if (g_opt.mix_cp_ppt == 2) {
                 auto k = mix_cp_kernel<BN, STAGES, 2>;
                 if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
                 k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
-            } else if (g_opt.cp_ppt == 4) {
+            } else if (g_opt.mix_cp_ppt == 4) {
                 auto k = mix_cp_kernel<BN, STAGES, 4>;
                 if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
                 k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);

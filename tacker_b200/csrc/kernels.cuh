@@ -54,12 +54,12 @@ stencil_tma_kernel(const __grid_constant__ CUtensorMap tmap_grid, const StencilA
 }
 
 template <int PPT, bool EXACT>
-__global__ void __launch_bounds__(512) cp_kernel(const CpArgs a) {
+__global__ void __launch_bounds__(512, 1) cp_kernel(const CpArgs a) {
     cp_role<PPT, EXACT>(a, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
 }
 
 template <bool ACCURATE>
-__global__ void __launch_bounds__(512) mriq_kernel(const MriqArgs m) {
+__global__ void __launch_bounds__(512, 1) mriq_kernel(const MriqArgs m) {
     mriq_role<ACCURATE>(m, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
 }
 

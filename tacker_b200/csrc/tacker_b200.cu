@@ -42,6 +42,7 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "tzgemm_bn")) return &g_opt.tzgemm_bn;
     if (!std::strcmp(name, "cp_exact")) return &g_opt.cp_exact;
     if (!std::strcmp(name, "cp_ppt")) return &g_opt.cp_ppt;
+    if (!std::strcmp(name, "mix_cp_ppt")) return &g_opt.mix_cp_ppt;
     if (!std::strcmp(name, "mriq_accurate")) return &g_opt.mriq_accurate;
     if (!std::strcmp(name, "stencil_prefetch")) return &g_opt.stencil_prefetch;
     if (!std::strcmp(name, "stencil_tma")) return &g_opt.stencil_tma;
@@ -56,7 +57,7 @@ TK_API int tk_set_option(const char* name, int value) {
     int* slot = option_slot(name);
     if (!slot) return TK_ERR_UNKNOWN_KEY;
     if (slot == &g_opt.tzgemm_bn && value != 0 && value != 128 && value != 256) return TK_ERR_ARGS;
-    if (slot == &g_opt.cp_ppt && value != 8 && value != 4 && value != 2) return TK_ERR_ARGS;
+    if ((slot == &g_opt.cp_ppt || slot == &g_opt.mix_cp_ppt) && value != 8 && value != 4 && value != 2) return TK_ERR_ARGS;
     if (slot == &g_opt.stencil_prefetch && value != 0 && value != 8) return TK_ERR_ARGS;
     if ((slot == &g_opt.stencil_ring || slot == &g_opt.mix_stencil_ring) && (value < kStMinRing || value > kStMaxRing))
         return TK_ERR_ARGS;
@@ -191,7 +192,7 @@ TK_API int tk_launch_ori_cp(void** params, int nparams, const unsigned grid[3], 
     if ((rc = parse_cp(p, 10, 12, &a)) != TK_OK) return rc;
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
-    return run_cp(a, static_cast<unsigned>(d->sm_count), 256, static_cast<cudaStream_t>(stream));
+    return run_cp(a, static_cast<unsigned>(d->sm_count) * 2u, 256, static_cast<cudaStream_t>(stream));
 }
 
 TK_API int tk_launch_ori_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
@@ -208,7 +209,7 @@ TK_API int tk_launch_ori_mriq(void** params, int nparams, const unsigned grid[3]
     if ((rc = parse_mriq(p, 14, 16, &m)) != TK_OK) return rc;
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
-    return run_mriq(m, static_cast<unsigned>(d->sm_count), 256, static_cast<cudaStream_t>(stream));
+    return run_mriq(m, static_cast<unsigned>(d->sm_count) * 4u, 256, static_cast<cudaStream_t>(stream));
 }
 
 // ---- preparation ----
@@ -408,7 +409,7 @@ TK_API int tk_mriq_compute(const float* kx, const float* ky, const float* kz, co
     if (!x || !y || !z || !Qr || !Qi) return TK_ERR_ARGS;
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
-    return run_mriq(m, static_cast<unsigned>(d->sm_count), 256, static_cast<cudaStream_t>(stream));
+    return run_mriq(m, static_cast<unsigned>(d->sm_count) * 4u, 256, static_cast<cudaStream_t>(stream));
 }
 
 TK_API int tk_coulomb_compute(const float* atoms_xyzq, int numatoms, float zplane, float gridspacing, float* energygrid,
@@ -429,7 +430,7 @@ TK_API int tk_coulomb_compute(const float* atoms_xyzq, int numatoms, float zplan
     a.end = a.gx * a.gy;
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
-    return run_cp(a, static_cast<unsigned>(d->sm_count), 256, static_cast<cudaStream_t>(stream));
+    return run_cp(a, static_cast<unsigned>(d->sm_count) * 2u, 256, static_cast<cudaStream_t>(stream));
 }
 
 // =================================================================================================

@@ -260,13 +260,13 @@ def gptb_stencil(c0, c1, A0, Anext, nx, ny, nz, start=0, end=None, grid=None, bl
 def gptb_cp(numatoms, spacing, energygrid, atoms, nx, ny, start=0, end=None, grid=None, block=256) -> GPTBKernel:
     ori = OriCPKernel(numatoms, spacing, energygrid, atoms, nx, ny)
     total = ori.launchGridDim[0] * ori.launchGridDim[1]
-    return GPTBKernel("cp", "gptb_cp", ori, (grid or sm_count(), 1, 1), (block, 1, 1), start,
+    return GPTBKernel("cp", "gptb_cp", ori, (grid or sm_count() * 2, 1, 1), (block, 1, 1), start,
                       total if end is None else end)
 
 
 def gptb_mriq(numK, x, y, z, Qr, Qi, kvals, numX, start=0, end=None, grid=None, block=256) -> GPTBKernel:
     ori = OriMRIQKernel(numK, x, y, z, Qr, Qi, kvals, numX)
-    return GPTBKernel("mriq", "gptb_mriq", ori, (grid or sm_count(), 1, 1), (block, 1, 1), start,
+    return GPTBKernel("mriq", "gptb_mriq", ori, (grid or sm_count() * 4, 1, 1), (block, 1, 1), start,
                       ori.launchGridDim[0] if end is None else end)
 
 
