@@ -45,9 +45,10 @@ METRIC = "fused GEMM+stencil pairs per second (fused vs sequential kernel time i
 SWEEP_BYTES = 8 * NX * NY * NZ
 GEMM_BYTES = 2 * (M * K + N * K) + 4 * M * N
 LAUNCH_BYTES = SWEEP_BYTES + GEMM_BYTES / SWEEPS
-# dram__bytes_read.sum + dram__bytes_write.sum of one fused launch, from the ncu capture
-# summarised in profiles/mix_stencil_config2_ncu.md (None until a capture exists)
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
+# profiles/stencil_tma_kernel_config2_ncu.md and profiles/mix_stencil_kernel_config2_ncu.md (caches flushed
+# by ncu before the launch; part of the output is still dirty in L2 when the kernel ends)
+NCU_TRAFFIC_BYTES = {"stencil_tma_kernel": 94.05e6, "mix_stencil_kernel": 108.3e6}
 
 
 def measured_peaks():
