@@ -256,6 +256,18 @@ int tk_merge_heads_f32(const float* ctx, int B, int S, int heads, int dh, float*
 int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int N, int K, int batch, long long stride_a,
                       long long stride_b, long long stride_c, float alpha, void* stream);
 
+/* ---- work-distribution plans (host only, no device needed) -------------------------------------------------
+ * The enumeration code of the persistent kernels, run on the host so that its invariants can be checked
+ * exhaustively (the reference relies on compute-sanitizer-free trial runs of generated binaries,
+ * fusion/code/gen_run.py:164-196).
+ * tk_plan_tzgemm: cover[t] += 1 for every 64x64 tile t of the M x N result that a launch of `ctas` CTAs with
+ *   super-tile width bn writes for [start, end); work[c] (optional) += super-tiles of CTA c.
+ * tk_plan_stencil: planes[b*nz + k] += 1 for every plane k of bundle b some warp computes, loads[b*nz + k]
+ *   (optional) += 1 for every plane streamed; split = {slabs per bundle, planes per slab} chosen for the launch. */
+int tk_plan_tzgemm(int M, int N, int bn, int start, int end, int ctas, int* cover, int* work);
+int tk_plan_stencil(int nz, int blocks_start, int blocks_end, int gx, int gy, int ctas, int warps_per_cta,
+                    int* planes, int* loads, int split[2]);
+
 /* ---- MRI-Q for callers that cannot allocate device memory ----------------------------------------------
  * (No counterpart in the reference: it always cudaMallocs its buffers up front.)
  * Same computation and same results as tk_mriq_compute, but the packed k-space table is a fixed array

@@ -61,7 +61,7 @@ struct SuperTileWalk {
     int per;    // candidates per batch entry
     int start, end, mt;
 
-    __device__ __forceinline__ void init(const GemmArgs& g) {
+    __host__ __device__ __forceinline__ void init(const GemmArgs& g) {
         nt = g.N / 64;
         mt = g.M / 64;
         sc = (g.N + BN - 1) / BN;
@@ -80,7 +80,7 @@ struct SuperTileWalk {
     }
 
     // bit (h * (BN/64) + cb) set <=> sub-tile (64-row half h, 64-column block cb) is in range
-    __device__ __forceinline__ uint32_t mask(int cand, int& R, int& Cc, int& b) const {
+    __host__ __device__ __forceinline__ uint32_t mask(int cand, int& R, int& Cc, int& b) const {
         b = cand / per;
         cand -= b * per;
         R = r0 + cand / sc;

@@ -61,7 +61,7 @@ struct StencilPlaneCursor {
     int item, q, n;      // current item, plane index inside it, planes in it (0 = stream exhausted)
     int x0, j0, kbase;   // tile origin of the item: columns x0.., rows j0.., plane kbase = k0 - 1
 
-    __device__ __forceinline__ void seek(const StencilArgs& s, int it, int nitems) {
+    __host__ __device__ __forceinline__ void seek(const StencilArgs& s, int it, int nitems) {
         item = it;
         q = 0;
         n = 0;
@@ -69,7 +69,7 @@ struct StencilPlaneCursor {
             const int p = s.start + item / s.slabs;
             const int slab = item % s.slabs;
             const int k0 = 1 + slab * s.per;
-            const int k1 = min(k0 + s.per, s.nz - 1);
+            const int k1 = (k0 + s.per < s.nz - 1) ? k0 + s.per : s.nz - 1;
             if (k0 < k1) {
                 n = k1 - k0 + 2;
                 x0 = (p % s.gx) * 64;
@@ -80,7 +80,7 @@ struct StencilPlaneCursor {
             item += stride;
         }
     }
-    __device__ __forceinline__ void advance(const StencilArgs& s, int nitems) {
+    __host__ __device__ __forceinline__ void advance(const StencilArgs& s, int nitems) {
         if (++q == n) seek(s, item + stride, nitems);
     }
     int stride;

@@ -841,3 +841,76 @@ TK_API int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int 
     if (rc != TK_OK) return rc;
     return run_tzgemm(c, static_cast<unsigned>(d->sm_count), static_cast<cudaStream_t>(stream));
 }
+
+// =================================================================================================
+// work-distribution plans, evaluated on the host (no device needed): the same enumeration code the
+// kernels run, exposed so that its invariants can be checked exhaustively
+// =================================================================================================
+// cover[t] += 1 for every 64x64 tile t that some CTA of a `ctas`-CTA launch would write for the range
+// [start, end); a correct plan has cover == 1 inside the range and 0 outside.  work[c] = super-tiles of CTA c.
+TK_API int tk_plan_tzgemm(int M, int N, int bn, int start, int end, int ctas, int* cover, int* work) {
+    if (!cover || M < 128 || N < 64 || M % 128 || N % 64 || ctas < 1 || (bn != 128 && bn != 256)) return TK_ERR_ARGS;
+    GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.M = M;
+    g.N = N;
+    g.K = 64;
+    g.start = start;
+    g.end = end;
+    g.batch = 1;
+    const int nt = N / 64;
+    auto plan = [&](auto walk) {
+        walk.init(g);
+        const int per_row = bn / 64;
+        for (int cta = 0; cta < ctas; ++cta)
+            for (int cand = cta; cand < walk.ncand; cand += ctas) {
+                int R, Cc, b;
+                const uint32_t m = walk.mask(cand, R, Cc, b);
+                if (m == 0u) continue;
+                if (work) work[cta] += 1;
+                for (int h = 0; h < 2; ++h)
+                    for (int cb = 0; cb < per_row; ++cb)
+                        if ((m >> (h * per_row + cb)) & 1u) cover[(2 * R + h) * nt + Cc * per_row + cb] += 1;
+            }
+    };
+    if (bn == 256) plan(SuperTileWalk<256>());
+    else plan(SuperTileWalk<128>());
+    return TK_OK;
+}
+
+// planes[b * nz + k] += 1 for every (bundle b of [start, end), plane k) that some warp computes, and
+// loads[...] += 1 for every plane a warp streams through its ring (computed planes plus the two halo planes of
+// each item); `groups` = warps (TMA role) of the whole launch.  Returns the chosen split in split[2].
+TK_API int tk_plan_stencil(int nz, int blocks_start, int blocks_end, int gx, int gy, int ctas, int warps_per_cta,
+                           int* planes, int* loads, int split[2]) {
+    if (!planes || nz < 1 || gx < 1 || gy < 1 || ctas < 1 || warps_per_cta < 1 || blocks_start < 0) return TK_ERR_ARGS;
+    StencilArgs s;
+    std::memset(&s, 0, sizeof(s));
+    s.nz = nz;
+    s.gx = gx;
+    s.gy = gy;
+    s.start = blocks_start;
+    s.end = blocks_end > gx * gy ? gx * gy : blocks_end;
+    if (s.start >= s.end) return TK_OK;
+    stencil_pick_split(nz, s.end - s.start, static_cast<long long>(ctas) * warps_per_cta, &s.slabs, &s.per);
+    if (split) {
+        split[0] = s.slabs;
+        split[1] = s.per;
+    }
+    if (nz < 3) return TK_OK;
+    const int nitems = (s.end - s.start) * s.slabs;
+    for (int cta = 0; cta < ctas; ++cta)
+        for (int w = 0; w < warps_per_cta; ++w) {
+            StencilPlaneCursor c;
+            c.stride = ctas * warps_per_cta;
+            c.seek(s, w * ctas + cta, nitems);
+            while (c.n != 0) {
+                const int bundle = s.start + c.item / s.slabs;
+                const int k = c.kbase + c.q;
+                if (loads) loads[bundle * nz + k] += 1;
+                if (c.q >= 1 && c.q <= c.n - 2) planes[bundle * nz + k] += 1;
+                c.advance(s, nitems);
+            }
+        }
+    return TK_OK;
+}
