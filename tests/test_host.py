@@ -12,7 +12,7 @@ def test_host_selftest_passes():
     from tacker_b200 import _build
 
     exe = _build.build_host_selftest()
-    out = subprocess.run([exe, os.path.join(HOST, "config")], capture_output=True, text=True, timeout=120)
+    out = subprocess.run([exe, os.path.join(HOST, "tests", "config")], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "0 failed" in out.stdout
 
