@@ -32,7 +32,7 @@ sys.path.insert(0, ROOT)
 M, N, K = 4096, 4096, 1024
 NX, NY, NZ, SWEEPS = 512, 512, 64, 10
 C0, C1 = 1.0 / 6.0, -1.0 / 6.0
-CD_THREADS = 512        # CUDA-core threads of the fused CTA (16 warps next to the 6 tensor-role warps)
+CD_THREADS = 448        # CUDA-core threads of the fused CTA (14 warps next to the 6 tensor-role warps)
 SOLO_CD_THREADS = 256   # solo stencil: 2 CTAs of 8 warps per SM
 TILES = (M // 64) * (N // 64)
 CD_BLOCKS = (NX // 64) * (NY // 4)
@@ -476,10 +476,10 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
                                                                  kv.data_ptr(), numX, start=s, end=e, grid=grid or sms * 4,
                                                                  block=block)
     t_g, t_m = t_of([tz4()], 10), t_of([mq()], 3)
-    t_f = t_of([ops.mix(mq(), tz4(), cd_threads=704, grid=sms)], 3)
+    t_f = t_of([ops.mix(mq(), tz4(), cd_threads=576, grid=sms)], 3)
     nb = max(148, int(round(1024 * t_g / t_m)))
     t_mb = t_of([mq(0, nb)], 5)
-    t_fb = t_of([ops.mix(mq(0, nb), tz4(), cd_threads=704, grid=sms)], 5)
+    t_fb = t_of([ops.mix(mq(0, nb), tz4(), cd_threads=576, grid=sms)], 5)
     out["config4_gemm4096x2048_mriq"] = {
         "gemm_us": round(t_g, 1), "mriq_us": round(t_m, 1), "fused_us": round(t_f, 1),
         "fused_vs_sequential": round(t_f / (t_g + t_m), 4), "mriq_gpairs_per_s": round(numK * numX / t_m / 1e3, 1),

@@ -9,8 +9,9 @@
 //   warp 0      TMA producer : A 128x64 and B BNx64 fp16 tiles, 128-byte swizzle, STAGES deep
 //   warp 1      MMA issuer   : one thread issues tcgen05.mma 128xBNx16, accumulators in TMEM,
 //                              two accumulator buffers so tile i+1 starts while tile i drains
-//   warps 2..5  epilogue     : tcgen05.ld -> scale by alpha -> 128-bit global stores, masked per
-//                              64x64 sub-tile so that exactly the tiles in [start, end) are written
+//   warps 2..5  epilogue     : tcgen05.ld -> scale by alpha -> transpose through shared memory -> 128-bit
+//                              global stores of whole rows, masked per 64x64 sub-tile so that exactly the
+//                              tiles in [start, end) are written
 //
 // The six warps synchronise among themselves on named barrier 1 only, so other warps of the
 // same CTA (the CUDA-core role of a fused kernel) are never involved.
@@ -38,7 +39,9 @@ struct GemmArgs {
     int l2_hints;        // 1: operand tiles are loaded with the evict-last L2 priority
 };
 
-template <int BN, int STAGES>
+// STAGED = the epilogue transposes through shared memory (coalesced row stores, 18 KB); the unstaged form writes
+// 16 bytes per lane and row straight from registers and leaves that memory to a co-running role.
+template <int BN, int STAGES, bool STAGED = true>
 struct GemmSmem {
     static constexpr int kABytes = kGemmBM * kGemmBK * 2;
     static constexpr int kBBytes = BN * kGemmBK * 2;
@@ -47,8 +50,13 @@ struct GemmSmem {
     static constexpr int kNumBars = 2 * STAGES + 4;
     static constexpr int kTmemSlotOffset = kBarOffset + kNumBars * 8;
     static constexpr int kAbortOffset = kTmemSlotOffset + 4;
+    // epilogue staging: each of the four epilogue warps transposes its 32 x 32 chunk here so that its global
+    // stores cover whole rows (pitch 36 floats keeps both the row-wise writes and the 4-row reads conflict free)
+    static constexpr int kEpiPitch = 36;
+    static constexpr int kEpiWarpBytes = 32 * kEpiPitch * 4;
+    static constexpr int kEpiOffset = ((kAbortOffset + 4 + 127) / 128) * 128;
     // rounded so that whatever follows (a CUDA-core role's scratch) starts 128-byte aligned
-    static constexpr int kBytes = ((kAbortOffset + 4 + 127) / 128) * 128;
+    static constexpr int kBytes = kEpiOffset + (STAGED ? 4 * kEpiWarpBytes : 0);
 };
 
 // Enumeration of the super-tiles that intersect [start, end); identical in every role.
@@ -102,11 +110,11 @@ struct SuperTileWalk {
 };
 
 // `warp` is the warp index inside the role (0..5); all 192 threads of the role must call this.
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool STAGED = true>
 __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a,
                                           const CUtensorMap* __restrict__ tmap_b, const GemmArgs g,
                                           uint8_t* smem, const int warp, const int lane) {
-    using L = GemmSmem<BN, STAGES>;
+    using L = GemmSmem<BN, STAGES, STAGED>;
     constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers (256 or 512: powers of two)
     constexpr uint32_t kIdesc = umma_idesc_f16_f32(kGemmBM, BN);
 
@@ -237,25 +245,50 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
             ok = mbar_wait(tfull_bar(as), aphase, abort_flag, g.status, DEV_TIMEOUT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after_sync();
-            const int row = R * kGemmBM + q * 32 + lane;
-            float* crow = g.C + static_cast<size_t>(b) * g.stride_c + static_cast<size_t>(row) * g.N +
-                          static_cast<size_t>(Cc) * BN;
+            // this warp's 32 rows of the super-tile; lane `lane` holds row (row0 + lane) after the TMEM load and
+            // writes rows row0 + 4i + lane/8, columns 4 (lane % 8) .. +3 after the transpose
+            const int row0 = R * kGemmBM + q * 32;
+            float* cbase = g.C + static_cast<size_t>(b) * g.stride_c + static_cast<size_t>(row0) * g.N +
+                           static_cast<size_t>(Cc) * BN;
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * BN;
+            float* stage = reinterpret_cast<float*>(smem + L::kEpiOffset) + (warp - 2) * (32 * L::kEpiPitch);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 if (((m >> (h * (BN / 64) + (c >> 1))) & 1u) == 0u) continue;  // warp-uniform
                 uint32_t r[32];
                 tmem_ld_32x32(t_lane + c * 32, r);
                 tmem_ld_wait();
-                float4* dst = reinterpret_cast<float4*>(crow + c * 32);
+                if (STAGED) {
+                    float4* srow = reinterpret_cast<float4*>(stage + lane * L::kEpiPitch);
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    float4 o;
-                    o.x = g.alpha * __uint_as_float(r[4 * v + 0]);
-                    o.y = g.alpha * __uint_as_float(r[4 * v + 1]);
-                    o.z = g.alpha * __uint_as_float(r[4 * v + 2]);
-                    o.w = g.alpha * __uint_as_float(r[4 * v + 3]);
-                    dst[v] = o;
+                    for (int v = 0; v < 8; ++v) {
+                        float4 o;
+                        o.x = g.alpha * __uint_as_float(r[4 * v + 0]);
+                        o.y = g.alpha * __uint_as_float(r[4 * v + 1]);
+                        o.z = g.alpha * __uint_as_float(r[4 * v + 2]);
+                        o.w = g.alpha * __uint_as_float(r[4 * v + 3]);
+                        srow[v] = o;
+                    }
+                    __syncwarp();
+                    float* cchunk = cbase + c * 32 + (lane & 7) * 4;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = 4 * i + (lane >> 3);
+                        const float4 o = *reinterpret_cast<const float4*>(stage + rr * L::kEpiPitch + (lane & 7) * 4);
+                        *reinterpret_cast<float4*>(cchunk + static_cast<size_t>(rr) * g.N) = o;
+                    }
+                    __syncwarp();
+                } else {
+                    float4* dst = reinterpret_cast<float4*>(cbase + static_cast<size_t>(lane) * g.N + c * 32);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        float4 o;
+                        o.x = g.alpha * __uint_as_float(r[4 * v + 0]);
+                        o.y = g.alpha * __uint_as_float(r[4 * v + 1]);
+                        o.z = g.alpha * __uint_as_float(r[4 * v + 2]);
+                        o.w = g.alpha * __uint_as_float(r[4 * v + 3]);
+                        dst[v] = o;
+                    }
                 }
             }
             tc_fence_before_sync();

@@ -399,21 +399,26 @@ struct CdCall {
 // The stencil's rings share the CTA's shared memory with the tensor role's stages, so the fused stencil
 // kernel exists in several (super-tile width, stage count) shapes: a launch whose GEMM share is small gives
 // most of the shared memory to the rings, a GEMM-heavy launch keeps a deep operand pipeline.
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool STAGED>
 static int launch_mix_stencil(const GemmCall& c, StencilArgs s, unsigned ctas, unsigned threads, cudaStream_t st) {
-    constexpr int kGemmBytes = GemmSmem<BN, STAGES>::kBytes + 1024;
-    auto k = mix_stencil_kernel<BN, STAGES>;
+    constexpr int kGemmBytes = GemmSmem<BN, STAGES, STAGED>::kBytes + 1024;
+    auto k = mix_stencil_kernel<BN, STAGES, STAGED>;
     CUtensorMap ta, tb, tg;
     std::memset(&tg, 0, sizeof(tg));
     int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
     if (rc != TK_OK) return rc;
     if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN)) != TK_OK) return rc;
-    const int nwarps = static_cast<int>((threads - kGemmThreads) / 32);
+    int nwarps = static_cast<int>((threads - kGemmThreads) / 32);
     int ring = 0, smem = kGemmBytes;
     if (stencil_tma_ok(s)) {
-        ring = g_opt.mix_stencil_ring;
-        while (ring >= kStMinRing && kGemmBytes + nwarps * stencil_tma_warp_bytes(ring) > kMaxDynSmem) --ring;
-        if (ring < kStMinRing) ring = 0;
+        // as many of the requested warps as get at least the minimum ring next to the GEMM's stages
+        const int fit = (kMaxDynSmem - kGemmBytes) / stencil_tma_warp_bytes(kStMinRing);
+        if (fit >= 1) {
+            if (nwarps > fit) nwarps = fit;
+            ring = g_opt.mix_stencil_ring;
+            while (ring > kStMinRing && kGemmBytes + nwarps * stencil_tma_warp_bytes(ring) > kMaxDynSmem) --ring;
+            threads = kGemmThreads + 32u * static_cast<unsigned>(nwarps);
+        }
     }
     if (ring > 0) {
         if ((rc = make_tmap_grid(&tg, s.A0, s.nx, s.ny, s.nz)) != TK_OK) return rc;
@@ -432,14 +437,19 @@ static int launch_mix_stencil(const GemmCall& c, StencilArgs s, unsigned ctas, u
 
 static int run_mix_stencil(const GemmCall& c, const StencilArgs& s, unsigned ctas, unsigned threads, cudaStream_t st) {
     int cfg = g_opt.mix_stencil_cfg;
-    // Measured on B200 (config 2, 8 to 22 CUDA-core warps, 64 to 4096 GEMM tiles): the 128-wide super-tile with
-    // 4 stages is the best or within 2% of the best everywhere -- it leaves ~100 KB to the stencil's rings.
-    if (cfg == 0) cfg = 2;
+    if (cfg == 0) {
+        // Measured on B200 (config 2; 8 to 18 stencil warps; 64 to 4096 GEMM tiles): the 128-wide super-tile with
+        // 4 stages is best up to about one GEMM-time of stencil work per launch -- it leaves ~75 KB to the
+        // stencil's rings -- and the 256-wide one with 3 stages once the GEMM dominates the launch.
+        const double t_gemm = 2.0 * 4096.0 * (c.g.end - c.g.start) * c.g.K / 1.0e15;
+        const double t_cd = 8.0 * 256.0 * (s.end - s.start) * (s.nz > 2 ? s.nz - 2 : 1) / 5.0e12;
+        cfg = (t_gemm > 1.2 * t_cd && c.g.N % 256 == 0) ? 1 : 2;
+    }
     switch (cfg) {
-        case 1: return launch_mix_stencil<256, 3>(c, s, ctas, threads, st);
-        case 2: return launch_mix_stencil<128, 4>(c, s, ctas, threads, st);
-        case 3: return launch_mix_stencil<128, 3>(c, s, ctas, threads, st);
-        default: return launch_mix_stencil<128, 2>(c, s, ctas, threads, st);
+        case 1: return launch_mix_stencil<256, 3, true>(c, s, ctas, threads, st);
+        case 2: return launch_mix_stencil<128, 4, true>(c, s, ctas, threads, st);
+        case 3: return launch_mix_stencil<128, 3, true>(c, s, ctas, threads, st);
+        default: return launch_mix_stencil<128, 2, true>(c, s, ctas, threads, st);
     }
 }
 

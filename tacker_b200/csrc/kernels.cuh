@@ -19,7 +19,7 @@ __device__ unsigned g_dev_status;
 // -------------------------------------------------------------------------------------------------
 // kernels
 // -------------------------------------------------------------------------------------------------
-constexpr int kMaxMixThreads = 896;  // 192 tensor-role threads + up to 704 CUDA-core threads (<= 73 registers each)
+constexpr int kMaxMixThreads = 768;  // 192 tensor-role threads + up to 576 CUDA-core threads (<= 85 registers each)
 
 __device__ __forceinline__ uint8_t* align_smem_1024(uint8_t* p) {
     const uint32_t a = smem_u32(p);
@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(512, 1) mriq_kernel(const MriqArgs m) {
 // same way, src/mix_kernel/tzgemm_stencil.cu:284-298).
 // ring > 0: the stencil warps use the TMA-fed role with their rings placed behind the tensor role's
 // shared memory; ring == 0: the register role (shapes TMA cannot describe).
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool STAGED>
 __global__ void __launch_bounds__(kMaxMixThreads, 1)
 mix_stencil_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                    const GemmArgs g, const __grid_constant__ CUtensorMap tmap_grid, const StencilArgs s,
@@ -77,9 +77,9 @@ mix_stencil_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const int warp = threadIdx.x >> 5;
     uint8_t* smem = align_smem_1024(smem_raw);
     if (warp < kGemmWarps) {
-        gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31);
+        gemm_role<BN, STAGES, STAGED>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31);
     } else if (ring > 0) {
-        stencil_role_tma(&tmap_grid, s, smem + GemmSmem<BN, STAGES>::kBytes, ring, warp - kGemmWarps,
+        stencil_role_tma(&tmap_grid, s, smem + GemmSmem<BN, STAGES, STAGED>::kBytes, ring, warp - kGemmWarps,
                          (blockDim.x >> 5) - kGemmWarps, threadIdx.x & 31, blockIdx.x, gridDim.x, g.status);
     } else {
         stencil_role<0>(s, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);

@@ -374,7 +374,7 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
     info->threads_cd_default = 256;
     if (k == "tzgemm_stencil") {
         info->threads_cd_min = 32;
-        return fill_info(mix_stencil_kernel<256, 3>, kGemmThreads + 256, gsm, info);
+        return fill_info(mix_stencil_kernel<128, 4, true>, kGemmThreads + 256, gsm, info);
     }
     if (k == "tzgemm_cp") {
         info->threads_cd_min = 32;

@@ -46,7 +46,9 @@ class GemmConfig:
     @property
     def smem(self) -> int:
         stage = 128 * 64 * 2 + self.bn * 64 * 2
-        return self.stages * stage + (2 * self.stages + 4) * 8 + 8 + 1024 + 128
+        pipeline = self.stages * stage + (2 * self.stages + 4) * 8 + 8
+        staging = 4 * 32 * 36 * 4            # epilogue transpose buffers of the four epilogue warps
+        return (pipeline + 127) // 128 * 128 + staging + 1024
 
     @property
     def tmem(self) -> int:

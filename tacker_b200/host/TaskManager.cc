@@ -221,9 +221,26 @@ ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pa
         t += -std::log(1.0 - static_cast<double>(tk_unit_draw(seed, i))) / qps * 1e3;
         arrivals.push_back(t);
     }
-    // One phase: serve every arrival in order; when idle, run the best-effort task one kernel at a time
-    // (or just wait, in the solo phase).  A query's latency runs from its arrival to the end of its last kernel,
-    // so queueing behind an earlier query or behind a best-effort kernel in flight is part of it.
+    // Per-kernel times of the best-effort task (one profiled pass): the idle loop uses them to enqueue the
+    // longest run of kernels that is predicted to fit into `be_chunk_ms` before it looks at the clock again.
+    // The chunk bounds how long an arriving query can be held up by best-effort work in flight.
+    std::vector<float> be_ms(be_task->kernels.size(), 0.0f);
+    {
+        void* e0 = be.eventCreate();
+        void* e1 = be.eventCreate();
+        be_task->initExecution();
+        for (size_t k = 0; k < be_task->kernels.size(); ++k) {
+            be.eventRecord(e0, stream);
+            be_task->kernels[k]->execute(stream);
+            be.eventRecord(e1, stream);
+            be_ms[k] = be.eventElapsedMs(e0, e1);
+        }
+        be.eventDestroy(e0);
+        be.eventDestroy(e1);
+    }
+    // One phase: serve every arrival in order; when idle, run a chunk of the best-effort task (or just wait,
+    // in the solo phase).  A query's latency runs from its arrival to the end of its last kernel, so queueing
+    // behind an earlier query or behind best-effort kernels in flight is part of it.
     size_t be_pos = 0;
     auto phase = [&](Task* be_or_null, std::vector<double>& lat, long long* be_queries) {
         size_t next = 0;
@@ -241,13 +258,17 @@ ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pa
                 continue;
             }
             if (!be_or_null) continue;
-            be_or_null->kernels[be_pos]->execute(stream);
+            float budget = static_cast<float>(be_chunk_ms);
+            do {
+                be_or_null->kernels[be_pos]->execute(stream);
+                budget -= be_ms[be_pos];
+                if (++be_pos == be_or_null->kernels.size()) {
+                    be_pos = 0;
+                    *be_queries += be_queries_per_pass;
+                    be_or_null->initExecution();
+                }
+            } while (budget > be_ms[be_pos]);
             be.streamSync(stream);
-            if (++be_pos == be_or_null->kernels.size()) {
-                be_pos = 0;
-                *be_queries += be_queries_per_pass;
-                be_or_null->initExecution();
-            }
         }
         return (now_ms() - start) / 1e3;
     };

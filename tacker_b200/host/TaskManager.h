@@ -56,6 +56,7 @@ public:
     float qos_budget_ms = 50.0f;  // src/TaskManager.cu:571
     float qos_guard_ms = 4.0f;    // src/TaskManager.cu:586
     int profile_passes = 10, schedule_passes = 5, warmup_passes = 5;
+    double be_chunk_ms = 0.15;  // best-effort work enqueued at once while idle (bounds the extra LC wait)
 
 private:
     float blockRatio(const std::string& pair, int k_global);

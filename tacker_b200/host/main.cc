@@ -1,6 +1,6 @@
 // aker -- command line of the runtime (reference: src/main.cu:246-336).
 //   aker -s <aker|tacker> -m <vgg16|resnet50|bert> [-d device] [-c config_dir]
-//        [--colocate seconds] [--qps rate] [--qos factor] [--be model]
+//        [--colocate seconds] [--qps rate] [--qos factor] [--be model] [--be-chunk-ms ms]
 // Without --colocate it runs the reference's experiment (both modes unless -s picks one); with it, the
 // request-driven co-location of `-m` (latency-critical) with `--be` (best-effort) on this GPU.
 #include <cstdio>
@@ -30,7 +30,7 @@ static void usage(const char* argv0) {
 int main(int argc, char* argv[]) {
     std::string system_name, model, config_dir = "config", be_model = "bert";
     int device_no = 0;
-    double colocate = 0.0, qps = 200.0, qos = 1.5;
+    double colocate = 0.0, qps = 200.0, qos = 1.5, be_chunk = -1.0;
     for (int i = 1; i < argc; ++i) {
         const std::string a = argv[i];
         auto val = [&](const char* what) -> std::string {
@@ -48,6 +48,7 @@ int main(int argc, char* argv[]) {
         else if (a == "--qps") qps = std::atof(val("--qps").c_str());
         else if (a == "--qos") qos = std::atof(val("--qos").c_str());
         else if (a == "--be") be_model = val("--be");
+        else if (a == "--be-chunk-ms") be_chunk = std::atof(val("--be-chunk-ms").c_str());
         else {
             usage(argv[0]);
             return 0;
@@ -77,6 +78,7 @@ int main(int argc, char* argv[]) {
         const std::string a = sget_kernel_info("throughput_test", "a"), b = sget_kernel_info("throughput_test", "b");
         std::printf("[Result] cd1: %s, cd2: %s, dnn: %s\n", a.c_str(), b.c_str(), model.c_str());
         TaskManager taskManager(lc_task.get(), a, b);
+        if (be_chunk >= 0.0) taskManager.be_chunk_ms = be_chunk;
         if (colocate > 0.0) {
             std::unique_ptr<Task> be_task(createTask(be_model));
             const int per_pass = be_model == "bert" ? static_cast<Bert*>(be_task.get())->batch : 1;

@@ -68,7 +68,7 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
                                                end=e), 256, 448),
         "mriq": (lambda s=0, e=None: ops.gptb_mriq(2048, xyz[0].data_ptr(), xyz[1].data_ptr(), xyz[2].data_ptr(),
                                                    qr.data_ptr(), qi.data_ptr(), kv.data_ptr(), 262144, start=s,
-                                                   end=e), 1024, 704),
+                                                   end=e), 1024, 576),
     }
     out = {}
     for cd, (mk, blocks, cd_threads) in cds.items():

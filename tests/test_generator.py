@@ -18,7 +18,7 @@ def test_candidates_respect_the_sm_limits():
             assert c.name == f"tzgemm_{cd}_1_{c.r2}"
     # the stencil's rings compete with the GEMM stages for shared memory: the deepest pipeline leaves no room
     names = {(c.gemm.bn, c.gemm.stages, c.r2) for c in data.fuse_kernel_info("stencil")}
-    assert (256, 3, 12) in names and (256, 4, 24) not in names
+    assert (128, 4, 12) in names and (256, 3, 8) in names and (256, 3, 12) not in names and (256, 4, 24) not in names
 
 
 def test_emitted_source_compiles_and_exports_its_launcher(tmp_path):
