@@ -5,6 +5,7 @@
 // and the scheduling rules can be checked on a machine without a GPU.  There is no CPU compute path.
 #pragma once
 #include <cstddef>
+#include <functional>
 #include <string>
 
 #include "tacker_b200.h"
@@ -34,6 +35,12 @@ public:
     virtual void eventDestroy(void* e) = 0;
     virtual void eventRecord(void* e, stream_t s) = 0;
     virtual float eventElapsedMs(void* start, void* stop) = 0;  // waits for `stop`
+    // Records everything `body` enqueues on `s` into a CUDA graph and returns an executable handle (nullptr when
+    // the backend cannot capture: the caller then just runs `body`).  Launch-bound kernel sequences -- a whole
+    // inference of the LC task, a chunk of the BE task -- are replayed with one call instead of dozens.
+    virtual void* graphCapture(stream_t s, const std::function<void()>& body) = 0;
+    virtual void graphLaunch(void* graph, stream_t s) = 0;
+    virtual void graphDestroy(void* graph) = 0;
     // input preparation and LC-layer helpers of the library
     virtual int cpPackAtoms(const float* atoms, int count, float zplane, float* packed, stream_t s) = 0;
     virtual int mriqPackKvalues(const float* kx, const float* ky, const float* kz, const float* phiR,

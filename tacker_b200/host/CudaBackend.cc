@@ -71,6 +71,31 @@ public:
         CU(cudaEventElapsedTime(&ms, static_cast<cudaEvent_t>(a), static_cast<cudaEvent_t>(b)));
         return ms;
     }
+    void* graphCapture(stream_t s, const std::function<void()>& body) override {
+        cudaStream_t st = static_cast<cudaStream_t>(s);
+        if (st == nullptr) return nullptr;  // the legacy default stream cannot be captured
+        cudaGraph_t graph = nullptr;
+        CU(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        try {
+            body();
+        } catch (...) {
+            cudaStreamEndCapture(st, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            throw;
+        }
+        CU(cudaStreamEndCapture(st, &graph));
+        cudaGraphExec_t exec = nullptr;
+        cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) throw std::runtime_error(std::string("cudaGraphInstantiate failed: ") + cudaGetErrorString(e));
+        return exec;
+    }
+    void graphLaunch(void* graph, stream_t s) override {
+        CU(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph), static_cast<cudaStream_t>(s)));
+    }
+    void graphDestroy(void* graph) override {
+        if (graph) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph));
+    }
     int cpPackAtoms(const float* atoms, int count, float zplane, float* packed, stream_t s) override {
         return tk_cp_pack_atoms(atoms, count, zplane, packed, s);
     }

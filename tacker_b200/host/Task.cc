@@ -4,6 +4,7 @@
 #include "Recorder.h"
 
 Task::~Task() {
+    dropGraphs();
     if (evStart) backend().eventDestroy(evStart);
     if (evStop) backend().eventDestroy(evStop);
     logger.DEBUG("task name: " + taskName + ", id: " + std::to_string(taskId) + " is destroyed!");
@@ -30,4 +31,27 @@ void Task::executeTask(ExecutionMode mode, int idx, stream_t stream) {
 
 void Task::enqueue(stream_t stream) {
     for (auto& kernel : kernels) kernel->execute(stream);
+}
+
+void Task::enqueueGraph(size_t begin, size_t end, stream_t stream) {
+    for (auto& g : graphs)
+        if (g.begin == begin && g.end == end && g.stream == stream) {
+            if (g.graph) backend().graphLaunch(g.graph, stream);
+            else
+                for (size_t k = begin; k < end; ++k) kernels[k]->execute(stream);
+            return;
+        }
+    // first use: one plain pass (lazy set-up inside the library must not happen during capture), then capture
+    for (size_t k = begin; k < end; ++k) kernels[k]->execute(stream);
+    backend().streamSync(stream);
+    void* graph = backend().graphCapture(stream, [this, begin, end, stream] {
+        for (size_t k = begin; k < end; ++k) kernels[k]->execute(stream);
+    });
+    graphs.push_back(CapturedRange{begin, end, stream, graph});  // this call's work was done by the plain pass
+}
+
+void Task::dropGraphs() {
+    for (auto& g : graphs)
+        if (g.graph) backend().graphDestroy(g.graph);
+    graphs.clear();
 }

@@ -19,6 +19,11 @@ public:
     void executeTask(ExecutionMode mode, int idx, stream_t stream);
     // runs every kernel back to back without per-kernel synchronisation; returns nothing, times nothing
     void enqueue(stream_t stream);
+    // the same through CUDA graphs: kernels [begin, end) are captured once per (range, stream) and replayed
+    // afterwards; falls back to plain launches when the backend cannot capture
+    void enqueueGraph(stream_t stream) { enqueueGraph(0, kernels.size(), stream); }
+    void enqueueGraph(size_t begin, size_t end, stream_t stream);
+    void dropGraphs();
     virtual void initExecution() = 0;  // bring the task's input to the device
 
     int taskId;
@@ -31,6 +36,12 @@ public:
     int InputSize[3] = {0, 0, 0};
 
 private:
+    struct CapturedRange {
+        size_t begin, end;
+        stream_t stream;
+        void* graph;
+    };
+    std::vector<CapturedRange> graphs;
     void* evStart = nullptr;  // created once, destroyed with the task (the reference leaks a pair per call)
     void* evStop = nullptr;
 };

@@ -241,7 +241,21 @@ ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pa
     // One phase: serve every arrival in order; when idle, run a chunk of the best-effort task (or just wait,
     // in the solo phase).  A query's latency runs from its arrival to the end of its last kernel, so queueing
     // behind an earlier query or behind best-effort kernels in flight is part of it.
-    size_t be_pos = 0;
+    // cut the best-effort pass into consecutive chunks of at most be_chunk_ms of predicted device time
+    struct Chunk {
+        size_t begin, end;
+    };
+    std::vector<Chunk> chunks;
+    for (size_t k = 0; k < be_ms.size();) {
+        size_t e = k;
+        float t = 0.0f;
+        do {
+            t += be_ms[e++];
+        } while (e < be_ms.size() && t + be_ms[e] <= static_cast<float>(be_chunk_ms));
+        chunks.push_back(Chunk{k, e});
+        k = e;
+    }
+    size_t be_chunk = 0;
     auto phase = [&](Task* be_or_null, std::vector<double>& lat, long long* be_queries) {
         size_t next = 0;
         const double start = now_ms();
@@ -251,23 +265,21 @@ ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pa
             if (now >= seconds * 1e3) break;
             if (next < arrivals.size() && arrivals[next] <= now) {
                 lc_task->initExecution();
-                lc_task->enqueue(stream);
+                lc_task->enqueueGraph(stream);
                 be.streamSync(stream);
                 lat.push_back(now_ms() - start - arrivals[next]);
                 ++next;
                 continue;
             }
             if (!be_or_null) continue;
-            float budget = static_cast<float>(be_chunk_ms);
-            do {
-                be_or_null->kernels[be_pos]->execute(stream);
-                budget -= be_ms[be_pos];
-                if (++be_pos == be_or_null->kernels.size()) {
-                    be_pos = 0;
-                    *be_queries += be_queries_per_pass;
-                    be_or_null->initExecution();
-                }
-            } while (budget > be_ms[be_pos]);
+            // one pre-cut chunk of the best-effort task, replayed as a graph
+            const Chunk& c = chunks[be_chunk];
+            be_or_null->enqueueGraph(c.begin, c.end, stream);
+            if (++be_chunk == chunks.size()) {
+                be_chunk = 0;
+                *be_queries += be_queries_per_pass;
+                be_or_null->initExecution();
+            }
             be.streamSync(stream);
         }
         return (now_ms() - start) / 1e3;

@@ -128,6 +128,16 @@ public:
     float eventElapsedMs(void* a, void* b) override {
         return static_cast<float>(*static_cast<double*>(b) - *static_cast<double*>(a));
     }
+    int captures = 0, replays = 0;
+    void* graphCapture(stream_t, const std::function<void()>& body) override {
+        ++captures;
+        return new std::function<void()>(body);
+    }
+    void graphLaunch(void* g, stream_t) override {
+        ++replays;
+        (*static_cast<std::function<void()>*>(g))();
+    }
+    void graphDestroy(void* g) override { delete static_cast<std::function<void()>*>(g); }
     int op() {
         ++ops;
         g_clock_ms += 0.004;
@@ -308,6 +318,7 @@ int main(int argc, char** argv) {
         tm2.warmup_passes = 1;
         ColocationResult co = tm2.runColocation(&be_task, 8, 0.05, 2000.0, 1.5, 7, nullptr);
         CHECK(co.lc_served > 10 && co.be_queries > 0 && co.be_queries % 8 == 0 && co.lc_p99_ms >= co.lc_p50_ms);
+        CHECK(fake.captures >= 2 && fake.replays > fake.captures);  // LC pass and BE chunks are replayed as graphs
     }
     CHECK(throws([] { logger.ERROR("boom"); }));
     destroyCreatedKernels();
