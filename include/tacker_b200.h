@@ -86,7 +86,7 @@ int tk_get_option(const char* name, int* value);
 int tk_device_status(unsigned* code);
 
 /* ---- the fmap replacement --------------------------------------------------------------
- * Keys (same strings as the reference table): "gptb_tzgemm", "gptb_stencil", "gptb_cp",
+ * Keys (same strings as the reference table): "gptb_tzgemm", "gptb_tzgemm_acc", "gptb_stencil", "gptb_cp",
  * "gptb_mriq", "tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq"; plus "ori_stencil", "ori_cp",
  * "ori_mriq" for the non-persistent launch shape of the solo kernels. */
 tk_launch_fn tk_lookup(const char* key);
@@ -123,6 +123,14 @@ int tk_query(const char* key, tk_kernel_info* info);
  *   A, B, C 16-byte aligned. */
 int tk_launch_gptb_tzgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
                           unsigned smem_bytes, void* stream);
+
+/* gptb_tzgemm_acc  the same kernel and argument list for skinny problems (few 64x64 tiles, long K: the
+ *   batch-1 dense layers).  No counterpart in the reference, whose tzgemm leaves most SMs idle on such shapes.
+ *   K is cut into ranges handled by different CTAs and the partial products are added into C with
+ *   reductions, so C MUST BE ZERO on entry; the order of the additions, and with it the last bits of the
+ *   result, can differ from run to run. */
+int tk_launch_gptb_tzgemm_acc(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                              unsigned smem_bytes, void* stream);
 
 /* gptb_stencil  replaces general_ptb_stencil (src/gptb_kernel/stencil_kernel.cu:3-105).
  *   params (17): float c0, float c1, float* A0, float* Anext, int nx, int ny, int nz,

@@ -23,7 +23,7 @@ _lib = None
 LAUNCH_FN = C.CFUNCTYPE(C.c_int, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_uint), C.POINTER(C.c_uint),
                         C.c_uint, C.c_void_p)
 
-KEYS = ("gptb_tzgemm", "gptb_stencil", "gptb_cp", "gptb_mriq", "tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq",
+KEYS = ("gptb_tzgemm", "gptb_tzgemm_acc", "gptb_stencil", "gptb_cp", "gptb_mriq", "tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq",
         "ori_stencil", "ori_cp", "ori_mriq")
 
 

@@ -37,6 +37,7 @@ struct GemmArgs {
     int batch;           // independent problems of the same shape (1 for the reference's tzgemm)
     long long stride_c;  // elements between consecutive C matrices of a batch
     int l2_hints;        // 1: operand tiles are loaded with the evict-last L2 priority
+    int splitk;          // > 1: K is cut into that many ranges handled by different CTAs, C += partial (red.add)
 };
 
 // STAGED = the epilogue transposes through shared memory (coalesced row stores, 18 KB); the unstaged form writes
@@ -66,7 +67,8 @@ struct SuperTileWalk {
     int sc;     // super-tile columns
     int r0;     // first super-tile row touched
     int ncand;  // candidates = batch x touched super-tile rows x sc
-    int per;    // candidates per batch entry
+    int per;    // candidates per batch entry (before the K split)
+    int nsplit; // K ranges per super-tile
     int start, end, mt;
 
     __host__ __device__ __forceinline__ void init(const GemmArgs& g) {
@@ -76,6 +78,7 @@ struct SuperTileWalk {
         start = g.start < 0 ? 0 : g.start;
         end = g.end > nt * mt ? nt * mt : g.end;
         per = 1;
+        nsplit = 1;
         if (start >= end) {
             ncand = 0;
             r0 = 0;
@@ -84,11 +87,20 @@ struct SuperTileWalk {
         r0 = (start / nt) / 2;
         const int r1 = ((end - 1) / nt) / 2;
         per = (r1 - r0 + 1) * sc;
-        ncand = per * (g.batch > 0 ? g.batch : 1);
+        nsplit = g.splitk > 1 ? g.splitk : 1;
+        ncand = per * (g.batch > 0 ? g.batch : 1) * nsplit;
+    }
+
+    // K-block range [kb0, kb1) of candidate `cand` (the split index is the fastest-varying part of it)
+    __host__ __device__ __forceinline__ void krange(int cand, int kblocks, int& kb0, int& kb1) const {
+        const int sp = cand % nsplit;
+        kb0 = static_cast<int>(static_cast<long long>(kblocks) * sp / nsplit);
+        kb1 = static_cast<int>(static_cast<long long>(kblocks) * (sp + 1) / nsplit);
     }
 
     // bit (h * (BN/64) + cb) set <=> sub-tile (64-row half h, 64-column block cb) is in range
     __host__ __device__ __forceinline__ uint32_t mask(int cand, int& R, int& Cc, int& b) const {
+        cand /= nsplit;
         b = cand / per;
         cand -= b * per;
         R = r0 + cand / sc;
@@ -165,7 +177,9 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
             for (int cand = blockIdx.x; cand < walk.ncand && ok; cand += gridDim.x) {
                 int R, Cc, b;
                 if (walk.mask(cand, R, Cc, b) == 0u) continue;
-                for (int kb = 0; kb < kblocks; ++kb) {
+                int kb0, kb1;
+                walk.krange(cand, kblocks, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
                     mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
@@ -208,7 +222,9 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + as * BN;
-                for (int kb = 0; kb < kblocks; ++kb) {
+                int kb0, kb1;
+                walk.krange(cand, kblocks, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     ok = mbar_wait(full_bar(stage), phase, abort_flag, g.status, DEV_TIMEOUT_FULL);
                     if (!ok) break;
                     tc_fence_after_sync();
@@ -218,7 +234,7 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
 #pragma unroll
                     for (int k = 0; k < kGemmBK / 16; ++k) {
                         // 16 fp16 = 32 bytes further along K inside the swizzled row: +2 in units of 16 B
-                        umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, (kb > kb0 || k != 0) ? 1u : 0u);
                     }
                     umma_commit(empty_bar(stage));  // frees the stage once these UMMAs have read it
                     if (++stage == STAGES) {
@@ -275,7 +291,9 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
                     for (int i = 0; i < 8; ++i) {
                         const int rr = 4 * i + (lane >> 3);
                         const float4 o = *reinterpret_cast<const float4*>(stage + rr * L::kEpiPitch + (lane & 7) * 4);
-                        *reinterpret_cast<float4*>(cchunk + static_cast<size_t>(rr) * g.N) = o;
+                        float* dstp = cchunk + static_cast<size_t>(rr) * g.N;
+                        if (g.splitk > 1) red_add_v4(dstp, o);
+                        else *reinterpret_cast<float4*>(dstp) = o;
                     }
                     __syncwarp();
                 } else {
@@ -287,7 +305,8 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
                         o.y = g.alpha * __uint_as_float(r[4 * v + 1]);
                         o.z = g.alpha * __uint_as_float(r[4 * v + 2]);
                         o.w = g.alpha * __uint_as_float(r[4 * v + 3]);
-                        dst[v] = o;
+                        if (g.splitk > 1) red_add_v4(reinterpret_cast<float*>(dst + v), o);
+                        else dst[v] = o;
                     }
                 }
             }

@@ -170,6 +170,7 @@ static int parse_gemm(void** params, int base, int i_start, int i_end, GemmCall*
     c->g.batch = 1;
     c->g.stride_c = 0;
     c->g.l2_hints = 0;
+    c->g.splitk = 1;
     const bool empty = c->g.start >= c->g.end;
     if (c->g.M < 128 || c->g.N < 64 || c->g.K < 64) return TK_ERR_SHAPE;
     if (c->g.M % 128 || c->g.N % 64 || c->g.K % 64) return TK_ERR_SHAPE;
@@ -307,7 +308,7 @@ static int launch_tzgemm(const GemmCall& c, unsigned ctas, cudaStream_t st) {
     return launch_error("tzgemm_kernel launch");
 }
 
-static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st) {
+static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st, bool allow_splitk = false) {
     DeviceInfo* d = nullptr;
     int rc = device_info(&d);
     if (rc != TK_OK) return rc;
@@ -315,6 +316,18 @@ static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st) {
     if (c.g.start >= c.g.end) return TK_OK;
     // one CTA per SM holds the whole tensor memory; more CTAs than SMs would only queue
     const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
+    if (allow_splitk) {
+        // a skinny problem has fewer super-tiles than SMs: cut K so that every SM gets a share (C was zeroed by
+        // the caller and receives the partial products as reductions)
+        const int bn = choose_bn(c.g, static_cast<int>(ctas));
+        const long long tiles = c.g.end - c.g.start;
+        const long long nsuper = (tiles * 64 * 64 + 128ll * bn - 1) / (128ll * bn) * (c.g.batch > 0 ? c.g.batch : 1);
+        int split = static_cast<int>(ctas / (nsuper > 0 ? nsuper : 1));
+        const int kblocks = c.g.K / kGemmBK;
+        if (split > kblocks / 4) split = kblocks / 4;  // at least four K-blocks per share
+        if (split > 32) split = 32;
+        c.g.splitk = split > 1 ? split : 1;
+    }
     return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_tzgemm<256>(c, ctas, st)
                                                         : launch_tzgemm<128>(c, ctas, st);
 }

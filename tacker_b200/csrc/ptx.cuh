@@ -139,6 +139,12 @@ __device__ __forceinline__ void tma_load_tile_hint(uint32_t dst_smem, const void
         : "memory");
 }
 
+// C += partial for the K-split GEMM: one 16-byte reduction, no value returned
+__device__ __forceinline__ void red_add_v4(float* addr, const float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
 // ---- tcgen05 ---------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t result_slot_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot_smem),

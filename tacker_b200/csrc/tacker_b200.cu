@@ -94,6 +94,16 @@ TK_API int tk_launch_gptb_tzgemm(void** params, int nparams, const unsigned grid
     return run_tzgemm(c, grid[0], static_cast<cudaStream_t>(stream));
 }
 
+TK_API int tk_launch_gptb_tzgemm_acc(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                     unsigned, void* stream) {
+    int rc = check_params(params, nparams, 17);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    GemmCall c;
+    if ((rc = parse_gemm(params, 0, 13, 15, &c)) != TK_OK) return rc;
+    return run_tzgemm(c, grid[0], static_cast<cudaStream_t>(stream), true);
+}
+
 TK_API int tk_launch_gptb_stencil(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
                                   unsigned, void* stream) {
     int rc = check_params(params, nparams, 17);
@@ -304,6 +314,7 @@ struct KeyEntry {
 };
 static const KeyEntry kKeys[] = {
     {"gptb_tzgemm", tk_launch_gptb_tzgemm, 17},       {"gptb_stencil", tk_launch_gptb_stencil, 17},
+    {"gptb_tzgemm_acc", tk_launch_gptb_tzgemm_acc, 17},
     {"gptb_cp", tk_launch_gptb_cp, 14},               {"gptb_mriq", tk_launch_gptb_mriq, 18},
     {"tzgemm_stencil", tk_launch_mix_tzgemm_stencil, 32}, {"tzgemm_cp", tk_launch_mix_tzgemm_cp, 29},
     {"tzgemm_mriq", tk_launch_mix_tzgemm_mriq, 33},   {"ori_stencil", tk_launch_ori_stencil, 7},
@@ -349,7 +360,7 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
     info->nparams = kKeys[idx].nparams;
     const std::string k(key);
     const int gsm = gemm_smem_bytes<256>();
-    if (k == "gptb_tzgemm") {
+    if (k == "gptb_tzgemm" || k == "gptb_tzgemm_acc") {
         info->threads_tensor = kGemmThreads;
         info->tmem_columns = 512;
         return fill_info(tzgemm_kernel<256, kStages256>, kGemmThreads, gsm, info);
@@ -485,6 +496,7 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     c.g.batch = 1;
     c.g.stride_c = 0;
     c.g.l2_hints = 0;
+    c.g.splitk = 1;
     if (M < 128 || N < 64 || K < 64 || M % 128 || N % 64 || K % 64) return TK_ERR_SHAPE;
     const int tiles = (M / 64) * (N / 64);
     CdCall cd;
@@ -575,16 +587,32 @@ __global__ void im2col_nhwc_f16_kernel(const float* __restrict__ x, int H, int W
         const int k0 = static_cast<int>(e % (K_pad / 8)) * 8;
         __align__(16) __half v[8];
         const int oh = m / OW, ow = m % OW;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int k = k0 + u;
-            float val = 0.0f;
-            if (m < M && k < K) {
-                const int tap = k / C, c = k % C;
-                const int hi = oh * stride - pad + tap / kw, wi = ow * stride - pad + tap % kw;
-                if (hi >= 0 && wi >= 0 && hi < H && wi < W) val = __ldg(x + (static_cast<size_t>(hi) * W + wi) * C + c);
+        if ((C & 7) == 0 && m < M && k0 + 8 <= K && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+            // eight consecutive k of one filter tap: 32 contiguous bytes of the image (every layer but the first)
+            const int tap = k0 / C, c = k0 - tap * C;
+            const int hi = oh * stride - pad + tap / kw, wi = ow * stride - pad + tap % kw;
+            float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo;
+            if (hi >= 0 && wi >= 0 && hi < H && wi < W) {
+                const float4* src = reinterpret_cast<const float4*>(x + (static_cast<size_t>(hi) * W + wi) * C + c);
+                lo = __ldg(src);
+                hi4 = __ldg(src + 1);
             }
-            v[u] = __float2half_rn(val);
+            v[0] = __float2half_rn(lo.x), v[1] = __float2half_rn(lo.y), v[2] = __float2half_rn(lo.z);
+            v[3] = __float2half_rn(lo.w), v[4] = __float2half_rn(hi4.x), v[5] = __float2half_rn(hi4.y);
+            v[6] = __float2half_rn(hi4.z), v[7] = __float2half_rn(hi4.w);
+        } else {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int k = k0 + u;
+                float val = 0.0f;
+                if (m < M && k < K) {
+                    const int tap = k / C, c = k % C;
+                    const int hi = oh * stride - pad + tap / kw, wi = ow * stride - pad + tap % kw;
+                    if (hi >= 0 && wi >= 0 && hi < H && wi < W)
+                        val = __ldg(x + (static_cast<size_t>(hi) * W + wi) * C + c);
+                }
+                v[u] = __float2half_rn(val);
+            }
         }
         *reinterpret_cast<uint4*>(A + static_cast<size_t>(m) * K_pad + k0) = *reinterpret_cast<const uint4*>(v);
     }
@@ -835,6 +863,7 @@ TK_API int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int 
     c.g.status = nullptr;
     c.g.batch = batch;
     c.g.l2_hints = 0;
+    c.g.splitk = 1;
     c.g.stride_c = stride_c > 0 ? stride_c : static_cast<long long>(M) * N;
     DeviceInfo* d = nullptr;
     int rc = device_info(&d);

@@ -103,10 +103,14 @@ ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream)
         lc_task->initExecution();
         for (size_t k = 0; k < n; ++k) lc_kernel_time_vec[k] += timed(lc_task->kernels[k]);
     }
-    for (auto& t : lc_kernel_time_vec) {
-        t /= profile_passes;
-        res.lc_solo_ms += t;
+    for (size_t k = 0; k < n; ++k) {
+        lc_kernel_time_vec[k] /= profile_passes;
+        res.lc_solo_ms += lc_kernel_time_vec[k];
+        if (mode == ExecutionMode::Aker)  // the per-kernel profile is what the Recorder writes out at exit
+            recorder.recordKernel(lc_task->taskId, lc_task->kernels[k]->Id, lc_task->kernels[k]->kernelName,
+                                  lc_kernel_time_vec[k]);
     }
+    if (mode == ExecutionMode::Aker) recorder.recordTask(lc_task->taskId, lc_task->taskName);
     for (auto* k : lc_task->kernels) res.mixable_times += (k->mixable != 0);
     std::vector<float> lc_headroom_vec(lc_kernel_time_vec);  // time still to come from kernel i on
     for (int i = static_cast<int>(n) - 2; i >= 0; --i) lc_headroom_vec[i] += lc_headroom_vec[i + 1];

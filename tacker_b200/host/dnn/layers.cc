@@ -74,8 +74,15 @@ void TzLayer::buildGemm(int id) {
     ori->M_GLOBAL = M_pad;
     ori->ori_blks = (M_pad / 64) * (N_pad / 64);
     ori->launchGridDim = dim3h(static_cast<unsigned>(ori->ori_blks), 1, 1);
-    gptb.reset(new GPTBKernel(id, "tzgemm", "gptb_tzgemm", ori.get(), dim3h(static_cast<unsigned>(backend().smCount()), 1, 1),
-                              dim3h(192, 1, 1), 0, ori->ori_blks));
+    const unsigned sms = static_cast<unsigned>(backend().smCount());
+    gptb.reset(new GPTBKernel(id, "tzgemm", "gptb_tzgemm", ori.get(), dim3h(sms, 1, 1), dim3h(192, 1, 1), 0, ori->ori_blks));
+    // a layer with fewer 128 x 256 super-tiles than half the SMs and a long K (the batch-1 dense layers) runs
+    // alone through the K-split form, which needs C zeroed first; fused launches keep the plain kernel
+    const long long nsuper = static_cast<long long>(M_pad / 128) * ((N_pad + 255) / 256);
+    skinny = nsuper * 2 <= sms && K_pad >= 1024;
+    if (skinny)
+        gptb_acc.reset(new GPTBKernel(id, "tzgemm", "gptb_tzgemm_acc", ori.get(), dim3h(sms, 1, 1), dim3h(192, 1, 1), 0,
+                                      ori->ori_blks));
 }
 
 ConvKernel::ConvKernel(int id, const std::string& name, DnnArena& arena, const float* input, int H, int W, int Cin,

@@ -44,10 +44,16 @@ public:
 protected:
     void executeImpl(stream_t stream) override {  // solo LC path: operand preparation + tzgemm alone
         prepare(stream);
-        gptb->execute(stream);
+        if (skinny) {
+            backend().fillZero(C, static_cast<size_t>(M_pad) * N_pad * sizeof(float), stream);
+            gptb_acc->execute(stream);
+        } else {
+            gptb->execute(stream);
+        }
     }
+    bool skinny = false;
     std::unique_ptr<OriTZGEMMKernel> ori;
-    std::unique_ptr<GPTBKernel> gptb;
+    std::unique_ptr<GPTBKernel> gptb, gptb_acc;
 };
 
 // 2-D convolution, NHWC, square kernel (mixable = 2; getArgs = the 14 ints of cudnnConvolutionForward in

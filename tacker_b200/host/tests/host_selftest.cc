@@ -97,7 +97,7 @@ FAKE_LAUNCHER(l_omq, "ori_mriq")
 class FakeBackend : public Backend {
 public:
     std::map<std::string, tk_launch_fn> table = {
-        {"gptb_tzgemm", l_tz}, {"gptb_stencil", l_st}, {"gptb_cp", l_cp},       {"gptb_mriq", l_mq},
+        {"gptb_tzgemm", l_tz}, {"gptb_tzgemm_acc", l_tz}, {"gptb_stencil", l_st}, {"gptb_cp", l_cp},       {"gptb_mriq", l_mq},
         {"tzgemm_stencil", l_mst}, {"tzgemm_cp", l_mcp}, {"tzgemm_mriq", l_mmq}, {"ori_stencil", l_ost},
         {"ori_cp", l_ocp},     {"ori_mriq", l_omq}};
     int ops = 0;

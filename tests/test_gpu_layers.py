@@ -7,17 +7,19 @@ from helpers import to_dev
 pytestmark = pytest.mark.gpu
 
 
-def test_conv_as_im2col_plus_tzgemm(cuda, oracle):
-    """A 3x3 convolution computed the way ConvKernel does it: NHWC im2col to fp16, tzgemm, bias + ReLU."""
+@pytest.mark.parametrize("geom", [(12, 10, 5, 7, 3, 1, 1), (9, 11, 16, 40, 3, 1, 2), (14, 14, 8, 64, 1, 0, 1)])
+def test_conv_as_im2col_plus_tzgemm(cuda, oracle, geom):
+    """A convolution computed the way ConvKernel does it: NHWC im2col to fp16, tzgemm, bias + ReLU."""
     from tacker_b200 import ops
 
-    H, W, Cin, Cout, k, pad, stride = 12, 10, 5, 7, 3, 1, 1
+    H, W, Cin, Cout, k, pad, stride = geom
     x = oracle.uniform_f32(H * W * Cin, 1, -1.0, 1.0).reshape(H, W, Cin)
     w_bits, w = oracle.uniform_f16(Cout * k * k * Cin, 2, -0.5, 0.5)
     w = w.reshape(Cout, k, k, Cin)
     bias = oracle.uniform_f32(Cout, 3, -0.1, 0.1)
-    M, K = H * W, k * k * Cin
-    M_pad, N_pad, K_pad = 128, 64, 64
+    OH, OW = (H + 2 * pad - k) // stride + 1, (W + 2 * pad - k) // stride + 1
+    M, K = OH * OW, k * k * Cin
+    M_pad, N_pad, K_pad = -(-M // 128) * 128, 64, -(-K // 64) * 64
     Bw = np.zeros((N_pad, K_pad), dtype=np.uint16)
     Bw[:Cout, :K] = w_bits.reshape(Cout, K)
     dx, dB = to_dev(cuda, x), cuda.from_numpy(Bw.view(np.float16)).cuda()
@@ -31,7 +33,8 @@ def test_conv_as_im2col_plus_tzgemm(cuda, oracle):
     cuda.cuda.synchronize()
     # the im2col operand is bit-exact: fp16 rounding of the gathered inputs
     xp = np.pad(x, ((pad, pad), (pad, pad), (0, 0)))
-    cols = np.stack([xp[i:i + H, j:j + W, :] for i in range(k) for j in range(k)], axis=2).reshape(M, K)
+    cols = np.stack([xp[i:i + stride * OH:stride, j:j + stride * OW:stride, :] for i in range(k) for j in range(k)],
+                    axis=2).reshape(M, K)
     A = dA.cpu().numpy()
     assert np.array_equal(A[:M, :K].view(np.uint16), oracle.f32_to_f16_bits(cols).reshape(M, K))
     assert not A[M:].any() and not A[:, K:].any()

@@ -155,3 +155,22 @@ def test_bad_arguments_return_status(cuda):
     assert status(128, 128, 128, a_ptr=A.data_ptr() + 2) == -2
     assert status(128, 128, 128, nparams=16) == -1
     cuda.cuda.synchronize()
+
+
+@pytest.mark.parametrize("shape", [(128, 512, 4096), (128, 4096, 2048), (256, 64, 8192), (1024, 1024, 1024)])
+def test_k_split_form_for_skinny_problems(cuda, oracle, shape):
+    """gptb_tzgemm_acc: K ranges on different CTAs, partial products reduced into a zeroed C."""
+    import ctypes as C
+
+    from tacker_b200 import ops
+
+    M, N, K = shape
+    a_bits, a, b_bits, b = gemm_inputs(oracle, M, N, K, seed=K)
+    A, B = half_dev(cuda, a_bits), half_dev(cuda, b_bits)
+    Cd = cuda.zeros((M, N), dtype=cuda.float32, device="cuda")
+    ori = ops.OriTZGEMMKernel(A.data_ptr(), B.data_ptr(), Cd.data_ptr(), M, N, K, 1.1, round_dims=False)
+    k = ops.GPTBKernel("tzgemm", "gptb_tzgemm_acc", ori, (ops.sm_count(), 1, 1), (192, 1, 1), 0, ori.ori_blks)
+    k.execute(cuda.cuda.current_stream().cuda_stream)
+    cuda.cuda.synchronize()
+    assert ops.device_status() == 0
+    _check(oracle, Cd.cpu().numpy(), a, b, 1.1)
