@@ -451,10 +451,10 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
                                                                start=s, end=e, grid=grid or sms * 2, block=block)
     try:
         t_g, t_c = t_of([tz()], 10), t_of([cp()], 3)
-        t_f = t_of([ops.mix(cp(), tz(), cd_threads=448, grid=sms)], 3)
+        t_f = t_of([ops.mix(cp(), tz(), cd_threads=832, grid=sms)], 3)
         nb = max(8, int(round(256 * t_g / t_c)))           # blocks of Coulomb work worth one GEMM
         t_cb = t_of([cp(0, nb)], 5)
-        t_fb = t_of([ops.mix(cp(0, nb), tz(), cd_threads=448, grid=sms)], 5)
+        t_fb = t_of([ops.mix(cp(0, nb), tz(), cd_threads=832, grid=sms)], 5)
     finally:
         pass
     pairs3 = 8192.0 * 512 * 512
@@ -476,10 +476,10 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
                                                                  kv.data_ptr(), numX, start=s, end=e, grid=grid or sms * 4,
                                                                  block=block)
     t_g, t_m = t_of([tz4()], 10), t_of([mq()], 3)
-    t_f = t_of([ops.mix(mq(), tz4(), cd_threads=576, grid=sms)], 3)
+    t_f = t_of([ops.mix(mq(), tz4(), cd_threads=704, grid=sms)], 3)
     nb = max(148, int(round(1024 * t_g / t_m)))
     t_mb = t_of([mq(0, nb)], 5)
-    t_fb = t_of([ops.mix(mq(0, nb), tz4(), cd_threads=576, grid=sms)], 5)
+    t_fb = t_of([ops.mix(mq(0, nb), tz4(), cd_threads=704, grid=sms)], 5)
     out["config4_gemm4096x2048_mriq"] = {
         "gemm_us": round(t_g, 1), "mriq_us": round(t_m, 1), "fused_us": round(t_f, 1),
         "fused_vs_sequential": round(t_f / (t_g + t_m), 4), "mriq_gpairs_per_s": round(numK * numX / t_m / 1e3, 1),

@@ -516,7 +516,8 @@ static int run_mix(GemmCall& c, const CdCall& cd_in, unsigned grid0, unsigned bl
     if (gemm_empty && cd.empty()) return TK_OK;
     if (block0 <= static_cast<unsigned>(kGemmThreads)) return TK_ERR_LAUNCH_CONFIG;
     const unsigned granule = 32;
-    const unsigned cdt = cd_threads(block0 - kGemmThreads, granule, kMaxMixThreads - kGemmThreads);
+    const unsigned cap = (cd.kind == CD_STENCIL ? kMaxMixThreads : kMaxMixThreadsSfu) - kGemmThreads;
+    const unsigned cdt = cd_threads(block0 - kGemmThreads, granule, cap);
     if (cdt == 0) return TK_ERR_LAUNCH_CONFIG;
     if (gemm_empty) {  // nothing for the tensor role: run the CUDA-core kernel alone
         switch (cd.kind) {

@@ -19,7 +19,8 @@ __device__ unsigned g_dev_status;
 // -------------------------------------------------------------------------------------------------
 // kernels
 // -------------------------------------------------------------------------------------------------
-constexpr int kMaxMixThreads = 768;  // 192 tensor-role threads + up to 576 CUDA-core threads (<= 85 registers each)
+constexpr int kMaxMixThreads = 768;     // stencil pair: 192 tensor-role threads + up to 576 CUDA-core threads (<= 85 registers)
+constexpr int kMaxMixThreadsSfu = 1024;  // Coulomb / MRI-Q pairs: their roles need many warps and few registers (<= 64)
 
 __device__ __forceinline__ uint8_t* align_smem_1024(uint8_t* p) {
     const uint32_t a = smem_u32(p);
@@ -87,7 +88,7 @@ mix_stencil_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 }
 
 template <int BN, int STAGES, int PPT>
-__global__ void __launch_bounds__(kMaxMixThreads, 1)
+__global__ void __launch_bounds__(kMaxMixThreadsSfu, 1)
 mix_cp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const GemmArgs g, const CpArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -100,7 +101,7 @@ mix_cp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(kMaxMixThreads, 1)
+__global__ void __launch_bounds__(kMaxMixThreadsSfu, 1)
 mix_mriq_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const GemmArgs g, const MriqArgs m) {
     extern __shared__ uint8_t smem_raw[];

@@ -65,10 +65,10 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
         "stencil": (lambda s=0, e=None: ops.gptb_stencil(1 / 6, 1 / 36, grid0.data_ptr(), grid1.data_ptr(), 512, 512,
                                                          64, start=s, end=e), 1024, 512),
         "cp": (lambda s=0, e=None: ops.gptb_cp(8192, 0.125, lat.data_ptr(), packed.data_ptr(), 512, 512, start=s,
-                                               end=e), 256, 448),
+                                               end=e), 256, 832),
         "mriq": (lambda s=0, e=None: ops.gptb_mriq(2048, xyz[0].data_ptr(), xyz[1].data_ptr(), xyz[2].data_ptr(),
                                                    qr.data_ptr(), qi.data_ptr(), kv.data_ptr(), 262144, start=s,
-                                                   end=e), 1024, 576),
+                                                   end=e), 1024, 704),
     }
     out = {}
     for cd, (mk, blocks, cd_threads) in cds.items():
