@@ -449,6 +449,29 @@ TK_API int tk_coulomb_compute(const float* atoms_xyzq, int numatoms, float zplan
 // =================================================================================================
 static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
+// upload stream and the two events that order it against the caller's stream, one set per device
+struct PairStreams {
+    cudaStream_t upload = nullptr;
+    cudaEvent_t inputs_ready = nullptr, compute_done = nullptr;  // compute_done: kernels finished and grid downloaded
+};
+static std::map<int, PairStreams> g_pair_streams;
+
+static int pair_streams(PairStreams** out) {
+    int dev = 0;
+    TK_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_pair_streams.find(dev);
+    if (it == g_pair_streams.end()) {
+        PairStreams p;
+        TK_CUDA(cudaStreamCreateWithFlags(&p.upload, cudaStreamNonBlocking));
+        TK_CUDA(cudaEventCreateWithFlags(&p.inputs_ready, cudaEventDisableTiming));
+        TK_CUDA(cudaEventCreateWithFlags(&p.compute_done, cudaEventDisableTiming));
+        it = g_pair_streams.emplace(dev, p).first;
+    }
+    *out = &it->second;
+    return TK_OK;
+}
+
 TK_API int tk_pair_tzgemm_stencil_workspace(int M, int N, int K, int nx, int ny, int nz, size_t* bytes) {
     if (!bytes || M <= 0 || N <= 0 || K <= 0 || nx <= 0 || ny <= 0 || nz <= 0) return TK_ERR_ARGS;
     const size_t grid = align256(sizeof(float) * static_cast<size_t>(nx) * ny * nz);
@@ -477,13 +500,20 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     float* dC = reinterpret_cast<float*>(w + align256(a_bytes) + align256(b_bytes));
     float* g0 = reinterpret_cast<float*>(w + align256(a_bytes) + align256(b_bytes) + align256(c_bytes));
     float* g1 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(g0) + align256(g_bytes));
-    TK_CUDA(cudaMemcpyAsync(dA, A_host, a_bytes, cudaMemcpyHostToDevice, st));
-    TK_CUDA(cudaMemcpyAsync(dB, B_host, b_bytes, cudaMemcpyHostToDevice, st));
-    TK_CUDA(cudaMemcpyAsync(g0, A0_host, g_bytes, cudaMemcpyHostToDevice, st));
-    TK_CUDA(cudaMemcpyAsync(g1, g0, g_bytes, cudaMemcpyDeviceToDevice, st));  // boundary cells of the second buffer
-
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
+    // Uploads run on their own stream: the upload of call i+1 only has to wait until call i has finished with the
+    // input buffers (kernels done, result grid downloaded), not for the download of C, so consecutive calls
+    // overlap the two PCIe directions.
+    PairStreams* ps = nullptr;
+    if ((rc = pair_streams(&ps)) != TK_OK) return rc;
+    TK_CUDA(cudaStreamWaitEvent(ps->upload, ps->compute_done, 0));
+    TK_CUDA(cudaMemcpyAsync(dA, A_host, a_bytes, cudaMemcpyHostToDevice, ps->upload));
+    TK_CUDA(cudaMemcpyAsync(dB, B_host, b_bytes, cudaMemcpyHostToDevice, ps->upload));
+    TK_CUDA(cudaMemcpyAsync(g0, A0_host, g_bytes, cudaMemcpyHostToDevice, ps->upload));
+    TK_CUDA(cudaMemcpyAsync(g1, g0, g_bytes, cudaMemcpyDeviceToDevice, ps->upload));  // boundary cells of buffer 2
+    TK_CUDA(cudaEventRecord(ps->inputs_ready, ps->upload));
+    TK_CUDA(cudaStreamWaitEvent(st, ps->inputs_ready, 0));
     GemmCall c;
     c.A = dA;
     c.B = dB;
@@ -527,8 +557,12 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
         }
         if (rc != TK_OK) return rc;
     }
-    TK_CUDA(cudaMemcpyAsync(C_host, dC, c_bytes, cudaMemcpyDeviceToHost, st));
+    // the downloads stay on the caller's stream: synchronising it means the results are in the host buffers.
+    // The grid goes first: once it has left, every buffer the next call's upload writes (A, B, both grids) is
+    // free, and that upload runs while C is still on its way down.
     TK_CUDA(cudaMemcpyAsync(Aout_host, (sweeps & 1) ? g1 : g0, g_bytes, cudaMemcpyDeviceToHost, st));
+    TK_CUDA(cudaEventRecord(ps->compute_done, st));
+    TK_CUDA(cudaMemcpyAsync(C_host, dC, c_bytes, cudaMemcpyDeviceToHost, st));
     return TK_OK;
 }
 
