@@ -223,6 +223,12 @@ def run_ours(args):
                     k.execute(st)
         return timed(make_graph(fn), 3, 2) / reps * 1e3
 
+    if args.only_pairs:  # just the Coulomb and MRI-Q pairs (used for the ncu captures of those kernels)
+        if rank == 0:
+            print(json.dumps({"pairs": other_pairs(torch, ops, sms, gen, t_of, st)}), flush=True)
+        rep.close()
+        return
+
     # ---------------- config 2: GEMM 4096 x 4096 x 1024 + 10 Jacobi sweeps ----------------
     A = (torch.rand(M, K, device="cuda", generator=gen) * 2 - 1).half()
     B = (torch.rand(N, K, device="cuda", generator=gen) * 2 - 1).half()
@@ -499,6 +505,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="skip the ratio sweep, the CPU sample and the reference kernels")
     ap.add_argument("--sustain-ms", type=float, default=400.0)
     ap.add_argument("--colocate-s", type=float, default=5.0, help="seconds of the LC/BE co-location run (0 = skip)")
+    ap.add_argument("--only-pairs", action="store_true", help="run only the Coulomb and MRI-Q pairs and print them")
     ap.add_argument("--fuse-sweeps", type=int, default=0, choices=(0, 1, 2, 10),
                     help="how many sweeps are fused with the GEMM (0 = time 10, 2 and 1 briefly and take the best)")
     args = ap.parse_args()
