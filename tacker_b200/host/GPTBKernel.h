@@ -10,22 +10,19 @@ public:
     GPTBKernel(int id, const std::string kernelName, const std::string funcKey, Kernel* kernel, dim3h gridDim,
                dim3h blockDim, int ptb_start_block_pos, int ptb_end_block_pos)
         : kernel_(kernel) {
+        Id = id;
         this->kernelName = kernelName;
         this->funcKey = funcKey;
-        this->launchGridDim = gridDim;
-        this->launchBlockDim = blockDim;
-        this->Id = id;
-        gptbParams.grid_dimension_x = kernel_->launchGridDim.x;
-        gptbParams.grid_dimension_y = kernel_->launchGridDim.y;
-        gptbParams.grid_dimension_z = kernel_->launchGridDim.z;
-        gptbParams.block_dimension_x = kernel_->launchBlockDim.x;
-        gptbParams.block_dimension_y = kernel_->launchBlockDim.y;
-        gptbParams.block_dimension_z = kernel_->launchBlockDim.z;
-        gptbParams.ptb_iter_block_step = gridDim.x * gridDim.y * gridDim.z;
-        gptbParams.ptb_start_block_pos = ptb_start_block_pos;
-        gptbParams.ptb_end_block_pos = ptb_end_block_pos;
-        this->kernelParams = kernel_->kernelParams;
-        this->smem = kernel_->smem;
+        launchGridDim = gridDim;     // persistent CTAs
+        launchBlockDim = blockDim;
+        smem = kernel->smem;
+        const dim3h& og = kernel->launchGridDim;   // geometry of the launch being emulated
+        const dim3h& ob = kernel->launchBlockDim;
+        gptbParams = GPTBParams{static_cast<int>(og.x), static_cast<int>(og.y), static_cast<int>(og.z),
+                                static_cast<int>(ob.x), static_cast<int>(ob.y), static_cast<int>(ob.z),
+                                ptb_start_block_pos, static_cast<int>(gridDim.x * gridDim.y * gridDim.z),
+                                ptb_end_block_pos};
+        kernelParams = kernel->kernelParams;       // the solo argument list comes first
         loadKernel();
         initParams();
     }

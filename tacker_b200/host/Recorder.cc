@@ -6,32 +6,28 @@
 Recorder recorder;
 
 float Recorder::taskTime(int taskId) const {
-    auto it = task_time_map.find(taskId);
+    const auto it = tasks.find(taskId);
+    if (it == tasks.end()) return 0.0f;
     float total = 0.0f;
-    if (it != task_time_map.end())
-        for (float t : it->second) total += t;
+    for (const KernelRecord& k : it->second.kernels) total += k.ms;
     return total;
 }
 
 size_t Recorder::text(const std::string& filename) {
     std::ofstream file(filename);
-    if (!file.is_open()) {
+    if (!file) {
         std::cerr << "cannot open file: " << filename << std::endl;
         return 0;
     }
-    size_t n = 0;
-    for (auto& task_pair : task_time_map) {
-        const int taskId = task_pair.first;
-        auto& times = task_pair.second;
-        auto& kernelIds = task_kernel_map[taskId];
-        file << "taskID: " << taskId << ", taskName: " << task_name_map[taskId] << "\n";
-        float total = 0.0f;
-        for (size_t i = 0; i < times.size(); ++i, ++n) {
-            total += times[i];
-            file << "    kernelID: " << kernelIds[i] << ", kernelName: " << task_kernel_name_vec[taskId][i]
-                 << ", execTime: " << times[i] << "ms\n";
+    size_t written = 0;
+    for (const auto& entry : tasks) {
+        const TaskRecord& task = entry.second;
+        file << "taskID: " << entry.first << ", taskName: " << task.name << "\n";
+        for (const KernelRecord& k : task.kernels) {
+            file << "    kernelID: " << k.kernelId << ", kernelName: " << k.kernelName << ", execTime: " << k.ms << "ms\n";
+            ++written;
         }
-        file << "    task running time: " << total << "ms\n\n";
+        file << "    task running time: " << taskTime(entry.first) << "ms\n\n";
     }
-    return n;
+    return written;
 }

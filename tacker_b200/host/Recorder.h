@@ -1,5 +1,5 @@
-// Recorder.h -- per-task kernel ids / names / times, written out at exit
-// (reference: src/Recorder.h:7-27, src/Recorder.cc:12-44).
+// Recorder.h -- what ran and how long it took, per task; dumped as text when the run ends
+// (the role of the reference's Recorder: src/Recorder.h:7-27, src/Recorder.cc:12-44).
 #pragma once
 #include <map>
 #include <string>
@@ -7,21 +7,26 @@
 
 class Recorder {
 public:
+    struct KernelRecord {
+        int kernelId;
+        std::string kernelName;
+        float ms;
+    };
     void recordKernel(int taskId, int kernelId, const std::string& kernelName, float executionTime) {
-        task_time_map[taskId].push_back(executionTime);
-        task_kernel_map[taskId].push_back(kernelId);
-        task_kernel_name_vec[taskId].push_back(kernelName);
+        tasks[taskId].kernels.push_back(KernelRecord{kernelId, kernelName, executionTime});
     }
-    void recordTask(int taskId, const std::string& taskName) { task_name_map[taskId] = taskName; }
-    // writes recorder_output.txt-style text; returns the number of kernel records written
+    void recordTask(int taskId, const std::string& taskName) { tasks[taskId].name = taskName; }
+    // One block per task: a header line, one line per kernel record, the task's total.  Returns the number of
+    // kernel records written.
     size_t text(const std::string& filename = "recorder_output.txt");
     float taskTime(int taskId) const;
 
 private:
-    std::map<int, std::vector<float>> task_time_map;
-    std::map<int, std::vector<int>> task_kernel_map;
-    std::map<int, std::vector<std::string>> task_kernel_name_vec;
-    std::map<int, std::string> task_name_map;
+    struct TaskRecord {
+        std::string name;
+        std::vector<KernelRecord> kernels;
+    };
+    std::map<int, TaskRecord> tasks;  // ordered by task id, so the dump is stable
 };
 
 extern Recorder recorder;
