@@ -238,7 +238,7 @@ int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, float* C
 
 /* ---- layer kernels of the LC / BE DNN tasks -------------------------------------------------------------
  * The reference's generated DNN classes call cuDNN / cuBLAS and NNFusion element-wise kernels for
- * everything that is not routed to tzgemm (src/dnn/<model>/*_kernel_class.h); these are the hand-written
+ * everything that is not routed to tzgemm (the `<model>_kernel_class.h` files under src/dnn/); these are the hand-written
  * stand-ins.  Activations are fp32, NHWC for images, [rows][cols] for sequences.
  * tk_im2col_nhwc_f16: conv input -> tzgemm A operand in one pass (im2col_gpu_kernel + convertFp32ToFp16,
  *   src/include/dnn.h:45-99): A[m][k] fp16, m = oh*OW + ow, k = (i*kw + j)*C + c, zero padded to
