@@ -29,14 +29,16 @@ double DnnTask::gemmFlops() const {
 
 float* DnnTask::conv(const float* x, int H, int W, int Cin, int Cout, int k, int pad, int stride, int act, int* OH,
                      int* OW) {
-    auto* c = new ConvKernel(nextId++, "Convolution_" + std::to_string(nextId), arena, x, H, W, Cin, Cout, k, pad, stride,
-                             1000 + nextId);
+    const int id1 = nextId++;
+    auto* c = new ConvKernel(id1, "Convolution_" + std::to_string(id1), arena, x, H, W, Cin, Cout, k, pad, stride,
+                             1000 + id1);
     keep(c);
     *OH = c->OH;
     *OW = c->OW;
     float* y = arena.act(static_cast<size_t>(c->M) * Cout);
     float* bias = arena.weightsF32(Cout, 5000 + nextId, -0.05f, 0.05f);
-    auto* b = new OpKernel(nextId++, "BiasAct_" + std::to_string(nextId), OpKernel::BiasAct);
+    const int id2 = nextId++;
+    auto* b = new OpKernel(id2, "BiasAct_" + std::to_string(id2), OpKernel::BiasAct);
     b->a = c->C;
     b->b = bias;
     b->out = y;
@@ -50,11 +52,13 @@ float* DnnTask::conv(const float* x, int H, int W, int Cin, int Cout, int k, int
 }
 
 float* DnnTask::dense(const float* x, int rows, int in, int out, int act) {
-    auto* g = new GemmKernel(nextId++, "Dot_" + std::to_string(nextId), arena, x, rows, in, out, 2000 + nextId);
+    const int id3 = nextId++;
+    auto* g = new GemmKernel(id3, "Dot_" + std::to_string(id3), arena, x, rows, in, out, 2000 + id3);
     keep(g);
     float* y = arena.act(static_cast<size_t>(rows) * out);
     float* bias = arena.weightsF32(out, 6000 + nextId, -0.05f, 0.05f);
-    auto* b = new OpKernel(nextId++, "BiasAct_" + std::to_string(nextId), OpKernel::BiasAct);
+    const int id4 = nextId++;
+    auto* b = new OpKernel(id4, "BiasAct_" + std::to_string(id4), OpKernel::BiasAct);
     b->a = g->C;
     b->b = bias;
     b->out = y;
@@ -69,7 +73,8 @@ float* DnnTask::dense(const float* x, int rows, int in, int out, int act) {
 
 float* DnnTask::pool(const float* x, int H, int W, int C) {
     float* y = arena.act(static_cast<size_t>(H / 2) * (W / 2) * C);
-    auto* p = new OpKernel(nextId++, "MaxPool_" + std::to_string(nextId), OpKernel::MaxPool);
+    const int id5 = nextId++;
+    auto* p = new OpKernel(id5, "MaxPool_" + std::to_string(id5), OpKernel::MaxPool);
     p->a = x;
     p->out = y;
     p->i0 = H;
@@ -81,7 +86,8 @@ float* DnnTask::pool(const float* x, int H, int W, int C) {
 
 float* DnnTask::addTo(const float* a, const float* b, int rows, int cols, int act) {
     float* y = arena.act(static_cast<size_t>(rows) * cols);
-    auto* k = new OpKernel(nextId++, "Add_" + std::to_string(nextId), OpKernel::Add);
+    const int id6 = nextId++;
+    auto* k = new OpKernel(id6, "Add_" + std::to_string(id6), OpKernel::Add);
     k->a = a;
     k->b = b;
     k->out = y;
@@ -89,7 +95,8 @@ float* DnnTask::addTo(const float* a, const float* b, int rows, int cols, int ac
     k->i1 = cols;
     keep(k);
     if (act) {
-        auto* r = new OpKernel(nextId++, "Relu_" + std::to_string(nextId), OpKernel::BiasAct);
+        const int id7 = nextId++;
+        auto* r = new OpKernel(id7, "Relu_" + std::to_string(id7), OpKernel::BiasAct);
         r->a = y;
         r->b = nullptr;
         r->out = y;
@@ -105,7 +112,8 @@ float* DnnTask::addTo(const float* a, const float* b, int rows, int cols, int ac
 
 float* DnnTask::layernorm(const float* x, int rows, int cols) {
     float* y = arena.act(static_cast<size_t>(rows) * cols);
-    auto* k = new OpKernel(nextId++, "LayerNorm_" + std::to_string(nextId), OpKernel::LayerNorm);
+    const int id8 = nextId++;
+    auto* k = new OpKernel(id8, "LayerNorm_" + std::to_string(id8), OpKernel::LayerNorm);
     k->a = x;
     k->b = arena.weightsF32(cols, 7000 + nextId, 0.9f, 1.1f);
     k->c = arena.weightsF32(cols, 7500 + nextId, -0.05f, 0.05f);
@@ -147,7 +155,8 @@ VGG16::VGG16(int numClasses) : DnnTask(0, "vgg16") {
     x = dense(x, 1, 4096, 4096, 1);
     x = dense(x, 1, 4096, numClasses, 0);
     float* probs = arena.act(numClasses);
-    auto* sm = new OpKernel(nextId++, "Softmax", OpKernel::SoftmaxRows);
+    const int id9 = nextId++;
+    auto* sm = new OpKernel(id9, "Softmax", OpKernel::SoftmaxRows);
     sm->a = x;
     sm->out = probs;
     sm->i0 = 1;
@@ -214,31 +223,37 @@ Bert::Bert(int layers, int batch_, int seq_) : DnnTask(2, "bert"), batch(batch_)
         const float* src[3] = {q, k, v};
         void* dst[3] = {qh, kh, vt};
         for (int i = 0; i < 3; ++i) {
-            auto* s = new OpKernel(nextId++, "SplitHeads_" + std::to_string(nextId), OpKernel::SplitHeads);
+            const int id10 = nextId++;
+            auto* s = new OpKernel(id10, "SplitHeads_" + std::to_string(id10), OpKernel::SplitHeads);
             s->a = src[i];
             s->hout = dst[i];
             s->i0 = batch, s->i1 = seq, s->i2 = hidden, s->i3 = 0, s->i4 = heads, s->i5 = dh, s->i6 = (i == 2);
             keep(s);
         }
         float* scores = arena.act(static_cast<size_t>(bh) * seq * seq);
-        auto* g1 = new OpKernel(nextId++, "BatchMatMul_" + std::to_string(nextId), OpKernel::BatchedGemm);
+        const int id11 = nextId++;
+        auto* g1 = new OpKernel(id11, "BatchMatMul_" + std::to_string(id11), OpKernel::BatchedGemm);
         g1->ha = qh, g1->hb = kh, g1->out = scores;
         g1->i0 = seq, g1->i1 = seq, g1->i2 = dh, g1->i3 = bh, g1->f0 = 1.0f / std::sqrt(static_cast<float>(dh));
         keep(g1);
-        auto* sm = new OpKernel(nextId++, "Softmax_" + std::to_string(nextId), OpKernel::SoftmaxRows);
+        const int id12 = nextId++;
+        auto* sm = new OpKernel(id12, "Softmax_" + std::to_string(id12), OpKernel::SoftmaxRows);
         sm->a = scores, sm->out = scores, sm->i0 = bh, sm->i1 = seq, sm->i2 = seq, sm->f0 = 1.0f;
         keep(sm);
         void* ph = arena.half(static_cast<size_t>(bh) * seq * seq);
-        auto* th = new OpKernel(nextId++, "Convert_" + std::to_string(nextId), OpKernel::RowsToHalf);
+        const int id13 = nextId++;
+        auto* th = new OpKernel(id13, "Convert_" + std::to_string(id13), OpKernel::RowsToHalf);
         th->a = scores, th->hout = ph, th->i0 = bh * seq, th->i1 = seq;
         keep(th);
         float* ctx = arena.act(static_cast<size_t>(rows) * hidden);
-        auto* g2 = new OpKernel(nextId++, "BatchMatMul_" + std::to_string(nextId), OpKernel::BatchedGemm);
+        const int id14 = nextId++;
+        auto* g2 = new OpKernel(id14, "BatchMatMul_" + std::to_string(id14), OpKernel::BatchedGemm);
         g2->ha = ph, g2->hb = vt, g2->out = ctx;
         g2->i0 = seq, g2->i1 = dh, g2->i2 = seq, g2->i3 = bh, g2->f0 = 1.0f;
         keep(g2);
         float* merged = arena.act(static_cast<size_t>(rows) * hidden);
-        auto* mh = new OpKernel(nextId++, "MergeHeads_" + std::to_string(nextId), OpKernel::MergeHeads);
+        const int id15 = nextId++;
+        auto* mh = new OpKernel(id15, "MergeHeads_" + std::to_string(id15), OpKernel::MergeHeads);
         mh->a = ctx, mh->out = merged, mh->i0 = batch, mh->i1 = seq, mh->i4 = heads, mh->i5 = dh;
         keep(mh);
         const float* proj = dense(merged, rows, hidden, hidden, 0);
