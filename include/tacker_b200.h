@@ -73,6 +73,8 @@ const char* tk_last_error(void);
 int tk_sm_count(int* sm_count);
 /* tuning / numerics switches (name -> integer):
  *   "tzgemm_bn"      0 = choose per shape, 128 or 256 = force the super-tile width
+ *   "tzgemm_m256"    solo tzgemm with 256 x 256 super-tiles (a third less operand traffic per flop, no second
+ *                    accumulator buffer): 0 = for large dense problems, 1 = always, -1 = never
  *   "cp_exact"       1 = IEEE 1/sqrt as the reference computes it (default 0: hardware rsqrt)
  *   "cp_ppt"         solo Coulomb kernel: points per thread and work item, 8 (reference granularity), 4
  *                    (default) or 2; "mix_cp_ppt" the same for the fused kernel (default 8)
@@ -275,6 +277,7 @@ int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int N, int 
  * tk_plan_stencil: planes[b*nz + k] += 1 for every plane k of bundle b some warp computes, loads[b*nz + k]
  *   (optional) += 1 for every plane streamed; split = {slabs per bundle, planes per slab} chosen for the launch. */
 int tk_plan_tzgemm(int M, int N, int bn, int start, int end, int ctas, int* cover, int* work);
+int tk_plan_tzgemm_m256(int M, int N, int start, int end, int ctas, int* cover); /* 256 x 256 super-tile kernel */
 int tk_plan_stencil(int nz, int blocks_start, int blocks_end, int gx, int gy, int ctas, int warps_per_cta,
                     int* planes, int* loads, int split[2]);
 

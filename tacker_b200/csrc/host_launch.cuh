@@ -40,6 +40,7 @@ struct Options {
     int stencil_tma = 1;        // 1 = TMA-fed role whenever the shape allows, 0 = always the register role
     int stencil_ring = 4;       // ring depth per warp, solo kernel (2 planes in flight per warp measured best)
     int mix_stencil_ring = 12;  // upper bound of the ring depth in the fused kernel (shared memory decides)
+    int tzgemm_m256 = 0;        // solo tzgemm with 256 x 256 super-tiles: 0 = by shape, 1 = always, -1 = never
     int l2_hints = 0;           // fused kernels: GEMM tiles evict-last, stencil planes evict-first in L2
     int mix_stencil_cfg = 0;    // tensor-role shape of the fused stencil kernel: 0 auto, 1 = 256x3 stages,
                                 // 2 = 128x4, 3 = 128x3, 4 = 128x2
@@ -327,6 +328,22 @@ static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st, bool allow_s
         if (split > kblocks / 4) split = kblocks / 4;  // at least four K-blocks per share
         if (split > 32) split = 32;
         c.g.splitk = split > 1 ? split : 1;
+    }
+    // Large dense problems: 256 x 256 super-tiles stream a third less operand data per flop but have no second
+    // accumulator buffer.  Measured on B200: +7 % at 4096 x 4096 x 2048 / x 4096 and +5 % at 8192 x 8192 x 1024, no
+    // gain at 4096 x 4096 x 1024, a loss when there are fewer super-tiles than SMs.
+    const long long full_tiles = static_cast<long long>(c.g.M / 64) * (c.g.N / 64);
+    const long long tiles256 = static_cast<long long>((c.g.M + 255) / 256) * (c.g.N / 256);
+    const bool big = c.g.N % 256 == 0 && c.g.end - c.g.start == full_tiles && tiles256 >= static_cast<long long>(ctas) &&
+                     (c.g.K >= 2048 || tiles256 >= 4ll * ctas);
+    if (c.g.batch <= 1 && c.g.splitk <= 1 && (g_opt.tzgemm_m256 > 0 || (g_opt.tzgemm_m256 == 0 && big))) {
+        CUtensorMap ta, tb;
+        if ((rc = make_tmap(&ta, c.A, c.g.M, c.g.K, 256)) != TK_OK) return rc;
+        if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, 256)) != TK_OK) return rc;
+        constexpr int smem = Gemm256Smem::kBytes + 1024;
+        if ((rc = enable_smem(tzgemm256_kernel, smem)) != TK_OK) return rc;
+        tzgemm256_kernel<<<ctas, kGemm256Threads, smem, st>>>(ta, tb, c.g);
+        return launch_error("tzgemm256_kernel launch");
     }
     return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_tzgemm<256>(c, ctas, st)
                                                         : launch_tzgemm<128>(c, ctas, st);

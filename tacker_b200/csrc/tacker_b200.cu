@@ -49,6 +49,7 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "stencil_ring")) return &g_opt.stencil_ring;
     if (!std::strcmp(name, "mix_stencil_ring")) return &g_opt.mix_stencil_ring;
     if (!std::strcmp(name, "l2_hints")) return &g_opt.l2_hints;
+    if (!std::strcmp(name, "tzgemm_m256")) return &g_opt.tzgemm_m256;
     if (!std::strcmp(name, "mix_stencil_cfg")) return &g_opt.mix_stencil_cfg;
     return nullptr;
 }
@@ -938,6 +939,30 @@ TK_API int tk_plan_tzgemm(int M, int N, int bn, int start, int end, int ctas, in
     };
     if (bn == 256) plan(SuperTileWalk<256>());
     else plan(SuperTileWalk<128>());
+    return TK_OK;
+}
+
+// the same for the kernel with 256 x 256 super-tiles
+TK_API int tk_plan_tzgemm_m256(int M, int N, int start, int end, int ctas, int* cover) {
+    if (!cover || M < 128 || N < 64 || M % 128 || N % 64 || ctas < 1) return TK_ERR_ARGS;
+    GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.M = M;
+    g.N = N;
+    g.K = 64;
+    g.start = start;
+    g.end = end;
+    SuperTileWalk256 walk;
+    walk.init(g);
+    const int nt = N / 64;
+    for (int cta = 0; cta < ctas; ++cta)
+        for (int cand = cta; cand < walk.ncand; cand += ctas) {
+            int R, Cc;
+            const uint32_t m = walk.mask(cand, R, Cc);
+            for (int rh = 0; rh < 4; ++rh)
+                for (int cb = 0; cb < 4; ++cb)
+                    if ((m >> (rh * 4 + cb)) & 1u) cover[(4 * R + rh) * nt + 4 * Cc + cb] += 1;
+        }
     return TK_OK;
 }
 

@@ -71,7 +71,25 @@ def test_small_and_ragged_shapes(cuda, oracle, shape, bn):
         ops.set_option("tzgemm_bn", 0)
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (384, 320, 192), (1024, 1024, 1024), (640, 1280, 256)])
+def test_m256_super_tile_kernel(cuda, oracle, shape):
+    """The 256 x 256 super-tile form of the solo kernel: same results as the 128-row form, bit for bit."""
+    from tacker_b200 import ops
+
+    M, N, K = shape
+    a_bits, a, b_bits, b = gemm_inputs(oracle, M, N, K, seed=M + K)
+    out = {}
+    for mode in (-1, 1):
+        ops.set_option("tzgemm_m256", mode)
+        try:
+            out[mode] = _run(cuda, ops, a_bits, b_bits, M, N, K, 1.1, grid=5)
+        finally:
+            ops.set_option("tzgemm_m256", 0)
+    _check(oracle, out[1], a, b, 1.1)
+    assert np.array_equal(out[1], out[-1])
+
+
+@pytest.mark.parametrize("bn", [128, 256, 512])
 @pytest.mark.parametrize("rng", [(0, 1), (5, 6), (3, 17), (7, 8), (0, 24), (23, 24), (9, 9), (11, 40)])
 def test_virtual_block_range_is_exact(cuda, oracle, bn, rng):
     """Tiles outside [start, end) keep the sentinel; tiles inside match (src/gptb_kernel/tzgemm_kernel.cu:243-249)."""
@@ -79,12 +97,17 @@ def test_virtual_block_range_is_exact(cuda, oracle, bn, rng):
 
     M, N, K = 256, 384, 128          # 4 x 6 = 24 tiles of 64 x 64
     start, end = rng
-    ops.set_option("tzgemm_bn", bn)
+    if bn == 512:                    # stands for the 256 x 256 super-tile kernel
+        ops.set_option("tzgemm_m256", 1)
+    else:
+        ops.set_option("tzgemm_bn", bn)
+        ops.set_option("tzgemm_m256", -1)
     try:
         a_bits, a, b_bits, b = gemm_inputs(oracle, M, N, K, seed=9)
         got = _run(cuda, ops, a_bits, b_bits, M, N, K, 1.1, start=start, end=end, grid=2, sentinel=-123.0)
     finally:
         ops.set_option("tzgemm_bn", 0)
+        ops.set_option("tzgemm_m256", 0)
     want = oracle.tzgemm_f64(a, b, alpha=1.1)
     inside = np.zeros((M, N), dtype=bool)
     for p in range(start, min(end, 24)):

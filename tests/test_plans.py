@@ -76,3 +76,19 @@ def test_stencil_split_fills_the_launched_warps(lib):
     assert (split[0], split[1]) == (2, 31)
     assert lib.tk_plan_stencil(64, 0, 1024, 8, 128, 1, 1, _p(planes), None, split) == 0
     assert (split[0], split[1]) == (1, 62)          # one warp: no reason to pay for extra halo planes
+
+
+@pytest.mark.parametrize("shape", [(128, 64), (256, 256), (384, 320), (1024, 1024), (128, 896), (640, 1280)])
+def test_tzgemm_m256_plan_covers_each_tile_of_the_range_exactly_once(lib, shape):
+    M, N = shape
+    tiles = (M // 64) * (N // 64)
+    rng = np.random.default_rng(7 * M + N)
+    ranges = [(0, tiles), (0, 1), (tiles - 1, tiles), (2, 2), (0, tiles + 9)]
+    ranges += [tuple(sorted(rng.integers(0, tiles + 1, 2))) for _ in range(12)]
+    for start, end in ranges:
+        for ctas in (1, 3, 148):
+            cover = np.zeros(tiles, dtype=np.int32)
+            assert lib.tk_plan_tzgemm_m256(M, N, int(start), int(end), ctas, _p(cover)) == 0
+            want = np.zeros(tiles, dtype=np.int32)
+            want[int(start):min(int(end), tiles)] = 1
+            assert np.array_equal(cover, want), (shape, start, end, ctas)
