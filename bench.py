@@ -6,10 +6,11 @@
 
 One "step" = one fused GEMM + stencil pair of the headline configuration: tzgemm
 M = N = 4096, K = 1024 (fp16 in, fp32 out) together with 10 ping-pong Jacobi sweeps of the 7-point
-stencil on a 512 x 512 x 64 fp32 grid, executed as 10 launches of the fused persistent kernel
-(sweep i co-runs with the i-th tenth of the GEMM's 4096 tiles: 1 tensor tile per 2.5 CUDA-core
-blocks).  The same work run unfused (1 tzgemm launch + 10 stencil launches) gives
-`fused_vs_sequential`.  Multi-GPU = independent replicas, one process per GPU, no collective on
+stencil on a 512 x 512 x 64 fp32 grid.  The GEMM's 4096 tiles are fused with the first 10, 2 or 1 of
+the sweeps (each fused launch = one sweep + an equal share of the tiles), the remaining sweeps run
+alone; the three schedules are timed briefly and the best one is the timed step.  The same work
+run unfused (1 tzgemm launch + 10 stencil launches) gives `fused_vs_sequential`; `ratio_sweep` holds
+single fused launches at tensor : CUDA-core tile ratios 1:1 ... 1:8, `pairs` the other two pairs.  Multi-GPU = independent replicas, one process per GPU, no collective on
 the data path (co-location is per GPU).
 
 Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the same pair on
@@ -37,7 +38,7 @@ SOLO_CD_THREADS = 256   # solo stencil: 2 CTAs of 8 warps per SM
 TILES = (M // 64) * (N // 64)
 CD_BLOCKS = (NX // 64) * (NY // 4)
 WORKLOAD = (f"config 2: fused tzgemm {M}x{N}x{K} fp16->fp32 + {SWEEPS} Jacobi sweeps of the 7-point stencil on "
-            f"{NX}x{NY}x{NZ} fp32 (c0=1/6, c1=-1/6, zero boundary), {SWEEPS} fused launches per pair")
+            f"{NX}x{NY}x{NZ} fp32 (c0=1/6, c1=-1/6, zero boundary)")
 METRIC = "fused GEMM+stencil pairs per second (fused vs sequential kernel time in fused_vs_sequential)"
 
 # algorithmic bytes of one fused launch: one sweep (one fp32 read + one fp32 write per cell) plus

@@ -21,9 +21,6 @@ from typing import List, Sequence
 
 from . import LAUNCH_FN, KernelInfo, TackerError, check, lib
 
-SM_NUM_FALLBACK = 148
-
-
 def sm_count() -> int:
     n = C.c_int(0)
     check(lib().tk_sm_count(C.byref(n)), "tk_sm_count")
