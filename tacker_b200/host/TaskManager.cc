@@ -39,6 +39,12 @@ void run_fused(TzLayer* layer, GPTBKernel* cd, int cd_start, int cd_end, stream_
     it->second->execute(stream);
 }
 
+}  // namespace
+
+// the fused kernels cached per (layer, best-effort kernel) refer to both; drop them before either goes away
+void releaseFusedKernels() { g_mix_cache.clear(); }
+
+namespace {
 double now_ms() {
     using namespace std::chrono;
     return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();

@@ -18,6 +18,9 @@ void mixcudnnConvolutionForward(TzLayer* layer, GPTBKernel* gptb_cd_kernel, int 
                                 stream_t stream);
 void mixcublasSgemm(TzLayer* layer, GPTBKernel* gptb_cd_kernel, int cd_start_blk, int cd_end_blk, stream_t stream);
 
+// forget the cached fused kernels (call before destroying the tasks or the best-effort kernels they were built from)
+void releaseFusedKernels();
+
 struct ScheduleResult {
     float lc_solo_ms = 0;        // sum of the profiled solo kernel times
     float lc_colocated_ms = 0;   // LC time of the last scheduling pass
@@ -40,6 +43,7 @@ struct ColocationResult {
 class TaskManager {
 public:
     TaskManager(Task* lc_task, const std::string& be_task1_name, const std::string& be_task2_name);
+    ~TaskManager() { releaseFusedKernels(); }  // they point into lc_task's layers
     // The reference's experiment: profile the LC task kernel by kernel, then walk it under a latency budget and
     // fuse every mixable layer that still has headroom with best-effort blocks.
     //   Tacker: all blocks of the best-effort kernel with every layer;

@@ -98,6 +98,7 @@ int main(int argc, char* argv[]) {
         const unsigned status = be->deviceStatus();
         if (status != 0) logger.WARNING("device status word: " + std::to_string(status));
         recorder.text();
+        releaseFusedKernels();
         lc_task.reset();
         destroyCreatedKernels();
         tzgemmScratch.release();

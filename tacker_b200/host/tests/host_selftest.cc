@@ -321,6 +321,7 @@ int main(int argc, char** argv) {
         CHECK(fake.captures >= 2 && fake.replays > fake.captures);  // LC pass and BE chunks are replayed as graphs
     }
     CHECK(throws([] { logger.ERROR("boom"); }));
+    releaseFusedKernels();
     destroyCreatedKernels();
     tzgemmScratch.release();
     std::printf("host selftest: %d checks, %d failed\n", g_checks, g_failed);
