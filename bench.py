@@ -4,7 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-One "step" = one fused GEMM + stencil pair of the headline configuration: tzgemm
+One "step" = a batch of PAIRS_PER_STEP fused GEMM + stencil pairs of the headline configuration (the graph of
+one pair replayed that many times, so that the timed region is long enough to average): tzgemm
 M = N = 4096, K = 1024 (fp16 in, fp32 out) together with 10 ping-pong Jacobi sweeps of the 7-point
 stencil on a 512 x 512 x 64 fp32 grid.  The GEMM's 4096 tiles are fused with the first 10, 2 or 1 of
 the sweeps (each fused launch = one sweep + an equal share of the tiles), the remaining sweeps run
@@ -14,8 +15,8 @@ single fused launches at tensor : CUDA-core tile ratios 1:1 ... 1:8, `pairs` the
 the data path (co-location is per GPU).
 
 Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the same pair on
-the host cores instead (the reference project has no CPU implementation and its CUDA kernels are
-timed separately, see `ref_gpu` in the default arm's line).
+the host cores instead, one whole pair per step (the reference project has no CPU implementation and its
+CUDA kernels are timed separately, see `ref_gpu` in the default arm's line).
 """
 from __future__ import annotations
 
@@ -33,6 +34,7 @@ sys.path.insert(0, ROOT)
 M, N, K = 4096, 4096, 1024
 NX, NY, NZ, SWEEPS = 512, 512, 64, 10
 C0, C1 = 1.0 / 6.0, -1.0 / 6.0
+PAIRS_PER_STEP = 50     # pairs per timed step (graph replays)
 CD_THREADS = 448        # CUDA-core threads of the fused CTA (14 warps next to the 6 tensor-role warps)
 SOLO_CD_THREADS = 256   # solo stencil: 2 CTAs of 8 warps per SM
 TILES = (M // 64) * (N // 64)
@@ -46,9 +48,8 @@ METRIC = "fused GEMM+stencil pairs per second (fused vs sequential kernel time i
 SWEEP_BYTES = 8 * NX * NY * NZ
 GEMM_BYTES = 2 * (M * K + N * K) + 4 * M * N
 LAUNCH_BYTES = SWEEP_BYTES + GEMM_BYTES / SWEEPS
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
-# profiles/stencil_tma_kernel_config2_ncu.md and profiles/mix_stencil_kernel_config2_ncu.md (caches flushed
-# by ncu before the launch; part of the output is still dirty in L2 when the kernel ends)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from ncu captures of these two kernels on this
+# workload (caches flushed by ncu before the launch; part of the output is still dirty in L2 when the kernel ends)
 NCU_TRAFFIC_BYTES = {"stencil_tma_kernel": 94.05e6, "mix_stencil_kernel": 108.3e6}
 
 
@@ -130,17 +131,15 @@ def cpu_pair_setup():
     return oracle, np, a.reshape(M, K), b.reshape(N, K), grid
 
 
-def cpu_pair_sample(state, tile_frac=4, sweeps=5):
-    """Times 1/tile_frac of the GEMM's tiles and `sweeps` of the 10 sweeps; returns seconds per full pair."""
+def cpu_pair(state):
+    """One whole pair (all 4096 GEMM tiles, all 10 sweeps) on the host cores; returns seconds."""
     oracle, np, a, b, grid = state
     out = np.zeros((M, N), dtype=np.float32)
     x, y = grid.copy(), grid.copy()
     t0 = time.perf_counter()
-    oracle.tzgemm_f32(a, b, alpha=1.0, start=0, end=TILES // tile_frac, out=out)
-    t1 = time.perf_counter()
-    oracle.stencil_jacobi_f32(np.float32(C0), np.float32(C1), x, y, sweeps, contract=1)
-    t2 = time.perf_counter()
-    return (t1 - t0) * tile_frac + (t2 - t1) * (SWEEPS / sweeps)
+    oracle.tzgemm_f32(a, b, alpha=1.0, start=0, end=TILES, out=out)
+    oracle.stencil_jacobi_f32(np.float32(C0), np.float32(C1), x, y, SWEEPS, contract=1)
+    return time.perf_counter() - t0
 
 
 def run_reference(args):
@@ -151,16 +150,18 @@ def run_reference(args):
     oracle = state[0]
     cores = oracle.set_threads(os.cpu_count() or 1)
     for _ in range(args.warmup):
-        cpu_pair_sample(state)
-    t = [cpu_pair_sample(state) for _ in range(args.steps)]
+        cpu_pair(state)
+    t = [cpu_pair(state) for _ in range(args.steps)]
     sec = sum(t) / len(t)
-    sample = "per step: 1/4 of the GEMM's 64x64 tiles + 5 of the 10 sweeps, time scaled to the full pair"
+    sample = ("per step: ONE whole pair (all 4096 GEMM tiles + all 10 sweeps), measured, nothing scaled; the GPU arm's "
+              f"step is a batch of {PAIRS_PER_STEP} such pairs, so compare `value` (pairs/s), not ms_per_step")
     line = {
         "impl": "reference", "metric": METRIC, "value": 1.0 / sec, "unit": "pairs/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 inputs, f32 accumulate / f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "arm": "CPU restatement of the pair (the reference has no CPU code; "
-                                                 "oracle/tacker_oracle.c, OpenMP, scalar binary32)"},
+        "config": {"workload": WORKLOAD, "pairs_per_step": 1,
+                   "arm": "CPU restatement of the pair (the reference has no CPU code; oracle/tacker_oracle.c, OpenMP, "
+                          "scalar binary32)"},
         "cpu_baseline": {"value": 1.0 / sec, "unit": "pairs/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": 1.0 / sec, "unit": "pairs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -273,13 +274,21 @@ def run_ours(args):
     # pick the fused schedule (each candidate timed briefly; every rank picks the same one)
     cands = {}
     for f in (SWEEPS, 2, 1):
-        cands[f] = timed(runner(schedule(f)), 10 if not args.quick else 2, 3)
+        cands[f] = timed(runner(schedule(f)), 50 if not args.quick else 2, 3)
     best = min(cands, key=cands.get) if args.fuse_sweeps == 0 else args.fuse_sweeps
     fused_kernels = schedule(best)
     fused_fn = runner(fused_kernels)
     seq_fn = runner(sequential)
-    ms_fused = timed(fused_fn, args.steps, warm)
-    ms_seq = timed(seq_fn, args.steps, warm)
+
+    def batch(fn):
+        def step():
+            for _ in range(PAIRS_PER_STEP):
+                fn()
+        return step
+
+    ms_step = timed(batch(fused_fn), args.steps, warm)          # the timed region: K steps of PAIRS_PER_STEP pairs
+    ms_fused = ms_step / PAIRS_PER_STEP
+    ms_seq = timed(batch(seq_fn), max(1, args.steps // 4), 1) / PAIRS_PER_STEP
     # continuation of the same fused loop, only to give the 20 ms clock sampler enough samples
     t_end = time.time() + args.sustain_ms / 1e3
     with torch.cuda.stream(stream):
@@ -300,18 +309,24 @@ def run_ours(args):
                                    for i in range(2)]) / 2
     sweep = []
     if not args.quick:
+        def point(label, nt, f, w):
+            t_gs = t_of([tz_kernel(0, nt)])
+            s_ = t_gs + us_sweep
+            sweep.append({"tensor_to_cd_tiles": label, "gemm_tiles": nt, "cd_blocks": CD_BLOCKS, "cd_threads": w,
+                          "fused_us": round(f, 2), "sequential_us": round(s_, 2), "ratio": round(f / s_, 4),
+                          "attainable": round(max(t_gs, us_sweep) / s_, 4)})
+
         for r in (1, 2, 3, 4, 5, 6, 7, 8):
             nt = CD_BLOCKS // r  # GEMM tiles co-run with one sweep's 1024 CUDA-core blocks: 1 : r
-            f = t_of([ops.mix(cd_kernel(i), tz_kernel(), cd_threads=CD_THREADS, grid=sms, tz_range=(0, nt))
-                      for i in range(2)]) / 2
-            s_ = t_of([tz_kernel(0, nt)]) + us_sweep
-            sweep.append({"tensor_to_cd_tiles": f"1:{r}", "gemm_tiles": nt, "cd_blocks": CD_BLOCKS,
-                          "fused_us": round(f, 2), "sequential_us": round(s_, 2), "ratio": round(f / s_, 4)})
+            best_w = None
+            for w in (320, 448, 576):  # the other half of the ratio: CUDA-core threads next to the 192 tensor-role ones
+                f = t_of([ops.mix(cd_kernel(i), tz_kernel(), cd_threads=w, grid=sms, tz_range=(0, nt))
+                          for i in range(2)]) / 2
+                if best_w is None or f < best_w[0]:
+                    best_w = (f, w)
+            point(f"1:{r}", nt, best_w[0], best_w[1])
         for nt in (2048, 4096):
-            s_ = t_of([tz_kernel(0, nt)]) + us_sweep
-            f = us_fused_launch[TILES // nt]
-            sweep.append({"tensor_to_cd_tiles": f"{nt // CD_BLOCKS}:1", "gemm_tiles": nt, "cd_blocks": CD_BLOCKS,
-                          "fused_us": round(f, 2), "sequential_us": round(s_, 2), "ratio": round(f / s_, 4)})
+            point(f"{nt // CD_BLOCKS}:1", nt, us_fused_launch[TILES // nt], CD_THREADS)
 
     # ---- the other two pairs (configs 3 and 4): fused vs sequential on identical work ----
     pairs = None
@@ -331,10 +346,27 @@ def run_ours(args):
                                      hA0.data_ptr(), hOut.data_ptr(), NX, NY, NZ, SWEEPS, CD_THREADS, ws.data_ptr(),
                                      ws_bytes, st)
 
-    e2e_steps = max(3, min(args.steps, 20))
-    ms_e2e = timed(e2e_step, e2e_steps, 3)
+    e2e_pairs = 20 if not args.quick else 3
+    ms_e2e = timed(e2e_step, e2e_pairs, 3)
     h2d = hA.numel() * 2 + hB.numel() * 2 + hA0.numel() * 4
     d2h = hC.numel() * 4 + hOut.numel() * 4
+
+    # the ceiling of that call: the same bytes as plain cudaMemcpyAsync, both directions at once, no kernels
+    up_stream = torch.cuda.Stream()
+    dA, dB, dG, dC, dO = (torch.empty_like(t, device="cuda") for t in (hA, hB, hA0, hC, hOut))
+
+    def copy_only():
+        up_stream.wait_stream(stream)
+        with torch.cuda.stream(up_stream):
+            dA.copy_(hA, non_blocking=True)
+            dB.copy_(hB, non_blocking=True)
+            dG.copy_(hA0, non_blocking=True)
+        hOut.copy_(dO, non_blocking=True)
+        hC.copy_(dC, non_blocking=True)
+        stream.wait_stream(up_stream)
+
+    ms_copy = timed(copy_only, e2e_pairs, 3)
+    del dA, dB, dG, dC, dO
     clocks = sampler.stop()
 
     # ---- the reference's own fused kernel, recompiled for sm_100 (when the test build travelled) ----
@@ -386,10 +418,11 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.quick:
         state = cpu_pair_setup()
         cores = state[0].set_threads(os.cpu_count() or 1)
-        cpu_pair_sample(state)
-        sec = min(cpu_pair_sample(state) for _ in range(2))
+        cpu_pair(state)
+        secs = [cpu_pair(state) for _ in range(5)]
+        sec = sum(secs) / len(secs)
         cpu = {"value": 1.0 / sec, "unit": "pairs/s", "cores": cores, "kind": "port",
-               "sample": "1/4 of the GEMM's tiles + 5 of the 10 sweeps, scaled to one pair; best of 2"}
+               "sample": "5 whole pairs (all GEMM tiles + 10 sweeps each) after one warm-up pair, mean; nothing scaled"}
 
     if rank != 0:
         rep.close()
@@ -413,32 +446,80 @@ def run_ours(args):
                  "tensor_frac_solo_gemm": round(2.0 * M * N * K / (us_gemm * 1e-6) / 1e12 / tflops, 4)})
     line = {
         "metric": METRIC, "value": world * 1e3 / ms_fused, "unit": "pairs/s", "n_gpus": world, "steps": args.steps,
-        "warmup": warm, "ms_per_step": ms_fused, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": warm, "ms_per_step": ms_step, "ms_per_pair": ms_fused, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16 inputs, f32 accumulate (tensor role) / f32 (CUDA-core role)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "cd_threads": CD_THREADS, "grid": sms, "replicas": world,
+        "config": {"workload": WORKLOAD, "pairs_per_step": PAIRS_PER_STEP, "cd_threads": CD_THREADS, "grid": sms,
+                   "replicas": world, "colocation_seconds": args.colocate_s,
                    "schedule": f"{best} fused launches (sweep + {TILES // best} GEMM tiles each) + {SWEEPS - best} solo sweeps",
                    "l2": "inputs 80 MiB (GEMM) + 128 MiB (grids) exceed the 126 MB L2; no flush between steps",
                    "launch": "CUDA graph of the step's launches" if not args.no_graph else "stream launches"},
-        "fused_vs_sequential": ms_fused / ms_seq, "sequential_ms_per_step": ms_seq,
+        "fused_vs_sequential": ms_fused / ms_seq, "sequential_ms_per_pair": ms_seq,
+        "attainable": max(us_gemm, SWEEPS * us_sweep) / (us_gemm + SWEEPS * us_sweep),
         "schedules_ms_per_pair": {f"{f}_fused_launches": round(v, 4) for f, v in cands.items()},
         "solo_us": {"tzgemm_4096x4096x1024": round(us_gemm, 2), "stencil_sweep": round(us_sweep, 2),
                     "tzgemm_tflops": round(2.0 * M * N * K / (us_gemm * 1e-6) / 1e12, 1),
                     "stencil_gbs": round(SWEEP_BYTES / (us_sweep * 1e-6) / 1e9, 1),
                     "fused_launch_us": {f"sweep+{TILES // f}_tiles": round(v, 2) for f, v in us_fused_launch.items()}},
         "ratio_sweep": sweep, "pairs": pairs, "clocks": clocks,
-        "e2e": {"value": world * 1e3 / ms_e2e, "unit": "pairs/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e, "steps": e2e_steps,
+        "e2e": {"value": world * 1e3 / ms_e2e, "unit": "pairs/s", "h2d_bytes_per_step": h2d * PAIRS_PER_STEP,
+                "d2h_bytes_per_step": d2h * PAIRS_PER_STEP, "h2d_bytes_per_pair": h2d, "d2h_bytes_per_pair": d2h,
+                "ms_per_pair": ms_e2e, "pairs_timed": e2e_pairs,
+                "copy_ceiling_ms_per_pair": ms_copy, "frac_of_copy_ceiling": ms_copy / ms_e2e,
+                "copy_ceiling": "the pair's 84 MB up and 134 MB down as plain cudaMemcpyAsync from/to the same pinned "
+                                "buffers on two streams, no kernels, all ranks at once (max over ranks)",
                 "call": "tk_pair_tzgemm_stencil_host (pinned host buffers in and out)"},
-        "gpu_launches": args.steps * len(fused_kernels),
+        "gpu_launches": args.steps * PAIRS_PER_STEP * len(fused_kernels),
         "roofline": roof, "cpu_baseline": cpu, "ref_gpu": ref_gpu, "colocation": coloc, "device_status": status,
     }
     print(json.dumps(line), flush=True)
     rep.close()
 
 
+def balanced_quantum(t_of, make_cd, total_blocks, t_gemm, t_cd_full):
+    """Blocks of CUDA-core work whose solo time is within [0.8, 1.25] of the GEMM's, found by measurement."""
+    nb = max(1, min(total_blocks, int(round(total_blocks * t_gemm / t_cd_full))))
+    t = t_of([make_cd(0, nb)], 10)
+    for _ in range(3):
+        if 0.9 <= t / t_gemm <= 1.1:
+            break
+        nb2 = max(1, min(total_blocks, int(round(nb * t_gemm / t))))
+        if nb2 == nb:
+            break
+        nb = nb2
+        t = t_of([make_cd(0, nb)], 10)
+    return nb, t
+
+
+def pair_report(ops, sms, t_of, tz, make_cd, total_blocks, cd_name, w_sweep):
+    """One GEMM + CUDA-core pair: as stated (whole kernels) and balanced in time, fused vs the two solo launches.
+
+    `attainable` = max(a, b) / (a + b): what perfect overlap of the two solo kernels would give.  The fused launch is
+    timed for every CUDA-core thread count in `w_sweep` (the other half of the tensor : CUDA-core ratio)."""
+    t_g, t_c = t_of([tz()], 10), t_of([make_cd()], 5)
+    full = {}
+    for w in w_sweep:
+        full[w] = t_of([ops.mix(make_cd(), tz(), cd_threads=w, grid=sms)], 5)
+    wb = min(full, key=full.get)
+    nb, t_cb = balanced_quantum(t_of, make_cd, total_blocks, t_g, t_c)
+    bal = {}
+    for w in w_sweep:
+        bal[w] = t_of([ops.mix(make_cd(0, nb), tz(), cd_threads=w, grid=sms)], 10)
+    wbb = min(bal, key=bal.get)
+    return {
+        "gemm_us": round(t_g, 1), f"{cd_name}_us": round(t_c, 1), "fused_us": round(full[wb], 1), "cd_threads": wb,
+        "fused_vs_sequential": round(full[wb] / (t_g + t_c), 4), "attainable": round(max(t_g, t_c) / (t_g + t_c), 4),
+        "fused_us_by_cd_threads": {str(w): round(v, 1) for w, v in full.items()},
+        "balanced": {f"{cd_name}_blocks": nb, f"{cd_name}_us": round(t_cb, 1), "cd_over_gemm": round(t_cb / t_g, 3),
+                     "fused_us": round(bal[wbb], 1), "cd_threads": wbb,
+                     "fused_vs_sequential": round(bal[wbb] / (t_g + t_cb), 4),
+                     "attainable": round(max(t_g, t_cb) / (t_g + t_cb), 4),
+                     "fused_us_by_cd_threads": {str(w): round(v, 1) for w, v in bal.items()}}}
+
+
 def other_pairs(torch, ops, sms, gen, t_of, st):
     """Configs 3 and 4: GEMM + Coulomb (compute-bound CUDA-core pair), GEMM + MRI-Q (SFU-bound pair)."""
     out = {}
+    w_sweep = (320, 576, 832)
 
     def gemm(m, n, k):
         a = (torch.rand(m, k, device="cuda", generator=gen) * 2 - 1).half()
@@ -454,22 +535,13 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
     packed = torch.empty_like(atoms)
     lat = torch.zeros(512, 512, device="cuda")
     ops.cp_pack_atoms(atoms.data_ptr(), 8192, 32.0, packed.data_ptr(), st)
-    cp = lambda s=0, e=None, grid=None, block=256: ops.gptb_cp(8192, 0.125, lat.data_ptr(), packed.data_ptr(), 512, 512,
-                                                               start=s, end=e, grid=grid or sms * 2, block=block)
-    try:
-        t_g, t_c = t_of([tz()], 10), t_of([cp()], 3)
-        t_f = t_of([ops.mix(cp(), tz(), cd_threads=832, grid=sms)], 3)
-        nb = max(8, int(round(256 * t_g / t_c)))           # blocks of Coulomb work worth one GEMM
-        t_cb = t_of([cp(0, nb)], 5)
-        t_fb = t_of([ops.mix(cp(0, nb), tz(), cd_threads=832, grid=sms)], 5)
-    finally:
-        pass
-    pairs3 = 8192.0 * 512 * 512
-    out["config3_gemm2048_coulomb"] = {
-        "gemm_us": round(t_g, 1), "coulomb_us": round(t_c, 1), "fused_us": round(t_f, 1),
-        "fused_vs_sequential": round(t_f / (t_g + t_c), 4), "coulomb_gpairs_per_s": round(pairs3 / t_c / 1e3, 1),
-        "balanced": {"coulomb_blocks": nb, "coulomb_us": round(t_cb, 1), "fused_us": round(t_fb, 1),
-                     "fused_vs_sequential": round(t_fb / (t_g + t_cb), 4)}}
+    ops.set_option("cp_ppt", 8)
+    cp = lambda s=0, e=None: ops.gptb_cp(8192, 0.125, lat.data_ptr(), packed.data_ptr(), 512, 512, start=s, end=e,
+                                         grid=sms * 2, block=512)
+    r = pair_report(ops, sms, t_of, tz, cp, 256, "coulomb", w_sweep)
+    r["coulomb_gpairs_per_s"] = round(8192.0 * 512 * 512 / r["coulomb_us"] / 1e3, 1)
+    r["coulomb_frac_of_rsqrt_bound"] = round(8192.0 * 512 * 512 / (sms * 16 * 1.965e9) / (r["coulomb_us"] * 1e-6), 3)
+    out["config3_gemm2048_coulomb"] = r
 
     # config 4: GEMM 4096 x 4096 x 2048 + MRI-Q 2048 samples x 262144 voxels
     tz4, keep4 = gemm(4096, 4096, 2048)
@@ -478,20 +550,12 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
     kv[:, 3] = torch.rand(numK, device="cuda", generator=gen)
     xyz = [torch.rand(numX, device="cuda", generator=gen) * 64 - 32 for _ in range(3)]
     qr, qi = torch.zeros(numX, device="cuda"), torch.zeros(numX, device="cuda")
-    mq = lambda s=0, e=None, grid=None, block=256: ops.gptb_mriq(numK, xyz[0].data_ptr(), xyz[1].data_ptr(),
-                                                                 xyz[2].data_ptr(), qr.data_ptr(), qi.data_ptr(),
-                                                                 kv.data_ptr(), numX, start=s, end=e, grid=grid or sms * 4,
-                                                                 block=block)
-    t_g, t_m = t_of([tz4()], 10), t_of([mq()], 3)
-    t_f = t_of([ops.mix(mq(), tz4(), cd_threads=704, grid=sms)], 3)
-    nb = max(148, int(round(1024 * t_g / t_m)))
-    t_mb = t_of([mq(0, nb)], 5)
-    t_fb = t_of([ops.mix(mq(0, nb), tz4(), cd_threads=704, grid=sms)], 5)
-    out["config4_gemm4096x2048_mriq"] = {
-        "gemm_us": round(t_g, 1), "mriq_us": round(t_m, 1), "fused_us": round(t_f, 1),
-        "fused_vs_sequential": round(t_f / (t_g + t_m), 4), "mriq_gpairs_per_s": round(numK * numX / t_m / 1e3, 1),
-        "balanced": {"mriq_blocks": nb, "mriq_us": round(t_mb, 1), "fused_us": round(t_fb, 1),
-                     "fused_vs_sequential": round(t_fb / (t_g + t_mb), 4)}}
+    mq = lambda s=0, e=None: ops.gptb_mriq(numK, xyz[0].data_ptr(), xyz[1].data_ptr(), xyz[2].data_ptr(), qr.data_ptr(),
+                                           qi.data_ptr(), kv.data_ptr(), numX, start=s, end=e, grid=sms * 2, block=512)
+    r = pair_report(ops, sms, t_of, tz4, mq, 1024, "mriq", w_sweep)
+    r["mriq_gpairs_per_s"] = round(numK * numX / r["mriq_us"] / 1e3, 1)
+    r["mriq_frac_of_sfu_bound"] = round(2.0 * numK * numX / (sms * 16 * 1.965e9) / (r["mriq_us"] * 1e-6), 3)
+    out["config4_gemm4096x2048_mriq"] = r
     del keep3, keep4
     return out
 
@@ -499,20 +563,20 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-graph", action="store_true", help="launch the 10 kernels of a step one by one")
     ap.add_argument("--quick", action="store_true", help="skip the ratio sweep, the CPU sample and the reference kernels")
     ap.add_argument("--sustain-ms", type=float, default=400.0)
-    ap.add_argument("--colocate-s", type=float, default=5.0, help="seconds of the LC/BE co-location run (0 = skip)")
+    ap.add_argument("--colocate-s", type=float, default=60.0, help="seconds of the LC/BE co-location run (0 = skip)")
     ap.add_argument("--only-pairs", action="store_true", help="run only the Coulomb and MRI-Q pairs and print them")
     ap.add_argument("--fuse-sweeps", type=int, default=0, choices=(0, 1, 2, 10),
                     help="how many sweeps are fused with the GEMM (0 = time 10, 2 and 1 briefly and take the best)")
     args = ap.parse_args()
     if args.impl == "reference":
-        if args.steps == 200:
-            args.steps = 10
+        if args.steps == 40 and args.warmup == 5:
+            args.steps, args.warmup = 10, 2
         run_reference(args)
     else:
         run_ours(args)

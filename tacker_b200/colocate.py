@@ -10,6 +10,7 @@ import json
 import os
 import subprocess
 import sys
+import tempfile
 
 from . import _build
 
@@ -22,16 +23,21 @@ def run(gpus: int, seconds: float, qps: float, qos: float, lc: str = "vgg16", be
         raise RuntimeError(f"{exe} is missing: build it with `python -m tacker_b200._build`")
     devices = list(range(gpus)) if devices is None else list(devices)
     procs = []
+    workdir = tempfile.mkdtemp(prefix="aker_colocate_")  # the children's working directory (they write nothing)
     for d in devices:
         cmd = [exe, "-s", "aker", "-m", lc, "-d", str(d), "-c", os.path.join(HOST, "config"), "--colocate",
                str(seconds), "--qps", str(qps), "--qos", str(qos), "--be", be]
-        procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd="/tmp"))
+        procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd=workdir))
     per_gpu = []
     for d, p in zip(devices, procs):
         out, err = p.communicate(timeout=seconds * 3 + 300)
         if p.returncode != 0:
             raise RuntimeError(f"aker on device {d} failed: {err[-500:]}")
         per_gpu.append(json.loads([l for l in out.splitlines() if l.startswith("{")][-1]))
+    try:
+        os.rmdir(workdir)
+    except OSError:
+        pass
     return {
         "gpus": len(devices), "lc": lc, "be": be, "qps_offered_per_gpu": qps, "seconds": seconds,
         "be_qps_total": sum(r["be_qps"] for r in per_gpu),

@@ -1,13 +1,12 @@
 // CUDA-core roles: 7-point stencil, Coulomb direct summation, MRI-Q Fourier sum.
 //
-// Each role is a device function over a group of `nthreads` threads (a whole CTA for the solo
-// persistent kernels, the upper warps of a CTA in a fused kernel).  `tid` is the thread's
-// index inside the role (the reference's `threadIdx.x - thread_base`), `cta`/`ncta` give the
-// persistent-block stride: role instance `cta` handles virtual blocks start+cta, start+cta+ncta,
-// ... below `end`, i.e. the reference's GPTB loop
-// (src/gptb_kernel/stencil_kernel.cu:6-16: block_pos = blockIdx.x + start; += step; >= end -> return).
-// None of the roles needs shared memory or a CTA-wide barrier: neighbours are exchanged with warp
-// shuffles and the small read-only tables (atoms, k-space samples) are fetched with warp-uniform
+// Each role is a device function over the warps of a group (a whole CTA for the solo persistent kernels,
+// the upper warps of a CTA in a fused kernel); `cta`/`ncta` give the persistent-block stride of the
+// reference's GPTB loop (src/gptb_kernel/stencil_kernel.cu:6-16: block_pos = blockIdx.x + start; += step;
+// >= end -> return) over the virtual blocks [start, end).  The stencil role deals its work items statically
+// (`tid` is the thread's index inside the role, the reference's `threadIdx.x - thread_base`); the Coulomb and
+// MRI-Q roles claim theirs from a per-CTA counter.  No role needs a CTA-wide barrier: neighbours are exchanged
+// with warp shuffles and the small read-only tables (atoms, k-space samples) are fetched with warp-uniform
 // 128-bit loads that the L1 serves as broadcasts.
 #pragma once
 #include <cuda_runtime.h>
@@ -188,19 +187,55 @@ __device__ __forceinline__ void stencil_role(const StencilArgs s, const int tid,
 }
 
 // =====================================================================================
+// Work dealing for the Coulomb and MRI-Q roles.  The items of a launch are dealt CTA-first (CTA c owns
+// items c, c + ncta, ...), and the warps of a role take the next item of their own CTA from a counter in
+// shared memory.  Every SM therefore gets the same number of items whatever the warp count of the role is
+// (a fused CTA has fewer CUDA-core warps than a solo one), and inside the SM a warp that finishes early
+// simply takes more: no whole "rounds" of items, no global counter to reset between launches.
+// The counter must be zero when the first warp of the role calls claim_item.
+// =====================================================================================
+__device__ __forceinline__ long long claim_item(int* counter, const int lane, const int cta, const int ncta) {
+    int i = 0;
+    if (lane == 0) i = atomicAdd(counter, 1);
+    i = __shfl_sync(0xffffffffu, i, 0);
+    return static_cast<long long>(i) * ncta + cta;
+}
+
+__device__ __forceinline__ void red_add_f32(float* addr, float v) {
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+
+// Host-side choice of the second dimension of the items (atoms or k-space samples per item): enough items
+// for about `kItemsPerWarp` per launched warp, never below `granule` table entries.  0 = do not split.
+constexpr int kItemsPerWarp = 8;
+__host__ __device__ inline int cd_pick_split(long long tiles, long long warps, int table_len, int granule) {
+    if (tiles <= 0 || warps <= 0 || table_len <= granule) return 0;
+    const long long want = (kItemsPerWarp * warps + tiles - 1) / tiles;  // pieces per tile
+    if (want <= 1) return 0;
+    long long per = (table_len + want - 1) / want;
+    per = (per + granule - 1) / granule * granule;
+    if (per < granule) per = granule;
+    return per >= table_len ? 0 : static_cast<int>(per);
+}
+
+// =====================================================================================
 // Coulomb potential on a lattice slice (reference: src/ori_kernel/cp_kernel.cu:26-79,
 //   src/gptb_kernel/cp_kernel.cu:8-96).  Virtual block p = lattice patch of 128 x 8 points at
 //   (p % gx, (p / gx) % gy); reference thread (tx, ty) of 16 x 8 owns the eight points
 //   x = 128 bx + tx + 16 u, y = 8 by + ty and adds sum_a q_a / sqrt(dx^2 + dy^2 + dz_a^2) to them,
 //   with dx_1 = x*h - ax and dx_{u+1} = dx_u + 16 h.
 // The reference keeps the atoms in a 64-entry __constant__ array and launches once per 64 atoms;
-// here the packed atoms {x, y, dz^2, q} sit in global memory, any count, and the per-point sum is
-// still folded into the lattice every 64 atoms (same two-level summation order).
+// here the packed atoms {x, y, dz^2, q} sit in global memory, any count.
 // Work item = one warp = two rows of a patch (PPT = 8 points per thread), or a half / quarter of
-// the u range of those rows (PPT = 4 / 2) for finer load balance; the dx chain always starts at
+// the u range of those rows (PPT = 4 / 2), times a range of the atom list; the dx chain always starts at
 // u = 0 so every variant rounds exactly like the reference.
-// EXACT: IEEE 1/sqrt as in the reference (bit-exact against the binary32 restatement);
-// otherwise the hardware reciprocal square root (2 ulp).
+//   atoms_per_item == 0: an item walks the whole list and folds the per-point sum into the lattice every
+//     64 atoms with a rounded `+=` -- the reference's two-level summation order, deterministic, and with
+//     EXACT bit-identical to the binary32 restatement;
+//   atoms_per_item  > 0 (a multiple of 64; fast mode only): an item covers that many atoms and adds its
+//     partial sum to the lattice with one reduction per point.  Items are then small enough to balance
+//     a short quantum over all SMs; the order of the reductions, and with it the last bits, is not fixed.
+// EXACT: IEEE 1/sqrt as in the reference; otherwise the hardware reciprocal square root (2 ulp).
 // =====================================================================================
 struct CpArgs {
     int numatoms;
@@ -209,6 +244,7 @@ struct CpArgs {
     const float4* atoms;  // packed {x, y, dz^2, q}
     int gx, gy;
     int start, end;
+    int atoms_per_item;   // chosen by the host, see above
 };
 
 constexpr int kCpChunk = 64;  // atoms per `+=` into the lattice (reference MAXATOMS, src/header/cp_header.h:5)
@@ -221,22 +257,52 @@ __device__ __forceinline__ float cp_rsqrt(float x) {
     return y;
 }
 
+// e[u] += q / r for the PPT points of this thread and atoms [a0, a1)
 template <int PPT, bool EXACT>
-__device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int nthreads, const int cta,
+__device__ __forceinline__ void cp_accumulate(const float4* __restrict__ atoms, const int a0, const int a1,
+                                              const float spacing, const float spacing_u, const float xf,
+                                              const float yf, const int part, float (&e)[PPT]) {
+#pragma unroll 4
+    for (int i = a0; i < a1; ++i) {
+        const float4 at = __ldg(atoms + i);
+        // spacing * index - coordinate as the single fma nvcc makes of the reference's expression
+        const float dy = __fmaf_rn(spacing, yf, -at.y);
+        const float dyz2 = __fmaf_rn(dy, dy, at.z);
+        float dx = __fmaf_rn(spacing, xf, -at.x);
+#pragma unroll
+        for (int u = 0; u < PPT * part; ++u) dx = __fadd_rn(dx, spacing_u);
+#pragma unroll
+        for (int u = 0; u < PPT; ++u) {
+            const float r2 = __fmaf_rn(dx, dx, dyz2);
+            float inv;
+            if (EXACT) inv = __fdiv_rn(1.0f, __fsqrt_rn(r2));
+            else inv = cp_rsqrt(r2);
+            e[u] = __fmaf_rn(at.w, inv, e[u]);
+            dx = __fadd_rn(dx, spacing_u);
+        }
+    }
+}
+
+// All warps of the role call this with the role's shared counter (zeroed before the first call).
+template <int PPT, bool EXACT>
+__device__ __forceinline__ void cp_role(const CpArgs a, int* counter, const int lane, const int cta,
                                         const int ncta) {
     constexpr int kParts = 8 / PPT;
-    constexpr int kItemsPerBlock = 4 * kParts;
-    const int nwarp = nthreads >> 5, warp = tid >> 5, lane = tid & 31;
+    constexpr int kTilesPerBlock = 4 * kParts;
     const int tx = lane & 15, tyl = lane >> 4;
-    const long long nitems = static_cast<long long>(a.end - a.start) * kItemsPerBlock;
+    const bool split = !EXACT && a.atoms_per_item > 0 && a.atoms_per_item < a.numatoms;
+    const int per = split ? a.atoms_per_item : a.numatoms;
+    const int nchunks = split ? (a.numatoms + per - 1) / per : 1;
+    const long long nitems = static_cast<long long>(a.end - a.start) * kTilesPerBlock * nchunks;
     const int pitch = a.gx * 128;
     const float spacing_u = a.spacing * 16.0f;
 
-    // items are dealt CTA-first so that a short job spreads over all SMs
-    for (long long item = static_cast<long long>(warp) * ncta + cta; item < nitems;
-         item += static_cast<long long>(nwarp) * ncta) {
-        const int p = a.start + static_cast<int>(item / kItemsPerBlock);
-        const int sub = static_cast<int>(item % kItemsPerBlock);
+    for (long long item = claim_item(counter, lane, cta, ncta); item < nitems;
+         item = claim_item(counter, lane, cta, ncta)) {
+        const int chunk = static_cast<int>(item % nchunks);
+        const long long tile = item / nchunks;
+        const int p = a.start + static_cast<int>(tile / kTilesPerBlock);
+        const int sub = static_cast<int>(tile % kTilesPerBlock);
         const int wq = sub / kParts, part = sub % kParts;
         const int bx = p % a.gx, by = (p / a.gx) % a.gy;
         const unsigned xi = static_cast<unsigned>(bx * 128 + tx);
@@ -244,40 +310,32 @@ __device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int
         const float yf = static_cast<float>(yi), xf = static_cast<float>(xi);
         float* out = a.lattice + static_cast<size_t>(pitch) * yi + xi + 16 * PPT * part;
 
-        // running potential of this thread's points: starts from what the lattice holds and gets one
-        // rounded addition per 64-atom chunk, exactly the sequence of `+=` the reference's launches make
-        float acc[PPT];
-#pragma unroll
-        for (int u = 0; u < PPT; ++u) acc[u] = out[16 * u];
-        for (int a0 = 0; a0 < a.numatoms; a0 += kCpChunk) {
-            const int a1 = min(a0 + kCpChunk, a.numatoms);
+        if (split) {
             float e[PPT];
 #pragma unroll
             for (int u = 0; u < PPT; ++u) e[u] = 0.0f;
-#pragma unroll 4
-            for (int i = a0; i < a1; ++i) {
-                const float4 at = __ldg(a.atoms + i);
-                // spacing * index - coordinate as the single fma nvcc makes of the reference's expression
-                const float dy = __fmaf_rn(a.spacing, yf, -at.y);
-                const float dyz2 = __fmaf_rn(dy, dy, at.z);
-                float dx = __fmaf_rn(a.spacing, xf, -at.x);
+            const int a0 = chunk * per;
+            cp_accumulate<PPT, false>(a.atoms, a0, min(a0 + per, a.numatoms), a.spacing, spacing_u, xf, yf, part, e);
 #pragma unroll
-                for (int u = 0; u < PPT * part; ++u) dx = __fadd_rn(dx, spacing_u);
+            for (int u = 0; u < PPT; ++u) red_add_f32(out + 16 * u, e[u]);
+        } else {
+            // running potential of this thread's points: starts from what the lattice holds and gets one
+            // rounded addition per 64-atom chunk, exactly the sequence of `+=` the reference's launches make
+            float acc[PPT];
 #pragma unroll
-                for (int u = 0; u < PPT; ++u) {
-                    const float r2 = __fmaf_rn(dx, dx, dyz2);
-                    float inv;
-                    if (EXACT) inv = __fdiv_rn(1.0f, __fsqrt_rn(r2));
-                    else inv = cp_rsqrt(r2);
-                    e[u] = __fmaf_rn(at.w, inv, e[u]);
-                    dx = __fadd_rn(dx, spacing_u);
-                }
+            for (int u = 0; u < PPT; ++u) acc[u] = out[16 * u];
+            for (int a0 = 0; a0 < a.numatoms; a0 += kCpChunk) {
+                float e[PPT];
+#pragma unroll
+                for (int u = 0; u < PPT; ++u) e[u] = 0.0f;
+                cp_accumulate<PPT, EXACT>(a.atoms, a0, min(a0 + kCpChunk, a.numatoms), a.spacing, spacing_u, xf, yf,
+                                          part, e);
+#pragma unroll
+                for (int u = 0; u < PPT; ++u) acc[u] = __fadd_rn(acc[u], e[u]);
             }
 #pragma unroll
-            for (int u = 0; u < PPT; ++u) acc[u] = __fadd_rn(acc[u], e[u]);
+            for (int u = 0; u < PPT; ++u) out[16 * u] = acc[u];
         }
-#pragma unroll
-        for (int u = 0; u < PPT; ++u) out[16 * u] = acc[u];
     }
 }
 
@@ -287,7 +345,9 @@ __device__ __forceinline__ void cp_role(const CpArgs a, const int tid, const int
 //   argument formed in binary32 as 2pi_f32 * fma(Kz, z, fma(Kx, x, Ky * y)).
 // Virtual block p = 256 consecutive voxels ((p % gx) * 256 ...).  The reference streams the
 // samples through a 1024-entry __constant__ array; here they are read from global memory, any
-// count, in one launch.  Work item = one warp = 64 voxels (two per thread).
+// count, in one launch.  Work item = one warp = 64 voxels (two per thread) times a range of the samples:
+//   k_per_item == 0: all samples, running sum starting from Q as in the reference (deterministic);
+//   k_per_item  > 0: that many samples, partial sums added to Q with one reduction per voxel (order not fixed).
 // ACCURATE: cosf/sinf as the reference calls them; otherwise the argument is reduced to
 // [-pi, pi] with a two-constant Cody-Waite step and fed to the hardware sin/cos units.
 // =====================================================================================
@@ -301,6 +361,7 @@ struct MriqArgs {
     float* Qi;
     int gx;
     int start, end;
+    int k_per_item;  // chosen by the host, see above
 };
 
 constexpr float kMriq2Pi = 6.2831853071795864769252867665590058f;  // src/header/mriq_header.h:3
@@ -326,35 +387,80 @@ __device__ __forceinline__ void mriq_sincos(float a, float& s, float& c) {
 }
 
 template <bool ACCURATE>
-__device__ __forceinline__ void mriq_role(const MriqArgs m, const int tid, const int nthreads,
-                                          const int cta, const int ncta) {
-    constexpr int kItemsPerBlock = 4;
-    const int nwarp = nthreads >> 5, warp = tid >> 5, lane = tid & 31;
-    const long long nitems = static_cast<long long>(m.end - m.start) * kItemsPerBlock;
-    for (long long item = static_cast<long long>(warp) * ncta + cta; item < nitems;
-         item += static_cast<long long>(nwarp) * ncta) {
-        const int p = m.start + static_cast<int>(item / kItemsPerBlock);
-        const int sub = static_cast<int>(item % kItemsPerBlock);
+__device__ __forceinline__ void mriq_role(const MriqArgs m, int* counter, const int lane, const int cta,
+                                          const int ncta) {
+    constexpr int kTilesPerBlock = 4;
+    const bool split = m.k_per_item > 0 && m.k_per_item < m.numK;
+    const int per = split ? m.k_per_item : m.numK;
+    const int nchunks = split ? (m.numK + per - 1) / per : 1;
+    const long long nitems = static_cast<long long>(m.end - m.start) * kTilesPerBlock * nchunks;
+    for (long long item = claim_item(counter, lane, cta, ncta); item < nitems;
+         item = claim_item(counter, lane, cta, ncta)) {
+        const int chunk = static_cast<int>(item % nchunks);
+        const long long tile = item / nchunks;
+        const int p = m.start + static_cast<int>(tile / kTilesPerBlock);
+        const int sub = static_cast<int>(tile % kTilesPerBlock);
         const size_t i0 = static_cast<size_t>(p % m.gx) * 256 + sub * 64 + lane;
         const size_t i1 = i0 + 32;
         const float x0 = m.x[i0], y0 = m.y[i0], z0 = m.z[i0];
         const float x1 = m.x[i1], y1 = m.y[i1], z1 = m.z[i1];
-        float qr0 = m.Qr[i0], qi0 = m.Qi[i0], qr1 = m.Qr[i1], qi1 = m.Qi[i1];
-#pragma unroll 4
-        for (int k = 0; k < m.numK; ++k) {
-            const float4 kv = __ldg(m.kvals + k);
-            float s0, c0, s1, c1;
-            mriq_sincos<ACCURATE>(mriq_arg(kv, x0, y0, z0), s0, c0);
-            mriq_sincos<ACCURATE>(mriq_arg(kv, x1, y1, z1), s1, c1);
-            qr0 = __fmaf_rn(kv.w, c0, qr0);
-            qi0 = __fmaf_rn(kv.w, s0, qi0);
-            qr1 = __fmaf_rn(kv.w, c1, qr1);
-            qi1 = __fmaf_rn(kv.w, s1, qi1);
+        float qr0 = 0.0f, qi0 = 0.0f, qr1 = 0.0f, qi1 = 0.0f;
+        if (!split) {
+            qr0 = m.Qr[i0];
+            qi0 = m.Qi[i0];
+            qr1 = m.Qr[i1];
+            qi1 = m.Qi[i1];
         }
-        m.Qr[i0] = qr0;
-        m.Qi[i0] = qi0;
-        m.Qr[i1] = qr1;
-        m.Qi[i1] = qi1;
+        const int k0 = chunk * per;
+        const int k1 = min(k0 + per, m.numK);
+        if (ACCURATE) {
+#pragma unroll 4
+            for (int k = k0; k < k1; ++k) {
+                const float4 kv = __ldg(m.kvals + k);
+                float s0, c0, s1, c1;
+                mriq_sincos<true>(mriq_arg(kv, x0, y0, z0), s0, c0);
+                mriq_sincos<true>(mriq_arg(kv, x1, y1, z1), s1, c1);
+                qr0 = __fmaf_rn(kv.w, c0, qr0);
+                qi0 = __fmaf_rn(kv.w, s0, qi0);
+                qr1 = __fmaf_rn(kv.w, c1, qr1);
+                qi1 = __fmaf_rn(kv.w, s1, qi1);
+            }
+        } else {
+            // The same operations as mriq_arg / mriq_sincos<false>, rounded the same way, on the two voxels of the
+            // thread at once with the packed binary32 instructions: the loop is bound by issue slots as much as by
+            // the special-function pipe, and a packed operation takes one slot for both voxels.
+            const float2 X = make_float2(x0, x1), Y = make_float2(y0, y1), Z = make_float2(z0, z1);
+            float2 QR = make_float2(qr0, qr1), QI = make_float2(qi0, qi1);
+#pragma unroll 4
+            for (int k = k0; k < k1; ++k) {
+                const float4 kv = __ldg(m.kvals + k);
+                const float2 t = __ffma2_rn(make_float2(kv.z, kv.z), Z,
+                                            __ffma2_rn(make_float2(kv.x, kv.x), X, __fmul2_rn(make_float2(kv.y, kv.y), Y)));
+                const float2 a = __fmul2_rn(make_float2(kMriq2Pi, kMriq2Pi), t);
+                const float2 n = __fadd2_rn(__ffma2_rn(a, make_float2(0.15915494309189535f, 0.15915494309189535f),
+                                                       make_float2(12582912.0f, 12582912.0f)),
+                                            make_float2(-12582912.0f, -12582912.0f));
+                float2 r = __ffma2_rn(n, make_float2(-6.2831854820251465f, -6.2831854820251465f), a);
+                r = __ffma2_rn(n, make_float2(1.7484555314695172e-07f, 1.7484555314695172e-07f), r);
+                const float2 c = make_float2(__cosf(r.x), __cosf(r.y));
+                const float2 sn = make_float2(__sinf(r.x), __sinf(r.y));
+                const float2 w = make_float2(kv.w, kv.w);
+                QR = __ffma2_rn(w, c, QR);
+                QI = __ffma2_rn(w, sn, QI);
+            }
+            qr0 = QR.x, qr1 = QR.y, qi0 = QI.x, qi1 = QI.y;
+        }
+        if (split) {
+            red_add_f32(m.Qr + i0, qr0);
+            red_add_f32(m.Qi + i0, qi0);
+            red_add_f32(m.Qr + i1, qr1);
+            red_add_f32(m.Qi + i1, qi1);
+        } else {
+            m.Qr[i0] = qr0;
+            m.Qi[i0] = qi0;
+            m.Qr[i1] = qr1;
+            m.Qi[i1] = qi1;
+        }
     }
 }
 

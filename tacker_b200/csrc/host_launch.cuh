@@ -36,6 +36,10 @@ struct Options {
     int cp_ppt = 4;      // solo kernel: points per thread and work item (8 = the reference's granularity)
     int mix_cp_ppt = 8;  // fused kernel
     int mriq_accurate = 0;
+    // second dimension of the Coulomb / MRI-Q work items (fast modes only): -1 = the host picks the atoms /
+    // samples per item from the launch shape, 0 = never split (deterministic summation order), > 0 = that many
+    int cp_split = -1;
+    int mriq_split = -1;
     int stencil_prefetch = 0;   // register role: L2 prefetch distance in planes (0 or 8)
     int stencil_tma = 1;        // 1 = TMA-fed role whenever the shape allows, 0 = always the register role
     int stencil_ring = 4;       // ring depth per warp, solo kernel (2 planes in flight per warp measured best)
@@ -256,6 +260,7 @@ static int parse_cp(void** p, int i_start, int i_end, CpArgs* a) {
     const int bdx = arg<int>(p, 7), bdy = arg<int>(p, 8);
     a->start = arg<int>(p, i_start);
     a->end = arg<int>(p, i_end);
+    a->atoms_per_item = 0;
     if (a->numatoms < 0 || a->gx <= 0 || a->gy <= 0 || a->start < 0) return TK_ERR_ARGS;
     if (bdx != 16 || bdy != 8) return TK_ERR_SHAPE;
     if (a->end > a->gx * a->gy) a->end = a->gx * a->gy;
@@ -277,6 +282,7 @@ static int parse_mriq(void** p, int i_start, int i_end, MriqArgs* m) {
     const int bdx = arg<int>(p, 11);
     m->start = arg<int>(p, i_start);
     m->end = arg<int>(p, i_end);
+    m->k_per_item = 0;
     if (m->numK < 0 || m->gx <= 0 || m->start < 0) return TK_ERR_ARGS;
     if (bdx != 256) return TK_ERR_SHAPE;
     if (m->end > m->gx) m->end = m->gx;
@@ -383,11 +389,25 @@ static int run_stencil(StencilArgs s, unsigned grid0, unsigned block0, cudaStrea
     return launch_error("stencil_kernel launch");
 }
 
-static int run_cp(const CpArgs& a, unsigned grid0, unsigned block0, cudaStream_t st) {
+// atoms per work item for a launch of `warps` warps in total (see CpArgs::atoms_per_item)
+static int cp_split_for(const CpArgs& a, int ppt, long long warps) {
+    if (g_opt.cp_exact || g_opt.cp_split == 0) return 0;
+    if (g_opt.cp_split > 0) return (g_opt.cp_split + kCpChunk - 1) / kCpChunk * kCpChunk;
+    return cd_pick_split(static_cast<long long>(a.end - a.start) * 4 * (8 / ppt), warps, a.numatoms, kCpChunk);
+}
+
+static int mriq_split_for(const MriqArgs& m, long long warps) {
+    if (g_opt.mriq_accurate || g_opt.mriq_split == 0) return 0;
+    if (g_opt.mriq_split > 0) return g_opt.mriq_split;
+    return cd_pick_split(static_cast<long long>(m.end - m.start) * 4, warps, m.numK, 64);
+}
+
+static int run_cp(CpArgs a, unsigned grid0, unsigned block0, cudaStream_t st) {
     if (a.start >= a.end) return TK_OK;
     const unsigned threads = cd_threads(block0, 32, 512);
     if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
     const int ppt = g_opt.cp_ppt;
+    a.atoms_per_item = cp_split_for(a, ppt, static_cast<long long>(grid0) * (threads / 32));
     if (g_opt.cp_exact) {
         if (ppt == 2) cp_kernel<2, true><<<grid0, threads, 0, st>>>(a);
         else if (ppt == 4) cp_kernel<4, true><<<grid0, threads, 0, st>>>(a);
@@ -400,10 +420,11 @@ static int run_cp(const CpArgs& a, unsigned grid0, unsigned block0, cudaStream_t
     return launch_error("cp_kernel launch");
 }
 
-static int run_mriq(const MriqArgs& m, unsigned grid0, unsigned block0, cudaStream_t st) {
+static int run_mriq(MriqArgs m, unsigned grid0, unsigned block0, cudaStream_t st) {
     if (m.start >= m.end) return TK_OK;
     const unsigned threads = cd_threads(block0, 32, 512);
     if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    m.k_per_item = mriq_split_for(m, static_cast<long long>(grid0) * (threads / 32));
     if (g_opt.mriq_accurate) mriq_kernel<true><<<grid0, threads, 0, st>>>(m);
     else mriq_kernel<false><<<grid0, threads, 0, st>>>(m);
     return launch_error("mriq_kernel launch");
@@ -484,8 +505,11 @@ static int run_mix_stencil(const GemmCall& c, const StencilArgs& s, unsigned cta
 }
 
 template <int BN>
-static int launch_mix(const GemmCall& c, const CdCall& cd, unsigned ctas, unsigned threads, cudaStream_t st) {
+static int launch_mix(const GemmCall& c, CdCall cd, unsigned ctas, unsigned threads, cudaStream_t st) {
     constexpr int STAGES = StagesFor<BN>::value;
+    const long long cd_warps = static_cast<long long>(ctas) * ((threads - kGemmThreads) / 32);
+    if (cd.kind == CD_CP) cd.a.atoms_per_item = cp_split_for(cd.a, g_opt.mix_cp_ppt, cd_warps);
+    if (cd.kind == CD_MRIQ) cd.m.k_per_item = mriq_split_for(cd.m, cd_warps);
     CUtensorMap ta, tb;
     int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
     if (rc != TK_OK) return rc;
@@ -597,6 +621,9 @@ static int generated_mix_launch(CdKind kind, int cd_warps, void** params, int np
         stencil_pick_split(cd.s.nz, cd.s.end - cd.s.start, static_cast<long long>(ctas) * cd_warps, &cd.s.slabs,
                            &cd.s.per);
     }
+    const long long cd_warps_total = static_cast<long long>(ctas) * cd_warps;
+    if (kind == CD_CP) cd.a.atoms_per_item = cp_split_for(cd.a, 8, cd_warps_total);
+    if (kind == CD_MRIQ) cd.m.k_per_item = mriq_split_for(cd.m, cd_warps_total);
     rc = launch(ta, tb, c.g, tg, cd, ring, ctas, threads, smem, static_cast<cudaStream_t>(stream));
     if (rc != TK_OK) return rc;
     return launch_error("generated mix kernel launch");

@@ -63,14 +63,21 @@ stencil_tma_kernel(const __grid_constant__ CUtensorMap tmap_grid, const StencilA
                      threadIdx.x & 31, blockIdx.x, gridDim.x, status);
 }
 
+// Two CTAs of 512 threads per SM (<= 64 registers): 32 warps keep the special-function pipe busy.
 template <int PPT, bool EXACT>
-__global__ void __launch_bounds__(512, 1) cp_kernel(const CpArgs a) {
-    cp_role<PPT, EXACT>(a, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+__global__ void __launch_bounds__(512, 2) cp_kernel(const CpArgs a) {
+    __shared__ int item_counter;
+    if (threadIdx.x == 0) item_counter = 0;
+    __syncthreads();
+    cp_role<PPT, EXACT>(a, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
 }
 
 template <bool ACCURATE>
-__global__ void __launch_bounds__(512, 1) mriq_kernel(const MriqArgs m) {
-    mriq_role<ACCURATE>(m, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+__global__ void __launch_bounds__(512, 2) mriq_kernel(const MriqArgs m) {
+    __shared__ int item_counter;
+    if (threadIdx.x == 0) item_counter = 0;
+    __syncthreads();
+    mriq_role<ACCURATE>(m, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
 }
 
 // Fused kernels: warps 0..5 run the tensor role, the remaining warps the CUDA-core role.  The
@@ -96,16 +103,26 @@ mix_stencil_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
 }
 
+// The CUDA-core warps of a fused CTA (threads kGemmThreads .. blockDim.x - 1) zero their item counter and meet
+// on a named barrier of their own, so the tensor role is never involved.
+constexpr uint32_t kCdBarrierId = 2;
+__device__ __forceinline__ void cd_role_begin(int* item_counter) {
+    if (threadIdx.x == kGemmThreads) *item_counter = 0;
+    named_bar_sync(kCdBarrierId, blockDim.x - kGemmThreads);
+}
+
 template <int BN, int STAGES, int PPT>
 __global__ void __launch_bounds__(kMaxMixThreadsSfu, 1)
 mix_cp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
               const GemmArgs g, const CpArgs a) {
     extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
     const int warp = threadIdx.x >> 5;
     if (warp < kGemmWarps) {
         gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
     } else {
-        cp_role<PPT, false>(a, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+        cd_role_begin(&item_counter);
+        cp_role<PPT, false>(a, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
     }
 }
 
@@ -114,11 +131,13 @@ __global__ void __launch_bounds__(kMaxMixThreadsSfu, 1)
 mix_mriq_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const GemmArgs g, const MriqArgs m) {
     extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
     const int warp = threadIdx.x >> 5;
     if (warp < kGemmWarps) {
         gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
     } else {
-        mriq_role<false>(m, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+        cd_role_begin(&item_counter);
+        mriq_role<false>(m, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
     }
 }
 

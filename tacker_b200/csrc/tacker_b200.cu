@@ -44,6 +44,8 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "cp_ppt")) return &g_opt.cp_ppt;
     if (!std::strcmp(name, "mix_cp_ppt")) return &g_opt.mix_cp_ppt;
     if (!std::strcmp(name, "mriq_accurate")) return &g_opt.mriq_accurate;
+    if (!std::strcmp(name, "cp_split")) return &g_opt.cp_split;
+    if (!std::strcmp(name, "mriq_split")) return &g_opt.mriq_split;
     if (!std::strcmp(name, "stencil_prefetch")) return &g_opt.stencil_prefetch;
     if (!std::strcmp(name, "stencil_tma")) return &g_opt.stencil_tma;
     if (!std::strcmp(name, "stencil_ring")) return &g_opt.stencil_ring;
@@ -418,6 +420,7 @@ TK_API int tk_mriq_compute(const float* kx, const float* ky, const float* kz, co
     m.gx = numX / 256;
     m.start = 0;
     m.end = m.gx;
+    m.k_per_item = 0;
     if (!x || !y || !z || !Qr || !Qi) return TK_ERR_ARGS;
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
@@ -440,6 +443,7 @@ TK_API int tk_coulomb_compute(const float* atoms_xyzq, int numatoms, float zplan
     a.gy = ny / 8;
     a.start = 0;
     a.end = a.gx * a.gy;
+    a.atoms_per_item = 0;
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
     return run_cp(a, static_cast<unsigned>(d->sm_count) * 2u, 256, static_cast<cudaStream_t>(stream));

@@ -2,7 +2,8 @@
 which emit a main() that runs ORI, GPTB and the fused kernel on the same seeded inputs and compares).
 
 Here one harness serves every pair: it loads the module, launches the generated kernel and the library's solo
-kernels on identical seeded inputs and demands bit-identical outputs of the CUDA-core kernel and of the GEMM.
+kernels on identical seeded inputs and demands bit-identical outputs of the GEMM and of the stencil, and outputs
+within 1e-5 of the Coulomb / MRI-Q kernels (whose split work items sum in no fixed order).
 Needs a GPU; PyTorch only provides the device buffers.
 """
 from __future__ import annotations
@@ -68,5 +69,11 @@ def check_module(so_path: str, name: str, cd: str) -> dict:
         results[mode] = (Cm.cpu().numpy(), bufs[out_idx].cpu().numpy())
     same_gemm = bool(np.array_equal(results["solo"][0], results["generated"][0]))
     same_cd = bool(np.array_equal(results["solo"][1], results["generated"][1]))
+    # Coulomb / MRI-Q items that cover a part of the atom / sample list add their partial sums with reductions in
+    # no fixed order: those outputs are held to the operators' 1e-5 tolerance instead of bit identity
+    scale = float(np.abs(results["solo"][1]).max())
+    cd_err = float(np.abs(results["solo"][1] - results["generated"][1]).max()) / (scale if scale > 0 else 1.0)
+    cd_ok = same_cd if cd == "stencil" else cd_err <= 1e-5
     return {"name": name, "threads": threads, "gemm_bit_identical": same_gemm, "cd_bit_identical": same_cd,
-            "ok": same_gemm and same_cd and bool(np.abs(results["generated"][0]).max() > 0)}
+            "cd_max_rel_err": cd_err,
+            "ok": same_gemm and cd_ok and bool(np.abs(results["generated"][0]).max() > 0)}

@@ -65,6 +65,30 @@ def test_fast_mode_within_tolerance(cuda, oracle, ppt):
     assert oracle.max_scaled_err(got, ref64, mag) <= 1e-5
 
 
+@pytest.mark.parametrize("split", [64, 128, 0, -1])
+@pytest.mark.parametrize("natoms", [1, 64, 65, 200, 1000])
+def test_atom_split_items(cuda, oracle, split, natoms):
+    """Work items that cover a range of the atom list and add their partial sums with reductions: same result
+    within the tolerance for every split (including ragged last ranges), accumulating onto a non-zero lattice,
+    inside a virtual-block range only."""
+    from tacker_b200 import ops
+
+    nx, ny, h, z = 256, 32, 0.125, 3.0            # 2 x 4 patches
+    atoms = coulomb_inputs(oracle, natoms, 24.0, seed=100 + natoms, spacing=h, zplane=z)
+    base = oracle.uniform_f32(nx * ny, 78, -1.0, 1.0).reshape(ny, nx)
+    ops.set_option("cp_split", split)
+    try:
+        got, _ = _run(cuda, ops, atoms, z, h, nx, ny, base=base, start=1, end=7, grid=5, block=160)
+    finally:
+        ops.set_option("cp_split", -1)
+    packed = oracle.cp_pack_atoms(atoms, z)
+    ref32 = oracle.cp_f32(packed, h, base.copy(), start=1, end=7, chunk=64)
+    _, mag = oracle.cp_f64(packed, h, nx, ny, start=1, end=7)
+    touched = mag > 0
+    assert np.array_equal(got[~touched], base[~touched])
+    assert (np.abs(got - ref32)[touched] / (mag[touched] + np.abs(base[touched]))).max() <= 1e-5
+
+
 @pytest.mark.parametrize("rng", [(0, 1), (3, 4), (1, 6), (0, 8), (7, 8), (2, 2), (5, 20)])
 def test_virtual_block_range_is_exact(cuda, oracle, rng):
     from tacker_b200 import ops

@@ -1,8 +1,10 @@
 """Fused tensor-core + CUDA-core kernels through the C ABI (B200 only).
 
 A fused launch must leave exactly what the two solo launches leave: the CUDA-core role runs the
-same device function with the same summation order, so its output is bit-identical to the solo
-kernel's, and the tensor role's tiles are bit-identical to the solo tzgemm's.
+same device function, so with a fixed summation order (stencil always; Coulomb and MRI-Q with unsplit
+work items) its output is bit-identical to the solo kernel's, and the tensor role's tiles are bit-identical
+to the solo tzgemm's.  With split work items (the default of the fast modes: partial sums are added with
+reductions in no fixed order) the CUDA-core output is held to the operator's tolerance instead.
 """
 import numpy as np
 import pytest
@@ -55,9 +57,19 @@ def test_tzgemm_stencil(cuda, oracle, cd_threads, ranges):
         assert np.abs(out["fused"][0][written] - ref[written]).max() <= 1e-3 * K
 
 
+@pytest.mark.parametrize("split", [0, -1, 64])
 @pytest.mark.parametrize("cd_threads", [32, 256])
-def test_tzgemm_cp(cuda, oracle, cd_threads):
+def test_tzgemm_cp(cuda, oracle, cd_threads, split):
     from tacker_b200 import ops
+
+    ops.set_option("cp_split", split)
+    try:
+        _tzgemm_cp(cuda, oracle, ops, cd_threads, split)
+    finally:
+        ops.set_option("cp_split", -1)
+
+
+def _tzgemm_cp(cuda, oracle, ops, cd_threads, split):
 
     M, N, K = 384, 256, 128
     nx, ny, h, z = 256, 32, 0.125, 2.0
@@ -83,7 +95,8 @@ def test_tzgemm_cp(cuda, oracle, cd_threads):
         assert ops.device_status() == 0
         out[mode] = (Cd.cpu().numpy(), lat.cpu().numpy())
     assert np.array_equal(out["solo"][0], out["fused"][0])
-    assert np.array_equal(out["solo"][1], out["fused"][1])
+    if split == 0:
+        assert np.array_equal(out["solo"][1], out["fused"][1])
     pk = oracle.cp_pack_atoms(atoms, z)
     ref32 = oracle.cp_f32(pk, h, np.zeros((ny, nx), np.float32), start=1, end=7, chunk=64)
     _, mag = oracle.cp_f64(pk, h, nx, ny, start=1, end=7)
@@ -93,9 +106,19 @@ def test_tzgemm_cp(cuda, oracle, cd_threads):
     assert np.abs(out["fused"][0] - oracle.tzgemm_f64(a, b)).max() <= 1e-3 * K
 
 
+@pytest.mark.parametrize("split", [0, -1, 64])
 @pytest.mark.parametrize("cd_threads", [64, 256])
-def test_tzgemm_mriq(cuda, oracle, cd_threads):
+def test_tzgemm_mriq(cuda, oracle, cd_threads, split):
     from tacker_b200 import ops
+
+    ops.set_option("mriq_split", split)
+    try:
+        _tzgemm_mriq(cuda, oracle, ops, cd_threads, split)
+    finally:
+        ops.set_option("mriq_split", -1)
+
+
+def _tzgemm_mriq(cuda, oracle, ops, cd_threads, split):
 
     M, N, K = 256, 256, 192
     numK, numX = 200, 2048
@@ -125,7 +148,7 @@ def test_tzgemm_mriq(cuda, oracle, cd_threads):
         cuda.cuda.synchronize()
         assert ops.device_status() == 0
         out[mode] = (Cd.cpu().numpy(), qr.cpu().numpy(), qi.cpu().numpy())
-    for i in range(3):
+    for i in range(3 if split == 0 else 1):
         assert np.array_equal(out["solo"][i], out["fused"][i])
     kvh = kv.cpu().numpy()
     r64, i64 = oracle.mriq_f64(kvh, xyz[0], xyz[1], xyz[2])

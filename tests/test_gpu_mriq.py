@@ -58,6 +58,30 @@ def test_small_cases(cuda, oracle, accurate, numK):
     _tol_check(oracle, qr, qi, kv, xyz, numX)
 
 
+@pytest.mark.parametrize("split", [64, 100, 0, -1])
+@pytest.mark.parametrize("numK", [1, 65, 256, 1025])
+def test_sample_split_items(cuda, oracle, split, numK):
+    """Work items that cover a range of the samples and add their partial sums to Q with reductions."""
+    from tacker_b200 import ops
+
+    numX = 1024
+    k, phi, xyz = mriq_inputs(oracle, numK, numX, seed=50 + numK)
+    qr0 = oracle.uniform_f32(numX, 903, -2.0, 2.0)
+    qi0 = oracle.uniform_f32(numX, 904, -2.0, 2.0)
+    ops.set_option("mriq_split", split)
+    try:
+        qr, qi, kv = _run(cuda, ops, k, phi, xyz, qr0=qr0, qi0=qi0, start=1, end=3, grid=3, block=96)
+    finally:
+        ops.set_option("mriq_split", -1)
+    outside = np.ones(numX, dtype=bool)
+    outside[256:768] = False
+    assert np.array_equal(qr[outside], qr0[outside]) and np.array_equal(qi[outside], qi0[outside])
+    wr, wi = qr0.copy(), qi0.copy()
+    oracle.mriq_f32(kv, xyz[0], xyz[1], xyz[2], wr, wi, start=1, end=3)
+    scale = float(kv[:, 3].sum()) + 2.0
+    assert np.abs(qr - wr).max() <= 1e-5 * scale and np.abs(qi - wi).max() <= 1e-5 * scale
+
+
 @pytest.mark.parametrize("rng", [(0, 1), (2, 3), (1, 4), (0, 4), (3, 3), (2, 9)])
 def test_virtual_block_range_and_accumulate(cuda, oracle, rng):
     from tacker_b200 import ops
