@@ -225,9 +225,29 @@ def run_ours(args):
                     k.execute(st)
         return timed(make_graph(fn), 3, 2) / reps * 1e3
 
-    if args.only_pairs:  # just the Coulomb and MRI-Q pairs (used for the ncu captures of those kernels)
+    if args.profile_gemm:  # a few launches of the solo tzgemm on one shape (for profiler captures)
+        m, n, k = (int(v) for v in args.profile_gemm.lower().split("x"))
+        a = (torch.rand(m, k, device="cuda", generator=gen) * 2 - 1).half()
+        b = (torch.rand(n, k, device="cuda", generator=gen) * 2 - 1).half()
+        c = torch.zeros(m, n, device="cuda")
+        for name, value in (("tzgemm_pair", args.gemm_pair), ("tzgemm_m256", args.gemm_m256)):
+            ops.set_option(name, value)
+        kern = ops.gptb_tzgemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, alpha=1.0, grid=sms)
+        us = t_of([kern], 20)
+        for _ in range(3):
+            kern.execute(st)
+        torch.cuda.synchronize()
         if rank == 0:
-            print(json.dumps({"pairs": other_pairs(torch, ops, sms, gen, t_of, st)}), flush=True)
+            print(json.dumps({"profile_gemm": args.profile_gemm, "tzgemm_pair": args.gemm_pair,
+                              "tzgemm_m256": args.gemm_m256, "us": round(us, 2),
+                              "tflops": round(2.0 * m * n * k / us / 1e6, 1), "status": ops.device_status()}), flush=True)
+        rep.close()
+        return
+
+    if args.only_pairs or args.profile_pair:  # just the Coulomb and MRI-Q pairs (used for profiler captures of those kernels)
+        if rank == 0:
+            print(json.dumps({"pairs": other_pairs(torch, ops, sms, gen, t_of, st, args.profile_pair, args.profile_w)}),
+                  flush=True)
         rep.close()
         return
 
@@ -516,10 +536,22 @@ def pair_report(ops, sms, t_of, tz, make_cd, total_blocks, cd_name, w_sweep):
                      "fused_us_by_cd_threads": {str(w): round(v, 1) for w, v in bal.items()}}}
 
 
-def other_pairs(torch, ops, sms, gen, t_of, st):
-    """Configs 3 and 4: GEMM + Coulomb (compute-bound CUDA-core pair), GEMM + MRI-Q (SFU-bound pair)."""
+def other_pairs(torch, ops, sms, gen, t_of, st, profile=None, profile_w=832):
+    """Configs 3 and 4: GEMM + Coulomb (compute-bound CUDA-core pair), GEMM + MRI-Q (SFU-bound pair).
+
+    profile = "cp" | "mriq": only find that pair's balanced quantum with solo launches, then run its fused launch
+    three times with `profile_w` CUDA-core threads (the launches a profiler capture of the fused kernel wants)."""
     out = {}
     w_sweep = (320, 576, 832)
+
+    def profile_run(tz, make_cd, total_blocks):
+        t_g, t_c = t_of([tz()], 10), t_of([make_cd()], 5)
+        nb, t_cb = balanced_quantum(t_of, make_cd, total_blocks, t_g, t_c)
+        k = ops.mix(make_cd(0, nb), tz(), cd_threads=profile_w, grid=sms)
+        for _ in range(3):
+            k.execute(st)
+        torch.cuda.synchronize()
+        return {"gemm_us": round(t_g, 1), "cd_us": round(t_cb, 1), "cd_blocks": nb, "cd_threads": profile_w}
 
     def gemm(m, n, k):
         a = (torch.rand(m, k, device="cuda", generator=gen) * 2 - 1).half()
@@ -538,7 +570,9 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
     ops.set_option("cp_ppt", 8)
     cp = lambda s=0, e=None: ops.gptb_cp(8192, 0.125, lat.data_ptr(), packed.data_ptr(), 512, 512, start=s, end=e,
                                          grid=sms * 2, block=512)
-    r = pair_report(ops, sms, t_of, tz, cp, 256, "coulomb", w_sweep)
+    if profile == "cp":
+        return {"profile_cp": profile_run(tz, cp, 256)}
+    r = pair_report(ops, sms, t_of, tz, cp, 256, "coulomb", w_sweep) if profile is None else {"coulomb_us": 1.0}
     r["coulomb_gpairs_per_s"] = round(8192.0 * 512 * 512 / r["coulomb_us"] / 1e3, 1)
     r["coulomb_frac_of_rsqrt_bound"] = round(8192.0 * 512 * 512 / (sms * 16 * 1.965e9) / (r["coulomb_us"] * 1e-6), 3)
     out["config3_gemm2048_coulomb"] = r
@@ -552,6 +586,8 @@ def other_pairs(torch, ops, sms, gen, t_of, st):
     qr, qi = torch.zeros(numX, device="cuda"), torch.zeros(numX, device="cuda")
     mq = lambda s=0, e=None: ops.gptb_mriq(numK, xyz[0].data_ptr(), xyz[1].data_ptr(), xyz[2].data_ptr(), qr.data_ptr(),
                                            qi.data_ptr(), kv.data_ptr(), numX, start=s, end=e, grid=sms * 2, block=512)
+    if profile == "mriq":
+        return {"profile_mriq": profile_run(tz4, mq, 1024)}
     r = pair_report(ops, sms, t_of, tz4, mq, 1024, "mriq", w_sweep)
     r["mriq_gpairs_per_s"] = round(numK * numX / r["mriq_us"] / 1e3, 1)
     r["mriq_frac_of_sfu_bound"] = round(2.0 * numK * numX / (sms * 16 * 1.965e9) / (r["mriq_us"] * 1e-6), 3)
@@ -571,6 +607,13 @@ def main():
     ap.add_argument("--sustain-ms", type=float, default=400.0)
     ap.add_argument("--colocate-s", type=float, default=60.0, help="seconds of the LC/BE co-location run (0 = skip)")
     ap.add_argument("--only-pairs", action="store_true", help="run only the Coulomb and MRI-Q pairs and print them")
+    ap.add_argument("--profile-gemm", default=None, help="MxNxK: time the solo tzgemm on that shape, launch it three more "
+                                                         "times and exit")
+    ap.add_argument("--gemm-pair", type=int, default=0, help="tzgemm_pair option of the --profile-gemm launches")
+    ap.add_argument("--gemm-m256", type=int, default=0, help="tzgemm_m256 option of the --profile-gemm launches")
+    ap.add_argument("--profile-pair", choices=("cp", "mriq"), default=None,
+                    help="find that pair's balanced quantum, then launch its fused kernel three times and exit")
+    ap.add_argument("--profile-w", type=int, default=832, help="CUDA-core threads of the --profile-pair launches")
     ap.add_argument("--fuse-sweeps", type=int, default=0, choices=(0, 1, 2, 10),
                     help="how many sweeps are fused with the GEMM (0 = time 10, 2 and 1 briefly and take the best)")
     args = ap.parse_args()

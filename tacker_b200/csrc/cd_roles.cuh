@@ -345,7 +345,7 @@ __device__ __forceinline__ void cp_role(const CpArgs a, int* counter, const int 
 //   argument formed in binary32 as 2pi_f32 * fma(Kz, z, fma(Kx, x, Ky * y)).
 // Virtual block p = 256 consecutive voxels ((p % gx) * 256 ...).  The reference streams the
 // samples through a 1024-entry __constant__ array; here they are read from global memory, any
-// count, in one launch.  Work item = one warp = 64 voxels (two per thread) times a range of the samples:
+// count, in one launch.  Work item = one warp = 64 or 128 voxels (two or four per thread) times a range of the samples:
 //   k_per_item == 0: all samples, running sum starting from Q as in the reference (deterministic);
 //   k_per_item  > 0: that many samples, partial sums added to Q with one reduction per voxel (order not fixed).
 // ACCURATE: cosf/sinf as the reference calls them; otherwise the argument is reduced to
@@ -386,10 +386,33 @@ __device__ __forceinline__ void mriq_sincos(float a, float& s, float& c) {
     }
 }
 
-template <bool ACCURATE>
+// fast path of one sample for a pair of voxels: the operations of mriq_arg / mriq_sincos<false>, rounded the same
+// way, on both voxels at once with the packed binary32 instructions (the loop is bound by issue slots as much
+// as by the special-function pipe, and a packed operation takes one slot for two voxels)
+__device__ __forceinline__ void mriq_pair_step(const float2 kx, const float2 ky, const float2 kz, const float2 w,
+                                               const float2 X, const float2 Y, const float2 Z, float2& QR,
+                                               float2& QI) {
+    const float2 t = __ffma2_rn(kz, Z, __ffma2_rn(kx, X, __fmul2_rn(ky, Y)));
+    const float2 a = __fmul2_rn(make_float2(kMriq2Pi, kMriq2Pi), t);
+    const float2 n = __fadd2_rn(__ffma2_rn(a, make_float2(0.15915494309189535f, 0.15915494309189535f),
+                                           make_float2(12582912.0f, 12582912.0f)),
+                                make_float2(-12582912.0f, -12582912.0f));
+    float2 r = __ffma2_rn(n, make_float2(-6.2831854820251465f, -6.2831854820251465f), a);
+    r = __ffma2_rn(n, make_float2(1.7484555314695172e-07f, 1.7484555314695172e-07f), r);
+    const float2 c = make_float2(__cosf(r.x), __cosf(r.y));
+    const float2 sn = make_float2(__sinf(r.x), __sinf(r.y));
+    QR = __ffma2_rn(w, c, QR);
+    QI = __ffma2_rn(w, sn, QI);
+}
+
+// VPT = voxels per thread (2 or 4): a work item covers 32 * VPT consecutive voxels.  Every sample is one 16-byte
+// table read per warp, whatever VPT is, so the larger item halves the load traffic per (sample, voxel) pair -- which
+// matters inside a fused CTA, where those reads share the L1 data path with the tensor role's operand reads.
+template <bool ACCURATE, int VPT>
 __device__ __forceinline__ void mriq_role(const MriqArgs m, int* counter, const int lane, const int cta,
                                           const int ncta) {
-    constexpr int kTilesPerBlock = 4;
+    static_assert(VPT == 2 || VPT == 4, "two or four voxels per thread");
+    constexpr int kTilesPerBlock = 256 / (32 * VPT);
     const bool split = m.k_per_item > 0 && m.k_per_item < m.numK;
     const int per = split ? m.k_per_item : m.numK;
     const int nchunks = split ? (m.numK + per - 1) / per : 1;
@@ -400,66 +423,63 @@ __device__ __forceinline__ void mriq_role(const MriqArgs m, int* counter, const 
         const long long tile = item / nchunks;
         const int p = m.start + static_cast<int>(tile / kTilesPerBlock);
         const int sub = static_cast<int>(tile % kTilesPerBlock);
-        const size_t i0 = static_cast<size_t>(p % m.gx) * 256 + sub * 64 + lane;
-        const size_t i1 = i0 + 32;
-        const float x0 = m.x[i0], y0 = m.y[i0], z0 = m.z[i0];
-        const float x1 = m.x[i1], y1 = m.y[i1], z1 = m.z[i1];
-        float qr0 = 0.0f, qi0 = 0.0f, qr1 = 0.0f, qi1 = 0.0f;
-        if (!split) {
-            qr0 = m.Qr[i0];
-            qi0 = m.Qi[i0];
-            qr1 = m.Qr[i1];
-            qi1 = m.Qi[i1];
+        const size_t base = static_cast<size_t>(p % m.gx) * 256 + sub * (32 * VPT) + lane;  // voxels base + 32 v
+        float x[VPT], y[VPT], z[VPT], qr[VPT], qi[VPT];
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            x[v] = m.x[base + 32 * v];
+            y[v] = m.y[base + 32 * v];
+            z[v] = m.z[base + 32 * v];
+            qr[v] = split ? 0.0f : m.Qr[base + 32 * v];
+            qi[v] = split ? 0.0f : m.Qi[base + 32 * v];
         }
         const int k0 = chunk * per;
         const int k1 = min(k0 + per, m.numK);
         if (ACCURATE) {
-#pragma unroll 4
+#pragma unroll 2
             for (int k = k0; k < k1; ++k) {
                 const float4 kv = __ldg(m.kvals + k);
-                float s0, c0, s1, c1;
-                mriq_sincos<true>(mriq_arg(kv, x0, y0, z0), s0, c0);
-                mriq_sincos<true>(mriq_arg(kv, x1, y1, z1), s1, c1);
-                qr0 = __fmaf_rn(kv.w, c0, qr0);
-                qi0 = __fmaf_rn(kv.w, s0, qi0);
-                qr1 = __fmaf_rn(kv.w, c1, qr1);
-                qi1 = __fmaf_rn(kv.w, s1, qi1);
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) {
+                    float sv, cv;
+                    mriq_sincos<true>(mriq_arg(kv, x[v], y[v], z[v]), sv, cv);
+                    qr[v] = __fmaf_rn(kv.w, cv, qr[v]);
+                    qi[v] = __fmaf_rn(kv.w, sv, qi[v]);
+                }
             }
         } else {
-            // The same operations as mriq_arg / mriq_sincos<false>, rounded the same way, on the two voxels of the
-            // thread at once with the packed binary32 instructions: the loop is bound by issue slots as much as by
-            // the special-function pipe, and a packed operation takes one slot for both voxels.
-            const float2 X = make_float2(x0, x1), Y = make_float2(y0, y1), Z = make_float2(z0, z1);
-            float2 QR = make_float2(qr0, qr1), QI = make_float2(qi0, qi1);
+            float2 X[VPT / 2], Y[VPT / 2], Z[VPT / 2], QR[VPT / 2], QI[VPT / 2];
+#pragma unroll
+            for (int h = 0; h < VPT / 2; ++h) {
+                X[h] = make_float2(x[2 * h], x[2 * h + 1]);
+                Y[h] = make_float2(y[2 * h], y[2 * h + 1]);
+                Z[h] = make_float2(z[2 * h], z[2 * h + 1]);
+                QR[h] = make_float2(qr[2 * h], qr[2 * h + 1]);
+                QI[h] = make_float2(qi[2 * h], qi[2 * h + 1]);
+            }
 #pragma unroll 4
             for (int k = k0; k < k1; ++k) {
                 const float4 kv = __ldg(m.kvals + k);
-                const float2 t = __ffma2_rn(make_float2(kv.z, kv.z), Z,
-                                            __ffma2_rn(make_float2(kv.x, kv.x), X, __fmul2_rn(make_float2(kv.y, kv.y), Y)));
-                const float2 a = __fmul2_rn(make_float2(kMriq2Pi, kMriq2Pi), t);
-                const float2 n = __fadd2_rn(__ffma2_rn(a, make_float2(0.15915494309189535f, 0.15915494309189535f),
-                                                       make_float2(12582912.0f, 12582912.0f)),
-                                            make_float2(-12582912.0f, -12582912.0f));
-                float2 r = __ffma2_rn(n, make_float2(-6.2831854820251465f, -6.2831854820251465f), a);
-                r = __ffma2_rn(n, make_float2(1.7484555314695172e-07f, 1.7484555314695172e-07f), r);
-                const float2 c = make_float2(__cosf(r.x), __cosf(r.y));
-                const float2 sn = make_float2(__sinf(r.x), __sinf(r.y));
-                const float2 w = make_float2(kv.w, kv.w);
-                QR = __ffma2_rn(w, c, QR);
-                QI = __ffma2_rn(w, sn, QI);
+                const float2 kx = make_float2(kv.x, kv.x), ky = make_float2(kv.y, kv.y);
+                const float2 kz = make_float2(kv.z, kv.z), w = make_float2(kv.w, kv.w);
+#pragma unroll
+                for (int h = 0; h < VPT / 2; ++h) mriq_pair_step(kx, ky, kz, w, X[h], Y[h], Z[h], QR[h], QI[h]);
             }
-            qr0 = QR.x, qr1 = QR.y, qi0 = QI.x, qi1 = QI.y;
+#pragma unroll
+            for (int h = 0; h < VPT / 2; ++h) {
+                qr[2 * h] = QR[h].x, qr[2 * h + 1] = QR[h].y;
+                qi[2 * h] = QI[h].x, qi[2 * h + 1] = QI[h].y;
+            }
         }
-        if (split) {
-            red_add_f32(m.Qr + i0, qr0);
-            red_add_f32(m.Qi + i0, qi0);
-            red_add_f32(m.Qr + i1, qr1);
-            red_add_f32(m.Qi + i1, qi1);
-        } else {
-            m.Qr[i0] = qr0;
-            m.Qi[i0] = qi0;
-            m.Qr[i1] = qr1;
-            m.Qi[i1] = qi1;
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            if (split) {
+                red_add_f32(m.Qr + base + 32 * v, qr[v]);
+                red_add_f32(m.Qi + base + 32 * v, qi[v]);
+            } else {
+                m.Qr[base + 32 * v] = qr[v];
+                m.Qi[base + 32 * v] = qi[v];
+            }
         }
     }
 }

@@ -40,11 +40,16 @@ struct Options {
     // samples per item from the launch shape, 0 = never split (deterministic summation order), > 0 = that many
     int cp_split = -1;
     int mriq_split = -1;
+    int mriq_vpt = 2;      // voxels per thread and work item / 32, solo kernel (2 or 4)
+    int mix_mriq_vpt = 4;  // fused kernel: the larger item halves the table reads that compete with the tensor role
     int stencil_prefetch = 0;   // register role: L2 prefetch distance in planes (0 or 8)
     int stencil_tma = 1;        // 1 = TMA-fed role whenever the shape allows, 0 = always the register role
     int stencil_ring = 4;       // ring depth per warp, solo kernel (2 planes in flight per warp measured best)
     int mix_stencil_ring = 12;  // upper bound of the ring depth in the fused kernel (shared memory decides)
     int tzgemm_m256 = 0;        // solo tzgemm with 256 x 256 super-tiles: 0 = by shape, 1 = always, -1 = never
+    int tzgemm_pair = 0;        // solo tzgemm on CTA pairs (cta_group::2): 0 = by shape, 1 = whenever possible, -1 = never
+    int mix_pair = 0;           // the same for the tensor role of the fused kernels
+    int mix_pair_stages = 4;    // operand stages of the fused stencil kernel on CTA pairs (3 .. 5; the rest goes to the rings)
     int l2_hints = 0;           // fused kernels: GEMM tiles evict-last, stencil planes evict-first in L2
     int mix_stencil_cfg = 0;    // tensor-role shape of the fused stencil kernel: 0 auto, 1 = 256x3 stages,
                                 // 2 = 128x4, 3 = 128x3, 4 = 128x2
@@ -54,6 +59,8 @@ static Options g_opt;
 struct DeviceInfo {
     int sm_count = 0;
     unsigned* status_ptr = nullptr;
+    // per kernel (and launch shape): clusters of two CTAs that can be resident at once
+    std::map<std::tuple<const void*, unsigned, int>, int> pair_clusters;
 };
 static std::mutex g_mutex;
 static std::map<int, DeviceInfo> g_devices;
@@ -315,6 +322,66 @@ static int launch_tzgemm(const GemmCall& c, unsigned ctas, cudaStream_t st) {
     return launch_error("tzgemm_kernel launch");
 }
 
+constexpr int kStagesPair = 6;
+
+// How many CTA pairs of `kernel` the device can hold at once (a persistent launch must not exceed it: the
+// pairs wait on each other's barriers only inside a pair, but a pair that is not resident would start late).
+template <typename KernelT>
+static int max_resident_pairs(KernelT kernel, unsigned threads, int smem, int* out) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    TK_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    *out = n;
+    return TK_OK;
+}
+
+// number of CTA pairs to launch for a request of `ctas` CTAs: never more than fit at once
+template <typename KernelT>
+static int pairs_for(KernelT kernel, DeviceInfo* d, unsigned ctas, unsigned threads, int smem, unsigned* pairs) {
+    const auto key = std::make_tuple(reinterpret_cast<const void*>(kernel), threads, smem);
+    int resident = -1;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        auto it = d->pair_clusters.find(key);
+        if (it != d->pair_clusters.end()) resident = it->second;
+    }
+    if (resident < 0) {
+        int rc = max_resident_pairs(kernel, threads, smem, &resident);
+        if (rc != TK_OK) return rc;
+        std::lock_guard<std::mutex> lock(g_mutex);
+        d->pair_clusters[key] = resident;
+    }
+    unsigned p = ctas / 2;
+    if (p > static_cast<unsigned>(resident)) p = static_cast<unsigned>(resident);
+    if (p == 0) return TK_ERR_LAUNCH_CONFIG;
+    *pairs = p;
+    return TK_OK;
+}
+
+static int run_tzgemm_pair(const GemmCall& c, DeviceInfo* d, unsigned ctas, cudaStream_t st) {
+    constexpr int smem = Gemm2Smem<kStagesPair>::kBytes + 1024;
+    auto kernel = tzgemm2_kernel<kStagesPair>;
+    int rc = enable_smem(kernel, smem);
+    if (rc != TK_OK) return rc;
+    unsigned pairs = 0;
+    if ((rc = pairs_for(kernel, d, ctas, kGemm2Threads, smem, &pairs)) != TK_OK) return rc;
+    CUtensorMap ta, tb;
+    if ((rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM)) != TK_OK) return rc;
+    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, kGemm2BN / 2)) != TK_OK) return rc;
+    kernel<<<2 * pairs, kGemm2Threads, smem, st>>>(ta, tb, c.g);
+    return launch_error("tzgemm2_kernel launch");
+}
+
 static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st, bool allow_splitk = false) {
     DeviceInfo* d = nullptr;
     int rc = device_info(&d);
@@ -342,6 +409,13 @@ static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st, bool allow_s
     const long long tiles256 = static_cast<long long>((c.g.M + 255) / 256) * (c.g.N / 256);
     const bool big = c.g.N % 256 == 0 && c.g.end - c.g.start == full_tiles && tiles256 >= static_cast<long long>(ctas) &&
                      (c.g.K >= 2048 || tiles256 >= 4ll * ctas);
+    // CTA pairs (256 x 256 pair tiles, two accumulator buffers).  Measured on B200 against the forms below: ahead for
+    // short K with at least a wave of pair tiles (4096 x 4096 x 1024: 34.2 vs 35.9 us, 8192 x 8192 x 1024: 122.5 vs
+    // 125.5 us), behind the single-CTA 256 x 256 form from K = 2048 on and when there are fewer pair tiles than pairs.
+    const bool pair_ok = c.g.batch <= 1 && c.g.splitk <= 1 && c.g.M >= 256 && c.g.N >= 256 && ctas >= 2;
+    const bool pair_wins = c.g.end - c.g.start == full_tiles && c.g.N % 256 == 0 && c.g.K < 2048 &&
+                           tiles256 >= static_cast<long long>(ctas / 2);
+    if (pair_ok && (g_opt.tzgemm_pair > 0 || (g_opt.tzgemm_pair == 0 && pair_wins))) return run_tzgemm_pair(c, d, ctas, st);
     if (c.g.batch <= 1 && c.g.splitk <= 1 && (g_opt.tzgemm_m256 > 0 || (g_opt.tzgemm_m256 == 0 && big))) {
         CUtensorMap ta, tb;
         if ((rc = make_tmap(&ta, c.A, c.g.M, c.g.K, 256)) != TK_OK) return rc;
@@ -396,10 +470,10 @@ static int cp_split_for(const CpArgs& a, int ppt, long long warps) {
     return cd_pick_split(static_cast<long long>(a.end - a.start) * 4 * (8 / ppt), warps, a.numatoms, kCpChunk);
 }
 
-static int mriq_split_for(const MriqArgs& m, long long warps) {
+static int mriq_split_for(const MriqArgs& m, int vpt, long long warps) {
     if (g_opt.mriq_accurate || g_opt.mriq_split == 0) return 0;
     if (g_opt.mriq_split > 0) return g_opt.mriq_split;
-    return cd_pick_split(static_cast<long long>(m.end - m.start) * 4, warps, m.numK, 64);
+    return cd_pick_split(static_cast<long long>(m.end - m.start) * (8 / vpt), warps, m.numK, 64);
 }
 
 static int run_cp(CpArgs a, unsigned grid0, unsigned block0, cudaStream_t st) {
@@ -424,9 +498,11 @@ static int run_mriq(MriqArgs m, unsigned grid0, unsigned block0, cudaStream_t st
     if (m.start >= m.end) return TK_OK;
     const unsigned threads = cd_threads(block0, 32, 512);
     if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
-    m.k_per_item = mriq_split_for(m, static_cast<long long>(grid0) * (threads / 32));
-    if (g_opt.mriq_accurate) mriq_kernel<true><<<grid0, threads, 0, st>>>(m);
-    else mriq_kernel<false><<<grid0, threads, 0, st>>>(m);
+    const int vpt = g_opt.mriq_vpt == 4 ? 4 : 2;
+    m.k_per_item = mriq_split_for(m, vpt, static_cast<long long>(grid0) * (threads / 32));
+    if (g_opt.mriq_accurate) mriq_kernel<true, 2><<<grid0, threads, 0, st>>>(m);
+    else if (vpt == 4) mriq_kernel<false, 4><<<grid0, threads, 0, st>>>(m);
+    else mriq_kernel<false, 2><<<grid0, threads, 0, st>>>(m);
     return launch_error("mriq_kernel launch");
 }
 
@@ -504,12 +580,99 @@ static int run_mix_stencil(const GemmCall& c, const StencilArgs& s, unsigned cta
     }
 }
 
+// ---- fused launches on CTA pairs ----
+template <int STAGES>
+static int launch_mix_stencil_pair(const GemmCall& c, StencilArgs s, DeviceInfo* d, unsigned ctas, unsigned threads,
+                                   cudaStream_t st) {
+    constexpr int kGemmBytes = Gemm2Smem<STAGES>::kBytes + 1024;
+    auto k = mix_stencil2_kernel<STAGES>;
+    CUtensorMap ta, tb, tg;
+    std::memset(&tg, 0, sizeof(tg));
+    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
+    if (rc != TK_OK) return rc;
+    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, kGemm2BN / 2)) != TK_OK) return rc;
+    int nwarps = static_cast<int>((threads - kGemmThreads) / 32);
+    int ring = 0, smem = kGemmBytes;
+    if (stencil_tma_ok(s)) {
+        const int fit = (kMaxDynSmem - kGemmBytes) / stencil_tma_warp_bytes(kStMinRing);
+        if (fit >= 1) {
+            if (nwarps > fit) nwarps = fit;
+            ring = g_opt.mix_stencil_ring;
+            while (ring > kStMinRing && kGemmBytes + nwarps * stencil_tma_warp_bytes(ring) > kMaxDynSmem) --ring;
+            threads = kGemmThreads + 32u * static_cast<unsigned>(nwarps);
+        }
+    }
+    if (ring > 0) {
+        smem += nwarps * stencil_tma_warp_bytes(ring);
+    } else {
+        const unsigned groups = (threads - kGemmThreads) / kStencilGroup;
+        if (groups == 0) return TK_ERR_LAUNCH_CONFIG;
+        threads = kGemmThreads + groups * kStencilGroup;
+        nwarps = static_cast<int>(groups);
+    }
+    if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+    unsigned pairs = 0;
+    if ((rc = pairs_for(k, d, ctas, threads, smem, &pairs)) != TK_OK) return rc;
+    if (ring > 0 && (rc = make_tmap_grid(&tg, s.A0, s.nx, s.ny, s.nz)) != TK_OK) return rc;
+    stencil_pick_split(s.nz, s.end - s.start, static_cast<long long>(2 * pairs) * nwarps, &s.slabs, &s.per);
+    k<<<2 * pairs, threads, smem, st>>>(ta, tb, c.g, tg, s, ring);
+    return launch_error("mix_stencil2_kernel launch");
+}
+
+static int run_mix_stencil_pair(const GemmCall& c, const StencilArgs& s, DeviceInfo* d, unsigned ctas, unsigned threads,
+                                cudaStream_t st) {
+    switch (g_opt.mix_pair_stages) {
+        case 3: return launch_mix_stencil_pair<3>(c, s, d, ctas, threads, st);
+        case 5: return launch_mix_stencil_pair<5>(c, s, d, ctas, threads, st);
+        default: return launch_mix_stencil_pair<4>(c, s, d, ctas, threads, st);
+    }
+}
+
+template <typename KernelT, typename CdArgsT>
+static int launch_mix_pair_kernel(KernelT k, const GemmCall& c, const CdArgsT& cd_args, DeviceInfo* d, unsigned ctas,
+                                  unsigned threads, int cd_ppt_or_vpt, cudaStream_t st, CdArgsT (*split)(CdArgsT, int, long long)) {
+    constexpr int smem = Gemm2Smem<kStagesPair>::kBytes + 1024;
+    CUtensorMap ta, tb;
+    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
+    if (rc != TK_OK) return rc;
+    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, kGemm2BN / 2)) != TK_OK) return rc;
+    if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+    unsigned pairs = 0;
+    if ((rc = pairs_for(k, d, ctas, threads, smem, &pairs)) != TK_OK) return rc;
+    const CdArgsT a = split(cd_args, cd_ppt_or_vpt, static_cast<long long>(2 * pairs) * ((threads - kGemmThreads) / 32));
+    k<<<2 * pairs, threads, smem, st>>>(ta, tb, c.g, a);
+    return launch_error("fused kernel launch (CTA pairs)");
+}
+
+static CpArgs cp_with_split(CpArgs a, int ppt, long long warps) {
+    a.atoms_per_item = cp_split_for(a, ppt, warps);
+    return a;
+}
+static MriqArgs mriq_with_split(MriqArgs m, int vpt, long long warps) {
+    m.k_per_item = mriq_split_for(m, vpt, warps);
+    return m;
+}
+
+static int launch_mix_pair(const GemmCall& c, const CdCall& cd, DeviceInfo* d, unsigned ctas, unsigned threads,
+                           cudaStream_t st) {
+    if (cd.kind == CD_CP) {
+        const int ppt = g_opt.mix_cp_ppt;
+        if (ppt == 2) return launch_mix_pair_kernel(mix_cp2_kernel<kStagesPair, 2>, c, cd.a, d, ctas, threads, 2, st, cp_with_split);
+        if (ppt == 4) return launch_mix_pair_kernel(mix_cp2_kernel<kStagesPair, 4>, c, cd.a, d, ctas, threads, 4, st, cp_with_split);
+        return launch_mix_pair_kernel(mix_cp2_kernel<kStagesPair, 8>, c, cd.a, d, ctas, threads, 8, st, cp_with_split);
+    }
+    if (g_opt.mix_mriq_vpt == 4)
+        return launch_mix_pair_kernel(mix_mriq2_kernel<kStagesPair, 4>, c, cd.m, d, ctas, threads, 4, st, mriq_with_split);
+    return launch_mix_pair_kernel(mix_mriq2_kernel<kStagesPair, 2>, c, cd.m, d, ctas, threads, 2, st, mriq_with_split);
+}
+
 template <int BN>
 static int launch_mix(const GemmCall& c, CdCall cd, unsigned ctas, unsigned threads, cudaStream_t st) {
     constexpr int STAGES = StagesFor<BN>::value;
     const long long cd_warps = static_cast<long long>(ctas) * ((threads - kGemmThreads) / 32);
     if (cd.kind == CD_CP) cd.a.atoms_per_item = cp_split_for(cd.a, g_opt.mix_cp_ppt, cd_warps);
-    if (cd.kind == CD_MRIQ) cd.m.k_per_item = mriq_split_for(cd.m, cd_warps);
+    const int mvpt = g_opt.mix_mriq_vpt == 4 ? 4 : 2;
+    if (cd.kind == CD_MRIQ) cd.m.k_per_item = mriq_split_for(cd.m, mvpt, cd_warps);
     CUtensorMap ta, tb;
     int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
     if (rc != TK_OK) return rc;
@@ -536,9 +699,15 @@ static int launch_mix(const GemmCall& c, CdCall cd, unsigned ctas, unsigned thre
             break;
         }
         default: {
-            auto k = mix_mriq_kernel<BN, STAGES>;
-            if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
-            k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.m);
+            if (mvpt == 4) {
+                auto k = mix_mriq_kernel<BN, STAGES, 4>;
+                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.m);
+            } else {
+                auto k = mix_mriq_kernel<BN, STAGES, 2>;
+                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.m);
+            }
             break;
         }
     }
@@ -570,6 +739,14 @@ static int run_mix(GemmCall& c, const CdCall& cd_in, unsigned grid0, unsigned bl
     if (cd.empty()) return run_tzgemm(c, grid0, st);
     const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
     const unsigned threads = kGemmThreads + cdt;
+    // The tensor role on CTA pairs pays once the launch holds at least a wave of pair tiles (measured on the
+    // GEMM + stencil pair: 37.3 vs 41.4 us with 2048 tiles, 51.2 vs 55.4 us with 4096; behind by 2 us with 1024 and fewer).
+    const bool pair_ok = c.g.M >= 256 && c.g.N >= 256 && ctas >= 2;
+    const bool pair_wins = c.g.N % 256 == 0 && static_cast<long long>(c.g.end - c.g.start) >= 16ll * (ctas / 2);
+    if (pair_ok && (g_opt.mix_pair > 0 || (g_opt.mix_pair == 0 && pair_wins))) {
+        if (cd.kind == CD_STENCIL) return run_mix_stencil_pair(c, cd.s, d, ctas, threads, st);
+        return launch_mix_pair(c, cd, d, ctas, threads, st);
+    }
     if (cd.kind == CD_STENCIL) return run_mix_stencil(c, cd.s, ctas, threads, st);
     return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_mix<256>(c, cd, ctas, threads, st)
                                                         : launch_mix<128>(c, cd, ctas, threads, st);
@@ -623,7 +800,7 @@ static int generated_mix_launch(CdKind kind, int cd_warps, void** params, int np
     }
     const long long cd_warps_total = static_cast<long long>(ctas) * cd_warps;
     if (kind == CD_CP) cd.a.atoms_per_item = cp_split_for(cd.a, 8, cd_warps_total);
-    if (kind == CD_MRIQ) cd.m.k_per_item = mriq_split_for(cd.m, cd_warps_total);
+    if (kind == CD_MRIQ) cd.m.k_per_item = mriq_split_for(cd.m, 2, cd_warps_total);
     rc = launch(ta, tb, c.g, tg, cd, ring, ctas, threads, smem, static_cast<cudaStream_t>(stream));
     if (rc != TK_OK) return rc;
     return launch_error("generated mix kernel launch");

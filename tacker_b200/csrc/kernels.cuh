@@ -8,6 +8,7 @@
 #include "cd_roles.cuh"
 #include "gemm_role.cuh"
 #include "gemm_role_m256.cuh"
+#include "gemm_role2.cuh"
 #include "stencil_tma.cuh"
 
 namespace tk {
@@ -44,6 +45,16 @@ tzgemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     gemm_role_m256(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), threadIdx.x >> 5, threadIdx.x & 31);
 }
 
+// CTA pairs (clusters of two): 256 x 256 pair tiles with tcgen05.mma.cta_group::2; the grid must be even
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemm2Threads, 1)
+tzgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    gemm_role2<STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), threadIdx.x >> 5, threadIdx.x & 31,
+                       blockIdx.x >> 1, gridDim.x >> 1);
+}
+
 template <int PF>
 __global__ void __launch_bounds__(512) stencil_kernel(const StencilArgs s) {
     stencil_role<PF>(s, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
@@ -72,12 +83,12 @@ __global__ void __launch_bounds__(512, 2) cp_kernel(const CpArgs a) {
     cp_role<PPT, EXACT>(a, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
 }
 
-template <bool ACCURATE>
+template <bool ACCURATE, int VPT>
 __global__ void __launch_bounds__(512, 2) mriq_kernel(const MriqArgs m) {
     __shared__ int item_counter;
     if (threadIdx.x == 0) item_counter = 0;
     __syncthreads();
-    mriq_role<ACCURATE>(m, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    mriq_role<ACCURATE, VPT>(m, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
 }
 
 // Fused kernels: warps 0..5 run the tensor role, the remaining warps the CUDA-core role.  The
@@ -126,7 +137,7 @@ mix_cp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant_
     }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int VPT>
 __global__ void __launch_bounds__(kMaxMixThreadsSfu, 1)
 mix_mriq_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const GemmArgs g, const MriqArgs m) {
@@ -137,7 +148,64 @@ mix_mriq_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         gemm_role<BN, STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
     } else {
         cd_role_begin(&item_counter);
-        mriq_role<false>(m, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+        mriq_role<false, VPT>(m, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    }
+}
+
+// Fused kernels on CTA pairs: the tensor role is gemm_role2 (clusters of two CTAs, 256 x 256 pair tiles), the
+// CUDA-core role is unchanged and still works per CTA.  Its threads only arrive at the cluster barrier the tensor
+// roles of the pair wait on at start-up.
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxMixThreads, 1)
+mix_stencil2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmArgs g, const __grid_constant__ CUtensorMap tmap_grid, const StencilArgs s,
+                    const int ring) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    uint8_t* smem = align_smem_1024(smem_raw);
+    if (warp < kGemmWarps) {
+        gemm_role2<STAGES>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31, blockIdx.x >> 1, gridDim.x >> 1);
+    } else {
+        cluster_arrive();
+        if (ring > 0)
+            stencil_role_tma(&tmap_grid, s, smem + Gemm2Smem<STAGES>::kBytes, ring, warp - kGemmWarps,
+                             (blockDim.x >> 5) - kGemmWarps, threadIdx.x & 31, blockIdx.x, gridDim.x, g.status);
+        else
+            stencil_role<0>(s, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads, blockIdx.x, gridDim.x);
+    }
+}
+
+template <int STAGES, int PPT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxMixThreadsSfu, 1)
+mix_cp2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmArgs g, const CpArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role2<STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31, blockIdx.x >> 1,
+                           gridDim.x >> 1);
+    } else {
+        cluster_arrive();
+        cd_role_begin(&item_counter);
+        cp_role<PPT, false>(a, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    }
+}
+
+template <int STAGES, int VPT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxMixThreadsSfu, 1)
+mix_mriq2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmArgs g, const MriqArgs m) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role2<STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31, blockIdx.x >> 1,
+                           gridDim.x >> 1);
+    } else {
+        cluster_arrive();
+        cd_role_begin(&item_counter);
+        mriq_role<false, VPT>(m, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
     }
 }
 

@@ -46,6 +46,8 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "mriq_accurate")) return &g_opt.mriq_accurate;
     if (!std::strcmp(name, "cp_split")) return &g_opt.cp_split;
     if (!std::strcmp(name, "mriq_split")) return &g_opt.mriq_split;
+    if (!std::strcmp(name, "mriq_vpt")) return &g_opt.mriq_vpt;
+    if (!std::strcmp(name, "mix_mriq_vpt")) return &g_opt.mix_mriq_vpt;
     if (!std::strcmp(name, "stencil_prefetch")) return &g_opt.stencil_prefetch;
     if (!std::strcmp(name, "stencil_tma")) return &g_opt.stencil_tma;
     if (!std::strcmp(name, "stencil_ring")) return &g_opt.stencil_ring;
@@ -53,6 +55,9 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "l2_hints")) return &g_opt.l2_hints;
     if (!std::strcmp(name, "tzgemm_m256")) return &g_opt.tzgemm_m256;
     if (!std::strcmp(name, "mix_stencil_cfg")) return &g_opt.mix_stencil_cfg;
+    if (!std::strcmp(name, "tzgemm_pair")) return &g_opt.tzgemm_pair;
+    if (!std::strcmp(name, "mix_pair")) return &g_opt.mix_pair;
+    if (!std::strcmp(name, "mix_pair_stages")) return &g_opt.mix_pair_stages;
     return nullptr;
 }
 
@@ -62,6 +67,8 @@ TK_API int tk_set_option(const char* name, int value) {
     if (slot == &g_opt.tzgemm_bn && value != 0 && value != 128 && value != 256) return TK_ERR_ARGS;
     if ((slot == &g_opt.cp_ppt || slot == &g_opt.mix_cp_ppt) && value != 8 && value != 4 && value != 2) return TK_ERR_ARGS;
     if (slot == &g_opt.stencil_prefetch && value != 0 && value != 8) return TK_ERR_ARGS;
+    if (slot == &g_opt.mix_pair_stages && (value < 3 || value > 5)) return TK_ERR_ARGS;
+    if ((slot == &g_opt.mriq_vpt || slot == &g_opt.mix_mriq_vpt) && value != 2 && value != 4) return TK_ERR_ARGS;
     if ((slot == &g_opt.stencil_ring || slot == &g_opt.mix_stencil_ring) && (value < kStMinRing || value > kStMaxRing))
         return TK_ERR_ARGS;
     *slot = value;
@@ -381,7 +388,7 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
     if (k == "gptb_mriq" || k == "ori_mriq") {
         info->threads_cd_min = 32;
         info->threads_cd_default = 256;
-        return fill_info(mriq_kernel<false>, 256, 0, info);
+        return fill_info(mriq_kernel<false, 2>, 256, 0, info);
     }
     info->threads_tensor = kGemmThreads;
     info->tmem_columns = 512;
@@ -395,7 +402,7 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
         return fill_info(mix_cp_kernel<256, kStages256, 8>, kGemmThreads + 256, gsm, info);
     }
     info->threads_cd_min = 32;
-    return fill_info(mix_mriq_kernel<256, kStages256>, kGemmThreads + 256, gsm, info);
+    return fill_info(mix_mriq_kernel<256, kStages256, 4>, kGemmThreads + 256, gsm, info);
 }
 
 // =================================================================================================

@@ -26,7 +26,7 @@ def test_emitted_source_compiles_and_exports_its_launcher(tmp_path):
 
     c = [x for x in data.fuse_kernel_info("mriq") if x.r2 == 8][0]
     src = gen_mix.generate_mixed_kernel(c)
-    assert "__launch_bounds__(448, 1)" in src and "mriq_role<false>" in src and "gemm_role<256, 3>" in src
+    assert "__launch_bounds__(448, 1)" in src and "mriq_role<false, 2>" in src and "gemm_role<256, 3>" in src
     cu = gen_run.emit(c, str(tmp_path))
     so = gen_run.compile_module(cu)
     mod = ctypes.CDLL(so)

@@ -157,6 +157,69 @@ def _tzgemm_mriq(cuda, oracle, ops, cd_threads, split):
     assert np.abs(out["fused"][2] - i64).max() <= 1e-5 * scale
 
 
+@pytest.mark.parametrize("cd", ["stencil", "cp", "mriq"])
+@pytest.mark.parametrize("tz_range", [(0, 96), (7, 70), (95, 96)])
+def test_fused_kernels_on_cta_pairs(cuda, oracle, cd, tz_range):
+    """The fused kernels whose tensor role runs on clusters of two CTAs (option mix_pair = 1) leave what the
+    single-CTA fused kernels leave: GEMM tiles and stencil bit for bit, Coulomb / MRI-Q bit for bit with unsplit
+    work items."""
+    from tacker_b200 import ops
+
+    M, N, K = 512, 768, 128                       # 8 x 12 = 96 tiles
+    A, B, a, b = _gemm_setup(cuda, oracle, M, N, K, 31)
+    st = cuda.cuda.current_stream().cuda_stream
+    nz, ny, nx = 8, 16, 256
+    A0 = stencil_inputs(oracle, nx, ny, nz, seed=9)
+    atoms = coulomb_inputs(oracle, 100, 16.0, seed=4, spacing=0.125, zplane=2.0)
+    raw = to_dev(cuda, atoms)
+    packed = cuda.empty_like(raw)
+    ops.cp_pack_atoms(raw.data_ptr(), atoms.shape[0], 2.0, packed.data_ptr(), st)
+    k, phi, xyz = mriq_inputs(oracle, 96, 1024, seed=8)
+    dk = [to_dev(cuda, k[i]) for i in range(3)]
+    dphi = [to_dev(cuda, phi[i]) for i in range(2)]
+    dx = [to_dev(cuda, xyz[i]) for i in range(3)]
+    kv = cuda.empty((96, 4), dtype=cuda.float32, device="cuda")
+    ops.mriq_pack_kvalues(dk[0].data_ptr(), dk[1].data_ptr(), dk[2].data_ptr(), dphi[0].data_ptr(),
+                          dphi[1].data_ptr(), 96, kv.data_ptr(), st)
+    out = {}
+    ops.set_option("cp_split", 0)
+    ops.set_option("mriq_split", 0)
+    try:
+        for pair in (-1, 1):
+            ops.set_option("mix_pair", pair)
+            Cd = cuda.full((M, N), -3.0, dtype=cuda.float32, device="cuda")
+            tz = ops.gptb_tzgemm(A.data_ptr(), B.data_ptr(), Cd.data_ptr(), M, N, K, alpha=1.1, start=tz_range[0],
+                                 end=tz_range[1], grid=6, round_dims=False)
+            if cd == "stencil":
+                d0, d1 = to_dev(cuda, A0), to_dev(cuda, np.full_like(A0, 9.0))
+                cdk = ops.gptb_stencil(0.5, 0.25, d0.data_ptr(), d1.data_ptr(), nx, ny, nz, grid=6, block=192)
+                res = [d1]
+            elif cd == "cp":
+                lat = cuda.zeros((32, 256), dtype=cuda.float32, device="cuda")
+                cdk = ops.gptb_cp(atoms.shape[0], 0.125, lat.data_ptr(), packed.data_ptr(), 256, 32, grid=6, block=192)
+                res = [lat]
+            else:
+                qr = cuda.zeros(1024, dtype=cuda.float32, device="cuda")
+                qi = cuda.zeros(1024, dtype=cuda.float32, device="cuda")
+                cdk = ops.gptb_mriq(96, dx[0].data_ptr(), dx[1].data_ptr(), dx[2].data_ptr(), qr.data_ptr(), qi.data_ptr(),
+                                    kv.data_ptr(), 1024, grid=6, block=192)
+                res = [qr, qi]
+            ops.mix(cdk, tz, cd_threads=192, grid=6).execute(st)
+            cuda.cuda.synchronize()
+            assert ops.device_status() == 0
+            out[pair] = [Cd.cpu().numpy()] + [r.cpu().numpy() for r in res]
+    finally:
+        ops.set_option("mix_pair", 0)
+        ops.set_option("cp_split", -1)
+        ops.set_option("mriq_split", -1)
+    for x, y in zip(out[-1], out[1]):
+        assert np.array_equal(x, y)
+    written = out[1][0] != -3.0
+    assert written.sum() == (tz_range[1] - tz_range[0]) * 64 * 64
+    assert np.abs(out[1][0] - oracle.tzgemm_f64(a, b, alpha=1.1))[written].max() <= 1e-3 * K
+    assert np.abs(out[1][1]).max() > 0
+
+
 def test_fused_full_size_config2_properties(cuda, oracle):
     """GEMM 4096 x 4096 x 1024 fused with one 512 x 512 x 64 sweep per launch, GEMM tiles split over 10 launches."""
     from tacker_b200 import ops

@@ -89,7 +89,30 @@ def test_m256_super_tile_kernel(cuda, oracle, shape):
     assert np.array_equal(out[1], out[-1])
 
 
-@pytest.mark.parametrize("bn", [128, 256, 512])
+@pytest.mark.parametrize("grid", [2, 5, 148])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (384, 320, 192), (1024, 1024, 1024), (640, 1280, 256), (128, 512, 64)])
+def test_cta_pair_kernel(cuda, oracle, shape, grid):
+    """tzgemm on clusters of two CTAs (tcgen05.mma.cta_group::2, 256 x 256 pair tiles): same results as the 128-row
+    form, bit for bit -- including M = 128 (2k + 1), where the second CTA of the last pair has no rows, N not a
+    multiple of 256, and a shape the pair form does not take (M = 128: the launcher falls back)."""
+    from tacker_b200 import ops
+
+    M, N, K = shape
+    a_bits, a, b_bits, b = gemm_inputs(oracle, M, N, K, seed=M + K + 1)
+    out = {}
+    for mode in (-1, 1):
+        ops.set_option("tzgemm_pair", mode)
+        ops.set_option("tzgemm_m256", -1)
+        try:
+            out[mode] = _run(cuda, ops, a_bits, b_bits, M, N, K, 1.1, grid=grid)
+        finally:
+            ops.set_option("tzgemm_pair", 0)
+            ops.set_option("tzgemm_m256", 0)
+    _check(oracle, out[1], a, b, 1.1)
+    assert np.array_equal(out[1], out[-1])
+
+
+@pytest.mark.parametrize("bn", [128, 256, 512, 1024])
 @pytest.mark.parametrize("rng", [(0, 1), (5, 6), (3, 17), (7, 8), (0, 24), (23, 24), (9, 9), (11, 40)])
 def test_virtual_block_range_is_exact(cuda, oracle, bn, rng):
     """Tiles outside [start, end) keep the sentinel; tiles inside match (src/gptb_kernel/tzgemm_kernel.cu:243-249)."""
@@ -99,6 +122,8 @@ def test_virtual_block_range_is_exact(cuda, oracle, bn, rng):
     start, end = rng
     if bn == 512:                    # stands for the 256 x 256 super-tile kernel
         ops.set_option("tzgemm_m256", 1)
+    elif bn == 1024:                 # stands for the kernel on CTA pairs
+        ops.set_option("tzgemm_pair", 1)
     else:
         ops.set_option("tzgemm_bn", bn)
         ops.set_option("tzgemm_m256", -1)
@@ -108,6 +133,7 @@ def test_virtual_block_range_is_exact(cuda, oracle, bn, rng):
     finally:
         ops.set_option("tzgemm_bn", 0)
         ops.set_option("tzgemm_m256", 0)
+        ops.set_option("tzgemm_pair", 0)
     want = oracle.tzgemm_f64(a, b, alpha=1.1)
     inside = np.zeros((M, N), dtype=bool)
     for p in range(start, min(end, 24)):
