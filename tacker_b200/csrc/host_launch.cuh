@@ -33,7 +33,7 @@ static int cuda_fail(cudaError_t e, const char* what) {
 struct Options {
     int tzgemm_bn = 0;
     int cp_exact = 0;
-    int cp_ppt = 4;      // solo kernel: points per thread and work item (8 = the reference's granularity)
+    int cp_ppt = 8;      // solo kernel: points per thread and work item (8 = the reference's granularity, measured best)
     int mix_cp_ppt = 8;  // fused kernel
     int mriq_accurate = 0;
     // second dimension of the Coulomb / MRI-Q work items (fast modes only): -1 = the host picks the atoms /

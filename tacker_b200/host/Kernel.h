@@ -38,6 +38,11 @@ public:
     void* kernelFunc = nullptr;  // tk_launch_fn
     unsigned mixable = 0;        // 0 = never fused, 1 = GEMM (getArgs: m, n, k), 2 = convolution (14 ints)
     bool initialized = false;
+    // Stream on which a repeated initParams() queues its device work (re-zeroing of accumulated outputs): set it to
+    // the stream the kernel is launched on, so that the reset is ordered against those launches.  The reference's
+    // blocking streams gave that ordering implicitly; the streams of this runtime do not synchronise with the
+    // null stream.
+    stream_t initStream = nullptr;
 
 protected:
     virtual void executeImpl(stream_t stream) = 0;

@@ -30,6 +30,8 @@ public:
     std::string taskName;
     std::vector<Kernel*> kernels;
     TaskType taskType = LC;
+    // Stream on which initExecution() queues the upload of the task's input: the stream its kernels run on.
+    stream_t execStream = nullptr;
     void* Input[3] = {nullptr, nullptr, nullptr};
     void** Result = nullptr;
     void* InputHost[3] = {nullptr, nullptr, nullptr};

@@ -4,6 +4,7 @@
 #include <chrono>
 #include <cmath>
 #include <cstdio>
+#include <functional>
 #include <map>
 #include <memory>
 
@@ -71,6 +72,29 @@ void mixcublasSgemm(TzLayer* layer, GPTBKernel* cd, int cd_start_blk, int cd_end
 TaskManager::TaskManager(Task* lc, const std::string& a, const std::string& b)
     : lc_task(lc), be_task1_name(a), be_task2_name(b) {}
 
+// one launch of blocks [start, end) of a persistent kernel, timed with events (median of five)
+float TaskManager::timedBlocks(GPTBKernel* k, int start, int end, stream_t stream) {
+    Backend& be = backend();
+    void* e0 = be.eventCreate();
+    void* e1 = be.eventCreate();
+    const int keep_s = k->gptbParams.ptb_start_block_pos, keep_e = k->gptbParams.ptb_end_block_pos;
+    k->gptbParams.ptb_start_block_pos = start;
+    k->gptbParams.ptb_end_block_pos = end;
+    std::vector<float> t;
+    for (int i = 0; i < 5; ++i) {
+        be.eventRecord(e0, stream);
+        k->execute(stream);
+        be.eventRecord(e1, stream);
+        t.push_back(be.eventElapsedMs(e0, e1));
+    }
+    k->gptbParams.ptb_start_block_pos = keep_s;
+    k->gptbParams.ptb_end_block_pos = keep_e;
+    be.eventDestroy(e0);
+    be.eventDestroy(e1);
+    std::sort(t.begin(), t.end());
+    return t[t.size() / 2];
+}
+
 float TaskManager::blockRatio(const std::string& pair, int k_global) {
     float r = fget_kernel_info(pair, std::to_string(k_global));
     if (r == static_cast<float>(JSON_NOT_FOUND)) {
@@ -84,9 +108,16 @@ float TaskManager::blockRatio(const std::string& pair, int k_global) {
     return r;
 }
 
-ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream) {
+ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream) { return schedule(mode, stream, false); }
+
+ScheduleResult TaskManager::execute_with_one_cd_kernel(ExecutionMode mode, stream_t stream) {
+    return schedule(mode, stream, true);
+}
+
+ScheduleResult TaskManager::schedule(ExecutionMode mode, stream_t stream, bool one_cd) {
     Backend& be = backend();
     ScheduleResult res;
+    lc_task->execStream = stream;  // the input upload of every pass is ordered before the pass's kernels
     void* ev0 = be.eventCreate();
     void* ev1 = be.eventCreate();
     auto timed = [&](Kernel* k) {
@@ -124,7 +155,9 @@ ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream)
 
     // ---- the best-effort kernels alone (src/TaskManager.cu:533-561) ----
     GPTBKernel* be_kernel1 = createKernel(be_task1_name);
-    GPTBKernel* be_task2 = be_task2_name.empty() ? nullptr : createKernel(be_task2_name);
+    GPTBKernel* be_task2 = (one_cd || be_task2_name.empty()) ? nullptr : createKernel(be_task2_name);
+    be_kernel1->kernel_->initStream = stream;  // re-zeroing of its outputs is ordered against the fused launches
+    if (be_task2) be_task2->kernel_->initStream = stream;
     for (int i = 0; i < 3; ++i) {
         be_kernel1->execute(stream);
         if (be_task2) be_task2->execute(stream);
@@ -133,7 +166,16 @@ ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream)
     res.be1_ms = timed(be_kernel1);
     if (be_task2) res.be2_ms = timed(be_task2);
     const int be_blocks = be_kernel1->gptbParams.ptb_end_block_pos;
+    // What a few blocks of the best-effort kernel cost when they are launched alone: a launch of one block, measured.
+    // The reference charges blocks x (full time / all blocks); on this GPU a whole job lasts tens of microseconds, so
+    // the fixed part of a launch is a large share of a small quantum and leaving it out makes every small fusion look
+    // like a loss.
+    const float be1_fixed_ms = std::min(res.be1_ms, timedBlocks(be_kernel1, 0, 1, stream));
+    auto be1_solo_ms = [&](int blocks) {
+        return blocks <= 0 ? 0.0f : be1_fixed_ms + (res.be1_ms - be1_fixed_ms) * blocks / std::max(be_blocks, 1);
+    };
     const std::string pair = "tzgemm_" + be_task1_name;
+    const int sm_num = be.smCount();
 
     // ---- the scheduling passes (src/TaskManager.cu:563-656) ----
     std::vector<char> skip(n, 0);  // layers whose fusion did not pay off in an earlier pass are not fused again
@@ -152,6 +194,7 @@ ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream)
             int cd_block_num = 0;
             float duration;
             const bool fuse = lc_kernel->mixable != 0 && !skip[idx] && !(qos_headroom < lc_headroom_vec[idx] + qos_guard_ms);
+            bool fused = fuse;
             if (!fuse) {
                 duration = timed(lc_kernel);
             } else {
@@ -164,24 +207,38 @@ ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream)
                 if (mode == ExecutionMode::Tacker) {
                     cd_block_num = be_blocks;
                 } else {
-                    cd_block_num = std::min(static_cast<int>(layer->tiles() * blockRatio(pair, layer->K_pad)), be_blocks);
+                    cd_block_num = static_cast<int>(layer->tiles() * blockRatio(pair, layer->K_pad));
+                    // the one-kernel variant deals whole rounds of blocks: a multiple of the SM count, at least one
+                    // round (src/TaskManager.cu:862-863, 878-879, where SM_NUM is a compile-time constant)
+                    if (one_cd && cd_block_num > 0) cd_block_num = cd_block_num < sm_num ? sm_num : (cd_block_num / sm_num) * sm_num;
+                    cd_block_num = std::min(cd_block_num, be_blocks);
                 }
-                int cd_start = cd_cursor, cd_end = std::min(cd_cursor + cd_block_num, be_blocks);
-                if (cd_end <= cd_start) {  // the best-effort job is finished: start its next instance
-                    cd_start = 0;
-                    cd_end = std::min(cd_block_num, be_blocks);
+                if (cd_block_num <= 0) {  // the table has nothing to co-run with this layer: plain launch, cursor untouched
+                    fused = false;
+                    cd_block_num = 0;
+                    duration = timed(lc_kernel);
+                } else {
+                    int cd_start, cd_end;
+                    if (one_cd) {  // always the first blocks of the best-effort kernel (src/TaskManager.cu:866)
+                        cd_start = be_kernel1->gptbParams.ptb_start_block_pos;
+                        cd_end = std::min(cd_start + cd_block_num, be_blocks);
+                    } else {       // walk through the job; a finished job starts its next instance
+                        if (cd_cursor >= be_blocks) cd_cursor = 0;
+                        cd_start = cd_cursor;
+                        cd_end = std::min(cd_cursor + cd_block_num, be_blocks);
+                        cd_cursor = cd_end;
+                    }
+                    cd_block_num = cd_end - cd_start;
+                    be.eventRecord(ev0, stream);
+                    if (lc_kernel->mixable == 1) mixcublasSgemm(layer, be_kernel1, cd_start, cd_end, stream);
+                    else mixcudnnConvolutionForward(layer, be_kernel1, cd_start, cd_end, stream);
+                    be.eventRecord(ev1, stream);
+                    duration = be.eventElapsedMs(ev0, ev1);
                 }
-                cd_block_num = cd_end - cd_start;
-                be.eventRecord(ev0, stream);
-                if (lc_kernel->mixable == 1) mixcublasSgemm(layer, be_kernel1, cd_start, cd_end, stream);
-                else mixcudnnConvolutionForward(layer, be_kernel1, cd_start, cd_end, stream);
-                be.eventRecord(ev1, stream);
-                duration = be.eventElapsedMs(ev0, ev1);
-                cd_cursor = cd_end >= be_blocks ? 0 : cd_end;
             }
             // account the fusion only where it beat running the same work one after the other
-            const float unfused = lc_kernel_time_vec[idx] + res.be1_ms * cd_block_num / std::max(be_blocks, 1);
-            if (!fuse) {
+            const float unfused = lc_kernel_time_vec[idx] + be1_solo_ms(cd_block_num);
+            if (!fused) {
                 qos_headroom -= lc_kernel_time_vec[idx];
             } else if (duration > unfused) {
                 qos_headroom -= duration;  // it ran, so its time is spent (the reference books the solo time here)
@@ -202,11 +259,37 @@ ScheduleResult TaskManager::executeAllTasks(ExecutionMode mode, stream_t stream)
     std::printf("[Ori] be_task1: %s, be_task2: %s\n", be_task1_name.c_str(), be_task2_name.c_str());
     std::printf("[Ori] BE task1 + task2 took %f + %f = %f ms to execute.\n", res.be1_ms, res.be2_ms,
                 res.be1_ms + res.be2_ms);
-    // best-effort work done inside the budget: blocks co-run with the LC task, then the leftover budget
+    // best-effort work done inside the budget: blocks co-run with the LC task (stage 1), then the leftover budget
     res.stage1_be_ms = res.be_blocks * res.be1_ms / std::max(be_blocks, 1);
-    res.stage2_be_ms = std::max(0.0f, qos_headroom);
-    std::printf("[Result] %s BE task took %f + %f(%f) = %f ms to execute.\n", mode == ExecutionMode::Aker ? "Aker" : "Tacker",
-                res.stage1_be_ms, res.stage2_be_ms, qos_headroom, res.stage1_be_ms + res.stage2_be_ms);
+    if (one_cd) {  // src/TaskManager.cu:990-1000: the leftover is only reported
+        res.stage2_be_ms = std::max(0.0f, qos_headroom);
+        std::printf("[Result] %s throughput %f + %f = %f ms.\n", mode == ExecutionMode::Aker ? "Aker" : "Tacker",
+                    res.stage1_be_ms, res.stage2_be_ms, res.stage1_be_ms + res.stage2_be_ms);
+    } else {
+        // Stage 2 (src/TaskManager.cu:672-709 fills the leftover with a fused best-effort pair; such pairs are not
+        // built here): the best-effort kernels run alone, whole launches in turn, for as long as the next launch is
+        // predicted to fit into what the latency budget has left.  What is reported is what ran, not the budget.
+        const float window = std::max(0.0f, qos_headroom);
+        float predicted = 0.0f;
+        be.eventRecord(ev0, stream);
+        for (int turn = 0;; ++turn) {
+            GPTBKernel* k = (be_task2 && (turn & 1)) ? be_task2 : be_kernel1;
+            const float t = k == be_task2 ? res.be2_ms : res.be1_ms;
+            if (t <= 0.0f || predicted + t > window) break;
+            k->execute(stream);
+            predicted += t;
+            res.stage2_launches += 1;
+            if (k == be_task2) res.stage2_blocks2 += be_task2->gptbParams.ptb_end_block_pos;
+            else res.stage2_blocks1 += be_blocks;
+        }
+        be.eventRecord(ev1, stream);
+        res.stage2_be_ms = res.stage2_launches > 0 ? be.eventElapsedMs(ev0, ev1) : 0.0f;
+        std::printf("[Stage2] %d solo launches in the %f ms left: %lld blocks of %s, %lld blocks of %s, %f ms of device time\n",
+                    res.stage2_launches, window, res.stage2_blocks1, be_task1_name.c_str(), res.stage2_blocks2,
+                    be_task2 ? be_task2_name.c_str() : "-", res.stage2_be_ms);
+        std::printf("[Result] %s BE task took %f + %f(%f) = %f ms to execute.\n", mode == ExecutionMode::Aker ? "Aker" : "Tacker",
+                    res.stage1_be_ms, res.stage2_be_ms, qos_headroom, res.stage1_be_ms + res.stage2_be_ms);
+    }
     be.eventDestroy(ev0);
     be.eventDestroy(ev1);
     return res;
@@ -216,6 +299,8 @@ ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pa
                                             double qos_factor, uint64_t seed, stream_t stream) {
     Backend& be = backend();
     ColocationResult r;
+    lc_task->execStream = stream;
+    be_task->execStream = stream;
     // ---- warm both tasks ----
     for (int i = 0; i < warmup_passes; ++i) {
         lc_task->initExecution();
@@ -305,5 +390,166 @@ ColocationResult TaskManager::runColocation(Task* be_task, int be_queries_per_pa
     r.lc_p99_ms = percentile(lat, 0.99);
     r.be_qps = r.be_queries / std::max(r.seconds, 1e-9);
     r.qos_met = r.lc_p99_ms <= r.qos_bound_ms;
+    return r;
+}
+
+FusedColocationResult TaskManager::runFusedColocation(double seconds, double qps, double qos_factor, uint64_t seed,
+                                                      stream_t stream) {
+    Backend& be = backend();
+    FusedColocationResult r;
+    lc_task->execStream = stream;
+    GPTBKernel* bek = createKernel(be_task1_name);
+    bek->kernel_->initStream = stream;
+    const int be_blocks = bek->gptbParams.ptb_end_block_pos;
+    const std::string pair = "tzgemm_" + be_task1_name;
+    r.be_kernel = be_task1_name;
+    r.be_blocks_per_job = be_blocks;
+    void* ev0 = be.eventCreate();
+    void* ev1 = be.eventCreate();
+    auto timed_ms = [&](const std::function<void()>& body, int reps) {
+        be.eventRecord(ev0, stream);
+        for (int i = 0; i < reps; ++i) body();
+        be.eventRecord(ev1, stream);
+        return be.eventElapsedMs(ev0, ev1) / reps;
+    };
+    for (int i = 0; i < warmup_passes; ++i) {
+        lc_task->initExecution();
+        lc_task->enqueue(stream);
+        bek->execute(stream);
+    }
+    be.streamSync(stream);
+    const float be_full_ms = timed_ms([&] { bek->execute(stream); }, 3);
+    const float be_fixed_ms = std::min(be_full_ms, timedBlocks(bek, 0, 1, stream));  // see schedule()
+
+    // ---- which layers to fuse, and with how many blocks: the profiled table, then a measurement per layer ----
+    const size_t n = lc_task->kernels.size();
+    std::vector<int> ride(n, 0);  // best-effort blocks riding in layer idx (0 = plain launch)
+    for (size_t idx = 0; idx < n; ++idx) {
+        Kernel* k = lc_task->kernels[idx];
+        if (k->mixable == 0) continue;
+        r.mixable_layers += 1;
+        TzLayer* layer = static_cast<TzLayer*>(k);
+        const int nb = std::min(static_cast<int>(layer->tiles() * blockRatio(pair, layer->K_pad)), be_blocks);
+        if (nb <= 0) continue;
+        for (int i = 0; i < 2; ++i) {
+            k->execute(stream);
+            run_fused(layer, bek, 0, nb, stream);
+        }
+        const float solo = timed_ms([&] { k->execute(stream); }, 5);
+        const float fused = timed_ms([&] { run_fused(layer, bek, 0, nb, stream); }, 5);
+        // the rule of src/TaskManager.cu:631-645, with the measured fixed cost of a small solo launch
+        if (fused <= solo + be_fixed_ms + (be_full_ms - be_fixed_ms) * nb / be_blocks) {
+            ride[idx] = nb;
+            r.fused_layers += 1;
+            r.blocks_per_fused_query += nb;
+        }
+    }
+
+    // ---- the LC pass as graphs: plain, and fused variants that walk through the best-effort job ----
+    lc_task->initExecution();
+    lc_task->enqueueGraph(stream);  // first use captures
+    be.streamSync(stream);
+    const long long per_query = r.blocks_per_fused_query;
+    const int nvar = per_query > 0 ? static_cast<int>(std::max<long long>(1, std::min<long long>(8, be_blocks / per_query))) : 0;
+    std::vector<void*> fused_graphs;
+    for (int v = 0; v < nvar; ++v) {
+        auto body = [&] {
+            int cursor = static_cast<int>((static_cast<long long>(v) * per_query) % be_blocks);
+            for (size_t idx = 0; idx < n; ++idx) {
+                Kernel* k = lc_task->kernels[idx];
+                if (ride[idx] == 0) {
+                    k->execute(stream);
+                    continue;
+                }
+                if (cursor + ride[idx] > be_blocks) cursor = 0;  // the next instance of the job
+                run_fused(static_cast<TzLayer*>(k), bek, cursor, cursor + ride[idx], stream);
+                cursor += ride[idx];
+            }
+        };
+        body();  // lazy set-up outside the capture
+        be.streamSync(stream);
+        void* g = be.graphCapture(stream, body);
+        if (!g) break;  // a backend that cannot capture: the fused phase falls back to the plain pass
+        fused_graphs.push_back(g);
+    }
+    r.lc_graph_ms = timed_ms([&] { lc_task->enqueueGraph(stream); }, 20);
+    if (!fused_graphs.empty()) r.lc_fused_graph_ms = timed_ms([&] { be.graphLaunch(fused_graphs[0], stream); }, 20);
+
+    // ---- Poisson arrivals, the same for every phase ----
+    std::vector<double> arrivals;
+    double t = 0.0;
+    for (uint64_t i = 0; t < seconds * 1e3; ++i) {
+        t += -std::log(1.0 - static_cast<double>(tk_unit_draw(seed, i))) / qps * 1e3;
+        arrivals.push_back(t);
+    }
+    // idle-time chunk of the best-effort kernel: about be_chunk_ms of device time
+    const int chunk_blocks = std::max(1, std::min(be_blocks, static_cast<int>(be_blocks * be_chunk_ms / std::max(be_full_ms, 1e-6f))));
+    int idle_cursor = 0;
+    auto idle_chunk = [&]() -> int {
+        if (idle_cursor >= be_blocks) idle_cursor = 0;
+        const int s0 = idle_cursor, e0 = std::min(idle_cursor + chunk_blocks, be_blocks);
+        const int keep_s = bek->gptbParams.ptb_start_block_pos, keep_e = bek->gptbParams.ptb_end_block_pos;
+        bek->gptbParams.ptb_start_block_pos = s0;
+        bek->gptbParams.ptb_end_block_pos = e0;
+        bek->execute(stream);
+        bek->gptbParams.ptb_start_block_pos = keep_s;
+        bek->gptbParams.ptb_end_block_pos = keep_e;
+        idle_cursor = e0;
+        return e0 - s0;
+    };
+    // mode 0: LC alone; 1: time-sliced; 2: fused + time-sliced
+    auto phase = [&](int mode, std::vector<double>& lat, long long* blocks, long long* blocks_in_lc, long long* nfused,
+                     long long* nplain, double bound_ms) {
+        size_t next = 0, variant = 0;
+        const double start = now_ms();
+        while (true) {
+            const double now = now_ms() - start;
+            if (now >= seconds * 1e3) break;
+            if (next < arrivals.size() && arrivals[next] <= now) {
+                lc_task->initExecution();
+                // fuse only when the time already spent waiting leaves room for the longer fused pass
+                const bool fuse = mode == 2 && !fused_graphs.empty() &&
+                                  (now - arrivals[next]) + 1.25 * r.lc_fused_graph_ms <= bound_ms;
+                if (fuse) {
+                    be.graphLaunch(fused_graphs[variant], stream);
+                    variant = (variant + 1) % fused_graphs.size();
+                    *blocks += per_query;
+                    *blocks_in_lc += per_query;
+                    *nfused += 1;
+                } else {
+                    lc_task->enqueueGraph(stream);
+                    if (nplain) *nplain += 1;
+                }
+                be.streamSync(stream);
+                lat.push_back(now_ms() - start - arrivals[next]);
+                ++next;
+                continue;
+            }
+            if (mode == 0) continue;
+            *blocks += idle_chunk();
+            be.streamSync(stream);
+        }
+        return (now_ms() - start) / 1e3;
+    };
+    std::vector<double> solo, ts, fu;
+    phase(0, solo, nullptr, nullptr, nullptr, nullptr, 0.0);
+    r.lc_solo_p50_ms = percentile(solo, 0.50);
+    r.lc_solo_p99_ms = percentile(solo, 0.99);
+    r.qos_bound_ms = qos_factor * r.lc_solo_p99_ms;
+    long long dummy = 0;
+    const double ts_s = phase(1, ts, &r.ts_be_blocks, &dummy, &dummy, nullptr, r.qos_bound_ms);
+    r.ts_lc_p50_ms = percentile(ts, 0.50);
+    r.ts_lc_p99_ms = percentile(ts, 0.99);
+    r.ts_be_blocks_per_s = r.ts_be_blocks / std::max(ts_s, 1e-9);
+    r.ts_qos_met = r.ts_lc_p99_ms <= r.qos_bound_ms;
+    r.seconds = phase(2, fu, &r.fu_be_blocks, &r.fu_be_blocks_in_lc, &r.fu_fused_queries, &r.fu_plain_queries, r.qos_bound_ms);
+    r.lc_served = static_cast<long long>(fu.size());
+    r.fu_lc_p50_ms = percentile(fu, 0.50);
+    r.fu_lc_p99_ms = percentile(fu, 0.99);
+    r.fu_be_blocks_per_s = r.fu_be_blocks / std::max(r.seconds, 1e-9);
+    r.fu_qos_met = r.fu_lc_p99_ms <= r.qos_bound_ms;
+    for (void* g : fused_graphs) be.graphDestroy(g);
+    be.eventDestroy(ev0);
+    be.eventDestroy(ev1);
     return r;
 }

@@ -30,6 +30,7 @@ DnnArena::~DnnArena() {
 float* DnnArena::act(size_t floats) {
     void* p = backend().deviceAlloc(floats * sizeof(float));
     backend().fillZero(p, floats * sizeof(float), nullptr);
+    backend().streamSync(nullptr);  // set-up time: landed before any launch on another stream can read it
     owned.push_back(p);
     bytes += floats * sizeof(float);
     return static_cast<float*>(p);
@@ -38,6 +39,7 @@ float* DnnArena::act(size_t floats) {
 void* DnnArena::half(size_t halves) {
     void* p = backend().deviceAlloc(halves * 2);
     backend().fillZero(p, halves * 2, nullptr);
+    backend().streamSync(nullptr);
     owned.push_back(p);
     bytes += halves * 2;
     return p;

@@ -8,7 +8,7 @@ DnnTask::~DnnTask() {}
 
 void DnnTask::initExecution() {
     if (input && !hostInput.empty())
-        backend().upload(input, hostInput.data(), hostInput.size() * sizeof(float), nullptr);
+        backend().upload(input, hostInput.data(), hostInput.size() * sizeof(float), execStream);
 }
 
 size_t DnnTask::numMixable() const {

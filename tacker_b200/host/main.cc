@@ -1,8 +1,11 @@
 // aker -- command line of the runtime (reference: src/main.cu:246-336).
 //   aker -s <aker|tacker> -m <vgg16|resnet50|bert> [-d device] [-c config_dir]
-//        [--colocate seconds] [--qps rate] [--qos factor] [--be model] [--be-chunk-ms ms]
-// Without --colocate it runs the reference's experiment (both modes unless -s picks one); with it, the
-// request-driven co-location of `-m` (latency-critical) with `--be` (best-effort) on this GPU.
+//        [--colocate seconds] [--colocate-fused seconds] [--qps rate] [--qos factor] [--be model] [--be-chunk-ms ms]
+//        [--one-cd] [--be-kernel name] [--be-kernel2 name]
+// Without --colocate it runs the reference's experiment (both modes unless -s picks one; --one-cd: its variant
+// with one best-effort kernel); with --colocate, the request-driven co-location of `-m` (latency-critical) with the
+// model `--be` (best-effort) on this GPU; with --colocate-fused, the co-location with the benchmark kernel of the
+// configuration as the best-effort job, time-sliced and fused.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -28,9 +31,10 @@ static void usage(const char* argv0) {
 }
 
 int main(int argc, char* argv[]) {
-    std::string system_name, model, config_dir = "config", be_model = "bert";
+    std::string system_name, model, config_dir = "config", be_model = "bert", be_kernel_a, be_kernel_b;
     int device_no = 0;
-    double colocate = 0.0, qps = 200.0, qos = 1.5, be_chunk = -1.0;
+    double colocate = 0.0, colocate_fused = 0.0, qps = 200.0, qos = 1.5, be_chunk = -1.0;
+    bool one_cd = false;
     for (int i = 1; i < argc; ++i) {
         const std::string a = argv[i];
         auto val = [&](const char* what) -> std::string {
@@ -45,6 +49,10 @@ int main(int argc, char* argv[]) {
         else if (a == "-d" || a == "--device") device_no = std::atoi(val("-d").c_str());
         else if (a == "-c" || a == "--config") config_dir = val("-c");
         else if (a == "--colocate") colocate = std::atof(val("--colocate").c_str());
+        else if (a == "--colocate-fused") colocate_fused = std::atof(val("--colocate-fused").c_str());
+        else if (a == "--one-cd") one_cd = true;
+        else if (a == "--be-kernel") be_kernel_a = val("--be-kernel");    // overrides "throughput_test"."a"
+        else if (a == "--be-kernel2") be_kernel_b = val("--be-kernel2");  // overrides "throughput_test"."b"
         else if (a == "--qps") qps = std::atof(val("--qps").c_str());
         else if (a == "--qos") qos = std::atof(val("--qos").c_str());
         else if (a == "--be") be_model = val("--be");
@@ -75,7 +83,8 @@ int main(int argc, char* argv[]) {
             lc_task->enqueue(streams[0]);
             be->streamSync(streams[0]);
         }
-        const std::string a = sget_kernel_info("throughput_test", "a"), b = sget_kernel_info("throughput_test", "b");
+        const std::string a = be_kernel_a.empty() ? sget_kernel_info("throughput_test", "a") : be_kernel_a;
+        const std::string b = be_kernel_b.empty() ? sget_kernel_info("throughput_test", "b") : be_kernel_b;
         std::printf("[Result] cd1: %s, cd2: %s, dnn: %s\n", a.c_str(), b.c_str(), model.c_str());
         TaskManager taskManager(lc_task.get(), a, b);
         if (be_chunk >= 0.0) taskManager.be_chunk_ms = be_chunk;
@@ -91,6 +100,26 @@ int main(int argc, char* argv[]) {
                         device_no, model.c_str(), be_model.c_str(), r.seconds, qps, r.lc_served, r.lc_solo_p50_ms,
                         r.lc_solo_p99_ms, r.lc_p50_ms, r.lc_p99_ms, r.qos_bound_ms, r.qos_met ? "true" : "false",
                         r.be_queries, r.be_qps);
+        } else if (colocate_fused > 0.0) {
+            FusedColocationResult r = taskManager.runFusedColocation(colocate_fused, qps, qos, 1000 + static_cast<uint64_t>(device_no),
+                                                                     streams[0]);
+            std::printf("{\"device\": %d, \"lc\": \"%s\", \"be_kernel\": \"%s\", \"be_blocks_per_job\": %d, \"seconds\": %.3f, "
+                        "\"qps_offered\": %.1f, \"lc_served\": %lld, \"lc_solo_p50_ms\": %.4f, \"lc_solo_p99_ms\": %.4f, "
+                        "\"qos_bound_ms\": %.4f, \"mixable_layers\": %d, \"fused_layers\": %d, \"blocks_per_fused_query\": %lld, "
+                        "\"lc_graph_ms\": %.4f, \"lc_fused_graph_ms\": %.4f, "
+                        "\"timesliced\": {\"lc_p50_ms\": %.4f, \"lc_p99_ms\": %.4f, \"qos_met\": %s, \"be_blocks\": %lld, "
+                        "\"be_blocks_per_s\": %.1f}, "
+                        "\"fused\": {\"lc_p50_ms\": %.4f, \"lc_p99_ms\": %.4f, \"qos_met\": %s, \"be_blocks\": %lld, "
+                        "\"be_blocks_in_lc\": %lld, \"fused_queries\": %lld, \"plain_queries\": %lld, \"be_blocks_per_s\": %.1f}}\n",
+                        device_no, model.c_str(), r.be_kernel.c_str(), r.be_blocks_per_job, r.seconds, qps, r.lc_served,
+                        r.lc_solo_p50_ms, r.lc_solo_p99_ms, r.qos_bound_ms, r.mixable_layers, r.fused_layers,
+                        r.blocks_per_fused_query, r.lc_graph_ms, r.lc_fused_graph_ms, r.ts_lc_p50_ms, r.ts_lc_p99_ms,
+                        r.ts_qos_met ? "true" : "false", r.ts_be_blocks, r.ts_be_blocks_per_s, r.fu_lc_p50_ms, r.fu_lc_p99_ms,
+                        r.fu_qos_met ? "true" : "false", r.fu_be_blocks, r.fu_be_blocks_in_lc, r.fu_fused_queries,
+                        r.fu_plain_queries, r.fu_be_blocks_per_s);
+        } else if (one_cd) {
+            if (system_name == "aker" || system_name == "both") taskManager.execute_with_one_cd_kernel(ExecutionMode::Aker, streams[0]);
+            if (system_name == "tacker" || system_name == "both") taskManager.execute_with_one_cd_kernel(ExecutionMode::Tacker, streams[1]);
         } else {
             if (system_name == "aker" || system_name == "both") taskManager.executeAllTasks(ExecutionMode::Aker, streams[0]);
             if (system_name == "tacker" || system_name == "both") taskManager.executeAllTasks(ExecutionMode::Tacker, streams[1]);

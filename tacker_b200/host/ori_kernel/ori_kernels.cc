@@ -71,7 +71,7 @@ OriCPKernel::~OriCPKernel() {
 void OriCPKernel::initParams() {
     const size_t cells = static_cast<size_t>(prob.nx) * prob.ny;
     if (initialized) {  // the reference re-zeroes the lattice on every initParams (cp_kernel.cu:288)
-        backend().fillZero(energygrid, cells * sizeof(float), nullptr);
+        backend().fillZero(energygrid, cells * sizeof(float), initStream);
         return;
     }
     numatoms = prob.atoms;
@@ -91,6 +91,7 @@ void OriCPKernel::initParams() {
     backend().deviceFree(raw);
     energygrid = static_cast<float*>(backend().deviceAlloc(cells * sizeof(float)));
     backend().fillZero(energygrid, cells * sizeof(float), nullptr);
+    backend().streamSync(nullptr);
     cudaFreeList.push_back(atoms);
     cudaFreeList.push_back(energygrid);
     launchBlockDim = dim3h(16, 8, 1);  // BLOCKSIZEX, BLOCKSIZEY (src/header/cp_header.h:2-3)
@@ -118,8 +119,8 @@ OriMRIQKernel::~OriMRIQKernel() {
 void OriMRIQKernel::initParams() {
     const size_t nX = static_cast<size_t>(prob.numX);
     if (initialized) {
-        backend().fillZero(Qr, nX * sizeof(float), nullptr);
-        backend().fillZero(Qi, nX * sizeof(float), nullptr);
+        backend().fillZero(Qr, nX * sizeof(float), initStream);
+        backend().fillZero(Qi, nX * sizeof(float), initStream);
         return;
     }
     numK = prob.numK;
@@ -139,6 +140,7 @@ void OriMRIQKernel::initParams() {
     Qi = static_cast<float*>(backend().deviceAlloc(nX * sizeof(float)));
     backend().fillZero(Qr, nX * sizeof(float), nullptr);
     backend().fillZero(Qi, nX * sizeof(float), nullptr);
+    backend().streamSync(nullptr);
     for (float* p : {kvals, x, y, z, Qr, Qi}) cudaFreeList.push_back(p);
     launchBlockDim = dim3h(256, 1, 1);  // KERNEL_Q_THREADS_PER_BLOCK (src/header/mriq_header.h:9)
     launchGridDim = dim3h(prob.numX / 256, 1, 1);

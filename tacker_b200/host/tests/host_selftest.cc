@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <unistd.h>
 #include <fstream>
 #include <functional>
 #include <iostream>
@@ -116,9 +117,11 @@ public:
     void deviceFree(void* p) override { std::free(p); }
     void* hostAllocPinned(size_t bytes) override { return std::malloc(bytes); }
     void hostFreePinned(void* p) override { std::free(p); }
-    void upload(void*, const void*, size_t, stream_t) override {}  // buffers are never dereferenced here
+    // buffers are never dereferenced here; the streams of uploads and fills are recorded
+    std::vector<stream_t> upload_streams, fill_streams;
+    void upload(void*, const void*, size_t, stream_t s) override { upload_streams.push_back(s); }
     void download(void*, const void*, size_t, stream_t) override {}
-    void fillZero(void*, size_t, stream_t) override {}
+    void fillZero(void*, size_t, stream_t s) override { fill_streams.push_back(s); }
     stream_t streamCreate() override { return nullptr; }
     void streamSync(stream_t) override {}
     void deviceSync() override {}
@@ -273,7 +276,12 @@ int main(int argc, char** argv) {
         vgg.executeTask(ExecutionMode::Aker, nullptr);
         CHECK(g_launches.size() == 16);  // the tzgemm launches; every other node went through the layer calls
         CHECK(recorder.taskTime(vgg.taskId) > 0.0f);
-        CHECK(recorder.text("/tmp/tk_recorder_selftest.txt") == vgg.kernels.size());
+        char recorder_path[] = "tk_recorder_selftest_XXXXXX";
+        const int fd = mkstemp(recorder_path);
+        CHECK(fd >= 0);
+        if (fd >= 0) close(fd);
+        CHECK(recorder.text(recorder_path) == vgg.kernels.size());
+        std::remove(recorder_path);
     }
     // ---- scheduler ----
     {
@@ -305,6 +313,67 @@ int main(int argc, char** argv) {
         for (auto& l : g_launches)
             if (l.key == "tzgemm_stencil" && l.tail[0] == 0 && l.tail[1] == 1024) all_blocks = true;
         CHECK(all_blocks && tacker.be_blocks >= aker.be_blocks);
+        // stage 2: the leftover budget is filled with solo launches of both best-effort kernels, and what is
+        // reported is what ran
+        CHECK(aker.stage2_launches > 0 && aker.stage2_blocks1 > 0 && aker.stage2_blocks2 > 0);
+        CHECK(aker.stage2_blocks1 % 1024 == 0 && aker.stage2_blocks2 % 1024 == 0);
+        CHECK(aker.stage2_be_ms > 0 && aker.stage2_be_ms <= aker.qos_headroom_left + 1e-3f);
+        // uploads and re-initialisations are queued on the stream the kernels run on
+        {
+            stream_t s1 = reinterpret_cast<stream_t>(0x40);
+            fake.upload_streams.clear();
+            fake.fill_streams.clear();
+            TaskManager tm3(&vgg, "mriq", "cp");
+            tm3.profile_passes = 1, tm3.schedule_passes = 1, tm3.warmup_passes = 1;
+            tm3.executeAllTasks(ExecutionMode::Aker, s1);
+            bool all_on_s1 = !fake.upload_streams.empty() && !fake.fill_streams.empty();
+            for (stream_t s : fake.upload_streams) all_on_s1 = all_on_s1 && s == s1;
+            int fills_on_s1 = 0;
+            for (stream_t s : fake.fill_streams) fills_on_s1 += (s == s1);
+            CHECK(all_on_s1 && fills_on_s1 >= 2);  // the LC input of every pass; Qr and Qi of the best-effort kernel
+        }
+        // a ratio that rounds to zero blocks leaves the layer unfused and the cursor where it was
+        {
+            add_kernel_info("tzgemm_cp", "576", 0);  // conv1_2 (K = 576): nothing to co-run
+            TaskManager tm4(&vgg, "cp", "");
+            tm4.profile_passes = 1, tm4.schedule_passes = 1, tm4.warmup_passes = 1;
+            g_launches.clear();
+            tm4.executeAllTasks(ExecutionMode::Aker, nullptr);
+            int prev_end = 0, broken = 0, fused_cp = 0;
+            for (auto& l : g_launches)
+                if (l.key == "tzgemm_cp") {
+                    ++fused_cp;
+                    broken += !(l.tail[0] == prev_end || (l.tail[0] == 0 && prev_end >= 256));
+                    broken += (l.tail[3] == 784);  // conv1_2 must not have been fused
+                    prev_end = l.tail[1];
+                }
+            CHECK(fused_cp > 0 && broken == 0);
+        }
+        // the variant with one best-effort kernel: whole rounds of the SM count, always from block 0
+        {
+            TaskManager tm5(&vgg, "stencil", "mriq");
+            tm5.profile_passes = 1, tm5.schedule_passes = 1, tm5.warmup_passes = 1;
+            g_launches.clear();
+            ScheduleResult one = tm5.execute_with_one_cd_kernel(ExecutionMode::Aker, nullptr);
+            int bad = 0, n1 = 0;
+            for (auto& l : g_launches)
+                if (l.key == "tzgemm_stencil") {
+                    ++n1;
+                    const int nb = l.tail[1] - l.tail[0];
+                    bad += (l.tail[0] != 0) || !(nb == 1024 || nb % 148 == 0) || nb < 148;
+                }
+                else if (l.key == "gptb_mriq") ++bad;  // no second kernel in this variant
+            CHECK(n1 > 0 && bad == 0 && one.stage2_launches == 0);
+        }
+        // fused request-driven co-location on the double: layers ride, blocks are counted in both phases
+        {
+            TaskManager tm6(&vgg, "stencil", "");
+            tm6.warmup_passes = 1;
+            FusedColocationResult fc = tm6.runFusedColocation(0.05, 2000.0, 1.5, 7, nullptr);
+            CHECK(fc.mixable_layers == 16 && fc.fused_layers > 0 && fc.blocks_per_fused_query > 0);
+            CHECK(fc.ts_be_blocks > 0 && fc.fu_be_blocks > 0 && fc.fu_be_blocks_in_lc == fc.fu_fused_queries * fc.blocks_per_fused_query);
+            CHECK(fc.lc_served > 10 && fc.fu_fused_queries + fc.fu_plain_queries == fc.lc_served);
+        }
         // no headroom -> nothing is fused
         tm.qos_budget_ms = 0.001f;
         g_launches.clear();

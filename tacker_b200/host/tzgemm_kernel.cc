@@ -52,6 +52,7 @@ void TZGEMMScratch::reserve(long long a_bytes, long long b_bytes, long long c_by
         backend().deviceFree(C);
         C = static_cast<float*>(backend().deviceAlloc(static_cast<size_t>(c_bytes)));
         backend().fillZero(C, static_cast<size_t>(c_bytes), nullptr);
+        backend().streamSync(nullptr);
         bytesC = c_bytes;
     }
 }

@@ -2,7 +2,7 @@
 configuration files (the B200 form of the reference's fusion/gptb_profile/profile.py and
 fusion/expr_load_ratio/*.py, whose results are the `"<K>": ratio` tables of src/config/kinfo-*.json).
 
-    python -m tacker_b200.profile_ratios [--write] [--fill 0.8]
+    python -m tacker_b200.profile_ratios [--write] [--out DIR] [--fill 0.8]
 
 ratio[K] = CUDA-core virtual blocks to co-run per 64x64 tzgemm tile of depth K such that the CUDA-core part
 takes `fill` x the time of the GEMM part (both measured solo, per unit): the scheduler's Aker mode takes
@@ -61,18 +61,29 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
     kv = torch.rand(2048, 4, device="cuda") - 0.5
     xyz = [torch.rand(262144, device="cuda") * 64 - 32 for _ in range(3)]
     qr, qi = torch.zeros(262144, device="cuda"), torch.zeros(262144, device="cuda")
+    # solo launch shape (CTAs per SM, threads) and the CUDA-core thread counts tried for the fused kernel
     cds = {
         "stencil": (lambda s=0, e=None: ops.gptb_stencil(1 / 6, 1 / 36, grid0.data_ptr(), grid1.data_ptr(), 512, 512,
-                                                         64, start=s, end=e), 1024, 512),
+                                                         64, start=s, end=e, grid=sms * 2, block=256), 1024,
+                    (2, 256), (320, 448, 576)),
         "cp": (lambda s=0, e=None: ops.gptb_cp(8192, 0.125, lat.data_ptr(), packed.data_ptr(), 512, 512, start=s,
-                                               end=e), 256, 832),
+                                               end=e, grid=sms * 2, block=512), 256, (2, 512), (448, 576, 832)),
         "mriq": (lambda s=0, e=None: ops.gptb_mriq(2048, xyz[0].data_ptr(), xyz[1].data_ptr(), xyz[2].data_ptr(),
                                                    qr.data_ptr(), qi.data_ptr(), kv.data_ptr(), 262144, start=s,
-                                                   end=e), 1024, 704),
+                                                   end=e, grid=sms * 2, block=512), 1024, (2, 512), (576, 704, 832)),
     }
     out = {}
-    for cd, (mk, blocks, cd_threads) in cds.items():
+    for cd, (mk, blocks, solo_shape, w_sweep) in cds.items():
         t_block = t_us([mk()], 3) / blocks
+        # the CUDA-core thread count of the fused kernel: best on a quantum worth one 4096 x 4096 x 1152 GEMM
+        a = (torch.rand(m, 1152, device="cuda") * 2 - 1).half()
+        b = (torch.rand(n, 1152, device="cuda") * 2 - 1).half()
+        c = torch.zeros(m, n, device="cuda")
+        tz = ops.gptb_tzgemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, 1152, alpha=1.0, grid=sms)
+        nb = max(1, min(blocks, int(fill * t_us([tz]) / t_block)))
+        by_w = {w: t_us([ops.mix(mk(0, nb), tz, cd_threads=w, grid=sms)], 5) for w in w_sweep}
+        cd_threads = min(by_w, key=by_w.get)
+        del a, b, c, tz
         table = {}
         for k in KS:
             kk = max(128, (k // 128) * 128)  # the reference rounds K down to a multiple of 128
@@ -90,18 +101,26 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
             table[str(k)] = {"ratio": round(ratio if gain > 0.0 else 0.0, 5), "blocks": nb, "gemm_us": round(t_gemm, 2),
                              "cd_us": round(t_cd, 2), "fused_us": round(t_fused, 2),
                              "fused_vs_sequential": round(t_fused / (t_gemm + t_cd), 4)}
-        out[f"tzgemm_{cd}"] = {"cd_us_per_block": round(t_block, 4), "cd_threads": cd_threads, "table": table}
+        out[f"tzgemm_{cd}"] = {"cd_us_per_block": round(t_block, 4), "cd_threads": cd_threads, "solo_shape": solo_shape,
+                               "fused_us_by_cd_threads": {str(w): round(v, 2) for w, v in by_w.items()}, "table": table}
     return out
 
 
-def write_configs(result: dict, config_dir: str = HOST_CONFIG) -> list:
+def write_configs(result: dict, config_dir: str = HOST_CONFIG, out_dir: str | None = None) -> list:
+    """Stores the tables in every kinfo-<model>.json of `config_dir` (rewritten in place, or into `out_dir`)."""
     touched = []
+    if out_dir:
+        os.makedirs(out_dir, exist_ok=True)
     for path in sorted(glob.glob(os.path.join(config_dir, "kinfo-*.json"))):
         if path.endswith("kinfo-common.json"):
             continue
         with open(path) as f:
             cfg = json.load(f)
+        if out_dir:
+            path = os.path.join(out_dir, os.path.basename(path))
         for pair, r in result.items():
+            solo = cfg.setdefault(pair[len("tzgemm_"):], {})
+            solo["gridsize"], solo["blocksize"] = r["solo_shape"]
             entry = cfg.setdefault(pair, {})
             entry["gridsize"] = 1
             entry["blocksize"] = 192 + r["cd_threads"]
@@ -119,12 +138,13 @@ def write_configs(result: dict, config_dir: str = HOST_CONFIG) -> list:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--write", action="store_true", help="store the ratios in tacker_b200/host/config/kinfo-*.json")
+    ap.add_argument("--out", default=None, help="with --write: put the updated files there instead of rewriting in place")
     ap.add_argument("--fill", type=float, default=0.8)
     args = ap.parse_args(argv)
     result = profile(args.fill)
     print(json.dumps(result, indent=1))
     if args.write:
-        for p in write_configs(result):
+        for p in write_configs(result, out_dir=args.out):
             print("updated", p)
     return 0
 

@@ -40,7 +40,7 @@ def test_exact_mode_bit_exact(cuda, oracle, ppt, natoms):
         got, packed = _run(cuda, ops, atoms, z, h, nx, ny, base=base, grid=3, block=96)
     finally:
         ops.set_option("cp_exact", 0)
-        ops.set_option("cp_ppt", 4)
+        ops.set_option("cp_ppt", 8)
     assert oracle.bit_mismatches(packed, oracle.cp_pack_atoms(atoms, z)) == 0
     want = oracle.cp_f32(oracle.cp_pack_atoms(atoms, z), h, base.copy(), chunk=64)
     assert oracle.bit_mismatches(got, want) == 0
@@ -56,7 +56,7 @@ def test_fast_mode_within_tolerance(cuda, oracle, ppt):
     try:
         got, _ = _run(cuda, ops, atoms, z, h, nx, ny)
     finally:
-        ops.set_option("cp_ppt", 4)
+        ops.set_option("cp_ppt", 8)
     packed = oracle.cp_pack_atoms(atoms, z)
     ref32 = oracle.cp_f32(packed, h, np.zeros((ny, nx), np.float32), chunk=64)
     ref64, mag = oracle.cp_f64(packed, h, nx, ny)
