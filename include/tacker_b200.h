@@ -76,21 +76,41 @@ int tk_sm_count(int* sm_count);
  *   "tzgemm_m256"    solo tzgemm with 256 x 256 super-tiles (a third less operand traffic per flop, no second
  *                    accumulator buffer): 0 = for large dense problems, 1 = always, -1 = never
  *   "cp_exact"       1 = IEEE 1/sqrt as the reference computes it (default 0: hardware rsqrt)
- *   "cp_ppt"         solo Coulomb kernel: points per thread and work item, 8 (reference granularity), 4
- *                    (default) or 2; "mix_cp_ppt" the same for the fused kernel (default 8)
+ *   "tzgemm_pair"    solo tzgemm on clusters of two CTAs (tcgen05.mma.cta_group::2, 256 x 256 pair tiles): 0 = by
+ *                    shape, 1 = whenever the shape allows (M, N >= 256), -1 = never; "mix_pair" the same for the
+ *                    tensor role of the fused kernels, "mix_pair_stages" (3..5) its operand stages next to the stencil
+ *   "cp_exact"       1 = IEEE 1/sqrt as the reference computes it (default 0: hardware rsqrt)
+ *   "cp_ppt"         solo Coulomb kernel: points per thread and work item, 8 (default, the reference's granularity),
+ *                    4 or 2; "mix_cp_ppt" the same for the fused kernel (default 8)
+ *   "cp_split"       atoms per Coulomb work item in the fast mode: -1 (default) = chosen from the launch shape,
+ *                    0 = whole list (deterministic summation order), n = n rounded up to 64.  Items that cover a
+ *                    part of the list add their partial sums to the lattice with reductions in no fixed order.
  *   "mriq_accurate"  1 = cosf/sinf as the reference calls them (default 0: reduced argument +
- *                    hardware sin/cos)
+ *                    hardware sin/cos); "mrif_accurate" the same for MRI-FHd (plus the binary64 product of its phase)
+ *   "mriq_split"     samples per MRI-Q / MRI-FHd work item, as "cp_split"
+ *   "wait_budget_us" budget of every bounded device-side wait (default 1,000,000 = about a second); applies to the
+ *                    current device.  "test_skip_loads" n: test hook, the next n single-CTA tzgemm launches issue
+ *                    no operand loads, so that their waits run out.
+ *   "mriq_vpt"       voxels per thread (2 or 4; a work item is 32 x that many voxels) of the solo MRI-Q / MRI-FHd
+ *                    kernels, "mix_mriq_vpt" of the fused ones (default 4)
  */
 int tk_set_option(const char* name, int value);
 int tk_get_option(const char* name, int* value);
 /* Reads and clears the device status word that bounded device-side waits write when they
- * give up (0 = no expiry).  Synchronises the device. */
+ * give up (0 = no expiry; otherwise the code of the first wait that expired: 1 = a producer waited for a free
+ * operand stage, 2 = the MMA issuer for operand bytes, 3 = the MMA issuer for a drained accumulator, 4 = the
+ * epilogue for an accumulator).  Synchronises the device.  The launch that wrote the word has returned; its
+ * outputs are incomplete. */
 int tk_device_status(unsigned* code);
+/* The same as a status: TK_OK, or TK_ERR_DEVICE_WAIT when the word was not zero (also cleared). */
+int tk_device_check(void);
 
 /* ---- the fmap replacement --------------------------------------------------------------
  * Keys (same strings as the reference table): "gptb_tzgemm", "gptb_tzgemm_acc", "gptb_stencil", "gptb_cp",
- * "gptb_mriq", "tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq"; plus "ori_stencil", "ori_cp",
- * "ori_mriq" for the non-persistent launch shape of the solo kernels. */
+ * "gptb_mriq", "gptb_mrif", "tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq", "tzgemm_mrif"; plus "ori_stencil",
+ * "ori_cp", "ori_mriq", "ori_mrif" for the non-persistent launch shape of the solo kernels; and "gptb_tzconv",
+ * "tzconv_stencil", "tzconv_cp", "tzconv_mriq", "tzconv_mrif" for the implicit-GEMM convolution (not in the
+ * reference's table). */
 tk_launch_fn tk_lookup(const char* key);
 int tk_num_keys(void);
 const char* tk_key(int index);
@@ -159,14 +179,24 @@ int tk_launch_gptb_cp(void** params, int nparams, const unsigned grid[3], const 
 int tk_launch_gptb_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
                         unsigned smem_bytes, void* stream);
 
+/* gptb_mrif  replaces g_general_ptb_mrif (src/gptb_kernel/mrif_kernel.cu:6-92).
+ *   params (18): int numK, int kGlobalIndex (ignored), float* x, float* y, float* z, float* outR,
+ *                float* outI, float* kvals, 6 geometry ints, start, step, end, thread_base
+ *   kvals = the table tk_mrif_pack_kvalues writes (the reference reads a 256-entry __constant__ symbol,
+ *   src/ori_kernel/mrif_kernel.cu:9): numK x {Kx, Ky, Kz, RhoPhiR}, then numK x RhoPhiI; all numK samples
+ *   are summed in one launch.  geometry: grid_dimension_x = numX / 256, block_dimension_x = 256. */
+int tk_launch_gptb_mrif(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                        unsigned smem_bytes, void* stream);
+
 /* ---- fused kernels: tensor role + CUDA-core role in one persistent CTA ---------------------
- * Replace stencil_tzgemm_mix / cp_tzgemm_mix / mriq_tzgemm_mix
- * (src/mix_kernel/tzgemm_stencil.cu:281-299, tzgemm_cp.cu:994-1017, tzgemm_mriq.cu:638-657).
+ * Replace stencil_tzgemm_mix / cp_tzgemm_mix / mriq_tzgemm_mix / mrif_tzgemm_mix
+ * (src/mix_kernel/tzgemm_stencil.cu:281-299, tzgemm_cp.cu:994-1017, tzgemm_mriq.cu:638-657, tzgemm_mrif.cu).
  * params = CUDA-core kernel's list without thread_base, then tzgemm's list without thread_base,
  * the order MixKernel::initParams builds (src/MixKernel.h:55-73):
  *   tzgemm_stencil (32) = stencil 7 + 6 + 3, tzgemm 7 + 6 + 3
  *   tzgemm_cp      (29) = cp 4 + 6 + 3,      tzgemm 7 + 6 + 3
  *   tzgemm_mriq    (33) = mriq 8 + 6 + 3,    tzgemm 7 + 6 + 3
+ *   tzgemm_mrif    (33) = mrif 8 + 6 + 3,    tzgemm 7 + 6 + 3
  * block[0] = 192 + CUDA-core threads.  Either range may be empty. */
 int tk_launch_mix_tzgemm_stencil(void** params, int nparams, const unsigned grid[3],
                                  const unsigned block[3], unsigned smem_bytes, void* stream);
@@ -174,6 +204,41 @@ int tk_launch_mix_tzgemm_cp(void** params, int nparams, const unsigned grid[3], 
                             unsigned smem_bytes, void* stream);
 int tk_launch_mix_tzgemm_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
                               unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzgemm_mrif(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                              unsigned smem_bytes, void* stream);
+
+/* ---- implicit-GEMM convolution ---------------------------------------------------------------
+ * gptb_tzconv  replaces the im2col_gpu_kernel + convertFp32ToFp16 + tzgemm sequence of mycudnnConvolutionForward
+ * (src/include/dnn.h:45-99, 554-803) for 3 x 3 convolutions with stride 1 and padding 1: the A operand is never
+ * written to memory, bias and activation are applied in the epilogue.  Activations are zero-bordered NHWC fp16
+ * images [(H + 2)][(W + 2)][C]; the border of the output image is never written (zero it once).
+ *   params (22): half* X, half* Wt, half* Y, int M, int N, int K, float alpha, float* bias, int H, int W, int C,
+ *                int act, 6 geometry ints (ignored), start, step, end, thread_base
+ *   X = bordered input, C a multiple of 64; Wt = weights [N][K], K = 9 C, k = (3 i + j) C + c for tap (i, j);
+ *   Y = bordered output [(H + 2)][(W + 2)][N], N a multiple of 64; bias [N] or null; act 0 = none, 1 = ReLU;
+ *   M = H (W + 2) rounded up to a multiple of 128: GEMM row m is pixel (m / (W + 2), m % (W + 2)) of the bordered
+ *   grid, rows with m % (W + 2) >= W are computed and dropped.  [start, end) counts 64 x 64 tiles of that
+ *   M x N problem, row-major, like gptb_tzgemm.
+ * tzconv_<cd> (stencil 37, cp 34, mriq / mrif 38 params): the fused kernels with this tensor role; params = the
+ * CUDA-core list (n + 6 + 3), then tzconv's 12 + 6 + 3. */
+int tk_launch_gptb_tzconv(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                          unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzconv_stencil(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                 unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzconv_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                            unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzconv_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                              unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzconv_mrif(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                              unsigned smem_bytes, void* stream);
+/* helpers for the bordered fp16 activation format (no counterpart in the reference, whose activations are fp32 NCHW):
+ *   tk_bias_act_f16_bordered   Y[(h+1)][(w+1)][c] = act(x[h W + w][c] + bias[c]), x fp32 with leading dimension ldx
+ *   tk_maxpool2x2_f16_bordered 2 x 2 max pooling, bordered in, bordered out (C a multiple of 8)
+ *   tk_unborder_f16            the interior of a bordered image as one dense row of H W C halves */
+int tk_bias_act_f16_bordered(const float* x, int ldx, const float* bias, void* out_half, int H, int W, int C, int act,
+                             void* stream);
+int tk_maxpool2x2_f16_bordered(const void* x_half, int H, int W, int C, void* out_half, void* stream);
+int tk_unborder_f16(const void* x_half, int H, int W, int C, void* row_half, void* stream);
 
 /* ---- non-persistent launch shape of the solo kernels ------------------------------------------
  * ori_stencil (7 params, src/ori_kernel/stencil_kernel.cu:9), ori_cp (4 params with atoms_packed,
@@ -185,6 +250,9 @@ int tk_launch_ori_cp(void** params, int nparams, const unsigned grid[3], const u
                      unsigned smem_bytes, void* stream);
 int tk_launch_ori_mriq(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
                        unsigned smem_bytes, void* stream);
+/* ori_mrif (8 params with kvals, src/ori_kernel/mrif_kernel.cu:78) */
+int tk_launch_ori_mrif(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                       unsigned smem_bytes, void* stream);
 
 /* ---- input preparation the reference does on the host -------------------------------------------
  * tk_cp_pack_atoms  replaces copyatomstoconstbuf (src/ori_kernel/cp_kernel.cu:159-179):
@@ -194,6 +262,12 @@ int tk_cp_pack_atoms(const float* atoms_xyzq, int count, float zplane, float* pa
  * structs (src/ori_kernel/mriq_kernel.cu:47-54, src/header/mriq_header.h:12-17). */
 int tk_mriq_pack_kvalues(const float* kx, const float* ky, const float* kz, const float* phiR,
                          const float* phiI, int numK, float* kvals, void* stream);
+/* tk_mrif_pack_kvalues  replaces ComputeRhoPhiGPU plus the host loop that fills the kValues structs
+ * (src/ori_kernel/mrif_kernel.cu:63-76, src/header/mrif_header.h:27-33): RhoPhiR = phiR*dR + phiI*dI,
+ * RhoPhiI = phiR*dI - phiI*dR.  kvals (device, 16-byte aligned) receives 5 * numK floats. */
+int tk_mrif_pack_kvalues(const float* kx, const float* ky, const float* kz, const float* phiR,
+                         const float* phiI, const float* dR, const float* dI, int numK, float* kvals,
+                         void* stream);
 
 /* ---- LC-layer helpers -----------------------------------------------------------------------------
  * tk_im2col_f32  replaces im2col_gpu_kernel (src/include/dnn.h:45-92): Caffe layout,

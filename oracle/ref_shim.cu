@@ -7,7 +7,7 @@
 //     these kernels on seeded inputs are stored as fixtures under tests/golden/;
 //   * timing "the reference recompiled for sm_100" next to the new kernels.
 // Only the launch wrappers below are code of this repository; every kernel body comes from
-//   src/gptb_kernel/{stencil,cp,mriq}_kernel.cu and src/mix_kernel/tzgemm_{stencil,cp,mriq}.cu.
+//   src/gptb_kernel/{stencil,cp,mriq,mrif}_kernel.cu and src/mix_kernel/tzgemm_{stencil,cp,mriq}.cu.
 //
 // The reference force-defines AKER_INT8 (src/header/pets_common.h:1-3), an int8 experiment whose
 // GEMM drops its result.  All reference headers are included first (they carry #pragma once), the
@@ -19,6 +19,7 @@
 using namespace nvcuda;
 
 #include "header/cp_header.h"
+#include "header/mrif_header.h"
 #include "header/mriq_header.h"
 #include "header/stencil_header.h"
 #include "header/tzgemm_header.h"
@@ -31,7 +32,11 @@ __constant__ int4 atominfo_int[MAXATOMS];
 __constant__ __device__ mriq_kValues ck[KERNEL_Q_K_ELEMS_PER_GRID];
 __constant__ __device__ mriq_kValues_int ck_int[KERNEL_Q_K_ELEMS_PER_GRID];
 
+__constant__ __device__ mrif_kValues c[KERNEL_FH_K_ELEMS_PER_GRID];
+__constant__ __device__ mrif_kValues_int c_int[KERNEL_FH_K_ELEMS_PER_GRID];
+
 #include "gptb_kernel/cp_kernel.cu"
+#include "gptb_kernel/mrif_kernel.cu"
 #include "gptb_kernel/mriq_kernel.cu"
 #include "gptb_kernel/stencil_kernel.cu"
 #include "mix_kernel/tzgemm_cp.cu"
@@ -97,6 +102,25 @@ REF_API int ref_mriq(const float* kvals_host, int numK, float* x, float* y, floa
                                                 cudaMemcpyHostToDevice, st);
         if (e != cudaSuccess) return static_cast<int>(e);
         g_general_ptb_mriq<<<grid, 256, 0, st>>>(n, 0, x, y, z, Qr, Qi, gx, 1, 1, KERNEL_Q_THREADS_PER_BLOCK, 1, 1,
+                                                 start, grid, end, 0);
+        if (last_error()) return -1;
+        e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    return 0;
+}
+
+// kvals: host array of the reference's structs {Kx, Ky, Kz, RhoPhiR, RhoPhiI}; 256 per launch through the
+// constant buffer (src/header/mrif_header.h:12)
+REF_API int ref_mrif(const float* kvals_host, int numK, float* x, float* y, float* z, float* outR, float* outI, int gx,
+                     int start, int end, int grid, void* stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int k0 = 0; k0 < numK; k0 += KERNEL_FH_K_ELEMS_PER_GRID) {
+        const int n = numK - k0 < KERNEL_FH_K_ELEMS_PER_GRID ? numK - k0 : KERNEL_FH_K_ELEMS_PER_GRID;
+        cudaError_t e = cudaMemcpyToSymbolAsync(c, kvals_host + 5 * k0, n * sizeof(mrif_kValues), 0,
+                                                cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        g_general_ptb_mrif<<<grid, 256, 0, st>>>(n, 0, x, y, z, outR, outI, gx, 1, 1, KERNEL_FH_THREADS_PER_BLOCK, 1, 1,
                                                  start, grid, end, 0);
         if (last_error()) return -1;
         e = cudaStreamSynchronize(st);

@@ -488,6 +488,80 @@ TKO_API void tko_mriq_f64(const float *kvals, int numK, const float *x, const fl
 }
 
 /* ------------------------------------------------------------------------- */
+/* MRI-FHd                                                                    */
+/* reference: src/ori_kernel/mrif_kernel.cu:63-76 (RhoPhiR = phiR*dR +        */
+/*   phiI*dI, RhoPhiI = phiR*dI - phiI*dR), :78-150 and                       */
+/*   src/gptb_kernel/mrif_kernel.cu:6-92 (expArg = PIx2 * (Kx*x + Ky*y +      */
+/*   Kz*z) with PIx2 a binary64 literal, src/header/mrif_header.h:7, so the   */
+/*   product is taken in binary64 and rounded to binary32; outR += RhoPhiR*cos*/
+/*   - RhoPhiI*sin, outI += RhoPhiI*cos + RhoPhiR*sin; k ascending; block p = */
+/*   256 consecutive voxels).  The reference sums the samples of one 256-entry*/
+/*   constant tile per launch; here any count, in order.                      */
+/* Contractions as nvcc -fmad=true applies them: the dot product as in MRI-Q; */
+/* a*b - c*d -> fma(a, b, -(c*d)); a*b + c*d -> fma(a, b, c*d); the result is */
+/* then added to the accumulator (mode 0).  mode 1 keeps every operation      */
+/* separate (for the error budget of the choice).                             */
+/* packed table: numK x {Kx, Ky, Kz, RhoPhiR}, then numK x RhoPhiI.           */
+/* ------------------------------------------------------------------------- */
+#define TKO_MRIF_2PI_F64 6.2831853071795864769252867665590058
+
+TKO_API void tko_mrif_pack(const float *kx, const float *ky, const float *kz, const float *phiR, const float *phiI,
+                           const float *dR, const float *dI, float *kvals, int numK) {
+    for (int k = 0; k < numK; k++) {
+        kvals[4 * k] = kx[k]; kvals[4 * k + 1] = ky[k]; kvals[4 * k + 2] = kz[k];
+        kvals[4 * k + 3] = fmaf(phiR[k], dR[k], phiI[k] * dI[k]);
+        kvals[4 * (size_t)numK + k] = fmaf(phiR[k], dI[k], -(phiI[k] * dR[k]));
+    }
+}
+
+TKO_API void tko_mrif_f32(const float *kvals, int numK, const float *x, const float *y, const float *z,
+                          float *outR, float *outI, int gx, int start, int end, int mode) {
+    const float *rho_i = kvals + 4 * (size_t)numK;
+    for (int p = start; p < end; p++)
+#pragma omp parallel for schedule(static)
+        for (int t = 0; t < TKO_MRIQ_BLOCK; t++) {
+            int xi = (p % gx) * TKO_MRIQ_BLOCK + t;
+            float sx = x[xi], sy = y[xi], sz = z[xi], o_r = outR[xi], o_i = outI[xi];
+            for (int k = 0; k < numK; k++) {
+                const float *kv = kvals + 4 * (size_t)k;
+                float dot = fmaf(kv[2], sz, fmaf(kv[0], sx, kv[1] * sy));
+                float a32 = (float)(TKO_MRIF_2PI_F64 * (double)dot);
+                float c = (float)cos((double)a32), s = (float)sin((double)a32);
+                if (mode == 0) {
+                    o_r = o_r + fmaf(kv[3], c, -(rho_i[k] * s));
+                    o_i = o_i + fmaf(rho_i[k], c, kv[3] * s);
+                } else {
+                    o_r = o_r + (kv[3] * c - rho_i[k] * s);
+                    o_i = o_i + (rho_i[k] * c + kv[3] * s);
+                }
+            }
+            outR[xi] = o_r; outI[xi] = o_i;
+        }
+}
+
+/* binary64 accumulation of the same binary32 arguments */
+TKO_API void tko_mrif_f64(const float *kvals, int numK, const float *x, const float *y, const float *z,
+                          double *outR, double *outI, int gx, int start, int end) {
+    const float *rho_i = kvals + 4 * (size_t)numK;
+    for (int p = start; p < end; p++)
+#pragma omp parallel for schedule(static)
+        for (int t = 0; t < TKO_MRIQ_BLOCK; t++) {
+            int xi = (p % gx) * TKO_MRIQ_BLOCK + t;
+            float sx = x[xi], sy = y[xi], sz = z[xi];
+            double o_r = outR[xi], o_i = outI[xi];
+            for (int k = 0; k < numK; k++) {
+                const float *kv = kvals + 4 * (size_t)k;
+                float dot = fmaf(kv[2], sz, fmaf(kv[0], sx, kv[1] * sy));
+                double a = (double)(float)(TKO_MRIF_2PI_F64 * (double)dot);
+                double c = cos(a), s = sin(a);
+                o_r += (double)kv[3] * c - (double)rho_i[k] * s;
+                o_i += (double)rho_i[k] * c + (double)kv[3] * s;
+            }
+            outR[xi] = o_r; outI[xi] = o_i;
+        }
+}
+
+/* ------------------------------------------------------------------------- */
 /* im2col (Caffe layout) and the conv -> GEMM shape rule                      */
 /* reference: src/include/dnn.h:45-92 (one work item per (c_im, h_col, w_col),*/
 /*   column row index (c_im*kh*kw + i*kw + j), zero padding),                 */

@@ -244,6 +244,36 @@ def mriq_f64(kvals, x, y, z, start=0, end=None):
     return Qr, Qi
 
 
+def mrif_pack(kx, ky, kz, phiR, phiI, dR, dI) -> np.ndarray:
+    """The packed MRI-FHd table: numK x {Kx, Ky, Kz, RhoPhiR}, then numK x RhoPhiI (5 * numK floats)."""
+    n = kx.size
+    out = np.empty(5 * n, dtype=np.float32)
+    lib().tko_mrif_pack(*[_p(_c32(v), _f32p) for v in (kx, ky, kz, phiR, phiI, dR, dI)], _p(out, _f32p), n)
+    return out
+
+
+def mrif_f32(kvals, x, y, z, outR, outI, start=0, end=None, mode: int = 0):
+    gx = x.size // 256
+    if end is None:
+        end = gx
+    kvals = _c32(kvals)
+    lib().tko_mrif_f32(_p(kvals, _f32p), kvals.size // 5, _p(x, _f32p), _p(y, _f32p), _p(z, _f32p),
+                       _p(outR, _f32p), _p(outI, _f32p), gx, start, end, mode)
+    return outR, outI
+
+
+def mrif_f64(kvals, x, y, z, start=0, end=None):
+    gx = x.size // 256
+    if end is None:
+        end = gx
+    kvals = _c32(kvals)
+    o_r = np.zeros(x.size, dtype=np.float64)
+    o_i = np.zeros(x.size, dtype=np.float64)
+    lib().tko_mrif_f64(_p(kvals, _f32p), kvals.size // 5, _p(x, _f32p), _p(y, _f32p), _p(z, _f32p),
+                       _p(o_r, _f64p), _p(o_i, _f64p), gx, start, end)
+    return o_r, o_i
+
+
 # ---------------------------------------------------------------- im2col ----
 def conv_mnk(args14):
     a = (C.c_int * 14)(*[int(v) for v in args14])

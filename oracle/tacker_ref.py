@@ -79,6 +79,13 @@ def mix_cp(numatoms, spacing, lattice, gx, gy, cd_start, cd_end, A, B, Cm, M, N,
                             _vp(Cm), M, N, K, tz_start, tz_end, grid, _vp(stream))
 
 
+def mrif(kvals_aos_host: np.ndarray, x, y, z, outR, outI, gx, start, end, grid, stream=0) -> int:
+    """kvals_aos_host: [numK][5] float32 = {Kx, Ky, Kz, RhoPhiR, RhoPhiI} (the reference's struct order)."""
+    kvals_aos_host = np.ascontiguousarray(kvals_aos_host, dtype=np.float32)
+    return lib().ref_mrif(_f32p(kvals_aos_host), kvals_aos_host.shape[0], _vp(x), _vp(y), _vp(z), _vp(outR), _vp(outI),
+                          gx, start, end, grid, _vp(stream))
+
+
 def mriq_load_kvals(kvals_host: np.ndarray) -> int:
     kvals_host = np.ascontiguousarray(kvals_host, dtype=np.float32)
     return lib().ref_mriq_load_kvals(_f32p(kvals_host), kvals_host.shape[0])

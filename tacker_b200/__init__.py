@@ -23,8 +23,9 @@ _lib = None
 LAUNCH_FN = C.CFUNCTYPE(C.c_int, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_uint), C.POINTER(C.c_uint),
                         C.c_uint, C.c_void_p)
 
-KEYS = ("gptb_tzgemm", "gptb_tzgemm_acc", "gptb_stencil", "gptb_cp", "gptb_mriq", "tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq",
-        "ori_stencil", "ori_cp", "ori_mriq")
+KEYS = ("gptb_tzgemm", "gptb_tzgemm_acc", "gptb_stencil", "gptb_cp", "gptb_mriq", "gptb_mrif", "tzgemm_stencil",
+        "tzgemm_cp", "tzgemm_mriq", "tzgemm_mrif", "ori_stencil", "ori_cp", "ori_mriq", "ori_mrif", "gptb_tzconv",
+        "tzconv_stencil", "tzconv_cp", "tzconv_mriq", "tzconv_mrif")
 
 
 class TackerError(RuntimeError):

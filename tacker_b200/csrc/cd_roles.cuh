@@ -484,4 +484,128 @@ __device__ __forceinline__ void mriq_role(const MriqArgs m, int* counter, const 
     }
 }
 
+// =====================================================================================
+// MRI-FHd (reference: src/ori_kernel/mrif_kernel.cu:63-76 ComputeRhoPhiGPU, :78-150 ori_mrif,
+//   src/gptb_kernel/mrif_kernel.cu:6-92)
+//   outR[x] += sum_k RhoPhiR_k cos(a) - RhoPhiI_k sin(a),  outI[x] += sum_k RhoPhiI_k cos(a) + RhoPhiR_k sin(a),
+//   a = float(2 pi (binary64) * t), t = fma(Kz, z, fma(Kx, x, Ky * y)) in binary32, k ascending.
+// Same shape as MRI-Q (virtual block = 256 consecutive voxels, work item = one warp = 32 VPT voxels times a range
+// of the samples, split items add their partial sums with reductions).  The reference keeps 256 samples in a
+// __constant__ array; here the packed table sits in global memory, any count: numK float4 {Kx, Ky, Kz, RhoPhiR}
+// followed by numK floats RhoPhiI.
+// ACCURATE: the reference's arithmetic (binary64 product for the argument, cosf / sinf, the contractions nvcc
+// applies to its expressions); otherwise t is reduced exactly to [-1/2, 1/2] and fed to the hardware sin / cos.
+// =====================================================================================
+struct MrifArgs {
+    int numK;
+    const float4* kvals;  // {Kx, Ky, Kz, RhoPhiR} x numK, then RhoPhiI x numK
+    const float* x;
+    const float* y;
+    const float* z;
+    float* outR;
+    float* outI;
+    int gx;
+    int start, end;
+    int k_per_item;  // as MriqArgs::k_per_item
+};
+
+__device__ __forceinline__ void mrif_pair_step(const float2 kx, const float2 ky, const float2 kz, const float2 rr,
+                                               const float2 ri, const float2 X, const float2 Y, const float2 Z,
+                                               float2& OR, float2& OI) {
+    const float2 t = __ffma2_rn(kz, Z, __ffma2_rn(kx, X, __fmul2_rn(ky, Y)));
+    // u = t - nearest integer (exact); sin and cos of 2 pi t are those of 2 pi u
+    const float2 n = __fadd2_rn(__fadd2_rn(t, make_float2(12582912.0f, 12582912.0f)),
+                                make_float2(-12582912.0f, -12582912.0f));
+    const float2 u = __fadd2_rn(t, make_float2(-n.x, -n.y));
+    const float2 r = __fmul2_rn(u, make_float2(kMriq2Pi, kMriq2Pi));
+    const float2 c = make_float2(__cosf(r.x), __cosf(r.y));
+    const float2 sn = make_float2(__sinf(r.x), __sinf(r.y));
+    OR = __ffma2_rn(rr, c, OR);
+    OR = __ffma2_rn(make_float2(-ri.x, -ri.y), sn, OR);
+    OI = __ffma2_rn(ri, c, OI);
+    OI = __ffma2_rn(rr, sn, OI);
+}
+
+template <bool ACCURATE, int VPT>
+__device__ __forceinline__ void mrif_role(const MrifArgs m, int* counter, const int lane, const int cta,
+                                          const int ncta) {
+    static_assert(VPT == 2 || VPT == 4, "two or four voxels per thread");
+    constexpr int kTilesPerBlock = 256 / (32 * VPT);
+    const bool split = m.k_per_item > 0 && m.k_per_item < m.numK;
+    const int per = split ? m.k_per_item : m.numK;
+    const int nchunks = split ? (m.numK + per - 1) / per : 1;
+    const long long nitems = static_cast<long long>(m.end - m.start) * kTilesPerBlock * nchunks;
+    const float* __restrict__ rho_i = reinterpret_cast<const float*>(m.kvals + m.numK);
+    for (long long item = claim_item(counter, lane, cta, ncta); item < nitems;
+         item = claim_item(counter, lane, cta, ncta)) {
+        const int chunk = static_cast<int>(item % nchunks);
+        const long long tile = item / nchunks;
+        const int p = m.start + static_cast<int>(tile / kTilesPerBlock);
+        const int sub = static_cast<int>(tile % kTilesPerBlock);
+        const size_t base = static_cast<size_t>(p % m.gx) * 256 + sub * (32 * VPT) + lane;
+        float x[VPT], y[VPT], z[VPT], o_r[VPT], o_i[VPT];
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            x[v] = m.x[base + 32 * v];
+            y[v] = m.y[base + 32 * v];
+            z[v] = m.z[base + 32 * v];
+            o_r[v] = split ? 0.0f : m.outR[base + 32 * v];
+            o_i[v] = split ? 0.0f : m.outI[base + 32 * v];
+        }
+        const int k0 = chunk * per;
+        const int k1 = min(k0 + per, m.numK);
+        if (ACCURATE) {
+#pragma unroll 2
+            for (int k = k0; k < k1; ++k) {
+                const float4 kv = __ldg(m.kvals + k);
+                const float ri = __ldg(rho_i + k);
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) {
+                    const float t = __fmaf_rn(kv.z, z[v], __fmaf_rn(kv.x, x[v], __fmul_rn(kv.y, y[v])));
+                    const float a = __double2float_rn(6.2831853071795864769252867665590058 * static_cast<double>(t));
+                    const float cv = cosf(a), sv = sinf(a);
+                    // sOutR += R*c - I*s and sOutI += I*c + R*s with the contractions nvcc applies: the first product
+                    // of each expression is fused, the sum is then added to the accumulator
+                    o_r[v] = __fadd_rn(o_r[v], __fmaf_rn(kv.w, cv, -__fmul_rn(ri, sv)));
+                    o_i[v] = __fadd_rn(o_i[v], __fmaf_rn(ri, cv, __fmul_rn(kv.w, sv)));
+                }
+            }
+        } else {
+            float2 X[VPT / 2], Y[VPT / 2], Z[VPT / 2], OR[VPT / 2], OI[VPT / 2];
+#pragma unroll
+            for (int h = 0; h < VPT / 2; ++h) {
+                X[h] = make_float2(x[2 * h], x[2 * h + 1]);
+                Y[h] = make_float2(y[2 * h], y[2 * h + 1]);
+                Z[h] = make_float2(z[2 * h], z[2 * h + 1]);
+                OR[h] = make_float2(o_r[2 * h], o_r[2 * h + 1]);
+                OI[h] = make_float2(o_i[2 * h], o_i[2 * h + 1]);
+            }
+#pragma unroll 4
+            for (int k = k0; k < k1; ++k) {
+                const float4 kv = __ldg(m.kvals + k);
+                const float rho = __ldg(rho_i + k);
+                const float2 kx = make_float2(kv.x, kv.x), ky = make_float2(kv.y, kv.y), kz = make_float2(kv.z, kv.z);
+                const float2 rr = make_float2(kv.w, kv.w), ri = make_float2(rho, rho);
+#pragma unroll
+                for (int h = 0; h < VPT / 2; ++h) mrif_pair_step(kx, ky, kz, rr, ri, X[h], Y[h], Z[h], OR[h], OI[h]);
+            }
+#pragma unroll
+            for (int h = 0; h < VPT / 2; ++h) {
+                o_r[2 * h] = OR[h].x, o_r[2 * h + 1] = OR[h].y;
+                o_i[2 * h] = OI[h].x, o_i[2 * h + 1] = OI[h].y;
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            if (split) {
+                red_add_f32(m.outR + base + 32 * v, o_r[v]);
+                red_add_f32(m.outI + base + 32 * v, o_i[v]);
+            } else {
+                m.outR[base + 32 * v] = o_r[v];
+                m.outI[base + 32 * v] = o_i[v];
+            }
+        }
+    }
+}
+
 }  // namespace tk

@@ -38,6 +38,20 @@ struct GemmArgs {
     long long stride_c;  // elements between consecutive C matrices of a batch
     int l2_hints;        // 1: operand tiles are loaded with the evict-last L2 priority
     int splitk;          // > 1: K is cut into that many ranges handled by different CTAs, C += partial (red.add)
+    // Implicit-GEMM convolution (CONV form of the role; 3 x 3, stride 1, padding 1): A is not a matrix in memory but
+    // the zero-bordered NHWC fp16 image X[(H + 2)][(W + 2)][C].  GEMM row m stands for the pixel (m / (W + 2),
+    // m % (W + 2)) of the bordered grid, so that K-block kb = (tap (i, j), channels c0 .. c0 + 63) of that row is the
+    // image row m + i (W + 2) + j: every operand tile is one plain tile load at a shifted row.  The rows with
+    // m % (W + 2) >= W are computed and dropped.  The epilogue adds the bias, applies the activation and writes fp16
+    // into the bordered output image at row m + (W + 2) + 1.
+    int conv_c;          // input channels (a multiple of 64); 0 in the plain GEMM
+    int conv_w;          // image width W
+    int conv_oh;         // output rows (= H)
+    int conv_act;        // 0 none, 1 ReLU
+    const float* conv_bias;  // [N] or null
+    __half* conv_out;    // bordered fp16 output image [(H + 2)][(W + 2)][N]
+    int test_skip_loads; // test hook (single-CTA role only): the producer issues no loads, so the MMA issuer's bounded
+                         // wait for operand bytes runs out and the launch ends with DEV_TIMEOUT_FULL in the status word
 };
 
 // STAGED = the epilogue transposes through shared memory (coalesced row stores, 18 KB); the unstaged form writes
@@ -122,7 +136,9 @@ struct SuperTileWalk {
 };
 
 // `warp` is the warp index inside the role (0..5); all 192 threads of the role must call this.
-template <int BN, int STAGES, bool STAGED = true>
+// CONV: the implicit-GEMM convolution described at GemmArgs (tmap_a then describes the bordered image as
+// {C, (H + 2)(W + 2)} with a 64 x 128 box); needs STAGED.
+template <int BN, int STAGES, bool STAGED = true, bool CONV = false>
 __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a,
                                           const CUtensorMap* __restrict__ tmap_b, const GemmArgs g,
                                           uint8_t* smem, const int warp, const int lane) {
@@ -182,13 +198,20 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
                 for (int kb = kb0; kb < kb1; ++kb) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
+                    if (g.test_skip_loads) continue;  // nothing will ever arrive on the full barrier
                     mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+                    int ax = kb * kGemmBK, ay = R * kGemmBM;
+                    if (CONV) {  // K-block = one filter tap x 64 channels: the image rows shifted by the tap
+                        const int tap = ax / g.conv_c;
+                        ax -= tap * g.conv_c;
+                        ay += (tap / 3) * (g.conv_w + 2) + tap % 3;
+                    }
                     if (g.l2_hints) {
-                        tma_load_tile_hint(a_dst, tmap_a, full_bar(stage), kb * kGemmBK, R * kGemmBM, b, keep);
+                        tma_load_tile_hint(a_dst, tmap_a, full_bar(stage), ax, ay, b, keep);
                         tma_load_tile_hint(a_dst + L::kABytes, tmap_b, full_bar(stage), kb * kGemmBK, Cc * BN, b, keep);
                     } else {
-                        tma_load_tile(a_dst, tmap_a, full_bar(stage), kb * kGemmBK, R * kGemmBM, b);
+                        tma_load_tile(a_dst, tmap_a, full_bar(stage), ax, ay, b);
                         tma_load_tile(a_dst + L::kABytes, tmap_b, full_bar(stage), kb * kGemmBK, Cc * BN, b);
                     }
                     if (++stage == STAGES) {
@@ -286,6 +309,33 @@ __device__ __forceinline__ void gemm_role(const CUtensorMap* __restrict__ tmap_a
                         srow[v] = o;
                     }
                     __syncwarp();
+                    if (CONV) {
+                        // bias + activation + fp16, into the bordered output image; rows that stand for border pixels
+                        // of the enumeration (or lie below the image) are dropped, so the border stays zero
+                        const int col = Cc * BN + c * 32 + (lane & 7) * 4;
+                        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (g.conv_bias) bv = __ldg(reinterpret_cast<const float4*>(g.conv_bias + col));
+                        const int wp = g.conv_w + 2;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = 4 * i + (lane >> 3);
+                            const int m = row0 + rr;
+                            const int oh = m / wp, ow = m - oh * wp;
+                            if (ow >= g.conv_w || oh >= g.conv_oh) continue;
+                            float4 o = *reinterpret_cast<const float4*>(stage + rr * L::kEpiPitch + (lane & 7) * 4);
+                            o.x += bv.x, o.y += bv.y, o.z += bv.z, o.w += bv.w;
+                            if (g.conv_act == 1) {
+                                o.x = fmaxf(o.x, 0.f), o.y = fmaxf(o.y, 0.f), o.z = fmaxf(o.z, 0.f), o.w = fmaxf(o.w, 0.f);
+                            }
+                            const __half2 lo = __floats2half2_rn(o.x, o.y), hi = __floats2half2_rn(o.z, o.w);
+                            uint2 pk;
+                            pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                            pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(g.conv_out + static_cast<size_t>(m + wp + 1) * g.N + col) = pk;
+                        }
+                        __syncwarp();
+                        continue;
+                    }
                     float* cchunk = cbase + c * 32 + (lane & 7) * 4;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {

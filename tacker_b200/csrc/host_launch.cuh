@@ -36,6 +36,8 @@ struct Options {
     int cp_ppt = 8;      // solo kernel: points per thread and work item (8 = the reference's granularity, measured best)
     int mix_cp_ppt = 8;  // fused kernel
     int mriq_accurate = 0;
+    int mrif_accurate = 0;
+    // (mriq_split, mriq_vpt and mix_mriq_vpt also govern the MRI-FHd kernels, which have the same shape)
     // second dimension of the Coulomb / MRI-Q work items (fast modes only): -1 = the host picks the atoms /
     // samples per item from the launch shape, 0 = never split (deterministic summation order), > 0 = that many
     int cp_split = -1;
@@ -51,6 +53,8 @@ struct Options {
     int mix_pair = 0;           // the same for the tensor role of the fused kernels
     int mix_pair_stages = 4;    // operand stages of the fused stencil kernel on CTA pairs (3 .. 5; the rest goes to the rings)
     int l2_hints = 0;           // fused kernels: GEMM tiles evict-last, stencil planes evict-first in L2
+    int wait_budget_us = 1000000;  // budget of the bounded device-side waits, microseconds at 2 GHz
+    int test_skip_loads = 0;       // test hook: the next n single-CTA tzgemm launches issue no operand loads
     int mix_stencil_cfg = 0;    // tensor-role shape of the fused stencil kernel: 0 auto, 1 = 256x3 stages,
                                 // 2 = 128x4, 3 = 128x3, 4 = 128x2
 };
@@ -161,11 +165,28 @@ static int check_params(void** params, int nparams, int expected) {
 }
 
 struct GemmCall {
-    const __half* A;
+    const __half* A;  // the A matrix, or the bordered input image of the implicit-GEMM convolution
     const __half* B;
     GemmArgs g;
     long long stride_a = 0, stride_b = 0;  // elements between batch entries (0 = dense)
+    bool conv = false;
+    int conv_h = 0;  // image height (rows of the bordered image = conv_h + 2)
 };
+
+static void gemm_args_defaults(GemmArgs* g) {
+    g->status = nullptr;
+    g->batch = 1;
+    g->stride_c = 0;
+    g->l2_hints = 0;
+    g->splitk = 1;
+    g->conv_c = 0;
+    g->conv_w = 0;
+    g->conv_oh = 0;
+    g->conv_act = 0;
+    g->conv_bias = nullptr;
+    g->conv_out = nullptr;
+    g->test_skip_loads = 0;
+}
 
 // params[base .. base+6] = A, B, C, M, N, K, alpha; start/end at the given indices
 static int parse_gemm(void** params, int base, int i_start, int i_end, GemmCall* c) {
@@ -178,11 +199,7 @@ static int parse_gemm(void** params, int base, int i_start, int i_end, GemmCall*
     c->g.alpha = arg<float>(params, base + 6);
     c->g.start = arg<int>(params, i_start);
     c->g.end = arg<int>(params, i_end);
-    c->g.status = nullptr;
-    c->g.batch = 1;
-    c->g.stride_c = 0;
-    c->g.l2_hints = 0;
-    c->g.splitk = 1;
+    gemm_args_defaults(&c->g);
     const bool empty = c->g.start >= c->g.end;
     if (c->g.M < 128 || c->g.N < 64 || c->g.K < 64) return TK_ERR_SHAPE;
     if (c->g.M % 128 || c->g.N % 64 || c->g.K % 64) return TK_ERR_SHAPE;
@@ -192,6 +209,45 @@ static int parse_gemm(void** params, int base, int i_start, int i_end, GemmCall*
         return TK_ERR_ALIGN;
     if (c->g.start < 0) return TK_ERR_ARGS;
     return TK_OK;
+}
+
+// params[base .. base+11] = X (bordered NHWC fp16 image), Wt ([N][9 C] fp16), Y (bordered fp16 output image), M, N, K,
+// alpha, bias, H, W, C, act; start/end at the given indices.  M = H (W + 2) rounded up to 128.
+static int parse_conv(void** params, int base, int i_start, int i_end, GemmCall* c) {
+    gemm_args_defaults(&c->g);
+    c->conv = true;
+    c->A = arg<const __half*>(params, base + 0);
+    c->B = arg<const __half*>(params, base + 1);
+    c->g.conv_out = arg<__half*>(params, base + 2);
+    c->g.C = nullptr;
+    c->g.M = arg<int>(params, base + 3);
+    c->g.N = arg<int>(params, base + 4);
+    c->g.K = arg<int>(params, base + 5);
+    c->g.alpha = arg<float>(params, base + 6);
+    c->g.conv_bias = arg<const float*>(params, base + 7);
+    c->conv_h = arg<int>(params, base + 8);
+    c->g.conv_w = arg<int>(params, base + 9);
+    c->g.conv_c = arg<int>(params, base + 10);
+    c->g.conv_act = arg<int>(params, base + 11);
+    c->g.conv_oh = c->conv_h;
+    c->g.start = arg<int>(params, i_start);
+    c->g.end = arg<int>(params, i_end);
+    if (c->conv_h <= 0 || c->g.conv_w <= 0 || c->g.conv_c <= 0 || c->g.conv_act < 0 || c->g.conv_act > 1) return TK_ERR_ARGS;
+    if (c->g.conv_c % 64 || c->g.K != 9 * c->g.conv_c || c->g.N < 64 || c->g.N % 64) return TK_ERR_SHAPE;
+    if (c->g.M < 128 || c->g.M % 128 || c->g.M < c->conv_h * (c->g.conv_w + 2)) return TK_ERR_SHAPE;
+    const bool empty = c->g.start >= c->g.end;
+    if (!empty && (c->A == nullptr || c->B == nullptr || c->g.conv_out == nullptr)) return TK_ERR_ARGS;
+    if ((reinterpret_cast<uintptr_t>(c->A) & 15u) || (reinterpret_cast<uintptr_t>(c->B) & 15u) ||
+        (reinterpret_cast<uintptr_t>(c->g.conv_out) & 15u) || (reinterpret_cast<uintptr_t>(c->g.conv_bias) & 15u))
+        return TK_ERR_ALIGN;
+    if (c->g.start < 0) return TK_ERR_ARGS;
+    return TK_OK;
+}
+
+// tensor map of the A operand: the matrix, or the bordered image seen as [(H + 2)(W + 2)][C]
+static int make_tmap_a(CUtensorMap* m, const GemmCall& c, int box_rows) {
+    if (c.conv) return make_tmap(m, c.A, (c.conv_h + 2) * (c.g.conv_w + 2), c.g.conv_c, box_rows);
+    return make_tmap(m, c.A, c.g.M, c.g.K, box_rows, c.g.batch, c.stride_a);
 }
 
 static int choose_bn(const GemmArgs& g, int ctas) {
@@ -300,6 +356,25 @@ static int parse_mriq(void** p, int i_start, int i_end, MriqArgs* m) {
     return TK_OK;
 }
 
+// MRI-FHd has MRI-Q's argument list: numK, kGlobalIndex, x, y, z, outR, outI, packed table
+static int parse_mrif(void** p, int i_start, int i_end, MrifArgs* m) {
+    MriqArgs q;
+    const int rc = parse_mriq(p, i_start, i_end, &q);
+    if (rc != TK_OK) return rc;
+    m->numK = q.numK;
+    m->kvals = q.kvals;
+    m->x = q.x;
+    m->y = q.y;
+    m->z = q.z;
+    m->outR = q.Qr;
+    m->outI = q.Qi;
+    m->gx = q.gx;
+    m->start = q.start;
+    m->end = q.end;
+    m->k_per_item = 0;
+    return TK_OK;
+}
+
 static int launch_error(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, what);
@@ -311,14 +386,25 @@ template <int BN>
 static int launch_tzgemm(const GemmCall& c, unsigned ctas, cudaStream_t st) {
     constexpr int STAGES = StagesFor<BN>::value;
     CUtensorMap ta, tb;
-    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM, c.g.batch, c.stride_a);
+    int rc = make_tmap_a(&ta, c, kGemmBM);
     if (rc != TK_OK) return rc;
     rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN, c.g.batch, c.stride_b);
     if (rc != TK_OK) return rc;
+    if (c.conv) {
+        auto ck = tzconv_kernel<BN, STAGES>;
+        if ((rc = enable_smem(ck, gemm_smem_bytes<BN>())) != TK_OK) return rc;
+        ck<<<ctas, kGemmThreads, gemm_smem_bytes<BN>(), st>>>(ta, tb, c.g);
+        return launch_error("tzconv_kernel launch");
+    }
     auto kernel = tzgemm_kernel<BN, STAGES>;
     rc = enable_smem(kernel, gemm_smem_bytes<BN>());
     if (rc != TK_OK) return rc;
-    kernel<<<ctas, kGemmThreads, gemm_smem_bytes<BN>(), st>>>(ta, tb, c.g);
+    GemmArgs g = c.g;
+    if (g_opt.test_skip_loads > 0) {
+        --g_opt.test_skip_loads;
+        g.test_skip_loads = 1;
+    }
+    kernel<<<ctas, kGemmThreads, gemm_smem_bytes<BN>(), st>>>(ta, tb, g);
     return launch_error("tzgemm_kernel launch");
 }
 
@@ -390,6 +476,8 @@ static int run_tzgemm(GemmCall& c, unsigned grid0, cudaStream_t st, bool allow_s
     if (c.g.start >= c.g.end) return TK_OK;
     // one CTA per SM holds the whole tensor memory; more CTAs than SMs would only queue
     const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
+    if (c.conv)  // the convolution form exists for the single-CTA 128-row role only
+        return choose_bn(c.g, static_cast<int>(ctas)) == 256 ? launch_tzgemm<256>(c, ctas, st) : launch_tzgemm<128>(c, ctas, st);
     if (allow_splitk) {
         // a skinny problem has fewer super-tiles than SMs: cut K so that every SM gets a share (C was zeroed by
         // the caller and receives the partial products as reductions)
@@ -476,6 +564,24 @@ static int mriq_split_for(const MriqArgs& m, int vpt, long long warps) {
     return cd_pick_split(static_cast<long long>(m.end - m.start) * (8 / vpt), warps, m.numK, 64);
 }
 
+static int mrif_split_for(const MrifArgs& m, int vpt, long long warps) {
+    if (g_opt.mrif_accurate || g_opt.mriq_split == 0) return 0;
+    if (g_opt.mriq_split > 0) return g_opt.mriq_split;
+    return cd_pick_split(static_cast<long long>(m.end - m.start) * (8 / vpt), warps, m.numK, 64);
+}
+
+static int run_mrif(MrifArgs m, unsigned grid0, unsigned block0, cudaStream_t st) {
+    if (m.start >= m.end) return TK_OK;
+    const unsigned threads = cd_threads(block0, 32, 512);
+    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    const int vpt = g_opt.mriq_vpt == 4 ? 4 : 2;
+    m.k_per_item = mrif_split_for(m, vpt, static_cast<long long>(grid0) * (threads / 32));
+    if (g_opt.mrif_accurate) mrif_kernel<true, 2><<<grid0, threads, 0, st>>>(m);
+    else if (vpt == 4) mrif_kernel<false, 4><<<grid0, threads, 0, st>>>(m);
+    else mrif_kernel<false, 2><<<grid0, threads, 0, st>>>(m);
+    return launch_error("mrif_kernel launch");
+}
+
 static int run_cp(CpArgs a, unsigned grid0, unsigned block0, cudaStream_t st) {
     if (a.start >= a.end) return TK_OK;
     const unsigned threads = cd_threads(block0, 32, 512);
@@ -507,17 +613,19 @@ static int run_mriq(MriqArgs m, unsigned grid0, unsigned block0, cudaStream_t st
 }
 
 // ---- fused launches ----
-enum CdKind { CD_STENCIL, CD_CP, CD_MRIQ };
+enum CdKind { CD_STENCIL, CD_CP, CD_MRIQ, CD_MRIF };
 
 struct CdCall {
     CdKind kind;
     StencilArgs s;
     CpArgs a;
     MriqArgs m;
+    MrifArgs f;
     bool empty() const {
         switch (kind) {
             case CD_STENCIL: return s.start >= s.end;
             case CD_CP: return a.start >= a.end;
+            case CD_MRIF: return f.start >= f.end;
             default: return m.start >= m.end;
         }
     }
@@ -526,13 +634,13 @@ struct CdCall {
 // The stencil's rings share the CTA's shared memory with the tensor role's stages, so the fused stencil
 // kernel exists in several (super-tile width, stage count) shapes: a launch whose GEMM share is small gives
 // most of the shared memory to the rings, a GEMM-heavy launch keeps a deep operand pipeline.
-template <int BN, int STAGES, bool STAGED>
+template <int BN, int STAGES, bool STAGED, bool CONV = false>
 static int launch_mix_stencil(const GemmCall& c, StencilArgs s, unsigned ctas, unsigned threads, cudaStream_t st) {
     constexpr int kGemmBytes = GemmSmem<BN, STAGES, STAGED>::kBytes + 1024;
-    auto k = mix_stencil_kernel<BN, STAGES, STAGED>;
+    auto k = mix_stencil_kernel<BN, STAGES, STAGED, CONV>;
     CUtensorMap ta, tb, tg;
     std::memset(&tg, 0, sizeof(tg));
-    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
+    int rc = make_tmap_a(&ta, c, kGemmBM);
     if (rc != TK_OK) return rc;
     if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN)) != TK_OK) return rc;
     int nwarps = static_cast<int>((threads - kGemmThreads) / 32);
@@ -563,6 +671,7 @@ static int launch_mix_stencil(const GemmCall& c, StencilArgs s, unsigned ctas, u
 }
 
 static int run_mix_stencil(const GemmCall& c, const StencilArgs& s, unsigned ctas, unsigned threads, cudaStream_t st) {
+    if (c.conv) return launch_mix_stencil<128, 4, true, true>(c, s, ctas, threads, st);
     int cfg = g_opt.mix_stencil_cfg;
     if (cfg == 0) {
         // Measured on B200 (config 2; 8 to 18 stencil warps; 64 to 4096 GEMM tiles): the 128-wide super-tile with
@@ -652,6 +761,10 @@ static MriqArgs mriq_with_split(MriqArgs m, int vpt, long long warps) {
     m.k_per_item = mriq_split_for(m, vpt, warps);
     return m;
 }
+static MrifArgs mrif_with_split(MrifArgs m, int vpt, long long warps) {
+    m.k_per_item = mrif_split_for(m, vpt, warps);
+    return m;
+}
 
 static int launch_mix_pair(const GemmCall& c, const CdCall& cd, DeviceInfo* d, unsigned ctas, unsigned threads,
                            cudaStream_t st) {
@@ -661,18 +774,57 @@ static int launch_mix_pair(const GemmCall& c, const CdCall& cd, DeviceInfo* d, u
         if (ppt == 4) return launch_mix_pair_kernel(mix_cp2_kernel<kStagesPair, 4>, c, cd.a, d, ctas, threads, 4, st, cp_with_split);
         return launch_mix_pair_kernel(mix_cp2_kernel<kStagesPair, 8>, c, cd.a, d, ctas, threads, 8, st, cp_with_split);
     }
+    if (cd.kind == CD_MRIF) {
+        if (g_opt.mix_mriq_vpt == 4)
+            return launch_mix_pair_kernel(mix_mrif2_kernel<kStagesPair, 4>, c, cd.f, d, ctas, threads, 4, st, mrif_with_split);
+        return launch_mix_pair_kernel(mix_mrif2_kernel<kStagesPair, 2>, c, cd.f, d, ctas, threads, 2, st, mrif_with_split);
+    }
     if (g_opt.mix_mriq_vpt == 4)
         return launch_mix_pair_kernel(mix_mriq2_kernel<kStagesPair, 4>, c, cd.m, d, ctas, threads, 4, st, mriq_with_split);
     return launch_mix_pair_kernel(mix_mriq2_kernel<kStagesPair, 2>, c, cd.m, d, ctas, threads, 2, st, mriq_with_split);
+}
+
+// fused launches whose tensor role is the implicit-GEMM convolution: one CUDA-core item shape per pair
+// (Coulomb 8 points per thread, MRI-Q / MRI-FHd 4 voxels per thread)
+template <int BN>
+static int launch_mix_conv(const GemmCall& c, CdCall cd, unsigned ctas, unsigned threads, cudaStream_t st) {
+    constexpr int STAGES = StagesFor<BN>::value;
+    const long long cd_warps = static_cast<long long>(ctas) * ((threads - kGemmThreads) / 32);
+    CUtensorMap ta, tb;
+    int rc = make_tmap_a(&ta, c, kGemmBM);
+    if (rc != TK_OK) return rc;
+    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN)) != TK_OK) return rc;
+    const int smem = gemm_smem_bytes<BN>();
+    if (cd.kind == CD_CP) {
+        cd.a.atoms_per_item = cp_split_for(cd.a, 8, cd_warps);
+        auto k = mix_cp_kernel<BN, STAGES, 8, true>;
+        if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+        k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
+    } else if (cd.kind == CD_MRIF) {
+        cd.f.k_per_item = mrif_split_for(cd.f, 4, cd_warps);
+        auto k = mix_mrif_kernel<BN, STAGES, 4, true>;
+        if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+        k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.f);
+    } else if (cd.kind == CD_MRIQ) {
+        cd.m.k_per_item = mriq_split_for(cd.m, 4, cd_warps);
+        auto k = mix_mriq_kernel<BN, STAGES, 4, true>;
+        if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+        k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.m);
+    } else {
+        return TK_ERR_ARGS;  // the stencil pair goes through run_mix_stencil
+    }
+    return launch_error("fused convolution launch");
 }
 
 template <int BN>
 static int launch_mix(const GemmCall& c, CdCall cd, unsigned ctas, unsigned threads, cudaStream_t st) {
     constexpr int STAGES = StagesFor<BN>::value;
     const long long cd_warps = static_cast<long long>(ctas) * ((threads - kGemmThreads) / 32);
+    if (c.conv) return launch_mix_conv<BN>(c, cd, ctas, threads, st);
     if (cd.kind == CD_CP) cd.a.atoms_per_item = cp_split_for(cd.a, g_opt.mix_cp_ppt, cd_warps);
     const int mvpt = g_opt.mix_mriq_vpt == 4 ? 4 : 2;
     if (cd.kind == CD_MRIQ) cd.m.k_per_item = mriq_split_for(cd.m, mvpt, cd_warps);
+    if (cd.kind == CD_MRIF) cd.f.k_per_item = mrif_split_for(cd.f, mvpt, cd_warps);
     CUtensorMap ta, tb;
     int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
     if (rc != TK_OK) return rc;
@@ -695,6 +847,18 @@ static int launch_mix(const GemmCall& c, CdCall cd, unsigned ctas, unsigned thre
                 auto k = mix_cp_kernel<BN, STAGES, 8>;
                 if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
                 k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.a);
+            }
+            break;
+        }
+        case CD_MRIF: {
+            if (mvpt == 4) {
+                auto k = mix_mrif_kernel<BN, STAGES, 4>;
+                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.f);
+            } else {
+                auto k = mix_mrif_kernel<BN, STAGES, 2>;
+                if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+                k<<<ctas, threads, smem, st>>>(ta, tb, c.g, cd.f);
             }
             break;
         }
@@ -733,6 +897,7 @@ static int run_mix(GemmCall& c, const CdCall& cd_in, unsigned grid0, unsigned bl
         switch (cd.kind) {
             case CD_STENCIL: return run_stencil(cd.s, grid0, cdt, st);
             case CD_CP: return run_cp(cd.a, grid0, cdt, st);
+            case CD_MRIF: return run_mrif(cd.f, grid0, cdt, st);
             default: return run_mriq(cd.m, grid0, cdt, st);
         }
     }
@@ -741,7 +906,7 @@ static int run_mix(GemmCall& c, const CdCall& cd_in, unsigned grid0, unsigned bl
     const unsigned threads = kGemmThreads + cdt;
     // The tensor role on CTA pairs pays once the launch holds at least a wave of pair tiles (measured on the
     // GEMM + stencil pair: 37.3 vs 41.4 us with 2048 tiles, 51.2 vs 55.4 us with 4096; behind by 2 us with 1024 and fewer).
-    const bool pair_ok = c.g.M >= 256 && c.g.N >= 256 && ctas >= 2;
+    const bool pair_ok = !c.conv && c.g.M >= 256 && c.g.N >= 256 && ctas >= 2;
     const bool pair_wins = c.g.N % 256 == 0 && static_cast<long long>(c.g.end - c.g.start) >= 16ll * (ctas / 2);
     if (pair_ok && (g_opt.mix_pair > 0 || (g_opt.mix_pair == 0 && pair_wins))) {
         if (cd.kind == CD_STENCIL) return run_mix_stencil_pair(c, cd.s, d, ctas, threads, st);
@@ -773,6 +938,7 @@ static int generated_mix_launch(CdKind kind, int cd_warps, void** params, int np
     switch (kind) {
         case CD_STENCIL: rc = parse_stencil(params, i_start, i_end, &cd.s); break;
         case CD_CP: rc = parse_cp(params, i_start, i_end, &cd.a); break;
+        case CD_MRIF: rc = parse_mrif(params, i_start, i_end, &cd.f); break;
         default: rc = parse_mriq(params, i_start, i_end, &cd.m); break;
     }
     if (rc != TK_OK) return rc;

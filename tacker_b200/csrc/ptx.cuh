@@ -9,7 +9,8 @@
 namespace tk {
 
 // ---- device status word ------------------------------------------------------
-// 0 = ok.  A bounded wait that expires stores (code << 8 | site) once.
+// 0 = ok.  The first bounded wait that expires stores its code below (and nothing else: a later expiry does not
+// overwrite it); the host reads and clears the word.
 enum : unsigned {
     DEV_OK = 0,
     DEV_TIMEOUT_EMPTY = 1,      // producer waited for a free smem stage
@@ -19,8 +20,9 @@ enum : unsigned {
     DEV_TMEM_ALLOC = 5,
 };
 
-// about one second at 2 GHz
-constexpr long long kWaitBudgetCycles = 2000000000ll;
+// Clock budget of every bounded wait: about one second at 2 GHz unless the host stores another value (a test
+// shortens it to make a wait run out quickly).
+__device__ long long g_wait_budget_cycles = 2000000000ll;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -89,7 +91,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitBudgetCycles) {
+            if (clock64() - t0 > *const_cast<volatile long long*>(&g_wait_budget_cycles)) {
                 *abort_flag = 1u;
                 atomicCAS(status, 0u, code);
                 return false;

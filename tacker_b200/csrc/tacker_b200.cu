@@ -44,6 +44,7 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "cp_ppt")) return &g_opt.cp_ppt;
     if (!std::strcmp(name, "mix_cp_ppt")) return &g_opt.mix_cp_ppt;
     if (!std::strcmp(name, "mriq_accurate")) return &g_opt.mriq_accurate;
+    if (!std::strcmp(name, "mrif_accurate")) return &g_opt.mrif_accurate;
     if (!std::strcmp(name, "cp_split")) return &g_opt.cp_split;
     if (!std::strcmp(name, "mriq_split")) return &g_opt.mriq_split;
     if (!std::strcmp(name, "mriq_vpt")) return &g_opt.mriq_vpt;
@@ -55,6 +56,8 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "l2_hints")) return &g_opt.l2_hints;
     if (!std::strcmp(name, "tzgemm_m256")) return &g_opt.tzgemm_m256;
     if (!std::strcmp(name, "mix_stencil_cfg")) return &g_opt.mix_stencil_cfg;
+    if (!std::strcmp(name, "wait_budget_us")) return &g_opt.wait_budget_us;
+    if (!std::strcmp(name, "test_skip_loads")) return &g_opt.test_skip_loads;
     if (!std::strcmp(name, "tzgemm_pair")) return &g_opt.tzgemm_pair;
     if (!std::strcmp(name, "mix_pair")) return &g_opt.mix_pair;
     if (!std::strcmp(name, "mix_pair_stages")) return &g_opt.mix_pair_stages;
@@ -71,6 +74,12 @@ TK_API int tk_set_option(const char* name, int value) {
     if ((slot == &g_opt.mriq_vpt || slot == &g_opt.mix_mriq_vpt) && value != 2 && value != 4) return TK_ERR_ARGS;
     if ((slot == &g_opt.stencil_ring || slot == &g_opt.mix_stencil_ring) && (value < kStMinRing || value > kStMaxRing))
         return TK_ERR_ARGS;
+    if (slot == &g_opt.wait_budget_us) {  // takes effect on the current device, for the launches that follow
+        if (value < 1) return TK_ERR_ARGS;
+        const long long cycles = 2000ll * value;
+        TK_CUDA(cudaMemcpyToSymbol(g_wait_budget_cycles, &cycles, sizeof(cycles)));
+    }
+    if (slot == &g_opt.test_skip_loads && value < 0) return TK_ERR_ARGS;
     *slot = value;
     return TK_OK;
 }
@@ -93,6 +102,17 @@ TK_API int tk_device_status(unsigned* code) {
     return TK_OK;
 }
 
+TK_API int tk_device_check(void) {
+    unsigned code = 0;
+    const int rc = tk_device_status(&code);
+    if (rc != TK_OK) return rc;
+    if (code != 0u) {
+        t_last_error = "a bounded device-side wait expired (code " + std::to_string(code) + ")";
+        return TK_ERR_DEVICE_WAIT;
+    }
+    return TK_OK;
+}
+
 // ---- solo launchers ----
 TK_API int tk_launch_gptb_tzgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
                                  unsigned, void* stream) {
@@ -112,6 +132,16 @@ TK_API int tk_launch_gptb_tzgemm_acc(void** params, int nparams, const unsigned 
     GemmCall c;
     if ((rc = parse_gemm(params, 0, 13, 15, &c)) != TK_OK) return rc;
     return run_tzgemm(c, grid[0], static_cast<cudaStream_t>(stream), true);
+}
+
+TK_API int tk_launch_gptb_tzconv(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                 unsigned, void* stream) {
+    int rc = check_params(params, nparams, 22);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    GemmCall c;
+    if ((rc = parse_conv(params, 0, 18, 20, &c)) != TK_OK) return rc;
+    return run_tzgemm(c, grid[0], static_cast<cudaStream_t>(stream));
 }
 
 TK_API int tk_launch_gptb_stencil(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
@@ -144,11 +174,21 @@ TK_API int tk_launch_gptb_mriq(void** params, int nparams, const unsigned grid[3
     return run_mriq(m, grid[0], block[0], static_cast<cudaStream_t>(stream));
 }
 
+TK_API int tk_launch_gptb_mrif(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                               unsigned, void* stream) {
+    int rc = check_params(params, nparams, 18);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    MrifArgs m;
+    if ((rc = parse_mrif(params, 14, 16, &m)) != TK_OK) return rc;
+    return run_mrif(m, grid[0], block[0], static_cast<cudaStream_t>(stream));
+}
+
 // ---- fused launchers: params = CUDA-core list (n_cd + 6 + 3), then tzgemm (7 + 6 + 3) ----
 static int launch_mix_common(CdKind kind, int n_cd, void** params, int nparams, const unsigned grid[3],
-                             const unsigned block[3], void* stream) {
+                             const unsigned block[3], void* stream, bool conv = false) {
     const int cd_len = n_cd + 6 + 3;
-    int rc = check_params(params, nparams, cd_len + 16);
+    int rc = check_params(params, nparams, cd_len + (conv ? 21 : 16));
     if (rc != TK_OK) return rc;
     if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
     CdCall cd;
@@ -157,11 +197,14 @@ static int launch_mix_common(CdKind kind, int n_cd, void** params, int nparams, 
     switch (kind) {
         case CD_STENCIL: rc = parse_stencil(params, i_start, i_end, &cd.s); break;
         case CD_CP: rc = parse_cp(params, i_start, i_end, &cd.a); break;
+        case CD_MRIF: rc = parse_mrif(params, i_start, i_end, &cd.f); break;
         default: rc = parse_mriq(params, i_start, i_end, &cd.m); break;
     }
     if (rc != TK_OK) return rc;
     GemmCall c;
-    if ((rc = parse_gemm(params, cd_len, cd_len + 13, cd_len + 15, &c)) != TK_OK) return rc;
+    if (conv) rc = parse_conv(params, cd_len, cd_len + 18, cd_len + 20, &c);
+    else rc = parse_gemm(params, cd_len, cd_len + 13, cd_len + 15, &c);
+    if (rc != TK_OK) return rc;
     return run_mix(c, cd, grid[0], block[0], static_cast<cudaStream_t>(stream));
 }
 
@@ -178,6 +221,29 @@ TK_API int tk_launch_mix_tzgemm_cp(void** params, int nparams, const unsigned gr
 TK_API int tk_launch_mix_tzgemm_mriq(void** params, int nparams, const unsigned grid[3],
                                      const unsigned block[3], unsigned, void* stream) {
     return launch_mix_common(CD_MRIQ, 8, params, nparams, grid, block, stream);
+}
+
+TK_API int tk_launch_mix_tzgemm_mrif(void** params, int nparams, const unsigned grid[3],
+                                     const unsigned block[3], unsigned, void* stream) {
+    return launch_mix_common(CD_MRIF, 8, params, nparams, grid, block, stream);
+}
+
+// the same pairs with the implicit-GEMM convolution as the tensor role: CUDA-core list, then tzconv's 12 + 6 + 3
+TK_API int tk_launch_mix_tzconv_stencil(void** params, int nparams, const unsigned grid[3],
+                                        const unsigned block[3], unsigned, void* stream) {
+    return launch_mix_common(CD_STENCIL, 7, params, nparams, grid, block, stream, true);
+}
+TK_API int tk_launch_mix_tzconv_cp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                   unsigned, void* stream) {
+    return launch_mix_common(CD_CP, 4, params, nparams, grid, block, stream, true);
+}
+TK_API int tk_launch_mix_tzconv_mriq(void** params, int nparams, const unsigned grid[3],
+                                     const unsigned block[3], unsigned, void* stream) {
+    return launch_mix_common(CD_MRIQ, 8, params, nparams, grid, block, stream, true);
+}
+TK_API int tk_launch_mix_tzconv_mrif(void** params, int nparams, const unsigned grid[3],
+                                     const unsigned block[3], unsigned, void* stream) {
+    return launch_mix_common(CD_MRIF, 8, params, nparams, grid, block, stream, true);
 }
 
 // ---- non-persistent shape: every virtual block of the reference grid ----
@@ -232,6 +298,23 @@ TK_API int tk_launch_ori_mriq(void** params, int nparams, const unsigned grid[3]
     return run_mriq(m, static_cast<unsigned>(d->sm_count) * 4u, 256, static_cast<cudaStream_t>(stream));
 }
 
+TK_API int tk_launch_ori_mrif(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                              unsigned, void* stream) {
+    int rc = check_params(params, nparams, 8);
+    if (rc != TK_OK) return rc;
+    if (!grid || !block || grid[0] == 0) return TK_ERR_LAUNCH_CONFIG;
+    if (block[0] != 256) return TK_ERR_SHAPE;
+    int gx = static_cast<int>(grid[0]), one = 1, bx = 256;
+    int start = 0, end = gx, step = 0, tb = 0;
+    void* p[18] = {params[0], params[1], params[2], params[3], params[4], params[5], params[6], params[7],
+                   &gx, &one, &one, &bx, &one, &one, &start, &step, &end, &tb};
+    MrifArgs m;
+    if ((rc = parse_mrif(p, 14, 16, &m)) != TK_OK) return rc;
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    return run_mrif(m, static_cast<unsigned>(d->sm_count) * 2u, 512, static_cast<cudaStream_t>(stream));
+}
+
 // ---- preparation ----
 TK_API int tk_cp_pack_atoms(const float* atoms_xyzq, int count, float zplane, float* packed, void* stream) {
     if (count < 0) return TK_ERR_ARGS;
@@ -253,6 +336,18 @@ TK_API int tk_mriq_pack_kvalues(const float* kx, const float* ky, const float* k
     mriq_pack_kernel<<<(numK + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         kx, ky, kz, phiR, phiI, numK, reinterpret_cast<float4*>(kvals));
     return launch_error("mriq_pack_kernel launch");
+}
+
+TK_API int tk_mrif_pack_kvalues(const float* kx, const float* ky, const float* kz, const float* phiR,
+                                const float* phiI, const float* dR, const float* dI, int numK, float* kvals,
+                                void* stream) {
+    if (numK < 0) return TK_ERR_ARGS;
+    if (numK == 0) return TK_OK;
+    if (!kx || !ky || !kz || !phiR || !phiI || !dR || !dI || !kvals) return TK_ERR_ARGS;
+    if (reinterpret_cast<uintptr_t>(kvals) & 15u) return TK_ERR_ALIGN;
+    mrif_pack_kernel<<<(numK + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        kx, ky, kz, phiR, phiI, dR, dI, numK, reinterpret_cast<float4*>(kvals));
+    return launch_error("mrif_pack_kernel launch");
 }
 
 TK_API int tk_im2col_f32(const float* data_im, int channels, int height, int width, int kernel_h, int kernel_w,
@@ -326,6 +421,11 @@ static const KeyEntry kKeys[] = {
     {"gptb_tzgemm", tk_launch_gptb_tzgemm, 17},       {"gptb_stencil", tk_launch_gptb_stencil, 17},
     {"gptb_tzgemm_acc", tk_launch_gptb_tzgemm_acc, 17},
     {"gptb_cp", tk_launch_gptb_cp, 14},               {"gptb_mriq", tk_launch_gptb_mriq, 18},
+    {"gptb_mrif", tk_launch_gptb_mrif, 18},           {"tzgemm_mrif", tk_launch_mix_tzgemm_mrif, 33},
+    {"ori_mrif", tk_launch_ori_mrif, 8},
+    {"gptb_tzconv", tk_launch_gptb_tzconv, 22},       {"tzconv_stencil", tk_launch_mix_tzconv_stencil, 37},
+    {"tzconv_cp", tk_launch_mix_tzconv_cp, 34},       {"tzconv_mriq", tk_launch_mix_tzconv_mriq, 38},
+    {"tzconv_mrif", tk_launch_mix_tzconv_mrif, 38},
     {"tzgemm_stencil", tk_launch_mix_tzgemm_stencil, 32}, {"tzgemm_cp", tk_launch_mix_tzgemm_cp, 29},
     {"tzgemm_mriq", tk_launch_mix_tzgemm_mriq, 33},   {"ori_stencil", tk_launch_ori_stencil, 7},
     {"ori_cp", tk_launch_ori_cp, 4},                  {"ori_mriq", tk_launch_ori_mriq, 8},
@@ -375,6 +475,11 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
         info->tmem_columns = 512;
         return fill_info(tzgemm_kernel<256, kStages256>, kGemmThreads, gsm, info);
     }
+    if (k == "gptb_tzconv") {
+        info->threads_tensor = kGemmThreads;
+        info->tmem_columns = 512;
+        return fill_info(tzconv_kernel<256, kStages256>, kGemmThreads, gsm, info);
+    }
     if (k == "gptb_stencil" || k == "ori_stencil") {
         info->threads_cd_min = 32;
         info->threads_cd_default = 256;
@@ -390,9 +495,23 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
         info->threads_cd_default = 256;
         return fill_info(mriq_kernel<false, 2>, 256, 0, info);
     }
+    if (k == "gptb_mrif" || k == "ori_mrif") {
+        info->threads_cd_min = 32;
+        info->threads_cd_default = 256;
+        return fill_info(mrif_kernel<false, 2>, 256, 0, info);
+    }
     info->threads_tensor = kGemmThreads;
     info->tmem_columns = 512;
     info->threads_cd_default = 256;
+    if (k == "tzgemm_mrif") {
+        info->threads_cd_min = 32;
+        return fill_info(mix_mrif_kernel<256, kStages256, 4>, kGemmThreads + 256, gsm, info);
+    }
+    info->threads_cd_min = 32;
+    if (k == "tzconv_stencil") return fill_info(mix_stencil_kernel<128, 4, true, true>, kGemmThreads + 256, gsm, info);
+    if (k == "tzconv_cp") return fill_info(mix_cp_kernel<256, kStages256, 8, true>, kGemmThreads + 256, gsm, info);
+    if (k == "tzconv_mriq") return fill_info(mix_mriq_kernel<256, kStages256, 4, true>, kGemmThreads + 256, gsm, info);
+    if (k == "tzconv_mrif") return fill_info(mix_mrif_kernel<256, kStages256, 4, true>, kGemmThreads + 256, gsm, info);
     if (k == "tzgemm_stencil") {
         info->threads_cd_min = 32;
         return fill_info(mix_stencil_kernel<128, 4, true>, kGemmThreads + 256, gsm, info);
@@ -534,11 +653,7 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     c.g.N = N;
     c.g.K = K;
     c.g.alpha = alpha;
-    c.g.status = nullptr;
-    c.g.batch = 1;
-    c.g.stride_c = 0;
-    c.g.l2_hints = 0;
-    c.g.splitk = 1;
+    gemm_args_defaults(&c.g);
     if (M < 128 || N < 64 || K < 64 || M % 128 || N % 64 || K % 64) return TK_ERR_SHAPE;
     const int tiles = (M / 64) * (N / 64);
     CdCall cd;
@@ -820,6 +935,33 @@ TK_API int tk_im2col_nhwc_f16(const float* x, int H, int W, int C, int kh, int k
     return launch_error("im2col_nhwc_f16_kernel launch");
 }
 
+TK_API int tk_bias_act_f16_bordered(const float* x, int ldx, const float* bias, void* out_half, int H, int W, int C, int act,
+                                    void* stream) {
+    if (!x || !out_half || H <= 0 || W <= 0 || C <= 0 || ldx < C || act < 0 || act > 1) return TK_ERR_ARGS;
+    TK_LAYER_PROLOGUE();
+    bias_act_f16_bordered_kernel<<<blocks_for(static_cast<long long>(H) * W * C, d->sm_count), 256, 0, st>>>(
+        x, ldx, bias, static_cast<__half*>(out_half), H, W, C, act);
+    return launch_error("bias_act_f16_bordered_kernel launch");
+}
+
+TK_API int tk_maxpool2x2_f16_bordered(const void* x_half, int H, int W, int C, void* out_half, void* stream) {
+    if (!x_half || !out_half || H < 2 || W < 2 || C <= 0) return TK_ERR_ARGS;
+    if (C % 8 || H % 2 || W % 2) return TK_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x_half) & 15u) || (reinterpret_cast<uintptr_t>(out_half) & 15u)) return TK_ERR_ALIGN;
+    TK_LAYER_PROLOGUE();
+    maxpool2x2_f16_bordered_kernel<<<blocks_for(static_cast<long long>(H / 2) * (W / 2) * (C / 8), d->sm_count), 256, 0,
+                                     st>>>(static_cast<const __half*>(x_half), H, W, C, static_cast<__half*>(out_half));
+    return launch_error("maxpool2x2_f16_bordered_kernel launch");
+}
+
+TK_API int tk_unborder_f16(const void* x_half, int H, int W, int C, void* row_half, void* stream) {
+    if (!x_half || !row_half || H <= 0 || W <= 0 || C <= 0) return TK_ERR_ARGS;
+    TK_LAYER_PROLOGUE();
+    unborder_f16_kernel<<<blocks_for(static_cast<long long>(H) * W * C, d->sm_count), 256, 0, st>>>(
+        static_cast<const __half*>(x_half), H, W, C, static_cast<__half*>(row_half));
+    return launch_error("unborder_f16_kernel launch");
+}
+
 TK_API int tk_rows_f32_to_f16(const float* x, int rows, int cols, int ld_in, void* A_half, int rows_pad, int cols_pad,
                               void* stream) {
     if (!x || !A_half || rows <= 0 || cols <= 0 || ld_in < cols || rows_pad < rows || cols_pad < cols) return TK_ERR_ARGS;
@@ -906,10 +1048,8 @@ TK_API int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int 
     c.g.alpha = alpha;
     c.g.start = 0;
     c.g.end = (M / 64) * (N / 64);
-    c.g.status = nullptr;
+    gemm_args_defaults(&c.g);
     c.g.batch = batch;
-    c.g.l2_hints = 0;
-    c.g.splitk = 1;
     c.g.stride_c = stride_c > 0 ? stride_c : static_cast<long long>(M) * N;
     DeviceInfo* d = nullptr;
     int rc = device_info(&d);

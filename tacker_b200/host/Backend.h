@@ -45,8 +45,15 @@ public:
     virtual int cpPackAtoms(const float* atoms, int count, float zplane, float* packed, stream_t s) = 0;
     virtual int mriqPackKvalues(const float* kx, const float* ky, const float* kz, const float* phiR,
                                 const float* phiI, int numK, float* kvals, stream_t s) = 0;
+    virtual int mrifPackKvalues(const float* kx, const float* ky, const float* kz, const float* phiR,
+                                const float* phiI, const float* dR, const float* dI, int numK, float* kvals,
+                                stream_t s) = 0;
     virtual int im2colNhwcHalf(const float* x, int H, int W, int C, int kh, int kw, int pad, int stride, void* A,
                                int M_pad, int K_pad, stream_t s) = 0;
+    virtual int biasActHalfBordered(const float* x, int ldx, const float* bias, void* out, int H, int W, int C, int act,
+                                    stream_t s) = 0;
+    virtual int maxpoolHalfBordered(const void* x, int H, int W, int C, void* out, stream_t s) = 0;
+    virtual int unborderHalf(const void* x, int H, int W, int C, void* row, stream_t s) = 0;
     virtual int rowsToHalf(const float* x, int rows, int cols, int ld, void* A, int rows_pad, int cols_pad,
                            stream_t s) = 0;
     virtual int biasAct(const float* x, int ldx, const float* bias, float* out, int rows, int cols, int ldo, int act,

@@ -8,6 +8,7 @@
 StencilProblem creatorStencilProblem;
 CPProblem creatorCPProblem;
 MRIQProblem creatorMRIQProblem;
+MRIFProblem creatorMRIFProblem;
 
 namespace {
 std::map<std::string, GPTBKernel*> kernelMap;
@@ -34,10 +35,13 @@ GPTBKernel* createKernel(const std::string& name) {
     dim3h grid, block;
     if (name == "cp") {
         ori = new OriCPKernel(id = 10, creatorCPProblem);
-        geometry(name, 1, 256, &grid, &block);
+        geometry(name, 2, 512, &grid, &block);
     } else if (name == "mriq") {
         ori = new OriMRIQKernel(id = 18, creatorMRIQProblem);
-        geometry(name, 1, 256, &grid, &block);
+        geometry(name, 2, 512, &grid, &block);
+    } else if (name == "mrif") {  // id as in src/Creator.cu:109-121
+        ori = new OriMRIFKernel(id = 17, creatorMRIFProblem);
+        geometry(name, 2, 512, &grid, &block);
     } else if (name == "stencil") {
         ori = new OriSTENCILKernel(id = 20, creatorStencilProblem);
         geometry(name, 2, 256, &grid, &block);
@@ -58,6 +62,7 @@ MixKernel* createMixKernel(const std::string& name, int m, int n, int k) {
     if (m <= 0 || n <= 0 || k <= 0) {  // headline GEMM of each pair
         if (cd == "stencil") m = 4096, n = 4096, k = 1024;
         else if (cd == "cp") m = 2048, n = 2048, k = 2048;
+        else if (cd != "mriq" && cd != "mrif") logger.ERROR("createMixKernel: unknown pair {" + name + "}");
         else m = 4096, n = 4096, k = 2048;
     }
     const std::string key = name + ":" + std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k);

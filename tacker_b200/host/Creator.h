@@ -10,13 +10,14 @@
 #include "ori_kernel/ori_kernels.h"
 #include "tzgemm_kernel.h"
 
-// "cp", "stencil", "mriq": the persistent form of the benchmark kernel over all of its virtual blocks
+// "cp", "stencil", "mriq", "mrif": the persistent form of the benchmark kernel over all of its virtual blocks
 GPTBKernel* createKernel(const std::string& name);
-// "tzgemm_cp", "tzgemm_stencil", "tzgemm_mriq": the benchmark kernel fused with a tzgemm of m x n x k
+// "tzgemm_cp", "tzgemm_stencil", "tzgemm_mriq", "tzgemm_mrif": the benchmark kernel fused with a tzgemm of m x n x k
 // (default: the headline GEMM shape of each pair)
 MixKernel* createMixKernel(const std::string& name, int m = 0, int n = 0, int k = 0);
 // problem sizes used by createKernel (defaults = the headline configurations); set before the first call
 extern StencilProblem creatorStencilProblem;
 extern CPProblem creatorCPProblem;
 extern MRIQProblem creatorMRIQProblem;
+extern MRIFProblem creatorMRIFProblem;
 void destroyCreatedKernels();

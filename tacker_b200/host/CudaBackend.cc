@@ -103,9 +103,23 @@ public:
                         int numK, float* kvals, stream_t s) override {
         return tk_mriq_pack_kvalues(kx, ky, kz, phiR, phiI, numK, kvals, s);
     }
+    int mrifPackKvalues(const float* kx, const float* ky, const float* kz, const float* phiR, const float* phiI,
+                        const float* dR, const float* dI, int numK, float* kvals, stream_t s) override {
+        return tk_mrif_pack_kvalues(kx, ky, kz, phiR, phiI, dR, dI, numK, kvals, s);
+    }
     int im2colNhwcHalf(const float* x, int H, int W, int C, int kh, int kw, int pad, int stride, void* A, int M_pad,
                        int K_pad, stream_t s) override {
         return tk_im2col_nhwc_f16(x, H, W, C, kh, kw, pad, stride, A, M_pad, K_pad, s);
+    }
+    int biasActHalfBordered(const float* x, int ldx, const float* bias, void* out, int H, int W, int C, int act,
+                            stream_t s) override {
+        return tk_bias_act_f16_bordered(x, ldx, bias, out, H, W, C, act, s);
+    }
+    int maxpoolHalfBordered(const void* x, int H, int W, int C, void* out, stream_t s) override {
+        return tk_maxpool2x2_f16_bordered(x, H, W, C, out, s);
+    }
+    int unborderHalf(const void* x, int H, int W, int C, void* row, stream_t s) override {
+        return tk_unborder_f16(x, H, W, C, row, s);
     }
     int rowsToHalf(const float* x, int rows, int cols, int ld, void* A, int rows_pad, int cols_pad,
                    stream_t s) override {

@@ -55,6 +55,12 @@ public:
         if (!kernelFunc) logger.ERROR("load kernel {" + funcKey + "} failed!");
     }
     std::vector<int> getArgs() override { return std::vector<int>(); }
+    // Launch through a launcher of another module (a fused kernel emitted by the generator and registered with the
+    // ModuleCenter) instead of the library's own kernel of this key; same argument list.
+    void useFunction(tk_launch_fn fn, const std::string& module) {
+        kernelFunc = reinterpret_cast<void*>(fn);
+        moduleName = module;
+    }
 
 protected:
     void executeImpl(stream_t stream) override { launch(kernelParams, stream); }

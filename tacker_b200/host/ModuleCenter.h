@@ -16,10 +16,15 @@ public:
     bool hasModule(const std::string& moduleName) const;
     // launcher exported as `symbol` by the module, nullptr when absent
     tk_launch_fn getFunction(const std::string& moduleName, const std::string& symbol);
+    void* getSymbol(const std::string& moduleName, const std::string& symbol);
+    // Name of the launcher a generated module exports: "tk_launch_<kernel name>", where the kernel name is the file
+    // name of the module without directory and extension (tzgemm_mriq_1_16.so -> tk_launch_tzgemm_mriq_1_16).
+    std::string launcherOf(const std::string& moduleName) const;
     size_t size() const { return modules.size(); }
 
 private:
     std::map<std::string, void*> modules;
+    std::map<std::string, std::string> paths;
 };
 
 extern ModuleCenter moduleCenter;

@@ -9,6 +9,7 @@
 #include <memory>
 
 #include "Logger.h"
+#include "ModuleCenter.h"
 #include "Recorder.h"
 #include "json.h"
 
@@ -18,6 +19,8 @@ std::vector<int> get_mnk_from_cudnn_args(std::vector<int>& a) {
     return std::vector<int>(mnk, mnk + 3);
 }
 
+int generatedLaunchers = 0;
+
 namespace {
 std::map<std::pair<TzLayer*, GPTBKernel*>, std::unique_ptr<MixKernel>> g_mix_cache;
 
@@ -25,8 +28,9 @@ void run_fused(TzLayer* layer, GPTBKernel* cd, int cd_start, int cd_end, stream_
     auto key = std::make_pair(layer, cd);
     auto it = g_mix_cache.find(key);
     if (it == g_mix_cache.end()) {
-        const std::string name = "tzgemm_" + cd->kernelName;
-        int per_sm = get_kernel_info(name, "gridsize"), threads = get_kernel_info(name, "blocksize");
+        const std::string table = "tzgemm_" + cd->kernelName;                   // launch shape: the pair's JSON entry
+        const std::string name = layer->fusedPrefix() + cd->kernelName;         // kernel: GEMM or convolution form
+        int per_sm = get_kernel_info(table, "gridsize"), threads = get_kernel_info(table, "blocksize");
         if (per_sm == JSON_NOT_FOUND || per_sm <= 0) per_sm = 1;
         if (threads == JSON_NOT_FOUND || threads <= 192) threads = 192 + 384;
         it = g_mix_cache
@@ -34,6 +38,28 @@ void run_fused(TzLayer* layer, GPTBKernel* cd, int cd_start, int cd_end, stream_
                                    1, name, cd, layer->gemm(), dim3h(static_cast<unsigned>(backend().smCount() * per_sm), 1, 1),
                                    dim3h(static_cast<unsigned>(threads), 1, 1), cd_start, cd_end, 0, layer->tiles())))
                  .first;
+        // A generated module for this pair (JSON "tzgemm_<cd>"."module" = its name, or registered from the command
+        // line under the pair's name) replaces the library's fused kernel -- the step the reference takes by pasting
+        // the generator's output into src/mix_kernel and picking it through gridsize / blocksize
+        // (src/TaskManager.cu:253-264).  Generated kernels carry the GEMM form of the tensor role only.
+        if (!layer->implicit) {
+            std::string module = sget_kernel_info(table, "module");
+            if (module.empty() && moduleCenter.hasModule(table)) module = table;
+            if (!module.empty() && moduleCenter.hasModule(module)) {
+                std::string symbol = moduleCenter.launcherOf(module);
+                tk_launch_fn fn = moduleCenter.getFunction(module, symbol);
+                if (fn) {
+                    int info[4] = {0, 0, 0, 0};
+                    auto infofn = reinterpret_cast<int (*)(int*)>(moduleCenter.getSymbol(module, "tk_generated_info_" + symbol.substr(10)));
+                    if (infofn) infofn(info);
+                    if (info[0] > 0) it->second->launchBlockDim = dim3h(static_cast<unsigned>(info[0]), 1, 1);
+                    it->second->useFunction(fn, module);
+                    generatedLaunchers += 1;
+                } else {
+                    logger.WARNING("module {" + module + "} has no launcher " + symbol + "; using the library kernel");
+                }
+            }
+        }
     }
     it->second->setRanges(cd_start, cd_end, 0, layer->tiles());
     layer->prepare(stream);        // im2col / cast on the same stream as the fused launch
@@ -421,7 +447,39 @@ FusedColocationResult TaskManager::runFusedColocation(double seconds, double qps
     const float be_full_ms = timed_ms([&] { bek->execute(stream); }, 3);
     const float be_fixed_ms = std::min(be_full_ms, timedBlocks(bek, 0, 1, stream));  // see schedule()
 
-    // ---- which layers to fuse, and with how many blocks: the profiled table, then a measurement per layer ----
+    // Everything in this mode is replayed as CUDA graphs, so prices are taken on graphs too: a launch inside a graph
+    // costs far less than a launch timed from the host, and a rule fed with host-timed launches lets rides through
+    // that lose once captured.
+    auto graph_ms = [&](const std::function<void()>& body) -> float {
+        body();
+        be.streamSync(stream);
+        void* g = be.graphCapture(stream, body);
+        if (!g) return timed_ms(body, 10);
+        for (int i = 0; i < 3; ++i) be.graphLaunch(g, stream);
+        const float t = timed_ms([&] { be.graphLaunch(g, stream); }, 20);
+        be.streamSync(stream);
+        be.graphDestroy(g);
+        return t;
+    };
+    auto launch_blocks = [&](int s0, int e0) {
+        const int keep_s = bek->gptbParams.ptb_start_block_pos, keep_e = bek->gptbParams.ptb_end_block_pos;
+        bek->gptbParams.ptb_start_block_pos = s0;
+        bek->gptbParams.ptb_end_block_pos = e0;
+        bek->execute(stream);
+        bek->gptbParams.ptb_start_block_pos = keep_s;
+        bek->gptbParams.ptb_end_block_pos = keep_e;
+    };
+    // idle-time chunk of the best-effort kernel: about be_chunk_ms of device time; its price per block is what a
+    // block costs when it is time-sliced, i.e. what a ride has to beat
+    const int chunk_blocks = std::max(1, std::min(be_blocks, static_cast<int>(be_blocks * be_chunk_ms / std::max(be_full_ms, 1e-6f))));
+    const float block_price_ms = graph_ms([&] { launch_blocks(0, chunk_blocks); }) / chunk_blocks;
+    (void)be_fixed_ms;
+
+    // ---- which layers carry best-effort blocks, and how many ----
+    // A ride is sized in time, not by the per-K table of the batch experiment: blocks worth `ride_scale` times the
+    // layer's own duration (the latency budget of a query is spent on purpose, src/TaskManager.cu:586 does the same
+    // with its headroom test).  It is kept when, inside a graph, the fused layer costs less extra time than the
+    // same blocks cost time-sliced (the rule of src/TaskManager.cu:631-645 with graph prices).
     const size_t n = lc_task->kernels.size();
     std::vector<int> ride(n, 0);  // best-effort blocks riding in layer idx (0 = plain launch)
     for (size_t idx = 0; idx < n; ++idx) {
@@ -429,16 +487,10 @@ FusedColocationResult TaskManager::runFusedColocation(double seconds, double qps
         if (k->mixable == 0) continue;
         r.mixable_layers += 1;
         TzLayer* layer = static_cast<TzLayer*>(k);
-        const int nb = std::min(static_cast<int>(layer->tiles() * blockRatio(pair, layer->K_pad)), be_blocks);
-        if (nb <= 0) continue;
-        for (int i = 0; i < 2; ++i) {
-            k->execute(stream);
-            run_fused(layer, bek, 0, nb, stream);
-        }
-        const float solo = timed_ms([&] { k->execute(stream); }, 5);
-        const float fused = timed_ms([&] { run_fused(layer, bek, 0, nb, stream); }, 5);
-        // the rule of src/TaskManager.cu:631-645, with the measured fixed cost of a small solo launch
-        if (fused <= solo + be_fixed_ms + (be_full_ms - be_fixed_ms) * nb / be_blocks) {
+        const float plain = graph_ms([&] { k->execute(stream); });
+        const int nb = std::max(1, std::min(be_blocks, static_cast<int>(ride_scale * plain / std::max(block_price_ms, 1e-9f))));
+        const float fused = graph_ms([&] { run_fused(layer, bek, 0, nb, stream); });
+        if (fused - plain <= 0.9f * nb * block_price_ms) {
             ride[idx] = nb;
             r.fused_layers += 1;
             r.blocks_per_fused_query += nb;
@@ -482,18 +534,11 @@ FusedColocationResult TaskManager::runFusedColocation(double seconds, double qps
         t += -std::log(1.0 - static_cast<double>(tk_unit_draw(seed, i))) / qps * 1e3;
         arrivals.push_back(t);
     }
-    // idle-time chunk of the best-effort kernel: about be_chunk_ms of device time
-    const int chunk_blocks = std::max(1, std::min(be_blocks, static_cast<int>(be_blocks * be_chunk_ms / std::max(be_full_ms, 1e-6f))));
     int idle_cursor = 0;
     auto idle_chunk = [&]() -> int {
         if (idle_cursor >= be_blocks) idle_cursor = 0;
         const int s0 = idle_cursor, e0 = std::min(idle_cursor + chunk_blocks, be_blocks);
-        const int keep_s = bek->gptbParams.ptb_start_block_pos, keep_e = bek->gptbParams.ptb_end_block_pos;
-        bek->gptbParams.ptb_start_block_pos = s0;
-        bek->gptbParams.ptb_end_block_pos = e0;
-        bek->execute(stream);
-        bek->gptbParams.ptb_start_block_pos = keep_s;
-        bek->gptbParams.ptb_end_block_pos = keep_e;
+        launch_blocks(s0, e0);
         idle_cursor = e0;
         return e0 - s0;
     };

@@ -18,6 +18,9 @@ void mixcudnnConvolutionForward(TzLayer* layer, GPTBKernel* gptb_cd_kernel, int 
                                 stream_t stream);
 void mixcublasSgemm(TzLayer* layer, GPTBKernel* gptb_cd_kernel, int cd_start_blk, int cd_end_blk, stream_t stream);
 
+// how many cached fused kernels launch through a generated module instead of the library's kernel
+extern int generatedLaunchers;
+
 // forget the cached fused kernels (call before destroying the tasks or the best-effort kernels they were built from)
 void releaseFusedKernels();
 
@@ -90,6 +93,7 @@ public:
     float qos_budget_ms = 50.0f;  // src/TaskManager.cu:571
     float qos_guard_ms = 4.0f;    // src/TaskManager.cu:586
     int profile_passes = 10, schedule_passes = 5, warmup_passes = 5;
+    float ride_scale = 1.0f;    // fused co-location: a layer carries best-effort blocks worth this many layer times
     double be_chunk_ms = 0.15;  // best-effort work enqueued at once while idle (bounds the extra LC wait)
 
 private:

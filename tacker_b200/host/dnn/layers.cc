@@ -76,6 +76,7 @@ void TzLayer::buildGemm(int id) {
     ori->M_GLOBAL = M_pad;
     ori->ori_blks = (M_pad / 64) * (N_pad / 64);
     ori->launchGridDim = dim3h(static_cast<unsigned>(ori->ori_blks), 1, 1);
+    tiles_ = ori->ori_blks;
     const unsigned sms = static_cast<unsigned>(backend().smCount());
     gptb.reset(new GPTBKernel(id, "tzgemm", "gptb_tzgemm", ori.get(), dim3h(sms, 1, 1), dim3h(192, 1, 1), 0, ori->ori_blks));
     // a layer with fewer 128 x 256 super-tiles than half the SMs and a long K (the batch-1 dense layers) runs
@@ -117,6 +118,33 @@ void ConvKernel::prepare(stream_t stream) {
     TK_HOST_CHECK(backend().im2colNhwcHalf(input, H, W, Cin, ksize, ksize, pad, stride, A, M_pad, K_pad, stream));
 }
 
+ConvImplicitKernel::ConvImplicitKernel(int id, const std::string& name, DnnArena& arena, void* x_bordered, int H, int W,
+                                       int Cin, int Cout, int act, uint64_t seed, const float* bias, void* y_bordered)
+    : H(H), W(W), Cin(Cin), Cout(Cout) {
+    Id = id;
+    kernelName = name;
+    mixable = 2;
+    implicit = true;
+    M = H * W;
+    N = Cout;
+    K = 9 * Cin;
+    N_pad = N;
+    K_pad = K;
+    A = x_bordered;
+    // He initialisation as in ConvKernel: same seed, same layout [N][K], k = (3 i + j) Cin + c
+    B = arena.weightsHalf(static_cast<size_t>(N_pad) * K_pad, seed, std::sqrt(6.0f / static_cast<float>(K)));
+    C = nullptr;
+    ori_conv.reset(new OriTZCONVKernel(id, x_bordered, B, y_bordered, bias, H, W, Cin, Cout, act));
+    M_pad = ori_conv->M_GLOBAL;
+    tiles_ = ori_conv->ori_blks;
+    const unsigned sms = static_cast<unsigned>(backend().smCount());
+    gptb.reset(new GPTBKernel(id, "tzconv", "gptb_tzconv", ori_conv.get(), dim3h(sms, 1, 1), dim3h(192, 1, 1), 0, tiles_));
+}
+
+std::vector<int> ConvImplicitKernel::getArgs() {
+    return std::vector<int>{1, Cin, H, W, Cout, Cin, 3, 3, 1, 1, 1, 1, 1, 1};
+}
+
 GemmKernel::GemmKernel(int id, const std::string& name, DnnArena& arena, const float* input, int rows, int in_features,
                        int out_features, uint64_t seed)
     : input(input) {
@@ -136,7 +164,8 @@ GemmKernel::GemmKernel(int id, const std::string& name, DnnArena& arena, const f
 }
 
 void GemmKernel::prepare(stream_t stream) {
-    TK_HOST_CHECK(backend().rowsToHalf(input, M, K, K, A, M_pad, K_pad, stream));
+    if (bordered) TK_HOST_CHECK(backend().unborderHalf(bordered, bH, bW, bC, A, stream));  // rows 1.. of A stay zero
+    else TK_HOST_CHECK(backend().rowsToHalf(input, M, K, K, A, M_pad, K_pad, stream));
 }
 
 void OpKernel::executeImpl(stream_t s) {
@@ -165,6 +194,12 @@ void OpKernel::executeImpl(stream_t s) {
             break;
         case BatchedGemm:  // out[batch i3] = f0 * ha [M i0][K i2] * hb [N i1][K i2]^T
             TK_HOST_CHECK(be.tzgemmBatched(ha, hb, out, i0, i1, i2, i3, f0, s));
+            break;
+        case BiasActHalfBordered:  // a = x [H i0 * W i1][ld i3], b = bias, hout = bordered fp16 [H+2][W+2][C i2], act i4
+            TK_HOST_CHECK(be.biasActHalfBordered(a, i3, b, hout, i0, i1, i2, i4, s));
+            break;
+        case MaxPoolHalfBordered:  // ha = bordered fp16 [H i0 + 2][W i1 + 2][C i2] -> hout bordered [H/2 + 2][W/2 + 2][C]
+            TK_HOST_CHECK(be.maxpoolHalfBordered(ha, i0, i1, i2, hout, s));
             break;
         case RowsToHalf:  // a [rows i0][cols i1] -> hout (same shape, fp16)
             TK_HOST_CHECK(be.rowsToHalf(a, i0, i1, i1, hout, i0, i1, s));

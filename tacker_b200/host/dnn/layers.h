@@ -33,7 +33,10 @@ public:
     void buildGemm(int id);
     virtual void prepare(stream_t stream) = 0;  // fill the fp16 A operand from the layer input
     GPTBKernel* gemm() { return gptb.get(); }
-    int tiles() const { return ori->ori_blks; }
+    int tiles() const { return tiles_; }
+    // key prefix of the fused kernels this layer's tensor role belongs to: "tzgemm_" or "tzconv_"
+    const char* fusedPrefix() const { return implicit ? "tzconv_" : "tzgemm_"; }
+    bool implicit = false;
     int M = 0, N = 0, K = 0, M_pad = 0, N_pad = 0, K_pad = 0;
     void* A = nullptr;   // fp16 [M_pad][K_pad]
     void* B = nullptr;   // fp16 [N_pad][K_pad] weights
@@ -52,7 +55,9 @@ protected:
         }
     }
     bool skinny = false;
+    int tiles_ = 0;
     std::unique_ptr<OriTZGEMMKernel> ori;
+    std::unique_ptr<OriTZCONVKernel> ori_conv;
     std::unique_ptr<GPTBKernel> gptb, gptb_acc;
 };
 
@@ -68,6 +73,18 @@ public:
     int H, W, Cin, Cout, ksize, pad, stride, OH, OW;
 };
 
+// 3 x 3 convolution, stride 1, padding 1, as one implicit-GEMM kernel with bias and activation in its epilogue:
+// zero-bordered NHWC fp16 image in, zero-bordered NHWC fp16 image out, no operand preparation (same mixable /
+// getArgs contract as ConvKernel)
+class ConvImplicitKernel : public TzLayer {
+public:
+    ConvImplicitKernel(int id, const std::string& name, DnnArena& arena, void* x_bordered, int H, int W, int Cin,
+                       int Cout, int act, uint64_t seed, const float* bias, void* y_bordered);
+    std::vector<int> getArgs() override;
+    void prepare(stream_t) override {}
+    int H, W, Cin, Cout;
+};
+
 // dense layer y = x W^T on `rows` rows (mixable = 1; getArgs = m, n, k)
 class GemmKernel : public TzLayer {
 public:
@@ -76,12 +93,16 @@ public:
     std::vector<int> getArgs() override { return std::vector<int>{M, N, K}; }
     void prepare(stream_t stream) override;
     const float* input;
+    // alternative input: a bordered fp16 image [(bH + 2)][(bW + 2)][bC] whose interior, flattened, is the single row
+    const void* bordered = nullptr;
+    int bH = 0, bW = 0, bC = 0;
 };
 
 // everything that is not a GEMM (mixable = 0): one call into the library
 class OpKernel : public Kernel {
 public:
-    enum Op { BiasAct, MaxPool, Add, SoftmaxRows, LayerNorm, SplitHeads, MergeHeads, BatchedGemm, RowsToHalf };
+    enum Op { BiasAct, MaxPool, Add, SoftmaxRows, LayerNorm, SplitHeads, MergeHeads, BatchedGemm, RowsToHalf,
+              BiasActHalfBordered, MaxPoolHalfBordered };
     OpKernel(int id, const std::string& name, Op op) : op(op) {
         Id = id;
         kernelName = name;

@@ -11,6 +11,15 @@ void DnnTask::initExecution() {
         backend().upload(input, hostInput.data(), hostInput.size() * sizeof(float), execStream);
 }
 
+std::vector<float> DnnTask::downloadResult(stream_t stream) {
+    std::vector<float> h(resultCount);
+    if (result && resultCount) {
+        backend().download(h.data(), result, resultCount * sizeof(float), stream);
+        backend().streamSync(stream);
+    }
+    return h;
+}
+
 size_t DnnTask::numMixable() const {
     size_t n = 0;
     for (auto* k : kernels) n += (k->mixable != 0);
@@ -51,11 +60,11 @@ float* DnnTask::conv(const float* x, int H, int W, int Cin, int Cout, int k, int
     return y;
 }
 
-float* DnnTask::dense(const float* x, int rows, int in, int out, int act) {
+float* DnnTask::dense(const float* x, int rows, int in, int out, int act, float* y) {
     const int id3 = nextId++;
     auto* g = new GemmKernel(id3, "Dot_" + std::to_string(id3), arena, x, rows, in, out, 2000 + id3);
     keep(g);
-    float* y = arena.act(static_cast<size_t>(rows) * out);
+    if (!y) y = arena.act(static_cast<size_t>(rows) * out);
     float* bias = arena.weightsF32(out, 6000 + nextId, -0.05f, 0.05f);
     const int id4 = nextId++;
     auto* b = new OpKernel(id4, "BiasAct_" + std::to_string(id4), OpKernel::BiasAct);
@@ -81,6 +90,76 @@ float* DnnTask::pool(const float* x, int H, int W, int C) {
     p->i1 = W;
     p->i2 = C;
     keep(p);
+    return y;
+}
+
+void* DnnTask::borderedImage(int H, int W, int C) {
+    return arena.half(static_cast<size_t>(H + 2) * (W + 2) * C);  // zeroed: the border stays zero for good
+}
+
+void* DnnTask::convToBordered(const float* x, int H, int W, int Cin, int Cout, int act) {
+    const int id1 = nextId++;
+    auto* c = new ConvKernel(id1, "Convolution_" + std::to_string(id1), arena, x, H, W, Cin, Cout, 3, 1, 1, 1000 + id1);
+    keep(c);
+    void* y = borderedImage(H, W, Cout);
+    float* bias = arena.weightsF32(Cout, 5000 + nextId, -0.05f, 0.05f);
+    const int id2 = nextId++;
+    auto* b = new OpKernel(id2, "BiasAct_" + std::to_string(id2), OpKernel::BiasActHalfBordered);
+    b->a = c->C;
+    b->b = bias;
+    b->hout = y;
+    b->i0 = H;
+    b->i1 = W;
+    b->i2 = Cout;
+    b->i3 = c->N_pad;
+    b->i4 = act;
+    keep(b);
+    return y;
+}
+
+void* DnnTask::convBordered(void* x, int H, int W, int Cin, int Cout, int act) {
+    // numbered like conv(): one id for the convolution, one for the bias + activation node it has absorbed, so
+    // that the seeds of weights and biases do not depend on which form a layer takes
+    const int id1 = nextId++;
+    void* y = borderedImage(H, W, Cout);
+    float* bias = arena.weightsF32(Cout, 5000 + nextId, -0.05f, 0.05f);
+    nextId++;
+    keep(new ConvImplicitKernel(id1, "Convolution_" + std::to_string(id1), arena, x, H, W, Cin, Cout, act, 1000 + id1, bias, y));
+    return y;
+}
+
+void* DnnTask::poolBordered(void* x, int H, int W, int C) {
+    void* y = borderedImage(H / 2, W / 2, C);
+    const int id5 = nextId++;
+    auto* p = new OpKernel(id5, "MaxPool_" + std::to_string(id5), OpKernel::MaxPoolHalfBordered);
+    p->ha = x;
+    p->hout = y;
+    p->i0 = H;
+    p->i1 = W;
+    p->i2 = C;
+    keep(p);
+    return y;
+}
+
+float* DnnTask::denseFromBordered(void* x, int H, int W, int C, int out, int act) {
+    const int id3 = nextId++;
+    auto* g = new GemmKernel(id3, "Dot_" + std::to_string(id3), arena, nullptr, 1, H * W * C, out, 2000 + id3);
+    g->bordered = x;
+    g->bH = H, g->bW = W, g->bC = C;
+    keep(g);
+    float* y = arena.act(static_cast<size_t>(out));
+    float* bias = arena.weightsF32(out, 6000 + nextId, -0.05f, 0.05f);
+    const int id4 = nextId++;
+    auto* b = new OpKernel(id4, "BiasAct_" + std::to_string(id4), OpKernel::BiasAct);
+    b->a = g->C;
+    b->b = bias;
+    b->out = y;
+    b->i0 = 1;
+    b->i1 = out;
+    b->i2 = g->N_pad;
+    b->i3 = out;
+    b->i4 = act;
+    keep(b);
     return y;
 }
 
@@ -138,23 +217,29 @@ VGG16::VGG16(int numClasses) : DnnTask(0, "vgg16") {
     hostInput.resize(static_cast<size_t>(H) * W * C);
     normal_input(hostInput, 42);
     input = arena.act(hostInput.size());
-    const float* x = input;
+    // The first convolution (3 input channels) goes through im2col + tzgemm; from there on the activations are
+    // zero-bordered NHWC fp16 images and every convolution is one implicit-GEMM kernel with bias and ReLU in its
+    // epilogue.  Layer numbering (and with it every seed) is that of the explicit form.
     const int cfg[] = {64, 64, -1, 128, 128, -1, 256, 256, 256, -1, 512, 512, 512, -1, 512, 512, 512, -1};
+    void* img = nullptr;
     for (int c : cfg) {
         if (c < 0) {
-            x = pool(x, H, W, C);
+            img = poolBordered(img, H, W, C);
             H /= 2;
             W /= 2;
         } else {
-            int oh, ow;
-            x = conv(x, H, W, C, c, 3, 1, 1, 1, &oh, &ow);
+            img = img ? convBordered(img, H, W, C, c, 1) : convToBordered(input, H, W, C, c, 1);
             C = c;
         }
     }
-    x = dense(x, 1, H * W * C, 4096, 1);  // 7*7*512 = 25088
+    const float* x = denseFromBordered(img, H, W, C, 4096, 1);  // 7*7*512 = 25088
     x = dense(x, 1, 4096, 4096, 1);
-    x = dense(x, 1, 4096, numClasses, 0);
-    float* probs = arena.act(numClasses);
+    // scores and probabilities share one buffer so that both can be read back in one piece
+    float* scores = arena.act(2 * static_cast<size_t>(numClasses));
+    x = dense(x, 1, 4096, numClasses, 0, scores);
+    float* probs = scores + numClasses;
+    result = scores;
+    resultCount = 2 * static_cast<size_t>(numClasses);
     const int id9 = nextId++;
     auto* sm = new OpKernel(id9, "Softmax", OpKernel::SoftmaxRows);
     sm->a = x;

@@ -15,6 +15,11 @@ public:
     DnnTask(int id, const std::string& name) : Task(id, name) {}
     ~DnnTask() override;
     void initExecution() override;  // upload the input of one query
+    // the task's result on the device after a pass: `resultCount` floats (VGG16 / ResNet-50: the class scores
+    // before the softmax, then the probabilities; BERT: the last hidden state)
+    const float* result = nullptr;
+    size_t resultCount = 0;
+    std::vector<float> downloadResult(stream_t stream);
     size_t numMixable() const;
     double gemmFlops() const;       // 2*M*N*K summed over the tzgemm-backed layers (unpadded shapes)
     DnnArena arena;
@@ -32,8 +37,16 @@ protected:
     // helpers used by the builders; each returns the output activation
     float* conv(const float* x, int H, int W, int Cin, int Cout, int k, int pad, int stride, int act, int* OH,
                 int* OW);
-    float* dense(const float* x, int rows, int in, int out, int act);
+    float* dense(const float* x, int rows, int in, int out, int act, float* y = nullptr);  // y: where the output goes
     float* pool(const float* x, int H, int W, int C);
+    // the bordered fp16 activation path (3 x 3 / stride 1 / padding 1 convolutions as implicit GEMMs):
+    void* borderedImage(int H, int W, int C);  // zeroed [(H + 2)][(W + 2)][C] fp16
+    // first layer (few input channels): explicit im2col + tzgemm, then bias + activation into a bordered image
+    void* convToBordered(const float* x, int H, int W, int Cin, int Cout, int act);
+    void* convBordered(void* x, int H, int W, int Cin, int Cout, int act);  // implicit GEMM, one kernel
+    void* poolBordered(void* x, int H, int W, int C);
+    // dense layer on the flattened interior of a bordered image (one row)
+    float* denseFromBordered(void* x, int H, int W, int C, int out, int act);
     float* addTo(const float* a, const float* b, int rows, int cols, int act);
     float* layernorm(const float* x, int rows, int cols);
 };

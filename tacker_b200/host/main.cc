@@ -1,7 +1,8 @@
 // aker -- command line of the runtime (reference: src/main.cu:246-336).
 //   aker -s <aker|tacker> -m <vgg16|resnet50|bert> [-d device] [-c config_dir]
 //        [--colocate seconds] [--colocate-fused seconds] [--qps rate] [--qos factor] [--be model] [--be-chunk-ms ms]
-//        [--one-cd] [--be-kernel name] [--be-kernel2 name]
+//        [--one-cd] [--be-kernel name] [--be-kernel2 name] [--dump-output file]
+//        [--mix-module name=path.so]... [--module-dir dir]
 // Without --colocate it runs the reference's experiment (both modes unless -s picks one; --one-cd: its variant
 // with one best-effort kernel); with --colocate, the request-driven co-location of `-m` (latency-critical) with the
 // model `--be` (best-effort) on this GPU; with --colocate-fused, the co-location with the benchmark kernel of the
@@ -12,6 +13,7 @@
 #include <iostream>
 #include <memory>
 #include <string>
+#include <vector>
 
 #include "Backend.h"
 #include "Creator.h"
@@ -31,10 +33,12 @@ static void usage(const char* argv0) {
 }
 
 int main(int argc, char* argv[]) {
-    std::string system_name, model, config_dir = "config", be_model = "bert", be_kernel_a, be_kernel_b;
+    std::string system_name, model, config_dir = "config", be_model = "bert", be_kernel_a, be_kernel_b, dump_output;
     int device_no = 0;
-    double colocate = 0.0, colocate_fused = 0.0, qps = 200.0, qos = 1.5, be_chunk = -1.0;
+    double colocate = 0.0, colocate_fused = 0.0, qps = 200.0, qos = 1.5, be_chunk = -1.0, ride_scale = -1.0;
     bool one_cd = false;
+    std::vector<std::string> mix_modules;
+    std::string module_dir;
     for (int i = 1; i < argc; ++i) {
         const std::string a = argv[i];
         auto val = [&](const char* what) -> std::string {
@@ -51,12 +55,16 @@ int main(int argc, char* argv[]) {
         else if (a == "--colocate") colocate = std::atof(val("--colocate").c_str());
         else if (a == "--colocate-fused") colocate_fused = std::atof(val("--colocate-fused").c_str());
         else if (a == "--one-cd") one_cd = true;
+        else if (a == "--mix-module") mix_modules.push_back(val("--mix-module"));  // <name>=<path to .so>
+        else if (a == "--module-dir") module_dir = val("--module-dir");
+        else if (a == "--dump-output") dump_output = val("--dump-output");  // raw binary32 result of one LC pass
         else if (a == "--be-kernel") be_kernel_a = val("--be-kernel");    // overrides "throughput_test"."a"
         else if (a == "--be-kernel2") be_kernel_b = val("--be-kernel2");  // overrides "throughput_test"."b"
         else if (a == "--qps") qps = std::atof(val("--qps").c_str());
         else if (a == "--qos") qos = std::atof(val("--qos").c_str());
         else if (a == "--be") be_model = val("--be");
         else if (a == "--be-chunk-ms") be_chunk = std::atof(val("--be-chunk-ms").c_str());
+        else if (a == "--ride-scale") ride_scale = std::atof(val("--ride-scale").c_str());
         else {
             usage(argv[0]);
             return 0;
@@ -73,6 +81,27 @@ int main(int argc, char* argv[]) {
         setBackend(be.get());
         read_json(config_dir + "/kinfo-" + model + ".json");
         read_common_json(config_dir + "/kinfo-common.json");
+        // Fused kernels emitted by the generator: registered under a name from the command line (the pair's key, e.g.
+        // tzgemm_mriq=/path/tzgemm_mriq_1_16.so, replaces the library's kernel of that pair) or named by the model
+        // file ("tzgemm_<cd>": {"module": "tzgemm_<cd>_1_<W>"}) and looked up in the module directory.
+        for (const std::string& spec : mix_modules) {
+            const size_t eq = spec.find('=');
+            if (eq == std::string::npos || !moduleCenter.registerModule(spec.substr(0, eq), spec.substr(eq + 1)))
+                throw std::runtime_error("cannot load the module " + spec);
+        }
+        for (const char* pair : {"tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq", "tzgemm_mrif"}) {
+            const std::string module = sget_kernel_info(pair, "module");
+            if (module.empty() || moduleCenter.hasModule(module)) continue;
+            std::string dir = module_dir;
+            if (dir.empty()) {
+                dir = argv[0];
+                const size_t slash = dir.find_last_of('/');
+                dir = (slash == std::string::npos ? std::string(".") : dir.substr(0, slash)) + "/../fusion/mix_kernel";
+            }
+            if (!moduleCenter.registerModule(module, dir + "/" + module + ".so"))
+                logger.WARNING("model file names the module {" + module + "}, which is not in " + dir +
+                               " (python -m tacker_b200.fusion.gen_run builds it); the library kernel is used");
+        }
         be->setDevice(device_no);  // no device reset: the GPU may be shared (the reference calls cudaDeviceReset)
         std::cout << "SM count: " << be->smCount() << std::endl;
         stream_t streams[2] = {be->streamCreate(), be->streamCreate()};
@@ -83,11 +112,24 @@ int main(int argc, char* argv[]) {
             lc_task->enqueue(streams[0]);
             be->streamSync(streams[0]);
         }
+        if (!dump_output.empty()) {
+            auto* dnn = dynamic_cast<DnnTask*>(lc_task.get());
+            lc_task->execStream = streams[0];
+            lc_task->initExecution();
+            lc_task->enqueue(streams[0]);
+            const std::vector<float> out = dnn ? dnn->downloadResult(streams[0]) : std::vector<float>();
+            FILE* f = std::fopen(dump_output.c_str(), "wb");
+            if (!f || std::fwrite(out.data(), sizeof(float), out.size(), f) != out.size())
+                throw std::runtime_error("cannot write " + dump_output);
+            std::fclose(f);
+            std::printf("[Result] wrote %zu floats of the %s result to %s\n", out.size(), model.c_str(), dump_output.c_str());
+        }
         const std::string a = be_kernel_a.empty() ? sget_kernel_info("throughput_test", "a") : be_kernel_a;
         const std::string b = be_kernel_b.empty() ? sget_kernel_info("throughput_test", "b") : be_kernel_b;
         std::printf("[Result] cd1: %s, cd2: %s, dnn: %s\n", a.c_str(), b.c_str(), model.c_str());
         TaskManager taskManager(lc_task.get(), a, b);
         if (be_chunk >= 0.0) taskManager.be_chunk_ms = be_chunk;
+        if (ride_scale > 0.0) taskManager.ride_scale = static_cast<float>(ride_scale);
         if (colocate > 0.0) {
             std::unique_ptr<Task> be_task(createTask(be_model));
             const int per_pass = be_model == "bert" ? static_cast<Bert*>(be_task.get())->batch : 1;
@@ -124,6 +166,8 @@ int main(int argc, char* argv[]) {
             if (system_name == "aker" || system_name == "both") taskManager.executeAllTasks(ExecutionMode::Aker, streams[0]);
             if (system_name == "tacker" || system_name == "both") taskManager.executeAllTasks(ExecutionMode::Tacker, streams[1]);
         }
+        if (generatedLaunchers > 0)
+            std::printf("[Result] fused kernels launched through generated modules: %d\n", generatedLaunchers);
         const unsigned status = be->deviceStatus();
         if (status != 0) logger.WARNING("device status word: " + std::to_string(status));
         recorder.text();

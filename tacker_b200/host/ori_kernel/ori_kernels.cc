@@ -152,3 +152,53 @@ void OriMRIQKernel::loadKernel() {
     kernelFunc = reinterpret_cast<void*>(backend().lookup(funcKey));
     if (!kernelFunc) logger.ERROR("load kernel {" + funcKey + "} failed!");
 }
+
+// ---------------------------------------------------------------- mri-fhd ----
+OriMRIFKernel::OriMRIFKernel(int id, MRIFProblem p) : prob(p) {
+    Id = id;
+    kernelName = "mrif";
+    funcKey = "ori_mrif";
+    initParams();
+    loadKernel();
+}
+OriMRIFKernel::~OriMRIFKernel() {
+    for (auto& ptr : cudaFreeList) backend().deviceFree(ptr);
+}
+void OriMRIFKernel::initParams() {
+    const size_t nX = static_cast<size_t>(prob.numX);
+    if (initialized) {  // the outputs accumulate (+=): a new run starts from zero
+        backend().fillZero(outR, nX * sizeof(float), initStream);
+        backend().fillZero(outI, nX * sizeof(float), initStream);
+        return;
+    }
+    numK = prob.numK;
+    float* kx = upload_uniform(numK, 701, -0.5f, 0.5f);
+    float* ky = upload_uniform(numK, 702, -0.5f, 0.5f);
+    float* kz = upload_uniform(numK, 703, -0.5f, 0.5f);
+    float* phiR = upload_uniform(numK, 704, -1.0f, 1.0f);
+    float* phiI = upload_uniform(numK, 705, -1.0f, 1.0f);
+    float* dR = upload_uniform(numK, 706, -1.0f, 1.0f);
+    float* dI = upload_uniform(numK, 707, -1.0f, 1.0f);
+    kvals = static_cast<float*>(backend().deviceAlloc(5ull * numK * sizeof(float)));
+    TK_HOST_CHECK(backend().mrifPackKvalues(kx, ky, kz, phiR, phiI, dR, dI, numK, kvals, nullptr));  // ComputeRhoPhiGPU + pack
+    backend().streamSync(nullptr);
+    for (float* p : {kx, ky, kz, phiR, phiI, dR, dI}) backend().deviceFree(p);
+    x = upload_uniform(nX, 801, -32.0f, 32.0f);
+    y = upload_uniform(nX, 802, -32.0f, 32.0f);
+    z = upload_uniform(nX, 803, -32.0f, 32.0f);
+    outR = static_cast<float*>(backend().deviceAlloc(nX * sizeof(float)));
+    outI = static_cast<float*>(backend().deviceAlloc(nX * sizeof(float)));
+    backend().fillZero(outR, nX * sizeof(float), nullptr);
+    backend().fillZero(outI, nX * sizeof(float), nullptr);
+    backend().streamSync(nullptr);
+    for (float* p : {kvals, x, y, z, outR, outI}) cudaFreeList.push_back(p);
+    launchBlockDim = dim3h(256, 1, 1);  // KERNEL_FH_THREADS_PER_BLOCK (src/header/mrif_header.h:11)
+    launchGridDim = dim3h(prob.numX / 256, 1, 1);
+    kernelParams = {&numK, &kGlobalIndex, &x, &y, &z, &outR, &outI, &kvals};
+    smem = 0;
+    initialized = true;
+}
+void OriMRIFKernel::loadKernel() {
+    kernelFunc = reinterpret_cast<void*>(backend().lookup(funcKey));
+    if (!kernelFunc) logger.ERROR("load kernel {" + funcKey + "} failed!");
+}

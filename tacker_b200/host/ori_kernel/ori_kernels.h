@@ -1,6 +1,6 @@
-// The three CUDA-core benchmark operators as host objects: allocate and seed their inputs, hold the
+// The CUDA-core benchmark operators as host objects: allocate and seed their inputs, hold the
 // argument list and the original launch geometry (reference: src/ori_kernel/stencil_kernel.cu:114-204,
-// cp_kernel.cu:150-340, mriq_kernel.cu:107-330).  Inputs are seeded synthetically (the reference reads
+// cp_kernel.cu:150-340, mriq_kernel.cu:107-330, mrif_kernel.cu:152-330).  Inputs are seeded synthetically (the reference reads
 // MRI-Q input from a file that is not distributed and seeds the others with cuRAND / rand()).
 #pragma once
 #include "../Kernel.h"
@@ -14,6 +14,9 @@ struct CPProblem {
     float spacing = 0.125f, zplane = 32.0f, box = 64.0f;
 };
 struct MRIQProblem {
+    int numK = 2048, numX = 262144;
+};
+struct MRIFProblem {
     int numK = 2048, numX = 262144;
 };
 
@@ -61,6 +64,21 @@ public:
     MRIQProblem prob;
     int numK, kGlobalIndex = 0;
     float *x = nullptr, *y = nullptr, *z = nullptr, *Qr = nullptr, *Qi = nullptr, *kvals = nullptr;
+
+protected:
+    void executeImpl(stream_t stream) override { launch(kernelParams, stream); }
+};
+
+class OriMRIFKernel : public Kernel {
+public:
+    explicit OriMRIFKernel(int id, MRIFProblem p = MRIFProblem());
+    ~OriMRIFKernel() override;
+    void initParams() override;
+    void loadKernel() override;
+    std::vector<int> getArgs() override { return std::vector<int>(); }
+    MRIFProblem prob;
+    int numK, kGlobalIndex = 0;
+    float *x = nullptr, *y = nullptr, *z = nullptr, *outR = nullptr, *outI = nullptr, *kvals = nullptr;
 
 protected:
     void executeImpl(stream_t stream) override { launch(kernelParams, stream); }

@@ -64,7 +64,16 @@ static int record(const char* key, void** params, int n, const unsigned grid[3],
     if (k == "gptb_tzgemm") {
         l.tail = {argv_<int>(params, 13), argv_<int>(params, 14), argv_<int>(params, 15)};
         cost = 0.001 * range(13) * argv_<int>(params, 5) / 1024.0 + 0.005;
-    } else if (k == "gptb_stencil" || k == "gptb_mriq" || k == "gptb_cp") {
+    } else if (k == "gptb_tzconv") {  // 12 solo arguments, then geometry and the range
+        l.tail = {argv_<int>(params, 18), argv_<int>(params, 19), argv_<int>(params, 20)};
+        cost = 0.001 * range(18) * argv_<int>(params, 5) / 1024.0 + 0.005;
+    } else if (k.rfind("tzconv_", 0) == 0) {
+        const int cd_len = n - 21;
+        l.tail = {argv_<int>(params, cd_len - 3), argv_<int>(params, cd_len - 1), argv_<int>(params, n - 3),
+                  argv_<int>(params, n - 1)};
+        const double cd = 0.00003 * range(cd_len - 3), tz = 0.001 * range(n - 3) * argv_<int>(params, cd_len + 5) / 1024.0;
+        cost = std::max(cd, tz) + 0.25 * std::min(cd, tz) + 0.005;
+    } else if (k == "gptb_stencil" || k == "gptb_mriq" || k == "gptb_cp" || k == "gptb_mrif") {
         const int s = n - 4;
         l.tail = {argv_<int>(params, s), argv_<int>(params, s + 1), argv_<int>(params, s + 2)};
         cost = 0.00003 * range(s) + 0.003;
@@ -91,6 +100,14 @@ FAKE_LAUNCHER(l_mq, "gptb_mriq")
 FAKE_LAUNCHER(l_mst, "tzgemm_stencil")
 FAKE_LAUNCHER(l_mcp, "tzgemm_cp")
 FAKE_LAUNCHER(l_mmq, "tzgemm_mriq")
+FAKE_LAUNCHER(l_tc, "gptb_tzconv")
+FAKE_LAUNCHER(l_cst, "tzconv_stencil")
+FAKE_LAUNCHER(l_ccp, "tzconv_cp")
+FAKE_LAUNCHER(l_cmq, "tzconv_mriq")
+FAKE_LAUNCHER(l_cmf, "tzconv_mrif")
+FAKE_LAUNCHER(l_mf, "gptb_mrif")
+FAKE_LAUNCHER(l_mmf, "tzgemm_mrif")
+FAKE_LAUNCHER(l_omf, "ori_mrif")
 FAKE_LAUNCHER(l_ost, "ori_stencil")
 FAKE_LAUNCHER(l_ocp, "ori_cp")
 FAKE_LAUNCHER(l_omq, "ori_mriq")
@@ -100,7 +117,8 @@ public:
     std::map<std::string, tk_launch_fn> table = {
         {"gptb_tzgemm", l_tz}, {"gptb_tzgemm_acc", l_tz}, {"gptb_stencil", l_st}, {"gptb_cp", l_cp},       {"gptb_mriq", l_mq},
         {"tzgemm_stencil", l_mst}, {"tzgemm_cp", l_mcp}, {"tzgemm_mriq", l_mmq}, {"ori_stencil", l_ost},
-        {"ori_cp", l_ocp},     {"ori_mriq", l_omq}};
+        {"ori_cp", l_ocp},     {"ori_mriq", l_omq},    {"gptb_mrif", l_mf},   {"tzgemm_mrif", l_mmf}, {"ori_mrif", l_omf},
+        {"gptb_tzconv", l_tc}, {"tzconv_stencil", l_cst}, {"tzconv_cp", l_ccp}, {"tzconv_mriq", l_cmq}, {"tzconv_mrif", l_cmf}};
     int ops = 0;
     const char* name() const override { return "recording double"; }
     void setDevice(int) override {}
@@ -148,8 +166,13 @@ public:
     }
     int cpPackAtoms(const float*, int, float, float*, stream_t) override { return op(); }
     int mriqPackKvalues(const float*, const float*, const float*, const float*, const float*, int, float*, stream_t) override { return op(); }
+    int mrifPackKvalues(const float*, const float*, const float*, const float*, const float*, const float*, const float*, int,
+                        float*, stream_t) override { return op(); }
     int im2colNhwcHalf(const float*, int, int, int, int, int, int, int, void*, int, int, stream_t) override { return op(); }
     int rowsToHalf(const float*, int, int, int, void*, int, int, stream_t) override { return op(); }
+    int biasActHalfBordered(const float*, int, const float*, void*, int, int, int, int, stream_t) override { return op(); }
+    int maxpoolHalfBordered(const void*, int, int, int, void*, stream_t) override { return op(); }
+    int unborderHalf(const void*, int, int, int, void*, stream_t) override { return op(); }
     int biasAct(const float*, int, const float*, float*, int, int, int, int, stream_t) override { return op(); }
     int maxpool2x2(const float*, int, int, int, float*, stream_t) override { return op(); }
     int add(const float*, const float*, float*, long long, stream_t) override { return op(); }
@@ -248,6 +271,9 @@ int main(int argc, char** argv) {
         CHECK(g_launches[0].tail == (std::vector<int>{10, 20, 30, 40}));
         CHECK(createMixKernel("tzgemm_cp")->kernelParams.size() == 29);
         CHECK(createMixKernel("tzgemm_mriq")->kernelParams.size() == 33);
+        GPTBKernel* mf = createKernel("mrif");
+        CHECK(mf->funcKey == "gptb_mrif" && mf->kernelParams.size() == 8 + 6 && mf->gptbParams.ptb_end_block_pos == 1024);
+        CHECK(createMixKernel("tzgemm_mrif")->kernelParams.size() == 33);
         OriTZGEMMKernel ori(0, 300, 200, 130);
         CHECK(ori.M_GLOBAL == 256 && ori.N_GLOBAL == 128 && ori.K_GLOBAL == 128 && ori.ori_blks == 8);
         CHECK(throws([&] { ori.execute(nullptr); }));   // "should not execute ori tzgemm!"
@@ -261,10 +287,14 @@ int main(int argc, char** argv) {
         int convs = 0;
         for (auto* k : vgg.kernels) convs += (k->mixable == 2);
         CHECK(convs == 13);
-        auto* c2 = static_cast<ConvKernel*>(vgg.kernels[2]);  // conv1_2
+        auto* c1 = static_cast<TzLayer*>(vgg.kernels[0]);  // conv1_1: 3 input channels, explicit im2col + tzgemm
+        CHECK(!c1->implicit && std::string(c1->fusedPrefix()) == "tzgemm_" && c1->K_pad == 64);
+        auto* c2 = static_cast<TzLayer*>(vgg.kernels[2]);  // conv1_2: implicit GEMM over the bordered 224 x 226 grid
         std::vector<int> args = c2->getArgs();
         CHECK(args.size() == 14 && get_mnk_from_cudnn_args(args) == (std::vector<int>{50176, 64, 576}));
-        CHECK(c2->M_pad == 50176 && c2->N_pad == 64 && c2->K_pad == 576 && c2->tiles() == 784);
+        CHECK(c2->implicit && std::string(c2->fusedPrefix()) == "tzconv_" && c2->gemm()->funcKey == "gptb_tzconv");
+        CHECK(c2->M_pad == 50688 && c2->N_pad == 64 && c2->K_pad == 576 && c2->tiles() == 792);
+        CHECK(c2->gemm()->kernelParams.size() == 12 + 6);
         CHECK(std::abs(vgg.gemmFlops() / 1e9 - 30.95) < 0.3);  // ~15.5 GMAC
         Bert bert(12, 8, 128);
         CHECK(bert.numMixable() == 72 && bert.taskType == BE);
@@ -274,7 +304,7 @@ int main(int argc, char** argv) {
         g_launches.clear();
         vgg.initExecution();
         vgg.executeTask(ExecutionMode::Aker, nullptr);
-        CHECK(g_launches.size() == 16);  // the tzgemm launches; every other node went through the layer calls
+        CHECK(g_launches.size() == 16);  // the tzgemm / tzconv launches; every other node went through the layer calls
         CHECK(recorder.taskTime(vgg.taskId) > 0.0f);
         char recorder_path[] = "tk_recorder_selftest_XXXXXX";
         const int fd = mkstemp(recorder_path);
@@ -292,7 +322,7 @@ int main(int argc, char** argv) {
         ScheduleResult aker = tm.executeAllTasks(ExecutionMode::Aker, nullptr);
         int fused = 0, over = 0, last_end = -1, restarts = 0;
         for (auto& l : g_launches)
-            if (l.key == "tzgemm_stencil") {
+            if (l.key == "tzgemm_stencil" || l.key == "tzconv_stencil") {
                 ++fused;
                 over += (l.tail[1] > 1024 || l.tail[0] < 0 || l.tail[1] <= l.tail[0]);
                 restarts += (l.tail[0] == 0 && last_end > 0 && last_end != 0);
@@ -301,17 +331,17 @@ int main(int argc, char** argv) {
         CHECK(fused > 0 && over == 0);
         CHECK(aker.mixable_times == 16 && aker.mix_times > 0 && aker.mix_times <= 16);
         CHECK(aker.be_blocks > 0 && aker.stage1_be_ms > 0 && aker.lc_solo_ms > 0);
-        // Aker: blocks = tiles x ratio[K]; conv1_2 has 784 tiles and K = 576 -> ratio 1.2 * 576 / 4096
+        // Aker: blocks = tiles x ratio[K]; conv1_2 has 792 tiles and K = 576 -> ratio 1.2 * 576 / 4096
         bool saw = false;
         for (auto& l : g_launches)
-            if (l.key == "tzgemm_stencil" && l.tail[3] == 784 && l.tail[1] - l.tail[0] == static_cast<int>(784 * (1.2f * 576 / 4096.0f)))
+            if (l.key == "tzconv_stencil" && l.tail[3] == 792 && l.tail[1] - l.tail[0] == static_cast<int>(792 * (1.2f * 576 / 4096.0f)))
                 saw = true;
         CHECK(saw);
         g_launches.clear();
         ScheduleResult tacker = tm.executeAllTasks(ExecutionMode::Tacker, nullptr);
         bool all_blocks = false;
         for (auto& l : g_launches)
-            if (l.key == "tzgemm_stencil" && l.tail[0] == 0 && l.tail[1] == 1024) all_blocks = true;
+            if ((l.key == "tzgemm_stencil" || l.key == "tzconv_stencil") && l.tail[0] == 0 && l.tail[1] == 1024) all_blocks = true;
         CHECK(all_blocks && tacker.be_blocks >= aker.be_blocks);
         // stage 2: the leftover budget is filled with solo launches of both best-effort kernels, and what is
         // reported is what ran
@@ -341,10 +371,10 @@ int main(int argc, char** argv) {
             tm4.executeAllTasks(ExecutionMode::Aker, nullptr);
             int prev_end = 0, broken = 0, fused_cp = 0;
             for (auto& l : g_launches)
-                if (l.key == "tzgemm_cp") {
+                if (l.key == "tzgemm_cp" || l.key == "tzconv_cp") {
                     ++fused_cp;
                     broken += !(l.tail[0] == prev_end || (l.tail[0] == 0 && prev_end >= 256));
-                    broken += (l.tail[3] == 784);  // conv1_2 must not have been fused
+                    broken += (l.tail[3] == 792);  // conv1_2 must not have been fused
                     prev_end = l.tail[1];
                 }
             CHECK(fused_cp > 0 && broken == 0);
@@ -357,7 +387,7 @@ int main(int argc, char** argv) {
             ScheduleResult one = tm5.execute_with_one_cd_kernel(ExecutionMode::Aker, nullptr);
             int bad = 0, n1 = 0;
             for (auto& l : g_launches)
-                if (l.key == "tzgemm_stencil") {
+                if (l.key == "tzgemm_stencil" || l.key == "tzconv_stencil") {
                     ++n1;
                     const int nb = l.tail[1] - l.tail[0];
                     bad += (l.tail[0] != 0) || !(nb == 1024 || nb % 148 == 0) || nb < 148;
@@ -379,7 +409,7 @@ int main(int argc, char** argv) {
         g_launches.clear();
         ScheduleResult none = tm.executeAllTasks(ExecutionMode::Aker, nullptr);
         fused = 0;
-        for (auto& l : g_launches) fused += (l.key == "tzgemm_stencil");
+        for (auto& l : g_launches) fused += (l.key == "tzgemm_stencil" || l.key == "tzconv_stencil");
         CHECK(fused == 0 && none.mix_times == 0 && none.be_blocks == 0);
         // request-driven co-location on the double: every arrival is served, the best-effort task advances
         Bert be_task(1, 8, 128);

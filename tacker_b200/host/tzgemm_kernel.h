@@ -78,3 +78,38 @@ protected:
     void executeImpl(stream_t) override { logger.ERROR("should not execute ori tzgemm!"); }  // as the reference
     void loadKernel() override {}
 };
+
+// The implicit-GEMM convolution as a host object (no counterpart in the reference, whose convolutions are im2col +
+// tzgemm on scratch data, src/include/dnn.h:554-803): 3 x 3, stride 1, padding 1 on zero-bordered NHWC fp16 images.
+// Solo argument list of "gptb_tzconv": X, Wt, Y, M, N, K, alpha, bias, H, W, C, act.
+class OriTZCONVKernel : public Kernel {
+public:
+    OriTZCONVKernel(int id, void* X, void* Wt, void* Y, const float* bias, int H, int W, int Cin, int Cout, int act)
+        : X(X), Wt(Wt), Y(Y), bias(bias), H(H), W(W), Cin(Cin), act(act) {
+        this->Id = id;
+        this->kernelName = "tzconv";
+        M_GLOBAL = ((H * (W + 2) + 127) / 128) * 128;
+        N_GLOBAL = Cout;
+        K_GLOBAL = 9 * Cin;
+        ori_blks = (M_GLOBAL / 64) * (N_GLOBAL / 64);
+        initParams();
+    }
+    void initParams() override {
+        launchGridDim = dim3h(static_cast<unsigned>(ori_blks), 1, 1);
+        launchBlockDim = dim3h(192, 1, 1);
+        kernelParams = {&X, &Wt, &Y, &M_GLOBAL, &N_GLOBAL, &K_GLOBAL, &alpha, &bias, &H, &W, &Cin, &act};
+        smem = 0;
+    }
+    std::vector<int> getArgs() override { return std::vector<int>{M_GLOBAL, N_GLOBAL, K_GLOBAL}; }
+    void* X;
+    void* Wt;
+    void* Y;
+    const float* bias;
+    int H, W, Cin, act;
+    int M_GLOBAL, N_GLOBAL, K_GLOBAL, ori_blks;
+    float alpha = 1.0f;
+
+protected:
+    void executeImpl(stream_t) override { logger.ERROR("should not execute ori tzconv!"); }
+    void loadKernel() override {}
+};

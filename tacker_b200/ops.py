@@ -118,6 +118,26 @@ class OriTZGEMMKernel(Kernel):
         self.launchBlockDim = (192, 1, 1)
 
 
+class OriTZCONVKernel(Kernel):
+    """Implicit-GEMM 3 x 3 convolution (stride 1, padding 1) on bordered NHWC fp16 images; the launch goes through
+    GPTBKernel("tzconv", "gptb_tzconv", ...)."""
+
+    kernelName = "tzconv"
+    funcKey = "gptb_tzconv"
+
+    def __init__(self, X: int, Wt: int, Y: int, H: int, W: int, Cin: int, Cout: int, bias: int = 0, act: int = 1,
+                 alpha: float = 1.0):
+        super().__init__()
+        self.M_GLOBAL = ((H * (W + 2) + 127) // 128) * 128
+        self.N_GLOBAL, self.K_GLOBAL = Cout, 9 * Cin
+        self.ori_blks = (self.M_GLOBAL // 64) * (Cout // 64)
+        self.kernelParams = [C.c_void_p(X), C.c_void_p(Wt), C.c_void_p(Y), C.c_int(self.M_GLOBAL), C.c_int(Cout),
+                             C.c_int(9 * Cin), C.c_float(alpha), C.c_void_p(bias), C.c_int(H), C.c_int(W), C.c_int(Cin),
+                             C.c_int(act)]
+        self.launchGridDim = (self.ori_blks, 1, 1)
+        self.launchBlockDim = (192, 1, 1)
+
+
 class OriSTENCILKernel(Kernel):
     """src/ori_kernel/stencil_kernel.cu:114-204 (launch geometry :173-178)."""
 
@@ -155,6 +175,20 @@ class OriMRIQKernel(Kernel):
         super().__init__()
         self.kernelParams = [C.c_int(numK), C.c_int(0), C.c_void_p(x), C.c_void_p(y), C.c_void_p(z),
                              C.c_void_p(Qr), C.c_void_p(Qi), C.c_void_p(kvals)]
+        self.launchGridDim = (numX // 256, 1, 1)
+        self.launchBlockDim = (256, 1, 1)
+
+
+class OriMRIFKernel(Kernel):
+    """src/ori_kernel/mrif_kernel.cu:78-150; `kvals` = the packed table of mrif_pack_kvalues (5 * numK floats)."""
+
+    kernelName = "mrif"
+    funcKey = "ori_mrif"
+
+    def __init__(self, numK: int, x: int, y: int, z: int, outR: int, outI: int, kvals: int, numX: int):
+        super().__init__()
+        self.kernelParams = [C.c_int(numK), C.c_int(0), C.c_void_p(x), C.c_void_p(y), C.c_void_p(z),
+                             C.c_void_p(outR), C.c_void_p(outI), C.c_void_p(kvals)]
         self.launchGridDim = (numX // 256, 1, 1)
         self.launchBlockDim = (256, 1, 1)
 
@@ -222,6 +256,12 @@ def mriq_pack_kvalues(kx: int, ky: int, kz: int, phiR: int, phiI: int, numK: int
           "tk_mriq_pack_kvalues")
 
 
+def mrif_pack_kvalues(kx: int, ky: int, kz: int, phiR: int, phiI: int, dR: int, dI: int, numK: int, kvals: int,
+                      stream: int = 0) -> None:
+    check(lib().tk_mrif_pack_kvalues(*[C.c_void_p(p) for p in (kx, ky, kz, phiR, phiI, dR, dI)], numK,
+                                     C.c_void_p(kvals), C.c_void_p(stream)), "tk_mrif_pack_kvalues")
+
+
 def im2col_f32(data_im: int, channels: int, height: int, width: int, kh: int, kw: int, pad_h: int, pad_w: int,
                stride_h: int, stride_w: int, dil_h: int, dil_w: int, data_col: int, stream: int = 0) -> None:
     check(lib().tk_im2col_f32(C.c_void_p(data_im), channels, height, width, kh, kw, pad_h, pad_w, stride_h,
@@ -247,6 +287,12 @@ def gptb_tzgemm(A, B, Cm, m, n, k, alpha=1.1, start=0, end=None, grid=None, roun
                       ori.ori_blks if end is None else end)
 
 
+def gptb_tzconv(X, Wt, Y, H, W, Cin, Cout, bias=0, act=1, start=0, end=None, grid=None) -> GPTBKernel:
+    ori = OriTZCONVKernel(X, Wt, Y, H, W, Cin, Cout, bias, act)
+    return GPTBKernel("tzconv", "gptb_tzconv", ori, (grid or sm_count(), 1, 1), (192, 1, 1), start,
+                      ori.ori_blks if end is None else end)
+
+
 def gptb_stencil(c0, c1, A0, Anext, nx, ny, nz, start=0, end=None, grid=None, block=256) -> GPTBKernel:
     ori = OriSTENCILKernel(c0, c1, A0, Anext, nx, ny, nz)
     total = ori.launchGridDim[0] * ori.launchGridDim[1]
@@ -267,11 +313,17 @@ def gptb_mriq(numK, x, y, z, Qr, Qi, kvals, numX, start=0, end=None, grid=None, 
                       ori.launchGridDim[0] if end is None else end)
 
 
+def gptb_mrif(numK, x, y, z, outR, outI, kvals, numX, start=0, end=None, grid=None, block=256) -> GPTBKernel:
+    ori = OriMRIFKernel(numK, x, y, z, outR, outI, kvals, numX)
+    return GPTBKernel("mrif", "gptb_mrif", ori, (grid or sm_count() * 2, 1, 1), (block, 1, 1), start,
+                      ori.launchGridDim[0] if end is None else end)
+
+
 def mix(cd: GPTBKernel, tz: GPTBKernel, cd_threads=256, grid=None, cd_range=None, tz_range=None) -> MixKernel:
     """tzgemm_<cd> fused kernel as TaskManager builds it (src/TaskManager.cu:253-264)."""
     cs, ce = cd_range if cd_range is not None else (cd.ptb_start_block_pos, cd.ptb_end_block_pos)
     ts, te = tz_range if tz_range is not None else (tz.ptb_start_block_pos, tz.ptb_end_block_pos)
-    return MixKernel("tzgemm_" + cd.kernelName, cd, tz, (grid or sm_count(), 1, 1), (192 + cd_threads, 1, 1),
+    return MixKernel(tz.kernelName + "_" + cd.kernelName, cd, tz, (grid or sm_count(), 1, 1), (192 + cd_threads, 1, 1),
                      cs, ce, ts, te)
 
 
@@ -320,6 +372,19 @@ def _vp(x):
 def im2col_nhwc_f16(x, H, W, Cin, kh, kw, pad, stride, A_half, M_pad, K_pad, stream: int = 0) -> None:
     check(lib().tk_im2col_nhwc_f16(_vp(x), H, W, Cin, kh, kw, pad, stride, _vp(A_half), M_pad, K_pad, _vp(stream)),
           "tk_im2col_nhwc_f16")
+
+
+def bias_act_f16_bordered(x, ldx, bias, out_half, H, W, Cn, act, stream: int = 0) -> None:
+    check(lib().tk_bias_act_f16_bordered(_vp(x), ldx, _vp(bias), _vp(out_half), H, W, Cn, act, _vp(stream)),
+          "tk_bias_act_f16_bordered")
+
+
+def maxpool2x2_f16_bordered(x_half, H, W, Cn, out_half, stream: int = 0) -> None:
+    check(lib().tk_maxpool2x2_f16_bordered(_vp(x_half), H, W, Cn, _vp(out_half), _vp(stream)), "tk_maxpool2x2_f16_bordered")
+
+
+def unborder_f16(x_half, H, W, Cn, row_half, stream: int = 0) -> None:
+    check(lib().tk_unborder_f16(_vp(x_half), H, W, Cn, _vp(row_half), _vp(stream)), "tk_unborder_f16")
 
 
 def rows_f32_to_f16(x, rows, cols, ld_in, A_half, rows_pad, cols_pad, stream: int = 0) -> None:

@@ -61,6 +61,8 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
     kv = torch.rand(2048, 4, device="cuda") - 0.5
     xyz = [torch.rand(262144, device="cuda") * 64 - 32 for _ in range(3)]
     qr, qi = torch.zeros(262144, device="cuda"), torch.zeros(262144, device="cuda")
+    fkv = torch.rand(5 * 2048, device="cuda") - 0.5
+    fr, fi = torch.zeros(262144, device="cuda"), torch.zeros(262144, device="cuda")
     # solo launch shape (CTAs per SM, threads) and the CUDA-core thread counts tried for the fused kernel
     cds = {
         "stencil": (lambda s=0, e=None: ops.gptb_stencil(1 / 6, 1 / 36, grid0.data_ptr(), grid1.data_ptr(), 512, 512,
@@ -70,6 +72,9 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
                                                end=e, grid=sms * 2, block=512), 256, (2, 512), (448, 576, 832)),
         "mriq": (lambda s=0, e=None: ops.gptb_mriq(2048, xyz[0].data_ptr(), xyz[1].data_ptr(), xyz[2].data_ptr(),
                                                    qr.data_ptr(), qi.data_ptr(), kv.data_ptr(), 262144, start=s,
+                                                   end=e, grid=sms * 2, block=512), 1024, (2, 512), (576, 704, 832)),
+        "mrif": (lambda s=0, e=None: ops.gptb_mrif(2048, xyz[0].data_ptr(), xyz[1].data_ptr(), xyz[2].data_ptr(),
+                                                   fr.data_ptr(), fi.data_ptr(), fkv.data_ptr(), 262144, start=s,
                                                    end=e, grid=sms * 2, block=512), 1024, (2, 512), (576, 704, 832)),
     }
     out = {}

@@ -16,7 +16,7 @@ sys.path[:0] = [ROOT, os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests")]
 
 import tacker_oracle as oracle  # noqa: E402
 import tacker_ref as ref  # noqa: E402
-from helpers import coulomb_inputs, gemm_inputs, mriq_inputs, stencil_inputs  # noqa: E402
+from helpers import coulomb_inputs, gemm_inputs, mrif_inputs, mriq_inputs, stencil_inputs  # noqa: E402
 
 CASES = {
     "stencil": dict(nx=192, ny=12, nz=7, c0=1.0 / 6.0, c1=1.0 / 36.0, seed=11),
@@ -24,6 +24,7 @@ CASES = {
     "cp": dict(nx=128, ny=16, natoms=130, spacing=0.1, zplane=0.0, box=12.0, seed=13),
     "cp_cfg3spacing": dict(nx=128, ny=8, natoms=64, spacing=0.125, zplane=4.0, box=8.0, seed=14),
     "mriq": dict(numK=96, numX=512, seed=15),
+    "mrif": dict(numK=300, numX=512, seed=16),
     "tzgemm": dict(M=128, N=128, K=256, seed=16),
 }
 
@@ -77,6 +78,27 @@ def main(out_dir):
     scale = float(kv[:, 3].sum())
     report.append(f"mriq: oracle f32 vs reference max abs diff Qr {np.abs(out_r - wr).max():.3e} Qi "
                   f"{np.abs(out_i - wi).max():.3e} (sum phiMag {scale:.3f}, max |Q| {np.abs(wr).max():.3f})")
+
+    c = CASES["mrif"]
+    k, phi, d, xyz = mrif_inputs(oracle, c["numK"], c["numX"], seed=c["seed"])
+    kv = oracle.mrif_pack(k[0], k[1], k[2], phi[0], phi[1], d[0], d[1])
+    nk = c["numK"]
+    aos = np.concatenate([kv[:4 * nk].reshape(nk, 4), kv[4 * nk:].reshape(nk, 1)], axis=1)   # the reference's struct order
+    dx = [dev(xyz[i]) for i in range(3)]
+    o_r = torch.zeros(c["numX"], dtype=torch.float32, device="cuda")
+    o_i = torch.zeros(c["numX"], dtype=torch.float32, device="cuda")
+    gx = c["numX"] // 256
+    assert ref.mrif(aos, dx[0].data_ptr(), dx[1].data_ptr(), dx[2].data_ptr(), o_r.data_ptr(), o_i.data_ptr(), gx, 0, gx, 2) == 0
+    torch.cuda.synchronize()
+    out_r, out_i = o_r.cpu().numpy(), o_i.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "ref_mrif.npz"), outR=out_r, outI=out_i,
+                        **{k_: np.asarray(v) for k_, v in c.items()})
+    for mode in (0, 1):
+        wr, wi = oracle.mrif_f32(kv, xyz[0], xyz[1], xyz[2], np.zeros(c["numX"], np.float32),
+                                 np.zeros(c["numX"], np.float32), mode=mode)
+        report.append(f"mrif: oracle f32 (contraction mode {mode}) vs reference: bit mismatches outR "
+                      f"{oracle.bit_mismatches(out_r, wr)} outI {oracle.bit_mismatches(out_i, wi)} of {out_r.size}, max abs "
+                      f"diff {max(np.abs(out_r - wr).max(), np.abs(out_i - wi).max()):.3e} (max |out| {np.abs(wr).max():.3f})")
 
     c = CASES["tzgemm"]
     a_bits, a, b_bits, b = gemm_inputs(oracle, c["M"], c["N"], c["K"], seed=c["seed"])

@@ -38,3 +38,12 @@ def mriq_inputs(oracle, numK, numX, seed=0):
     phi = oracle.uniform_f32(2 * numK, 500 + seed, 0.0, 1.0).reshape(2, numK)
     xyz = oracle.uniform_f32(3 * numX, 600 + seed, -32.0, 32.0).reshape(3, numX)
     return k, phi, xyz
+
+
+def mrif_inputs(oracle, numK, numX, seed=0):
+    """k-space samples, phi and d (real / imaginary, uniform in [-1, 1)), voxel coordinates in [-32, 32)^3."""
+    k = oracle.uniform_f32(3 * numK, 700 + seed, -0.5, 0.5).reshape(3, numK)
+    phi = oracle.uniform_f32(2 * numK, 800 + seed, -1.0, 1.0).reshape(2, numK)
+    d = oracle.uniform_f32(2 * numK, 900 + seed, -1.0, 1.0).reshape(2, numK)
+    xyz = oracle.uniform_f32(3 * numX, 1000 + seed, -32.0, 32.0).reshape(3, numX)
+    return k, phi, d, xyz

@@ -52,10 +52,10 @@ def test_status_strings_and_options(tk):
         assert lib.tk_status_string(s) != b"unknown status"
     from tacker_b200 import ops
 
-    assert ops.get_option("cp_ppt") == 4
-    ops.set_option("cp_ppt", 8)
     assert ops.get_option("cp_ppt") == 8
     ops.set_option("cp_ppt", 4)
+    assert ops.get_option("cp_ppt") == 4
+    ops.set_option("cp_ppt", 8)
     assert lib.tk_set_option(b"cp_ppt", 3) == -1
     assert lib.tk_set_option(b"tzgemm_bn", 64) == -1
     assert lib.tk_set_option(b"nope", 1) == -4

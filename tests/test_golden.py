@@ -9,7 +9,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import coulomb_inputs, gemm_inputs, mriq_inputs, stencil_inputs
+from helpers import coulomb_inputs, gemm_inputs, mrif_inputs, mriq_inputs, stencil_inputs
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -56,6 +56,23 @@ def test_mriq_restatement_matches_to_sincos_rounding(oracle):
     assert np.abs(qr - g["qr"]).max() <= 4e-7 * peak and np.abs(qi - g["qi"]).max() <= 4e-7 * peak
     r64, i64 = oracle.mriq_f64(kv, xyz[0], xyz[1], xyz[2])
     assert np.abs(g["qr"] - r64).max() <= 1e-5 * peak and np.abs(g["qi"] - i64).max() <= 1e-5 * peak
+
+
+def test_mrif_restatement_matches_to_sincos_rounding(oracle):
+    """MRI-FHd: the reference's g_general_ptb_mrif (300 samples: one full 256-entry constant tile and a ragged one)
+    against the restatement with the contractions nvcc applies (mode 0); the other choice (mode 1) is further off."""
+    g = _load("mrif")
+    k, phi, d, xyz = mrif_inputs(oracle, g["numK"], g["numX"], seed=g["seed"])
+    kv = oracle.mrif_pack(k[0], k[1], k[2], phi[0], phi[1], d[0], d[1])
+    n = g["numX"]
+    err = {}
+    for mode in (0, 1):
+        o_r, o_i = oracle.mrif_f32(kv, xyz[0], xyz[1], xyz[2], np.zeros(n, np.float32), np.zeros(n, np.float32), mode=mode)
+        err[mode] = max(np.abs(o_r - g["outR"]).max(), np.abs(o_i - g["outI"]).max())
+    peak = max(np.abs(g["outR"]).max(), np.abs(g["outI"]).max())
+    assert err[0] <= 4e-7 * peak and err[0] <= err[1]
+    r64, i64 = oracle.mrif_f64(kv, xyz[0], xyz[1], xyz[2])
+    assert np.abs(g["outR"] - r64).max() <= 1e-5 * peak and np.abs(g["outI"] - i64).max() <= 1e-5 * peak
 
 
 def test_tzgemm_restatement_matches_reference_wmma(oracle):

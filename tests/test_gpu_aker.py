@@ -29,6 +29,42 @@ def test_reference_experiment_runs_both_modes(cuda, model, tmp_path):
     assert [r[0] for r in results] == ["Aker", "Tacker"]
     assert all(float(r[1]) >= 0 for r in results)
     assert "mix times:" in out.stdout and os.path.exists(tmp_path / "recorder_output.txt")
+    # the scheduler fuses: in both modes some layers carried best-effort blocks and that saved time
+    mixes = re.findall(r"execed be blks: (\d+), mix times: (\d+)/(\d+), time earned: ([\d.]+)", out.stdout)
+    assert len(mixes) == 2
+    for blks, fused, mixable, earned in mixes:
+        assert 0 <= int(fused) <= int(mixable)
+        if model == "vgg16":
+            assert int(blks) > 0 and int(fused) > 0 and float(earned) > 0.0
+    # stage 2 ran best-effort kernels in the leftover budget and reports what ran
+    stage2 = re.findall(r"\[Stage2\] (\d+) solo launches in the ([\d.]+) ms left: (\d+) blocks of \w+, (\d+) blocks of \w+, "
+                        r"([\d.]+) ms of device time", out.stdout)
+    assert len(stage2) == 2
+    for launches, window, b1, b2, ms in stage2:
+        assert int(launches) > 0 and int(b1) > 0 and int(b2) > 0 and 0 < float(ms) <= float(window) * 1.05
+
+
+def test_one_best_effort_kernel_variant(cuda, tmp_path):
+    """execute_with_one_cd_kernel (src/TaskManager.cu:717-1005): whole rounds of blocks from block 0, no stage 2."""
+    out = subprocess.run([_aker(), "-s", "aker", "-m", "vgg16", "-c", os.path.join(HOST, "config"), "--one-cd"],
+                         capture_output=True, text=True, timeout=600, cwd=tmp_path)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    m = re.search(r"execed be blks: (\d+), mix times: (\d+)/16, time earned: ([\d.]+)", out.stdout)
+    assert m and int(m.group(1)) > 0 and int(m.group(2)) > 0
+    assert re.search(r"\[Result\] Aker throughput [\d.]+ \+ [\d.]+ = [\d.]+ ms", out.stdout) and "[Stage2]" not in out.stdout
+
+
+def test_fused_colocation_beats_time_slicing_within_qos(cuda, tmp_path):
+    """Request-driven co-location with the benchmark kernel as the best-effort job: layers of the LC pass carry
+    best-effort blocks, the latency bound holds in both phases, and riding does not cost throughput."""
+    out = subprocess.run([_aker(), "-s", "aker", "-m", "vgg16", "-c", os.path.join(HOST, "config"), "--colocate-fused", "4",
+                          "--qps", "200", "--qos", "1.5"], capture_output=True, text=True, timeout=600, cwd=tmp_path)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    r = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert r["mixable_layers"] == 16 and r["fused_layers"] > 0 and r["blocks_per_fused_query"] > 0
+    assert r["timesliced"]["qos_met"] and r["fused"]["qos_met"]
+    assert r["fused"]["fused_queries"] > 0 and r["fused"]["be_blocks_in_lc"] > 0
+    assert r["fused"]["be_blocks_per_s"] >= 0.98 * r["timesliced"]["be_blocks_per_s"]
 
 
 def test_colocation_meets_qos(cuda, tmp_path):
@@ -40,6 +76,47 @@ def test_colocation_meets_qos(cuda, tmp_path):
     r = json.loads(line)
     assert r["lc_served"] > 400 and r["be_queries"] > 0 and r["be_qps"] > 0
     assert r["lc_p99_ms"] >= r["lc_p50_ms"] > 0
+    assert r["qos_met"] is True and r["lc_p99_ms"] <= r["qos_bound_ms"]
+
+
+def test_vgg16_scores_match_the_cpu_forward(cuda, oracle, tmp_path):
+    """The whole LC model, end to end: the class scores `aker` computes on its seeded input and weights against
+    a numpy forward of the same network (fp16 operands, fp32 accumulation), within 1e-2 of the largest score."""
+    import numpy as np
+
+    import vgg16_numpy
+
+    dump = tmp_path / "vgg16_result.bin"
+    out = subprocess.run([_aker(), "-s", "aker", "-m", "vgg16", "-c", os.path.join(HOST, "config"), "--dump-output",
+                          str(dump), "--colocate", "0.2"], capture_output=True, text=True, timeout=600, cwd=tmp_path)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    got = np.fromfile(dump, dtype=np.float32)
+    assert got.size == 2000
+    scores, probs = vgg16_numpy.forward(oracle)
+    scale = float(np.abs(scores).max())
+    assert scale > 0 and np.isfinite(got).all()
+    assert np.abs(got[:1000] - scores).max() <= 1e-2 * scale
+    assert int(np.argmax(got[:1000])) == int(np.argmax(scores))
+    assert np.abs(got[1000:] - probs).max() <= 1e-2 * float(probs.max())
+    assert abs(float(got[1000:].sum()) - 1.0) <= 1e-4
+
+
+def test_scheduler_launches_a_generated_module(cuda, tmp_path):
+    """Generator -> runtime: a fused kernel emitted for one thread ratio, compiled into a module and registered
+    under the pair's key replaces the library's kernel in the scheduler's fused launches
+    (reference: generated kernels become src/mix_kernel/*.cu and are picked via the model file, src/TaskManager.cu:253-264)."""
+    from tacker_b200.fusion import data, gen_run
+
+    c = [x for x in data.fuse_kernel_info("mriq") if x.r2 == 16][0]
+    so = gen_run.compile_module(gen_run.emit(c, str(tmp_path)))
+    out = subprocess.run([_aker(), "-s", "aker", "-m", "bert", "-c", os.path.join(HOST, "config"), "--be-kernel", "mriq",
+                          "--mix-module", f"tzgemm_mriq={so}"], capture_output=True, text=True, timeout=600, cwd=tmp_path)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    m = re.search(r"fused kernels launched through generated modules: (\d+)", out.stdout)
+    assert m and int(m.group(1)) > 0
+    m = re.search(r"execed be blks: (\d+), mix times: (\d+)/72", out.stdout)
+    assert m and int(m.group(1)) > 0 and int(m.group(2)) > 0
+    assert "device status word" not in out.stdout + out.stderr
 
 
 def test_bert_as_the_lc_task(cuda, tmp_path):
@@ -59,7 +136,7 @@ def test_resource_query_for_every_key(cuda):
     for key in tacker_b200.KEYS:
         info = ops.query(key)
         assert info.regs_per_thread > 0 and info.max_ctas_per_sm >= 1 and info.nparams > 0, key
-        if key.startswith("tzgemm_") or key.startswith("gptb_tzgemm"):
+        if key.startswith(("tzgemm_", "tzconv_", "gptb_tzgemm", "gptb_tzconv")):
             assert info.threads_tensor == 192 and info.tmem_columns == 512 and info.dynamic_smem > 100000
         else:
             assert info.threads_tensor == 0 and info.threads_cd_min == 32

@@ -223,3 +223,36 @@ def test_k_split_form_for_skinny_problems(cuda, oracle, shape):
     cuda.cuda.synchronize()
     assert ops.device_status() == 0
     _check(oracle, Cd.cpu().numpy(), a, b, 1.1)
+
+
+def test_bounded_wait_runs_out_and_reports(cuda, oracle):
+    """A wait that nothing satisfies ends by itself: with the test hook the producer issues no operand loads, the MMA
+    issuer's wait for them expires after the (shortened) budget, the kernel returns with its tensor memory freed, the
+    status word names the wait, and the next ordinary launch is correct."""
+    import tacker_b200
+    from tacker_b200 import ops
+
+    M, N, K = 128, 128, 128
+    a_bits, a, b_bits, b = gemm_inputs(oracle, M, N, K, seed=77)
+    A, B = half_dev(cuda, a_bits), half_dev(cuda, b_bits)
+    Cd = cuda.full((M, N), -5.0, dtype=cuda.float32, device="cuda")
+    st = cuda.cuda.current_stream().cuda_stream
+    ops.set_option("tzgemm_pair", -1)
+    ops.set_option("wait_budget_us", 200)
+    ops.set_option("test_skip_loads", 1)
+    try:
+        k = ops.gptb_tzgemm(A.data_ptr(), B.data_ptr(), Cd.data_ptr(), M, N, K, alpha=1.0, grid=1, round_dims=False)
+        k.execute(st)
+        cuda.cuda.synchronize()                      # the launch ends by itself
+        assert ops.get_option("test_skip_loads") == 0
+        assert tacker_b200.lib().tk_device_check() == -7     # TK_ERR_DEVICE_WAIT, and the word is cleared
+        assert ops.device_status() == 0
+        assert bool((Cd == -5.0).all())              # nothing was written
+    finally:
+        ops.set_option("wait_budget_us", 1000000)
+        ops.set_option("test_skip_loads", 0)
+        ops.set_option("tzgemm_pair", 0)
+    k.execute(st)                                    # the same kernel object, ordinary launch
+    cuda.cuda.synchronize()
+    assert ops.device_status() == 0
+    _check(oracle, Cd.cpu().numpy(), a, b, 1.0)
