@@ -246,7 +246,8 @@ def run_ours(args):
 
     if args.only_pairs or args.profile_pair:  # just the Coulomb and MRI-Q pairs (used for profiler captures of those kernels)
         if rank == 0:
-            print(json.dumps({"pairs": other_pairs(torch, ops, sms, gen, t_of, st, args.profile_pair, args.profile_w)}),
+            print(json.dumps({"pairs": other_pairs(torch, ops, sms, gen, t_of, st, args.profile_pair, args.profile_w,
+                                                       args.profile_blocks)}),
                   flush=True)
         rep.close()
         return
@@ -426,13 +427,27 @@ def run_ours(args):
             c = colocate.run(1, args.colocate_s, 200.0, 1.5, devices=[physical_gpu_index(local)])
             coloc = {k: c[k] for k in ("be_qps_total", "lc_p99_ms_max", "lc_solo_p99_ms_max", "qos_met_all", "seconds",
                                        "lc", "be", "qps_offered_per_gpu")}
+            # the same LC stream with the benchmark kernel as the best-effort job: blocks riding inside the LC layers'
+            # fused kernels against plain time slicing (shorter phases: three of them)
+            f = colocate.run_fused(1, min(args.colocate_s, 20.0), 200.0, 1.5, devices=[physical_gpu_index(local)])
+            coloc["fused_mode"] = {k: f[k] for k in ("be_kernel", "seconds_per_phase", "fused_layers", "mixable_layers",
+                                                     "blocks_per_fused_query", "timesliced_be_blocks_per_s",
+                                                     "fused_be_blocks_per_s", "timesliced_lc_p99_ms_max",
+                                                     "fused_lc_p99_ms_max", "qos_bound_ms_min", "qos_met_all")}
         except Exception as e:
             coloc = {"unavailable": repr(e)[:200]}
         gathered = rep.gather(coloc)
         if all(isinstance(g, dict) and "be_qps_total" in g for g in gathered):
+            fm = [g.get("fused_mode") for g in gathered]
             coloc = dict(coloc, be_qps_total=sum(g["be_qps_total"] for g in gathered),
                          lc_p99_ms_max=max(g["lc_p99_ms_max"] for g in gathered),
                          qos_met_all=all(g["qos_met_all"] for g in gathered), gpus=world)
+            if all(isinstance(m, dict) for m in fm):
+                coloc["fused_mode"] = dict(fm[0], timesliced_be_blocks_per_s=sum(m["timesliced_be_blocks_per_s"] for m in fm),
+                                           fused_be_blocks_per_s=sum(m["fused_be_blocks_per_s"] for m in fm),
+                                           fused_lc_p99_ms_max=max(m["fused_lc_p99_ms_max"] for m in fm),
+                                           timesliced_lc_p99_ms_max=max(m["timesliced_lc_p99_ms_max"] for m in fm),
+                                           qos_met_all=all(m["qos_met_all"] for m in fm))
 
     cpu = None
     if rank == 0 and world == 1 and not args.quick:
@@ -536,17 +551,20 @@ def pair_report(ops, sms, t_of, tz, make_cd, total_blocks, cd_name, w_sweep):
                      "fused_us_by_cd_threads": {str(w): round(v, 1) for w, v in bal.items()}}}
 
 
-def other_pairs(torch, ops, sms, gen, t_of, st, profile=None, profile_w=832):
+def other_pairs(torch, ops, sms, gen, t_of, st, profile=None, profile_w=832, profile_blocks=0):
     """Configs 3 and 4: GEMM + Coulomb (compute-bound CUDA-core pair), GEMM + MRI-Q (SFU-bound pair).
 
     profile = "cp" | "mriq": only find that pair's balanced quantum with solo launches, then run its fused launch
     three times with `profile_w` CUDA-core threads (the launches a profiler capture of the fused kernel wants)."""
     out = {}
-    w_sweep = (320, 576, 832)
+    w_sweep = (448, 576, 704, 832)
 
     def profile_run(tz, make_cd, total_blocks):
-        t_g, t_c = t_of([tz()], 10), t_of([make_cd()], 5)
-        nb, t_cb = balanced_quantum(t_of, make_cd, total_blocks, t_g, t_c)
+        if profile_blocks > 0:
+            nb, t_g, t_cb = profile_blocks, 0.0, 0.0
+        else:
+            t_g, t_c = t_of([tz()], 10), t_of([make_cd()], 5)
+            nb, t_cb = balanced_quantum(t_of, make_cd, total_blocks, t_g, t_c)
         k = ops.mix(make_cd(0, nb), tz(), cd_threads=profile_w, grid=sms)
         for _ in range(3):
             k.execute(st)
@@ -592,6 +610,15 @@ def other_pairs(torch, ops, sms, gen, t_of, st, profile=None, profile_w=832):
     r["mriq_gpairs_per_s"] = round(numK * numX / r["mriq_us"] / 1e3, 1)
     r["mriq_frac_of_sfu_bound"] = round(2.0 * numK * numX / (sms * 16 * 1.965e9) / (r["mriq_us"] * 1e-6), 3)
     out["config4_gemm4096x2048_mriq"] = r
+
+    # the same GEMM with MRI-FHd, the best-effort kernel of the shipped schedule (2048 samples x 262144 voxels)
+    fkv = torch.rand(5 * numK, device="cuda", generator=gen) - 0.5
+    fr, fi = torch.zeros(numX, device="cuda"), torch.zeros(numX, device="cuda")
+    mf = lambda s=0, e=None: ops.gptb_mrif(numK, xyz[0].data_ptr(), xyz[1].data_ptr(), xyz[2].data_ptr(), fr.data_ptr(),
+                                           fi.data_ptr(), fkv.data_ptr(), numX, start=s, end=e, grid=sms * 2, block=512)
+    r = pair_report(ops, sms, t_of, tz4, mf, 1024, "mrif", w_sweep)
+    r["mrif_frac_of_sfu_bound"] = round(2.0 * numK * numX / (sms * 16 * 1.965e9) / (r["mrif_us"] * 1e-6), 3)
+    out["gemm4096x2048_mrif"] = r
     del keep3, keep4
     return out
 
@@ -614,6 +641,9 @@ def main():
     ap.add_argument("--profile-pair", choices=("cp", "mriq"), default=None,
                     help="find that pair's balanced quantum, then launch its fused kernel three times and exit")
     ap.add_argument("--profile-w", type=int, default=832, help="CUDA-core threads of the --profile-pair launches")
+    ap.add_argument("--profile-blocks", type=int, default=0,
+                    help="CUDA-core blocks of the --profile-pair launches (0 = balance against the GEMM by measurement; "
+                         "under a profiler that measurement is distorted, so pass the value a plain run found)")
     ap.add_argument("--fuse-sweeps", type=int, default=0, choices=(0, 1, 2, 10),
                     help="how many sweeps are fused with the GEMM (0 = time 10, 2 and 1 briefly and take the best)")
     args = ap.parse_args()

@@ -118,16 +118,54 @@ struct Gemm2Smem {
     static constexpr int kBytes = kEpiOffset + 4 * kEpiWarpBytes;
 };
 
+// The pair tiles of a launch as every role of a pair walks them.  Whole waves of 256 x 256 tiles first; when the
+// last wave would leave at least half of the pairs idle (and the launcher supplied the 64-row B map), its tiles
+// are cut into two 256 x 128 halves so that twice as many pairs share it: 256 tiles on 74 pairs take 3.5 tile
+// times instead of 4.
+struct PairTileList {
+    int nfull;    // candidates walked as whole tiles: cand = pair, pair + npairs, ... < nfull
+    int nhalves;  // half tiles after them: pair p < nhalves takes half (p & 1) of candidate nfull + p / 2
+    __device__ __forceinline__ void init(const SuperTileWalk256& w, const GemmArgs& g, int npairs, bool can_split) {
+        nfull = w.ncand;
+        nhalves = 0;
+        const bool whole = w.start == 0 && w.end == w.nt * w.mt && w.mt % 4 == 0 && w.nt % 4 == 0;
+        const int rem = w.ncand % npairs;
+        if (can_split && whole && rem > 0 && 2 * rem <= npairs) {
+            nfull = w.ncand - rem;
+            nhalves = 2 * rem;
+        }
+        (void)g;
+    }
+    // step k of pair `pair`: false when its list is exhausted; half = -1 for a whole tile, else 0 / 1
+    __device__ __forceinline__ bool get(int k, int pair, int npairs, int& cand, int& half) const {
+        const int nw = nfull > pair ? (nfull - pair + npairs - 1) / npairs : 0;
+        half = -1;
+        if (k < nw) {
+            cand = pair + k * npairs;
+            return true;
+        }
+        if (k == nw && pair < nhalves) {
+            cand = nfull + pair / 2;
+            half = pair & 1;
+            return true;
+        }
+        return false;
+    }
+};
+
 // `pair`/`npairs`: index of this cluster and number of clusters of the launch.  All 192 tensor-role threads of
 // both CTAs call this; every OTHER thread of the two CTAs must have executed cluster_arrive() once.
-// tmap_a: box 64 x 128 rows; tmap_b: box 64 x 128 rows (a half of the pair's B tile).
+// tmap_a: box 64 x 128 rows; tmap_b: box 64 x 128 rows (a half of the pair's B tile); tmap_bh: box 64 x 64 rows
+// (a quarter: this CTA's share of a half tile) or null, in which case no tile is ever cut.
 template <int STAGES>
 __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_a,
                                            const CUtensorMap* __restrict__ tmap_b, const GemmArgs g, uint8_t* smem,
-                                           const int warp, const int lane, const int pair, const int npairs) {
+                                           const int warp, const int lane, const int pair, const int npairs,
+                                           const CUtensorMap* __restrict__ tmap_bh = nullptr) {
     using L = Gemm2Smem<STAGES>;
     constexpr uint32_t kTmemCols = 512;  // two 256-column accumulator buffers
     constexpr uint32_t kIdesc = umma_idesc_f16_f32(256, kGemm2BN);
+    constexpr uint32_t kIdescHalf = umma_idesc_f16_f32(256, kGemm2BN / 2);
 
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
@@ -142,6 +180,8 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
 
     SuperTileWalk256 walk;
     walk.init(g);
+    PairTileList list;
+    list.init(walk, g, npairs, tmap_bh != nullptr);
     const int kblocks = g.K / kGemmBK;
 
     // ---- set-up ----
@@ -177,18 +217,22 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int cand = pair; cand < walk.ncand && ok; cand += npairs) {
+            int cand, half;
+            for (int step = 0; ok && list.get(step, pair, npairs, cand, half); ++step) {
                 int R, Cc;
                 if (walk.mask(cand, R, Cc) == 0u) continue;
+                // this CTA's share of the B tile: 128 of 256 rows, or 64 of the 128 rows of a half tile
+                const uint32_t b_bytes = half < 0 ? L::kBBytes : L::kBBytes / 2;
+                const int b_row = half < 0 ? Cc * kGemm2BN + static_cast<int>(rank) * (kGemm2BN / 2)
+                                           : Cc * kGemm2BN + half * (kGemm2BN / 2) + static_cast<int>(rank) * (kGemm2BN / 4);
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_EMPTY);
                     if (!ok) break;
-                    if (leader) mbar_arrive_expect_tx(full_bar(stage), 2u * L::kStageBytes);
+                    if (leader) mbar_arrive_expect_tx(full_bar(stage), 2u * (L::kABytes + b_bytes));
                     const uint32_t full_leader = mapa_shared(full_bar(stage), 0u);
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
                     tma_load_tile_pair(a_dst, tmap_a, full_leader, kb * kGemmBK, R * 256 + static_cast<int>(rank) * 128, 0);
-                    tma_load_tile_pair(a_dst + L::kABytes, tmap_b, full_leader, kb * kGemmBK,
-                                       Cc * kGemm2BN + static_cast<int>(rank) * (kGemm2BN / 2), 0);
+                    tma_load_tile_pair(a_dst + L::kABytes, half < 0 ? tmap_b : tmap_bh, full_leader, kb * kGemmBK, b_row, 0);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -212,7 +256,8 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
             uint32_t phase = 0;
             uint32_t it = 0;
             bool ok = true;
-            for (int cand = pair; cand < walk.ncand && ok; cand += npairs) {
+            int cand, half;
+            for (int step = 0; ok && list.get(step, pair, npairs, cand, half); ++step) {
                 int R, Cc;
                 if (walk.mask(cand, R, Cc) == 0u) continue;
                 const uint32_t as = it & 1u, aphase = (it >> 1) & 1u;
@@ -220,6 +265,7 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + as * kGemm2BN;
+                const uint32_t idesc = half < 0 ? kIdesc : kIdescHalf;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait(full_bar(stage), phase, abort_flag, g.status, DEV_TIMEOUT_FULL);
                     if (!ok) break;
@@ -229,7 +275,7 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
                     const uint64_t b_desc = umma_smem_desc_sw128(a_src + L::kABytes);
 #pragma unroll
                     for (int k = 0; k < kGemmBK / 16; ++k)
-                        umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, (kb > 0 || k != 0) ? 1u : 0u);
+                        umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb > 0 || k != 0) ? 1u : 0u);
                     // the stage is free in BOTH CTAs once these MMAs have read it
                     umma_commit_pair(empty_bar(stage));
                     umma_commit_pair(mapa_shared(empty_bar(stage), 1u));
@@ -258,7 +304,8 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
         const uint32_t tempty_leader0 = mapa_shared(tempty_bar(0), 0u);
         uint32_t it = 0;
         bool ok = true;
-        for (int cand = pair; cand < walk.ncand && ok; cand += npairs) {
+        int cand, half;
+        for (int step = 0; ok && list.get(step, pair, npairs, cand, half); ++step) {
             int R, Cc;
             const uint32_t m16 = walk.mask(cand, R, Cc);
             if (m16 == 0u) continue;
@@ -267,13 +314,19 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
             if (!ok) break;
             tc_fence_after_sync();
             // the 4 mask bits of this warp's 64-row quarter of the pair tile
-            const uint32_t m = (m16 >> ((2 * static_cast<int>(rank) + h) * 4)) & 0xFu;
+            uint32_t m = (m16 >> ((2 * static_cast<int>(rank) + h) * 4)) & 0xFu;
             const int row0 = R * 256 + static_cast<int>(rank) * 128 + q * 32;
             float* cbase = g.C + static_cast<size_t>(row0) * g.N + static_cast<size_t>(Cc) * kGemm2BN;
+            int nchunks = kGemm2BN / 32;
+            if (half >= 0) {  // a half tile: accumulator columns 0 .. 127 are C columns 128 half .. 128 half + 127
+                cbase += half * (kGemm2BN / 2);
+                m >>= 2 * half;
+                nchunks = kGemm2BN / 64;
+            }
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kGemm2BN;
             float* stage = reinterpret_cast<float*>(smem + L::kEpiOffset) + (warp - 2) * (32 * L::kEpiPitch);
 #pragma unroll 1
-            for (int c = 0; c < kGemm2BN / 32; ++c) {
+            for (int c = 0; c < nchunks; ++c) {
                 if (((m >> (c >> 1)) & 1u) == 0u) continue;  // warp-uniform
                 uint32_t r[32];
                 tmem_ld_32x32(t_lane + c * 32, r);

@@ -50,6 +50,7 @@ struct Options {
     int mix_stencil_ring = 12;  // upper bound of the ring depth in the fused kernel (shared memory decides)
     int tzgemm_m256 = 0;        // solo tzgemm with 256 x 256 super-tiles: 0 = by shape, 1 = always, -1 = never
     int tzgemm_pair = 0;        // solo tzgemm on CTA pairs (cta_group::2): 0 = by shape, 1 = whenever possible, -1 = never
+    int tzgemm_pair_split = 1;  // solo kernel on CTA pairs: cut the tiles of a short last wave into column halves
     int mix_pair = 0;           // the same for the tensor role of the fused kernels
     int mix_pair_stages = 4;    // operand stages of the fused stencil kernel on CTA pairs (3 .. 5; the rest goes to the rings)
     int l2_hints = 0;           // fused kernels: GEMM tiles evict-last, stencil planes evict-first in L2
@@ -461,10 +462,11 @@ static int run_tzgemm_pair(const GemmCall& c, DeviceInfo* d, unsigned ctas, cuda
     if (rc != TK_OK) return rc;
     unsigned pairs = 0;
     if ((rc = pairs_for(kernel, d, ctas, kGemm2Threads, smem, &pairs)) != TK_OK) return rc;
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tbh;
     if ((rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM)) != TK_OK) return rc;
     if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, kGemm2BN / 2)) != TK_OK) return rc;
-    kernel<<<2 * pairs, kGemm2Threads, smem, st>>>(ta, tb, c.g);
+    if ((rc = make_tmap(&tbh, c.B, c.g.N, c.g.K, kGemm2BN / 4)) != TK_OK) return rc;
+    kernel<<<2 * pairs, kGemm2Threads, smem, st>>>(ta, tb, tbh, c.g, g_opt.tzgemm_pair_split);
     return launch_error("tzgemm2_kernel launch");
 }
 

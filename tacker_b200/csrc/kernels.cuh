@@ -59,10 +59,10 @@ tzgemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 template <int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemm2Threads, 1)
 tzgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const GemmArgs g) {
+               const __grid_constant__ CUtensorMap tmap_bh, const GemmArgs g, const int split_tail) {
     extern __shared__ uint8_t smem_raw[];
     gemm_role2<STAGES>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), threadIdx.x >> 5, threadIdx.x & 31,
-                       blockIdx.x >> 1, gridDim.x >> 1);
+                       blockIdx.x >> 1, gridDim.x >> 1, split_tail ? &tmap_bh : nullptr);
 }
 
 template <int PF>

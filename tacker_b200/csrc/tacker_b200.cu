@@ -59,6 +59,7 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "wait_budget_us")) return &g_opt.wait_budget_us;
     if (!std::strcmp(name, "test_skip_loads")) return &g_opt.test_skip_loads;
     if (!std::strcmp(name, "tzgemm_pair")) return &g_opt.tzgemm_pair;
+    if (!std::strcmp(name, "tzgemm_pair_split")) return &g_opt.tzgemm_pair_split;
     if (!std::strcmp(name, "mix_pair")) return &g_opt.mix_pair;
     if (!std::strcmp(name, "mix_pair_stages")) return &g_opt.mix_pair_stages;
     return nullptr;

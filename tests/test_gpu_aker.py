@@ -68,15 +68,16 @@ def test_fused_colocation_beats_time_slicing_within_qos(cuda, tmp_path):
 
 
 def test_colocation_meets_qos(cuda, tmp_path):
-    out = subprocess.run([_aker(), "-s", "aker", "-m", "vgg16", "-c", os.path.join(HOST, "config"), "--colocate", "3",
+    # 10 s per phase: the bound is 1.5 x the p99 of the solo phase, and a p99 over a few hundred queries is too noisy
+    out = subprocess.run([_aker(), "-s", "aker", "-m", "vgg16", "-c", os.path.join(HOST, "config"), "--colocate", "10",
                           "--qps", "200", "--qos", "1.5", "--be", "bert"], capture_output=True, text=True, timeout=600,
                          cwd=tmp_path)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
     r = json.loads(line)
-    assert r["lc_served"] > 400 and r["be_queries"] > 0 and r["be_qps"] > 0
+    assert r["lc_served"] > 1500 and r["be_queries"] > 0 and r["be_qps"] > 0
     assert r["lc_p99_ms"] >= r["lc_p50_ms"] > 0
-    assert r["qos_met"] is True and r["lc_p99_ms"] <= r["qos_bound_ms"]
+    assert r["qos_met"] is True and r["lc_p99_ms"] <= r["qos_bound_ms"], r
 
 
 def test_vgg16_scores_match_the_cpu_forward(cuda, oracle, tmp_path):
