@@ -50,7 +50,8 @@ GEMM_BYTES = 2 * (M * K + N * K) + 4 * M * N
 LAUNCH_BYTES = SWEEP_BYTES + GEMM_BYTES / SWEEPS
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from ncu captures of these two kernels on this
 # workload (caches flushed by ncu before the launch; part of the output is still dirty in L2 when the kernel ends)
-NCU_TRAFFIC_BYTES = {"stencil_tma_kernel": 94.05e6, "mix_stencil_kernel": 108.3e6}
+# mix_stencil_kernel: the launch with a tenth of the tiles; mix_stencil2_kernel: the CTA-pair launch with half of them
+NCU_TRAFFIC_BYTES = {"stencil_tma_kernel": 94.05e6, "mix_stencil_kernel": 108.3e6, "mix_stencil2_kernel": 138.0e6}
 
 
 def measured_peaks():
