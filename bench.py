@@ -323,6 +323,28 @@ def run_ours(args):
 
     # ---- the kernels one by one (explain the headline) ----
     us_gemm = t_of([tz_kernel()])
+
+    # yardstick only, never on the measured path: the vendor library's GEMM on the same operands, timed the same way
+    # (fp32 output like tzgemm where this torch has `out_dtype`, else the cheaper fp16 output)
+    def library_gemm_us():
+        Bt = B.t()
+        try:
+            torch.mm(A, Bt, out_dtype=torch.float32)
+            call, out = (lambda: torch.mm(A, Bt, out_dtype=torch.float32)), "fp32 out"
+        except Exception:
+            call, out = (lambda: torch.mm(A, Bt)), "fp16 out"
+        reps = 2 if args.quick else 20
+
+        def fn():
+            for _ in range(reps):
+                call()
+        with torch.cuda.stream(stream):
+            us = timed(make_graph(fn), 3, 2) / reps * 1e3
+        return us, out
+    try:
+        us_lib, lib_out = library_gemm_us()
+    except Exception as e:  # the yardstick must never take the benchmark down
+        us_lib, lib_out = None, f"unavailable: {type(e).__name__}"
     us_sweep = t_of([cd_kernel(i) for i in range(SWEEPS)]) / SWEEPS
     us_fused_launch = {}
     for f in (SWEEPS, 2, 1):
@@ -494,6 +516,8 @@ def run_ours(args):
         "schedules_ms_per_pair": {f"{f}_fused_launches": round(v, 4) for f, v in cands.items()},
         "solo_us": {"tzgemm_4096x4096x1024": round(us_gemm, 2), "stencil_sweep": round(us_sweep, 2),
                     "tzgemm_tflops": round(2.0 * M * N * K / (us_gemm * 1e-6) / 1e12, 1),
+                    "library_gemm_same_shape": {"us": None if us_lib is None else round(us_lib, 2), "output": lib_out,
+                                                "tzgemm_vs_library": None if us_lib is None else round(us_lib / us_gemm, 3)},
                     "stencil_gbs": round(SWEEP_BYTES / (us_sweep * 1e-6) / 1e9, 1),
                     "fused_launch_us": {f"sweep+{TILES // f}_tiles": round(v, 2) for f, v in us_fused_launch.items()}},
         "ratio_sweep": sweep, "pairs": pairs, "clocks": clocks,

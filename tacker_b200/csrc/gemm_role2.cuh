@@ -16,9 +16,12 @@
 //                  warps 2..5 epilogue of its 128 rows
 //
 // Signals.  full[s] lives in the leader: one arrival (the leader's producer, which also announces the bytes of
-// BOTH CTAs) plus the bytes of both CTAs' loads.  empty[s] and tfull[a] exist in both CTAs; the MMA thread
-// signals each of them with its own tcgen05.commit (one to the local barrier, one to the peer's barrier through
-// its cluster address).  tempty[a] lives in the leader and counts the eight epilogue warps of the pair.
+// BOTH CTAs) plus the bytes of both CTAs' loads.  empty[s] exists in both CTAs: the MMA thread signals the
+// leader's with one tcgen05.commit per K-block, and the leader's producer, once it has seen that arrival, passes
+// it on to the peer's barrier with a plain remote arrive -- the MMA thread is the one serial instruction stream
+// the whole pair waits for (about 60 cycles per tcgen05 instruction against 128 cycles of tensor pipe per MMA),
+// so everything that can be is kept out of it.  tfull[a] exists in both CTAs (two commits per tile).  tempty[a]
+// lives in the leader and counts the eight epilogue warps of the pair.
 // No load is a cluster broadcast: every CTA fetches what it needs itself.  Every wait is bounded as in gemm_role.
 // The two CTAs never leave while the other may still touch them: everything a CTA sends to its peer is awaited
 // by a role of the peer before that role ends (see the tails of the producer and the MMA issuer).
@@ -55,6 +58,21 @@ __device__ __forceinline__ void cluster_wait() {
 // (tcgen05.wait::ld), and a release at cluster scope would make the warp wait for all its stores to C first.
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// non-blocking probe of a barrier phase
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
 }
 
 // operand tile load of a CTA pair: the data lands in this CTA, the bytes are counted on the barrier at
@@ -98,6 +116,26 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                  : "memory");
 }
+
+// ---- optional phase trace (diagnostic builds with -DTK_TRACE only) ------------------------------------------
+// Per CTA 16 values: [0] globaltimer at role entry, [1] clock at role entry, [2] clock after set-up, [3] clock when the
+// first operand stage had landed (leader), [4] clock after the last commit (leader), [5] clock when the last accumulator
+// was complete, [6] clock at the end of the last epilogue, [7] cycles spent in epilogues, [8] tiles, [9] clock at role
+// exit, [10] globaltimer at role exit, [11] cycles the MMA thread waited for operands after the first stage, [12] cycles
+// it waited for a free accumulator, [13] cycles the producer waited for free stages.  tk_debug_trace() copies them out.
+#ifdef TK_TRACE
+__device__ long long g_tk_trace[512 * 16];
+__device__ __forceinline__ long long tk_gtime() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TK_TR(slot, val) (g_tk_trace[(blockIdx.x & 511) * 16 + (slot)] = (val))
+#define TK_TRACE_ONLY(...) __VA_ARGS__
+#else
+#define TK_TR(slot, val) ((void)0)
+#define TK_TRACE_ONLY(...)
+#endif
 
 // ---- the role ------------------------------------------------------------------------------------------
 constexpr int kGemm2BN = 256;          // columns of a pair tile
@@ -183,6 +221,8 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
     PairTileList list;
     list.init(walk, g, npairs, tmap_bh != nullptr);
     const int kblocks = g.K / kGemmBK;
+    TK_TRACE_ONLY(if (warp == 2 && lane == 0) { TK_TR(0, tk_gtime()); TK_TR(1, clock64()); } long long tr_a = 0, tr_b = 0;
+                  bool tr_first = true;)
 
     // ---- set-up ----
     if (warp == 0 && lane == 0) {
@@ -210,6 +250,7 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
     named_bar_sync(kGemmBarrierId, kGemm2Threads);
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    TK_TRACE_ONLY(if (warp == 2 && lane == 0) TK_TR(2, clock64());)
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
@@ -218,6 +259,12 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
             uint32_t phase = 0;
             bool ok = true;
             int cand, half;
+            // The leader's wait number i (counted over the whole launch) sees the commit of K-block i - STAGES; the
+            // first STAGES waits pass without any arrival, in both CTAs.  Every later one is passed on to the peer with
+            // a relaxed arrive: no data travels with it, the MMAs' reads of the peer's stage ended before the commit
+            // arrived here, and a release at cluster scope would stall this thread for a memory fence per K-block.
+            int waits = 0;
+            const uint32_t empty_peer0 = mapa_shared(empty_bar(0), 1u);
             for (int step = 0; ok && list.get(step, pair, npairs, cand, half); ++step) {
                 int R, Cc;
                 if (walk.mask(cand, R, Cc) == 0u) continue;
@@ -226,8 +273,12 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
                 const int b_row = half < 0 ? Cc * kGemm2BN + static_cast<int>(rank) * (kGemm2BN / 2)
                                            : Cc * kGemm2BN + half * (kGemm2BN / 2) + static_cast<int>(rank) * (kGemm2BN / 4);
                 for (int kb = 0; kb < kblocks; ++kb) {
+                    TK_TRACE_ONLY(const long long tw = clock64();)
                     ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_EMPTY);
+                    TK_TRACE_ONLY(tr_a += clock64() - tw;)
                     if (!ok) break;
+                    if (leader && waits >= STAGES) mbar_arrive_cluster_relaxed(empty_peer0 + 8u * stage);
+                    ++waits;
                     if (leader) mbar_arrive_expect_tx(full_bar(stage), 2u * (L::kABytes + b_bytes));
                     const uint32_t full_leader = mapa_shared(full_bar(stage), 0u);
                     const uint32_t a_dst = smem_base + stage * L::kStageBytes;
@@ -243,11 +294,14 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
             // do not let the CTA retire before they have landed and the MMAs have stopped reading its stages
             for (int s = 0; s < STAGES && ok; ++s) {
                 ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_EMPTY);
+                if (ok && leader && waits >= STAGES) mbar_arrive_cluster_relaxed(empty_peer0 + 8u * stage);
+                ++waits;
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
                 }
             }
+            TK_TR(13, tr_a);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader only) ----------------
@@ -256,39 +310,50 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
             uint32_t phase = 0;
             uint32_t it = 0;
             bool ok = true;
+            bool ready = false;  // the full barrier of `stage` was already seen complete
             int cand, half;
             for (int step = 0; ok && list.get(step, pair, npairs, cand, half); ++step) {
                 int R, Cc;
                 if (walk.mask(cand, R, Cc) == 0u) continue;
                 const uint32_t as = it & 1u, aphase = (it >> 1) & 1u;
+                TK_TRACE_ONLY(const long long tw = clock64();)
                 ok = mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, g.status, DEV_TIMEOUT_TMEM_EMPTY);
+                TK_TRACE_ONLY(tr_b += clock64() - tw;)
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + as * kGemm2BN;
                 const uint32_t idesc = half < 0 ? kIdesc : kIdescHalf;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    ok = mbar_wait(full_bar(stage), phase, abort_flag, g.status, DEV_TIMEOUT_FULL);
-                    if (!ok) break;
+                    if (!ready) {
+                        TK_TRACE_ONLY(const long long tw = clock64();)
+                        ok = mbar_wait(full_bar(stage), phase, abort_flag, g.status, DEV_TIMEOUT_FULL);
+                        TK_TRACE_ONLY(if (tr_first) TK_TR(3, clock64()); else tr_a += clock64() - tw;)
+                        if (!ok) break;
+                    }
+                    TK_TRACE_ONLY(tr_first = false;)
                     tc_fence_after_sync();
                     const uint32_t a_src = smem_base + stage * L::kStageBytes;
                     const uint64_t a_desc = umma_smem_desc_sw128(a_src);
                     const uint64_t b_desc = umma_smem_desc_sw128(a_src + L::kABytes);
-#pragma unroll
-                    for (int k = 0; k < kGemmBK / 16; ++k)
-                        umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb > 0 || k != 0) ? 1u : 0u);
-                    // the stage is free in BOTH CTAs once these MMAs have read it
-                    umma_commit_pair(empty_bar(stage));
-                    umma_commit_pair(mapa_shared(empty_bar(stage), 1u));
+                    const uint32_t this_empty = empty_bar(stage);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
+                    // probe the next stage now: the answer arrives while the MMAs below are being issued
+                    ready = mbar_test_wait(full_bar(stage), phase);
+#pragma unroll
+                    for (int k = 0; k < kGemmBK / 16; ++k)
+                        umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb > 0 || k != 0) ? 1u : 0u);
+                    // the stage is free in both CTAs once these MMAs have read it (the leader's producer tells the peer)
+                    umma_commit_pair(this_empty);
                 }
                 if (!ok) break;
                 umma_commit_pair(tfull_bar(as));  // accumulator complete: tell both epilogues
                 umma_commit_pair(mapa_shared(tfull_bar(as), 1u));
                 ++it;
             }
+            TK_TRACE_ONLY(TK_TR(4, clock64()); TK_TR(11, tr_a); TK_TR(12, tr_b);)
             // tail: the peer's epilogue warps arrive on this CTA's tempty barriers; wait until the last two accumulators
             // have been released by all eight warps before this CTA may retire
             for (int j = 0; j < 2 && ok; ++j) {
@@ -313,6 +378,7 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
             ok = mbar_wait(tfull_bar(as), aphase, abort_flag, g.status, DEV_TIMEOUT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after_sync();
+            TK_TRACE_ONLY(const long long tw = clock64();)
             // the 4 mask bits of this warp's 64-row quarter of the pair tile
             uint32_t m = (m16 >> ((2 * static_cast<int>(rank) + h) * 4)) & 0xFu;
             const int row0 = R * 256 + static_cast<int>(rank) * 128 + q * 32;
@@ -347,7 +413,8 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
                 for (int i = 0; i < 8; ++i) {
                     const int rr = 4 * i + (lane >> 3);
                     const float4 o = *reinterpret_cast<const float4*>(stage + rr * L::kEpiPitch + (lane & 7) * 4);
-                    *reinterpret_cast<float4*>(cchunk + static_cast<size_t>(rr) * g.N) = o;
+                    // C is written once and not read by this launch: streaming stores leave the operands in L2
+                    __stcs(reinterpret_cast<float4*>(cchunk + static_cast<size_t>(rr) * g.N), o);
                 }
                 __syncwarp();
             }
@@ -355,6 +422,8 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader0 + 8u * as);
             ++it;
+            TK_TRACE_ONLY(tr_a += clock64() - tw; if (warp == 2 && lane == 0) { TK_TR(5, tw); TK_TR(6, clock64()); TK_TR(7, tr_a);
+                              TK_TR(8, static_cast<long long>(it)); })
         }
     }
 
@@ -365,6 +434,7 @@ __device__ __forceinline__ void gemm_role2(const CUtensorMap* __restrict__ tmap_
     named_bar_sync(kGemmBarrierId, kGemm2Threads);
     tc_fence_after_sync();
     if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+    TK_TRACE_ONLY(if (warp == 2 && lane == 0) { TK_TR(9, clock64()); TK_TR(10, tk_gtime()); })
 }
 
 }  // namespace tk

@@ -949,6 +949,19 @@ static int generated_mix_launch(CdKind kind, int cd_warps, void** params, int np
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
     c.g.status = d->status_ptr;
+    // empty ranges as in the library's fused launchers: nothing to do, or the other kernel alone
+    const bool gemm_empty = c.g.start >= c.g.end;
+    if (gemm_empty && cd.empty()) return TK_OK;
+    if (gemm_empty) {
+        const unsigned cdt = 32u * static_cast<unsigned>(cd_warps);
+        switch (kind) {
+            case CD_STENCIL: return run_stencil(cd.s, grid[0], cdt, static_cast<cudaStream_t>(stream));
+            case CD_CP: return run_cp(cd.a, grid[0], cdt, static_cast<cudaStream_t>(stream));
+            case CD_MRIF: return run_mrif(cd.f, grid[0], cdt, static_cast<cudaStream_t>(stream));
+            default: return run_mriq(cd.m, grid[0], cdt, static_cast<cudaStream_t>(stream));
+        }
+    }
+    if (cd.empty()) return run_tzgemm(c, grid[0], static_cast<cudaStream_t>(stream));
     const unsigned ctas = grid[0] < static_cast<unsigned>(d->sm_count) ? grid[0] : static_cast<unsigned>(d->sm_count);
     const unsigned threads = kGemmThreads + 32u * static_cast<unsigned>(cd_warps);
     CUtensorMap ta, tb, tg;
@@ -969,6 +982,7 @@ static int generated_mix_launch(CdKind kind, int cd_warps, void** params, int np
     const long long cd_warps_total = static_cast<long long>(ctas) * cd_warps;
     if (kind == CD_CP) cd.a.atoms_per_item = cp_split_for(cd.a, 8, cd_warps_total);
     if (kind == CD_MRIQ) cd.m.k_per_item = mriq_split_for(cd.m, 2, cd_warps_total);
+    if (kind == CD_MRIF) cd.f.k_per_item = mrif_split_for(cd.f, 2, cd_warps_total);
     rc = launch(ta, tb, c.g, tg, cd, ring, ctas, threads, smem, static_cast<cudaStream_t>(stream));
     if (rc != TK_OK) return rc;
     return launch_error("generated mix kernel launch");

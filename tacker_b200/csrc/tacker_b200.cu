@@ -622,6 +622,8 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     if (!A_host || !B_host || !C_host || !A0_host || !Aout_host || !workspace || sweeps < 1) return TK_ERR_ARGS;
     if (workspace_bytes < need) return TK_ERR_CAPACITY;
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return TK_ERR_ALIGN;
+    // every argument is checked before the first copy is queued: a refused call leaves nothing on the streams
+    if (M < 128 || N < 64 || K < 64 || M % 128 || N % 64 || K % 64) return TK_ERR_SHAPE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* w = static_cast<uint8_t*>(workspace);
     const size_t a_bytes = 2 * static_cast<size_t>(M) * K, b_bytes = 2 * static_cast<size_t>(N) * K;
@@ -655,7 +657,6 @@ TK_API int tk_pair_tzgemm_stencil_host(const void* A_host, const void* B_host, f
     c.g.K = K;
     c.g.alpha = alpha;
     gemm_args_defaults(&c.g);
-    if (M < 128 || N < 64 || K < 64 || M % 128 || N % 64 || K % 64) return TK_ERR_SHAPE;
     const int tiles = (M / 64) * (N / 64);
     CdCall cd;
     cd.kind = CD_STENCIL;
@@ -1154,3 +1155,11 @@ TK_API int tk_plan_stencil(int nz, int blocks_start, int blocks_end, int gx, int
         }
     return TK_OK;
 }
+
+// Diagnostic builds (-DTK_TRACE) only: the per-CTA phase timestamps of the last tzgemm launch on CTA pairs
+// (512 CTAs x 16 values, layout in gemm_role2.cuh).
+#ifdef TK_TRACE
+TK_API int tk_debug_trace(long long* out) {
+    return cudaMemcpyFromSymbol(out, tk::g_tk_trace, sizeof(long long) * 512 * 16) == cudaSuccess ? 0 : 1;
+}
+#endif

@@ -51,7 +51,15 @@ def check_module(so_path: str, name: str, cd: str) -> dict:
 
     st = torch.cuda.current_stream().cuda_stream
     results = {}
-    for mode in ("solo", "generated"):
+    def launch_generated(cdk, tz, cd_range=None, tz_range=None):
+        mk = ops.mix(cdk, tz, cd_threads=threads - 192, grid=sms, cd_range=cd_range, tz_range=tz_range)
+        arr = (C.c_void_p * len(mk.kernelParams))(*[C.cast(C.pointer(p), C.c_void_p) for p in mk.kernelParams])
+        rc = fn(arr, len(mk.kernelParams), (C.c_uint * 3)(sms, 1, 1), (C.c_uint * 3)(threads, 1, 1), 0, C.c_void_p(st))
+        assert rc == 0, f"generated launcher returned {rc}"
+
+    # "halves": the pair as two launches with one side's block range empty (the launcher then runs the other
+    # kernel alone), then one with both empty (nothing runs)
+    for mode in ("solo", "generated", "halves"):
         bufs, out_idx = fresh()
         Cm = torch.zeros(M, N, device="cuda")
         tz = ops.gptb_tzgemm(A.data_ptr(), B.data_ptr(), Cm.data_ptr(), M, N, K, alpha=1.1, grid=sms)
@@ -59,12 +67,12 @@ def check_module(so_path: str, name: str, cd: str) -> dict:
         if mode == "solo":
             tz.execute(st)
             cdk.execute(st)
+        elif mode == "generated":
+            launch_generated(cdk, tz)
         else:
-            mk = ops.mix(cdk, tz, cd_threads=threads - 192, grid=sms)
-            arr = (C.c_void_p * len(mk.kernelParams))(*[C.cast(C.pointer(p), C.c_void_p) for p in mk.kernelParams])
-            rc = fn(arr, len(mk.kernelParams), (C.c_uint * 3)(sms, 1, 1), (C.c_uint * 3)(threads, 1, 1), 0,
-                    C.c_void_p(st))
-            assert rc == 0, f"generated launcher returned {rc}"
+            launch_generated(cdk, tz, tz_range=(0, 0))
+            launch_generated(cdk, tz, cd_range=(0, 0))
+            launch_generated(cdk, tz, cd_range=(0, 0), tz_range=(0, 0))
         torch.cuda.synchronize()
         results[mode] = (Cm.cpu().numpy(), bufs[out_idx].cpu().numpy())
     same_gemm = bool(np.array_equal(results["solo"][0], results["generated"][0]))
@@ -74,6 +82,9 @@ def check_module(so_path: str, name: str, cd: str) -> dict:
     scale = float(np.abs(results["solo"][1]).max())
     cd_err = float(np.abs(results["solo"][1] - results["generated"][1]).max()) / (scale if scale > 0 else 1.0)
     cd_ok = same_cd if cd == "stencil" else cd_err <= 1e-5
+    halves_err = float(np.abs(results["solo"][1] - results["halves"][1]).max()) / (scale if scale > 0 else 1.0)
+    halves_ok = bool(np.array_equal(results["solo"][0], results["halves"][0])) and halves_err <= 1e-5
+    same_gemm = same_gemm and halves_ok
     return {"name": name, "threads": threads, "gemm_bit_identical": same_gemm, "cd_bit_identical": same_cd,
-            "cd_max_rel_err": cd_err,
+            "cd_max_rel_err": cd_err, "empty_ranges_ok": halves_ok,
             "ok": same_gemm and cd_ok and bool(np.abs(results["generated"][0]).max() > 0)}

@@ -70,3 +70,24 @@ def test_pair_host_buffers(cuda, oracle):
     with pytest.raises(Exception, match="capacity"):
         ops.pair_tzgemm_stencil_host(hA.data_ptr(), hB.data_ptr(), hC.data_ptr(), M, N, K, 1.0, 0.5, 0.25,
                                      hA0.data_ptr(), hOut.data_ptr(), nx, ny, nz, sweeps, 128, ws.data_ptr(), 1024, st)
+
+
+def test_pair_host_rejected_shape_queues_nothing(cuda, oracle):
+    """A call refused for its GEMM shape returns before any copy is queued: the workspace keeps its bytes."""
+    from tacker_b200 import ops
+
+    M, N, K = 256, 256, 96          # K is not a multiple of 64
+    nx, ny, nz = 128, 16, 8
+    hA = cuda.ones((M, K), dtype=cuda.float16).pin_memory()
+    hB = cuda.ones((N, K), dtype=cuda.float16).pin_memory()
+    hA0 = cuda.ones((nz, ny, nx), dtype=cuda.float32).pin_memory()
+    hC = cuda.empty((M, N), dtype=cuda.float32).pin_memory()
+    hOut = cuda.empty((nz, ny, nx), dtype=cuda.float32).pin_memory()
+    nbytes = ops.pair_tzgemm_stencil_workspace(M, N, K, nx, ny, nz)
+    ws = cuda.full((nbytes,), 0xA5, dtype=cuda.uint8, device="cuda")
+    st = cuda.cuda.current_stream().cuda_stream
+    with pytest.raises(Exception, match="shape"):
+        ops.pair_tzgemm_stencil_host(hA.data_ptr(), hB.data_ptr(), hC.data_ptr(), M, N, K, 1.0, 0.5, 0.25, hA0.data_ptr(),
+                                     hOut.data_ptr(), nx, ny, nz, 2, 128, ws.data_ptr(), nbytes, st)
+    cuda.cuda.synchronize()
+    assert bool((ws == 0xA5).all())
