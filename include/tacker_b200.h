@@ -110,7 +110,7 @@ int tk_device_check(void);
  * "gptb_mriq", "gptb_mrif", "tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq", "tzgemm_mrif"; plus "ori_stencil",
  * "ori_cp", "ori_mriq", "ori_mrif" for the non-persistent launch shape of the solo kernels; and "gptb_tzconv",
  * "tzconv_stencil", "tzconv_cp", "tzconv_mriq", "tzconv_mrif" for the implicit-GEMM convolution (not in the
- * reference's table). */
+ * reference's table); and "gptb_<k>", "tzgemm_<k>", "tzconv_<k>", "ori_<k>" for k = sgemm, lbm, fft, cutcp. */
 tk_launch_fn tk_lookup(const char* key);
 int tk_num_keys(void);
 const char* tk_key(int index);
@@ -253,6 +253,62 @@ int tk_launch_ori_mriq(void** params, int nparams, const unsigned grid[3], const
 /* ori_mrif (8 params with kvals, src/ori_kernel/mrif_kernel.cu:78) */
 int tk_launch_ori_mrif(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
                        unsigned smem_bytes, void* stream);
+
+/* ---- sgemm, lbm, fft, cutcp ------------------------------------------------------------------------
+ * The other four Parboil kernels the reference pairs with tzgemm (src/Creator.cu:53-178, src/main.cu:108-159).
+ * gptb_<k> (solo list + 6 geometry ints + start, step, end, thread_base), tzgemm_<k> (the list without
+ * thread_base, then tzgemm's 7 + 6 + 3) and ori_<k> (the solo list; grid / block = the original launch).
+ *   sgemm (6)  float* A, float* B, float* C, int M, int N, int K      C = 2 C + 2 A B; A [K][M], B [K][N], C [N][M];
+ *              original grid (M / 128, N / 16), block (16, 8)           replaces general_ptb_sgemm
+ *                                                                       (src/gptb_kernel/sgemm_kernel.cu:3-64)
+ *   lbm (2)    float* srcGrid, float* dstGrid                           one D3Q19 step, scatter form; the pointers
+ *              original grid (ny, nz), block (nx)                       address cell (0,0,0), two z-planes of margin
+ *                                                                       on either side; nx % 32 == 0; replaces
+ *                                                                       general_ptb_lbm (src/gptb_kernel/lbm_kernel.cu)
+ *   fft (1)    float2* data                                             256-point transforms in place; replaces
+ *              original grid (batch), block (128)                       g_general_ptb_fft (src/gptb_kernel/fft_kernel.cu)
+ *   cutcp (10) int binDim_x, int binDim_y, float4* binZeroAddr,         replaces general_ptb_cutcp
+ *              float h, float cutoff2, float inv_cutoff2,               (src/gptb_kernel/cutcp_kernel.cu:12-183);
+ *              float* regionZeroAddr, int zRegionIndex_t,               nbr / nbrlen added: the table
+ *              int4* nbr, int nbrlen                                    tk_cutcp_pack_neighbours writes, replacing
+ *              original grid (gx, gy, gz) regions, block (8, 2, 8)      the __constant__ NbrList / NbrListLen
+ *                                                                       (src/ori_kernel/cutcp_kernel.cu:12-13)
+ * Results are the reference's bit for bit (each output has one fixed sequence of operations in all four). */
+int tk_launch_gptb_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                         unsigned smem_bytes, void* stream);
+int tk_launch_gptb_lbm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                       unsigned smem_bytes, void* stream);
+int tk_launch_gptb_fft(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                       unsigned smem_bytes, void* stream);
+int tk_launch_gptb_cutcp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                         unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzgemm_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                               unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzgemm_lbm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                             unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzgemm_fft(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                             unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzgemm_cutcp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                               unsigned smem_bytes, void* stream);
+/* tzconv_<k>: the same pairs with the implicit-GEMM convolution as the tensor role (list, then tzconv's 12 + 6 + 3) */
+int tk_launch_mix_tzconv_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                               unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzconv_lbm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                             unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzconv_fft(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                             unsigned smem_bytes, void* stream);
+int tk_launch_mix_tzconv_cutcp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                               unsigned smem_bytes, void* stream);
+int tk_launch_ori_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                        unsigned smem_bytes, void* stream);
+int tk_launch_ori_lbm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                      unsigned smem_bytes, void* stream);
+int tk_launch_ori_fft(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                      unsigned smem_bytes, void* stream);
+int tk_launch_ori_cutcp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                        unsigned smem_bytes, void* stream);
+/* neighbour offsets {dx, dy, dz} x n (device) -> the table of the cutcp kernels (device, 16-byte aligned, 16 n bytes) */
+int tk_cutcp_pack_neighbours(const int* nbr_xyz, int n, void* table, void* stream);
 
 /* ---- input preparation the reference does on the host -------------------------------------------
  * tk_cp_pack_atoms  replaces copyatomstoconstbuf (src/ori_kernel/cp_kernel.cu:159-179):

@@ -25,6 +25,7 @@
  * -ffp-contract=off matters: the host compiler must not invent FMAs.
  */
 #include <math.h>
+#include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -592,6 +593,298 @@ TKO_API void tko_im2col_f32(const float *im, int channels, int height, int width
                                                         : 0.0f;
                     }
             }
+}
+
+/* ------------------------------------------------------------------------- */
+/* sgemm: C = 2 C + 2 A B, Parboil register-tiled SGEMM                       */
+/* reference: src/gptb_kernel/sgemm_kernel.cu:3-64, src/header/sgemm_header.h */
+/*   A [K][M] (lda = M), B [K][N] (ldb = N), C [N][M] (ldc = M); block        */
+/*   (bx, by) of the (M/128, N/16) grid owns rows 128 bx .., columns 16 by ..;*/
+/*   each output accumulates k = 0 .. K-1 in order with one fused multiply-add*/
+/*   per step; the update C*2 + 2*c is exact in both products.                */
+/* ------------------------------------------------------------------------- */
+#define TKO_SGEMM_TM 128
+#define TKO_SGEMM_TN 16
+
+TKO_API void tko_sgemm_f32(const float *A, const float *B, float *C, int M, int N, int K, int start, int end) {
+    const int gx = M / TKO_SGEMM_TM, gy = N / TKO_SGEMM_TN;
+#pragma omp parallel for schedule(dynamic)
+    for (int p = start; p < end; p++) {
+        int bx = p % gx, by = (p / gx) % gy;
+        for (int i = 0; i < TKO_SGEMM_TM; i++) {
+            int m = bx * TKO_SGEMM_TM + i;
+            for (int j = 0; j < TKO_SGEMM_TN; j++) {
+                int n = by * TKO_SGEMM_TN + j;
+                float c = 0.0f;
+                for (int k = 0; k < K; k++) c = fmaf(A[m + (size_t)k * M], B[n + (size_t)k * N], c);
+                size_t t = (size_t)n * M + m;
+                C[t] = C[t] * 2.0f + 2.0f * c;
+            }
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* lbm: one D3Q19 lattice-Boltzmann step, scatter form (Parboil / SPEC 470)   */
+/* reference: src/gptb_kernel/lbm_kernel.cu:3-177, src/header/lbm_header.h    */
+/*   layout: element e of cell (x, y, z) at e * cells + x + y nx + z nx ny;   */
+/*   elements C N S E W T B NE NW SE SW NT NB ST SB ET EB WT WB FLAGS; block  */
+/*   p of the (ny, nz) grid is the row y = p % ny, z = p / ny; each cell      */
+/*   reads its own 19 values, relaxes them (or reflects them in an obstacle   */
+/*   cell) and writes value d to the neighbour in direction d -- by flat      */
+/*   index, so rows at the faces write into the next row / the margin planes. */
+/*   contract = 1 fuses a*b + c the way nvcc -fmad=true does for these        */
+/*   expressions; contract = 0 keeps every operation separate.                */
+/* ------------------------------------------------------------------------- */
+enum { L_C, L_N, L_S, L_E, L_W, L_T, L_B, L_NE, L_NW, L_SE, L_SW, L_NT, L_NB, L_ST, L_SB, L_ET, L_EB, L_WT, L_WB,
+       L_FLAGS, L_ENTRIES };
+static const int lbm_dx[19] = {0, 0, 0, 1, -1, 0, 0, 1, -1, 1, -1, 0, 0, 0, 0, 1, 1, -1, -1};
+static const int lbm_dy[19] = {0, 1, -1, 0, 0, 0, 0, 1, 1, -1, -1, 1, 1, -1, -1, 0, 0, 0, 0};
+static const int lbm_dz[19] = {0, 0, 0, 0, 0, 1, -1, 0, 0, 0, 0, 1, -1, 1, -1, 1, -1, 1, -1};
+
+static inline float lbm_mad(float a, float b, float c, int contract) { return contract ? fmaf(a, b, c) : a * b + c; }
+
+/* temp2*f + temp1*(q*(4.5 q + sign 3) - u2) */
+static inline float lbm_relax(float f, float q, float sign3, float u2, float temp1, float temp2, int contract) {
+    float inner = lbm_mad(4.5f, q, sign3, contract);           /* 4.5 q + 3 */
+    float poly = lbm_mad(q, inner, -u2, contract);             /* q (..) - u2 */
+    float rhs = temp1 * poly;
+    return lbm_mad(temp2, f, rhs, contract);
+}
+
+TKO_API int tko_lbm_entries(void) { return L_ENTRIES; }
+
+TKO_API void tko_lbm_f32(const float *src, float *dst, int nx, int ny, int nz, int start, int end, int contract) {
+    const size_t cells = (size_t)nx * ny * nz;
+    const float OMEGA = 1.95f, DFL1 = 1.0f / 3.0f, DFL2 = 1.0f / 18.0f, DFL3 = 1.0f / 36.0f;
+    for (int p = start; p < end; p++) {
+        int y = p % ny, z = (p / ny) % nz;
+        for (int x = 0; x < nx; x++) {
+            ptrdiff_t cell = x + (ptrdiff_t)y * nx + (ptrdiff_t)z * nx * ny;
+            float f[19];
+            for (int e = 0; e < 19; e++) f[e] = src[e * cells + cell];
+            uint32_t flags = f32_bits(src[L_FLAGS * cells + cell]);
+            if (flags & 1u) {                                   /* obstacle: reflect */
+                float t;
+                t = f[L_N]; f[L_N] = f[L_S]; f[L_S] = t;
+                t = f[L_E]; f[L_E] = f[L_W]; f[L_W] = t;
+                t = f[L_T]; f[L_T] = f[L_B]; f[L_B] = t;
+                t = f[L_NE]; f[L_NE] = f[L_SW]; f[L_SW] = t;
+                t = f[L_NW]; f[L_NW] = f[L_SE]; f[L_SE] = t;
+                t = f[L_NT]; f[L_NT] = f[L_SB]; f[L_SB] = t;
+                t = f[L_NB]; f[L_NB] = f[L_ST]; f[L_ST] = t;
+                t = f[L_ET]; f[L_ET] = f[L_WB]; f[L_WB] = t;
+                t = f[L_EB]; f[L_EB] = f[L_WT]; f[L_WT] = t;
+            } else {
+                float rho = f[L_C] + f[L_N] + f[L_S] + f[L_E] + f[L_W] + f[L_T] + f[L_B] + f[L_NE] + f[L_NW] + f[L_SE] +
+                            f[L_SW] + f[L_NT] + f[L_NB] + f[L_ST] + f[L_SB] + f[L_ET] + f[L_EB] + f[L_WT] + f[L_WB];
+                float ux = +f[L_E] - f[L_W] + f[L_NE] - f[L_NW] + f[L_SE] - f[L_SW] + f[L_ET] + f[L_EB] - f[L_WT] - f[L_WB];
+                float uy = +f[L_N] - f[L_S] + f[L_NE] + f[L_NW] - f[L_SE] - f[L_SW] + f[L_NT] + f[L_NB] - f[L_ST] - f[L_SB];
+                float uz = +f[L_T] - f[L_B] + f[L_NT] - f[L_NB] + f[L_ST] - f[L_SB] + f[L_ET] - f[L_EB] + f[L_WT] - f[L_WB];
+                ux /= rho; uy /= rho; uz /= rho;
+                if (flags & 2u) { ux = 0.005f; uy = 0.002f; uz = 0.000f; }
+                /* 1.5 (ux ux + uy uy + uz uz) - 1 */
+                float sq = lbm_mad(uz, uz, lbm_mad(uy, uy, ux * ux, contract), contract);
+                float u2 = lbm_mad(1.5f, sq, -1.0f, contract);
+                float base = OMEGA * rho, temp2 = 1.0f - OMEGA;
+                float temp1 = DFL1 * base;
+                f[L_C] = lbm_mad(temp2, f[L_C], temp1 * (-u2), contract);
+                temp1 = DFL2 * base;
+                f[L_N] = lbm_relax(f[L_N], uy, 3.0f, u2, temp1, temp2, contract);
+                f[L_S] = lbm_relax(f[L_S], uy, -3.0f, u2, temp1, temp2, contract);
+                f[L_T] = lbm_relax(f[L_T], uz, 3.0f, u2, temp1, temp2, contract);
+                f[L_B] = lbm_relax(f[L_B], uz, -3.0f, u2, temp1, temp2, contract);
+                f[L_E] = lbm_relax(f[L_E], ux, 3.0f, u2, temp1, temp2, contract);
+                f[L_W] = lbm_relax(f[L_W], ux, -3.0f, u2, temp1, temp2, contract);
+                temp1 = DFL3 * base;
+                f[L_NT] = lbm_relax(f[L_NT], +uy + uz, 3.0f, u2, temp1, temp2, contract);
+                f[L_NB] = lbm_relax(f[L_NB], +uy - uz, 3.0f, u2, temp1, temp2, contract);
+                f[L_ST] = lbm_relax(f[L_ST], -uy + uz, 3.0f, u2, temp1, temp2, contract);
+                f[L_SB] = lbm_relax(f[L_SB], -uy - uz, 3.0f, u2, temp1, temp2, contract);
+                f[L_NE] = lbm_relax(f[L_NE], +ux + uy, 3.0f, u2, temp1, temp2, contract);
+                f[L_SE] = lbm_relax(f[L_SE], +ux - uy, 3.0f, u2, temp1, temp2, contract);
+                f[L_ET] = lbm_relax(f[L_ET], +ux + uz, 3.0f, u2, temp1, temp2, contract);
+                f[L_EB] = lbm_relax(f[L_EB], +ux - uz, 3.0f, u2, temp1, temp2, contract);
+                f[L_NW] = lbm_relax(f[L_NW], -ux + uy, 3.0f, u2, temp1, temp2, contract);
+                f[L_SW] = lbm_relax(f[L_SW], -ux - uy, 3.0f, u2, temp1, temp2, contract);
+                f[L_WT] = lbm_relax(f[L_WT], -ux + uz, 3.0f, u2, temp1, temp2, contract);
+                f[L_WB] = lbm_relax(f[L_WB], -ux - uz, 3.0f, u2, temp1, temp2, contract);
+            }
+            for (int e = 0; e < 19; e++)
+                dst[(ptrdiff_t)(e * cells) + cell + lbm_dx[e] + (ptrdiff_t)lbm_dy[e] * nx + (ptrdiff_t)lbm_dz[e] * nx * ny] = f[e];
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* fft: batches of 256-point complex transforms, radix-2 Stockham             */
+/* reference: src/gptb_kernel/fft_kernel.cu:3-80, src/header/fft_header.h     */
+/*   thread j of 128 holds points j and j + 128; in pass Ns = 1, 2, .., 128   */
+/*   point 1 is multiplied by (cos a, sin a), a = float(-2 pi (j % Ns)/(2 Ns))*/
+/*   (the quotient in binary64), the pair is replaced by (sum, difference)    */
+/*   and written to expand(j, Ns, 2) + r Ns; the next pass reads j, j + 128.  */
+/*   The complex product is (a.x b.x - a.y b.y, a.x b.y + a.y b.x); contract  */
+/*   = 1 fuses each as fma(a, b, +-(c d)).  Point 0 is multiplied by (1, 0)   */
+/*   like every other, which only matters for signed zeros.                   */
+/* ------------------------------------------------------------------------- */
+#define TKO_FFT_N 256
+
+TKO_API void tko_fft256_f32(float *data, int nfft, int start, int end, int contract) {
+#pragma omp parallel for schedule(static)
+    for (int p = start; p < end; p++) {
+        float *d = data + 2 * (size_t)TKO_FFT_N * (p % nfft);
+        float a[2 * TKO_FFT_N], b[2 * TKO_FFT_N];
+        memcpy(a, d, sizeof(a));
+        for (int Ns = 1; Ns < TKO_FFT_N; Ns *= 2) {
+            for (int j = 0; j < TKO_FFT_N / 2; j++) {
+                float angle = (float)(-2.0 * M_PI * (double)(j % Ns) / (double)(Ns * 2));
+                float wr = cosf(1.0f * angle), wi = sinf(1.0f * angle);
+                float x0r = a[2 * j], x0i = a[2 * j + 1];
+                float x1r = a[2 * (j + 128)], x1i = a[2 * (j + 128) + 1];
+                float tr, ti;
+                if (contract) { tr = fmaf(x1r, wr, -(x1i * wi)); ti = fmaf(x1r, wi, x1i * wr); }
+                else { tr = x1r * wr - x1i * wi; ti = x1r * wi + x1i * wr; }
+                int idx = (j / Ns) * Ns * 2 + (j % Ns);
+                b[2 * idx] = x0r + tr; b[2 * idx + 1] = x0i + ti;
+                b[2 * (idx + Ns)] = x0r - tr; b[2 * (idx + Ns) + 1] = x0i - ti;
+            }
+            memcpy(a, b, sizeof(a));
+        }
+        memcpy(d, a, sizeof(a));
+    }
+}
+
+/* binary64 transform of the same input (error budget) */
+TKO_API void tko_fft256_f64(const float *data, double *out, int nfft) {
+#pragma omp parallel for schedule(static)
+    for (int p = 0; p < nfft; p++) {
+        const float *d = data + 2 * (size_t)TKO_FFT_N * p;
+        double *o = out + 2 * (size_t)TKO_FFT_N * p;
+        for (int k = 0; k < TKO_FFT_N; k++) {
+            double sr = 0.0, si = 0.0;
+            for (int n = 0; n < TKO_FFT_N; n++) {
+                double ang = -2.0 * M_PI * (double)((k * n) % TKO_FFT_N) / TKO_FFT_N;
+                double c = cos(ang), s = sin(ang);
+                sr += d[2 * n] * c - d[2 * n + 1] * s;
+                si += d[2 * n] * s + d[2 * n + 1] * c;
+            }
+            o[2 * k] = sr; o[2 * k + 1] = si;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* cutcp: cutoff Coulomb potential on a lattice, atoms in spatial bins        */
+/* reference: src/gptb_kernel/cutcp_kernel.cu:12-183 (kernel),                */
+/*   src/header/cutcp_header.h:106-300 (binning and neighbour list).          */
+/*   bins of 4 A hold up to 8 atoms {x, y, z, q} (q = 0 ends a bin); a region */
+/*   of 8 x 8 x 8 lattice points visits the bins at its centre bin + every    */
+/*   offset of the neighbour list, in list order, atoms in bin order, and     */
+/*   adds q * rsqrt(r2) * (1 - r2 / cutoff2)^2 where r2 < cutoff2.  Region    */
+/*   (x, y, z) of the (gx, gy, gz) grid is block (x * gy + y) * gz + z and    */
+/*   lies at ((z * gy + y) * gx + x) * 512, points ordered [z][y][x].         */
+/* ------------------------------------------------------------------------- */
+#define TKO_CUTCP_BIN_DEPTH 8
+#define TKO_CUTCP_BIN_LEN 4.0f
+#define TKO_CUTCP_NBR_DIM 11
+
+/* the neighbour offsets for lattice spacing h and a cutoff; returns their number (0 on unsupported h / cutoff) */
+TKO_API int tko_cutcp_neighbours(float h, float cutoff, int *nbr_xyz) {
+    const float inv = 1.f / TKO_CUTCP_BIN_LEN;
+    int c = (int)ceil(cutoff * inv), cnt = 0;
+    float s, r2;
+    if (ceilf(TKO_CUTCP_BIN_LEN / (8 * h)) == floorf(TKO_CUTCP_BIN_LEN / (8 * h))) {
+        s = sqrtf(3);
+        if (2 * c + 1 > TKO_CUTCP_NBR_DIM) return 0;
+    } else if (8 * h <= 2 * TKO_CUTCP_BIN_LEN) {
+        s = 2.f * sqrtf(3);
+        if (2 * c + 3 > TKO_CUTCP_NBR_DIM) return 0;
+    } else {
+        return 0;
+    }
+    r2 = (cutoff + s * TKO_CUTCP_BIN_LEN) * (cutoff + s * TKO_CUTCP_BIN_LEN);
+    for (int k = -c; k <= c; k++)
+        for (int j = -c; j <= c; j++)
+            for (int i = -c; i <= c; i++) {
+                if ((i * i + j * j + k * k) * TKO_CUTCP_BIN_LEN * TKO_CUTCP_BIN_LEN >= r2) continue;
+                nbr_xyz[3 * cnt] = i; nbr_xyz[3 * cnt + 1] = j; nbr_xyz[3 * cnt + 2] = k;
+                cnt++;
+            }
+    return cnt;
+}
+
+/* bin dimensions {x, y, z, margin c} for a lattice of nx x ny x nz points */
+TKO_API void tko_cutcp_bin_dims(int nx, int ny, int nz, float h, float cutoff, int out[4]) {
+    const float inv = 1.f / TKO_CUTCP_BIN_LEN;
+    int c = (int)ceil(cutoff * inv);
+    int lnx = 8 * (int)ceilf(nx / 8.f), lny = 8 * (int)ceilf(ny / 8.f), lnz = 8 * (int)ceilf(nz / 8.f);
+    out[0] = (int)ceil(lnx * h * inv) + 2 * c;
+    out[1] = (int)ceil(lny * h * inv) + 2 * c;
+    out[2] = (int)ceil(lnz * h * inv) + 2 * c;
+    out[3] = c;
+}
+
+/* geometric hashing of the atoms into bins (bins zeroed by the caller); returns the atoms that found no room */
+TKO_API int tko_cutcp_bin_atoms(const float *atoms_xyzq, int natoms, const int dims[4], float *bins) {
+    const float inv = 1.f / TKO_CUTCP_BIN_LEN;
+    const int bx = dims[0], by = dims[1], bz = dims[2], c = dims[3];
+    int *count = (int *)calloc((size_t)bx * by * bz, sizeof(int));
+    int extra = 0;
+    for (int n = 0; n < natoms; n++) {
+        const float *a = atoms_xyzq + 4 * (size_t)n;
+        int i = (int)floorf(a[0] * inv), j = (int)floorf(a[1] * inv), k = (int)floorf(a[2] * inv);
+        if (i >= -c && i < bx - c && j >= -c && j < by - c && k >= -c && k < bz - c && a[3] != 0) {
+            size_t index = ((size_t)(k + c) * by + (j + c)) * bx + (i + c);
+            if (count[index] < TKO_CUTCP_BIN_DEPTH) {
+                memcpy(bins + 4 * (index * TKO_CUTCP_BIN_DEPTH + count[index]), a, 4 * sizeof(float));
+                count[index]++;
+            } else {
+                extra++;
+            }
+        }
+    }
+    free(count);
+    return extra;
+}
+
+TKO_API void tko_cutcp_f32(const float *bins, const int dims[4], const int *nbr_xyz, int nbrlen, float h, float cutoff2,
+                           float inv_cutoff2, float *regions, int gx, int gy, int gz, int start, int end, int contract) {
+    const float inv = 1.f / TKO_CUTCP_BIN_LEN;
+    const int bx = dims[0], by = dims[1], c = dims[3];
+#pragma omp parallel for schedule(dynamic)
+    for (int p = start; p < end; p++) {
+        int rx = p / (gy * gz), ry = (p / gz) % gy, rz = p % gz;
+        float *region = regions + (((size_t)rz * gy + ry) * gx + rx) * 512;
+        int cx = (int)floorf((8 * rx + 4) * h * inv), cy = (int)floorf((8 * ry + 4) * h * inv),
+            cz = (int)floorf((8 * rz + 4) * h * inv);
+        for (int tz = 0; tz < 8; tz++)
+            for (int ty = 0; ty < 2; ty++)
+                for (int tx = 0; tx < 8; tx++) {
+                    float x = (8 * rx + tx) * h, y = (8 * ry + ty) * h, z = (8 * rz + tz) * h;
+                    float e[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int nb = 0; nb < nbrlen; nb++) {
+                        int i = cx + nbr_xyz[3 * nb] + c, j = cy + nbr_xyz[3 * nb + 1] + c, k = cz + nbr_xyz[3 * nb + 2] + c;
+                        const float *bin = bins + 4 * ((((size_t)k * by + j) * bx + i) * TKO_CUTCP_BIN_DEPTH);
+                        for (int a = 0; a < TKO_CUTCP_BIN_DEPTH; a++) {
+                            float aq = bin[4 * a + 3];
+                            if (aq == 0.f) break;
+                            float dx = bin[4 * a] - x, dz = bin[4 * a + 2] - z;
+                            float dxdz2 = contract ? fmaf(dx, dx, dz * dz) : dx * dx + dz * dz;
+                            float dy = bin[4 * a + 1] - y;
+                            for (int q = 0; q < 4; q++) {
+                                float r2 = contract ? fmaf(dy, dy, dxdz2) : dy * dy + dxdz2;
+                                if (r2 < cutoff2) {
+                                    float s = contract ? fmaf(-r2, inv_cutoff2, 1.f) : 1.f - r2 * inv_cutoff2;
+                                    float t = aq * (1.0f / sqrtf(r2)) * s;
+                                    e[q] = contract ? fmaf(t, s, e[q]) : e[q] + t * s;
+                                }
+                                dy = contract ? fmaf(-2.0f, h, dy) : dy - 2.0f * h;
+                            }
+                        }
+                    }
+                    for (int q = 0; q < 4; q++) region[tz * 64 + q * 16 + ty * 8 + tx] = e[q];
+                }
+    }
 }
 
 /* ------------------------------------------------------------------------- */

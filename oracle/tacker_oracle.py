@@ -293,6 +293,93 @@ def im2col_f32(im, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h=1, dil_w=1) -
     return col
 
 
+# ------------------------------------------------------------------ sgemm ----
+def sgemm_grid(M: int, N: int):
+    return M // 128, N // 16
+
+
+def sgemm_f32(A_km, B_kn, C_nm, start=0, end=None) -> np.ndarray:
+    """C = 2 C + 2 A B in place; A_km [K][M], B_kn [K][N], C_nm [N][M] (the reference's layouts)."""
+    K, M = A_km.shape
+    N = B_kn.shape[1]
+    gx, gy = sgemm_grid(M, N)
+    if end is None:
+        end = gx * gy
+    lib().tko_sgemm_f32(_p(_c32(A_km), _f32p), _p(_c32(B_kn), _f32p), _p(C_nm, _f32p), M, N, K, start, end)
+    return C_nm
+
+
+# -------------------------------------------------------------------- lbm ----
+LBM_ENTRIES = 20
+
+
+def lbm_margin(nx: int, ny: int) -> int:
+    """floats in front of (and behind) the grid: two z-planes (src/header/lbm_header.h:246, REAL_MARGIN)"""
+    return 2 * nx * ny
+
+
+def lbm_f32(src_full, dst_full, nx, ny, nz, start=0, end=None, contract=1) -> np.ndarray:
+    """One time step.  src_full / dst_full: flat arrays of margin + 20 nx ny nz + margin floats."""
+    if end is None:
+        end = ny * nz
+    m = lbm_margin(nx, ny)
+    assert src_full.size == dst_full.size == 2 * m + LBM_ENTRIES * nx * ny * nz and dst_full.dtype == np.float32
+    src_full = _c32(src_full)
+    lib().tko_lbm_f32(_p(src_full[m:], _f32p), _p(dst_full[m:], _f32p), nx, ny, nz, start, end, contract)
+    return dst_full
+
+
+# -------------------------------------------------------------------- fft ----
+def fft256_f32(data, start=0, end=None, contract=1) -> np.ndarray:
+    """data: [nfft][256][2] float32, transformed in place."""
+    nfft = data.shape[0]
+    if end is None:
+        end = nfft
+    assert data.dtype == np.float32 and data.flags.c_contiguous and data.shape[1:] == (256, 2)
+    lib().tko_fft256_f32(_p(data, _f32p), nfft, start, end, contract)
+    return data
+
+
+def fft256_f64(data) -> np.ndarray:
+    data = _c32(data)
+    out = np.empty(data.shape, dtype=np.float64)
+    lib().tko_fft256_f64(_p(data, _f32p), _p(out, _f64p), data.shape[0])
+    return out
+
+
+# ------------------------------------------------------------------ cutcp ----
+def cutcp_neighbours(h: float, cutoff: float) -> np.ndarray:
+    nbr = np.zeros((11 * 11 * 11, 3), dtype=np.int32)
+    n = lib().tko_cutcp_neighbours(C.c_float(h), C.c_float(cutoff), _p(nbr, _i32p))
+    return np.ascontiguousarray(nbr[:n])
+
+
+def cutcp_bin_dims(nx, ny, nz, h, cutoff):
+    out = (C.c_int * 4)()
+    lib().tko_cutcp_bin_dims(nx, ny, nz, C.c_float(h), C.c_float(cutoff), out)
+    return tuple(out)
+
+
+def cutcp_bin_atoms(atoms_xyzq, dims):
+    """bins [bz][by][bx][8][4] (margin bins included) and the number of atoms that found no room"""
+    atoms_xyzq = _c32(atoms_xyzq)
+    bins = np.zeros((dims[2], dims[1], dims[0], 8, 4), dtype=np.float32)
+    extra = lib().tko_cutcp_bin_atoms(_p(atoms_xyzq, _f32p), atoms_xyzq.shape[0], (C.c_int * 4)(*dims), _p(bins, _f32p))
+    return bins, int(extra)
+
+
+def cutcp_f32(bins, dims, nbr, h, cutoff, regions, gx, gy, gz, start=0, end=None, contract=1) -> np.ndarray:
+    """regions: [gz][gy][gx][512] float32, overwritten for the blocks of [start, end)"""
+    if end is None:
+        end = gx * gy * gz
+    nbr = np.ascontiguousarray(nbr, dtype=np.int32)
+    cutoff2 = np.float32(cutoff) * np.float32(cutoff)
+    lib().tko_cutcp_f32(_p(_c32(bins), _f32p), (C.c_int * 4)(*dims), _p(nbr, _i32p), nbr.shape[0], C.c_float(h),
+                        C.c_float(cutoff2), C.c_float(np.float32(1.0) / cutoff2), _p(regions, _f32p), gx, gy, gz, start, end,
+                        contract)
+    return regions
+
+
 # ------------------------------------------------------------ comparisons ----
 def bit_mismatches(a, b) -> int:
     a, b = _c32(a).ravel(), _c32(b).ravel()

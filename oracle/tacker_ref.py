@@ -98,3 +98,57 @@ def mriq_launch(numK, x, y, z, Qr, Qi, gx, start, end, grid, stream=0) -> int:
 def mix_mriq(numK, x, y, z, Qr, Qi, gx, cd_start, cd_end, A, B, Cm, M, N, K, tz_start, tz_end, grid, stream=0) -> int:
     return lib().ref_mix_mriq(numK, _vp(x), _vp(y), _vp(z), _vp(Qr), _vp(Qi), gx, cd_start, cd_end, _vp(A), _vp(B),
                               _vp(Cm), M, N, K, tz_start, tz_end, grid, _vp(stream))
+
+
+# ---- sgemm, lbm, fft, cutcp (oracle/_ref/libtacker_ref_more.so) ----------------------------------------------
+LIB_MORE_PATH = os.path.join(_HERE, "_ref", "libtacker_ref_more.so")
+_lib_more = None
+
+
+def more_available() -> bool:
+    return os.path.exists(LIB_MORE_PATH)
+
+
+def lib_more() -> C.CDLL:
+    global _lib_more
+    if _lib_more is None:
+        _lib_more = C.CDLL(LIB_MORE_PATH)
+    return _lib_more
+
+
+def sgemm(A, B, Cm, M, N, K, start, end, grid, stream=0) -> int:
+    return lib_more().ref_sgemm(_vp(A), _vp(B), _vp(Cm), M, N, K, start, end, grid, _vp(stream))
+
+
+def lbm_dims():
+    out = (C.c_int * 4)()
+    lib_more().ref_lbm_dims(out)
+    return tuple(out)
+
+
+def lbm(src, dst, start, end, grid, stream=0) -> int:
+    return lib_more().ref_lbm(_vp(src), _vp(dst), start, end, grid, _vp(stream))
+
+
+def fft(data, nfft, start, end, grid, stream=0) -> int:
+    return lib_more().ref_fft(_vp(data), nfft, start, end, grid, _vp(stream))
+
+
+def cutcp_prepare(atoms_xyzq: np.ndarray, nx, ny, nz, h, cutoff, nbins_cap=65536):
+    """The reference's own binning: (bins [nbins_cap][8][4] from the base address, neighbour offsets [1331][3], dims)."""
+    atoms_xyzq = np.ascontiguousarray(atoms_xyzq, dtype=np.float32)
+    bins = np.zeros((nbins_cap, 8, 4), dtype=np.float32)
+    nbr = np.zeros((11 * 11 * 11, 3), dtype=np.int32)
+    dims = (C.c_int * 5)()
+    rc = lib_more().ref_cutcp_prepare(_f32p(atoms_xyzq), atoms_xyzq.shape[0], nx, ny, nz, C.c_float(h), C.c_float(cutoff),
+                                      _f32p(bins), nbins_cap, nbr.ctypes.data_as(C.POINTER(C.c_int)), dims)
+    assert rc == 0, rc
+    return bins, nbr, tuple(dims)
+
+
+def cutcp(nbr_host: np.ndarray, bx, by, c, bins_dev, h, cutoff2, inv_cutoff2, regions_dev, gx, gy, gz, start, end, grid,
+          stream=0) -> int:
+    nbr_host = np.ascontiguousarray(nbr_host, dtype=np.int32)
+    return lib_more().ref_cutcp(nbr_host.ctypes.data_as(C.POINTER(C.c_int)), nbr_host.shape[0], bx, by, c, _vp(bins_dev),
+                                C.c_float(h), C.c_float(cutoff2), C.c_float(inv_cutoff2), _vp(regions_dev), gx, gy, gz,
+                                start, end, grid, _vp(stream))

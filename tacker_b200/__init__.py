@@ -25,7 +25,10 @@ LAUNCH_FN = C.CFUNCTYPE(C.c_int, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_u
 
 KEYS = ("gptb_tzgemm", "gptb_tzgemm_acc", "gptb_stencil", "gptb_cp", "gptb_mriq", "gptb_mrif", "tzgemm_stencil",
         "tzgemm_cp", "tzgemm_mriq", "tzgemm_mrif", "ori_stencil", "ori_cp", "ori_mriq", "ori_mrif", "gptb_tzconv",
-        "tzconv_stencil", "tzconv_cp", "tzconv_mriq", "tzconv_mrif")
+        "tzconv_stencil", "tzconv_cp", "tzconv_mriq", "tzconv_mrif",
+        "gptb_sgemm", "tzgemm_sgemm", "ori_sgemm", "gptb_lbm", "tzgemm_lbm", "ori_lbm",
+        "gptb_fft", "tzgemm_fft", "ori_fft", "gptb_cutcp", "tzgemm_cutcp", "ori_cutcp",
+        "tzconv_sgemm", "tzconv_lbm", "tzconv_fft", "tzconv_cutcp")
 
 
 class TackerError(RuntimeError):

@@ -1,0 +1,388 @@
+// Kernels and launchers of the sgemm / lbm / fft / cutcp roles (cd_roles_more.cuh): one solo kernel each and one
+// fused kernel each with tzgemm as the tensor role.  Included by tacker_b200.cu after host_launch.cuh.
+#pragma once
+#include "cd_roles_more.cuh"
+#include "host_launch.cuh"
+
+namespace tk {
+
+// -------------------------------------------------------------------------------------------------
+// solo kernels
+// -------------------------------------------------------------------------------------------------
+// 16 warps of 32 accumulators per lane with a ring of S slots each: one CTA per SM
+template <int S>
+__global__ void __launch_bounds__(512, 1) sgemm_kernel(const SgemmArgs g) {
+    extern __shared__ __align__(16) uint8_t more_smem[];
+    sgemm_role<S>(g, more_smem, threadIdx.x >> 5, blockDim.x >> 5, threadIdx.x & 31, blockIdx.x, gridDim.x);
+}
+
+__global__ void __launch_bounds__(512, 2) lbm_kernel(const LbmArgs g) {
+    __shared__ int item_counter;
+    if (threadIdx.x == 0) item_counter = 0;
+    __syncthreads();
+    lbm_role(g, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+}
+
+__global__ void __launch_bounds__(512, 2) fft_kernel(const FftArgs g) {
+    extern __shared__ __align__(16) uint8_t more_smem[];
+    fft_role(g, more_smem, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x, 0);
+}
+
+__global__ void __launch_bounds__(512, 2) cutcp_kernel(const CutcpArgs g) {
+    __shared__ int item_counter;
+    if (threadIdx.x == 0) item_counter = 0;
+    __syncthreads();
+    cutcp_role(g, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+}
+
+// {dx, dy, dz} triples -> the int4 table the cutcp role reads
+__global__ void cutcp_pack_nbr_kernel(const int* __restrict__ xyz, int n, int4* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = make_int4(xyz[3 * i], xyz[3 * i + 1], xyz[3 * i + 2], 0);
+}
+
+// -------------------------------------------------------------------------------------------------
+// fused kernels: warps 0..5 the tensor role (128-wide super-tiles, 4 stages: 146 KB; CONV = the implicit-GEMM
+// convolution), the remaining warps the CUDA-core role, whose shared memory (sgemm rings, FFT buffers) lies behind it
+// -------------------------------------------------------------------------------------------------
+constexpr int kMoreBN = 128, kMoreStages = 4;
+constexpr int kMaxMixThreadsSgemm = 576;  // 192 + 12 warps at up to 113 registers
+constexpr int kSgemmSlotsSolo = 4;
+
+template <int S, bool CONV = false>
+__global__ void __launch_bounds__(kMaxMixThreadsSgemm, 1)
+mix_sgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
+                 const SgemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    uint8_t* smem = align_smem_1024(smem_raw);
+    if (warp < kGemmWarps) {
+        gemm_role<kMoreBN, kMoreStages, true, CONV>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31);
+    } else {
+        sgemm_role<S>(a, smem + GemmSmem<kMoreBN, kMoreStages>::kBytes, warp - kGemmWarps, (blockDim.x >> 5) - kGemmWarps,
+                   threadIdx.x & 31, blockIdx.x, gridDim.x);
+    }
+}
+
+template <bool CONV = false>
+__global__ void __launch_bounds__(kMaxMixThreadsSfu, 1)
+mix_lbm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
+               const LbmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role<kMoreBN, kMoreStages, true, CONV>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
+    } else {
+        cd_role_begin(&item_counter);
+        lbm_role(a, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    }
+}
+
+template <bool CONV = false>
+__global__ void __launch_bounds__(kMaxMixThreadsSfu, 1)
+mix_fft_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
+               const FftArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    uint8_t* smem = align_smem_1024(smem_raw);
+    if (warp < kGemmWarps) {
+        gemm_role<kMoreBN, kMoreStages, true, CONV>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31);
+    } else {
+        fft_role(a, smem + GemmSmem<kMoreBN, kMoreStages>::kBytes, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads,
+                 blockIdx.x, gridDim.x, kCdBarrierId);
+    }
+}
+
+template <bool CONV = false>
+__global__ void __launch_bounds__(kMaxMixThreadsSfu, 1)
+mix_cutcp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
+                 const CutcpArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role<kMoreBN, kMoreStages, true, CONV>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31);
+    } else {
+        cd_role_begin(&item_counter);
+        cutcp_role(a, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// argument parsing (reference argument order; p = the CUDA-core list, geometry ints at n_solo .. n_solo + 5)
+// -------------------------------------------------------------------------------------------------
+static bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+
+// sgemm: A, B, C, M, N, K (src/gptb_kernel/sgemm_kernel.cu:3-5)
+static int parse_sgemm(void** p, int i_start, int i_end, SgemmArgs* g) {
+    g->A = arg<const float*>(p, 0);
+    g->B = arg<const float*>(p, 1);
+    g->C = arg<float*>(p, 2);
+    g->M = arg<int>(p, 3);
+    g->N = arg<int>(p, 4);
+    g->K = arg<int>(p, 5);
+    g->gx = arg<int>(p, 6);
+    g->gy = arg<int>(p, 7);
+    const int bdx = arg<int>(p, 9), bdy = arg<int>(p, 10);
+    g->start = arg<int>(p, i_start);
+    g->end = arg<int>(p, i_end);
+    if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->start < 0) return TK_ERR_ARGS;
+    if (g->M % 128 || g->N % 16) return TK_ERR_SHAPE;
+    if (g->gx != g->M / 128 || g->gy != g->N / 16 || bdx != 16 || bdy != 8) return TK_ERR_SHAPE;
+    if (g->end > g->gx * g->gy) g->end = g->gx * g->gy;
+    if (g->start < g->end && (!g->A || !g->B || !g->C)) return TK_ERR_ARGS;
+    if (misaligned16(g->A) || misaligned16(g->B) || misaligned16(g->C)) return TK_ERR_ALIGN;
+    return TK_OK;
+}
+
+// lbm: srcGrid, dstGrid; the grid is (ny, nz), the block nx threads (src/ori_kernel/lbm_kernel.cu:209-213)
+static int parse_lbm(void** p, int i_start, int i_end, LbmArgs* g) {
+    g->src = arg<const float*>(p, 0);
+    g->dst = arg<float*>(p, 1);
+    g->ny = arg<int>(p, 2);
+    g->nz = arg<int>(p, 3);
+    g->nx = arg<int>(p, 5);
+    g->start = arg<int>(p, i_start);
+    g->end = arg<int>(p, i_end);
+    if (g->nx <= 0 || g->ny <= 0 || g->nz <= 0 || g->start < 0) return TK_ERR_ARGS;
+    if (g->nx % 32) return TK_ERR_SHAPE;
+    if (g->end > g->ny * g->nz) g->end = g->ny * g->nz;
+    if (g->start < g->end && (!g->src || !g->dst)) return TK_ERR_ARGS;
+    if ((reinterpret_cast<uintptr_t>(g->src) & 3u) || (reinterpret_cast<uintptr_t>(g->dst) & 3u)) return TK_ERR_ALIGN;
+    return TK_OK;
+}
+
+// fft: data; the grid is the batch, the block 128 threads (src/ori_kernel/fft_kernel.cu:107-110)
+static int parse_fft(void** p, int i_start, int i_end, FftArgs* g) {
+    g->data = arg<float2*>(p, 0);
+    g->nfft = arg<int>(p, 1);
+    const int bdx = arg<int>(p, 4);
+    g->start = arg<int>(p, i_start);
+    g->end = arg<int>(p, i_end);
+    if (g->nfft <= 0 || g->start < 0) return TK_ERR_ARGS;
+    if (bdx != 128) return TK_ERR_SHAPE;
+    if (g->end > g->nfft) g->end = g->nfft;
+    if (g->start < g->end && !g->data) return TK_ERR_ARGS;
+    if (reinterpret_cast<uintptr_t>(g->data) & 7u) return TK_ERR_ALIGN;
+    return TK_OK;
+}
+
+// cutcp: binDim_x, binDim_y, binZeroAddr, h, cutoff2, inv_cutoff2, regionZeroAddr, zRegionIndex_t
+// (src/gptb_kernel/cutcp_kernel.cu:12-31), then the neighbour table and its length, which the reference keeps in
+// __constant__ symbols (src/ori_kernel/cutcp_kernel.cu:12-13); the grid is the regions, the block (8, 2, 8)
+static int parse_cutcp(void** p, int i_start, int i_end, CutcpArgs* g) {
+    g->bin_dim_x = arg<int>(p, 0);
+    g->bin_dim_y = arg<int>(p, 1);
+    g->bins = arg<const float4*>(p, 2);
+    g->h = arg<float>(p, 3);
+    g->cutoff2 = arg<float>(p, 4);
+    g->inv_cutoff2 = arg<float>(p, 5);
+    g->regions = arg<float*>(p, 6);
+    g->nbr = arg<const int4*>(p, 8);
+    g->nbrlen = arg<int>(p, 9);
+    g->gx = arg<int>(p, 10);
+    g->gy = arg<int>(p, 11);
+    g->gz = arg<int>(p, 12);
+    const int bdx = arg<int>(p, 13), bdy = arg<int>(p, 14), bdz = arg<int>(p, 15);
+    g->start = arg<int>(p, i_start);
+    g->end = arg<int>(p, i_end);
+    if (g->bin_dim_x <= 0 || g->bin_dim_y <= 0 || g->gx <= 0 || g->gy <= 0 || g->gz <= 0 || g->nbrlen < 0 || g->start < 0)
+        return TK_ERR_ARGS;
+    if (bdx != 8 || bdy != 2 || bdz != 8) return TK_ERR_SHAPE;
+    if (g->end > g->gx * g->gy * g->gz) g->end = g->gx * g->gy * g->gz;
+    if (g->start < g->end && (!g->bins || !g->regions || (g->nbrlen > 0 && !g->nbr))) return TK_ERR_ARGS;
+    if (misaligned16(g->bins) || misaligned16(g->nbr) || (reinterpret_cast<uintptr_t>(g->regions) & 3u)) return TK_ERR_ALIGN;
+    return TK_OK;
+}
+
+// -------------------------------------------------------------------------------------------------
+// solo launches
+// -------------------------------------------------------------------------------------------------
+static int run_sgemm(const SgemmArgs& g, unsigned grid0, unsigned block0, cudaStream_t st) {
+    if (g.start >= g.end) return TK_OK;
+    const unsigned threads = cd_threads(block0, 32, 512);
+    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    const int smem = sgemm_role_smem(static_cast<int>(threads / 32), kSgemmSlotsSolo);
+    int rc = enable_smem(sgemm_kernel<kSgemmSlotsSolo>, smem);
+    if (rc != TK_OK) return rc;
+    sgemm_kernel<kSgemmSlotsSolo><<<grid0, threads, smem, st>>>(g);
+    return launch_error("sgemm_kernel launch");
+}
+
+static int run_lbm(const LbmArgs& g, unsigned grid0, unsigned block0, cudaStream_t st) {
+    if (g.start >= g.end) return TK_OK;
+    const unsigned threads = cd_threads(block0, 32, 512);
+    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    lbm_kernel<<<grid0, threads, 0, st>>>(g);
+    return launch_error("lbm_kernel launch");
+}
+
+static int run_fft(const FftArgs& g, unsigned grid0, unsigned block0, cudaStream_t st) {
+    if (g.start >= g.end) return TK_OK;
+    const unsigned threads = cd_threads(block0, 32, 512);
+    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    fft_kernel<<<grid0, threads, fft_role_smem(static_cast<int>(threads / 32)), st>>>(g);
+    return launch_error("fft_kernel launch");
+}
+
+static int run_cutcp(const CutcpArgs& g, unsigned grid0, unsigned block0, cudaStream_t st) {
+    if (g.start >= g.end) return TK_OK;
+    const unsigned threads = cd_threads(block0, 32, 512);
+    if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    cutcp_kernel<<<grid0, threads, 0, st>>>(g);
+    return launch_error("cutcp_kernel launch");
+}
+
+// -------------------------------------------------------------------------------------------------
+// fused launches
+// -------------------------------------------------------------------------------------------------
+enum MoreKind { MORE_SGEMM, MORE_LBM, MORE_FFT, MORE_CUTCP };
+
+struct MoreCall {
+    MoreKind kind;
+    SgemmArgs sg;
+    LbmArgs lb;
+    FftArgs ff;
+    CutcpArgs cc;
+    bool empty() const {
+        switch (kind) {
+            case MORE_SGEMM: return sg.start >= sg.end;
+            case MORE_LBM: return lb.start >= lb.end;
+            case MORE_FFT: return ff.start >= ff.end;
+            default: return cc.start >= cc.end;
+        }
+    }
+};
+
+static int run_more_solo(const MoreCall& m, unsigned grid0, unsigned threads, cudaStream_t st) {
+    switch (m.kind) {
+        case MORE_SGEMM: return run_sgemm(m.sg, grid0, threads, st);
+        case MORE_LBM: return run_lbm(m.lb, grid0, threads, st);
+        case MORE_FFT: return run_fft(m.ff, grid0, threads, st);
+        default: return run_cutcp(m.cc, grid0, threads, st);
+    }
+}
+
+template <bool CONV>
+static int launch_mix_more_kernels(const GemmCall& c, const MoreCall& m, const CUtensorMap& ta, const CUtensorMap& tb,
+                                   unsigned ctas, unsigned threads, unsigned cdt, cudaStream_t st) {
+    constexpr int kGemmBytes = GemmSmem<kMoreBN, kMoreStages>::kBytes + 1024;
+    int rc = TK_OK;
+    switch (m.kind) {
+        case MORE_SGEMM: {  // the deepest ring that fits behind the tensor role's stages
+            const int nw = static_cast<int>(cdt / 32), room = kMaxDynSmem - kGemmBytes;
+            if (sgemm_role_smem(nw, 4) <= room) {
+                const int smem = kGemmBytes + sgemm_role_smem(nw, 4);
+                if ((rc = enable_smem(mix_sgemm_kernel<4, CONV>, smem)) != TK_OK) return rc;
+                mix_sgemm_kernel<4, CONV><<<ctas, threads, smem, st>>>(ta, tb, c.g, m.sg);
+            } else if (sgemm_role_smem(nw, 3) <= room) {
+                const int smem = kGemmBytes + sgemm_role_smem(nw, 3);
+                if ((rc = enable_smem(mix_sgemm_kernel<3, CONV>, smem)) != TK_OK) return rc;
+                mix_sgemm_kernel<3, CONV><<<ctas, threads, smem, st>>>(ta, tb, c.g, m.sg);
+            } else {
+                const int smem = kGemmBytes + sgemm_role_smem(nw, 2);
+                if ((rc = enable_smem(mix_sgemm_kernel<2, CONV>, smem)) != TK_OK) return rc;
+                mix_sgemm_kernel<2, CONV><<<ctas, threads, smem, st>>>(ta, tb, c.g, m.sg);
+            }
+            break;
+        }
+        case MORE_LBM:
+            if ((rc = enable_smem(mix_lbm_kernel<CONV>, kGemmBytes)) != TK_OK) return rc;
+            mix_lbm_kernel<CONV><<<ctas, threads, kGemmBytes, st>>>(ta, tb, c.g, m.lb);
+            break;
+        case MORE_FFT: {
+            const int smem = kGemmBytes + fft_role_smem(static_cast<int>(cdt / 32));
+            if ((rc = enable_smem(mix_fft_kernel<CONV>, smem)) != TK_OK) return rc;
+            mix_fft_kernel<CONV><<<ctas, threads, smem, st>>>(ta, tb, c.g, m.ff);
+            break;
+        }
+        default:
+            if ((rc = enable_smem(mix_cutcp_kernel<CONV>, kGemmBytes)) != TK_OK) return rc;
+            mix_cutcp_kernel<CONV><<<ctas, threads, kGemmBytes, st>>>(ta, tb, c.g, m.cc);
+            break;
+    }
+    return launch_error("fused kernel launch");
+}
+
+static int run_mix_more(GemmCall& c, const MoreCall& m, unsigned grid0, unsigned block0, cudaStream_t st) {
+    DeviceInfo* d = nullptr;
+    int rc = device_info(&d);
+    if (rc != TK_OK) return rc;
+    c.g.status = d->status_ptr;
+    c.g.l2_hints = g_opt.l2_hints;
+    const bool gemm_empty = c.g.start >= c.g.end;
+    if (gemm_empty && m.empty()) return TK_OK;
+    if (block0 <= static_cast<unsigned>(kGemmThreads)) return TK_ERR_LAUNCH_CONFIG;
+    constexpr int kGemmBytes = GemmSmem<kMoreBN, kMoreStages>::kBytes + 1024;
+    unsigned cap = (m.kind == MORE_SGEMM ? kMaxMixThreadsSgemm : kMaxMixThreadsSfu) - kGemmThreads;
+    if (m.kind == MORE_SGEMM) {  // as many warps as find a ring of two slots behind the tensor role's stages
+        const unsigned fit = static_cast<unsigned>((kMaxDynSmem - kGemmBytes) / (2 * kSgemmSlotBytes)) * 32u;
+        if (fit < cap) cap = fit;
+    }
+    if (m.kind == MORE_FFT) {  // as many warps as find a buffer behind the tensor role's stages
+        const unsigned fit = static_cast<unsigned>((kMaxDynSmem - kGemmBytes - kFftTwiddleBytes) / kFftWarpBytes) * 32u;
+        if (fit < cap) cap = fit;
+    }
+    const unsigned cdt = cd_threads(block0 - kGemmThreads, 32, cap);
+    if (cdt == 0) return TK_ERR_LAUNCH_CONFIG;
+    if (gemm_empty) return run_more_solo(m, grid0, cdt, st);
+    if (m.empty()) return run_tzgemm(c, grid0, st);
+    const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
+    const unsigned threads = kGemmThreads + cdt;
+    CUtensorMap ta, tb;
+    if ((rc = make_tmap_a(&ta, c, kGemmBM)) != TK_OK) return rc;
+    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, kMoreBN)) != TK_OK) return rc;
+    if (c.conv) return launch_mix_more_kernels<true>(c, m, ta, tb, ctas, threads, cdt, st);
+    return launch_mix_more_kernels<false>(c, m, ta, tb, ctas, threads, cdt, st);
+}
+
+// number of solo arguments of each kind (before the six geometry ints)
+static int more_solo_args(MoreKind k) {
+    switch (k) {
+        case MORE_SGEMM: return 6;
+        case MORE_LBM: return 2;
+        case MORE_FFT: return 1;
+        default: return 10;
+    }
+}
+
+static int parse_more(MoreKind kind, void** params, MoreCall* m) {
+    const int n = more_solo_args(kind);
+    m->kind = kind;
+    switch (kind) {
+        case MORE_SGEMM: return parse_sgemm(params, n + 6, n + 8, &m->sg);
+        case MORE_LBM: return parse_lbm(params, n + 6, n + 8, &m->lb);
+        case MORE_FFT: return parse_fft(params, n + 6, n + 8, &m->ff);
+        default: return parse_cutcp(params, n + 6, n + 8, &m->cc);
+    }
+}
+
+// gptb_<kind>: solo list + 6 geometry ints + start, step, end, thread_base
+static int launch_more_gptb(MoreKind kind, void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                            void* stream) {
+    int rc = check_params(params, nparams, more_solo_args(kind) + 10);
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    MoreCall m;
+    if ((rc = parse_more(kind, params, &m)) != TK_OK) return rc;
+    return run_more_solo(m, grid[0], block[0], static_cast<cudaStream_t>(stream));
+}
+
+// tzgemm_<kind> / tzconv_<kind>: CUDA-core list (solo + 6 + 3), then tzgemm's (7 + 6 + 3) or tzconv's (12 + 6 + 3)
+static int launch_more_mix(MoreKind kind, void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                           void* stream, bool conv = false) {
+    const int cd_len = more_solo_args(kind) + 9;
+    int rc = check_params(params, nparams, cd_len + (conv ? 21 : 16));
+    if (rc != TK_OK) return rc;
+    if ((rc = validate_grid(grid, block)) != TK_OK) return rc;
+    MoreCall m;
+    if ((rc = parse_more(kind, params, &m)) != TK_OK) return rc;
+    GemmCall c;
+    if (conv) rc = parse_conv(params, cd_len, cd_len + 18, cd_len + 20, &c);
+    else rc = parse_gemm(params, cd_len, cd_len + 13, cd_len + 15, &c);
+    if (rc != TK_OK) return rc;
+    return run_mix_more(c, m, grid[0], block[0], static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace tk

@@ -1,5 +1,6 @@
 // libtacker_b200.so: the C-ABI entry points (see include/tacker_b200.h for the contract).
 #include "host_launch.cuh"
+#include "more_kernels.cuh"
 
 #define TK_API extern "C" __attribute__((visibility("default")))
 
@@ -247,6 +248,109 @@ TK_API int tk_launch_mix_tzconv_mrif(void** params, int nparams, const unsigned 
     return launch_mix_common(CD_MRIF, 8, params, nparams, grid, block, stream, true);
 }
 
+// ---- sgemm, lbm, fft, cutcp: persistent-block and fused launchers ----
+TK_API int tk_launch_gptb_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
+                                void* stream) {
+    return launch_more_gptb(MORE_SGEMM, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_gptb_lbm(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
+                              void* stream) {
+    return launch_more_gptb(MORE_LBM, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_gptb_fft(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
+                              void* stream) {
+    return launch_more_gptb(MORE_FFT, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_gptb_cutcp(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
+                                void* stream) {
+    return launch_more_gptb(MORE_CUTCP, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_mix_tzgemm_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                      unsigned, void* stream) {
+    return launch_more_mix(MORE_SGEMM, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_mix_tzgemm_lbm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                    unsigned, void* stream) {
+    return launch_more_mix(MORE_LBM, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_mix_tzgemm_fft(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                    unsigned, void* stream) {
+    return launch_more_mix(MORE_FFT, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_mix_tzgemm_cutcp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                      unsigned, void* stream) {
+    return launch_more_mix(MORE_CUTCP, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_mix_tzconv_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                      unsigned, void* stream) {
+    return launch_more_mix(MORE_SGEMM, params, nparams, grid, block, stream, true);
+}
+TK_API int tk_launch_mix_tzconv_lbm(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                    unsigned, void* stream) {
+    return launch_more_mix(MORE_LBM, params, nparams, grid, block, stream, true);
+}
+TK_API int tk_launch_mix_tzconv_fft(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                    unsigned, void* stream) {
+    return launch_more_mix(MORE_FFT, params, nparams, grid, block, stream, true);
+}
+TK_API int tk_launch_mix_tzconv_cutcp(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                                      unsigned, void* stream) {
+    return launch_more_mix(MORE_CUTCP, params, nparams, grid, block, stream, true);
+}
+
+// The whole original grid of one of the four, from the solo argument list alone (the shape the reference's Ori
+// classes launch): grid / block are the ORIGINAL launch dimensions, from which the geometry ints are filled in.
+static int launch_more_ori(MoreKind kind, void** params, int nparams, const unsigned grid[3], const unsigned block[3],
+                           void* stream) {
+    const int n = more_solo_args(kind);
+    int rc = check_params(params, nparams, n);
+    if (rc != TK_OK) return rc;
+    if (!grid || !block || grid[0] == 0 || block[0] == 0) return TK_ERR_LAUNCH_CONFIG;
+    int geo[6] = {static_cast<int>(grid[0]), static_cast<int>(grid[1] ? grid[1] : 1), static_cast<int>(grid[2] ? grid[2] : 1),
+                  static_cast<int>(block[0]), static_cast<int>(block[1] ? block[1] : 1),
+                  static_cast<int>(block[2] ? block[2] : 1)};
+    int start = 0, step = 0, tb = 0, end = geo[0] * geo[1] * geo[2];
+    void* p[20];
+    for (int i = 0; i < n; ++i) p[i] = params[i];
+    for (int i = 0; i < 6; ++i) p[n + i] = &geo[i];
+    p[n + 6] = &start;
+    p[n + 7] = &step;
+    p[n + 8] = &end;
+    p[n + 9] = &tb;
+    MoreCall m;
+    if ((rc = parse_more(kind, p, &m)) != TK_OK) return rc;
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    const unsigned ctas = static_cast<unsigned>(d->sm_count) * (kind == MORE_SGEMM ? 1u : 2u);
+    return run_more_solo(m, ctas, 512, static_cast<cudaStream_t>(stream));
+}
+TK_API int tk_launch_ori_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
+                               void* stream) {
+    return launch_more_ori(MORE_SGEMM, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_ori_lbm(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
+                             void* stream) {
+    return launch_more_ori(MORE_LBM, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_ori_fft(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
+                             void* stream) {
+    return launch_more_ori(MORE_FFT, params, nparams, grid, block, stream);
+}
+TK_API int tk_launch_ori_cutcp(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
+                               void* stream) {
+    return launch_more_ori(MORE_CUTCP, params, nparams, grid, block, stream);
+}
+
+// neighbour offsets {dx, dy, dz} x n (device) -> the int4 table of the cutcp kernels (device, 16 n bytes)
+TK_API int tk_cutcp_pack_neighbours(const int* nbr_xyz, int n, void* table, void* stream) {
+    if (n < 0 || (n > 0 && (!nbr_xyz || !table))) return TK_ERR_ARGS;
+    if (reinterpret_cast<uintptr_t>(table) & 15u) return TK_ERR_ALIGN;
+    if (n == 0) return TK_OK;
+    cutcp_pack_nbr_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(nbr_xyz, n,
+                                                                                          static_cast<int4*>(table));
+    return launch_error("cutcp_pack_nbr_kernel launch");
+}
+
 // ---- non-persistent shape: every virtual block of the reference grid ----
 TK_API int tk_launch_ori_stencil(void** params, int nparams, const unsigned grid[3], const unsigned block[3],
                                  unsigned, void* stream) {
@@ -430,6 +534,14 @@ static const KeyEntry kKeys[] = {
     {"tzgemm_stencil", tk_launch_mix_tzgemm_stencil, 32}, {"tzgemm_cp", tk_launch_mix_tzgemm_cp, 29},
     {"tzgemm_mriq", tk_launch_mix_tzgemm_mriq, 33},   {"ori_stencil", tk_launch_ori_stencil, 7},
     {"ori_cp", tk_launch_ori_cp, 4},                  {"ori_mriq", tk_launch_ori_mriq, 8},
+    {"gptb_sgemm", tk_launch_gptb_sgemm, 16},         {"tzgemm_sgemm", tk_launch_mix_tzgemm_sgemm, 31},
+    {"gptb_lbm", tk_launch_gptb_lbm, 12},             {"tzgemm_lbm", tk_launch_mix_tzgemm_lbm, 27},
+    {"gptb_fft", tk_launch_gptb_fft, 11},             {"tzgemm_fft", tk_launch_mix_tzgemm_fft, 26},
+    {"gptb_cutcp", tk_launch_gptb_cutcp, 20},         {"tzgemm_cutcp", tk_launch_mix_tzgemm_cutcp, 35},
+    {"ori_sgemm", tk_launch_ori_sgemm, 6},            {"ori_lbm", tk_launch_ori_lbm, 2},
+    {"ori_fft", tk_launch_ori_fft, 1},                {"ori_cutcp", tk_launch_ori_cutcp, 10},
+    {"tzconv_sgemm", tk_launch_mix_tzconv_sgemm, 36}, {"tzconv_lbm", tk_launch_mix_tzconv_lbm, 32},
+    {"tzconv_fft", tk_launch_mix_tzconv_fft, 31},     {"tzconv_cutcp", tk_launch_mix_tzconv_cutcp, 40},
 };
 static constexpr int kNumKeys = sizeof(kKeys) / sizeof(kKeys[0]);
 
@@ -500,6 +612,34 @@ TK_API int tk_query(const char* key, tk_kernel_info* info) {
         info->threads_cd_min = 32;
         info->threads_cd_default = 256;
         return fill_info(mrif_kernel<false, 2>, 256, 0, info);
+    }
+    {
+        const std::string tail = k.substr(k.find('_') + 1);
+        const bool solo = k.rfind("gptb_", 0) == 0 || k.rfind("ori_", 0) == 0;
+        if (tail == "sgemm" || tail == "lbm" || tail == "fft" || tail == "cutcp") {
+            info->threads_cd_min = 32;
+            info->threads_cd_default = 256;
+            if (solo) {
+                if (tail == "sgemm") return fill_info(sgemm_kernel<kSgemmSlotsSolo>, 256, sgemm_role_smem(8, kSgemmSlotsSolo), info);
+                if (tail == "lbm") return fill_info(lbm_kernel, 256, 0, info);
+                if (tail == "fft") return fill_info(fft_kernel, 256, fft_role_smem(8), info);
+                return fill_info(cutcp_kernel, 256, 0, info);
+            }
+            info->threads_tensor = kGemmThreads;
+            info->tmem_columns = 512;
+            const int msm = GemmSmem<kMoreBN, kMoreStages>::kBytes + 1024;
+            if (k.rfind("tzconv_", 0) == 0) {
+                if (tail == "sgemm")
+                    return fill_info(mix_sgemm_kernel<3, true>, kGemmThreads + 256, msm + sgemm_role_smem(8, 3), info);
+                if (tail == "lbm") return fill_info(mix_lbm_kernel<true>, kGemmThreads + 256, msm, info);
+                if (tail == "fft") return fill_info(mix_fft_kernel<true>, kGemmThreads + 256, msm + fft_role_smem(8), info);
+                return fill_info(mix_cutcp_kernel<true>, kGemmThreads + 256, msm, info);
+            }
+            if (tail == "sgemm") return fill_info(mix_sgemm_kernel<3>, kGemmThreads + 256, msm + sgemm_role_smem(8, 3), info);
+            if (tail == "lbm") return fill_info(mix_lbm_kernel<false>, kGemmThreads + 256, msm, info);
+            if (tail == "fft") return fill_info(mix_fft_kernel<false>, kGemmThreads + 256, msm + fft_role_smem(8), info);
+            return fill_info(mix_cutcp_kernel<false>, kGemmThreads + 256, msm, info);
+        }
     }
     info->threads_tensor = kGemmThreads;
     info->tmem_columns = 512;

@@ -9,6 +9,10 @@ StencilProblem creatorStencilProblem;
 CPProblem creatorCPProblem;
 MRIQProblem creatorMRIQProblem;
 MRIFProblem creatorMRIFProblem;
+SGEMMProblem creatorSGEMMProblem;
+LBMProblem creatorLBMProblem;
+FFTProblem creatorFFTProblem;
+CUTCPProblem creatorCUTCPProblem;
 
 namespace {
 std::map<std::string, GPTBKernel*> kernelMap;
@@ -45,6 +49,18 @@ GPTBKernel* createKernel(const std::string& name) {
     } else if (name == "stencil") {
         ori = new OriSTENCILKernel(id = 20, creatorStencilProblem);
         geometry(name, 2, 256, &grid, &block);
+    } else if (name == "cutcp") {  // ids as in src/Creator.cu:53-178
+        ori = new OriCUTCPKernel(id = 11, creatorCUTCPProblem);
+        geometry(name, 2, 512, &grid, &block);
+    } else if (name == "fft") {
+        ori = new OriFFTKernel(id = 12, creatorFFTProblem);
+        geometry(name, 2, 512, &grid, &block);
+    } else if (name == "lbm") {
+        ori = new OriLBMKernel(id = 16, creatorLBMProblem);
+        geometry(name, 2, 512, &grid, &block);
+    } else if (name == "sgemm") {
+        ori = new OriSGEMMKernel(id = 19, creatorSGEMMProblem);
+        geometry(name, 1, 512, &grid, &block);
     } else {
         logger.ERROR("createKernel: unknown kernel {" + name + "}");
     }
@@ -62,8 +78,9 @@ MixKernel* createMixKernel(const std::string& name, int m, int n, int k) {
     if (m <= 0 || n <= 0 || k <= 0) {  // headline GEMM of each pair
         if (cd == "stencil") m = 4096, n = 4096, k = 1024;
         else if (cd == "cp") m = 2048, n = 2048, k = 2048;
-        else if (cd != "mriq" && cd != "mrif") logger.ERROR("createMixKernel: unknown pair {" + name + "}");
-        else m = 4096, n = 4096, k = 2048;
+        else if (cd == "mriq" || cd == "mrif" || cd == "sgemm" || cd == "lbm" || cd == "fft" || cd == "cutcp")
+            m = 4096, n = 4096, k = 2048;
+        else logger.ERROR("createMixKernel: unknown pair {" + name + "}");
     }
     const std::string key = name + ":" + std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k);
     auto it = mixKernelMap.find(key);

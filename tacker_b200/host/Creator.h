@@ -10,9 +10,9 @@
 #include "ori_kernel/ori_kernels.h"
 #include "tzgemm_kernel.h"
 
-// "cp", "stencil", "mriq", "mrif": the persistent form of the benchmark kernel over all of its virtual blocks
+// "cp", "stencil", "mriq", "mrif", "sgemm", "lbm", "fft", "cutcp": the persistent form of the benchmark kernel over all of its virtual blocks
 GPTBKernel* createKernel(const std::string& name);
-// "tzgemm_cp", "tzgemm_stencil", "tzgemm_mriq", "tzgemm_mrif": the benchmark kernel fused with a tzgemm of m x n x k
+// "tzgemm_<one of them>": the benchmark kernel fused with a tzgemm of m x n x k
 // (default: the headline GEMM shape of each pair)
 MixKernel* createMixKernel(const std::string& name, int m = 0, int n = 0, int k = 0);
 // problem sizes used by createKernel (defaults = the headline configurations); set before the first call
@@ -20,4 +20,8 @@ extern StencilProblem creatorStencilProblem;
 extern CPProblem creatorCPProblem;
 extern MRIQProblem creatorMRIQProblem;
 extern MRIFProblem creatorMRIFProblem;
+extern SGEMMProblem creatorSGEMMProblem;
+extern LBMProblem creatorLBMProblem;
+extern FFTProblem creatorFFTProblem;
+extern CUTCPProblem creatorCUTCPProblem;
 void destroyCreatedKernels();

@@ -89,7 +89,8 @@ int main(int argc, char* argv[]) {
             if (eq == std::string::npos || !moduleCenter.registerModule(spec.substr(0, eq), spec.substr(eq + 1)))
                 throw std::runtime_error("cannot load the module " + spec);
         }
-        for (const char* pair : {"tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq", "tzgemm_mrif"}) {
+        for (const char* pair : {"tzgemm_stencil", "tzgemm_cp", "tzgemm_mriq", "tzgemm_mrif", "tzgemm_sgemm", "tzgemm_lbm",
+                                 "tzgemm_fft", "tzgemm_cutcp"}) {
             const std::string module = sget_kernel_info(pair, "module");
             if (module.empty() || moduleCenter.hasModule(module)) continue;
             std::string dir = module_dir;

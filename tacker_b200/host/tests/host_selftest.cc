@@ -73,7 +73,8 @@ static int record(const char* key, void** params, int n, const unsigned grid[3],
                   argv_<int>(params, n - 1)};
         const double cd = 0.00003 * range(cd_len - 3), tz = 0.001 * range(n - 3) * argv_<int>(params, cd_len + 5) / 1024.0;
         cost = std::max(cd, tz) + 0.25 * std::min(cd, tz) + 0.005;
-    } else if (k == "gptb_stencil" || k == "gptb_mriq" || k == "gptb_cp" || k == "gptb_mrif") {
+    } else if (k == "gptb_stencil" || k == "gptb_mriq" || k == "gptb_cp" || k == "gptb_mrif" || k == "gptb_sgemm" ||
+               k == "gptb_lbm" || k == "gptb_fft" || k == "gptb_cutcp") {
         const int s = n - 4;
         l.tail = {argv_<int>(params, s), argv_<int>(params, s + 1), argv_<int>(params, s + 2)};
         cost = 0.00003 * range(s) + 0.003;
@@ -111,6 +112,22 @@ FAKE_LAUNCHER(l_omf, "ori_mrif")
 FAKE_LAUNCHER(l_ost, "ori_stencil")
 FAKE_LAUNCHER(l_ocp, "ori_cp")
 FAKE_LAUNCHER(l_omq, "ori_mriq")
+FAKE_LAUNCHER(l_sg, "gptb_sgemm")
+FAKE_LAUNCHER(l_lb, "gptb_lbm")
+FAKE_LAUNCHER(l_ff, "gptb_fft")
+FAKE_LAUNCHER(l_cc, "gptb_cutcp")
+FAKE_LAUNCHER(l_msg, "tzgemm_sgemm")
+FAKE_LAUNCHER(l_mlb, "tzgemm_lbm")
+FAKE_LAUNCHER(l_mff, "tzgemm_fft")
+FAKE_LAUNCHER(l_mcc, "tzgemm_cutcp")
+FAKE_LAUNCHER(l_csg, "tzconv_sgemm")
+FAKE_LAUNCHER(l_clb, "tzconv_lbm")
+FAKE_LAUNCHER(l_cff, "tzconv_fft")
+FAKE_LAUNCHER(l_ccc, "tzconv_cutcp")
+FAKE_LAUNCHER(l_osg, "ori_sgemm")
+FAKE_LAUNCHER(l_olb, "ori_lbm")
+FAKE_LAUNCHER(l_off, "ori_fft")
+FAKE_LAUNCHER(l_occ, "ori_cutcp")
 
 class FakeBackend : public Backend {
 public:
@@ -118,7 +135,11 @@ public:
         {"gptb_tzgemm", l_tz}, {"gptb_tzgemm_acc", l_tz}, {"gptb_stencil", l_st}, {"gptb_cp", l_cp},       {"gptb_mriq", l_mq},
         {"tzgemm_stencil", l_mst}, {"tzgemm_cp", l_mcp}, {"tzgemm_mriq", l_mmq}, {"ori_stencil", l_ost},
         {"ori_cp", l_ocp},     {"ori_mriq", l_omq},    {"gptb_mrif", l_mf},   {"tzgemm_mrif", l_mmf}, {"ori_mrif", l_omf},
-        {"gptb_tzconv", l_tc}, {"tzconv_stencil", l_cst}, {"tzconv_cp", l_ccp}, {"tzconv_mriq", l_cmq}, {"tzconv_mrif", l_cmf}};
+        {"gptb_tzconv", l_tc}, {"tzconv_stencil", l_cst}, {"tzconv_cp", l_ccp}, {"tzconv_mriq", l_cmq}, {"tzconv_mrif", l_cmf},
+        {"gptb_sgemm", l_sg},  {"gptb_lbm", l_lb},     {"gptb_fft", l_ff},    {"gptb_cutcp", l_cc},
+        {"tzgemm_sgemm", l_msg}, {"tzgemm_lbm", l_mlb}, {"tzgemm_fft", l_mff}, {"tzgemm_cutcp", l_mcc},
+        {"ori_sgemm", l_osg},  {"ori_lbm", l_olb},     {"ori_fft", l_off},    {"ori_cutcp", l_occ},
+        {"tzconv_sgemm", l_csg}, {"tzconv_lbm", l_clb}, {"tzconv_fft", l_cff}, {"tzconv_cutcp", l_ccc}};
     int ops = 0;
     const char* name() const override { return "recording double"; }
     void setDevice(int) override {}
@@ -249,7 +270,7 @@ int main(int argc, char** argv) {
         CHECK(cp->gptbParams.block_dimension_x == 16 && cp->gptbParams.block_dimension_y == 8);
         CHECK(cp->gptbParams.ptb_end_block_pos == 256);
         CHECK(throws([] { createKernel("pc"); }));      // an anagram is not a hit
-        CHECK(throws([] { createKernel("fft"); }));     // outside the path
+        CHECK(throws([] { createKernel("hot3d"); }));     // outside the path
         CHECK(throws([] { createMixKernel("cp_fft"); }));
         GPTBKernel* st = createKernel("stencil");
         CHECK(st->kernelParams.size() == 7 + 6 && st->gptbParams.ptb_end_block_pos == 1024);
@@ -274,6 +295,27 @@ int main(int argc, char** argv) {
         GPTBKernel* mf = createKernel("mrif");
         CHECK(mf->funcKey == "gptb_mrif" && mf->kernelParams.size() == 8 + 6 && mf->gptbParams.ptb_end_block_pos == 1024);
         CHECK(createMixKernel("tzgemm_mrif")->kernelParams.size() == 33);
+        // the other four Parboil kernels: argument counts and original grids of the reference's defaults
+        creatorSGEMMProblem = SGEMMProblem{256, 64, 16};
+        creatorLBMProblem = LBMProblem{32, 4, 3};
+        creatorFFTProblem = FFTProblem{40};
+        creatorCUTCPProblem = CUTCPProblem{16, 16, 16, 0.5f, 12.0f, 0.1f};
+        GPTBKernel* sg = createKernel("sgemm");
+        CHECK(sg->funcKey == "gptb_sgemm" && sg->kernelParams.size() == 6 + 6 && sg->gptbParams.ptb_end_block_pos == 2 * 4);
+        GPTBKernel* lb = createKernel("lbm");
+        CHECK(lb->funcKey == "gptb_lbm" && lb->kernelParams.size() == 2 + 6 && lb->gptbParams.ptb_end_block_pos == 12);
+        GPTBKernel* ff = createKernel("fft");
+        CHECK(ff->funcKey == "gptb_fft" && ff->kernelParams.size() == 1 + 6 && ff->gptbParams.ptb_end_block_pos == 40);
+        GPTBKernel* cc = createKernel("cutcp");
+        CHECK(cc->funcKey == "gptb_cutcp" && cc->kernelParams.size() == 10 + 6 && cc->gptbParams.ptb_end_block_pos == 8);
+        {
+            OriCUTCPKernel* oc = static_cast<OriCUTCPKernel*>(cc->kernel_);
+            CHECK(oc->nbrlen == 335 && oc->binDim_x == 8 && oc->binDim_y == 8 && oc->binDim_z == 8);   // 7^3 cube without corners
+            CHECK(*static_cast<int*>(cc->kernelParams[10]) == 2 && *static_cast<int*>(cc->kernelParams[13]) == 8 &&
+                  *static_cast<int*>(cc->kernelParams[14]) == 2);
+        }
+        CHECK(createMixKernel("tzgemm_sgemm")->kernelParams.size() == 31 && createMixKernel("tzgemm_lbm")->kernelParams.size() == 27);
+        CHECK(createMixKernel("tzgemm_fft")->kernelParams.size() == 26 && createMixKernel("tzgemm_cutcp")->kernelParams.size() == 35);
         OriTZGEMMKernel ori(0, 300, 200, 130);
         CHECK(ori.M_GLOBAL == 256 && ori.N_GLOBAL == 128 && ori.K_GLOBAL == 128 && ori.ori_blks == 8);
         CHECK(throws([&] { ori.execute(nullptr); }));   // "should not execute ori tzgemm!"

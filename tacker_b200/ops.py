@@ -193,6 +193,62 @@ class OriMRIFKernel(Kernel):
         self.launchBlockDim = (256, 1, 1)
 
 
+class OriSGEMMKernel(Kernel):
+    """src/ori_kernel/sgemm_kernel.cu:9-150: C = 2 C + 2 A B; A [K][M], B [K][N], C [N][M]."""
+
+    kernelName = "sgemm"
+    funcKey = "ori_sgemm"
+
+    def __init__(self, A: int, B: int, Cm: int, M: int, N: int, K: int):
+        super().__init__()
+        self.kernelParams = [C.c_void_p(A), C.c_void_p(B), C.c_void_p(Cm), C.c_int(M), C.c_int(N), C.c_int(K)]
+        self.launchGridDim = (M // 128, N // 16, 1)
+        self.launchBlockDim = (16, 8, 1)
+
+
+class OriLBMKernel(Kernel):
+    """src/ori_kernel/lbm_kernel.cu:9-225: one time step; src / dst address cell (0, 0, 0) of element 0."""
+
+    kernelName = "lbm"
+    funcKey = "ori_lbm"
+
+    def __init__(self, src: int, dst: int, nx: int, ny: int, nz: int):
+        super().__init__()
+        self.kernelParams = [C.c_void_p(src), C.c_void_p(dst)]
+        self.launchGridDim = (ny, nz, 1)
+        self.launchBlockDim = (nx, 1, 1)
+
+
+class OriFFTKernel(Kernel):
+    """src/ori_kernel/fft_kernel.cu:40-125: `nfft` transforms of 256 complex points, in place."""
+
+    kernelName = "fft"
+    funcKey = "ori_fft"
+
+    def __init__(self, data: int, nfft: int):
+        super().__init__()
+        self.kernelParams = [C.c_void_p(data)]
+        self.launchGridDim = (nfft, 1, 1)
+        self.launchBlockDim = (128, 1, 1)
+
+
+class OriCUTCPKernel(Kernel):
+    """src/ori_kernel/cutcp_kernel.cu:19-330; `nbr` = the table of cutcp_pack_neighbours, `bins_zero` the bin at the
+    lattice origin, `regions` gx * gy * gz regions of 512 floats."""
+
+    kernelName = "cutcp"
+    funcKey = "ori_cutcp"
+
+    def __init__(self, binDim_x: int, binDim_y: int, bins_zero: int, h: float, cutoff2: float, inv_cutoff2: float,
+                 regions: int, nbr: int, nbrlen: int, gx: int, gy: int, gz: int):
+        super().__init__()
+        self.kernelParams = [C.c_int(binDim_x), C.c_int(binDim_y), C.c_void_p(bins_zero), C.c_float(h),
+                             C.c_float(cutoff2), C.c_float(inv_cutoff2), C.c_void_p(regions), C.c_int(gz - 1),
+                             C.c_void_p(nbr), C.c_int(nbrlen)]
+        self.launchGridDim = (gx, gy, gz)
+        self.launchBlockDim = (8, 2, 8)
+
+
 class GPTBKernel(Kernel):
     """src/GPTBKernel.h:12-124."""
 
@@ -317,6 +373,35 @@ def gptb_mrif(numK, x, y, z, outR, outI, kvals, numX, start=0, end=None, grid=No
     ori = OriMRIFKernel(numK, x, y, z, outR, outI, kvals, numX)
     return GPTBKernel("mrif", "gptb_mrif", ori, (grid or sm_count() * 2, 1, 1), (block, 1, 1), start,
                       ori.launchGridDim[0] if end is None else end)
+
+
+def _gptb_of(name: str, ori: Kernel, start, end, grid, block) -> GPTBKernel:
+    g = ori.launchGridDim
+    return GPTBKernel(name, "gptb_" + name, ori, (grid or sm_count() * 2, 1, 1), (block, 1, 1), start,
+                      g[0] * g[1] * g[2] if end is None else end)
+
+
+def gptb_sgemm(A, B, Cm, M, N, K, start=0, end=None, grid=None, block=512) -> GPTBKernel:
+    return _gptb_of("sgemm", OriSGEMMKernel(A, B, Cm, M, N, K), start, end, grid or sm_count(), block)
+
+
+def gptb_lbm(src, dst, nx, ny, nz, start=0, end=None, grid=None, block=512) -> GPTBKernel:
+    return _gptb_of("lbm", OriLBMKernel(src, dst, nx, ny, nz), start, end, grid, block)
+
+
+def gptb_fft(data, nfft, start=0, end=None, grid=None, block=512) -> GPTBKernel:
+    return _gptb_of("fft", OriFFTKernel(data, nfft), start, end, grid, block)
+
+
+def gptb_cutcp(binDim_x, binDim_y, bins_zero, h, cutoff2, inv_cutoff2, regions, nbr, nbrlen, gx, gy, gz, start=0,
+               end=None, grid=None, block=512) -> GPTBKernel:
+    ori = OriCUTCPKernel(binDim_x, binDim_y, bins_zero, h, cutoff2, inv_cutoff2, regions, nbr, nbrlen, gx, gy, gz)
+    return _gptb_of("cutcp", ori, start, end, grid, block)
+
+
+def cutcp_pack_neighbours(nbr_xyz, n, table, stream: int = 0) -> None:
+    check(lib().tk_cutcp_pack_neighbours(C.c_void_p(nbr_xyz), n, C.c_void_p(table), C.c_void_p(stream)),
+          "tk_cutcp_pack_neighbours")
 
 
 def mix(cd: GPTBKernel, tz: GPTBKernel, cd_threads=256, grid=None, cd_range=None, tz_range=None) -> MixKernel:

@@ -20,7 +20,42 @@ KS = (128, 512, 1152, 2304, 4096, 4608)  # the K values the reference tabulates
 HOST_CONFIG = os.path.join(os.path.dirname(os.path.abspath(__file__)), "host", "config")
 
 
-def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
+def cutcp_problem(nx: int, ny: int, nz: int, h: float = 0.5, cutoff: float = 12.0, density: float = 0.1, seed: int = 0):
+    """Synthetic input of the cutoff-Coulomb kernel: atoms at `density` per cubic Angstrom hashed into bins of 4 A
+    (8 atoms each, further atoms of a full bin dropped) and the neighbour offsets, as the reference's host code
+    prepares them (src/header/cutcp_header.h:106-300).  Returns bins [bz][by][bx][8][4], offsets [n][4], margin c."""
+    import numpy as np
+
+    c = int(np.ceil(cutoff / 4.0))
+    g = [(v + 7) // 8 for v in (nx, ny, nz)]
+    dims = [int(np.ceil(8 * gi * h / 4.0)) + 2 * c for gi in g]                      # x, y, z
+    ext = np.array(dims, dtype=np.float64) * 4.0
+    rng = np.random.default_rng(seed)
+    n = int(density * ext.prod())
+    pos = (rng.random((n, 3)) * ext - 4.0 * c).astype(np.float32)
+    q = (rng.random(n) * 2 - 1).astype(np.float32)
+    q[q == 0] = 0.5
+    ijk = np.floor(pos / 4.0).astype(np.int64) + c
+    index = (ijk[:, 2] * dims[1] + ijk[:, 1]) * dims[0] + ijk[:, 0]
+    order = np.argsort(index, kind="stable")
+    index, pos, q = index[order], pos[order], q[order]
+    first = np.searchsorted(index, index, side="left")
+    rank = np.arange(n) - first
+    keep = rank < 8
+    bins = np.zeros((dims[2] * dims[1] * dims[0], 8, 4), dtype=np.float32)
+    bins[index[keep], rank[keep], :3] = pos[keep]
+    bins[index[keep], rank[keep], 3] = q[keep]
+    s = np.sqrt(3.0) if (4.0 / (8 * h)).is_integer() else 2 * np.sqrt(3.0)
+    r2 = (cutoff + s * 4.0) ** 2
+    r = np.arange(-c, c + 1)
+    kk, jj, ii = np.meshgrid(r, r, r, indexing="ij")
+    ok = (ii * ii + jj * jj + kk * kk) * 16.0 < r2
+    nbr = np.stack([ii[ok], jj[ok], kk[ok], np.zeros(ok.sum(), dtype=np.int64)], axis=1).astype(np.int32)
+    return bins.reshape(dims[2], dims[1], dims[0], 8, 4), np.ascontiguousarray(nbr), c
+
+
+def profile(fill: float = 0.8, m: int = 4096, n: int = 4096, only=None) -> dict:
+    import numpy as np
     import torch
 
     from . import ops
@@ -77,6 +112,31 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
                                                    fr.data_ptr(), fi.data_ptr(), fkv.data_ptr(), 262144, start=s,
                                                    end=e, grid=sms * 2, block=512), 1024, (2, 512), (576, 704, 832)),
     }
+    # the other four at the reference's sizes: sgemm 4096 x 4128 x 4064, lbm 128^3, fft 10240 x 256, cutcp 208 x 208 x 16
+    sa, sb = torch.rand(4064, 4096, device="cuda"), torch.rand(4064, 4128, device="cuda")
+    sc = torch.zeros(4128, 4096, device="cuda")
+    lmargin, lcells = 2 * 128 * 128, 128 ** 3
+    lsrc, ldst = torch.rand(20 * lcells + 2 * lmargin, device="cuda"), torch.rand(20 * lcells + 2 * lmargin, device="cuda")
+    fdata = torch.rand(10240, 256, 2, device="cuda") * 2 - 1
+    cbins, cnbr, cmargin = cutcp_problem(208, 208, 16)
+    dbins, dnbr = torch.from_numpy(cbins).cuda(), torch.from_numpy(cnbr).cuda()
+    bdz, bdy, bdx = cbins.shape[:3]
+    czero = dbins.data_ptr() + 128 * ((cmargin * bdy + cmargin) * bdx + cmargin)
+    cregions = torch.zeros(2 * 26 * 26 * 512, device="cuda")
+    cds.update({
+        "sgemm": (lambda s=0, e=None: ops.gptb_sgemm(sa.data_ptr(), sb.data_ptr(), sc.data_ptr(), 4096, 4128, 4064, start=s,
+                                                     end=e, grid=sms, block=512), 32 * 258, (1, 512), (192, 288, 384)),
+        "lbm": (lambda s=0, e=None: ops.gptb_lbm(lsrc.data_ptr() + 4 * lmargin, ldst.data_ptr() + 4 * lmargin, 128, 128, 128,
+                                                 start=s, end=e, grid=sms * 2, block=512), 128 * 128, (2, 512),
+                (448, 576, 832)),
+        "fft": (lambda s=0, e=None: ops.gptb_fft(fdata.data_ptr(), 10240, start=s, end=e, grid=sms * 2, block=512), 10240,
+                (2, 512), (320, 576, 832)),
+        "cutcp": (lambda s=0, e=None: ops.gptb_cutcp(bdx, bdy, czero, 0.5, 144.0, float(np.float32(1.0) / np.float32(144.0)),
+                                                     cregions.data_ptr(), dnbr.data_ptr(), cnbr.shape[0], 26, 26, 2, start=s,
+                                                     end=e, grid=sms * 2, block=512), 26 * 26 * 2, (2, 512), (448, 576, 832)),
+    })
+    if only:
+        cds = {k: v for k, v in cds.items() if k in only}
     out = {}
     for cd, (mk, blocks, solo_shape, w_sweep) in cds.items():
         t_block = t_us([mk()], 3) / blocks
@@ -107,6 +167,7 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096) -> dict:
                              "cd_us": round(t_cd, 2), "fused_us": round(t_fused, 2),
                              "fused_vs_sequential": round(t_fused / (t_gemm + t_cd), 4)}
         out[f"tzgemm_{cd}"] = {"cd_us_per_block": round(t_block, 4), "cd_threads": cd_threads, "solo_shape": solo_shape,
+                               "blocks": blocks,
                                "fused_us_by_cd_threads": {str(w): round(v, 2) for w, v in by_w.items()}, "table": table}
     return out
 
@@ -126,6 +187,7 @@ def write_configs(result: dict, config_dir: str = HOST_CONFIG, out_dir: str | No
         for pair, r in result.items():
             solo = cfg.setdefault(pair[len("tzgemm_"):], {})
             solo["gridsize"], solo["blocksize"] = r["solo_shape"]
+            solo["ori_blks"] = r["blocks"]
             entry = cfg.setdefault(pair, {})
             entry["gridsize"] = 1
             entry["blocksize"] = 192 + r["cd_threads"]
@@ -145,8 +207,9 @@ def main(argv=None) -> int:
     ap.add_argument("--write", action="store_true", help="store the ratios in tacker_b200/host/config/kinfo-*.json")
     ap.add_argument("--out", default=None, help="with --write: put the updated files there instead of rewriting in place")
     ap.add_argument("--fill", type=float, default=0.8)
+    ap.add_argument("--only", default=None, help="comma-separated CUDA-core kernels to profile (default: all eight)")
     args = ap.parse_args(argv)
-    result = profile(args.fill)
+    result = profile(args.fill, only=args.only.split(",") if args.only else None)
     print(json.dumps(result, indent=1))
     if args.write:
         for p in write_configs(result, out_dir=args.out):

@@ -37,7 +37,7 @@ def test_registry_mirrors_fmap_keys(tk):
     assert set(keys) == set(tk.KEYS)
     for k in keys:
         assert lib.tk_lookup(k.encode())
-    assert not lib.tk_lookup(b"gptb_fft")          # outside the hot path: not registered
+    assert not lib.tk_lookup(b"gptb_hot3d")        # outside the hot path: not registered
     assert lib.tk_key(99) is None
     from tacker_b200 import ops
 

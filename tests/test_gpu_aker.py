@@ -120,6 +120,25 @@ def test_scheduler_launches_a_generated_module(cuda, tmp_path):
     assert "device status word" not in out.stdout + out.stderr
 
 
+@pytest.mark.parametrize("a,b", [("cutcp", "fft"), ("lbm", "sgemm")])
+def test_scheduler_with_the_other_parboil_kernels(cuda, tmp_path, a, b):
+    """sgemm, lbm, fft and cutcp as the best-effort pair (src/Creator.cu:53-178): the experiment runs in both modes,
+    stage 2 launches the solo kernels, and the pairs whose measured ratios are not zero ride along LC layers."""
+    out = subprocess.run([_aker(), "-s", "both", "-m", "vgg16", "-c", os.path.join(HOST, "config"), "--be-kernel", a,
+                          "--be-kernel2", b], capture_output=True, text=True, timeout=600, cwd=tmp_path)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    results = re.findall(r"\[Result\] (Aker|Tacker) BE task took ([\d.]+) \+ ([\d.eE+-]+)", out.stdout)
+    assert [r[0] for r in results] == ["Aker", "Tacker"]
+    mixes = re.findall(r"execed be blks: (\d+), mix times: (\d+)/(\d+), time earned: ([\d.]+)", out.stdout)
+    assert len(mixes) == 2 and all(0 <= int(f) <= int(m) for _, f, m, _ in mixes)
+    # whether a layer carries blocks is the scheduler's call (a quarter region of cutcp or half a block of sgemm outlasts
+    # most VGG16 layers, so it mostly declines); what ran must be accounted for
+    stage2 = re.findall(r"\[Stage2\] (\d+) solo launches in the ([\d.]+) ms left: (\d+) blocks of (\w+), (\d+) blocks of (\w+)",
+                        out.stdout)
+    assert len(stage2) == 2 and all(s[3] == a and s[5] == b for s in stage2)
+    assert "device status word" not in out.stdout + out.stderr
+
+
 def test_bert_as_the_lc_task(cuda, tmp_path):
     """The reference also schedules its BERT graph as the latency-critical task (src/main.cu:227-244)."""
     out = subprocess.run([_aker(), "-s", "tacker", "-m", "bert", "-c", os.path.join(HOST, "config")], capture_output=True,
@@ -142,4 +161,4 @@ def test_resource_query_for_every_key(cuda):
         else:
             assert info.threads_tensor == 0 and info.threads_cd_min == 32
     with pytest.raises(tacker_b200.TackerError):
-        ops.query("gptb_fft")
+        ops.query("gptb_hot3d")

@@ -56,7 +56,7 @@ def test_profile_ratios_writes_the_reference_schema(tmp_path):
     table = {str(k): {"ratio": 0.001 * (i + 1), "blocks": 8, "gemm_us": 1.0, "cd_us": 1.0, "fused_us": 1.5,
                       "fused_vs_sequential": 0.75} for i, k in enumerate(profile_ratios.KS)}
     table["2304"]["ratio"] = 0.0                                # a pair / K where fusing did not pay: never fused
-    result = {"tzgemm_mrif": {"cd_us_per_block": 0.25, "cd_threads": 704, "solo_shape": (2, 512),
+    result = {"tzgemm_mrif": {"cd_us_per_block": 0.25, "cd_threads": 704, "solo_shape": (2, 512), "blocks": 1024,
                               "fused_us_by_cd_threads": {"704": 10.0}, "table": table}}
     before = {p: open(os.path.join(HOST, "config", p)).read() for p in os.listdir(os.path.join(HOST, "config"))}
     touched = profile_ratios.write_configs(result, out_dir=str(tmp_path))
@@ -67,7 +67,7 @@ def test_profile_ratios_writes_the_reference_schema(tmp_path):
         assert e["gridsize"] == 1 and e["blocksize"] == 192 + 704
         assert [e[str(k)] for k in profile_ratios.KS] == [0.001, 0.002, 0.003, 0.0, 0.005, 0.006]
         assert e["block_ratio"] == e["4096"] == 0.005 and e["best_block_ratio"] == 0.006
-        assert cfg["mrif"]["gridsize"] == 2 and cfg["mrif"]["blocksize"] == 512
+        assert cfg["mrif"]["gridsize"] == 2 and cfg["mrif"]["blocksize"] == 512 and cfg["mrif"]["ori_blks"] == 1024
         assert "throughput_test" in cfg and "tzgemm_stencil" in cfg          # everything else is carried over
     after = {p: open(os.path.join(HOST, "config", p)).read() for p in os.listdir(os.path.join(HOST, "config"))}
     assert before == after
