@@ -245,6 +245,12 @@ def run_ours(args):
         rep.close()
         return
 
+    if args.only_more:  # just sgemm, lbm, fft and cutcp with their pairs
+        if rank == 0:
+            print(json.dumps({"pairs": more_kernels(torch, ops, sms, gen, t_of, measured_peaks()[0])}), flush=True)
+        rep.close()
+        return
+
     if args.only_pairs or args.profile_pair:  # just the Coulomb and MRI-Q pairs (used for profiler captures of those kernels)
         if rank == 0:
             print(json.dumps({"pairs": other_pairs(torch, ops, sms, gen, t_of, st, args.profile_pair, args.profile_w,
@@ -376,6 +382,7 @@ def run_ours(args):
     pairs = None
     if not args.quick:
         pairs = other_pairs(torch, ops, sms, gen, t_of, st)
+        pairs.update(more_kernels(torch, ops, sms, gen, t_of, measured_peaks()[0]))
 
     # ---- end to end through the host-buffer C-ABI call ----
     hA, hB = A.cpu().pin_memory(), B.cpu().pin_memory()
@@ -648,6 +655,70 @@ def other_pairs(torch, ops, sms, gen, t_of, st, profile=None, profile_w=832, pro
     return out
 
 
+def more_kernels(torch, ops, sms, gen, t_of, hbm_gbs):
+    """sgemm, lbm, fft and cutcp at the reference's sizes: solo time with the bound that applies, and each fused with the
+    GEMM 4096 x 4096 x 2048 (as stated and balanced in time)."""
+    import numpy as np
+
+    from tacker_b200.profile_ratios import cutcp_problem
+
+    a = (torch.rand(4096, 2048, device="cuda", generator=gen) * 2 - 1).half()
+    b = (torch.rand(4096, 2048, device="cuda", generator=gen) * 2 - 1).half()
+    c = torch.zeros(4096, 4096, device="cuda")
+    tz = lambda s=0, e=None: ops.gptb_tzgemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), 4096, 4096, 2048, alpha=1.0, start=s,
+                                             end=e, grid=sms)
+    out = {}
+    fp32_peak = sms * 128 * 2 * 1.965e9  # fused multiply-adds of the CUDA cores at the maximum clock
+
+    M, N, K = 4096, 4128, 4064           # src/ori_kernel/sgemm_kernel.cu:85-87
+    sa, sb = torch.rand(K, M, device="cuda", generator=gen), torch.rand(K, N, device="cuda", generator=gen)
+    sc = torch.zeros(N, M, device="cuda")
+    sg = lambda s=0, e=None: ops.gptb_sgemm(sa.data_ptr(), sb.data_ptr(), sc.data_ptr(), M, N, K, start=s, end=e, grid=sms,
+                                            block=512)
+    r = pair_report(ops, sms, t_of, tz, sg, (M // 128) * (N // 16), "sgemm", (192, 384))
+    r["sgemm_tflops"] = round(2.0 * M * N * K / r["sgemm_us"] / 1e6, 2)
+    r["sgemm_frac_of_fp32_peak"] = round(2.0 * M * N * K / (r["sgemm_us"] * 1e-6) / fp32_peak, 3)
+    out["gemm4096x2048_sgemm"] = r
+    del sa, sb, sc
+
+    nx = ny = nz = 128                    # src/header/lbm_header.h:17-19
+    cells, margin = nx * ny * nz, 2 * nx * ny
+    lsrc = torch.rand(20 * cells + 2 * margin, device="cuda", generator=gen)
+    ldst = torch.rand(20 * cells + 2 * margin, device="cuda", generator=gen)
+    lb = lambda s=0, e=None: ops.gptb_lbm(lsrc.data_ptr() + 4 * margin, ldst.data_ptr() + 4 * margin, nx, ny, nz, start=s, end=e,
+                                          grid=sms * 2, block=512)
+    r = pair_report(ops, sms, t_of, tz, lb, ny * nz, "lbm", (448, 576))
+    r["lbm_gbs"] = round(156.0 * cells / r["lbm_us"] / 1e3, 1)   # 20 values read, 19 written per cell
+    r["lbm_frac_of_hbm"] = round(156.0 * cells / (r["lbm_us"] * 1e-6) / 1e9 / hbm_gbs, 3)
+    out["gemm4096x2048_lbm"] = r
+    del lsrc, ldst
+
+    nfft = 10240                          # FFT_B, src/header/fft_header.h:13
+    fdata = torch.rand(nfft, 256, 2, device="cuda", generator=gen) * 2 - 1
+    ff = lambda s=0, e=None: ops.gptb_fft(fdata.data_ptr(), nfft, start=s, end=e, grid=sms * 2, block=512)
+    r = pair_report(ops, sms, t_of, tz, ff, nfft, "fft", (320, 576))
+    r["fft_gbs"] = round(4096.0 * nfft / r["fft_us"] / 1e3, 1)   # 2 KB in, 2 KB out per transform
+    r["fft_gflops"] = round(5.0 * 256 * 8 * nfft / r["fft_us"] / 1e3, 1)
+    out["gemm4096x2048_fft"] = r
+
+    bins, nbr, cm = cutcp_problem(208, 208, 16)   # the reference's lattice, two slabs of regions in z
+    dbins, dnbr = torch.from_numpy(bins).cuda(), torch.from_numpy(nbr).cuda()
+    bdz, bdy, bdx = bins.shape[:3]
+    zero = dbins.data_ptr() + 128 * ((cm * bdy + cm) * bdx + cm)
+    regions = torch.zeros(2 * 26 * 26 * 512, device="cuda")
+    inv = float(np.float32(1.0) / np.float32(144.0))
+    cc = lambda s=0, e=None: ops.gptb_cutcp(bdx, bdy, zero, 0.5, 144.0, inv, regions.data_ptr(), dnbr.data_ptr(), nbr.shape[0],
+                                            26, 26, 2, start=s, end=e, grid=sms * 2, block=512)
+    r = pair_report(ops, sms, t_of, tz, cc, 26 * 26 * 2, "cutcp", (448, 576))
+    count = (bins[..., 3] != 0).sum(axis=3).astype(np.int64)     # atoms per bin
+    pairs = 0
+    for dx, dy, dz, _ in nbr:                                     # every region's centre bin is the lattice bin (rx, ry, rz)
+        pairs += int(count[cm + dz:cm + dz + 2, cm + dy:cm + dy + 26, cm + dx:cm + dx + 26].sum())
+    r["cutcp_gpairs_per_s"] = round(512.0 * pairs / r["cutcp_us"] / 1e3, 1)   # (lattice point, atom) evaluations
+    out["gemm4096x2048_cutcp"] = r
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -659,6 +730,7 @@ def main():
     ap.add_argument("--sustain-ms", type=float, default=400.0)
     ap.add_argument("--colocate-s", type=float, default=60.0, help="seconds of the LC/BE co-location run (0 = skip)")
     ap.add_argument("--only-pairs", action="store_true", help="run only the Coulomb and MRI-Q pairs and print them")
+    ap.add_argument("--only-more", action="store_true", help="run only sgemm, lbm, fft and cutcp with their pairs and print them")
     ap.add_argument("--profile-gemm", default=None, help="MxNxK: time the solo tzgemm on that shape, launch it three more "
                                                          "times and exit")
     ap.add_argument("--gemm-pair", type=int, default=0, help="tzgemm_pair option of the --profile-gemm launches")
