@@ -23,6 +23,8 @@ uint16_t half_bits(float f) {  // round to nearest even; inputs are small normal
 }
 }  // namespace
 
+uint16_t dnn_half_bits(float f) { return half_bits(f); }
+
 DnnArena::~DnnArena() {
     for (void* p : owned) backend().deviceFree(p);
 }

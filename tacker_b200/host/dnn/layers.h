@@ -24,6 +24,7 @@ struct DnnArena {
 };
 
 inline int roundUp(int v, int m) { return ((v + m - 1) / m) * m; }
+uint16_t dnn_half_bits(float f);  // binary32 -> binary16 bits, round to nearest even
 
 // Common part of the two tzgemm-backed layers: operands, the persistent GEMM kernel over all tiles and
 // what the scheduler needs to fuse it with a best-effort kernel.

@@ -46,6 +46,8 @@ float* DnnTask::conv(const float* x, int H, int W, int Cin, int Cout, int k, int
     *OW = c->OW;
     float* y = arena.act(static_cast<size_t>(c->M) * Cout);
     float* bias = arena.weightsF32(Cout, 5000 + nextId, -0.05f, 0.05f);
+    lastLayer = c;
+    lastBias = bias;
     const int id2 = nextId++;
     auto* b = new OpKernel(id2, "BiasAct_" + std::to_string(id2), OpKernel::BiasAct);
     b->a = c->C;
@@ -66,6 +68,8 @@ float* DnnTask::dense(const float* x, int rows, int in, int out, int act, float*
     keep(g);
     if (!y) y = arena.act(static_cast<size_t>(rows) * out);
     float* bias = arena.weightsF32(out, 6000 + nextId, -0.05f, 0.05f);
+    lastLayer = g;
+    lastBias = bias;
     const int id4 = nextId++;
     auto* b = new OpKernel(id4, "BiasAct_" + std::to_string(id4), OpKernel::BiasAct);
     b->a = g->C;
@@ -103,6 +107,8 @@ void* DnnTask::convToBordered(const float* x, int H, int W, int Cin, int Cout, i
     keep(c);
     void* y = borderedImage(H, W, Cout);
     float* bias = arena.weightsF32(Cout, 5000 + nextId, -0.05f, 0.05f);
+    lastLayer = c;
+    lastBias = bias;
     const int id2 = nextId++;
     auto* b = new OpKernel(id2, "BiasAct_" + std::to_string(id2), OpKernel::BiasActHalfBordered);
     b->a = c->C;
@@ -124,7 +130,10 @@ void* DnnTask::convBordered(void* x, int H, int W, int Cin, int Cout, int act) {
     void* y = borderedImage(H, W, Cout);
     float* bias = arena.weightsF32(Cout, 5000 + nextId, -0.05f, 0.05f);
     nextId++;
-    keep(new ConvImplicitKernel(id1, "Convolution_" + std::to_string(id1), arena, x, H, W, Cin, Cout, act, 1000 + id1, bias, y));
+    auto* c = new ConvImplicitKernel(id1, "Convolution_" + std::to_string(id1), arena, x, H, W, Cin, Cout, act, 1000 + id1, bias, y);
+    keep(c);
+    lastLayer = c;
+    lastBias = bias;
     return y;
 }
 
@@ -149,6 +158,8 @@ float* DnnTask::denseFromBordered(void* x, int H, int W, int C, int out, int act
     keep(g);
     float* y = arena.act(static_cast<size_t>(out));
     float* bias = arena.weightsF32(out, 6000 + nextId, -0.05f, 0.05f);
+    lastLayer = g;
+    lastBias = bias;
     const int id4 = nextId++;
     auto* b = new OpKernel(id4, "BiasAct_" + std::to_string(id4), OpKernel::BiasAct);
     b->a = g->C;
@@ -353,5 +364,6 @@ Task* createTask(const std::string& taskName) {
     if (taskName == "vgg16") return new VGG16(1000);
     if (taskName == "resnet50") return new Resnet50(1000);
     if (taskName == "bert") return new Bert(12, 8, 128);
+    if (taskName.size() > 5 && taskName.compare(taskName.size() - 5, 5, ".json") == 0) return new GraphTask(taskName);
     logger.ERROR("Task name not found: " + taskName);
 }

@@ -47,6 +47,9 @@ protected:
     void* poolBordered(void* x, int H, int W, int C);
     // dense layer on the flattened interior of a bordered image (one row)
     float* denseFromBordered(void* x, int H, int W, int C, int out, int act);
+    // what the last conv / dense helper created, for builders that replace the seeded constants by loaded ones
+    TzLayer* lastLayer = nullptr;
+    float* lastBias = nullptr;
     float* addTo(const float* a, const float* b, int rows, int cols, int act);
     float* layernorm(const float* x, int rows, int cols);
 };
@@ -70,4 +73,29 @@ public:
     int batch, seq;
 };
 
-Task* createTask(const std::string& taskName);  // "vgg16", "resnet50", "bert" (src/main.cu:227-244)
+// A model read from a description file instead of being compiled in -- the role the reference gives to the classes
+// src/nnf/gen_code.py generates from NNFusion output (src/nnf/gen_code.py:69-246) and to the Constant_<n>_0.bin files
+// those classes read (src/dnn/vgg16/vgg16_kernel_class.h:378-391).  JSON:
+//   {"name": "..", "config": "vgg16",                       model file whose kernel tables the scheduler uses
+//    "input": {"h": 32, "w": 32, "c": 3, "seed": 42, "file": "input.bin"},
+//    "constants": "Constant",                               directory of the .bin files, relative to the description
+//    "layers": [{"op": "conv3x3", "out": 64, "act": "relu", "weight": "Constant_1_0.bin", "bias": "Constant_2_0.bin"},
+//               {"op": "maxpool"}, {"op": "dense", "out": 10, "act": "none", ...}, {"op": "softmax"}]}
+// Constants are raw little-endian fp32 in NNFusion's layouts: convolution filters [3][3][Cin][Cout], dense weights
+// [in][out], biases [out]; a layer without files keeps its seeded constants.  Convolutions are 3 x 3 / stride 1 /
+// padding 1; after the first one the channel counts must be multiples of 64 (the implicit-GEMM form).
+class GraphTask : public DnnTask {
+public:
+    explicit GraphTask(const std::string& descriptionFile);
+    std::string config = "vgg16";
+    int loadedConstants = 0;  // files read
+
+private:
+    std::vector<float> readConstant(const std::string& file, size_t count);
+    void loadConv(const std::string& wfile, const std::string& bfile, int Cin, int Cout);
+    void loadDense(const std::string& wfile, const std::string& bfile, int in, int out);
+    std::string constantDir;
+};
+
+// "vgg16", "resnet50", "bert" (src/main.cu:227-244), or the path of a model description (*.json)
+Task* createTask(const std::string& taskName);

@@ -7,6 +7,8 @@
 // with one best-effort kernel); with --colocate, the request-driven co-location of `-m` (latency-critical) with the
 // model `--be` (best-effort) on this GPU; with --colocate-fused, the co-location with the benchmark kernel of the
 // configuration as the best-effort job, time-sliced and fused.
+#include <fstream>
+#include <sstream>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -22,6 +24,7 @@
 #include "Recorder.h"
 #include "TaskManager.h"
 #include "dnn/models.h"
+#include "json.h"
 #include "json.h"
 
 static void usage(const char* argv0) {
@@ -79,7 +82,17 @@ int main(int argc, char* argv[]) {
     try {
         std::unique_ptr<Backend> be(makeCudaBackend());
         setBackend(be.get());
-        read_json(config_dir + "/kinfo-" + model + ".json");
+        // a model description file (GraphTask) names the model whose kernel tables it is scheduled with
+        std::string table_model = model;
+        if (model.size() > 5 && model.compare(model.size() - 5, 5, ".json") == 0) {
+            std::ifstream mf(model);
+            std::stringstream ms;
+            ms << mf.rdbuf();
+            const std::shared_ptr<JsonValue> root = parse_json(ms.str());
+            const JsonValue* c = root->get("config");
+            table_model = c && c->kind == JsonValue::String ? c->str : std::string("vgg16");
+        }
+        read_json(config_dir + "/kinfo-" + table_model + ".json");
         read_common_json(config_dir + "/kinfo-common.json");
         // Fused kernels emitted by the generator: registered under a name from the command line (the pair's key, e.g.
         // tzgemm_mriq=/path/tzgemm_mriq_1_16.so, replaces the library's kernel of that pair) or named by the model

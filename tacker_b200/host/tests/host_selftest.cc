@@ -156,9 +156,13 @@ public:
     void deviceFree(void* p) override { std::free(p); }
     void* hostAllocPinned(size_t bytes) override { return std::malloc(bytes); }
     void hostFreePinned(void* p) override { std::free(p); }
-    // buffers are never dereferenced here; the streams of uploads and fills are recorded
+    // kernels never run here; small uploads are copied so that loaded constants can be inspected, and the streams of
+    // uploads and fills are recorded
     std::vector<stream_t> upload_streams, fill_streams;
-    void upload(void*, const void*, size_t, stream_t s) override { upload_streams.push_back(s); }
+    void upload(void* dst, const void* src, size_t bytes, stream_t s) override {
+        upload_streams.push_back(s);
+        if (bytes <= (1u << 20)) std::memcpy(dst, src, bytes);  // allocations are capped at 1 MB: larger copies are dropped
+    }
     void download(void*, const void*, size_t, stream_t) override {}
     void fillZero(void*, size_t, stream_t s) override { fill_streams.push_back(s); }
     stream_t streamCreate() override { return nullptr; }
@@ -343,6 +347,39 @@ int main(int argc, char** argv) {
         Resnet50 rn;
         CHECK(rn.numMixable() == 54);  // 53 convolutions + the classifier
         CHECK(throws([] { createTask("alexnet"); }));
+        // a model from a description file with NNFusion-style constant files
+        {
+            char dir[] = "tk_graph_selftest_XXXXXX";
+            CHECK(mkdtemp(dir) != nullptr);
+            const std::string d(dir);
+            auto write_bin = [&](const std::string& name, size_t floats, float value) {
+                std::vector<float> v(floats, value);
+                std::ofstream f(d + "/" + name, std::ios::binary);
+                f.write(reinterpret_cast<const char*>(v.data()), static_cast<std::streamsize>(floats * sizeof(float)));
+            };
+            write_bin("Constant_1_0.bin", 9 * 3 * 64, 0.5f);   // filter [3][3][3][64]
+            write_bin("Constant_2_0.bin", 64, 0.25f);
+            write_bin("Constant_3_0.bin", 4 * 4 * 64 * 10, 0.125f);   // dense [1024][10]
+            {
+                std::ofstream f(d + "/model.json");
+                f << R"({"name": "tiny", "config": "vgg16", "input": {"h": 8, "w": 8, "c": 3, "seed": 7}, "constants": ".",
+                         "layers": [{"op": "conv3x3", "out": 64, "act": "relu", "weight": "Constant_1_0.bin", "bias": "Constant_2_0.bin"},
+                                    {"op": "maxpool"}, {"op": "dense", "out": 10, "act": "none", "weight": "Constant_3_0.bin"},
+                                    {"op": "softmax"}]})";
+            }
+            std::unique_ptr<Task> t(createTask(d + "/model.json"));
+            GraphTask* g = static_cast<GraphTask*>(t.get());
+            CHECK(g->taskName == "tiny" && g->config == "vgg16" && g->loadedConstants == 3 && g->numMixable() == 2);
+            CHECK(g->resultCount == 20);
+            auto* conv = static_cast<TzLayer*>(g->kernels[0]);
+            // B[n][(3 i + j) Cin + c] of the loaded filter: 0.5 = 0x3800 in binary16, zero in the padding of K
+            const uint16_t* b = static_cast<const uint16_t*>(conv->B);
+            CHECK(conv->K == 27 && conv->K_pad == 64 && b[0] == 0x3800 && b[26] == 0x3800 && b[27] == 0 && b[64] == 0x3800);
+            write_bin("Constant_3_0.bin", 7, 0.0f);
+            CHECK(throws([&] { createTask(d + "/model.json"); }));   // wrong size: refused, the file is named
+            for (const char* f : {"Constant_1_0.bin", "Constant_2_0.bin", "Constant_3_0.bin", "model.json"}) unlink((d + "/" + f).c_str());
+            rmdir(dir);
+        }
         g_launches.clear();
         vgg.initExecution();
         vgg.executeTask(ExecutionMode::Aker, nullptr);

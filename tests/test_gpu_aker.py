@@ -102,6 +102,39 @@ def test_vgg16_scores_match_the_cpu_forward(cuda, oracle, tmp_path):
     assert abs(float(got[1000:].sum()) - 1.0) <= 1e-4
 
 
+def test_model_from_description_and_constant_files(cuda, tmp_path):
+    """A model read from a description with NNFusion-style constant files (raw fp32: filters [3][3][Cin][Cout], dense
+    weights [in][out]) -- what the reference's generated classes do with Constant_<n>_0.bin
+    (src/dnn/vgg16/vgg16_kernel_class.h:378-391): the scores `aker` computes against a numpy forward of the same files."""
+    import numpy as np
+
+    import graph_numpy
+    from tacker_b200 import nnf
+
+    layers = [{"op": "conv3x3", "out": 64, "act": "relu"}, {"op": "conv3x3", "out": 64, "act": "relu"}, {"op": "maxpool"},
+              {"op": "conv3x3", "out": 128, "act": "relu"}, {"op": "maxpool"}, {"op": "dense", "out": 256, "act": "relu"},
+              {"op": "dense", "out": 10, "act": "none"}, {"op": "softmax"}]
+    x = np.random.default_rng(3).standard_normal((32, 32, 3)).astype(np.float32)
+    model = nnf.write_model(str(tmp_path / "m"), "tiny", 32, 32, 3, layers, nnf.random_constants(layers, 32, 32, 3, seed=5),
+                            input_array=x)
+    dump = tmp_path / "result.bin"
+    out = subprocess.run([_aker(), "-s", "aker", "-m", model, "-c", os.path.join(HOST, "config"), "--dump-output", str(dump),
+                          "--colocate", "0.2"], capture_output=True, text=True, timeout=600, cwd=tmp_path)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    got = np.fromfile(dump, dtype=np.float32)
+    assert got.size == 20
+    scores, probs = graph_numpy.forward(model, x)
+    scale = float(np.abs(scores).max())
+    assert scale > 0 and np.abs(got[:10] - scores).max() <= 1e-2 * scale
+    assert int(np.argmax(got[:10])) == int(np.argmax(scores)) and np.abs(got[10:] - probs).max() <= 1e-2
+    # a constant of the wrong size is refused with the file's name, as the reference's loader refuses a missing file
+    with open(tmp_path / "m" / "Constant" / "Constant_1_0.bin", "ab") as f:
+        f.write(b"\0\0\0\0")
+    bad = subprocess.run([_aker(), "-s", "aker", "-m", model, "-c", os.path.join(HOST, "config")], capture_output=True,
+                         text=True, timeout=600, cwd=tmp_path)
+    assert bad.returncode != 0 and "Constant_1_0.bin" in bad.stdout + bad.stderr
+
+
 def test_scheduler_launches_a_generated_module(cuda, tmp_path):
     """Generator -> runtime: a fused kernel emitted for one thread ratio, compiled into a module and registered
     under the pair's key replaces the library's kernel in the scheduler's fused launches
