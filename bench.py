@@ -675,7 +675,7 @@ def more_kernels(torch, ops, sms, gen, t_of, hbm_gbs):
     sc = torch.zeros(N, M, device="cuda")
     sg = lambda s=0, e=None: ops.gptb_sgemm(sa.data_ptr(), sb.data_ptr(), sc.data_ptr(), M, N, K, start=s, end=e, grid=sms,
                                             block=512)
-    r = pair_report(ops, sms, t_of, tz, sg, (M // 128) * (N // 16), "sgemm", (192, 384))
+    r = pair_report(ops, sms, t_of, tz, sg, (M // 128) * (N // 16), "sgemm", (256, 384))
     r["sgemm_tflops"] = round(2.0 * M * N * K / r["sgemm_us"] / 1e6, 2)
     r["sgemm_frac_of_fp32_peak"] = round(2.0 * M * N * K / (r["sgemm_us"] * 1e-6) / fp32_peak, 3)
     out["gemm4096x2048_sgemm"] = r
@@ -687,7 +687,7 @@ def more_kernels(torch, ops, sms, gen, t_of, hbm_gbs):
     ldst = torch.rand(20 * cells + 2 * margin, device="cuda", generator=gen)
     lb = lambda s=0, e=None: ops.gptb_lbm(lsrc.data_ptr() + 4 * margin, ldst.data_ptr() + 4 * margin, nx, ny, nz, start=s, end=e,
                                           grid=sms * 2, block=512)
-    r = pair_report(ops, sms, t_of, tz, lb, ny * nz, "lbm", (448, 576))
+    r = pair_report(ops, sms, t_of, tz, lb, ny * nz, "lbm", (576, 832))
     r["lbm_gbs"] = round(156.0 * cells / r["lbm_us"] / 1e3, 1)   # 20 values read, 19 written per cell
     r["lbm_frac_of_hbm"] = round(156.0 * cells / (r["lbm_us"] * 1e-6) / 1e9 / hbm_gbs, 3)
     out["gemm4096x2048_lbm"] = r
@@ -709,7 +709,7 @@ def more_kernels(torch, ops, sms, gen, t_of, hbm_gbs):
     inv = float(np.float32(1.0) / np.float32(144.0))
     cc = lambda s=0, e=None: ops.gptb_cutcp(bdx, bdy, zero, 0.5, 144.0, inv, regions.data_ptr(), dnbr.data_ptr(), nbr.shape[0],
                                             26, 26, 2, start=s, end=e, grid=sms * 2, block=512)
-    r = pair_report(ops, sms, t_of, tz, cc, 26 * 26 * 2, "cutcp", (448, 576))
+    r = pair_report(ops, sms, t_of, tz, cc, 26 * 26 * 2, "cutcp", (576, 832))
     count = (bins[..., 3] != 0).sum(axis=3).astype(np.int64)     # atoms per bin
     pairs = 0
     for dx, dy, dz, _ in nbr:                                     # every region's centre bin is the lattice bin (rx, ry, rz)

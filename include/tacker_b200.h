@@ -88,6 +88,11 @@ int tk_sm_count(int* sm_count);
  *   "mriq_accurate"  1 = cosf/sinf as the reference calls them (default 0: reduced argument +
  *                    hardware sin/cos); "mrif_accurate" the same for MRI-FHd (plus the binary64 product of its phase)
  *   "mriq_split"     samples per MRI-Q / MRI-FHd work item, as "cp_split"
+ *   "sgemm_split"    k-steps per sgemm work item (a multiple of 8), "cutcp_split" neighbour bins per cutcp work item:
+ *                    -1 (default) = chosen from the launch shape (launches with many blocks per warp are never split),
+ *                    0 = never (the reference's order of additions, bit for bit), n = n.  Split items add partial
+ *                    sums with reductions in no fixed order, after a short kernel on the same stream that doubles C
+ *                    (sgemm: C = 2 C + 2 A B) or zeroes the regions (cutcp).
  *   "wait_budget_us" budget of every bounded device-side wait (default 1,000,000 = about a second); applies to the
  *                    current device.  "test_skip_loads" n: test hook, the next n single-CTA tzgemm launches issue
  *                    no operand loads, so that their waits run out.

@@ -43,6 +43,11 @@ struct SgemmArgs {
     int M, N, K;
     int gx, gy;      // M / 128, N / 16
     int start, end;  // original blocks, bx fastest
+    // 0: a work item is half a block over the whole K (the reference's order of additions, bit for bit).
+    // > 0 (a multiple of 8): a work item covers that many k-steps and adds 2 x its partial sums to C with reductions;
+    // C must already hold 2 x its old value (sgemm_scale_c_kernel) -- half a block of K = 4064 is 280 us of one warp,
+    // far too long a unit to share an SM with a GEMM of tens of microseconds.
+    int k_per_item;
 };
 
 constexpr int kSgemmChunk = 8;                                       // k-steps per ring slot
@@ -61,7 +66,8 @@ __device__ __forceinline__ void cp_async_wait() {
 // rows 64 * half .. + 63 of block (bx, by); ring: this warp's S slots
 template <int S>
 __device__ __forceinline__ void sgemm_half_block(const SgemmArgs& g, const int bx, const int by, const int half,
-                                                 uint8_t* ring, const int lane) {
+                                                 uint8_t* ring, const int lane, const int k_begin, const int k_end,
+                                                 const bool partial) {
     float c[2][16];
 #pragma unroll
     for (int r = 0; r < 2; ++r)
@@ -69,9 +75,9 @@ __device__ __forceinline__ void sgemm_half_block(const SgemmArgs& g, const int b
         for (int j = 0; j < 16; ++j) c[r][j] = 0.0f;
     const int m0 = bx * 128 + half * 64;
     const size_t lda = static_cast<size_t>(g.M), ldb = static_cast<size_t>(g.N);
-    const float* __restrict__ a_ptr = g.A + m0;
-    const float* __restrict__ b_ptr = g.B + by * 16;
-    const int K = g.K;
+    const float* __restrict__ a_ptr = g.A + m0 + static_cast<size_t>(k_begin) * lda;
+    const float* __restrict__ b_ptr = g.B + by * 16 + static_cast<size_t>(k_begin) * ldb;
+    const int K = k_end - k_begin;  // k-steps of this item
     const int nchunks = (K + kSgemmChunk - 1) / kSgemmChunk;
     const uint32_t ring_u32 = smem_u32(ring);
     // slot layout: A [8][64] floats, then B [8][16] floats
@@ -120,6 +126,14 @@ __device__ __forceinline__ void sgemm_half_block(const SgemmArgs& g, const int b
     cp_async_wait<0>();
     // C = C * beta + alpha * c with alpha = beta = 2 (src/gptb_kernel/sgemm_kernel.cu:12-13, 59-62)
     float* c_ptr = g.C + static_cast<size_t>(by) * 16 * lda + m0 + 2 * lane;
+    if (partial) {  // C already holds 2 x its old value
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            red_add_f32(c_ptr + j * lda, 2.0f * c[0][j]);
+            red_add_f32(c_ptr + j * lda + 1, 2.0f * c[1][j]);
+        }
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         float2* p = reinterpret_cast<float2*>(c_ptr + j * lda);
@@ -130,11 +144,25 @@ __device__ __forceinline__ void sgemm_half_block(const SgemmArgs& g, const int b
     }
 }
 
-// warp `w` of `nw` in CTA `cta` of `ncta`; smem: sgemm_role_smem(nw, S) bytes, 16-byte aligned
+// warp `w` of `nw` in CTA `cta` of `ncta`; smem: sgemm_role_smem(nw, S) bytes, 16-byte aligned; counter: the CTA's
+// item counter (zero on entry; used when the items are split in k)
 template <int S>
-__device__ __forceinline__ void sgemm_role(const SgemmArgs& g, uint8_t* smem, const int w, const int nw, const int lane,
-                                           const int cta, const int ncta) {
+__device__ __forceinline__ void sgemm_role(const SgemmArgs& g, uint8_t* smem, int* counter, const int w, const int nw,
+                                           const int lane, const int cta, const int ncta) {
     uint8_t* ring = smem + w * (S * kSgemmSlotBytes);
+    if (g.k_per_item > 0) {
+        const int nchunks = (g.K + g.k_per_item - 1) / g.k_per_item;
+        const long long nitems = 2ll * (g.end - g.start) * nchunks;
+        for (long long item = claim_item(counter, lane, cta, ncta); item < nitems; item = claim_item(counter, lane, cta, ncta)) {
+            const int chunk = static_cast<int>(item % nchunks);
+            const long long hb = item / nchunks;
+            const int pos = g.start + static_cast<int>(hb >> 1);
+            const int k0 = chunk * g.k_per_item;
+            sgemm_half_block<S>(g, pos % g.gx, (pos / g.gx) % g.gy, static_cast<int>(hb & 1), ring, lane, k0,
+                                min(k0 + g.k_per_item, g.K), true);
+        }
+        return;
+    }
     // groups of nw consecutive by at one (bx, half); (bx, half) fastest so that neighbouring CTAs share B rows
     const int ygroups = (g.gy + nw - 1) / nw;
     const int ngroups = 2 * g.gx * ygroups;
@@ -143,7 +171,21 @@ __device__ __forceinline__ void sgemm_role(const SgemmArgs& g, uint8_t* smem, co
         if (by >= g.gy) continue;
         const int pos = by * g.gx + (xh >> 1);
         if (pos < g.start || pos >= g.end) continue;
-        sgemm_half_block<S>(g, xh >> 1, by, xh & 1, ring, lane);
+        sgemm_half_block<S>(g, xh >> 1, by, xh & 1, ring, lane, 0, g.K, false);
+    }
+}
+
+// C *= 2 on the blocks of [start, end): the first half of C = 2 C + 2 A B when the items are split in k
+__device__ __forceinline__ void sgemm_scale_c(const SgemmArgs& g, const int t, const int nt, const int cta, const int ncta) {
+    for (int pos = g.start + cta; pos < g.end; pos += ncta) {
+        const int bx = pos % g.gx, by = (pos / g.gx) % g.gy;
+        float* c = g.C + static_cast<size_t>(by) * 16 * g.M + bx * 128;
+        for (int i = t; i < 16 * 32; i += nt) {
+            float4* p = reinterpret_cast<float4*>(c + static_cast<size_t>(i >> 5) * g.M) + (i & 31);
+            float4 v = *p;
+            v.x *= 2.0f, v.y *= 2.0f, v.z *= 2.0f, v.w *= 2.0f;
+            *p = v;
+        }
     }
 }
 
@@ -353,10 +395,14 @@ struct CutcpArgs {
     const int4* nbr;      // neighbour offsets {dx, dy, dz, 0}
     int nbrlen;
     int start, end;
+    // 0: a work item is a quarter region over the whole neighbour list (the reference's order of additions, bit for
+    // bit).  > 0: a work item covers that many neighbour bins and adds its partial sums to the region with reductions;
+    // the region must be zero before (cutcp_zero) -- a quarter region over 335 bins is 370 us of one warp.
+    int nbr_per_item;
 };
 
 __device__ __forceinline__ void cutcp_quarter(const CutcpArgs& g, const int rx, const int ry, const int rz, const int quarter,
-                                              const int lane) {
+                                              const int lane, const int nb_begin, const int nb_end, const bool partial) {
     constexpr float kBinInvLen = 1.f / 4.f;
     const int tid = 32 * quarter + lane;
     const int tx = tid & 7, ty = (tid >> 3) & 1, tz = tid >> 4;
@@ -368,7 +414,7 @@ __device__ __forceinline__ void cutcp_quarter(const CutcpArgs& g, const int rx, 
     const int cz = static_cast<int>(floorf((8 * rz + 4) * g.h * kBinInvLen));
     float e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f;
     const float h2 = 2.0f * g.h, cutoff2 = g.cutoff2, inv_cutoff2 = g.inv_cutoff2;
-    for (int nb = 0; nb < g.nbrlen; ++nb) {
+    for (int nb = nb_begin; nb < nb_end; ++nb) {
         const int4 o = __ldg(g.nbr + nb);
         const float4* bin = g.bins + ((static_cast<long long>(cz + o.z) * g.bin_dim_y + (cy + o.y)) * g.bin_dim_x + (cx + o.x)) * 8;
         float4 atom[8];
@@ -409,6 +455,13 @@ __device__ __forceinline__ void cutcp_quarter(const CutcpArgs& g, const int rx, 
         }
     }
     float* out = g.regions + ((static_cast<size_t>(rz) * g.gy + ry) * g.gx + rx) * 512 + (tid >> 4) * 64 + (tid & 15);
+    if (partial) {
+        red_add_f32(out, e0);
+        red_add_f32(out + 16, e1);
+        red_add_f32(out + 32, e2);
+        red_add_f32(out + 48, e3);
+        return;
+    }
     out[0] = e0;
     out[16] = e1;
     out[32] = e2;
@@ -416,10 +469,25 @@ __device__ __forceinline__ void cutcp_quarter(const CutcpArgs& g, const int rx, 
 }
 
 __device__ __forceinline__ void cutcp_role(const CutcpArgs& g, int* counter, const int lane, const int cta, const int ncta) {
-    const long long nitems = 4ll * (g.end - g.start);
+    const bool split = g.nbr_per_item > 0 && g.nbr_per_item < g.nbrlen;
+    const int per = split ? g.nbr_per_item : g.nbrlen;
+    const int nchunks = split ? (g.nbrlen + per - 1) / per : 1;
+    const long long nitems = 4ll * (g.end - g.start) * nchunks;
     for (long long item = claim_item(counter, lane, cta, ncta); item < nitems; item = claim_item(counter, lane, cta, ncta)) {
-        const int p = g.start + static_cast<int>(item >> 2);
-        cutcp_quarter(g, p / (g.gy * g.gz), (p / g.gz) % g.gy, p % g.gz, static_cast<int>(item & 3), lane);
+        const int chunk = static_cast<int>(item % nchunks);
+        const long long q = item / nchunks;
+        const int p = g.start + static_cast<int>(q >> 2);
+        cutcp_quarter(g, p / (g.gy * g.gz), (p / g.gz) % g.gy, p % g.gz, static_cast<int>(q & 3), lane, chunk * per,
+                      min(chunk * per + per, g.nbrlen), split);
+    }
+}
+
+// zero the regions of [start, end): the starting point of the partial sums when the items are split
+__device__ __forceinline__ void cutcp_zero(const CutcpArgs& g, const int t, const int nt, const int cta, const int ncta) {
+    for (int p = g.start + cta; p < g.end; p += ncta) {
+        const int rx = p / (g.gy * g.gz), ry = (p / g.gz) % g.gy, rz = p % g.gz;
+        float4* region = reinterpret_cast<float4*>(g.regions + ((static_cast<size_t>(rz) * g.gy + ry) * g.gx + rx) * 512);
+        for (int i = t; i < 128; i += nt) region[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
 }
 

@@ -42,6 +42,9 @@ struct Options {
     // samples per item from the launch shape, 0 = never split (deterministic summation order), > 0 = that many
     int cp_split = -1;
     int mriq_split = -1;
+    // the same for sgemm (k-steps per work item) and cutcp (neighbour bins per work item)
+    int sgemm_split = -1;
+    int cutcp_split = -1;
     int mriq_vpt = 2;      // voxels per thread and work item / 32, solo kernel (2 or 4)
     int mix_mriq_vpt = 4;  // fused kernel: the larger item halves the table reads that compete with the tensor role
     int stencil_prefetch = 0;   // register role: L2 prefetch distance in planes (0 or 8)

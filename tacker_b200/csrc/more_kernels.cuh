@@ -13,7 +13,18 @@ namespace tk {
 template <int S>
 __global__ void __launch_bounds__(512, 1) sgemm_kernel(const SgemmArgs g) {
     extern __shared__ __align__(16) uint8_t more_smem[];
-    sgemm_role<S>(g, more_smem, threadIdx.x >> 5, blockDim.x >> 5, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    __shared__ int item_counter;
+    if (threadIdx.x == 0) item_counter = 0;
+    __syncthreads();
+    sgemm_role<S>(g, more_smem, &item_counter, threadIdx.x >> 5, blockDim.x >> 5, threadIdx.x & 31, blockIdx.x, gridDim.x);
+}
+
+// the passes that precede a launch with split work items: C *= 2 (sgemm), regions = 0 (cutcp)
+__global__ void __launch_bounds__(256) sgemm_scale_c_kernel(const SgemmArgs g) {
+    sgemm_scale_c(g, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
+}
+__global__ void __launch_bounds__(128) cutcp_zero_kernel(const CutcpArgs g) {
+    cutcp_zero(g, threadIdx.x, blockDim.x, blockIdx.x, gridDim.x);
 }
 
 __global__ void __launch_bounds__(512, 2) lbm_kernel(const LbmArgs g) {
@@ -54,13 +65,15 @@ __global__ void __launch_bounds__(kMaxMixThreadsSgemm, 1)
 mix_sgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
                  const SgemmArgs a) {
     extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
     const int warp = threadIdx.x >> 5;
     uint8_t* smem = align_smem_1024(smem_raw);
     if (warp < kGemmWarps) {
         gemm_role<kMoreBN, kMoreStages, true, CONV>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31);
     } else {
-        sgemm_role<S>(a, smem + GemmSmem<kMoreBN, kMoreStages>::kBytes, warp - kGemmWarps, (blockDim.x >> 5) - kGemmWarps,
-                   threadIdx.x & 31, blockIdx.x, gridDim.x);
+        cd_role_begin(&item_counter);
+        sgemm_role<S>(a, smem + GemmSmem<kMoreBN, kMoreStages>::kBytes, &item_counter, warp - kGemmWarps,
+                      (blockDim.x >> 5) - kGemmWarps, threadIdx.x & 31, blockIdx.x, gridDim.x);
     }
 }
 
@@ -110,6 +123,79 @@ mix_cutcp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 // -------------------------------------------------------------------------------------------------
+// the same pairs with the tensor role on CTA pairs (gemm_role2; launches that hold at least a wave of pair tiles):
+// the CUDA-core role is unchanged and works per CTA, its threads only arrive at the cluster barrier the tensor roles
+// of the pair wait on at start-up.  sgemm and fft keep their shared memory behind four operand stages, lbm and cutcp
+// need none and leave the tensor role its six.
+// -------------------------------------------------------------------------------------------------
+constexpr int kMorePairStagesSmem = 4;
+
+template <int S>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxMixThreadsSgemm, 1)
+mix_sgemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
+                  const SgemmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
+    const int warp = threadIdx.x >> 5;
+    uint8_t* smem = align_smem_1024(smem_raw);
+    if (warp < kGemmWarps) {
+        gemm_role2<kMorePairStagesSmem>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31, blockIdx.x >> 1, gridDim.x >> 1);
+    } else {
+        cluster_arrive();
+        cd_role_begin(&item_counter);
+        sgemm_role<S>(a, smem + Gemm2Smem<kMorePairStagesSmem>::kBytes, &item_counter, warp - kGemmWarps,
+                      (blockDim.x >> 5) - kGemmWarps, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxMixThreadsSfu, 1)
+mix_lbm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
+                const LbmArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role2<kStagesPair>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31, blockIdx.x >> 1,
+                                gridDim.x >> 1);
+    } else {
+        cluster_arrive();
+        cd_role_begin(&item_counter);
+        lbm_role(a, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxMixThreadsSfu, 1)
+mix_fft2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
+                const FftArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    uint8_t* smem = align_smem_1024(smem_raw);
+    if (warp < kGemmWarps) {
+        gemm_role2<kMorePairStagesSmem>(&tmap_a, &tmap_b, g, smem, warp, threadIdx.x & 31, blockIdx.x >> 1, gridDim.x >> 1);
+    } else {
+        cluster_arrive();
+        fft_role(a, smem + Gemm2Smem<kMorePairStagesSmem>::kBytes, threadIdx.x - kGemmThreads, blockDim.x - kGemmThreads,
+                 blockIdx.x, gridDim.x, kCdBarrierId);
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxMixThreadsSfu, 1)
+mix_cutcp2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g,
+                  const CutcpArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int item_counter;
+    const int warp = threadIdx.x >> 5;
+    if (warp < kGemmWarps) {
+        gemm_role2<kStagesPair>(&tmap_a, &tmap_b, g, align_smem_1024(smem_raw), warp, threadIdx.x & 31, blockIdx.x >> 1,
+                                gridDim.x >> 1);
+    } else {
+        cluster_arrive();
+        cd_role_begin(&item_counter);
+        cutcp_role(a, &item_counter, threadIdx.x & 31, blockIdx.x, gridDim.x);
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
 // argument parsing (reference argument order; p = the CUDA-core list, geometry ints at n_solo .. n_solo + 5)
 // -------------------------------------------------------------------------------------------------
 static bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
@@ -127,6 +213,7 @@ static int parse_sgemm(void** p, int i_start, int i_end, SgemmArgs* g) {
     const int bdx = arg<int>(p, 9), bdy = arg<int>(p, 10);
     g->start = arg<int>(p, i_start);
     g->end = arg<int>(p, i_end);
+    g->k_per_item = 0;
     if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->start < 0) return TK_ERR_ARGS;
     if (g->M % 128 || g->N % 16) return TK_ERR_SHAPE;
     if (g->gx != g->M / 128 || g->gy != g->N / 16 || bdx != 16 || bdy != 8) return TK_ERR_SHAPE;
@@ -187,22 +274,52 @@ static int parse_cutcp(void** p, int i_start, int i_end, CutcpArgs* g) {
     const int bdx = arg<int>(p, 13), bdy = arg<int>(p, 14), bdz = arg<int>(p, 15);
     g->start = arg<int>(p, i_start);
     g->end = arg<int>(p, i_end);
+    g->nbr_per_item = 0;
     if (g->bin_dim_x <= 0 || g->bin_dim_y <= 0 || g->gx <= 0 || g->gy <= 0 || g->gz <= 0 || g->nbrlen < 0 || g->start < 0)
         return TK_ERR_ARGS;
     if (bdx != 8 || bdy != 2 || bdz != 8) return TK_ERR_SHAPE;
     if (g->end > g->gx * g->gy * g->gz) g->end = g->gx * g->gy * g->gz;
     if (g->start < g->end && (!g->bins || !g->regions || (g->nbrlen > 0 && !g->nbr))) return TK_ERR_ARGS;
-    if (misaligned16(g->bins) || misaligned16(g->nbr) || (reinterpret_cast<uintptr_t>(g->regions) & 3u)) return TK_ERR_ALIGN;
+    if (misaligned16(g->bins) || misaligned16(g->nbr) || misaligned16(g->regions)) return TK_ERR_ALIGN;
     return TK_OK;
 }
 
 // -------------------------------------------------------------------------------------------------
 // solo launches
 // -------------------------------------------------------------------------------------------------
-static int run_sgemm(const SgemmArgs& g, unsigned grid0, unsigned block0, cudaStream_t st) {
+// k-steps / neighbour bins per work item: about eight items per launched warp when the launch has few blocks
+// (option > 0: that many; 0: never split, the reference's order of additions; -1: by this rule)
+static int sgemm_split_for(const SgemmArgs& g, long long warps) {
+    if (g_opt.sgemm_split == 0) return 0;
+    if (g_opt.sgemm_split > 0) return (g_opt.sgemm_split + 7) / 8 * 8;
+    return cd_pick_split(2ll * (g.end - g.start), warps, g.K, 64);
+}
+static int cutcp_split_for(const CutcpArgs& g, long long warps) {
+    if (g_opt.cutcp_split == 0) return 0;
+    if (g_opt.cutcp_split > 0) return g_opt.cutcp_split;
+    return cd_pick_split(4ll * (g.end - g.start), warps, g.nbrlen, 8);
+}
+// the pass a launch with split items needs first (same stream, so it is complete when the items start adding)
+static int sgemm_prepass(const SgemmArgs& g, cudaStream_t st) {
+    if (g.k_per_item <= 0) return TK_OK;
+    const int blocks = g.end - g.start;
+    sgemm_scale_c_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, st>>>(g);
+    return launch_error("sgemm_scale_c_kernel launch");
+}
+static int cutcp_prepass(const CutcpArgs& g, cudaStream_t st) {
+    if (g.nbr_per_item <= 0 || g.nbr_per_item >= g.nbrlen) return TK_OK;
+    const int blocks = g.end - g.start;
+    cutcp_zero_kernel<<<blocks < 1184 ? blocks : 1184, 128, 0, st>>>(g);
+    return launch_error("cutcp_zero_kernel launch");
+}
+
+static int run_sgemm(SgemmArgs g, unsigned grid0, unsigned block0, cudaStream_t st) {
     if (g.start >= g.end) return TK_OK;
     const unsigned threads = cd_threads(block0, 32, 512);
     if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    g.k_per_item = sgemm_split_for(g, static_cast<long long>(grid0) * (threads / 32));
+    int prc = sgemm_prepass(g, st);
+    if (prc != TK_OK) return prc;
     const int smem = sgemm_role_smem(static_cast<int>(threads / 32), kSgemmSlotsSolo);
     int rc = enable_smem(sgemm_kernel<kSgemmSlotsSolo>, smem);
     if (rc != TK_OK) return rc;
@@ -226,10 +343,13 @@ static int run_fft(const FftArgs& g, unsigned grid0, unsigned block0, cudaStream
     return launch_error("fft_kernel launch");
 }
 
-static int run_cutcp(const CutcpArgs& g, unsigned grid0, unsigned block0, cudaStream_t st) {
+static int run_cutcp(CutcpArgs g, unsigned grid0, unsigned block0, cudaStream_t st) {
     if (g.start >= g.end) return TK_OK;
     const unsigned threads = cd_threads(block0, 32, 512);
     if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
+    g.nbr_per_item = cutcp_split_for(g, static_cast<long long>(grid0) * (threads / 32));
+    int prc = cutcp_prepass(g, st);
+    if (prc != TK_OK) return prc;
     cutcp_kernel<<<grid0, threads, 0, st>>>(g);
     return launch_error("cutcp_kernel launch");
 }
@@ -305,6 +425,40 @@ static int launch_mix_more_kernels(const GemmCall& c, const MoreCall& m, const C
     return launch_error("fused kernel launch");
 }
 
+// fused launch with the tensor role on CTA pairs
+template <typename KernelT, typename ArgsT>
+static int launch_more_pair(KernelT k, const GemmCall& c, const ArgsT& a, DeviceInfo* d, unsigned ctas, unsigned threads, int smem,
+                            cudaStream_t st) {
+    CUtensorMap ta, tb;
+    int rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM);
+    if (rc != TK_OK) return rc;
+    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, kGemm2BN / 2)) != TK_OK) return rc;
+    if ((rc = enable_smem(k, smem)) != TK_OK) return rc;
+    unsigned pairs = 0;
+    if ((rc = pairs_for(k, d, ctas, threads, smem, &pairs)) != TK_OK) return rc;
+    k<<<2 * pairs, threads, smem, st>>>(ta, tb, c.g, a);
+    return launch_error("fused kernel launch (CTA pairs)");
+}
+
+static int launch_mix_more_pair(const GemmCall& c, const MoreCall& m, DeviceInfo* d, unsigned ctas, unsigned threads,
+                                unsigned cdt, cudaStream_t st) {
+    constexpr int kBytes6 = Gemm2Smem<kStagesPair>::kBytes + 1024, kBytes4 = Gemm2Smem<kMorePairStagesSmem>::kBytes + 1024;
+    const int nw = static_cast<int>(cdt / 32);
+    switch (m.kind) {
+        case MORE_SGEMM: {
+            const int room = kMaxDynSmem - kBytes4;
+            if (sgemm_role_smem(nw, 4) <= room)
+                return launch_more_pair(mix_sgemm2_kernel<4>, c, m.sg, d, ctas, threads, kBytes4 + sgemm_role_smem(nw, 4), st);
+            if (sgemm_role_smem(nw, 3) <= room)
+                return launch_more_pair(mix_sgemm2_kernel<3>, c, m.sg, d, ctas, threads, kBytes4 + sgemm_role_smem(nw, 3), st);
+            return launch_more_pair(mix_sgemm2_kernel<2>, c, m.sg, d, ctas, threads, kBytes4 + sgemm_role_smem(nw, 2), st);
+        }
+        case MORE_LBM: return launch_more_pair(mix_lbm2_kernel, c, m.lb, d, ctas, threads, kBytes6, st);
+        case MORE_FFT: return launch_more_pair(mix_fft2_kernel, c, m.ff, d, ctas, threads, kBytes4 + fft_role_smem(nw), st);
+        default: return launch_more_pair(mix_cutcp2_kernel, c, m.cc, d, ctas, threads, kBytes6, st);
+    }
+}
+
 static int run_mix_more(GemmCall& c, const MoreCall& m, unsigned grid0, unsigned block0, cudaStream_t st) {
     DeviceInfo* d = nullptr;
     int rc = device_info(&d);
@@ -314,7 +468,12 @@ static int run_mix_more(GemmCall& c, const MoreCall& m, unsigned grid0, unsigned
     const bool gemm_empty = c.g.start >= c.g.end;
     if (gemm_empty && m.empty()) return TK_OK;
     if (block0 <= static_cast<unsigned>(kGemmThreads)) return TK_ERR_LAUNCH_CONFIG;
-    constexpr int kGemmBytes = GemmSmem<kMoreBN, kMoreStages>::kBytes + 1024;
+    // The tensor role on CTA pairs pays once the launch holds at least a wave of pair tiles (as for the other pairs).
+    const unsigned ctas0 = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
+    const bool pair_ok = !c.conv && c.g.M >= 256 && c.g.N >= 256 && ctas0 >= 2;
+    const bool pair_wins = c.g.N % 256 == 0 && static_cast<long long>(c.g.end - c.g.start) >= 16ll * (ctas0 / 2);
+    const bool use_pair = pair_ok && (g_opt.mix_pair > 0 || (g_opt.mix_pair == 0 && pair_wins));
+    const int kGemmBytes = use_pair ? Gemm2Smem<kMorePairStagesSmem>::kBytes + 1024 : GemmSmem<kMoreBN, kMoreStages>::kBytes + 1024;
     unsigned cap = (m.kind == MORE_SGEMM ? kMaxMixThreadsSgemm : kMaxMixThreadsSfu) - kGemmThreads;
     if (m.kind == MORE_SGEMM) {  // as many warps as find a ring of two slots behind the tensor role's stages
         const unsigned fit = static_cast<unsigned>((kMaxDynSmem - kGemmBytes) / (2 * kSgemmSlotBytes)) * 32u;
@@ -328,13 +487,26 @@ static int run_mix_more(GemmCall& c, const MoreCall& m, unsigned grid0, unsigned
     if (cdt == 0) return TK_ERR_LAUNCH_CONFIG;
     if (gemm_empty) return run_more_solo(m, grid0, cdt, st);
     if (m.empty()) return run_tzgemm(c, grid0, st);
-    const unsigned ctas = grid0 < static_cast<unsigned>(d->sm_count) ? grid0 : static_cast<unsigned>(d->sm_count);
+    const unsigned ctas = ctas0;
     const unsigned threads = kGemmThreads + cdt;
     CUtensorMap ta, tb;
-    if ((rc = make_tmap_a(&ta, c, kGemmBM)) != TK_OK) return rc;
-    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, kMoreBN)) != TK_OK) return rc;
-    if (c.conv) return launch_mix_more_kernels<true>(c, m, ta, tb, ctas, threads, cdt, st);
-    return launch_mix_more_kernels<false>(c, m, ta, tb, ctas, threads, cdt, st);
+    if (!use_pair) {
+        if ((rc = make_tmap_a(&ta, c, kGemmBM)) != TK_OK) return rc;
+        if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, kMoreBN)) != TK_OK) return rc;
+    }
+    // work items sized for the CUDA-core warps of this launch; what split items need done first goes ahead on the stream
+    MoreCall mm = m;
+    const long long cd_warps = static_cast<long long>(ctas) * (cdt / 32);
+    if (mm.kind == MORE_SGEMM) {
+        mm.sg.k_per_item = sgemm_split_for(mm.sg, cd_warps);
+        if ((rc = sgemm_prepass(mm.sg, st)) != TK_OK) return rc;
+    } else if (mm.kind == MORE_CUTCP) {
+        mm.cc.nbr_per_item = cutcp_split_for(mm.cc, cd_warps);
+        if ((rc = cutcp_prepass(mm.cc, st)) != TK_OK) return rc;
+    }
+    if (use_pair) return launch_mix_more_pair(c, mm, d, ctas, threads, cdt, st);
+    if (c.conv) return launch_mix_more_kernels<true>(c, mm, ta, tb, ctas, threads, cdt, st);
+    return launch_mix_more_kernels<false>(c, mm, ta, tb, ctas, threads, cdt, st);
 }
 
 // number of solo arguments of each kind (before the six geometry ints)

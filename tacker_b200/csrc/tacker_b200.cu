@@ -46,6 +46,8 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "mix_cp_ppt")) return &g_opt.mix_cp_ppt;
     if (!std::strcmp(name, "mriq_accurate")) return &g_opt.mriq_accurate;
     if (!std::strcmp(name, "mrif_accurate")) return &g_opt.mrif_accurate;
+    if (!std::strcmp(name, "sgemm_split")) return &g_opt.sgemm_split;
+    if (!std::strcmp(name, "cutcp_split")) return &g_opt.cutcp_split;
     if (!std::strcmp(name, "cp_split")) return &g_opt.cp_split;
     if (!std::strcmp(name, "mriq_split")) return &g_opt.mriq_split;
     if (!std::strcmp(name, "mriq_vpt")) return &g_opt.mriq_vpt;

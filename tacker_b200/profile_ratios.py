@@ -125,15 +125,15 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096, only=None) -> dict:
     cregions = torch.zeros(2 * 26 * 26 * 512, device="cuda")
     cds.update({
         "sgemm": (lambda s=0, e=None: ops.gptb_sgemm(sa.data_ptr(), sb.data_ptr(), sc.data_ptr(), 4096, 4128, 4064, start=s,
-                                                     end=e, grid=sms, block=512), 32 * 258, (1, 512), (192, 288, 384)),
+                                                     end=e, grid=sms, block=512), 32 * 258, (1, 512), (256, 384)),
         "lbm": (lambda s=0, e=None: ops.gptb_lbm(lsrc.data_ptr() + 4 * lmargin, ldst.data_ptr() + 4 * lmargin, 128, 128, 128,
                                                  start=s, end=e, grid=sms * 2, block=512), 128 * 128, (2, 512),
-                (448, 576, 832)),
+                (576, 832)),
         "fft": (lambda s=0, e=None: ops.gptb_fft(fdata.data_ptr(), 10240, start=s, end=e, grid=sms * 2, block=512), 10240,
                 (2, 512), (320, 576, 832)),
         "cutcp": (lambda s=0, e=None: ops.gptb_cutcp(bdx, bdy, czero, 0.5, 144.0, float(np.float32(1.0) / np.float32(144.0)),
                                                      cregions.data_ptr(), dnbr.data_ptr(), cnbr.shape[0], 26, 26, 2, start=s,
-                                                     end=e, grid=sms * 2, block=512), 26 * 26 * 2, (2, 512), (448, 576, 832)),
+                                                     end=e, grid=sms * 2, block=512), 26 * 26 * 2, (2, 512), (576, 832)),
     })
     if only:
         cds = {k: v for k, v in cds.items() if k in only}

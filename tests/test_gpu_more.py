@@ -21,6 +21,20 @@ def _st(torch):
     return torch.cuda.current_stream().cuda_stream
 
 
+@pytest.fixture(autouse=True)
+def unsplit_items(cuda):
+    """The bit-for-bit comparisons need work items that keep the reference's order of additions (launches as small as
+    these would otherwise be cut into items that add partial sums in no fixed order); the split forms have tests of
+    their own below."""
+    from tacker_b200 import ops
+
+    ops.set_option("sgemm_split", 0)
+    ops.set_option("cutcp_split", 0)
+    yield
+    ops.set_option("sgemm_split", -1)
+    ops.set_option("cutcp_split", -1)
+
+
 def _golden(name):
     path = os.path.join(GOLDEN, f"ref_{name}.npz")
     assert os.path.exists(path), f"{path} is missing (tests/golden/make_golden_more.py writes it)"
@@ -74,6 +88,22 @@ def test_sgemm_reference_fixture(cuda, oracle, name):
     a, b, c = sgemm_inputs(oracle, M, N, K, seed=int(g["seed"]))
     got = _sgemm(cuda, ops, a, b, c, start=int(g["start"]), end=int(g["end"]))
     assert oracle.bit_mismatches(got, g["out"]) == 0
+
+
+@pytest.mark.parametrize("split", [-1, 8, 24, 64])
+def test_sgemm_split_items(cuda, oracle, split):
+    """Work items that cover a part of K: C is doubled by a kernel of its own, then every item adds 2 x its partial sums."""
+    from tacker_b200 import ops
+
+    M, N, K = 256, 48, 200
+    a, b, c = sgemm_inputs(oracle, M, N, K, seed=9)
+    ops.set_option("sgemm_split", split)
+    got = _sgemm(cuda, ops, a, b, c, start=1, end=5, grid=4, block=128)
+    want = oracle.sgemm_f32(a, b, c.copy(), 1, 5)
+    assert np.array_equal(got != c, want != c)                 # the same blocks, nothing else
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    if split > 0:
+        assert oracle.bit_mismatches(got, want) > 0            # really another order of additions
 
 
 # ------------------------------------------------------------------------------------------ lbm ----
@@ -239,6 +269,27 @@ def test_cutcp_range(cuda, oracle):
             assert not got[rz, ry, rx].any()
 
 
+@pytest.mark.parametrize("split", [-1, 8, 50])
+def test_cutcp_split_items(cuda, oracle, split):
+    """Work items that cover a part of the neighbour list: the regions are zeroed by a kernel of its own, then every item
+    adds its partial sums.  Regions outside the block range keep what they held."""
+    from tacker_b200 import ops
+
+    s = _cutcp_setup(cuda, ops, oracle, 16, 0.5, 12.0, seed=12)
+    g = s["g"]
+    ops.set_option("cutcp_split", 0)
+    exact = _cutcp(cuda, ops, s, start=2, end=7)
+    ops.set_option("cutcp_split", split)
+    pre = cuda.full((g, g, g, 512), 3.5, dtype=cuda.float32, device="cuda")
+    got = _cutcp(cuda, ops, s, start=2, end=7, grid=4, block=256, regions=pre)
+    for p in range(g * g * g):
+        rx, ry, rz = p // (g * g), (p // g) % g, p % g
+        if 2 <= p < 7:
+            assert np.abs(got[rz, ry, rx] - exact[rz, ry, rx]).max() <= 1e-5 * np.abs(exact).max()
+        else:
+            assert (got[rz, ry, rx] == 3.5).all()
+
+
 @pytest.mark.parametrize("name", ["cutcp", "cutcp_256"])
 def test_cutcp_reference_fixture(cuda, oracle, name):
     from tacker_b200 import ops
@@ -251,9 +302,19 @@ def test_cutcp_reference_fixture(cuda, oracle, name):
 
 
 # ---------------------------------------------------------------------------------------- fused ----
+@pytest.fixture(params=[-1, 1], ids=["one_cta", "cta_pairs"])
+def tensor_role(request, cuda):
+    """Both forms of the tensor role inside the fused kernels: on one CTA, and on CTA pairs."""
+    from tacker_b200 import ops
+
+    ops.set_option("mix_pair", request.param)
+    yield request.param
+    ops.set_option("mix_pair", 0)
+
+
 @pytest.mark.parametrize("cd_threads", [64, 256, 512])
 @pytest.mark.parametrize("kind", ["sgemm", "lbm", "fft", "cutcp"])
-def test_fused_with_tzgemm_is_bit_identical_to_solo(cuda, oracle, kind, cd_threads):
+def test_fused_with_tzgemm_is_bit_identical_to_solo(cuda, oracle, kind, cd_threads, tensor_role):
     from tacker_b200 import ops
 
     M, N, K = 512, 512, 128
@@ -312,6 +373,18 @@ def test_fused_with_tzgemm_is_bit_identical_to_solo(cuda, oracle, kind, cd_threa
     assert not res["fused_empty_gemm"][0].any() and np.array_equal(res["fused_empty_gemm"][1][once], res["solo"][1][once])
     assert np.array_equal(res["fused_empty_cd"][0], res["solo"][0])
     assert np.array_equal(res["fused_empty_cd"][1], make().cpu().numpy())
+    if kind in ("sgemm", "cutcp"):      # the default, split work items inside the fused kernel: same values to 1e-5
+        ops.set_option("sgemm_split", -1)
+        ops.set_option("cutcp_split", -1)
+        Cd = cuda.zeros((M, N), dtype=cuda.float32, device="cuda")
+        out = make()
+        tz = ops.gptb_tzgemm(A.data_ptr(), B.data_ptr(), Cd.data_ptr(), M, N, K, alpha=1.0, start=5, end=60, grid=4,
+                             round_dims=False)
+        ops.mix(cdk(out), tz, cd_threads=cd_threads, grid=4).execute(st)
+        cuda.cuda.synchronize()
+        assert ops.device_status() == 0
+        assert np.array_equal(Cd.cpu().numpy(), res["solo"][0])
+        assert np.abs(out.cpu().numpy() - res["solo"][1]).max() <= 1e-5 * np.abs(res["solo"][1]).max()
     ref = oracle.tzgemm_f64(a, b)
     tiles = np.zeros((M // 64, N // 64), bool).ravel()
     tiles[5:60] = True
