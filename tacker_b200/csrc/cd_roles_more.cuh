@@ -17,6 +17,7 @@
 #include <stdint.h>
 
 #include "cd_roles.cuh"
+#include "ptx.cuh"
 
 namespace tk {
 

@@ -557,4 +557,47 @@ static int launch_more_mix(MoreKind kind, void** params, int nparams, const unsi
     return run_mix_more(c, m, grid[0], block[0], static_cast<cudaStream_t>(stream));
 }
 
+// ---- launcher body for kernels of these four roles emitted by the fused-kernel generator -----------------------
+// As generated_mix_launch (host_launch.cuh): the module fixes super-tile width, stage count and the number of
+// CUDA-core warps at compile time; `role_smem` is what its CUDA-core role needs behind the tensor role's stages
+// (sgemm: its rings, fft: its buffers).  `launch` receives everything parsed and encoded.
+template <int BN, int STAGES, typename LaunchFn>
+static int generated_more_launch(MoreKind kind, int cd_warps, int role_smem, void** params, int nparams,
+                                 const unsigned grid[3], void* stream, LaunchFn launch) {
+    const int cd_len = more_solo_args(kind) + 9;
+    int rc = check_params(params, nparams, cd_len + 16);
+    if (rc != TK_OK) return rc;
+    if (grid == nullptr || grid[0] == 0) return TK_ERR_LAUNCH_CONFIG;
+    MoreCall m;
+    if ((rc = parse_more(kind, params, &m)) != TK_OK) return rc;
+    GemmCall c;
+    if ((rc = parse_gemm(params, cd_len, cd_len + 13, cd_len + 15, &c)) != TK_OK) return rc;
+    DeviceInfo* d = nullptr;
+    if ((rc = device_info(&d)) != TK_OK) return rc;
+    c.g.status = d->status_ptr;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool gemm_empty = c.g.start >= c.g.end;
+    if (gemm_empty && m.empty()) return TK_OK;
+    if (gemm_empty) return run_more_solo(m, grid[0], 32u * static_cast<unsigned>(cd_warps), st);
+    if (m.empty()) return run_tzgemm(c, grid[0], st);
+    const unsigned ctas = grid[0] < static_cast<unsigned>(d->sm_count) ? grid[0] : static_cast<unsigned>(d->sm_count);
+    const unsigned threads = kGemmThreads + 32u * static_cast<unsigned>(cd_warps);
+    const int smem = GemmSmem<BN, STAGES>::kBytes + 1024 + role_smem;
+    if (smem > kMaxDynSmem) return TK_ERR_CAPACITY;
+    CUtensorMap ta, tb;
+    if ((rc = make_tmap(&ta, c.A, c.g.M, c.g.K, kGemmBM)) != TK_OK) return rc;
+    if ((rc = make_tmap(&tb, c.B, c.g.N, c.g.K, BN)) != TK_OK) return rc;
+    const long long warps = static_cast<long long>(ctas) * cd_warps;
+    if (kind == MORE_SGEMM) {
+        m.sg.k_per_item = sgemm_split_for(m.sg, warps);
+        if ((rc = sgemm_prepass(m.sg, st)) != TK_OK) return rc;
+    } else if (kind == MORE_CUTCP) {
+        m.cc.nbr_per_item = cutcp_split_for(m.cc, warps);
+        if ((rc = cutcp_prepass(m.cc, st)) != TK_OK) return rc;
+    }
+    rc = launch(ta, tb, c.g, m, ctas, threads, smem, st);
+    if (rc != TK_OK) return rc;
+    return launch_error("generated mix kernel launch");
+}
+
 }  // namespace tk

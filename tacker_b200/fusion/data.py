@@ -35,6 +35,11 @@ KERNELS = {
     "stencil": KernelInfo("stencil", 64, 3 * 1792 + 128, 32, "hbm"),       # >= 3 ring slots per warp
     "cp": KernelInfo("cp", 32, 0, 32, "sfu"),
     "mriq": KernelInfo("mriq", 32, 0, 32, "sfu"),
+    "mrif": KernelInfo("mrif", 32, 0, 32, "sfu"),
+    "sgemm": KernelInfo("sgemm", 96, 3 * 2560, 32, "fma"),                  # a ring of three slots per warp
+    "lbm": KernelInfo("lbm", 64, 0, 32, "hbm"),
+    "fft": KernelInfo("fft", 48, 2048 + 64, 32, "latency"),                 # 2 KB per warp + its share of the 1 KB table
+    "cutcp": KernelInfo("cutcp", 64, 0, 32, "issue"),
 }
 
 

@@ -11,6 +11,23 @@ from __future__ import annotations
 import ctypes as C
 
 
+def lbm_two_writer_mask(nx: int, ny: int, nz: int):
+    """Addresses of the lattice-Boltzmann array (margins included) that two cells write in one step: the 20 elements lie
+    back to back, so what leaves element e through its top face lands where element e + 1 receives through its bottom
+    face.  The reference's kernel has the same two writers and no order between them."""
+    import numpy as np
+
+    cells, m = nx * ny * nz, 2 * nx * ny
+    dx = [0, 0, 0, 1, -1, 0, 0, 1, -1, 1, -1, 0, 0, 0, 0, 1, 1, -1, -1]
+    dy = [0, 1, -1, 0, 0, 0, 0, 1, 1, -1, -1, 1, 1, -1, -1, 0, 0, 0, 0]
+    dz = [0, 0, 0, 0, 0, 1, -1, 0, 0, 0, 0, 1, -1, 1, -1, 1, -1, 1, -1]
+    count = np.zeros(2 * m + 20 * cells, dtype=np.int32)
+    cell = np.arange(cells)
+    for e in range(19):
+        np.add.at(count, m + e * cells + cell + dx[e] + dy[e] * nx + dz[e] * nx * ny, 1)
+    return count > 1
+
+
 def check_module(so_path: str, name: str, cd: str) -> dict:
     import numpy as np
     import torch
@@ -28,11 +45,33 @@ def check_module(so_path: str, name: str, cd: str) -> dict:
     B = (torch.rand(N, K, device="cuda", generator=gen) * 2 - 1).half()
     sms = ops.sm_count()
 
+    cut = None
+    if cd == "cutcp":
+        from ..profile_ratios import cutcp_problem
+
+        cbins, cnbr, cmargin = cutcp_problem(16, 16, 16, seed=3)
+        cut = dict(bins=torch.from_numpy(cbins).cuda(), nbr=torch.from_numpy(cnbr).cuda(), n=cnbr.shape[0],
+                   bdx=cbins.shape[2], bdy=cbins.shape[1], c=cmargin)
+        cut["zero"] = cut["bins"].data_ptr() + 128 * ((cmargin * cut["bdy"] + cmargin) * cut["bdx"] + cmargin)
+
     def cd_kernel(bufs):
         if cd == "stencil":
             return ops.gptb_stencil(0.5, 0.25, bufs[0].data_ptr(), bufs[1].data_ptr(), 192, 12, 10)
         if cd == "cp":
             return ops.gptb_cp(150, 0.125, bufs[1].data_ptr(), bufs[0].data_ptr(), 256, 32)
+        if cd == "mrif":
+            return ops.gptb_mrif(64, bufs[0].data_ptr(), bufs[1].data_ptr(), bufs[2].data_ptr(), bufs[3].data_ptr(),
+                                 bufs[4].data_ptr(), bufs[5].data_ptr(), 1024)
+        if cd == "sgemm":
+            return ops.gptb_sgemm(bufs[0].data_ptr(), bufs[1].data_ptr(), bufs[2].data_ptr(), 256, 64, 48)
+        if cd == "lbm":
+            return ops.gptb_lbm(bufs[0].data_ptr() + 4 * 2 * 64 * 4, bufs[1].data_ptr() + 4 * 2 * 64 * 4, 64, 4, 5)
+        if cd == "fft":
+            return ops.gptb_fft(bufs[0].data_ptr(), 48)
+        if cd == "cutcp":
+            inv = float(np.float32(1.0) / np.float32(144.0))
+            return ops.gptb_cutcp(cut["bdx"], cut["bdy"], cut["zero"], 0.5, 144.0, inv, bufs[0].data_ptr(),
+                                  cut["nbr"].data_ptr(), cut["n"], 2, 2, 2)
         return ops.gptb_mriq(64, bufs[0].data_ptr(), bufs[1].data_ptr(), bufs[2].data_ptr(), bufs[3].data_ptr(),
                              bufs[4].data_ptr(), bufs[5].data_ptr(), 1024)
 
@@ -45,8 +84,21 @@ def check_module(so_path: str, name: str, cd: str) -> dict:
             atoms = torch.rand(150, 4, device="cuda", generator=g) * 8
             atoms[:, 2] = (atoms[:, 2] - 4) ** 2 + 0.5
             return [atoms.contiguous(), torch.zeros(32, 256, device="cuda")], 1
+        if cd == "sgemm":
+            return [torch.rand(48, 256, device="cuda", generator=g), torch.rand(48, 64, device="cuda", generator=g),
+                    torch.rand(64, 256, device="cuda", generator=g)], 2
+        if cd == "lbm":
+            n = 20 * 64 * 4 * 5 + 2 * 2 * 64 * 4
+            return [torch.rand(n, device="cuda", generator=g), torch.rand(n, device="cuda", generator=g)], 1
+        if cd == "fft":
+            return [torch.rand(48, 256, 2, device="cuda", generator=g) * 2 - 1], 0
+        if cd == "cutcp":
+            return [torch.zeros(2, 2, 2, 512, device="cuda")], 0
         xyz = [torch.rand(1024, device="cuda", generator=g) * 64 - 32 for _ in range(3)]
-        kv = torch.rand(64, 4, device="cuda", generator=g) - 0.5
+        if cd == "mrif":
+            kv = torch.rand(5 * 64, device="cuda", generator=g) - 0.5
+        else:
+            kv = torch.rand(64, 4, device="cuda", generator=g) - 0.5
         return xyz + [torch.zeros(1024, device="cuda"), torch.zeros(1024, device="cuda"), kv.contiguous()], 3
 
     st = torch.cuda.current_stream().cuda_stream
@@ -75,13 +127,19 @@ def check_module(so_path: str, name: str, cd: str) -> dict:
             launch_generated(cdk, tz, cd_range=(0, 0), tz_range=(0, 0))
         torch.cuda.synchronize()
         results[mode] = (Cm.cpu().numpy(), bufs[out_idx].cpu().numpy())
+    if cd == "lbm":  # compare the addresses with one writer
+        once = ~lbm_two_writer_mask(64, 4, 5)
+        for mode in results:
+            results[mode] = (results[mode][0], results[mode][1][once])
     same_gemm = bool(np.array_equal(results["solo"][0], results["generated"][0]))
     same_cd = bool(np.array_equal(results["solo"][1], results["generated"][1]))
     # Coulomb / MRI-Q items that cover a part of the atom / sample list add their partial sums with reductions in
     # no fixed order: those outputs are held to the operators' 1e-5 tolerance instead of bit identity
     scale = float(np.abs(results["solo"][1]).max())
     cd_err = float(np.abs(results["solo"][1] - results["generated"][1]).max()) / (scale if scale > 0 else 1.0)
-    cd_ok = same_cd if cd == "stencil" else cd_err <= 1e-5
+    # bit identity where every output has one fixed sequence of operations and one writer; lbm has addresses with two
+    # writers (held to the tolerance), the others may run on work items that add partial sums in no fixed order
+    cd_ok = same_cd if cd in ("stencil", "fft") else cd_err <= 1e-5
     halves_err = float(np.abs(results["solo"][1] - results["halves"][1]).max()) / (scale if scale > 0 else 1.0)
     halves_ok = bool(np.array_equal(results["solo"][0], results["halves"][0])) and halves_err <= 1e-5
     same_gemm = same_gemm and halves_ok

@@ -40,7 +40,7 @@ def test_emitted_source_compiles_and_exports_its_launcher(tmp_path):
 def test_generated_modules_match_the_solo_kernels(cuda, tmp_path):
     from tacker_b200.fusion import data, gen_run, gen_test
 
-    for cd, w in (("stencil", 12), ("cp", 8), ("mriq", 16)):
+    for cd, w in (("stencil", 12), ("cp", 8), ("mriq", 16), ("mrif", 12), ("sgemm", 8), ("lbm", 12), ("fft", 8), ("cutcp", 16)):
         c = [x for x in data.fuse_kernel_info(cd) if x.r2 == w][0]
         so = gen_run.compile_module(gen_run.emit(c, str(tmp_path)))
         r = gen_test.check_module(so, c.name, cd)
