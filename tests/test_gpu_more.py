@@ -405,3 +405,89 @@ def test_ori_launch_shape(cuda, oracle):
     cuda.cuda.synchronize()
     assert oracle.bit_mismatches(dC.cpu().numpy(), oracle.sgemm_f32(a, b, c.copy())) == 0
     assert np.abs(dd.cpu().numpy() - oracle.fft256_f32(d.copy())).max() <= 1e-4
+
+
+# ------------------------------------------------------------------------- the reference's sizes ----
+def test_sgemm_reference_size_sampled(cuda, oracle):
+    """4096 x 4128 x 4064 (src/ori_kernel/sgemm_kernel.cu:85-87): sampled outputs against binary64 dot products, and the
+    default (split) items against the unsplit ones."""
+    from tacker_b200 import ops
+
+    M, N, K = 4096, 4128, 4064
+    gen = cuda.Generator(device="cuda").manual_seed(5)
+    A = cuda.rand(K, M, device="cuda", generator=gen)
+    B = cuda.rand(K, N, device="cuda", generator=gen)
+    C0 = cuda.rand(N, M, device="cuda", generator=gen)
+    outs = {}
+    for split in (0, -1):
+        ops.set_option("sgemm_split", split)
+        C = C0.clone()
+        ops.gptb_sgemm(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, grid=ops.sm_count(), block=512).execute(_st(cuda))
+        cuda.cuda.synchronize()
+        outs[split] = C
+    rng = np.random.default_rng(1)
+    ms, ns = rng.integers(0, M, 300), rng.integers(0, N, 300)
+    a = A[:, ms].double().cpu().numpy()
+    b = B[:, ns].double().cpu().numpy()
+    want = 2.0 * C0[ns, ms].double().cpu().numpy() + 2.0 * (a * b).sum(axis=0)
+    for split, C in outs.items():
+        got = C[ns, ms].cpu().numpy()
+        # 4064 binary32 additions in sequence (the reference's order): a few units of 1e-6 relative
+        assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max(), split
+    assert float((outs[0] - outs[-1]).abs().max()) <= 1e-5 * float(outs[0].abs().max())
+
+
+def test_fft_reference_size(cuda, oracle):
+    """10240 transforms (FFT_B, src/header/fft_header.h:13) against numpy's, and Parseval's sum on every one."""
+    from tacker_b200 import ops
+
+    d = fft_inputs(oracle, 10240, seed=77)
+    got = _fft(cuda, ops, d, grid=296, block=512)
+    want = np.fft.fft(d[..., 0].astype(np.float64) + 1j * d[..., 1].astype(np.float64), axis=1)
+    scale = float(np.abs(want).max())
+    assert np.abs(got[..., 0] + 1j * got[..., 1] - want).max() <= 1e-5 * scale
+    energy_in = (d.astype(np.float64) ** 2).sum(axis=(1, 2))
+    energy_out = (got.astype(np.float64) ** 2).sum(axis=(1, 2)) / 256.0
+    assert np.abs(energy_out - energy_in).max() <= 1e-5 * energy_in.max()
+
+
+def test_cutcp_reference_size_sampled(cuda, oracle):
+    """The reference's launch (26 x 26 x 2 regions of a 208-point lattice, 335 neighbour bins): a sample of regions against
+    the CPU checker, unsplit items bit for bit against split ones to 1e-5, and superposition (the potential of all atoms =
+    the potential of the even bins' atoms + that of the odd bins')."""
+    from tacker_b200 import ops
+
+    atoms = cutcp_inputs(oracle, 208, 208, 16, 0.5, seed=31)
+    dims = oracle.cutcp_bin_dims(208, 208, 16, 0.5, 12.0)
+    nbr = oracle.cutcp_neighbours(0.5, 12.0)
+    bins, _ = oracle.cutcp_bin_atoms(atoms, dims)
+    dN = cuda.zeros((nbr.shape[0], 4), dtype=cuda.int32, device="cuda")
+    ops.cutcp_pack_neighbours(to_dev(cuda, nbr).data_ptr(), nbr.shape[0], dN.data_ptr(), _st(cuda))
+    c = dims[3]
+
+    def run(b, split):
+        dB = to_dev(cuda, b)
+        zero = dB.data_ptr() + 128 * ((c * dims[1] + c) * dims[0] + c)
+        dR = cuda.zeros((2, 26, 26, 512), dtype=cuda.float32, device="cuda")
+        ops.set_option("cutcp_split", split)
+        ops.gptb_cutcp(dims[0], dims[1], zero, 0.5, 144.0, float(np.float32(1.0) / np.float32(144.0)), dR.data_ptr(),
+                       dN.data_ptr(), nbr.shape[0], 26, 26, 2, grid=296, block=512).execute(_st(cuda))
+        cuda.cuda.synchronize()
+        return dR.cpu().numpy()
+
+    exact, split = run(bins, 0), run(bins, -1)
+    scale = float(np.abs(exact).max())
+    assert np.abs(exact - split).max() <= 1e-5 * scale
+    want = np.zeros_like(exact)
+    picks = [0, 1, 27, 700, 1351]
+    for p in picks:
+        oracle.cutcp_f32(bins, dims, nbr, 0.5, 12.0, want, 26, 26, 2, p, p + 1)
+    for p in picks:
+        rx, ry, rz = p // 52, (p // 2) % 26, p % 2
+        assert np.abs(exact[rz, ry, rx] - want[rz, ry, rx]).max() <= 2e-5 * scale
+    even = bins.copy()
+    odd = bins.copy()
+    parity = (np.indices(bins.shape[:3]).sum(axis=0) % 2).astype(bool)
+    even[parity] = 0.0
+    odd[~parity] = 0.0
+    assert np.abs(run(even, 0) + run(odd, 0) - exact).max() <= 1e-5 * scale
