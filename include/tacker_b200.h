@@ -360,10 +360,12 @@ int tk_coulomb_compute(const float* atoms_xyzq, int numatoms, float zplane, floa
 /* ---- host-buffer pair (what an end-to-end caller times) ---------------------------------------------
  * C = alpha * A * B^T together with `sweeps` ping-pong stencil sweeps of A0: the first two sweeps are fused
  * launches that each co-run with half of the GEMM's tiles, the remaining sweeps run alone.  All five buffers are HOST memory (pinned
- * for full copy speed); inputs are uploaded on an internal stream (so that the upload of one call overlaps the
- * download of the previous one), kernels and downloads run on `stream`; the call returns once everything is
- * enqueued, and the results are in the host buffers once `stream` is synchronised.  Calls must use one
- * workspace per stream.  Mirrors what the reference's harness does around a
+ * for full copy speed).  Uploads, kernels and downloads run on three streams of the library and the workspace holds
+ * two sets of device buffers used in turn, so the upload and the kernels of one call overlap the downloads of the
+ * previous one (the downloads are the longer direction); `stream` joins at the end: the call returns once
+ * everything is enqueued, and the results are in the host buffers once `stream` is synchronised.  The host input
+ * buffers must be ready when the call is made (the uploads do not wait for `stream`), and host buffers must not be
+ * reused for two calls in flight.  Mirrors what the reference's harness does around a
  * fused launch: cudaMemcpy of the inputs in initParams (src/ori_kernel/stencil_kernel.cu:143-160), the
  * launch (src/TaskManager.cu:285), and the copy-back its test mains do (fusion/code/cp_code.py:99-121).
  * workspace: device memory of at least tk_pair_tzgemm_stencil_workspace() bytes, 256-byte aligned. */
