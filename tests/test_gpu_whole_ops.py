@@ -91,3 +91,38 @@ def test_pair_host_rejected_shape_queues_nothing(cuda, oracle):
                                      hOut.data_ptr(), nx, ny, nz, 2, 128, ws.data_ptr(), nbytes, st)
     cuda.cuda.synchronize()
     assert bool((ws == 0xA5).all())
+
+
+def test_pair_host_calls_in_flight_keep_their_own_results(cuda, oracle):
+    """Four calls queued back to back with different inputs and their own host buffers: the library overlaps their
+    uploads, kernels and downloads over two sets of device buffers (the third call reuses the first call's set), and every
+    call's results are its own."""
+    from tacker_b200 import ops
+
+    M, N, K = 256, 128, 64
+    nx, ny, nz, sweeps = 64, 8, 6, 2
+    nbytes = ops.pair_tzgemm_stencil_workspace(M, N, K, nx, ny, nz)
+    ws = cuda.empty(nbytes, dtype=cuda.uint8, device="cuda")
+    st = cuda.cuda.current_stream().cuda_stream
+    calls = []
+    for i in range(4):
+        a_bits, a, b_bits, b = gemm_inputs(oracle, M, N, K, seed=20 + i)
+        A0 = stencil_inputs(oracle, nx, ny, nz, seed=30 + i)
+        h = dict(a=a, b=b, A0=A0,
+                 hA=cuda.from_numpy(a_bits.view(np.float16).copy()).pin_memory(),
+                 hB=cuda.from_numpy(b_bits.view(np.float16).copy()).pin_memory(),
+                 hA0=cuda.from_numpy(A0.copy()).pin_memory(),
+                 hC=cuda.zeros((M, N), dtype=cuda.float32).pin_memory(),
+                 hOut=cuda.zeros((nz, ny, nx), dtype=cuda.float32).pin_memory())
+        calls.append(h)
+    for h in calls:
+        ops.pair_tzgemm_stencil_host(h["hA"].data_ptr(), h["hB"].data_ptr(), h["hC"].data_ptr(), M, N, K, 1.0, 0.5, 0.25,
+                                     h["hA0"].data_ptr(), h["hOut"].data_ptr(), nx, ny, nz, sweeps, 128, ws.data_ptr(), nbytes,
+                                     st)
+    cuda.cuda.synchronize()
+    assert ops.device_status() == 0
+    for h in calls:
+        x, y = h["A0"].copy(), h["A0"].copy()
+        want = oracle.stencil_jacobi_f32(0.5, 0.25, x, y, sweeps, contract=1)
+        assert oracle.bit_mismatches(h["hOut"].numpy(), want) == 0
+        assert np.abs(h["hC"].numpy() - oracle.tzgemm_f64(h["a"], h["b"])).max() <= 1e-3 * K
