@@ -279,7 +279,14 @@ __device__ __forceinline__ void lbm_role(const LbmArgs& g, int* counter, const i
     const int segs = g.nx / 32;
     const long long nitems = static_cast<long long>(g.end - g.start) * segs;
     const long long plane = static_cast<long long>(g.nx) * g.ny;
-    for (long long item = claim_item(counter, lane, cta, ncta); item < nitems; item = claim_item(counter, lane, cta, ncta)) {
+    // Items are dealt to a CTA in runs of 16: its warps work on 16 consecutive 32-cell pieces at a time, i.e. on 2 KB
+    // of each of the 39 arrays, instead of on pieces 128 bytes long that lie ncta pieces apart.
+    constexpr long long kRun = 16;
+    const long long nitems_padded = (nitems + kRun * ncta - 1) / (kRun * ncta) * (kRun * ncta);
+    for (long long raw = claim_item(counter, lane, cta, ncta); raw < nitems_padded; raw = claim_item(counter, lane, cta, ncta)) {
+        const long long k = raw / ncta;  // this CTA's k-th claim
+        const long long item = ((k / kRun) * ncta + cta) * kRun + k % kRun;
+        if (item >= nitems) continue;
         const int p = g.start + static_cast<int>(item / segs), seg = static_cast<int>(item % segs);
         const int y = p % g.ny, z = (p / g.ny) % g.nz;
         const long long cell = seg * 32 + lane + static_cast<long long>(y) * g.nx + z * plane;
