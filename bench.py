@@ -352,6 +352,22 @@ def run_ours(args):
     except Exception as e:  # the yardstick must never take the benchmark down
         us_lib, lib_out = None, f"unavailable: {type(e).__name__}"
     us_sweep = t_of([cd_kernel(i) for i in range(SWEEPS)]) / SWEEPS
+
+    # yardstick only: a plain device copy of one grid (the same 64 MiB read and 64 MiB written as one sweep), on
+    # buffers of its own
+    def grid_copy_us():
+        scratch = (torch.empty_like(g0), torch.empty_like(g0))
+        reps = 2 if args.quick else 20
+
+        def fn():
+            for i in range(reps):
+                scratch[(i + 1) & 1].copy_(scratch[i & 1])
+        with torch.cuda.stream(stream):
+            return timed(make_graph(fn), 3, 2) / reps * 1e3
+    try:
+        us_copy = grid_copy_us()
+    except Exception:  # the yardstick must never take the benchmark down
+        us_copy = None
     us_fused_launch = {}
     for f in (SWEEPS, 2, 1):
         lo, hi = 0, TILES // f
@@ -526,6 +542,7 @@ def run_ours(args):
                     "library_gemm_same_shape": {"us": None if us_lib is None else round(us_lib, 2), "output": lib_out,
                                                 "tzgemm_vs_library": None if us_lib is None else round(us_lib / us_gemm, 3)},
                     "stencil_gbs": round(SWEEP_BYTES / (us_sweep * 1e-6) / 1e9, 1),
+                    "device_copy_of_one_grid": None if us_copy is None else round(us_copy, 2),
                     "fused_launch_us": {f"sweep+{TILES // f}_tiles": round(v, 2) for f, v in us_fused_launch.items()}},
         "ratio_sweep": sweep, "pairs": pairs, "clocks": clocks,
         "e2e": {"value": world * 1e3 / ms_e2e, "unit": "pairs/s", "h2d_bytes_per_step": h2d * PAIRS_PER_STEP,

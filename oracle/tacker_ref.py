@@ -152,3 +152,60 @@ def cutcp(nbr_host: np.ndarray, bx, by, c, bins_dev, h, cutoff2, inv_cutoff2, re
     return lib_more().ref_cutcp(nbr_host.ctypes.data_as(C.POINTER(C.c_int)), nbr_host.shape[0], bx, by, c, _vp(bins_dev),
                                 C.c_float(h), C.c_float(cutoff2), C.c_float(inv_cutoff2), _vp(regions_dev), gx, gy, gz,
                                 start, end, grid, _vp(stream))
+
+
+# ---- the unfused ori_* kernels (oracle/_ref/libtacker_ref_ori.so) ----------------------------------------------
+LIB_ORI_PATH = os.path.join(_HERE, "_ref", "libtacker_ref_ori.so")
+_lib_ori = None
+
+
+def ori_available() -> bool:
+    return os.path.exists(LIB_ORI_PATH)
+
+
+def lib_ori() -> C.CDLL:
+    global _lib_ori
+    if _lib_ori is None:
+        _lib_ori = C.CDLL(LIB_ORI_PATH)
+    return _lib_ori
+
+
+def ori_stencil(c0, c1, A0, Anext, nx, ny, nz, stream=0) -> int:
+    return lib_ori().ref_ori_stencil(C.c_float(c0), C.c_float(c1), _vp(A0), _vp(Anext), nx, ny, nz, _vp(stream))
+
+
+def ori_cp(packed_host: np.ndarray, spacing, lattice, gx, gy, stream=0) -> int:
+    packed_host = np.ascontiguousarray(packed_host, dtype=np.float32)
+    return lib_ori().ref_ori_cp(_f32p(packed_host), packed_host.shape[0], C.c_float(spacing), _vp(lattice), gx, gy,
+                                _vp(stream))
+
+
+def ori_mriq(kvals_host: np.ndarray, x, y, z, Qr, Qi, numX, stream=0) -> int:
+    kvals_host = np.ascontiguousarray(kvals_host, dtype=np.float32)
+    return lib_ori().ref_ori_mriq(_f32p(kvals_host), kvals_host.shape[0], _vp(x), _vp(y), _vp(z), _vp(Qr), _vp(Qi), numX,
+                                  _vp(stream))
+
+
+def ori_mrif(kvals_aos_host: np.ndarray, x, y, z, outR, outI, numX, stream=0) -> int:
+    kvals_aos_host = np.ascontiguousarray(kvals_aos_host, dtype=np.float32)
+    return lib_ori().ref_ori_mrif(_f32p(kvals_aos_host), kvals_aos_host.shape[0], _vp(x), _vp(y), _vp(z), _vp(outR),
+                                  _vp(outI), numX, _vp(stream))
+
+
+def ori_sgemm(A, B, Cm, M, N, K, stream=0) -> int:
+    return lib_ori().ref_ori_sgemm(_vp(A), _vp(B), _vp(Cm), M, N, K, _vp(stream))
+
+
+def ori_lbm(src, dst, stream=0) -> int:
+    return lib_ori().ref_ori_lbm(_vp(src), _vp(dst), _vp(stream))
+
+
+def ori_fft(data, nfft, stream=0) -> int:
+    return lib_ori().ref_ori_fft(_vp(data), nfft, _vp(stream))
+
+
+def ori_cutcp(nbr_host: np.ndarray, bx, by, c, bins_dev, h, cutoff2, inv_cutoff2, regions_dev, gx, gy, gz, stream=0) -> int:
+    nbr_host = np.ascontiguousarray(nbr_host, dtype=np.int32)
+    return lib_ori().ref_ori_cutcp(nbr_host.ctypes.data_as(C.POINTER(C.c_int)), nbr_host.shape[0], bx, by, c,
+                                   _vp(bins_dev), C.c_float(h), C.c_float(cutoff2), C.c_float(inv_cutoff2),
+                                   _vp(regions_dev), gx, gy, gz, _vp(stream))
