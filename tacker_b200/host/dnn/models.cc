@@ -291,6 +291,8 @@ Resnet50::Resnet50(int numClasses) : DnnTask(1, "resnet50") {
         H /= 2, W /= 2;
     }
     x = dense(x, 1, C, numClasses, 0);
+    result = x;
+    resultCount = static_cast<size_t>(numClasses);
 }
 
 // ------------------------------------------------------------------- BERT ----
@@ -358,6 +360,8 @@ Bert::Bert(int layers, int batch_, int seq_) : DnnTask(2, "bert"), batch(batch_)
         const float* h2 = dense(h1, rows, ffn, hidden, 0);
         x = layernorm(addTo(h2, x, rows, hidden, 0), rows, hidden);
     }
+    result = x;  // the last layer's hidden states [batch * seq][hidden]
+    resultCount = static_cast<size_t>(rows) * hidden;
 }
 
 Task* createTask(const std::string& taskName) {

@@ -15,8 +15,8 @@ public:
     DnnTask(int id, const std::string& name) : Task(id, name) {}
     ~DnnTask() override;
     void initExecution() override;  // upload the input of one query
-    // the task's result on the device after a pass: `resultCount` floats (VGG16 / ResNet-50: the class scores
-    // before the softmax, then the probabilities; BERT: the last hidden state)
+    // the task's result on the device after a pass: `resultCount` floats (VGG16: the class scores before the
+    // softmax, then the probabilities; ResNet-50: the class scores; BERT: the last layer's hidden states)
     const float* result = nullptr;
     size_t resultCount = 0;
     std::vector<float> downloadResult(stream_t stream);

@@ -102,6 +102,46 @@ def test_vgg16_scores_match_the_cpu_forward(cuda, oracle, tmp_path):
     assert abs(float(got[1000:].sum()) - 1.0) <= 1e-4
 
 
+def _dump_of(model, tmp_path):
+    import numpy as np
+
+    dump = tmp_path / (model + "_result.bin")
+    out = subprocess.run([_aker(), "-s", "aker", "-m", model, "-c", os.path.join(HOST, "config"), "--dump-output",
+                          str(dump), "--colocate", "0.2"], capture_output=True, text=True, timeout=900, cwd=tmp_path)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    return np.fromfile(dump, dtype=np.float32)
+
+
+def test_resnet50_scores_match_the_cpu_forward(cuda, oracle, tmp_path):
+    """ResNet-50 end to end (53 convolutions of four shapes, 16 residual additions, one dense layer): the class scores
+    of `aker` against a numpy forward of the same seeded network, within 1e-2 of the largest score."""
+    import numpy as np
+
+    import resnet50_numpy
+
+    got = _dump_of("resnet50", tmp_path)
+    want = resnet50_numpy.forward(oracle)
+    assert got.size == want.size == 1000 and np.isfinite(got).all()
+    scale = float(np.abs(want).max())
+    assert scale > 0 and np.abs(got - want).max() <= 1e-2 * scale
+    assert int(np.argmax(got)) == int(np.argmax(want))
+
+
+def test_bert_hidden_states_match_the_cpu_forward(cuda, oracle, tmp_path):
+    """BERT-base end to end (12 layers, batch 8, 128 tokens: dense layers, batched attention products, softmax, GELU,
+    layer normalisation): the last hidden states of `aker` against a numpy forward of the same seeded encoder."""
+    import numpy as np
+
+    import bert_numpy
+
+    got = _dump_of("bert", tmp_path)
+    want = bert_numpy.forward(oracle)
+    assert got.size == want.size == 8 * 128 * 768 and np.isfinite(got).all()
+    scale = float(np.abs(want).max())
+    err = np.abs(got.reshape(want.shape) - want)
+    assert err.max() <= 2e-2 * scale and float(np.sqrt((err ** 2).mean())) <= 2e-3 * scale
+
+
 def test_model_from_description_and_constant_files(cuda, tmp_path):
     """A model read from a description with NNFusion-style constant files (raw fp32: filters [3][3][Cin][Cout], dense
     weights [in][out]) -- what the reference's generated classes do with Constant_<n>_0.bin
