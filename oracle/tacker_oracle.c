@@ -724,7 +724,8 @@ TKO_API void tko_lbm_f32(const float *src, float *dst, int nx, int ny, int nz, i
 /*   (the quotient in binary64), the pair is replaced by (sum, difference)    */
 /*   and written to expand(j, Ns, 2) + r Ns; the next pass reads j, j + 128.  */
 /*   The complex product is (a.x b.x - a.y b.y, a.x b.y + a.y b.x); contract  */
-/*   = 1 fuses each as fma(a, b, +-(c d)).  Point 0 is multiplied by (1, 0)   */
+/*   = 1 fuses them as nvcc does in the reference's build: fma(a.x, b.x,      */
+/*   -(a.y b.y)) and fma(a.y, b.x, a.x b.y).  Point 0 is multiplied by (1, 0)  */
 /*   like every other, which only matters for signed zeros.                   */
 /* ------------------------------------------------------------------------- */
 #define TKO_FFT_N 256
@@ -742,7 +743,7 @@ TKO_API void tko_fft256_f32(float *data, int nfft, int start, int end, int contr
                 float x0r = a[2 * j], x0i = a[2 * j + 1];
                 float x1r = a[2 * (j + 128)], x1i = a[2 * (j + 128) + 1];
                 float tr, ti;
-                if (contract) { tr = fmaf(x1r, wr, -(x1i * wi)); ti = fmaf(x1r, wi, x1i * wr); }
+                if (contract) { tr = fmaf(x1r, wr, -(x1i * wi)); ti = fmaf(x1i, wr, x1r * wi); }
                 else { tr = x1r * wr - x1i * wi; ti = x1r * wi + x1i * wr; }
                 int idx = (j / Ns) * Ns * 2 + (j % Ns);
                 b[2 * idx] = x0r + tr; b[2 * idx + 1] = x0i + ti;

@@ -321,13 +321,19 @@ __device__ __forceinline__ void lbm_role(const LbmArgs& g, int* counter, const i
 }
 
 // =====================================================================================
-// fft.  A warp transforms one batch entry of 256 complex points in place, radix 2, eight passes, through a buffer of
-// its own in shared memory (2 KB): in every pass butterfly j = 0 .. 127 reads points j and j + 128, multiplies the
-// second by w = (cos a, sin a), a = float(-2 pi (j % Ns) / (2 Ns)) with the quotient in binary64, and writes sum and
-// difference to expand(j, Ns, 2) and + Ns -- the reference's schedule (src/gptb_kernel/fft_kernel.cu:27-41) with four
-// butterflies per lane.  a only takes the values float(-2 pi t / 256), t = 0 .. 127 (the binary64 quotients agree
-// exactly because Ns is a power of two), so the role fills a 128-entry table with the same cosf / sinf calls once
-// and every pass reads w from it.
+// fft.  A warp transforms one batch entry of 256 complex points in place with the reference's radix-2 Stockham
+// schedule (src/gptb_kernel/fft_kernel.cu:27-41): in pass Ns = 1, 2, .., 128 butterfly j = 0 .. 127 reads points j
+// and j + 128, multiplies the second by w = (cos a, sin a), a = float(-2 pi (j % Ns) / (2 Ns)) with the quotient in
+// binary64, and writes sum and difference to expand(j, Ns, 2) and + Ns.  a only takes the values float(-2 pi t / 256),
+// t = 0 .. 127 (the binary64 quotients agree exactly because Ns is a power of two), so the role fills a 128-entry
+// table (per pass) with the same cosf / sinf calls once and every pass reads w from it.
+//
+// A pass takes the top bit of the point index as the butterfly dimension and re-inserts the result bit at position
+// log2 Ns, so three consecutive passes only combine points that differ in the top three index bits: the eight points
+// lane + 32 q that a lane holds anyway.  The eight passes therefore run as 3 + 3 + 2 passes in registers with two
+// exchanges through a warp-private buffer in shared memory (instead of eight round trips), the points come from
+// global memory straight into registers and leave from registers.  Every butterfly is the reference's, operation for
+// operation (the product is spelled with the contractions nvcc applies to it), so the result is bit-identical.
 // =====================================================================================
 struct FftArgs {
     float2* data;
@@ -335,51 +341,99 @@ struct FftArgs {
     int start, end;
 };
 
-constexpr int kFftTwiddleBytes = 128 * 8;
+// twiddles per pass, packed: entry (Ns - 1) + lo is w for j % Ns = lo, so that the lanes of a warp read neighbouring
+// entries in every pass (one table of 128 angles would be read with strides of up to 128 bytes)
+constexpr int kFftTwiddleBytes = 256 * 8;
 constexpr int kFftWarpBytes = 256 * 8;
 __host__ __device__ constexpr int fft_role_smem(int warps) { return kFftTwiddleBytes + warps * kFftWarpBytes; }
+
+// where point p lives in the warp's exchange buffer: the low four bits are mixed with bits 4..6 so that the writes
+// of both exchanges (strides of 8 points between lanes) and the reads (consecutive points) are free of bank conflicts
+__device__ __forceinline__ int fft_slot(const int p) { return p ^ ((p >> 4) & 7) ^ ((p >> 3) & 8); }
+__device__ __forceinline__ int fft_rev3(const int i) { return ((i & 1) << 2) | (i & 2) | (i >> 2); }
+
+// (a, b) <- (a + w b, a - w b)
+__device__ __forceinline__ void fft_bfly(float2& a, float2& b, const float2 w) {
+    // the two contractions nvcc applies to the reference's a.x*b.x - a.y*b.y and a.x*b.y + a.y*b.x (src/header/fft_header.h:20),
+    // found by comparing the four possible pairs with the reference's output bit for bit
+    const float tr = __fmaf_rn(b.x, w.x, -__fmul_rn(b.y, w.y));
+    const float ti = __fmaf_rn(b.y, w.x, __fmul_rn(b.x, w.y));
+    const float2 sum = make_float2(__fadd_rn(a.x, tr), __fadd_rn(a.y, ti));
+    b = make_float2(__fsub_rn(a.x, tr), __fsub_rn(a.y, ti));
+    a = sum;
+}
+
+// Passes Ns = 2^S, 2^(S+1), 2^(S+2) on the points e[q] = (index bits 7..5 = q, the rest fixed); lo0 = the low S index
+// bits.  Afterwards slot i = (tA tB tC) holds the point whose three new index bits above lo0 are (tC tB tA).
+template <int S>
+__device__ __forceinline__ void fft_passes3(float2 (&e)[8], const float2* __restrict__ tw, const int lo0) {
+    {
+        const float2 w = tw[(1 << S) - 1 + lo0];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) fft_bfly(e[i], e[i + 4], w);
+    }
+#pragma unroll
+    for (int tA = 0; tA < 2; ++tA) {
+        const float2 w = tw[(2 << S) - 1 + tA * (1 << S) + lo0];
+        fft_bfly(e[4 * tA], e[4 * tA + 2], w);
+        fft_bfly(e[4 * tA + 1], e[4 * tA + 3], w);
+    }
+#pragma unroll
+    for (int tA = 0; tA < 2; ++tA)
+#pragma unroll
+        for (int tB = 0; tB < 2; ++tB) {
+            const float2 w = tw[(4 << S) - 1 + tB * (2 << S) + tA * (1 << S) + lo0];
+            fft_bfly(e[4 * tA + 2 * tB], e[4 * tA + 2 * tB + 1], w);
+        }
+}
 
 // smem: fft_role_smem(nw) bytes, 16-byte aligned.  t / nt: thread index within the role and its thread count.
 __device__ __forceinline__ void fft_role(const FftArgs& g, uint8_t* smem, const int t, const int nt, const int cta,
                                          const int ncta, const uint32_t bar_id) {
     float2* tw = reinterpret_cast<float2*>(smem);
     const int w = t >> 5, lane = t & 31, nw = nt >> 5;
-    float2* buf = reinterpret_cast<float2*>(smem + kFftTwiddleBytes) + w * 256;
-    for (int i = t; i < 128; i += nt) {
-        const float angle = -2 * M_PI * i / 256;  // binary64 quotient rounded to binary32, as in the reference
+    float2* buf = reinterpret_cast<float2*>(smem + kFftTwiddleBytes) + w * (kFftWarpBytes / 8);
+    for (int i = t; i < 255; i += nt) {
+        const int Ns = 1 << (31 - __clz(i + 1)), lo = i + 1 - Ns;
+        const float angle = -2 * M_PI * (lo * (128 / Ns)) / 256;  // binary64 quotient rounded to binary32, as in the reference
         tw[i] = make_float2(cosf(angle), sinf(angle));
     }
     role_sync(bar_id, nt);
     for (int p = g.start + cta * nw + w; p < g.end; p += ncta * nw) {
         float2* d = g.data + static_cast<size_t>(p % g.nfft) * 256;
+        float2 e[8];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) buf[lane + 32 * q] = d[lane + 32 * q];
+        for (int q = 0; q < 8; ++q) e[q] = d[lane + 32 * q];
+        // passes 1, 2, 4: afterwards the point of slot i sits at index 8 lane + rev3(i)
+        fft_passes3<0>(e, tw, 0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) buf[fft_slot(8 * lane + fft_rev3(i))] = e[i];
         __syncwarp();
 #pragma unroll
-        for (int Ns = 1; Ns < 256; Ns *= 2) {
-            float2 o0[4], o1[4];
+        for (int q = 0; q < 8; ++q) e[q] = buf[fft_slot(lane + 32 * q)];
+        __syncwarp();
+        // passes 8, 16, 32: index bits (4 3 | new three | 2 1 0)
+        fft_passes3<3>(e, tw, lane & 7);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int j = lane + 32 * q;
-                const float2 v0 = buf[j], v1 = buf[j + 128];
-                const float2 wv = tw[(j % Ns) * (128 / Ns)];
-                const float2 tv = make_float2(v1.x * wv.x - v1.y * wv.y, v1.x * wv.y + v1.y * wv.x);
-                o0[q] = make_float2(v0.x + tv.x, v0.y + tv.y);
-                o1[q] = make_float2(v0.x - tv.x, v0.y - tv.y);
-            }
-            __syncwarp();
+        for (int i = 0; i < 8; ++i) buf[fft_slot(((lane >> 3) << 6) | (fft_rev3(i) << 3) | (lane & 7))] = e[i];
+        __syncwarp();
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int j = lane + 32 * q;
-                const int idx = (j / Ns) * Ns * 2 + (j % Ns);
-                buf[idx] = o0[q];
-                buf[idx + Ns] = o1[q];
-            }
-            __syncwarp();
+        for (int q = 0; q < 8; ++q) e[q] = buf[fft_slot(lane + 32 * q)];
+        __syncwarp();
+        // passes 64 and 128 on the two sets q & 1 = 0, 1 (index bit 5)
+#pragma unroll
+        for (int y5 = 0; y5 < 2; ++y5) {
+            const float2 wv = tw[63 + y5 * 32 + lane];
+            fft_bfly(e[y5], e[4 + y5], wv);
+            fft_bfly(e[2 + y5], e[6 + y5], wv);
         }
 #pragma unroll
-        for (int q = 0; q < 8; ++q) d[lane + 32 * q] = buf[lane + 32 * q];
-        __syncwarp();
+        for (int tA = 0; tA < 2; ++tA)
+#pragma unroll
+            for (int y5 = 0; y5 < 2; ++y5) fft_bfly(e[4 * tA + y5], e[4 * tA + 2 + y5], tw[127 + tA * 64 + y5 * 32 + lane]);
+        // slot (tA tB y5) is point 128 tB + 64 tA + 32 y5 + lane
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d[lane + 32 * (((i & 2) << 1) | ((i & 4) >> 1) | (i & 1))] = e[i];
     }
 }
 
