@@ -705,8 +705,8 @@ def more_kernels(torch, ops, sms, gen, t_of, hbm_gbs):
     M, N, K = 4096, 4128, 4064           # src/ori_kernel/sgemm_kernel.cu:85-87
     sa, sb = torch.rand(K, M, device="cuda", generator=gen), torch.rand(K, N, device="cuda", generator=gen)
     sc = torch.zeros(N, M, device="cuda")
-    sg = lambda s=0, e=None: ops.gptb_sgemm(sa.data_ptr(), sb.data_ptr(), sc.data_ptr(), M, N, K, start=s, end=e, grid=sms,
-                                            block=512)
+    sg = lambda s=0, e=None: ops.gptb_sgemm(sa.data_ptr(), sb.data_ptr(), sc.data_ptr(), M, N, K, start=s, end=e,
+                                            grid=sms * 2, block=256)
     r = pair_report(ops, sms, t_of, tz, sg, (M // 128) * (N // 16), "sgemm", (256, 384))
     r["sgemm_tflops"] = round(2.0 * M * N * K / r["sgemm_us"] / 1e6, 2)
     r["sgemm_frac_of_fp32_peak"] = round(2.0 * M * N * K / (r["sgemm_us"] * 1e-6) / fp32_peak, 3)

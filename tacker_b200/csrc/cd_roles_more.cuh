@@ -49,6 +49,10 @@ struct SgemmArgs {
     // C must already hold 2 x its old value (sgemm_scale_c_kernel) -- half a block of K = 4064 is 280 us of one warp,
     // far too long a unit to share an SM with a GEMM of tens of microseconds.
     int k_per_item;
+    // 1: the warps of a CTA work as a group on one (bx, half) and up to `nw` consecutive by, and share the A slices
+    // in shared memory (sgemm_group below); k_per_item then cuts the groups' work.  For launches that cover many by per
+    // bx; a short block range keeps the per-warp form.
+    int coop;
 };
 
 constexpr int kSgemmChunk = 8;                                       // k-steps per ring slot
@@ -145,11 +149,149 @@ __device__ __forceinline__ void sgemm_half_block(const SgemmArgs& g, const int b
     }
 }
 
+// The warps of the role as one group: all 128 rows of bx, warp w takes column block `by` (inactive warps only help
+// to fetch); lane l holds rows 4 l .. 4 l + 3 of the 16 columns (64 accumulators).  The A slice of a k-chunk
+// (16 x 128 floats) is fetched once for all warps, every warp fetches its own B slice; slot = A [16][128], then
+// B [nw][16][16].  One role-wide barrier per chunk: it publishes chunk ch and retires chunk ch - 1, whose slot the copies
+// issued right after it overwrite.  Per k-step a lane reads 16 bytes of A and four 16-byte broadcasts of B for 64
+// fused multiply-adds: half the shared-memory traffic per multiply-add of sgemm_half_block, whose reads and ring
+// fills together keep the shared-memory pipe as busy as the FMA pipe.  The arithmetic per output is the same sequence
+// of fused multiply-adds.  Needs nw >= 8 (the slots use the ring space of sgemm_role_smem).
+constexpr int kSgemmGroupChunk = 16;  // k-steps per ring slot of the group form
+template <int S>
+__device__ __forceinline__ void sgemm_group(const SgemmArgs& g, const int bx, const int by, const bool active,
+                                            uint8_t* ring, const int w, const int nw, const int lane, const int k_begin,
+                                            const int k_end, const bool partial, const uint32_t bar_id) {
+    static_assert(S >= 2, "the ring needs two slots");
+    float c[4][16];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) c[r][j] = 0.0f;
+    const int t = 32 * w + lane, nt = 32 * nw;
+    const int m0 = bx * 128;
+    const size_t lda = static_cast<size_t>(g.M), ldb = static_cast<size_t>(g.N);
+    const float* __restrict__ a_ptr = g.A + m0 + static_cast<size_t>(k_begin) * lda;
+    const float* __restrict__ b_ptr = g.B + (active ? by : 0) * 16 + static_cast<size_t>(k_begin) * ldb;
+    const int K = k_end - k_begin;
+    const int nchunks = (K + kSgemmGroupChunk - 1) / kSgemmGroupChunk;
+    const uint32_t slot_bytes = (kSgemmGroupChunk * 128 + nw * kSgemmGroupChunk * 16) * 4;
+    const uint32_t ring_u32 = smem_u32(ring);
+    auto issue = [&](int ch) {
+        if (ch < nchunks) {
+            const uint32_t slot = ring_u32 + (ch % S) * slot_bytes;
+            const int k0 = ch * kSgemmGroupChunk;
+            for (int idx = t; idx < kSgemmGroupChunk * 32; idx += nt) {  // 16 x 512 bytes of A: 512 pieces of 16 bytes
+                const int kl = idx >> 5, seg = idx & 31;
+                if (k0 + kl < K) cp_async_16(slot + (kl * 128 + seg * 4) * 4, a_ptr + (k0 + kl) * lda + seg * 4);
+            }
+#pragma unroll
+            for (int j = 0; j < kSgemmGroupChunk / 8; ++j) {  // this warp's 16 x 64 bytes of B
+                const int kl = (lane >> 2) + 8 * j, seg = lane & 3;
+                if (active && k0 + kl < K)
+                    cp_async_16(slot + (kSgemmGroupChunk * 128 + (w * kSgemmGroupChunk + kl) * 16 + seg * 4) * 4,
+                                b_ptr + (k0 + kl) * ldb + seg * 4);
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int q = 0; q < S - 1; ++q) issue(q);
+    for (int ch = 0; ch < nchunks; ++ch) {
+        cp_async_wait<S - 2>();  // this thread's copies of chunk ch have landed
+        role_sync(bar_id, nt);   // ... and everybody's; everybody is done with chunk ch - 1
+        issue(ch + S - 1);       // into the slot of chunk ch - 1
+        if (!active) continue;
+        const float* slot = reinterpret_cast<const float*>(ring + (ch % S) * slot_bytes);
+        const float* bs = slot + kSgemmGroupChunk * 128 + w * kSgemmGroupChunk * 16;
+        const int steps = min(kSgemmGroupChunk, K - ch * kSgemmGroupChunk);
+        auto k_step = [&](const float4 av, const float4 (&b)[4]) {
+            const float a4[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    c[r][4 * q + 0] = fmaf(a4[r], b[q].x, c[r][4 * q + 0]);
+                    c[r][4 * q + 1] = fmaf(a4[r], b[q].y, c[r][4 * q + 1]);
+                    c[r][4 * q + 2] = fmaf(a4[r], b[q].z, c[r][4 * q + 2]);
+                    c[r][4 * q + 3] = fmaf(a4[r], b[q].w, c[r][4 * q + 3]);
+                }
+        };
+        auto fetch = [&](const int kk, float4& av, float4 (&b)[4]) {
+            av = *reinterpret_cast<const float4*>(slot + kk * 128 + 4 * lane);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const float4*>(bs + kk * 16 + 4 * q);
+        };
+        if (steps == kSgemmGroupChunk) {
+            // whole chunk, no predicates: the operands of step kk + 1 are read while step kk multiplies
+            float4 av, b[4];
+            fetch(0, av, b);
+#pragma unroll
+            for (int kk = 0; kk < kSgemmGroupChunk; ++kk) {
+                float4 avn = av, bn[4] = {b[0], b[1], b[2], b[3]};
+                if (kk + 1 < kSgemmGroupChunk) fetch(kk + 1, avn, bn);
+                k_step(av, b);
+                av = avn;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) b[q] = bn[q];
+            }
+        } else {
+            for (int kk = 0; kk < steps; ++kk) {  // the ragged end of a K that is no multiple of 16
+                float4 av, b[4];
+                fetch(kk, av, b);
+                k_step(av, b);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    role_sync(bar_id, nt);  // the next group's first copies may overwrite any slot
+    if (!active) return;
+    // C = C * beta + alpha * c with alpha = beta = 2 (src/gptb_kernel/sgemm_kernel.cu:12-13, 59-62)
+    float* c_ptr = g.C + static_cast<size_t>(by) * 16 * lda + m0 + 4 * lane;
+    if (partial) {  // C already holds 2 x its old value
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) red_add_f32(c_ptr + j * lda + r, 2.0f * c[r][j]);
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        float4* p = reinterpret_cast<float4*>(c_ptr + j * lda);
+        float4 o = *p;
+        o.x = o.x * 2.0f + 2.0f * c[0][j];
+        o.y = o.y * 2.0f + 2.0f * c[1][j];
+        o.z = o.z * 2.0f + 2.0f * c[2][j];
+        o.w = o.w * 2.0f + 2.0f * c[3][j];
+        *p = o;
+    }
+}
+
 // warp `w` of `nw` in CTA `cta` of `ncta`; smem: sgemm_role_smem(nw, S) bytes, 16-byte aligned; counter: the CTA's
 // item counter (zero on entry; used when the items are split in k)
 template <int S>
 __device__ __forceinline__ void sgemm_role(const SgemmArgs& g, uint8_t* smem, int* counter, const int w, const int nw,
-                                           const int lane, const int cta, const int ncta) {
+                                           const int lane, const int cta, const int ncta, const uint32_t bar_id = 0) {
+    if (g.coop) {
+        // items: bx fastest, so that the CTAs running together share B rows; then the group of by; then the k-chunk.
+        // The by of a group are spread evenly (gy = 258 on 16 warps: groups of 15 and 16, not 16 x 16 + 2).
+        const int ygroups = (g.gy + nw - 1) / nw;
+        const int nk = g.k_per_item > 0 ? (g.K + g.k_per_item - 1) / g.k_per_item : 1;
+        const long long nitems = static_cast<long long>(g.gx) * ygroups * nk;
+        for (long long item = cta; item < nitems; item += ncta) {
+            const int bx = static_cast<int>(item % g.gx);
+            const int yg = static_cast<int>((item / g.gx) % ygroups);
+            const int kc = static_cast<int>(item / (static_cast<long long>(g.gx) * ygroups));
+            const int b0 = static_cast<int>(static_cast<long long>(yg) * g.gy / ygroups);
+            const int b1 = static_cast<int>(static_cast<long long>(yg + 1) * g.gy / ygroups);
+            const int by = b0 + w, pos = by * g.gx + bx;
+            const bool active = by < b1 && pos >= g.start && pos < g.end;
+            const bool split = g.k_per_item > 0;  // C then holds 2 x its old value already (sgemm_scale_c)
+            const int k0 = split ? kc * g.k_per_item : 0, k1 = split ? min(k0 + g.k_per_item, g.K) : g.K;
+            sgemm_group<S>(g, bx, by, active, smem, w, nw, lane, k0, k1, split, bar_id);
+        }
+        return;
+    }
     uint8_t* ring = smem + w * (S * kSgemmSlotBytes);
     if (g.k_per_item > 0) {
         const int nchunks = (g.K + g.k_per_item - 1) / g.k_per_item;

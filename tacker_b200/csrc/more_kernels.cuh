@@ -214,6 +214,7 @@ static int parse_sgemm(void** p, int i_start, int i_end, SgemmArgs* g) {
     g->start = arg<int>(p, i_start);
     g->end = arg<int>(p, i_end);
     g->k_per_item = 0;
+    g->coop = 0;
     if (g->M <= 0 || g->N <= 0 || g->K <= 0 || g->start < 0) return TK_ERR_ARGS;
     if (g->M % 128 || g->N % 16) return TK_ERR_SHAPE;
     if (g->gx != g->M / 128 || g->gy != g->N / 16 || bdx != 16 || bdy != 8) return TK_ERR_SHAPE;
@@ -317,7 +318,17 @@ static int run_sgemm(SgemmArgs g, unsigned grid0, unsigned block0, cudaStream_t 
     if (g.start >= g.end) return TK_OK;
     const unsigned threads = cd_threads(block0, 32, 512);
     if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
-    g.k_per_item = sgemm_split_for(g, static_cast<long long>(grid0) * (threads / 32));
+    const int nw = static_cast<int>(threads / 32);
+    // a range with at least half a group of by per bx: the warps of a CTA share the A slices (sgemm_group)
+    g.coop = g_opt.sgemm_coop != 0 && nw >= 8 && static_cast<long long>(g.end - g.start) * 2 >= static_cast<long long>(g.gx) * nw;
+    if (g.coop) {
+        const long long groups = static_cast<long long>(g.gx) * ((g.gy + nw - 1) / nw);
+        g.k_per_item = g_opt.sgemm_split == 0 ? 0
+                       : g_opt.sgemm_split > 0 ? (g_opt.sgemm_split + 7) / 8 * 8
+                                               : cd_pick_split(groups, grid0, g.K, 64);
+    } else {
+        g.k_per_item = sgemm_split_for(g, static_cast<long long>(grid0) * nw);
+    }
     int prc = sgemm_prepass(g, st);
     if (prc != TK_OK) return prc;
     const int smem = sgemm_role_smem(static_cast<int>(threads / 32), kSgemmSlotsSolo);

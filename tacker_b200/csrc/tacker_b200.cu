@@ -47,6 +47,7 @@ static int* option_slot(const char* name) {
     if (!std::strcmp(name, "mriq_accurate")) return &g_opt.mriq_accurate;
     if (!std::strcmp(name, "mrif_accurate")) return &g_opt.mrif_accurate;
     if (!std::strcmp(name, "sgemm_split")) return &g_opt.sgemm_split;
+    if (!std::strcmp(name, "sgemm_coop")) return &g_opt.sgemm_coop;
     if (!std::strcmp(name, "cutcp_split")) return &g_opt.cutcp_split;
     if (!std::strcmp(name, "cp_split")) return &g_opt.cp_split;
     if (!std::strcmp(name, "mriq_split")) return &g_opt.mriq_split;
@@ -323,8 +324,9 @@ static int launch_more_ori(MoreKind kind, void** params, int nparams, const unsi
     if ((rc = parse_more(kind, p, &m)) != TK_OK) return rc;
     DeviceInfo* d = nullptr;
     if ((rc = device_info(&d)) != TK_OK) return rc;
-    const unsigned ctas = static_cast<unsigned>(d->sm_count) * (kind == MORE_SGEMM ? 1u : 2u);
-    return run_more_solo(m, ctas, 512, static_cast<cudaStream_t>(stream));
+    // sgemm: two CTAs of eight warps per SM (128 registers each; a group of eight warps shares its A slices)
+    const unsigned ctas = static_cast<unsigned>(d->sm_count) * 2u;
+    return run_more_solo(m, ctas, kind == MORE_SGEMM ? 256 : 512, static_cast<cudaStream_t>(stream));
 }
 TK_API int tk_launch_ori_sgemm(void** params, int nparams, const unsigned grid[3], const unsigned block[3], unsigned,
                                void* stream) {

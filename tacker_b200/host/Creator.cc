@@ -60,7 +60,7 @@ GPTBKernel* createKernel(const std::string& name) {
         geometry(name, 2, 512, &grid, &block);
     } else if (name == "sgemm") {
         ori = new OriSGEMMKernel(id = 19, creatorSGEMMProblem);
-        geometry(name, 1, 512, &grid, &block);
+        geometry(name, 2, 256, &grid, &block);
     } else {
         logger.ERROR("createKernel: unknown kernel {" + name + "}");
     }

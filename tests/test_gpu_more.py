@@ -106,6 +106,39 @@ def test_sgemm_split_items(cuda, oracle, split):
         assert oracle.bit_mismatches(got, want) > 0            # really another order of additions
 
 
+@pytest.mark.parametrize("coop", [1, 0])
+@pytest.mark.parametrize("case", [(384, 320, 41, 0, None, 256), (128, 528, 24, 0, None, 512), (256, 272, 19, 5, 29, 128),
+                                  (384, 160, 64, 7, 8, 256)])
+def test_sgemm_warps_of_a_cta_as_one_group(cuda, oracle, coop, case):
+    """Launches over many column blocks: the warps of a CTA share the A slices (groups of 6 to 16 column blocks, ragged
+    last groups, block ranges that cut groups, a range too short for the form); bit for bit the same as the per-warp
+    form and the reference's order of additions."""
+    from tacker_b200 import ops
+
+    M, N, K, start, end, block = case
+    ops.set_option("sgemm_coop", coop)
+    a, b, c = sgemm_inputs(oracle, M, N, K, seed=M + N + K + 1)
+    got = _sgemm(cuda, ops, a, b, c, start=start, end=end, grid=3, block=block)
+    ops.set_option("sgemm_coop", 1)
+    total = (M // 128) * (N // 16)
+    want = oracle.sgemm_f32(a, b, c.copy(), start, total if end is None else end)
+    assert oracle.bit_mismatches(got, want) == 0
+
+
+@pytest.mark.parametrize("split", [-1, 16, 40])
+def test_sgemm_groups_split_in_k(cuda, oracle, split):
+    from tacker_b200 import ops
+
+    M, N, K = 256, 400, 136
+    a, b, c = sgemm_inputs(oracle, M, N, K, seed=31)
+    ops.set_option("sgemm_split", split)
+    got = _sgemm(cuda, ops, a, b, c, grid=2, block=256)
+    want = oracle.sgemm_f32(a, b, c.copy())
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    if split > 0:
+        assert oracle.bit_mismatches(got, want) > 0            # really another order of additions
+
+
 # ------------------------------------------------------------------------------------------ lbm ----
 def _lbm(torch, ops, oracle, src, dst, nx, ny, nz, start=0, end=None, grid=3, block=96):
     m = oracle.lbm_margin(nx, ny)
