@@ -93,9 +93,10 @@ int tk_sm_count(int* sm_count);
  *                    0 = never (the reference's order of additions, bit for bit), n = n.  Split items add partial
  *                    sums with reductions in no fixed order, after a short kernel on the same stream that doubles C
  *                    (sgemm: C = 2 C + 2 A B) or zeroes the regions (cutcp).
- *   "sgemm_coop"     1 (default) = a solo sgemm launch that covers many column blocks per row block lets the warps
- *                    of a CTA share the A slices through shared memory; 0 = every warp streams its own (the form of
- *                    the fused kernels and of short block ranges).  Same results either way.
+ *   "sgemm_coop"     1 (default) = a solo sgemm launch with at least one full group of column blocks per CTA lets the
+ *                    warps of a CTA share the A slices through shared memory; 0 = every warp streams its own (the form
+ *                    of the fused kernels and of short block ranges); 2 = the shared form for every range it can take
+ *                    (tests).  Same results either way.
  *   "wait_budget_us" budget of every bounded device-side wait (default 1,000,000 = about a second); applies to the
  *                    current device.  "test_skip_loads" n: test hook, the next n single-CTA tzgemm launches issue
  *                    no operand loads, so that their waits run out.

@@ -274,16 +274,18 @@ __device__ __forceinline__ void sgemm_role(const SgemmArgs& g, uint8_t* smem, in
                                            const int lane, const int cta, const int ncta, const uint32_t bar_id = 0) {
     if (g.coop) {
         // items: bx fastest, so that the CTAs running together share B rows; then the group of by; then the k-chunk.
-        // The by of a group are spread evenly (gy = 258 on 16 warps: groups of 15 and 16, not 16 x 16 + 2).
-        const int ygroups = (g.gy + nw - 1) / nw;
+        // Only the by the block range touches are grouped, and they are spread evenly over the groups (258 on 16
+        // warps: groups of 15 and 16, not 16 x 16 + 2).
+        const int by_lo = g.start / g.gx, nby = (g.end + g.gx - 1) / g.gx - by_lo;
+        const int ygroups = (nby + nw - 1) / nw;
         const int nk = g.k_per_item > 0 ? (g.K + g.k_per_item - 1) / g.k_per_item : 1;
         const long long nitems = static_cast<long long>(g.gx) * ygroups * nk;
         for (long long item = cta; item < nitems; item += ncta) {
             const int bx = static_cast<int>(item % g.gx);
             const int yg = static_cast<int>((item / g.gx) % ygroups);
             const int kc = static_cast<int>(item / (static_cast<long long>(g.gx) * ygroups));
-            const int b0 = static_cast<int>(static_cast<long long>(yg) * g.gy / ygroups);
-            const int b1 = static_cast<int>(static_cast<long long>(yg + 1) * g.gy / ygroups);
+            const int b0 = by_lo + static_cast<int>(static_cast<long long>(yg) * nby / ygroups);
+            const int b1 = by_lo + static_cast<int>(static_cast<long long>(yg + 1) * nby / ygroups);
             const int by = b0 + w, pos = by * g.gx + bx;
             const bool active = by < b1 && pos >= g.start && pos < g.end;
             const bool split = g.k_per_item > 0;  // C then holds 2 x its old value already (sgemm_scale_c)

@@ -44,7 +44,7 @@ struct Options {
     int mriq_split = -1;
     // the same for sgemm (k-steps per work item) and cutcp (neighbour bins per work item)
     int sgemm_split = -1;
-    int sgemm_coop = 1;    // 1: solo sgemm launches over many column blocks share the A slices per CTA (sgemm_group)
+    int sgemm_coop = 1;    // 1: large solo sgemm launches share the A slices per CTA (sgemm_group); 2: every launch that can; 0: none
     int cutcp_split = -1;
     int mriq_vpt = 2;      // voxels per thread and work item / 32, solo kernel (2 or 4)
     int mix_mriq_vpt = 4;  // fused kernel: the larger item halves the table reads that compete with the tensor role

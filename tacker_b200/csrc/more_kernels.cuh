@@ -319,10 +319,14 @@ static int run_sgemm(SgemmArgs g, unsigned grid0, unsigned block0, cudaStream_t 
     const unsigned threads = cd_threads(block0, 32, 512);
     if (threads == 0) return TK_ERR_LAUNCH_CONFIG;
     const int nw = static_cast<int>(threads / 32);
-    // a range with at least half a group of by per bx: the warps of a CTA share the A slices (sgemm_group)
-    g.coop = g_opt.sgemm_coop != 0 && nw >= 8 && static_cast<long long>(g.end - g.start) * 2 >= static_cast<long long>(g.gx) * nw;
+    // a range that gives every CTA at least one full group of column blocks: the warps of a CTA share the A slices
+    // (sgemm_group; option 2 forces the form for any range with at least half a group per row block)
+    const long long nblocks = g.end - g.start;
+    g.coop = nw >= 8 && nblocks * 2 >= static_cast<long long>(g.gx) * nw &&
+             (g_opt.sgemm_coop == 2 || (g_opt.sgemm_coop == 1 && nblocks >= static_cast<long long>(grid0) * nw));
     if (g.coop) {
-        const long long groups = static_cast<long long>(g.gx) * ((g.gy + nw - 1) / nw);
+        const int nby = (g.end + g.gx - 1) / g.gx - g.start / g.gx;  // column blocks the range touches
+        const long long groups = static_cast<long long>(g.gx) * ((nby + nw - 1) / nw);
         g.k_per_item = g_opt.sgemm_split == 0 ? 0
                        : g_opt.sgemm_split > 0 ? (g_opt.sgemm_split + 7) / 8 * 8
                                                : cd_pick_split(groups, grid0, g.K, 64);

@@ -125,7 +125,7 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096, only=None) -> dict:
     cregions = torch.zeros(2 * 26 * 26 * 512, device="cuda")
     cds.update({
         "sgemm": (lambda s=0, e=None: ops.gptb_sgemm(sa.data_ptr(), sb.data_ptr(), sc.data_ptr(), 4096, 4128, 4064, start=s,
-                                                     end=e, grid=sms, block=512), 32 * 258, (1, 512), (256, 384)),
+                                                     end=e, grid=sms * 2, block=256), 32 * 258, (2, 256), (256, 384)),
         "lbm": (lambda s=0, e=None: ops.gptb_lbm(lsrc.data_ptr() + 4 * lmargin, ldst.data_ptr() + 4 * lmargin, 128, 128, 128,
                                                  start=s, end=e, grid=sms * 2, block=512), 128 * 128, (2, 512),
                 (576, 832)),
@@ -139,7 +139,10 @@ def profile(fill: float = 0.8, m: int = 4096, n: int = 4096, only=None) -> dict:
         cds = {k: v for k, v in cds.items() if k in only}
     out = {}
     for cd, (mk, blocks, solo_shape, w_sweep) in cds.items():
+        if cd == "sgemm":   # per block in the form the fused kernels run (every warp on its own), not the group form
+            ops.set_option("sgemm_coop", 0)
         t_block = t_us([mk()], 3) / blocks
+        ops.set_option("sgemm_coop", 1)
         # the CUDA-core thread count of the fused kernel: best on a quantum worth one 4096 x 4096 x 1152 GEMM
         a = (torch.rand(m, 1152, device="cuda") * 2 - 1).half()
         b = (torch.rand(n, 1152, device="cuda") * 2 - 1).half()

@@ -106,13 +106,14 @@ def test_sgemm_split_items(cuda, oracle, split):
         assert oracle.bit_mismatches(got, want) > 0            # really another order of additions
 
 
-@pytest.mark.parametrize("coop", [1, 0])
-@pytest.mark.parametrize("case", [(384, 320, 41, 0, None, 256), (128, 528, 24, 0, None, 512), (256, 272, 19, 5, 29, 128),
-                                  (384, 160, 64, 7, 8, 256)])
+@pytest.mark.parametrize("coop", [2, 1, 0])
+@pytest.mark.parametrize("case", [(384, 320, 41, 0, None, 256), (128, 528, 24, 0, None, 512), (256, 272, 19, 5, 29, 256),
+                                  (384, 160, 64, 7, 8, 256), (128, 1024, 35, 0, None, 256)])
 def test_sgemm_warps_of_a_cta_as_one_group(cuda, oracle, coop, case):
     """Launches over many column blocks: the warps of a CTA share the A slices (groups of 6 to 16 column blocks, ragged
-    last groups, block ranges that cut groups, a range too short for the form); bit for bit the same as the per-warp
-    form and the reference's order of additions."""
+    last groups, block ranges that cut groups, a range too short for the form; coop = 2 takes the form wherever it
+    can, 1 only where every CTA gets a full group); bit for bit the same as the per-warp form and the reference's order
+    of additions."""
     from tacker_b200 import ops
 
     M, N, K, start, end, block = case
@@ -132,7 +133,9 @@ def test_sgemm_groups_split_in_k(cuda, oracle, split):
     M, N, K = 256, 400, 136
     a, b, c = sgemm_inputs(oracle, M, N, K, seed=31)
     ops.set_option("sgemm_split", split)
+    ops.set_option("sgemm_coop", 2)
     got = _sgemm(cuda, ops, a, b, c, grid=2, block=256)
+    ops.set_option("sgemm_coop", 1)
     want = oracle.sgemm_f32(a, b, c.copy())
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
     if split > 0:
