@@ -38,7 +38,7 @@ KERNELS = {
     "mrif": KernelInfo("mrif", 32, 0, 32, "sfu"),
     "sgemm": KernelInfo("sgemm", 96, 3 * 2560, 32, "fma"),                  # a ring of three slots per warp
     "lbm": KernelInfo("lbm", 64, 0, 32, "hbm"),
-    "fft": KernelInfo("fft", 48, 2048 + 64, 32, "latency"),                 # 2 KB per warp + its share of the 1 KB table
+    "fft": KernelInfo("fft", 64, 2048 + 128, 32, "latency"),                # 2 KB per warp + its share of the 2 KB tables
     "cutcp": KernelInfo("cutcp", 64, 0, 32, "issue"),
 }
 
