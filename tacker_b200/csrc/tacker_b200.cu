@@ -955,6 +955,60 @@ __global__ void rows_to_f16_kernel(const float* __restrict__ x, int rows, int co
     }
 }
 
+// the same, eight outputs (16 bytes) per thread; cols_pad % 8 == 0 and A 16-byte aligned.  vec: x, ld_in and cols
+// allow 16-byte loads
+__global__ void rows_to_f16_vec_kernel(const float* __restrict__ x, int rows, int cols, int ld_in, __half* __restrict__ A,
+                                       int rows_pad, int cols_pad, int vec) {
+    const int groups = cols_pad >> 3;
+    const long long total = static_cast<long long>(rows_pad) * groups;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(e / groups), c = static_cast<int>(e - static_cast<long long>(r) * groups) * 8;
+        float v[8];
+        if (r < rows && vec && c + 8 <= cols) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * ld_in + c));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * ld_in + c + 4));
+            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (r < rows && c + j < cols) ? __ldg(x + static_cast<size_t>(r) * ld_in + c + j) : 0.0f;
+        }
+        __half2 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+        *reinterpret_cast<uint4*>(A + static_cast<size_t>(r) * cols_pad + c) = *reinterpret_cast<const uint4*>(h);
+    }
+}
+
+__device__ __forceinline__ float act_of(float v, int act) {
+    if (act == 1) return fmaxf(v, 0.0f);
+    if (act == 2) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v;
+}
+
+// bias + activation, four columns per thread (cols, ldx, ldo multiples of 4, 16-byte aligned arrays)
+__global__ void bias_act_vec_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ bias,
+                                    float* __restrict__ out, int rows, int cols, int ldo, int act,
+                                    __half* __restrict__ out_half = nullptr, int ldh = 0) {
+    const int groups = cols >> 2;
+    const long long total = static_cast<long long>(rows) * groups;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(e / groups), c = static_cast<int>(e - static_cast<long long>(r) * groups) * 4;
+        float4 v = *reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * ldx + c);
+        if (bias) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(bias + c));
+            v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+        }
+        v.x = act_of(v.x, act), v.y = act_of(v.y, act), v.z = act_of(v.z, act), v.w = act_of(v.w, act);
+        if (out) *reinterpret_cast<float4*>(out + static_cast<size_t>(r) * ldo + c) = v;
+        if (out_half) {
+            __half2 h[2] = {__floats2half2_rn(v.x, v.y), __floats2half2_rn(v.z, v.w)};
+            *reinterpret_cast<uint2*>(out_half + static_cast<size_t>(r) * ldh + c) = *reinterpret_cast<const uint2*>(h);
+        }
+    }
+}
+
 // out[r][c] = act(x[r][c] + bias[c]); act: 0 none, 1 relu, 2 gelu (tanh form)
 __global__ void bias_act_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ bias,
                                 float* __restrict__ out, int rows, int cols, int ldo, int act) {
@@ -988,6 +1042,15 @@ __global__ void add_kernel(const float* __restrict__ a, const float* __restrict_
         out[e] = a[e] + b[e];
 }
 
+__global__ void add_vec_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ out,
+                               long long n4) {
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < n4;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float4 u = a[e], w = b[e];
+        out[e] = make_float4(u.x + w.x, u.y + w.y, u.z + w.z, u.w + w.w);
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -1000,13 +1063,14 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // one warp per row: out = softmax(scale * x) over `cols`
-__global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restrict__ out, long long rows, int cols,
+template <typename OUT>
+__global__ void softmax_rows_kernel(const float* __restrict__ x, OUT* __restrict__ out, long long rows, int cols,
                                     float scale) {
     const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
     const float* xr = x + row * cols;
-    float* orow = out + row * cols;
+    OUT* orow = out + row * cols;
     float m = -INFINITY;
     for (int c = lane; c < cols; c += 32) m = fmaxf(m, scale * xr[c]);
     m = warp_max(m);
@@ -1014,7 +1078,7 @@ __global__ void softmax_rows_kernel(const float* __restrict__ x, float* __restri
     for (int c = lane; c < cols; c += 32) s += __expf(scale * xr[c] - m);
     s = warp_sum(s);
     const float inv = 1.0f / s;
-    for (int c = lane; c < cols; c += 32) orow[c] = __expf(scale * xr[c] - m) * inv;
+    for (int c = lane; c < cols; c += 32) orow[c] = static_cast<OUT>(__expf(scale * xr[c] - m) * inv);
 }
 
 // one warp per row: out = (x - mean) / sqrt(var + eps) * gamma + beta
@@ -1067,6 +1131,164 @@ __global__ void merge_heads_kernel(const float* __restrict__ ctx, int B, int S, 
         const int h = static_cast<int>((e / (static_cast<long long>(dh) * S)) % heads);
         const int b = static_cast<int>(e / (static_cast<long long>(dh) * S * heads));
         out[(static_cast<size_t>(b) * S + s) * heads * dh + h * dh + d] = ctx[e];
+    }
+}
+
+// split, eight head columns per thread, untransposed output (dh % 8 == 0, ld and col0 multiples of 4, aligned arrays)
+__global__ void split_heads_vec_kernel(const float* __restrict__ x, int ld, int col0, int B, int S, int heads, int dh,
+                                       __half* __restrict__ out) {
+    const int g8 = dh >> 3;
+    const long long total = static_cast<long long>(B) * heads * S * g8;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int d = static_cast<int>(e % g8) * 8;
+        const int s = static_cast<int>((e / g8) % S);
+        const int h = static_cast<int>((e / (static_cast<long long>(g8) * S)) % heads);
+        const int b = static_cast<int>(e / (static_cast<long long>(g8) * S * heads));
+        const float* p = x + (static_cast<size_t>(b) * S + s) * ld + col0 + h * dh + d;
+        const float4 u = __ldg(reinterpret_cast<const float4*>(p)), w = __ldg(reinterpret_cast<const float4*>(p + 4));
+        __half2 hh[4] = {__floats2half2_rn(u.x, u.y), __floats2half2_rn(u.z, u.w), __floats2half2_rn(w.x, w.y),
+                         __floats2half2_rn(w.z, w.w)};
+        *reinterpret_cast<uint4*>(out + ((static_cast<size_t>(b) * heads + h) * S + s) * dh + d) =
+            *reinterpret_cast<const uint4*>(hh);
+    }
+}
+
+// split with transposed output [B*heads][dh][S]: tiles of 32 rows (s) x 32 head columns (d) through shared memory, so
+// that the reads run along d and the writes along s.  Block = 32 x 8 threads; S % 32 == 0, dh % 32 == 0.
+__global__ void split_heads_t_kernel(const float* __restrict__ x, int ld, int col0, int S, int heads, int dh,
+                                     __half* __restrict__ out) {
+    __shared__ float tile[32][33];
+    const int tiles_d = dh / 32, tiles_s = S / 32;
+    int t = blockIdx.x;
+    const int td = t % tiles_d;
+    t /= tiles_d;
+    const int ts = t % tiles_s;
+    t /= tiles_s;
+    const int h = t % heads, b = t / heads;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = ty; i < 32; i += 8)
+        tile[i][tx] = __ldg(x + (static_cast<size_t>(b) * S + ts * 32 + i) * ld + col0 + h * dh + td * 32 + tx);
+    __syncthreads();
+    __half* o = out + (static_cast<size_t>(b) * heads + h) * dh * S;
+#pragma unroll
+    for (int i = ty; i < 32; i += 8)
+        o[static_cast<size_t>(td * 32 + i) * S + ts * 32 + tx] = __float2half_rn(tile[tx][i]);
+}
+
+// q, k (eight head columns per thread) and v (transposed through shared-memory tiles) in one launch: blocks
+// 0 .. nb_qk - 1 stride over the q and k elements, every later block takes one 32 x 32 tile of v
+__global__ void split_qkv_heads_kernel(const float* __restrict__ x, int ld, int B, int S, int heads, int dh,
+                                       __half* __restrict__ q, __half* __restrict__ k, __half* __restrict__ vt, int nb_qk) {
+    __shared__ float tile[32][33];
+    const int hidden = heads * dh;
+    if (static_cast<int>(blockIdx.x) < nb_qk) {
+        const int g8 = dh >> 3;
+        const long long per = static_cast<long long>(B) * heads * S * g8;
+        for (long long e2 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e2 < 2 * per;
+             e2 += static_cast<long long>(nb_qk) * blockDim.x) {
+            const int part = e2 >= per;
+            const long long e = e2 - part * per;
+            const int d = static_cast<int>(e % g8) * 8;
+            const int s = static_cast<int>((e / g8) % S);
+            const int h = static_cast<int>((e / (static_cast<long long>(g8) * S)) % heads);
+            const int b = static_cast<int>(e / (static_cast<long long>(g8) * S * heads));
+            const float* p = x + (static_cast<size_t>(b) * S + s) * ld + part * hidden + h * dh + d;
+            const float4 u = __ldg(reinterpret_cast<const float4*>(p)), w = __ldg(reinterpret_cast<const float4*>(p + 4));
+            __half2 hh[4] = {__floats2half2_rn(u.x, u.y), __floats2half2_rn(u.z, u.w), __floats2half2_rn(w.x, w.y),
+                             __floats2half2_rn(w.z, w.w)};
+            *reinterpret_cast<uint4*>((part ? k : q) + ((static_cast<size_t>(b) * heads + h) * S + s) * dh + d) =
+                *reinterpret_cast<const uint4*>(hh);
+        }
+        return;
+    }
+    const int tiles_d = dh / 32, tiles_s = S / 32;
+    int t = static_cast<int>(blockIdx.x) - nb_qk;
+    const int td = t % tiles_d;
+    t /= tiles_d;
+    const int ts = t % tiles_s;
+    t /= tiles_s;
+    const int h = t % heads, b = t / heads;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = ty; i < 32; i += 8)
+        tile[i][tx] = __ldg(x + (static_cast<size_t>(b) * S + ts * 32 + i) * ld + 2 * hidden + h * dh + td * 32 + tx);
+    __syncthreads();
+    __half* o = vt + (static_cast<size_t>(b) * heads + h) * dh * S;
+#pragma unroll
+    for (int i = ty; i < 32; i += 8)
+        o[static_cast<size_t>(td * 32 + i) * S + ts * 32 + tx] = __float2half_rn(tile[tx][i]);
+}
+
+// merge, four head columns per thread (dh % 4 == 0, aligned arrays); fp32 output, fp16 output or both
+__global__ void merge_heads_vec_kernel(const float* __restrict__ ctx, int B, int S, int heads, int dh,
+                                       float* __restrict__ out, __half* __restrict__ out_half = nullptr) {
+    const int g4 = dh >> 2;
+    const long long total = static_cast<long long>(B) * heads * S * g4;
+    for (long long e = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int d = static_cast<int>(e % g4) * 4;
+        const int s = static_cast<int>((e / g4) % S);
+        const int h = static_cast<int>((e / (static_cast<long long>(g4) * S)) % heads);
+        const int b = static_cast<int>(e / (static_cast<long long>(g4) * S * heads));
+        const float4 v = reinterpret_cast<const float4*>(ctx)[e];
+        const size_t o = (static_cast<size_t>(b) * S + s) * heads * dh + h * dh + d;
+        if (out) *reinterpret_cast<float4*>(out + o) = v;
+        if (out_half) {
+            __half2 hh[2] = {__floats2half2_rn(v.x, v.y), __floats2half2_rn(v.z, v.w)};
+            *reinterpret_cast<uint2*>(out_half + o) = *reinterpret_cast<const uint2*>(hh);
+        }
+    }
+}
+
+// one warp per row, the row (plus an optional second operand `res`, added first) held in registers: NV float4 per
+// lane, cols = 128 NV.  Same two-pass mean / variance as layernorm_rows_kernel.
+template <int NV>
+__global__ void layernorm_rows_reg_kernel(const float* __restrict__ x, const float* __restrict__ res,
+                                          const float* __restrict__ gamma, const float* __restrict__ beta,
+                                          float* __restrict__ out, __half* __restrict__ out_half, long long rows,
+                                          float eps) {
+    constexpr int cols = 128 * NV;
+    const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = xr[lane + 32 * i];
+    if (res) {
+        const float4* rr = reinterpret_cast<const float4*>(res + row * cols);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const float4 r4 = rr[lane + 32 * i];
+            v[i].x += r4.x, v[i].y += r4.y, v[i].z += r4.z, v[i].w += r4.w;
+        }
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    const float mean = warp_sum(s) / cols;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+        q += (a * a + b * b) + (c * c + d * d);
+    }
+    const float rstd = rsqrtf(warp_sum(q) / cols + eps);
+    float4* orow = reinterpret_cast<float4*>(out + row * cols);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c4 = lane + 32 * i;
+        const float4 g = gamma ? __ldg(reinterpret_cast<const float4*>(gamma) + c4) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 b = beta ? __ldg(reinterpret_cast<const float4*>(beta) + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 o = make_float4((v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y,
+                                     (v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w);
+        orow[c4] = o;
+        if (out_half) {  // the fp16 operand of the product that follows, same values rounded once
+            __half2 h[2] = {__floats2half2_rn(o.x, o.y), __floats2half2_rn(o.z, o.w)};
+            *reinterpret_cast<uint2*>(out_half + row * cols + 4 * c4) = *reinterpret_cast<const uint2*>(h);
+        }
     }
 }
 
@@ -1131,6 +1353,12 @@ TK_API int tk_rows_f32_to_f16(const float* x, int rows, int cols, int ld_in, voi
                               void* stream) {
     if (!x || !A_half || rows <= 0 || cols <= 0 || ld_in < cols || rows_pad < rows || cols_pad < cols) return TK_ERR_ARGS;
     TK_LAYER_PROLOGUE();
+    if (cols_pad % 8 == 0 && (reinterpret_cast<uintptr_t>(A_half) & 15u) == 0) {
+        const int vec = cols % 4 == 0 && ld_in % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+        rows_to_f16_vec_kernel<<<blocks_for(static_cast<long long>(rows_pad) * (cols_pad / 8), d->sm_count), 256, 0, st>>>(
+            x, rows, cols, ld_in, static_cast<__half*>(A_half), rows_pad, cols_pad, vec);
+        return launch_error("rows_to_f16_vec_kernel launch");
+    }
     rows_to_f16_kernel<<<blocks_for(static_cast<long long>(rows_pad) * cols_pad, d->sm_count), 256, 0, st>>>(
         x, rows, cols, ld_in, static_cast<__half*>(A_half), rows_pad, cols_pad);
     return launch_error("rows_to_f16_kernel launch");
@@ -1140,6 +1368,12 @@ TK_API int tk_bias_act_f32(const float* x, int ldx, const float* bias, float* ou
                            int act, void* stream) {
     if (!x || !out || rows <= 0 || cols <= 0 || ldx < cols || ld_out < cols || act < 0 || act > 2) return TK_ERR_ARGS;
     TK_LAYER_PROLOGUE();
+    if (cols % 4 == 0 && ldx % 4 == 0 && ld_out % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias)) & 15u) == 0) {
+        bias_act_vec_kernel<<<blocks_for(static_cast<long long>(rows) * (cols / 4), d->sm_count), 256, 0, st>>>(
+            x, ldx, bias, out, rows, cols, ld_out, act);
+        return launch_error("bias_act_vec_kernel launch");
+    }
     bias_act_kernel<<<blocks_for(static_cast<long long>(rows) * cols, d->sm_count), 256, 0, st>>>(x, ldx, bias, out, rows,
                                                                                                 cols, ld_out, act);
     return launch_error("bias_act_kernel launch");
@@ -1156,6 +1390,13 @@ TK_API int tk_maxpool2x2_nhwc_f32(const float* x, int H, int W, int C, float* ou
 TK_API int tk_add_f32(const float* a, const float* b, float* out, long long n, void* stream) {
     if (!a || !b || !out || n <= 0) return TK_ERR_ARGS;
     TK_LAYER_PROLOGUE();
+    if (n % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0) {
+        add_vec_kernel<<<blocks_for(n / 4, d->sm_count), 256, 0, st>>>(reinterpret_cast<const float4*>(a),
+                                                                      reinterpret_cast<const float4*>(b),
+                                                                      reinterpret_cast<float4*>(out), n / 4);
+        return launch_error("add_vec_kernel launch");
+    }
     add_kernel<<<blocks_for(n, d->sm_count), 256, 0, st>>>(a, b, out, n);
     return launch_error("add_kernel launch");
 }
@@ -1163,17 +1404,58 @@ TK_API int tk_add_f32(const float* a, const float* b, float* out, long long n, v
 TK_API int tk_softmax_rows_f32(const float* x, float* out, long long rows, int cols, float scale, void* stream) {
     if (!x || !out || rows <= 0 || cols <= 0) return TK_ERR_ARGS;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    softmax_rows_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(x, out, rows, cols, scale);
+    softmax_rows_kernel<float><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(x, out, rows, cols, scale);
     return launch_error("softmax_rows_kernel launch");
+}
+
+TK_API int tk_softmax_rows_f16(const float* x, void* out_half, long long rows, int cols, float scale, void* stream) {
+    if (!x || !out_half || rows <= 0 || cols <= 0) return TK_ERR_ARGS;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    softmax_rows_kernel<__half><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(
+        x, static_cast<__half*>(out_half), rows, cols, scale);
+    return launch_error("softmax_rows_kernel launch");
+}
+
+// the register form takes rows of 128, 256, .., 1024 columns in 16-byte aligned arrays
+static bool layernorm_reg_ok(const float* x, const float* res, const float* gamma, const float* beta, const float* out,
+                             int cols) {
+    return cols % 128 == 0 && cols <= 1024 &&
+           ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(res) | reinterpret_cast<uintptr_t>(gamma) |
+             reinterpret_cast<uintptr_t>(beta) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+}
+static int launch_layernorm_reg(const float* x, const float* res, const float* gamma, const float* beta, float* out,
+                                __half* oh, long long rows, int cols, float eps, cudaStream_t st) {
+    const unsigned blocks = static_cast<unsigned>((rows * 32 + 127) / 128);
+    switch (cols / 128) {
+        case 1: tk::layernorm_rows_reg_kernel<1><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+        case 2: tk::layernorm_rows_reg_kernel<2><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+        case 3: tk::layernorm_rows_reg_kernel<3><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+        case 4: tk::layernorm_rows_reg_kernel<4><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+        case 5: tk::layernorm_rows_reg_kernel<5><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+        case 6: tk::layernorm_rows_reg_kernel<6><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+        case 7: tk::layernorm_rows_reg_kernel<7><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+        default: tk::layernorm_rows_reg_kernel<8><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+    }
+    return launch_error("layernorm_rows_reg_kernel launch");
 }
 
 TK_API int tk_layernorm_rows_f32(const float* x, const float* gamma, const float* beta, float* out, long long rows,
                                  int cols, float eps, void* stream) {
     if (!x || !out || rows <= 0 || cols <= 0) return TK_ERR_ARGS;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (layernorm_reg_ok(x, nullptr, gamma, beta, out, cols)) return launch_layernorm_reg(x, nullptr, gamma, beta, out, nullptr, rows, cols, eps, st);
     layernorm_rows_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(x, gamma, beta, out, rows, cols,
                                                                                           eps);
     return launch_error("layernorm_rows_kernel launch");
+}
+
+TK_API int tk_add_layernorm_rows_f32(const float* a, const float* b, const float* gamma, const float* beta, float* out,
+                                     void* out_half, long long rows, int cols, float eps, void* stream) {
+    if (!a || !out || rows <= 0 || cols <= 0) return TK_ERR_ARGS;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!layernorm_reg_ok(a, b, gamma, beta, out, cols)) return TK_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(out_half) & 7u) return TK_ERR_ALIGN;
+    return launch_layernorm_reg(a, b, gamma, beta, out, static_cast<__half*>(out_half), rows, cols, eps, st);
 }
 
 TK_API int tk_split_heads_f16(const float* x, int ld, int col0, int B, int S, int heads, int dh, int transpose,
@@ -1181,6 +1463,20 @@ TK_API int tk_split_heads_f16(const float* x, int ld, int col0, int B, int S, in
     if (!x || !out_half || B <= 0 || S <= 0 || heads <= 0 || dh <= 0 || col0 < 0 || ld < col0 + heads * dh)
         return TK_ERR_ARGS;
     TK_LAYER_PROLOGUE();
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out_half)) & 15u) == 0;
+    if (!transpose && dh % 8 == 0 && ld % 4 == 0 && col0 % 4 == 0 && aligned) {
+        split_heads_vec_kernel<<<blocks_for(static_cast<long long>(B) * heads * S * (dh / 8), d->sm_count), 256, 0, st>>>(
+            x, ld, col0, B, S, heads, dh, static_cast<__half*>(out_half));
+        return launch_error("split_heads_vec_kernel launch");
+    }
+    if (transpose && S % 32 == 0 && dh % 32 == 0) {
+        const long long tiles = static_cast<long long>(B) * heads * (S / 32) * (dh / 32);
+        if (tiles <= 0x7fffffffll) {
+            split_heads_t_kernel<<<static_cast<unsigned>(tiles), 256, 0, st>>>(x, ld, col0, S, heads, dh,
+                                                                               static_cast<__half*>(out_half));
+            return launch_error("split_heads_t_kernel launch");
+        }
+    }
     split_heads_kernel<<<blocks_for(static_cast<long long>(B) * heads * S * dh, d->sm_count), 256, 0, st>>>(
         x, ld, col0, B, S, heads, dh, transpose, static_cast<__half*>(out_half));
     return launch_error("split_heads_kernel launch");
@@ -1189,9 +1485,57 @@ TK_API int tk_split_heads_f16(const float* x, int ld, int col0, int B, int S, in
 TK_API int tk_merge_heads_f32(const float* ctx, int B, int S, int heads, int dh, float* out, void* stream) {
     if (!ctx || !out || B <= 0 || S <= 0 || heads <= 0 || dh <= 0) return TK_ERR_ARGS;
     TK_LAYER_PROLOGUE();
+    if (dh % 4 == 0 && ((reinterpret_cast<uintptr_t>(ctx) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0) {
+        merge_heads_vec_kernel<<<blocks_for(static_cast<long long>(B) * heads * S * (dh / 4), d->sm_count), 256, 0, st>>>(
+            ctx, B, S, heads, dh, out);
+        return launch_error("merge_heads_vec_kernel launch");
+    }
     merge_heads_kernel<<<blocks_for(static_cast<long long>(B) * heads * S * dh, d->sm_count), 256, 0, st>>>(ctx, B, S, heads,
                                                                                                          dh, out);
     return launch_error("merge_heads_kernel launch");
+}
+
+TK_API int tk_merge_heads_f16(const float* ctx, int B, int S, int heads, int dh, void* out_half, void* stream) {
+    if (!ctx || !out_half || B <= 0 || S <= 0 || heads <= 0 || dh <= 0) return TK_ERR_ARGS;
+    if (dh % 4 != 0) return TK_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(ctx) & 15u) || (reinterpret_cast<uintptr_t>(out_half) & 7u)) return TK_ERR_ALIGN;
+    TK_LAYER_PROLOGUE();
+    merge_heads_vec_kernel<<<blocks_for(static_cast<long long>(B) * heads * S * (dh / 4), d->sm_count), 256, 0, st>>>(
+        ctx, B, S, heads, dh, nullptr, static_cast<__half*>(out_half));
+    return launch_error("merge_heads_vec_kernel launch");
+}
+
+TK_API int tk_bias_act_f32_f16(const float* x, int ldx, const float* bias, float* out, int ld_out, void* out_half,
+                               int ld_half, int rows, int cols, int act, void* stream) {
+    if (!x || (!out && !out_half) || rows <= 0 || cols <= 0 || ldx < cols || act < 0 || act > 2) return TK_ERR_ARGS;
+    if ((out && ld_out < cols) || (out_half && ld_half < cols)) return TK_ERR_ARGS;
+    if (cols % 4 || ldx % 4 || (out && ld_out % 4) || (out_half && ld_half % 4)) return TK_ERR_SHAPE;
+    if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias)) & 15u) ||
+        (reinterpret_cast<uintptr_t>(out_half) & 7u))
+        return TK_ERR_ALIGN;
+    TK_LAYER_PROLOGUE();
+    bias_act_vec_kernel<<<blocks_for(static_cast<long long>(rows) * (cols / 4), d->sm_count), 256, 0, st>>>(
+        x, ldx, bias, out, rows, cols, ld_out, act, static_cast<__half*>(out_half), ld_half);
+    return launch_error("bias_act_vec_kernel launch");
+}
+
+// query, key and value heads out of one row of three projections side by side, in one launch: q and k as
+// [B*heads][S][dh], v transposed as [B*heads][dh][S]
+TK_API int tk_split_qkv_heads_f16(const float* x, int ld, int B, int S, int heads, int dh, void* q_half, void* k_half,
+                                  void* vt_half, void* stream) {
+    if (!x || !q_half || !k_half || !vt_half || B <= 0 || S <= 0 || heads <= 0 || dh <= 0 || ld < 3 * heads * dh)
+        return TK_ERR_ARGS;
+    if (dh % 32 || S % 32 || ld % 4) return TK_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q_half) | reinterpret_cast<uintptr_t>(k_half)) & 15u)
+        return TK_ERR_ALIGN;
+    TK_LAYER_PROLOGUE();
+    const long long tiles = static_cast<long long>(B) * heads * (S / 32) * (dh / 32);
+    const unsigned nb_qk = blocks_for(2ll * B * heads * S * (dh / 8), d->sm_count);
+    if (tiles + nb_qk > 0x7fffffffll) return TK_ERR_SHAPE;
+    split_qkv_heads_kernel<<<nb_qk + static_cast<unsigned>(tiles), 256, 0, st>>>(
+        x, ld, B, S, heads, dh, static_cast<__half*>(q_half), static_cast<__half*>(k_half), static_cast<__half*>(vt_half),
+        static_cast<int>(nb_qk));
+    return launch_error("split_qkv_heads_kernel launch");
 }
 
 TK_API int tk_tzgemm_batched(const void* A, const void* B, float* C, int M, int N, int K, int batch, long long stride_a,

@@ -166,6 +166,7 @@ GemmKernel::GemmKernel(int id, const std::string& name, DnnArena& arena, const f
 }
 
 void GemmKernel::prepare(stream_t stream) {
+    if (a_ready) return;
     if (bordered) TK_HOST_CHECK(backend().unborderHalf(bordered, bH, bW, bC, A, stream));  // rows 1.. of A stay zero
     else TK_HOST_CHECK(backend().rowsToHalf(input, M, K, K, A, M_pad, K_pad, stream));
 }
@@ -174,7 +175,8 @@ void OpKernel::executeImpl(stream_t s) {
     Backend& be = backend();
     switch (op) {
         case BiasAct:  // a = x [i0 rows][ld i2], b = bias, out [i0][i1 cols] ld i3, act i4
-            TK_HOST_CHECK(be.biasAct(a, i2, b, out, i0, i1, i3, i4, s));
+            if (hout) TK_HOST_CHECK(be.biasActHalf(a, i2, b, out, i3, hout, i5, i0, i1, i4, s));  // hout: ld i5; out may be null
+            else TK_HOST_CHECK(be.biasAct(a, i2, b, out, i0, i1, i3, i4, s));
             break;
         case MaxPool:  // a = x [H i0][W i1][C i2]
             TK_HOST_CHECK(be.maxpool2x2(a, i0, i1, i2, out, s));
@@ -183,16 +185,22 @@ void OpKernel::executeImpl(stream_t s) {
             TK_HOST_CHECK(be.add(a, b, out, static_cast<long long>(i0) * i1, s));
             break;
         case SoftmaxRows:  // rows i0 * i1, cols i2, scale f0
-            TK_HOST_CHECK(be.softmaxRows(a, out, static_cast<long long>(i0) * i1, i2, f0, s));
+            if (hout) TK_HOST_CHECK(be.softmaxRowsHalf(a, hout, static_cast<long long>(i0) * i1, i2, f0, s));
+            else TK_HOST_CHECK(be.softmaxRows(a, out, static_cast<long long>(i0) * i1, i2, f0, s));
             break;
-        case LayerNorm:  // rows i0, cols i1, gamma b, beta c
-            TK_HOST_CHECK(be.layernormRows(a, b, c, out, i0, i1, 1e-12f, s));
+        case LayerNorm:  // rows i0, cols i1, gamma b, beta c; res: added to a first
+            if (res || hout) TK_HOST_CHECK(be.addLayernormRows(a, res, b, c, out, hout, i0, i1, 1e-12f, s));
+            else TK_HOST_CHECK(be.layernormRows(a, b, c, out, i0, i1, 1e-12f, s));
             break;
         case SplitHeads:  // a [B i0 * S i1][ld i2] from col i3, heads i4, dh i5, transpose i6
             TK_HOST_CHECK(be.splitHeads(a, i2, i3, i0, i1, i4, i5, i6, hout, s));
             break;
         case MergeHeads:  // a [B*heads][S][dh] -> out [B*S][heads*dh]
-            TK_HOST_CHECK(be.mergeHeads(a, i0, i1, i4, i5, out, s));
+            if (hout) TK_HOST_CHECK(be.mergeHeadsHalf(a, i0, i1, i4, i5, hout, s));
+            else TK_HOST_CHECK(be.mergeHeads(a, i0, i1, i4, i5, out, s));
+            break;
+        case SplitQkv:  // a [B i0 * S i1][ld i2] = three projections side by side; heads i4, dh i5 -> hout, hout2, hout3
+            TK_HOST_CHECK(be.splitQkv(a, i2, i0, i1, i4, i5, hout, hout2, hout3, s));
             break;
         case BatchedGemm:  // out[batch i3] = f0 * ha [M i0][K i2] * hb [N i1][K i2]^T
             TK_HOST_CHECK(be.tzgemmBatched(ha, hb, out, i0, i1, i2, i3, f0, s));

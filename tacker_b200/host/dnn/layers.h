@@ -94,6 +94,7 @@ public:
     std::vector<int> getArgs() override { return std::vector<int>{M, N, K}; }
     void prepare(stream_t stream) override;
     const float* input;
+    bool a_ready = false;  // the producer of `input` writes the fp16 operand A itself: prepare() has nothing to do
     // alternative input: a bordered fp16 image [(bH + 2)][(bW + 2)][bC] whose interior, flattened, is the single row
     const void* bordered = nullptr;
     int bH = 0, bW = 0, bC = 0;
@@ -103,7 +104,7 @@ public:
 class OpKernel : public Kernel {
 public:
     enum Op { BiasAct, MaxPool, Add, SoftmaxRows, LayerNorm, SplitHeads, MergeHeads, BatchedGemm, RowsToHalf,
-              BiasActHalfBordered, MaxPoolHalfBordered };
+              BiasActHalfBordered, MaxPoolHalfBordered, SplitQkv };
     OpKernel(int id, const std::string& name, Op op) : op(op) {
         Id = id;
         kernelName = name;
@@ -117,8 +118,11 @@ public:
     const float* a = nullptr;
     const float* b = nullptr;
     const float* c = nullptr;
+    const float* res = nullptr;  // LayerNorm: second operand added to `a` before the normalisation (or null)
     float* out = nullptr;
-    void* hout = nullptr;
+    void* hout = nullptr;   // fp16 output; for BiasAct, SoftmaxRows, LayerNorm, MergeHeads: the operand of the next product
+    void* hout2 = nullptr;  // SplitQkv: key heads
+    void* hout3 = nullptr;  // SplitQkv: value heads, transposed
     const void* ha = nullptr;
     const void* hb = nullptr;
     int i0 = 0, i1 = 0, i2 = 0, i3 = 0, i4 = 0, i5 = 0, i6 = 0;

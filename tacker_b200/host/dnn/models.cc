@@ -81,6 +81,7 @@ float* DnnTask::dense(const float* x, int rows, int in, int out, int act, float*
     b->i3 = out;
     b->i4 = act;
     keep(b);
+    lastOp = b;
     return y;
 }
 
@@ -211,7 +212,72 @@ float* DnnTask::layernorm(const float* x, int rows, int cols) {
     k->i0 = rows;
     k->i1 = cols;
     keep(k);
+    lastOp = k;
     return y;
+}
+
+float* DnnTask::addLayernorm(const float* a, const float* b, int rows, int cols) {
+    if (cols % 128 != 0 || cols > 1024) return layernorm(addTo(a, b, rows, cols, 0), rows, cols);
+    nextId++;  // the addition's node: absorbed
+    float* y = arena.act(static_cast<size_t>(rows) * cols);
+    const int id8 = nextId++;
+    auto* k = new OpKernel(id8, "AddLayerNorm_" + std::to_string(id8), OpKernel::LayerNorm);
+    k->a = a;
+    k->res = b;
+    k->b = arena.weightsF32(cols, 7000 + nextId, 0.9f, 1.1f);
+    k->c = arena.weightsF32(cols, 7500 + nextId, -0.05f, 0.05f);
+    k->out = y;
+    k->i0 = rows;
+    k->i1 = cols;
+    keep(k);
+    lastOp = k;
+    return y;
+}
+
+float* DnnTask::denseParts(const float* x, int rows, int in, int out, int parts, int act) {
+    const int total = parts * out;
+    if (out % 64 != 0) throw std::runtime_error("denseParts: the parts must be multiples of 64 columns wide");
+    const int id3 = nextId;  // ids of part i: id3 + 2 i (product), id3 + 2 i + 1 (bias + activation)
+    auto* g = new GemmKernel(id3, "Dot_" + std::to_string(id3), arena, x, rows, in, total, 2000 + id3);
+    keep(g);
+    float* y = arena.act(static_cast<size_t>(rows) * total);
+    float* bias = arena.act(static_cast<size_t>(total));
+    const float scale = std::sqrt(6.0f / static_cast<float>(in));
+    std::vector<uint16_t> w(static_cast<size_t>(out) * g->K_pad);
+    std::vector<float> bv(out);
+    for (int p = 0; p < parts; ++p) {
+        // what dense() p would have drawn: weights [N_pad = out][K_pad] with seed 2000 + its id, bias with 6000 + the next id
+        for (size_t i = 0; i < w.size(); ++i) w[i] = dnn_half_bits((tk_unit_draw(2000 + id3 + 2 * p, i) * 2.0f - 1.0f) * scale);
+        backend().upload(static_cast<char*>(g->B) + static_cast<size_t>(p) * w.size() * 2, w.data(), w.size() * 2, nullptr);
+        for (int i = 0; i < out; ++i) bv[i] = -0.05f + tk_unit_draw(6000 + id3 + 2 * p + 1, i) * 0.1f;
+        backend().upload(bias + static_cast<size_t>(p) * out, bv.data(), bv.size() * sizeof(float), nullptr);
+    }
+    backend().streamSync(nullptr);
+    nextId += 2 * parts;
+    lastLayer = g;
+    lastBias = bias;
+    auto* b = new OpKernel(id3 + 1, "BiasAct_" + std::to_string(id3 + 1), OpKernel::BiasAct);
+    b->a = g->C;
+    b->b = bias;
+    b->out = y;
+    b->i0 = rows;
+    b->i1 = total;
+    b->i2 = g->N_pad;
+    b->i3 = total;
+    b->i4 = act;
+    keep(b);
+    lastOp = b;
+    return y;
+}
+
+bool DnnTask::feedHalf(OpKernel* producer, GemmKernel* consumer, int rows, int cols) {
+    if (!producer || !consumer || rows % 128 != 0 || cols % 64 != 0 || consumer->M_pad != rows || consumer->K_pad != cols)
+        return false;
+    if (producer->op == OpKernel::LayerNorm && (cols % 128 != 0 || cols > 1024)) return false;
+    if (producer->op == OpKernel::BiasAct) producer->i5 = consumer->K_pad;
+    producer->hout = consumer->A;
+    consumer->a_ready = true;
+    return true;
 }
 
 static void normal_input(std::vector<float>& h, uint64_t seed) {  // ~N(0,1) by Box-Muller on counter draws
@@ -310,39 +376,37 @@ Bert::Bert(int layers, int batch_, int seq_) : DnnTask(2, "bert"), batch(batch_)
                 (tk_unit_draw(1000 + token, c) - 0.5f) * 0.1f + (tk_unit_draw(900000 + (r % seq), c) - 0.5f) * 0.02f;
     }
     input = arena.act(hostInput.size());
+    // Every producer of a product's input writes that product's fp16 operand itself (normalisation, GELU, softmax and
+    // head merge have an fp16 output next to or instead of the fp32 one), the three attention projections are one
+    // product and their heads are cut out in one launch: 15 launches per layer instead of 30.  The node numbers, which
+    // fix the seeds, advance as if every absorbed node were still there.
     const float* x = layernorm(input, rows, hidden);
+    OpKernel* norm = lastOp;
     for (int l = 0; l < layers; ++l) {
-        const float* q = dense(x, rows, hidden, hidden, 0);
-        const float* k = dense(x, rows, hidden, hidden, 0);
-        const float* v = dense(x, rows, hidden, hidden, 0);
+        // query, key and value projections as one product of 3 x 768 columns
+        const float* qkv = denseParts(x, rows, hidden, hidden, 3, 0);
+        feedHalf(norm, static_cast<GemmKernel*>(lastLayer), rows, hidden);
         void* qh = arena.half(static_cast<size_t>(rows) * hidden);
         void* kh = arena.half(static_cast<size_t>(rows) * hidden);
         void* vt = arena.half(static_cast<size_t>(rows) * hidden);
-        const float* src[3] = {q, k, v};
-        void* dst[3] = {qh, kh, vt};
-        for (int i = 0; i < 3; ++i) {
-            const int id10 = nextId++;
-            auto* s = new OpKernel(id10, "SplitHeads_" + std::to_string(id10), OpKernel::SplitHeads);
-            s->a = src[i];
-            s->hout = dst[i];
-            s->i0 = batch, s->i1 = seq, s->i2 = hidden, s->i3 = 0, s->i4 = heads, s->i5 = dh, s->i6 = (i == 2);
-            keep(s);
-        }
+        const int id10 = nextId;
+        nextId += 3;  // the three head splits
+        auto* sp = new OpKernel(id10, "SplitHeads_" + std::to_string(id10), OpKernel::SplitQkv);
+        sp->a = qkv, sp->hout = qh, sp->hout2 = kh, sp->hout3 = vt;
+        sp->i0 = batch, sp->i1 = seq, sp->i2 = 3 * hidden, sp->i4 = heads, sp->i5 = dh;
+        keep(sp);
         float* scores = arena.act(static_cast<size_t>(bh) * seq * seq);
         const int id11 = nextId++;
         auto* g1 = new OpKernel(id11, "BatchMatMul_" + std::to_string(id11), OpKernel::BatchedGemm);
         g1->ha = qh, g1->hb = kh, g1->out = scores;
         g1->i0 = seq, g1->i1 = seq, g1->i2 = dh, g1->i3 = bh, g1->f0 = 1.0f / std::sqrt(static_cast<float>(dh));
         keep(g1);
+        void* ph = arena.half(static_cast<size_t>(bh) * seq * seq);
         const int id12 = nextId++;
         auto* sm = new OpKernel(id12, "Softmax_" + std::to_string(id12), OpKernel::SoftmaxRows);
-        sm->a = scores, sm->out = scores, sm->i0 = bh, sm->i1 = seq, sm->i2 = seq, sm->f0 = 1.0f;
+        sm->a = scores, sm->hout = ph, sm->i0 = bh, sm->i1 = seq, sm->i2 = seq, sm->f0 = 1.0f;  // probabilities as fp16
         keep(sm);
-        void* ph = arena.half(static_cast<size_t>(bh) * seq * seq);
-        const int id13 = nextId++;
-        auto* th = new OpKernel(id13, "Convert_" + std::to_string(id13), OpKernel::RowsToHalf);
-        th->a = scores, th->hout = ph, th->i0 = bh * seq, th->i1 = seq;
-        keep(th);
+        nextId++;  // the conversion node: absorbed by the softmax
         float* ctx = arena.act(static_cast<size_t>(rows) * hidden);
         const int id14 = nextId++;
         auto* g2 = new OpKernel(id14, "BatchMatMul_" + std::to_string(id14), OpKernel::BatchedGemm);
@@ -355,10 +419,16 @@ Bert::Bert(int layers, int batch_, int seq_) : DnnTask(2, "bert"), batch(batch_)
         mh->a = ctx, mh->out = merged, mh->i0 = batch, mh->i1 = seq, mh->i4 = heads, mh->i5 = dh;
         keep(mh);
         const float* proj = dense(merged, rows, hidden, hidden, 0);
-        x = layernorm(addTo(proj, x, rows, hidden, 0), rows, hidden);
+        feedHalf(mh, static_cast<GemmKernel*>(lastLayer), rows, hidden);  // the merge then writes fp16 only
+        x = addLayernorm(proj, x, rows, hidden);
+        norm = lastOp;
         const float* h1 = dense(x, rows, hidden, ffn, 2);
+        feedHalf(norm, static_cast<GemmKernel*>(lastLayer), rows, hidden);
+        OpKernel* gelu = lastOp;
         const float* h2 = dense(h1, rows, ffn, hidden, 0);
-        x = layernorm(addTo(h2, x, rows, hidden, 0), rows, hidden);
+        if (feedHalf(gelu, static_cast<GemmKernel*>(lastLayer), rows, ffn)) gelu->out = nullptr;  // nobody reads the fp32 copy
+        x = addLayernorm(h2, x, rows, hidden);
+        norm = lastOp;
     }
     result = x;  // the last layer's hidden states [batch * seq][hidden]
     resultCount = static_cast<size_t>(rows) * hidden;

@@ -50,8 +50,19 @@ protected:
     // what the last conv / dense helper created, for builders that replace the seeded constants by loaded ones
     TzLayer* lastLayer = nullptr;
     float* lastBias = nullptr;
+    // the last bias + activation or normalisation node created (dense(), denseParts(), layernorm(), addLayernorm())
+    OpKernel* lastOp = nullptr;
+    // Lets `producer` write the fp16 operand of `consumer` directly (no conversion pass in between).  Possible when the
+    // operand needs no padding: rows a multiple of 128, cols a multiple of 64.  Returns whether it was done.
+    bool feedHalf(OpKernel* producer, GemmKernel* consumer, int rows, int cols);
     float* addTo(const float* a, const float* b, int rows, int cols, int act);
     float* layernorm(const float* x, int rows, int cols);
+    // layernorm(a + b) as one kernel; numbered and seeded like addTo(a, b, ..., 0) followed by layernorm()
+    float* addLayernorm(const float* a, const float* b, int rows, int cols);
+    // `parts` dense layers of the same shape on the same input as ONE GEMM of parts * out columns (weights and biases
+    // of the parts side by side); numbered and seeded like `parts` consecutive dense() calls.  Returns the
+    // [rows][parts * out] output; part i is its columns i * out ...
+    float* denseParts(const float* x, int rows, int in, int out, int parts, int act);
 };
 
 // VGG16, batch 1, 224 x 224 x 3: 13 conv3x3 + 3 FC

@@ -500,6 +500,31 @@ def layernorm_rows_f32(x, gamma, beta, out, rows, cols, eps=1e-12, stream: int =
                                       C.c_float(eps), _vp(stream)), "tk_layernorm_rows_f32")
 
 
+def add_layernorm_rows_f32(a, b, gamma, beta, out, rows, cols, eps=1e-12, stream: int = 0, out_half=0) -> None:
+    check(lib().tk_add_layernorm_rows_f32(_vp(a), _vp(b), _vp(gamma), _vp(beta), _vp(out), _vp(out_half),
+                                          C.c_longlong(rows), cols, C.c_float(eps), _vp(stream)),
+          "tk_add_layernorm_rows_f32")
+
+
+def bias_act_f32_f16(x, ldx, bias, out, ld_out, out_half, ld_half, rows, cols, act, stream: int = 0) -> None:
+    check(lib().tk_bias_act_f32_f16(_vp(x), ldx, _vp(bias), _vp(out), ld_out, _vp(out_half), ld_half, rows, cols, act,
+                                    _vp(stream)), "tk_bias_act_f32_f16")
+
+
+def softmax_rows_f16(x, out_half, rows, cols, scale, stream: int = 0) -> None:
+    check(lib().tk_softmax_rows_f16(_vp(x), _vp(out_half), C.c_longlong(rows), cols, C.c_float(scale), _vp(stream)),
+          "tk_softmax_rows_f16")
+
+
+def merge_heads_f16(ctx, B, S, heads, dh, out_half, stream: int = 0) -> None:
+    check(lib().tk_merge_heads_f16(_vp(ctx), B, S, heads, dh, _vp(out_half), _vp(stream)), "tk_merge_heads_f16")
+
+
+def split_qkv_heads_f16(x, ld, B, S, heads, dh, q_half, k_half, vt_half, stream: int = 0) -> None:
+    check(lib().tk_split_qkv_heads_f16(_vp(x), ld, B, S, heads, dh, _vp(q_half), _vp(k_half), _vp(vt_half), _vp(stream)),
+          "tk_split_qkv_heads_f16")
+
+
 def split_heads_f16(x, ld, col0, B, S, heads, dh, transpose, out_half, stream: int = 0) -> None:
     check(lib().tk_split_heads_f16(_vp(x), ld, col0, B, S, heads, dh, transpose, _vp(out_half), _vp(stream)),
           "tk_split_heads_f16")

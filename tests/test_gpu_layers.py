@@ -77,6 +77,112 @@ def test_elementwise_and_row_kernels(cuda, oracle):
     assert np.array_equal(hh[:rows, :cols], x.astype(np.float16)) and not hh[rows:].any() and not hh[:, cols:].any()
 
 
+def test_row_kernels_on_aligned_shapes(cuda, oracle):
+    """The same kernels on the shapes the models use (columns a multiple of 128, 16-byte aligned arrays), where they
+    move 16 bytes per thread and the normalisation keeps its row in registers; plus layernorm(a + b) in one pass."""
+    from tacker_b200 import ops
+
+    rows, cols = 96, 768
+    x = oracle.normal_f32(rows * cols, 14).reshape(rows, cols)
+    y = oracle.normal_f32(rows * cols, 15).reshape(rows, cols)
+    g = oracle.uniform_f32(cols, 5, 0.5, 1.5)
+    b = oracle.uniform_f32(cols, 6, -0.5, 0.5)
+    dx, dy, dg, db = to_dev(cuda, x), to_dev(cuda, y), to_dev(cuda, g), to_dev(cuda, b)
+    out = cuda.zeros((rows, cols), dtype=cuda.float32, device="cuda")
+    x64, y64 = x.astype(np.float64), y.astype(np.float64)
+    ln = lambda v: (v - v.mean(1, keepdims=True)) / np.sqrt(v.var(1, keepdims=True) + 1e-5) * g + b
+    ops.layernorm_rows_f32(dx.data_ptr(), dg.data_ptr(), db.data_ptr(), out.data_ptr(), rows, cols, 1e-5)
+    assert np.abs(out.cpu().numpy() - ln(x64)).max() < 1e-4
+    ops.add_layernorm_rows_f32(dx.data_ptr(), dy.data_ptr(), dg.data_ptr(), db.data_ptr(), out.data_ptr(), rows, cols, 1e-5)
+    assert np.abs(out.cpu().numpy() - ln((x + y).astype(np.float64))).max() < 1e-4
+    with pytest.raises(Exception):
+        ops.add_layernorm_rows_f32(dx.data_ptr(), dy.data_ptr(), dg.data_ptr(), db.data_ptr(), out.data_ptr(), rows, 200, 1e-5)
+    wide = cuda.zeros((rows, 832), dtype=cuda.float32, device="cuda")                       # leading dimensions beyond cols
+    ops.bias_act_f32(dx.data_ptr(), cols, db.data_ptr(), wide.data_ptr(), rows, cols, 832, 2)
+    v = x64 + b
+    gelu = 0.5 * v * (1 + np.tanh(0.7978845608028654 * (v + 0.044715 * v ** 3)))
+    w = wide.cpu().numpy()
+    assert np.abs(w[:, :cols] - gelu).max() < 1e-5 and not w[:, cols:].any()
+    ops.bias_act_f32(dx.data_ptr(), cols, 0, out.data_ptr(), rows, cols, cols, 1)
+    assert np.array_equal(out.cpu().numpy(), np.maximum(x, 0))
+    ops.add_f32(dx.data_ptr(), dy.data_ptr(), out.data_ptr(), rows * cols)
+    assert np.array_equal(out.cpu().numpy(), x + y)
+    half = cuda.zeros((128, 832), dtype=cuda.float16, device="cuda")
+    ops.rows_f32_to_f16(dx.data_ptr(), rows, cols, cols, half.data_ptr(), 128, 832)
+    hh = half.cpu().numpy()
+    assert np.array_equal(hh[:rows, :cols], x.astype(np.float16)) and not hh[rows:].any() and not hh[:, cols:].any()
+    ops.rows_f32_to_f16(dx.data_ptr(), rows, 764, cols, half.data_ptr(), 128, 832)       # a ragged last group of 8
+    hh = half.cpu().numpy()
+    assert np.array_equal(hh[:rows, :764], x[:, :764].astype(np.float16)) and not hh[:, 764:].any()
+    # heads cut out of a wider row (three projections side by side), both output layouts
+    B, S, heads, dh = 2, 64, 3, 64
+    q = oracle.normal_f32(B * S * 3 * heads * dh, 16).reshape(B * S, 3 * heads * dh)
+    dq = to_dev(cuda, q)
+    for part, transpose in ((0, 0), (1, 0), (2, 1)):
+        oh = cuda.zeros(B * heads * S * dh, dtype=cuda.float16, device="cuda")
+        ops.split_heads_f16(dq.data_ptr(), 3 * heads * dh, part * heads * dh, B, S, heads, dh, transpose, oh.data_ptr())
+        cuda.cuda.synchronize()
+        want = q[:, part * heads * dh:(part + 1) * heads * dh].reshape(B, S, heads, dh).transpose(0, 2, 1, 3)
+        if transpose:
+            want = want.transpose(0, 1, 3, 2)
+        assert np.array_equal(oh.cpu().numpy().reshape(want.shape), want.astype(np.float16))
+
+
+def test_producers_that_write_the_next_operand(cuda, oracle):
+    """Normalisation, bias + GELU, softmax and head merge with an fp16 output (the operand of the product that follows),
+    and the heads of three projections cut out in one launch: the same values as the two-step forms, rounded once."""
+    from tacker_b200 import ops
+
+    rows, cols = 128, 768
+    x = oracle.normal_f32(rows * cols, 21).reshape(rows, cols)
+    y = oracle.normal_f32(rows * cols, 22).reshape(rows, cols)
+    g = oracle.uniform_f32(cols, 5, 0.5, 1.5)
+    b = oracle.uniform_f32(cols, 6, -0.5, 0.5)
+    dx, dy, dg, db = to_dev(cuda, x), to_dev(cuda, y), to_dev(cuda, g), to_dev(cuda, b)
+    out = cuda.zeros((rows, cols), dtype=cuda.float32, device="cuda")
+    oh = cuda.zeros((rows, cols), dtype=cuda.float16, device="cuda")
+    for res in (dy.data_ptr(), 0):
+        ops.add_layernorm_rows_f32(dx.data_ptr(), res, dg.data_ptr(), db.data_ptr(), out.data_ptr(), rows, cols, 1e-5,
+                                   out_half=oh.data_ptr())
+        cuda.cuda.synchronize()
+        assert np.array_equal(oh.cpu().numpy(), out.cpu().numpy().astype(np.float16))
+        v = (x + y if res else x).astype(np.float64)
+        ln = (v - v.mean(1, keepdims=True)) / np.sqrt(v.var(1, keepdims=True) + 1e-5) * g + b
+        assert np.abs(out.cpu().numpy() - ln).max() < 1e-4
+    ops.bias_act_f32(dx.data_ptr(), cols, db.data_ptr(), out.data_ptr(), rows, cols, cols, 2)
+    wide = cuda.zeros((rows, 832), dtype=cuda.float16, device="cuda")
+    ops.bias_act_f32_f16(dx.data_ptr(), cols, db.data_ptr(), 0, 0, wide.data_ptr(), 832, rows, cols, 2)
+    cuda.cuda.synchronize()
+    w = wide.cpu().numpy()
+    assert np.array_equal(w[:, :cols], out.cpu().numpy().astype(np.float16)) and not w[:, cols:].any()
+    both = cuda.zeros((rows, cols), dtype=cuda.float32, device="cuda")
+    ops.bias_act_f32_f16(dx.data_ptr(), cols, db.data_ptr(), both.data_ptr(), cols, oh.data_ptr(), cols, rows, cols, 2)
+    assert np.array_equal(both.cpu().numpy(), out.cpu().numpy()) and np.array_equal(oh.cpu().numpy(), w[:, :cols])
+    sm = cuda.zeros((rows, cols), dtype=cuda.float32, device="cuda")
+    ops.softmax_rows_f32(dx.data_ptr(), sm.data_ptr(), rows, cols, 0.5)
+    ops.softmax_rows_f16(dx.data_ptr(), oh.data_ptr(), rows, cols, 0.5)
+    cuda.cuda.synchronize()
+    assert np.array_equal(oh.cpu().numpy(), sm.cpu().numpy().astype(np.float16))
+    B, S, heads, dh = 2, 64, 3, 64
+    hidden = heads * dh
+    qkv = oracle.normal_f32(B * S * 3 * hidden, 23).reshape(B * S, 3 * hidden)
+    dq = to_dev(cuda, qkv)
+    q, k, vt = (cuda.zeros(B * heads * S * dh, dtype=cuda.float16, device="cuda") for _ in range(3))
+    ops.split_qkv_heads_f16(dq.data_ptr(), 3 * hidden, B, S, heads, dh, q.data_ptr(), k.data_ptr(), vt.data_ptr())
+    cuda.cuda.synchronize()
+    for part, got in enumerate((q, k, vt)):
+        want = qkv[:, part * hidden:(part + 1) * hidden].reshape(B, S, heads, dh).transpose(0, 2, 1, 3)
+        if part == 2:
+            want = want.transpose(0, 1, 3, 2)
+        assert np.array_equal(got.cpu().numpy().reshape(want.shape), want.astype(np.float16))
+    ctx = oracle.normal_f32(B * heads * S * dh, 24).reshape(B * heads, S, dh)
+    mh = cuda.zeros((B * S, hidden), dtype=cuda.float16, device="cuda")
+    ops.merge_heads_f16(to_dev(cuda, ctx).data_ptr(), B, S, heads, dh, mh.data_ptr())
+    cuda.cuda.synchronize()
+    want = ctx.reshape(B, heads, S, dh).transpose(0, 2, 1, 3).reshape(B * S, hidden)
+    assert np.array_equal(mh.cpu().numpy(), want.astype(np.float16))
+
+
 def test_attention_through_batched_tzgemm(cuda, oracle):
     """softmax(Q K^T / sqrt(d)) V for B*heads independent heads: split, two batched tzgemms, merge."""
     from tacker_b200 import ops
