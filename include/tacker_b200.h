@@ -399,22 +399,22 @@ int tk_add_f32(const float* a, const float* b, float* out, long long n, void* st
 int tk_softmax_rows_f32(const float* x, float* out, long long rows, int cols, float scale, void* stream);
 int tk_layernorm_rows_f32(const float* x, const float* gamma, const float* beta, float* out, long long rows, int cols,
                           float eps, void* stream);
-/* out = layernorm(a + b) row by row (the residual addition and the normalisation that follows it in one pass; b may
- * be null); rows of 128, 256, .., 1024 columns in 16-byte aligned arrays, else TK_ERR_SHAPE */
-int tk_add_layernorm_rows_f32(const float* a, const float* b, const float* gamma, const float* beta, float* out,
-                              void* out_half, long long rows, int cols, float eps, void* stream);
+/* out = layernorm((a + bias) + b) row by row (the bias of the product that made a, the residual addition and the
+ * normalisation in one pass; bias [cols] and b may be null); rows of 128, 256, .., 1024 columns in 16-byte aligned arrays, else TK_ERR_SHAPE */
+int tk_add_layernorm_rows_f32(const float* a, const float* bias, const float* b, const float* gamma, const float* beta,
+                              float* out, void* out_half, long long rows, int cols, float eps, void* stream);
 /* Producers that also (or only) write the fp16 operand of the product that follows, so that it needs no conversion
  * pass of its own: tk_add_layernorm_rows_f32 (b and out_half may be null; out_half is [rows][cols] fp16),
  * tk_bias_act_f32_f16 (out or out_half may be null; columns and leading dimensions multiples of 4),
  * tk_softmax_rows_f16, tk_merge_heads_f16, and tk_split_qkv_heads_f16: the heads of three projections that lie side by
- * side in one row (ld >= 3 * heads * dh), q and k as [B*heads][S][dh], v transposed [B*heads][dh][S], in one launch
- * (S and dh multiples of 32). */
+ * side in one row (ld >= 3 * heads * dh; bias [3 * heads * dh] or null is added first), q and k as [B*heads][S][dh],
+ * v transposed [B*heads][dh][S], in one launch (S and dh multiples of 32). */
 int tk_bias_act_f32_f16(const float* x, int ldx, const float* bias, float* out, int ld_out, void* out_half, int ld_half,
                         int rows, int cols, int act, void* stream);
 int tk_softmax_rows_f16(const float* x, void* out_half, long long rows, int cols, float scale, void* stream);
 int tk_merge_heads_f16(const float* ctx, int B, int S, int heads, int dh, void* out_half, void* stream);
-int tk_split_qkv_heads_f16(const float* x, int ld, int B, int S, int heads, int dh, void* q_half, void* k_half,
-                           void* vt_half, void* stream);
+int tk_split_qkv_heads_f16(const float* x, const float* bias, int ld, int B, int S, int heads, int dh, void* q_half,
+                           void* k_half, void* vt_half, void* stream);
 /* x [B*S][ld] fp32, `heads` blocks of `dh` columns from col0 -> fp16 [B*heads][S][dh] (transpose 0) or
  * [B*heads][dh][S] (transpose 1); and the way back for the attention context */
 int tk_split_heads_f16(const float* x, int ld, int col0, int B, int S, int heads, int dh, int transpose,

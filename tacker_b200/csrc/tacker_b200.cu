@@ -1179,8 +1179,9 @@ __global__ void split_heads_t_kernel(const float* __restrict__ x, int ld, int co
 
 // q, k (eight head columns per thread) and v (transposed through shared-memory tiles) in one launch: blocks
 // 0 .. nb_qk - 1 stride over the q and k elements, every later block takes one 32 x 32 tile of v
-__global__ void split_qkv_heads_kernel(const float* __restrict__ x, int ld, int B, int S, int heads, int dh,
-                                       __half* __restrict__ q, __half* __restrict__ k, __half* __restrict__ vt, int nb_qk) {
+__global__ void split_qkv_heads_kernel(const float* __restrict__ x, const float* __restrict__ bias, int ld, int B, int S,
+                                       int heads, int dh, __half* __restrict__ q, __half* __restrict__ k,
+                                       __half* __restrict__ vt, int nb_qk) {
     __shared__ float tile[32][33];
     const int hidden = heads * dh;
     if (static_cast<int>(blockIdx.x) < nb_qk) {
@@ -1194,8 +1195,15 @@ __global__ void split_qkv_heads_kernel(const float* __restrict__ x, int ld, int 
             const int s = static_cast<int>((e / g8) % S);
             const int h = static_cast<int>((e / (static_cast<long long>(g8) * S)) % heads);
             const int b = static_cast<int>(e / (static_cast<long long>(g8) * S * heads));
-            const float* p = x + (static_cast<size_t>(b) * S + s) * ld + part * hidden + h * dh + d;
-            const float4 u = __ldg(reinterpret_cast<const float4*>(p)), w = __ldg(reinterpret_cast<const float4*>(p + 4));
+            const int col = part * hidden + h * dh + d;
+            const float* p = x + (static_cast<size_t>(b) * S + s) * ld + col;
+            float4 u = __ldg(reinterpret_cast<const float4*>(p)), w = __ldg(reinterpret_cast<const float4*>(p + 4));
+            if (bias) {
+                const float4 bu = __ldg(reinterpret_cast<const float4*>(bias + col));
+                const float4 bw = __ldg(reinterpret_cast<const float4*>(bias + col + 4));
+                u.x += bu.x, u.y += bu.y, u.z += bu.z, u.w += bu.w;
+                w.x += bw.x, w.y += bw.y, w.z += bw.z, w.w += bw.w;
+            }
             __half2 hh[4] = {__floats2half2_rn(u.x, u.y), __floats2half2_rn(u.z, u.w), __floats2half2_rn(w.x, w.y),
                              __floats2half2_rn(w.z, w.w)};
             *reinterpret_cast<uint4*>((part ? k : q) + ((static_cast<size_t>(b) * heads + h) * S + s) * dh + d) =
@@ -1211,9 +1219,11 @@ __global__ void split_qkv_heads_kernel(const float* __restrict__ x, int ld, int 
     t /= tiles_s;
     const int h = t % heads, b = t / heads;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int vcol = 2 * hidden + h * dh + td * 32 + tx;
+    const float vb = bias ? __ldg(bias + vcol) : 0.0f;
 #pragma unroll
     for (int i = ty; i < 32; i += 8)
-        tile[i][tx] = __ldg(x + (static_cast<size_t>(b) * S + ts * 32 + i) * ld + 2 * hidden + h * dh + td * 32 + tx);
+        tile[i][tx] = __ldg(x + (static_cast<size_t>(b) * S + ts * 32 + i) * ld + vcol) + vb;
     __syncthreads();
     __half* o = vt + (static_cast<size_t>(b) * heads + h) * dh * S;
 #pragma unroll
@@ -1245,8 +1255,9 @@ __global__ void merge_heads_vec_kernel(const float* __restrict__ ctx, int B, int
 // one warp per row, the row (plus an optional second operand `res`, added first) held in registers: NV float4 per
 // lane, cols = 128 NV.  Same two-pass mean / variance as layernorm_rows_kernel.
 template <int NV>
-__global__ void layernorm_rows_reg_kernel(const float* __restrict__ x, const float* __restrict__ res,
-                                          const float* __restrict__ gamma, const float* __restrict__ beta,
+__global__ void layernorm_rows_reg_kernel(const float* __restrict__ x, const float* __restrict__ bias,
+                                          const float* __restrict__ res, const float* __restrict__ gamma,
+                                          const float* __restrict__ beta,
                                           float* __restrict__ out, __half* __restrict__ out_half, long long rows,
                                           float eps) {
     constexpr int cols = 128 * NV;
@@ -1257,6 +1268,13 @@ __global__ void layernorm_rows_reg_kernel(const float* __restrict__ x, const flo
     float4 v[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) v[i] = xr[lane + 32 * i];
+    if (bias) {  // the bias of the product whose raw output x is: added first, as the separate pass did
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias) + lane + 32 * i);
+            v[i].x += b4.x, v[i].y += b4.y, v[i].z += b4.z, v[i].w += b4.w;
+        }
+    }
     if (res) {
         const float4* rr = reinterpret_cast<const float4*>(res + row * cols);
 #pragma unroll
@@ -1423,18 +1441,18 @@ static bool layernorm_reg_ok(const float* x, const float* res, const float* gamm
            ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(res) | reinterpret_cast<uintptr_t>(gamma) |
              reinterpret_cast<uintptr_t>(beta) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
 }
-static int launch_layernorm_reg(const float* x, const float* res, const float* gamma, const float* beta, float* out,
-                                __half* oh, long long rows, int cols, float eps, cudaStream_t st) {
+static int launch_layernorm_reg(const float* x, const float* bias, const float* res, const float* gamma, const float* beta,
+                                float* out, __half* oh, long long rows, int cols, float eps, cudaStream_t st) {
     const unsigned blocks = static_cast<unsigned>((rows * 32 + 127) / 128);
     switch (cols / 128) {
-        case 1: tk::layernorm_rows_reg_kernel<1><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
-        case 2: tk::layernorm_rows_reg_kernel<2><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
-        case 3: tk::layernorm_rows_reg_kernel<3><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
-        case 4: tk::layernorm_rows_reg_kernel<4><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
-        case 5: tk::layernorm_rows_reg_kernel<5><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
-        case 6: tk::layernorm_rows_reg_kernel<6><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
-        case 7: tk::layernorm_rows_reg_kernel<7><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
-        default: tk::layernorm_rows_reg_kernel<8><<<blocks, 128, 0, st>>>(x, res, gamma, beta, out, oh, rows, eps); break;
+        case 1: tk::layernorm_rows_reg_kernel<1><<<blocks, 128, 0, st>>>(x, bias, res, gamma, beta, out, oh, rows, eps); break;
+        case 2: tk::layernorm_rows_reg_kernel<2><<<blocks, 128, 0, st>>>(x, bias, res, gamma, beta, out, oh, rows, eps); break;
+        case 3: tk::layernorm_rows_reg_kernel<3><<<blocks, 128, 0, st>>>(x, bias, res, gamma, beta, out, oh, rows, eps); break;
+        case 4: tk::layernorm_rows_reg_kernel<4><<<blocks, 128, 0, st>>>(x, bias, res, gamma, beta, out, oh, rows, eps); break;
+        case 5: tk::layernorm_rows_reg_kernel<5><<<blocks, 128, 0, st>>>(x, bias, res, gamma, beta, out, oh, rows, eps); break;
+        case 6: tk::layernorm_rows_reg_kernel<6><<<blocks, 128, 0, st>>>(x, bias, res, gamma, beta, out, oh, rows, eps); break;
+        case 7: tk::layernorm_rows_reg_kernel<7><<<blocks, 128, 0, st>>>(x, bias, res, gamma, beta, out, oh, rows, eps); break;
+        default: tk::layernorm_rows_reg_kernel<8><<<blocks, 128, 0, st>>>(x, bias, res, gamma, beta, out, oh, rows, eps); break;
     }
     return launch_error("layernorm_rows_reg_kernel launch");
 }
@@ -1443,19 +1461,20 @@ TK_API int tk_layernorm_rows_f32(const float* x, const float* gamma, const float
                                  int cols, float eps, void* stream) {
     if (!x || !out || rows <= 0 || cols <= 0) return TK_ERR_ARGS;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (layernorm_reg_ok(x, nullptr, gamma, beta, out, cols)) return launch_layernorm_reg(x, nullptr, gamma, beta, out, nullptr, rows, cols, eps, st);
+    if (layernorm_reg_ok(x, nullptr, gamma, beta, out, cols)) return launch_layernorm_reg(x, nullptr, nullptr, gamma, beta, out, nullptr, rows, cols, eps, st);
     layernorm_rows_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, st>>>(x, gamma, beta, out, rows, cols,
                                                                                           eps);
     return launch_error("layernorm_rows_kernel launch");
 }
 
-TK_API int tk_add_layernorm_rows_f32(const float* a, const float* b, const float* gamma, const float* beta, float* out,
-                                     void* out_half, long long rows, int cols, float eps, void* stream) {
+TK_API int tk_add_layernorm_rows_f32(const float* a, const float* bias, const float* b, const float* gamma,
+                                     const float* beta, float* out, void* out_half, long long rows, int cols, float eps,
+                                     void* stream) {
     if (!a || !out || rows <= 0 || cols <= 0) return TK_ERR_ARGS;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!layernorm_reg_ok(a, b, gamma, beta, out, cols)) return TK_ERR_SHAPE;
-    if (reinterpret_cast<uintptr_t>(out_half) & 7u) return TK_ERR_ALIGN;
-    return launch_layernorm_reg(a, b, gamma, beta, out, static_cast<__half*>(out_half), rows, cols, eps, st);
+    if ((reinterpret_cast<uintptr_t>(out_half) & 7u) || (reinterpret_cast<uintptr_t>(bias) & 15u)) return TK_ERR_ALIGN;
+    return launch_layernorm_reg(a, bias, b, gamma, beta, out, static_cast<__half*>(out_half), rows, cols, eps, st);
 }
 
 TK_API int tk_split_heads_f16(const float* x, int ld, int col0, int B, int S, int heads, int dh, int transpose,
@@ -1521,20 +1540,21 @@ TK_API int tk_bias_act_f32_f16(const float* x, int ldx, const float* bias, float
 
 // query, key and value heads out of one row of three projections side by side, in one launch: q and k as
 // [B*heads][S][dh], v transposed as [B*heads][dh][S]
-TK_API int tk_split_qkv_heads_f16(const float* x, int ld, int B, int S, int heads, int dh, void* q_half, void* k_half,
-                                  void* vt_half, void* stream) {
+TK_API int tk_split_qkv_heads_f16(const float* x, const float* bias, int ld, int B, int S, int heads, int dh, void* q_half,
+                                  void* k_half, void* vt_half, void* stream) {
     if (!x || !q_half || !k_half || !vt_half || B <= 0 || S <= 0 || heads <= 0 || dh <= 0 || ld < 3 * heads * dh)
         return TK_ERR_ARGS;
     if (dh % 32 || S % 32 || ld % 4) return TK_ERR_SHAPE;
-    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q_half) | reinterpret_cast<uintptr_t>(k_half)) & 15u)
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q_half) | reinterpret_cast<uintptr_t>(k_half) |
+         reinterpret_cast<uintptr_t>(bias)) & 15u)
         return TK_ERR_ALIGN;
     TK_LAYER_PROLOGUE();
     const long long tiles = static_cast<long long>(B) * heads * (S / 32) * (dh / 32);
     const unsigned nb_qk = blocks_for(2ll * B * heads * S * (dh / 8), d->sm_count);
     if (tiles + nb_qk > 0x7fffffffll) return TK_ERR_SHAPE;
     split_qkv_heads_kernel<<<nb_qk + static_cast<unsigned>(tiles), 256, 0, st>>>(
-        x, ld, B, S, heads, dh, static_cast<__half*>(q_half), static_cast<__half*>(k_half), static_cast<__half*>(vt_half),
-        static_cast<int>(nb_qk));
+        x, bias, ld, B, S, heads, dh, static_cast<__half*>(q_half), static_cast<__half*>(k_half),
+        static_cast<__half*>(vt_half), static_cast<int>(nb_qk));
     return launch_error("split_qkv_heads_kernel launch");
 }
 

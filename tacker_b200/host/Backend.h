@@ -65,14 +65,16 @@ public:
                               float eps, stream_t s) = 0;
     // out = layernorm(a + res): rows of 128 .. 1024 columns (a multiple of 128)
     // (res may be null; out_half, if given, also receives the result as fp16 [rows][cols])
-    virtual int addLayernormRows(const float* a, const float* res, const float* g, const float* b, float* out, void* out_half,
-                                 long long rows, int cols, float eps, stream_t s) = 0;
+    // bias [cols], if given, is added to a first (the bias of the product that made a)
+    virtual int addLayernormRows(const float* a, const float* bias, const float* res, const float* g, const float* b, float* out,
+                                 void* out_half, long long rows, int cols, float eps, stream_t s) = 0;
     // producers that write the fp16 operand of the product that follows (see the library header)
     virtual int biasActHalf(const float* x, int ldx, const float* bias, float* out, int ldo, void* out_half, int ldh, int rows,
                             int cols, int act, stream_t s) = 0;
     virtual int softmaxRowsHalf(const float* x, void* out_half, long long rows, int cols, float scale, stream_t s) = 0;
     virtual int mergeHeadsHalf(const float* ctx, int B, int S, int heads, int dh, void* out_half, stream_t s) = 0;
-    virtual int splitQkv(const float* x, int ld, int B, int S, int heads, int dh, void* q, void* k, void* vt, stream_t s) = 0;
+    virtual int splitQkv(const float* x, const float* bias, int ld, int B, int S, int heads, int dh, void* q, void* k, void* vt,
+                         stream_t s) = 0;
     virtual int splitHeads(const float* x, int ld, int col0, int B, int S, int heads, int dh, int transpose, void* out,
                            stream_t s) = 0;
     virtual int mergeHeads(const float* ctx, int B, int S, int heads, int dh, float* out, stream_t s) = 0;

@@ -142,9 +142,9 @@ public:
                       stream_t s) override {
         return tk_layernorm_rows_f32(x, g, b, out, rows, cols, eps, s);
     }
-    int addLayernormRows(const float* a, const float* res, const float* g, const float* b, float* out, void* out_half,
-                         long long rows, int cols, float eps, stream_t s) override {
-        return tk_add_layernorm_rows_f32(a, res, g, b, out, out_half, rows, cols, eps, s);
+    int addLayernormRows(const float* a, const float* bias, const float* res, const float* g, const float* b, float* out,
+                         void* out_half, long long rows, int cols, float eps, stream_t s) override {
+        return tk_add_layernorm_rows_f32(a, bias, res, g, b, out, out_half, rows, cols, eps, s);
     }
     int biasActHalf(const float* x, int ldx, const float* bias, float* out, int ldo, void* out_half, int ldh, int rows, int cols,
                     int act, stream_t s) override {
@@ -156,8 +156,9 @@ public:
     int mergeHeadsHalf(const float* ctx, int B, int S, int heads, int dh, void* out_half, stream_t s) override {
         return tk_merge_heads_f16(ctx, B, S, heads, dh, out_half, s);
     }
-    int splitQkv(const float* x, int ld, int B, int S, int heads, int dh, void* q, void* k, void* vt, stream_t s) override {
-        return tk_split_qkv_heads_f16(x, ld, B, S, heads, dh, q, k, vt, s);
+    int splitQkv(const float* x, const float* bias, int ld, int B, int S, int heads, int dh, void* q, void* k, void* vt,
+                 stream_t s) override {
+        return tk_split_qkv_heads_f16(x, bias, ld, B, S, heads, dh, q, k, vt, s);
     }
     int splitHeads(const float* x, int ld, int col0, int B, int S, int heads, int dh, int transpose, void* out,
                    stream_t s) override {

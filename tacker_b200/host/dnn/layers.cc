@@ -172,6 +172,7 @@ void GemmKernel::prepare(stream_t stream) {
 }
 
 void OpKernel::executeImpl(stream_t s) {
+    if (absorbed) return;
     Backend& be = backend();
     switch (op) {
         case BiasAct:  // a = x [i0 rows][ld i2], b = bias, out [i0][i1 cols] ld i3, act i4
@@ -189,7 +190,7 @@ void OpKernel::executeImpl(stream_t s) {
             else TK_HOST_CHECK(be.softmaxRows(a, out, static_cast<long long>(i0) * i1, i2, f0, s));
             break;
         case LayerNorm:  // rows i0, cols i1, gamma b, beta c; res: added to a first
-            if (res || hout) TK_HOST_CHECK(be.addLayernormRows(a, res, b, c, out, hout, i0, i1, 1e-12f, s));
+            if (res || hout || bias) TK_HOST_CHECK(be.addLayernormRows(a, bias, res, b, c, out, hout, i0, i1, 1e-12f, s));
             else TK_HOST_CHECK(be.layernormRows(a, b, c, out, i0, i1, 1e-12f, s));
             break;
         case SplitHeads:  // a [B i0 * S i1][ld i2] from col i3, heads i4, dh i5, transpose i6
@@ -200,7 +201,7 @@ void OpKernel::executeImpl(stream_t s) {
             else TK_HOST_CHECK(be.mergeHeads(a, i0, i1, i4, i5, out, s));
             break;
         case SplitQkv:  // a [B i0 * S i1][ld i2] = three projections side by side; heads i4, dh i5 -> hout, hout2, hout3
-            TK_HOST_CHECK(be.splitQkv(a, i2, i0, i1, i4, i5, hout, hout2, hout3, s));
+            TK_HOST_CHECK(be.splitQkv(a, bias, i2, i0, i1, i4, i5, hout, hout2, hout3, s));
             break;
         case BatchedGemm:  // out[batch i3] = f0 * ha [M i0][K i2] * hb [N i1][K i2]^T
             TK_HOST_CHECK(be.tzgemmBatched(ha, hb, out, i0, i1, i2, i3, f0, s));

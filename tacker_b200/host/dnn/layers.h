@@ -119,6 +119,8 @@ public:
     const float* b = nullptr;
     const float* c = nullptr;
     const float* res = nullptr;  // LayerNorm: second operand added to `a` before the normalisation (or null)
+    const float* bias = nullptr; // LayerNorm, SplitQkv: bias of the product whose raw output `a` is (added first), or null
+    bool absorbed = false;       // the node's work is done by its consumer: executing it launches nothing
     float* out = nullptr;
     void* hout = nullptr;   // fp16 output; for BiasAct, SoftmaxRows, LayerNorm, MergeHeads: the operand of the next product
     void* hout2 = nullptr;  // SplitQkv: key heads

@@ -203,11 +203,11 @@ public:
     int add(const float*, const float*, float*, long long, stream_t) override { return op(); }
     int softmaxRows(const float*, float*, long long, int, float, stream_t) override { return op(); }
     int layernormRows(const float*, const float*, const float*, float*, long long, int, float, stream_t) override { return op(); }
-    int addLayernormRows(const float*, const float*, const float*, const float*, float*, void*, long long, int, float, stream_t) override { return op(); }
+    int addLayernormRows(const float*, const float*, const float*, const float*, const float*, float*, void*, long long, int, float, stream_t) override { return op(); }
     int biasActHalf(const float*, int, const float*, float*, int, void*, int, int, int, int, stream_t) override { return op(); }
     int softmaxRowsHalf(const float*, void*, long long, int, float, stream_t) override { return op(); }
     int mergeHeadsHalf(const float*, int, int, int, int, void*, stream_t) override { return op(); }
-    int splitQkv(const float*, int, int, int, int, int, void*, void*, void*, stream_t) override { return op(); }
+    int splitQkv(const float*, const float*, int, int, int, int, int, void*, void*, void*, stream_t) override { return op(); }
     int splitHeads(const float*, int, int, int, int, int, int, int, void*, stream_t) override { return op(); }
     int mergeHeads(const float*, int, int, int, int, float*, stream_t) override { return op(); }
     int tzgemmBatched(const void*, const void*, float*, int, int, int, int, float, stream_t) override { return op(); }

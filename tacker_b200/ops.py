@@ -500,8 +500,8 @@ def layernorm_rows_f32(x, gamma, beta, out, rows, cols, eps=1e-12, stream: int =
                                       C.c_float(eps), _vp(stream)), "tk_layernorm_rows_f32")
 
 
-def add_layernorm_rows_f32(a, b, gamma, beta, out, rows, cols, eps=1e-12, stream: int = 0, out_half=0) -> None:
-    check(lib().tk_add_layernorm_rows_f32(_vp(a), _vp(b), _vp(gamma), _vp(beta), _vp(out), _vp(out_half),
+def add_layernorm_rows_f32(a, b, gamma, beta, out, rows, cols, eps=1e-12, stream: int = 0, out_half=0, bias=0) -> None:
+    check(lib().tk_add_layernorm_rows_f32(_vp(a), _vp(bias), _vp(b), _vp(gamma), _vp(beta), _vp(out), _vp(out_half),
                                           C.c_longlong(rows), cols, C.c_float(eps), _vp(stream)),
           "tk_add_layernorm_rows_f32")
 
@@ -520,8 +520,9 @@ def merge_heads_f16(ctx, B, S, heads, dh, out_half, stream: int = 0) -> None:
     check(lib().tk_merge_heads_f16(_vp(ctx), B, S, heads, dh, _vp(out_half), _vp(stream)), "tk_merge_heads_f16")
 
 
-def split_qkv_heads_f16(x, ld, B, S, heads, dh, q_half, k_half, vt_half, stream: int = 0) -> None:
-    check(lib().tk_split_qkv_heads_f16(_vp(x), ld, B, S, heads, dh, _vp(q_half), _vp(k_half), _vp(vt_half), _vp(stream)),
+def split_qkv_heads_f16(x, ld, B, S, heads, dh, q_half, k_half, vt_half, stream: int = 0, bias=0) -> None:
+    check(lib().tk_split_qkv_heads_f16(_vp(x), _vp(bias), ld, B, S, heads, dh, _vp(q_half), _vp(k_half), _vp(vt_half),
+                                       _vp(stream)),
           "tk_split_qkv_heads_f16")
 
 

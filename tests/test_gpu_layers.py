@@ -149,6 +149,12 @@ def test_producers_that_write_the_next_operand(cuda, oracle):
         v = (x + y if res else x).astype(np.float64)
         ln = (v - v.mean(1, keepdims=True)) / np.sqrt(v.var(1, keepdims=True) + 1e-5) * g + b
         assert np.abs(out.cpu().numpy() - ln).max() < 1e-4
+    # the bias of the product that made `a`, folded in: layernorm((a + bias) + res)
+    ops.add_layernorm_rows_f32(dx.data_ptr(), dy.data_ptr(), dg.data_ptr(), db.data_ptr(), out.data_ptr(), rows, cols, 1e-5,
+                               bias=dg.data_ptr())
+    v = ((x + g) + y).astype(np.float64)
+    ln = (v - v.mean(1, keepdims=True)) / np.sqrt(v.var(1, keepdims=True) + 1e-5) * g + b
+    assert np.abs(out.cpu().numpy() - ln).max() < 1e-4
     ops.bias_act_f32(dx.data_ptr(), cols, db.data_ptr(), out.data_ptr(), rows, cols, cols, 2)
     wide = cuda.zeros((rows, 832), dtype=cuda.float16, device="cuda")
     ops.bias_act_f32_f16(dx.data_ptr(), cols, db.data_ptr(), 0, 0, wide.data_ptr(), 832, rows, cols, 2)
@@ -172,6 +178,15 @@ def test_producers_that_write_the_next_operand(cuda, oracle):
     cuda.cuda.synchronize()
     for part, got in enumerate((q, k, vt)):
         want = qkv[:, part * hidden:(part + 1) * hidden].reshape(B, S, heads, dh).transpose(0, 2, 1, 3)
+        if part == 2:
+            want = want.transpose(0, 1, 3, 2)
+        assert np.array_equal(got.cpu().numpy().reshape(want.shape), want.astype(np.float16))
+    qb = oracle.uniform_f32(3 * hidden, 25, -0.5, 0.5)
+    ops.split_qkv_heads_f16(dq.data_ptr(), 3 * hidden, B, S, heads, dh, q.data_ptr(), k.data_ptr(), vt.data_ptr(),
+                            bias=to_dev(cuda, qb).data_ptr())
+    cuda.cuda.synchronize()
+    for part, got in enumerate((q, k, vt)):
+        want = (qkv + qb)[:, part * hidden:(part + 1) * hidden].reshape(B, S, heads, dh).transpose(0, 2, 1, 3)
         if part == 2:
             want = want.transpose(0, 1, 3, 2)
         assert np.array_equal(got.cpu().numpy().reshape(want.shape), want.astype(np.float16))
